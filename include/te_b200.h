@@ -1,0 +1,197 @@
+/*
+ * te_b200.h -- C ABI of the B200 (sm_100a) FP32 matmul backend for TorchEngine.
+ *
+ * Every entry point is plain C: pointers, sizes, int status codes.  Nothing here
+ * throws, allocates on behalf of the caller in the hot call, or synchronises the
+ * device unless the comment says so.  Device pointers are raw addresses already
+ * offset by the caller, exactly as the reference passes them to its own
+ * launchers (reference src/cuda/elementwise_cuda.h:90 and src/tensor/tensor.h:646-648).
+ *
+ * Matrices are described the way reference src/tensor/tensor.h:623-627
+ * (`cublas_params`) accepts them: every 2-D slice is row-major (last-dim stride 1)
+ * or column-major (second-last-dim stride 1) with an explicit leading dimension
+ * in elements.  Anything else is TE_ERR_UNSUPPORTED_LAYOUT, the C spelling of the
+ * reference's "CUDA matmul only supports row- or column-major 2D slices".
+ */
+#ifndef TE_B200_H
+#define TE_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#if defined(__GNUC__)
+#define TE_API __attribute__((visibility("default")))
+#else
+#define TE_API
+#endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- status codes (0 = ok) ------------------------------------------------ */
+enum {
+    TE_OK = 0,
+    TE_ERR_BAD_ARGUMENT = 1,        /* null pointer, negative size, bad enum          */
+    TE_ERR_UNSUPPORTED_LAYOUT = 2,  /* slice is neither row- nor column-major          */
+    TE_ERR_SHAPE_NDIM = 3,          /* "Matmul requires tensors with at least 2 dimensions" (tensor.h:537) */
+    TE_ERR_SHAPE_INNER = 4,         /* "Inner dimensions must match for matmul"       (tensor.h:547) */
+    TE_ERR_SHAPE_BROADCAST = 5,     /* "Batch dimensions are not broadcastable"       (tensor.h:858) */
+    TE_ERR_WORKSPACE = 6,           /* context workspace too small for this call       */
+    TE_ERR_CUDA = 7,                /* a CUDA runtime / driver call failed             */
+    TE_ERR_DEVICE_TIMEOUT = 8,      /* a bounded device-side wait gave up              */
+    TE_ERR_NO_DEVICE = 9            /* library loaded on a machine without a usable GPU */
+};
+
+enum { TE_ROW_MAJOR = 0, TE_COL_MAJOR = 1 };
+enum { TE_PREC_TF32 = 0, TE_PREC_3XTF32 = 1 };
+enum { TE_EPI_NONE = 0, TE_EPI_BIAS = 1, TE_EPI_BIAS_GELU = 2 };
+enum { TE_SCALE_NONE = 0, TE_SCALE_MUL = 1, TE_SCALE_DIV = 2 };
+
+typedef struct te_b200_ctx te_b200_ctx;   /* one per device; owns the workspace   */
+typedef void* te_stream_t;                /* a cudaStream_t; NULL = legacy default */
+
+/*
+ * One (optionally strided-batched) GEMM:  C[b] = epi( scale( A[b] . B[b] ) ).
+ * A[b] is M x K, B[b] is K x N, C[b] is M x N row-major with leading dim ldc.
+ * Replaces the argument lists of cublasSgemm / cublasSgemmStridedBatched as the
+ * reference issues them (src/tensor/tensor.h:690-698, :756-765) and of
+ * cuda_matmul_double_buffered_cpasync (src/cuda/elementwise_cuda.h:90).
+ *
+ * Batches are indexed on two levels, outer x inner, so that attention operands
+ * viewed as [B,H,T,d] with strides [T*E, d, E, 1] need no copy
+ * (src/nn/multi_head_attention.cpp:19-42).  A stride of 0 broadcasts the operand
+ * (the Linear weight of src/nn/linear.cpp:21 under a 3-D input).
+ */
+typedef struct te_gemm_desc {
+    int64_t M, N, K;
+    const float* a;            /* device */
+    const float* b;            /* device */
+    float*       c;            /* device, fully overwritten (beta = 0) */
+    int64_t lda, ldb, ldc;     /* elements */
+    int32_t a_major, b_major;  /* TE_ROW_MAJOR: (i,j) at i*ld+j;  TE_COL_MAJOR: (i,j) at i+j*ld */
+    int64_t batch_outer, batch_inner;          /* >= 1 each; total = outer*inner */
+    int64_t a_stride_outer, a_stride_inner;    /* elements; 0 = broadcast        */
+    int64_t b_stride_outer, b_stride_inner;
+    int64_t c_stride_outer, c_stride_inner;
+    float   alpha;             /* used when scale_mode != TE_SCALE_NONE */
+    int32_t scale_mode;        /* TE_SCALE_DIV reproduces `S / sqrt(d)` of src/nn/scaledot.cpp:22 */
+    int32_t epilogue;          /* TE_EPI_*; bias has N entries, added per column (src/nn/linear.cpp:22) */
+    const float* bias;         /* device or NULL */
+    float*  preact_out;        /* optional: value before GELU (what GeluBackward needs,
+                                  src/core/grad_fn.cpp:169); same layout as c; NULL to skip */
+    int32_t precision;         /* TE_PREC_* */
+    int32_t reserved;
+} te_gemm_desc;
+
+/* ---- context --------------------------------------------------------------- */
+
+/* Creates the per-device context on `device` and reserves `workspace_bytes` of
+ * device scratch (operand packing for 3xTF32 and for operands TMA cannot address).
+ * Replaces the process-wide lazily created cuBLAS handle of
+ * src/core/cuda_utils.cpp:48-55.  Returns TE_ERR_NO_DEVICE when no GPU is usable. */
+TE_API int te_b200_init(int device, size_t workspace_bytes, te_b200_ctx** out_ctx);
+TE_API int te_b200_destroy(te_b200_ctx* ctx);
+
+/* Scratch bytes a call with this descriptor needs (0 when operands are used in place). */
+TE_API int te_b200_gemm_workspace_size(const te_gemm_desc* d, size_t* out_bytes);
+
+/* Number of kernels of this library launched through `ctx` since creation. */
+TE_API int64_t te_b200_launch_count(const te_b200_ctx* ctx);
+
+/* Human-readable text for the last non-zero status returned on this thread. */
+TE_API const char* te_b200_last_error(void);
+/* Fixed message for a status code; the shape errors repeat the reference's text. */
+TE_API const char* te_b200_status_string(int status);
+
+/* After a stream has been synchronised: returns TE_ERR_DEVICE_TIMEOUT if any kernel
+ * launched through ctx gave up a bounded wait since the last call, else TE_OK. */
+TE_API int te_b200_check_device_status(te_b200_ctx* ctx);
+
+/* ---- GEMM ------------------------------------------------------------------ */
+
+/* Asynchronous on `stream`.  Replaces the body of Tensor::cuda_matmul_impl_f32
+ * (src/tensor/tensor.h:614-793) for one uniformly strided group of batches. */
+TE_API int te_b200_gemm_f32(te_b200_ctx* ctx, const te_gemm_desc* d, te_stream_t stream);
+
+/* N-D matmul with NumPy batch broadcasting over raw shape/stride arrays (strides in
+ * elements), i.e. Tensor::matmul -> matmul_impl<float> -> cuda_matmul_impl_f32
+ * (src/tensor/tensor.cpp:761-785, src/tensor/tensor.h:529-612, :838-906).
+ * `c` is a fresh contiguous [batch..., M, N] buffer.  out_shape (capacity 8) and
+ * out_ndim receive the result shape when non-NULL.  If `c` is NULL only the shape is
+ * computed and validated (no GPU needed). */
+TE_API int te_b200_matmul_nd(te_b200_ctx* ctx,
+                      const float* a, const int64_t* a_shape, const int64_t* a_strides, int a_ndim,
+                      const float* b, const int64_t* b_shape, const int64_t* b_strides, int b_ndim,
+                      float* c, int64_t* out_shape, int* out_ndim,
+                      int precision, te_stream_t stream);
+
+/* Same GEMM with HOST buffers: copies A and B to the device, runs, copies C back and
+ * synchronises.  This is the call a CPU-resident reference Tensor would make
+ * (Tensor::toDevice + matmul + toDevice back, src/tensor/tensor.cpp:308-340). */
+TE_API int te_b200_gemm_f32_host(te_b200_ctx* ctx, const te_gemm_desc* d_host);
+
+/* ---- row operations around the attention GEMMs ----------------------------- */
+
+/* out[r,:] = softmax(in[r,:]) over `cols` contiguous floats, rows*cols dense.
+ * Replaces cuda_softmax_forward (src/cuda/elementwise_cuda.cu:2424-2448, :2469). in may equal out. */
+TE_API int te_b200_softmax_rows_f32(te_b200_ctx* ctx, const float* in, float* out,
+                             int64_t rows, int64_t cols, te_stream_t stream);
+/* dx = s * (dy - sum(dy*s)) per row.  Replaces cuda_softmax_backward (:2450-2467, :2476). */
+TE_API int te_b200_softmax_backward_rows_f32(te_b200_ctx* ctx, const float* s, const float* dy, float* dx,
+                                      int64_t rows, int64_t cols, te_stream_t stream);
+/* y = gelu_tanh(x).  Replaces cuda_gelu (:2701-2707, :2726). */
+TE_API int te_b200_gelu_f32(te_b200_ctx* ctx, const float* x, float* y, int64_t n, te_stream_t stream);
+/* dx = dy * gelu'(x) with x the pre-activation.  Replaces cuda_gelu_backward (:2709-2724, :2732). */
+TE_API int te_b200_gelu_backward_f32(te_b200_ctx* ctx, const float* x, const float* dy, float* dx,
+                              int64_t n, te_stream_t stream);
+/* out[j] = sum_i in[i*ld + j], i < rows, j < cols: the bias gradient that AddBackward obtains
+ * through reduce_gradient -> cuda_sum_dim (src/core/grad_fn.cpp:13-58, :93-102). */
+TE_API int te_b200_colsum_f32(te_b200_ctx* ctx, const float* in, int64_t rows, int64_t cols, int64_t ld,
+                       float* out, te_stream_t stream);
+
+/* ---- fused callers ---------------------------------------------------------- */
+
+/* Y[rows,out] = act(X[rows,in] . W[out,in]^T + bias).  Linear::forward (src/nn/linear.cpp:14-23)
+ * with the bias add, and optionally FeedForward's GELU (src/nn/ffn.cpp:12-16), in the epilogue.
+ * gelu != 0 selects bias+GELU; preact (optional) receives X.W^T+bias. */
+TE_API int te_b200_linear_forward(te_b200_ctx* ctx, const float* x, const float* w, const float* bias,
+                           float* y, float* preact, int64_t rows, int64_t in_features,
+                           int64_t out_features, int gelu, int precision, te_stream_t stream);
+/* dX = dY.W, dW[out,in] = dY^T.X (one GEMM with K = rows, written directly as [out,in]),
+ * db = column sums of dY.  MatMulBackward + AddBackward + TransposeBackward of the Linear graph
+ * (src/core/grad_fn.cpp:93-102, :126-139, :397-403).  Any of dx/dw/db may be NULL. */
+TE_API int te_b200_linear_backward(te_b200_ctx* ctx, const float* x, const float* w, const float* dy,
+                            float* dx, float* dw, float* db, int64_t rows, int64_t in_features,
+                            int64_t out_features, int precision, te_stream_t stream);
+
+/* O = softmax(Q.K^T / sqrt(d)) . V for Q,K,V viewed as [B,H,T,d] with explicit element
+ * strides (last-dim stride must be 1).  ScaledDot::forward (src/nn/scaledot.cpp:8-27).
+ * p_out is a dense [B,H,T,T] buffer that receives the probabilities (SoftmaxBackward and
+ * the backward GEMMs need them); o is dense [B,H,T,d] with strides o_strides. */
+typedef struct te_attn_desc {
+    int64_t B, H, T, d;
+    const float* q; const float* k; const float* v;
+    int64_t q_strides[3];   /* element strides of dims B, H, T (dim d has stride 1) */
+    int64_t k_strides[3];
+    int64_t v_strides[3];
+    float* p_out;           /* [B,H,T,T] dense, required */
+    float* o;               /* output */
+    int64_t o_strides[3];
+    int32_t precision;
+    int32_t reserved;
+} te_attn_desc;
+TE_API int te_b200_attention_forward(te_b200_ctx* ctx, const te_attn_desc* d, te_stream_t stream);
+
+/* ---- sharding helpers (multi-GPU: one process per GPU) ----------------------- */
+
+/* Splits `total` units (N columns, or batch indices) over `world` ranks in blocks that are
+ * multiples of `align` (the last rank takes the ragged tail).  No reference counterpart:
+ * the reference has no multi-device code (README.md:47). */
+TE_API int te_b200_shard_range(int64_t total, int world, int rank, int64_t align,
+                        int64_t* out_begin, int64_t* out_count);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TE_B200_H */

@@ -1,0 +1,304 @@
+"""numpy-facing ctypes bindings of the checkers.  TEST INFRASTRUCTURE ONLY.
+
+`Oracle`    - liboracle.so, the plain-C restatement (te_oracle.c); built by `make -C oracle`.
+`Reference` - _ref/libref_cpu.so, the reference's own CPU path compiled from its sources (ref_driver.cpp).
+              Present only where it was built; it travels as a prebuilt file.
+Only tests/, the smoke check and the benchmark's CPU legs may import this module.
+"""
+import ctypes as C
+import os
+import subprocess
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+ORACLE_PATH = os.path.join(_HERE, "liboracle.so")
+REF_PATH = os.path.join(_HERE, "_ref", "libref_cpu.so")
+
+_f32p = np.ctypeslib.ndpointer(dtype=np.float32, flags="C_CONTIGUOUS")
+
+
+def build(reference_root="/root/reference"):
+    """Runs the Makefile: liboracle.so always, _ref/libref_cpu.so when the reference sources are present."""
+    subprocess.run(["make", "-s", "-C", _HERE, "-j8", "REF=" + reference_root], check=True)
+
+
+def _i64(seq):
+    return (C.c_int64 * max(len(seq), 1))(*[int(s) for s in seq])
+
+
+def _fptr(a):
+    return a.ctypes.data_as(C.c_void_p)
+
+
+class OracleError(RuntimeError):
+    def __init__(self, code, msg):
+        super().__init__(msg)
+        self.code = code
+
+
+_ORACLE_ERR = {3: "Matmul requires tensors with at least 2 dimensions", 4: "Inner dimensions must match for matmul",
+               5: "Batch dimensions are not broadcastable", 1: "bad argument"}
+
+
+class Oracle:
+    def __init__(self):
+        if not os.path.exists(ORACLE_PATH):
+            build()
+        self.lib = C.CDLL(ORACLE_PATH)
+
+    def matmul(self, a, b):
+        """a @ b for float32 numpy arrays of any strides (views allowed), reference CPU summation order."""
+        assert a.dtype == np.float32 and b.dtype == np.float32
+        es = 4
+        a_str = [s // es for s in a.strides]
+        b_str = [s // es for s in b.strides]
+        out_shape = (C.c_int64 * 8)()
+        nd = C.c_int()
+        rc = self.lib.oracle_matmul_nd_f32(None, _i64(a.shape), _i64(a_str), a.ndim, None, _i64(b.shape), _i64(b_str),
+                                           b.ndim, None, out_shape, C.byref(nd))
+        if rc:
+            raise OracleError(rc, _ORACLE_ERR.get(rc, "error"))
+        shape = tuple(out_shape[i] for i in range(nd.value))
+        c = np.empty(shape, dtype=np.float32)
+        rc = self.lib.oracle_matmul_nd_f32(_fptr(a), _i64(a.shape), _i64(a_str), a.ndim, _fptr(b), _i64(b.shape),
+                                           _i64(b_str), b.ndim, _fptr(c), None, None)
+        if rc:
+            raise OracleError(rc, _ORACLE_ERR.get(rc, "error"))
+        return c
+
+    def matmul_2d_threads(self, a, b, threads=None):
+        """Dense 2-D a @ b split by row blocks over host threads; bit-identical to matmul()."""
+        from concurrent.futures import ThreadPoolExecutor
+        M, K = a.shape
+        N = b.shape[1]
+        c = np.empty((M, N), dtype=np.float32)
+        threads = threads or os.cpu_count() or 1
+        a_s = [s // 4 for s in a.strides]
+        b_s = [s // 4 for s in b.strides]
+        fn = self.lib.oracle_matmul_rows_f32
+        fn.restype = None
+
+        def work(r):
+            fn(_fptr(a), C.c_int64(a_s[0]), C.c_int64(a_s[1]), _fptr(b), C.c_int64(b_s[0]), C.c_int64(b_s[1]),
+               _fptr(c), C.c_int64(M), C.c_int64(K), C.c_int64(N), C.c_int64(r[0]), C.c_int64(r[1]))
+        step = max(1, (M + threads * 4 - 1) // (threads * 4))
+        ranges = [(i, min(i + step, M)) for i in range(0, M, step)]
+        with ThreadPoolExecutor(threads) as ex:
+            list(ex.map(work, ranges))
+        return c
+
+    def matmul_f64(self, a, b, rows=None):
+        """Double-accumulated product of selected rows (all rows when None) of dense 2-D a @ b."""
+        from concurrent.futures import ThreadPoolExecutor
+        M, K = a.shape
+        N = b.shape[1]
+        c = np.zeros((M, N), dtype=np.float64)
+        a_s = [s // 4 for s in a.strides]
+        b_s = [s // 4 for s in b.strides]
+        fn = self.lib.oracle_matmul_rows_f64acc
+        fn.restype = None
+        rows = range(M) if rows is None else rows
+
+        def work(r):
+            fn(_fptr(a), C.c_int64(a_s[0]), C.c_int64(a_s[1]), _fptr(b), C.c_int64(b_s[0]), C.c_int64(b_s[1]),
+               _fptr(c), C.c_int64(K), C.c_int64(N), C.c_int64(r), C.c_int64(r + 1))
+        with ThreadPoolExecutor(os.cpu_count() or 1) as ex:
+            list(ex.map(work, rows))
+        return c
+
+    def add_bias(self, y, bias):
+        y = np.ascontiguousarray(y, dtype=np.float32).copy()
+        cols = y.shape[-1]
+        self.lib.oracle_add_bias_f32(_fptr(y), _fptr(np.ascontiguousarray(bias, dtype=np.float32)),
+                                     C.c_int64(y.size // cols), C.c_int64(cols))
+        return y
+
+    def gelu(self, x):
+        x = np.ascontiguousarray(x, dtype=np.float32)
+        y = np.empty_like(x)
+        self.lib.oracle_gelu_f32(_fptr(x), _fptr(y), C.c_int64(x.size))
+        return y
+
+    def gelu_backward(self, x, dy):
+        x = np.ascontiguousarray(x, dtype=np.float32)
+        dy = np.ascontiguousarray(dy, dtype=np.float32)
+        dx = np.empty_like(x)
+        self.lib.oracle_gelu_backward_f32(_fptr(x), _fptr(dy), _fptr(dx), C.c_int64(x.size))
+        return dx
+
+    def softmax(self, x):
+        x = np.ascontiguousarray(x, dtype=np.float32)
+        y = np.empty_like(x)
+        cols = x.shape[-1]
+        self.lib.oracle_softmax_rows_f32(_fptr(x), _fptr(y), C.c_int64(x.size // cols), C.c_int64(cols))
+        return y
+
+    def softmax_backward(self, s, dy):
+        s = np.ascontiguousarray(s, dtype=np.float32)
+        dy = np.ascontiguousarray(dy, dtype=np.float32)
+        dx = np.empty_like(s)
+        cols = s.shape[-1]
+        self.lib.oracle_softmax_backward_rows_f32(_fptr(s), _fptr(dy), _fptr(dx), C.c_int64(s.size // cols),
+                                                  C.c_int64(cols))
+        return dx
+
+    def colsum(self, x2d):
+        x2d = np.ascontiguousarray(x2d, dtype=np.float32)
+        out = np.empty(x2d.shape[1], dtype=np.float32)
+        self.lib.oracle_colsum_f32(_fptr(x2d), C.c_int64(x2d.shape[0]), C.c_int64(x2d.shape[1]),
+                                   C.c_int64(x2d.shape[1]), _fptr(out))
+        return out
+
+    # Compositions that follow the reference call sequence.
+    def linear(self, x, w, bias, gelu=False):
+        """Linear::forward (+ Tensor::gelu): x . w^T through the transposed view, then the broadcast bias add."""
+        pre = self.add_bias(self.matmul(x, w.T), bias)
+        return (self.gelu(pre), pre) if gelu else (pre, pre)
+
+    def scaled_dot(self, q, k, v):
+        """ScaledDot::forward: S = q . k^T; S / sqrt(d); softmax; . v.  Returns (o, p)."""
+        s = self.matmul(q, np.swapaxes(k, -1, -2))
+        s = (s / np.float32(np.sqrt(np.float32(q.shape[-1])))).astype(np.float32)
+        p = self.softmax(s)
+        return self.matmul(p, v), p
+
+
+class RefView(C.Structure):
+    _fields_ = [("ndim", C.c_int32), ("shape", C.c_int64 * 8), ("view_ndim", C.c_int32), ("view_shape", C.c_int64 * 8),
+                ("t1", C.c_int32), ("t2", C.c_int32)]
+
+
+def ref_view(shape, view=None, transpose=None):
+    v = RefView()
+    v.ndim = len(shape)
+    for i, s in enumerate(shape):
+        v.shape[i] = s
+    v.view_ndim = len(view) if view else 0
+    for i, s in enumerate(view or ()):
+        v.view_shape[i] = s
+    v.t1, v.t2 = transpose if transpose else (-1, -1)
+    return v
+
+
+class Reference:
+    """The reference's own CPU implementation behind ref_driver.cpp."""
+
+    @staticmethod
+    def available():
+        return os.path.exists(REF_PATH)
+
+    def __init__(self):
+        if not os.path.exists(REF_PATH):
+            raise RuntimeError("reference CPU library not built (needs the reference sources): " + REF_PATH)
+        self.lib = C.CDLL(REF_PATH)
+        self.lib.ref_last_error.restype = C.c_char_p
+
+    def _check(self, rc):
+        if rc:
+            raise RuntimeError(self.lib.ref_last_error().decode())
+
+    def view_strides(self, view):
+        shape, strides, nd = (C.c_int64 * 8)(), (C.c_int64 * 8)(), C.c_int32()
+        self._check(self.lib.ref_view_strides(C.byref(view), shape, strides, C.byref(nd)))
+        return tuple(shape[i] for i in range(nd.value)), tuple(strides[i] for i in range(nd.value))
+
+    def matmul(self, a, va, b, vb):
+        """a, b: dense base arrays; va, vb: recipes (ref_view).  Raises RuntimeError with the reference's text."""
+        a = np.ascontiguousarray(a, dtype=np.float32)
+        b = np.ascontiguousarray(b, dtype=np.float32)
+        shape, nd = (C.c_int64 * 8)(), C.c_int32()
+        self._check(self.lib.ref_matmul(_fptr(a), C.byref(va), _fptr(b), C.byref(vb), None, shape, C.byref(nd)))
+        out = np.empty(tuple(shape[i] for i in range(nd.value)), dtype=np.float32)
+        self._check(self.lib.ref_matmul(_fptr(a), C.byref(va), _fptr(b), C.byref(vb), _fptr(out), None, None))
+        return out
+
+    def matmul_i32(self, a, b):
+        a = np.ascontiguousarray(a, dtype=np.int32)
+        b = np.ascontiguousarray(b, dtype=np.int32)
+        out = np.empty((a.shape[0], b.shape[1]), dtype=np.int32)
+        self._check(self.lib.ref_matmul_i32(_fptr(a), _fptr(b), _fptr(out), C.c_int64(a.shape[0]),
+                                            C.c_int64(a.shape[1]), C.c_int64(b.shape[1])))
+        return out
+
+    def linear(self, x, w, bias, gelu=False, dy=None):
+        x = np.ascontiguousarray(x, dtype=np.float32)
+        w = np.ascontiguousarray(w, dtype=np.float32)
+        bias = np.ascontiguousarray(bias, dtype=np.float32)
+        out_f, in_f = w.shape
+        y = np.empty(x.shape[:-1] + (out_f,), dtype=np.float32)
+        pre = np.empty_like(y)
+        res = {"y": y, "preact": pre}
+        if dy is not None:
+            dy = np.ascontiguousarray(dy, dtype=np.float32)
+            res.update(dx=np.empty_like(x), dw=np.empty_like(w), db=np.empty_like(bias))
+        p = lambda k: _fptr(res[k]) if k in res else None
+        self._check(self.lib.ref_linear(_fptr(x), _i64(x.shape), x.ndim, _fptr(w), _fptr(bias), C.c_int64(in_f),
+                                        C.c_int64(out_f), int(gelu), _fptr(dy) if dy is not None else None,
+                                        p("y"), p("preact"), p("dx"), p("dw"), p("db")))
+        return res
+
+    def ffn(self, x, w1, b1, w2, b2, dy=None):
+        arrs = [np.ascontiguousarray(t, dtype=np.float32) for t in (x, w1, b1, w2, b2)]
+        x, w1, b1, w2, b2 = arrs
+        ff, embed = w1.shape
+        res = {"y": np.empty_like(x)}
+        if dy is not None:
+            dy = np.ascontiguousarray(dy, dtype=np.float32)
+            res.update(dx=np.empty_like(x), dw1=np.empty_like(w1), db1=np.empty_like(b1), dw2=np.empty_like(w2),
+                       db2=np.empty_like(b2))
+        p = lambda k: _fptr(res[k]) if k in res else None
+        self._check(self.lib.ref_ffn(_fptr(x), _i64(x.shape), x.ndim, C.c_int64(embed), C.c_int64(ff), _fptr(w1),
+                                     _fptr(b1), _fptr(w2), _fptr(b2), _fptr(dy) if dy is not None else None, p("y"),
+                                     p("dx"), p("dw1"), p("db1"), p("dw2"), p("db2")))
+        return res
+
+    def scaled_dot(self, q, vq, k, vk, v, vv, out_shape, d_o=None):
+        q, k, v = [np.ascontiguousarray(t, dtype=np.float32) for t in (q, k, v)]
+        res = {"o": np.empty(out_shape, dtype=np.float32)}
+        if d_o is not None:
+            d_o = np.ascontiguousarray(d_o, dtype=np.float32)
+            res.update(dq=np.empty_like(q), dk=np.empty_like(k), dv=np.empty_like(v))
+        p = lambda n: _fptr(res[n]) if n in res else None
+        self._check(self.lib.ref_scaled_dot(_fptr(q), C.byref(vq), _fptr(k), C.byref(vk), _fptr(v), C.byref(vv),
+                                            _fptr(d_o) if d_o is not None else None, p("o"), p("dq"), p("dk"), p("dv")))
+        return res
+
+    def mha(self, x, params, H, dy=None):
+        x = np.ascontiguousarray(x, dtype=np.float32)
+        params = [np.ascontiguousarray(t, dtype=np.float32) for t in params]
+        B, T, E = x.shape
+        res = {"y": np.empty_like(x)}
+        pp = (C.c_void_p * 8)(*[t.ctypes.data for t in params])
+        dpp = None
+        if dy is not None:
+            dy = np.ascontiguousarray(dy, dtype=np.float32)
+            res["dx"] = np.empty_like(x)
+            res["dparams"] = [np.empty_like(t) for t in params]
+            dpp = (C.c_void_p * 8)(*[t.ctypes.data for t in res["dparams"]])
+        self._check(self.lib.ref_mha(_fptr(x), C.c_int64(B), C.c_int64(T), C.c_int64(E), C.c_int64(H), pp,
+                                     _fptr(dy) if dy is not None else None, _fptr(res["y"]),
+                                     _fptr(res["dx"]) if dy is not None else None, dpp))
+        return res
+
+    def gpt_param_layout(self, vocab, max_seq, E, H, Lyr, ff):
+        n = C.c_int64()
+        sizes, ranks = (C.c_int64 * 256)(), (C.c_int64 * 256)()
+        self._check(self.lib.ref_gpt_param_count(C.c_int64(vocab), C.c_int64(max_seq), C.c_int64(E), C.c_int64(H),
+                                                 C.c_int64(Lyr), C.c_int64(ff), C.byref(n), sizes, ranks))
+        return [(sizes[i], ranks[i]) for i in range(n.value)]
+
+    def gpt_step(self, vocab, max_seq, E, H, Lyr, ff, flat_params, tokens, targets, want_grads=True, want_logits=False):
+        flat_params = np.ascontiguousarray(flat_params, dtype=np.float32)
+        tokens = np.ascontiguousarray(tokens, dtype=np.int64)
+        targets = np.ascontiguousarray(targets, dtype=np.int64)
+        batch, seq = tokens.shape
+        loss = C.c_float()
+        grads = np.empty_like(flat_params) if want_grads else None
+        logits = np.empty((batch, seq, vocab), dtype=np.float32) if want_logits else None
+        self._check(self.lib.ref_gpt_step(C.c_int64(vocab), C.c_int64(max_seq), C.c_int64(E), C.c_int64(H),
+                                          C.c_int64(Lyr), C.c_int64(ff), C.c_int64(batch), C.c_int64(seq),
+                                          _fptr(flat_params), _fptr(tokens), _fptr(targets), C.byref(loss),
+                                          _fptr(logits) if want_logits else None,
+                                          _fptr(grads) if want_grads else None))
+        return loss.value, logits, grads

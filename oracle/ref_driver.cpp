@@ -1,0 +1,250 @@
+// ref_driver.cpp -- C entry points over the UNMODIFIED reference (compiled from its sources where they
+// lie; see Makefile).  TEST INFRASTRUCTURE ONLY: it pins the C restatement in te_oracle.c, generates
+// the golden fixtures under tests/golden/, and serves as the timed CPU reference in the benchmark.
+// Everything here goes through the reference's public API: Tensor, transpose_view/view, matmul,
+// Linear, FeedForward, ScaledDot, MultiHeadAttention, GPT, crossEntropyLoss, backward().
+#include <cstdint>
+#include <cstring>
+#include <random>
+#include <stdexcept>
+#include <string>
+#include <vector>
+
+#include "tensor/tensor.h"
+#include "nn/linear.h"
+#include "nn/ffn.h"
+#include "nn/scaledot.h"
+#include "nn/multi_head_attention.h"
+#include "nn/gpt.h"
+#include "loss/CrossEntropyLoss.h"
+
+#define REF_API extern "C" __attribute__((visibility("default")))
+
+namespace {
+
+thread_local std::string g_err;
+
+// An operand recipe: contiguous base tensor -> optional view(new shape) -> optional transpose_view(t1, t2).
+struct RefView {
+    int32_t ndim;
+    int64_t shape[8];
+    int32_t view_ndim;      // 0 = no view
+    int64_t view_shape[8];
+    int32_t t1, t2;         // -1 = no transpose
+};
+
+Tensor from_host(const float* data, const std::vector<int64_t>& shape) {
+    Tensor t(shape, DType::Float32, Device::CPU);
+    std::memcpy(t.data(), data, t.numel() * sizeof(float));
+    return t;
+}
+
+Tensor build(const float* data, const RefView& v) {
+    Tensor t = from_host(data, std::vector<int64_t>(v.shape, v.shape + v.ndim));
+    if (v.view_ndim > 0) t = t.view(std::vector<int64_t>(v.view_shape, v.view_shape + v.view_ndim));
+    if (v.t1 >= 0) t = t.transpose_view((size_t)v.t1, (size_t)v.t2);
+    return t;
+}
+
+void copy_out(const Tensor& t, float* dst) {
+    Tensor c = t.contiguous();
+    std::memcpy(dst, c.data(), c.numel() * sizeof(float));
+}
+
+void copy_grad(const Tensor& leaf, float* dst) {
+    if (!dst) return;
+    auto g = leaf.grad();
+    if (!g) throw std::runtime_error("leaf has no gradient");
+    copy_out(*g, dst);
+}
+
+// Backpropagates an arbitrary upstream gradient: (y * dY).backward() seeds ones, so y receives dY.
+void backward_with(const Tensor& y, const float* dy) {
+    Tensor w = from_host(dy, y.shape());
+    Tensor z = y * w;
+    z.backward();
+}
+
+template <typename F>
+int guarded(F&& f) {
+    try {
+        f();
+        return 0;
+    } catch (const std::exception& e) {
+        g_err = e.what();
+        return 1;
+    }
+}
+
+}  // namespace
+
+REF_API const char* ref_last_error() { return g_err.c_str(); }
+
+// Tensor::matmul on the reference CPU path.  out may be NULL to query the shape / the thrown message only.
+REF_API int ref_matmul(const float* a, const RefView* va, const float* b, const RefView* vb, float* out,
+                       int64_t* out_shape, int32_t* out_ndim) {
+    return guarded([&] {
+        Tensor A = build(a, *va), B = build(b, *vb);
+        Tensor C = A.matmul(B);
+        if (out_ndim) *out_ndim = (int32_t)C.shape().size();
+        if (out_shape) for (size_t i = 0; i < C.shape().size(); ++i) out_shape[i] = C.shape()[i];
+        if (out) copy_out(C, out);
+    });
+}
+
+// Strides the reference gives an operand built from the recipe (to feed the same view to the CUDA backend).
+REF_API int ref_view_strides(const RefView* v, int64_t* shape, int64_t* strides, int32_t* ndim) {
+    return guarded([&] {
+        int64_t n = 1;
+        for (int i = 0; i < v->ndim; ++i) n *= v->shape[i];
+        std::vector<float> zeros((size_t)n, 0.0f);
+        Tensor t = build(zeros.data(), *v);
+        *ndim = (int32_t)t.shape().size();
+        for (size_t i = 0; i < t.shape().size(); ++i) { shape[i] = t.shape()[i]; strides[i] = t.strides()[i]; }
+    });
+}
+
+// Int32 matmul (tensor_test.cpp:571-595 pins it); 2-D only.
+REF_API int ref_matmul_i32(const int32_t* a, const int32_t* b, int32_t* out, int64_t M, int64_t K, int64_t N) {
+    return guarded([&] {
+        Tensor A({M, K}, DType::Int32, Device::CPU), B({K, N}, DType::Int32, Device::CPU);
+        std::memcpy(A.data(), a, sizeof(int32_t) * M * K);
+        std::memcpy(B.data(), b, sizeof(int32_t) * K * N);
+        Tensor C = A.matmul(B);
+        std::memcpy(out, C.data(), sizeof(int32_t) * M * N);
+    });
+}
+
+// Linear (optionally followed by gelu, as FeedForward's first half does) forward + backward.
+// x: [x_shape...] with last dim = in; w: [out,in]; bias: [out].  dy NULL -> forward only.
+REF_API int ref_linear(const float* x, const int64_t* x_shape, int32_t x_ndim, const float* w, const float* bias,
+                       int64_t in_f, int64_t out_f, int32_t gelu, const float* dy, float* y, float* preact,
+                       float* dx, float* dw, float* db) {
+    return guarded([&] {
+        Linear lin(in_f, out_f, DType::Float32);
+        auto params = lin.parameters();
+        std::memcpy(params[0].data(), w, sizeof(float) * in_f * out_f);
+        std::memcpy(params[1].data(), bias, sizeof(float) * out_f);
+        Tensor X = from_host(x, std::vector<int64_t>(x_shape, x_shape + x_ndim));
+        X.setRequiresGrad(true);
+        Tensor pre = lin.forward(X);
+        if (preact) copy_out(pre, preact);
+        Tensor Y = gelu ? pre.gelu() : pre;
+        if (y) copy_out(Y, y);
+        if (dy) {
+            backward_with(Y, dy);
+            copy_grad(X, dx);
+            copy_grad(params[0], dw);
+            copy_grad(params[1], db);
+        }
+    });
+}
+
+// FeedForward::forward (Linear -> GELU -> Linear) + backward.  Parameter order: w1,b1,w2,b2.
+REF_API int ref_ffn(const float* x, const int64_t* x_shape, int32_t x_ndim, int64_t embed, int64_t ff,
+                    const float* w1, const float* b1, const float* w2, const float* b2, const float* dy, float* y,
+                    float* dx, float* dw1, float* db1, float* dw2, float* db2) {
+    return guarded([&] {
+        FeedForward ffn(embed, ff, DType::Float32);
+        auto p = ffn.parameters();
+        std::memcpy(p[0].data(), w1, sizeof(float) * embed * ff);
+        std::memcpy(p[1].data(), b1, sizeof(float) * ff);
+        std::memcpy(p[2].data(), w2, sizeof(float) * embed * ff);
+        std::memcpy(p[3].data(), b2, sizeof(float) * embed);
+        Tensor X = from_host(x, std::vector<int64_t>(x_shape, x_shape + x_ndim));
+        X.setRequiresGrad(true);
+        Tensor Y = ffn.forward(X);
+        if (y) copy_out(Y, y);
+        if (dy) {
+            backward_with(Y, dy);
+            copy_grad(X, dx);
+            copy_grad(p[0], dw1); copy_grad(p[1], db1); copy_grad(p[2], dw2); copy_grad(p[3], db2);
+        }
+    });
+}
+
+// ScaledDot::forward.  Operands given by recipe so that both contiguous [B,H,T,d] tensors and the
+// MultiHeadAttention views ([B,T,E] -> view [B,T,H,hd] -> transpose_view(1,2)) can be exercised.
+REF_API int ref_scaled_dot(const float* q, const RefView* vq, const float* k, const RefView* vk, const float* v,
+                           const RefView* vv, const float* d_o, float* o, float* dq, float* dk, float* dv) {
+    return guarded([&] {
+        Tensor Qb = from_host(q, std::vector<int64_t>(vq->shape, vq->shape + vq->ndim));
+        Tensor Kb = from_host(k, std::vector<int64_t>(vk->shape, vk->shape + vk->ndim));
+        Tensor Vb = from_host(v, std::vector<int64_t>(vv->shape, vv->shape + vv->ndim));
+        Qb.setRequiresGrad(true); Kb.setRequiresGrad(true); Vb.setRequiresGrad(true);
+        auto apply = [](Tensor t, const RefView& r) {
+            if (r.view_ndim > 0) t = t.view(std::vector<int64_t>(r.view_shape, r.view_shape + r.view_ndim));
+            if (r.t1 >= 0) t = t.transpose_view((size_t)r.t1, (size_t)r.t2);
+            return t;
+        };
+        ScaledDot att;
+        Tensor O = att.forward(apply(Qb, *vq), apply(Kb, *vk), apply(Vb, *vv));
+        if (o) copy_out(O, o);
+        if (d_o) {
+            backward_with(O, d_o);
+            copy_grad(Qb, dq); copy_grad(Kb, dk); copy_grad(Vb, dv);
+        }
+    });
+}
+
+// MultiHeadAttention::forward + backward.  Parameter order: wq,bq,wk,bk,wv,bv,wo,bo, each w [E,E].
+REF_API int ref_mha(const float* x, int64_t B, int64_t T, int64_t E, int64_t H, const float* const* params,
+                    const float* dy, float* y, float* dx, float* const* dparams) {
+    return guarded([&] {
+        MultiHeadAttention mha(E, H, DType::Float32);
+        auto p = mha.parameters();
+        for (size_t i = 0; i < p.size(); ++i) std::memcpy(p[i].data(), params[i], p[i].numel() * sizeof(float));
+        Tensor X = from_host(x, {B, T, E});
+        X.setRequiresGrad(true);
+        Tensor Y = mha.forward(X);
+        if (y) copy_out(Y, y);
+        if (dy) {
+            backward_with(Y, dy);
+            copy_grad(X, dx);
+            if (dparams) for (size_t i = 0; i < p.size(); ++i) copy_grad(p[i], dparams[i]);
+        }
+    });
+}
+
+// One GPT training step's forward + backward (src/benchmarks/gpt_benchmark_gpu.cpp:230-236 without the
+// optimizer).  Parameters are taken in GPT::parameters() order from one flat buffer; grads come back the same way.
+REF_API int ref_gpt_param_count(int64_t vocab, int64_t max_seq, int64_t E, int64_t H, int64_t L, int64_t ff,
+                                int64_t* n_tensors, int64_t* sizes /* capacity 256 */, int64_t* ranks) {
+    return guarded([&] {
+        GPT model(vocab, max_seq, E, H, L, ff, DType::Float32, 0.0f);
+        auto p = model.parameters();
+        *n_tensors = (int64_t)p.size();
+        for (size_t i = 0; i < p.size() && i < 256; ++i) { sizes[i] = (int64_t)p[i].numel(); ranks[i] = (int64_t)p[i].shape().size(); }
+    });
+}
+
+REF_API int ref_gpt_step(int64_t vocab, int64_t max_seq, int64_t E, int64_t H, int64_t L, int64_t ff, int64_t batch,
+                         int64_t seq, const float* flat_params, const int64_t* tokens, const int64_t* targets,
+                         float* loss_out, float* logits_out, float* flat_grads) {
+    return guarded([&] {
+        GPT model(vocab, max_seq, E, H, L, ff, DType::Float32, 0.0f);
+        auto p = model.parameters();
+        size_t off = 0;
+        for (auto& t : p) {
+            std::memcpy(t.data(), flat_params + off, t.numel() * sizeof(float));
+            off += t.numel();
+        }
+        Tensor tok({batch, seq}, DType::Int64, Device::CPU), tgt({batch, seq}, DType::Int64, Device::CPU);
+        std::memcpy(tok.data(), tokens, sizeof(int64_t) * batch * seq);
+        std::memcpy(tgt.data(), targets, sizeof(int64_t) * batch * seq);
+        model.zero_grad();
+        Tensor logits = model.forward(tok);
+        if (logits_out) copy_out(logits, logits_out);
+        crossEntropyLoss ce;
+        Tensor loss = ce.forward_batched(logits, tgt);
+        *loss_out = static_cast<float*>(loss.data())[0];
+        if (flat_grads) {
+            loss.backward();
+            off = 0;
+            for (auto& t : p) {
+                copy_grad(t, flat_grads + off);
+                off += t.numel();
+            }
+        }
+    });
+}

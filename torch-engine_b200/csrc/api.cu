@@ -1,0 +1,554 @@
+// C-ABI layer: argument validation, the per-device context, and the host-side dispatch that the
+// reference performs inside Tensor::matmul / matmul_impl / cuda_matmul_impl_f32
+// (reference src/tensor/tensor.cpp:761-785, src/tensor/tensor.h:529-612, :614-793, :838-906):
+// shape checks, NumPy batch broadcasting, per-slice row/column-major detection, batching.
+// There is no CPU compute path here: without a usable sm_100 GPU every compute entry fails.
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <math.h>
+#include <stdint.h>
+#include <stdio.h>
+#include <string.h>
+
+#include <string>
+#include <vector>
+
+#include "te_internal.h"
+
+namespace te {
+
+static thread_local std::string g_last_error;
+
+void set_error(const std::string& msg) { g_last_error = msg; }
+
+int cuda_fail(cudaError_t e, const char* what) {
+    g_last_error = std::string(what) + ": " + cudaGetErrorString(e);
+    return TE_ERR_CUDA;
+}
+
+static int fail(int code, const std::string& msg) {
+    g_last_error = msg;
+    return code;
+}
+
+static inline int64_t round_up(int64_t x, int64_t a) { return (x + a - 1) / a * a; }
+
+// Device scratch carved out of the context workspace, 256-byte granules.
+struct Carver {
+    char* base;
+    size_t cap, used = 0;
+    Carver(void* b, size_t c) : base(static_cast<char*>(b)), cap(c) {}
+    float* take(int64_t bytes) {
+        const size_t need = (size_t)round_up(bytes, 256);
+        if (used + need > cap) return nullptr;
+        float* p = reinterpret_cast<float*>(base + used);
+        used += need;
+        return p;
+    }
+};
+
+static int64_t packed_batches(const Operand& op, int64_t bi, int64_t bo) {
+    const int64_t i = (bi > 1 && op.stride_inner != 0) ? bi : 1;
+    const int64_t o = (bo > 1 && op.stride_outer != 0) ? bo : 1;
+    return i * o;
+}
+static int64_t plane_bytes(const Operand& op, int64_t K, int64_t bi, int64_t bo) {
+    return round_up(packed_batches(op, bi, bo) * op.rows * round_up(K, 4) * 4, 256);
+}
+
+static int validate_desc(const te_gemm_desc* d) {
+    if (!d) return fail(TE_ERR_BAD_ARGUMENT, "gemm descriptor is NULL");
+    if (d->M < 0 || d->N < 0 || d->K < 0) return fail(TE_ERR_BAD_ARGUMENT, "negative GEMM extent");
+    if (d->M > INT32_MAX || d->N > INT32_MAX || d->K > INT32_MAX)
+        return fail(TE_ERR_BAD_ARGUMENT, "GEMM extent exceeds 2^31-1");
+    if (d->batch_outer < 1 || d->batch_inner < 1) return fail(TE_ERR_BAD_ARGUMENT, "batch counts must be >= 1");
+    if (d->batch_outer * d->batch_inner > INT32_MAX) return fail(TE_ERR_BAD_ARGUMENT, "too many batches");
+    if ((d->a_major != TE_ROW_MAJOR && d->a_major != TE_COL_MAJOR) ||
+        (d->b_major != TE_ROW_MAJOR && d->b_major != TE_COL_MAJOR))
+        return fail(TE_ERR_UNSUPPORTED_LAYOUT, te_b200_status_string(TE_ERR_UNSUPPORTED_LAYOUT));
+    if (d->precision != TE_PREC_TF32 && d->precision != TE_PREC_3XTF32)
+        return fail(TE_ERR_BAD_ARGUMENT, "precision must be TE_PREC_TF32 or TE_PREC_3XTF32");
+    if (d->epilogue < TE_EPI_NONE || d->epilogue > TE_EPI_BIAS_GELU) return fail(TE_ERR_BAD_ARGUMENT, "bad epilogue");
+    if (d->scale_mode < TE_SCALE_NONE || d->scale_mode > TE_SCALE_DIV) return fail(TE_ERR_BAD_ARGUMENT, "bad scale_mode");
+    if (d->epilogue == TE_EPI_BIAS && !d->bias) return fail(TE_ERR_BAD_ARGUMENT, "TE_EPI_BIAS needs a bias pointer");
+    if (d->M == 0 || d->N == 0) return TE_OK;
+    if (!d->c) return fail(TE_ERR_BAD_ARGUMENT, "C pointer is NULL");
+    if (d->K > 0 && (!d->a || !d->b)) return fail(TE_ERR_BAD_ARGUMENT, "A or B pointer is NULL");
+    // leading dimensions must cover the contiguous extent of a slice
+    const int64_t a_need = d->a_major == TE_ROW_MAJOR ? d->K : d->M;
+    const int64_t a_rows = d->a_major == TE_ROW_MAJOR ? d->M : d->K;
+    const int64_t b_need = d->b_major == TE_ROW_MAJOR ? d->N : d->K;
+    const int64_t b_rows = d->b_major == TE_ROW_MAJOR ? d->K : d->N;
+    if (d->K > 0 && ((a_rows > 1 && d->lda < a_need) || (b_rows > 1 && d->ldb < b_need)))
+        return fail(TE_ERR_UNSUPPORTED_LAYOUT, "leading dimension smaller than the slice's contiguous extent");
+    if (d->M > 1 && d->ldc < d->N) return fail(TE_ERR_UNSUPPORTED_LAYOUT, "ldc smaller than N");
+    if (d->a_stride_outer < 0 || d->a_stride_inner < 0 || d->b_stride_outer < 0 || d->b_stride_inner < 0 ||
+        d->c_stride_outer < 0 || d->c_stride_inner < 0)
+        return fail(TE_ERR_BAD_ARGUMENT, "negative batch stride");
+    return TE_OK;
+}
+
+static void operands_from_desc(const te_gemm_desc* d, Operand& a, Operand& b) {
+    a.ptr = d->a; a.mn_major = (d->a_major == TE_COL_MAJOR); a.rows = d->M; a.ld = d->lda;
+    a.stride_inner = d->a_stride_inner; a.stride_outer = d->a_stride_outer;
+    b.ptr = d->b; b.mn_major = (d->b_major == TE_ROW_MAJOR); b.rows = d->N; b.ld = d->ldb;
+    b.stride_inner = d->b_stride_inner; b.stride_outer = d->b_stride_outer;
+    // A single row/column slice may legally carry any ld; give TMA a valid one.
+    if (a.ld < 4) a.ld = 4;
+    if (b.ld < 4) b.ld = 4;
+}
+
+static size_t workspace_need(const te_gemm_desc* d) {
+    if (d->M == 0 || d->N == 0 || d->K == 0) return 0;
+    Operand a, b;
+    operands_from_desc(d, a, b);
+    size_t need = 0;
+    if (d->precision == TE_PREC_3XTF32) {
+        need += 2 * (size_t)plane_bytes(a, d->K, d->batch_inner, d->batch_outer);
+        need += 2 * (size_t)plane_bytes(b, d->K, d->batch_inner, d->batch_outer);
+    } else {
+        if (!operand_tma_ok(a, d->batch_inner, d->batch_outer))
+            need += (size_t)plane_bytes(a, d->K, d->batch_inner, d->batch_outer);
+        if (!operand_tma_ok(b, d->batch_inner, d->batch_outer))
+            need += (size_t)plane_bytes(b, d->K, d->batch_inner, d->batch_outer);
+    }
+    return need;
+}
+
+// Replaces `op` by its packed K-major form living in workspace.
+static int pack_into(te_b200_ctx* ctx, Carver& ws, Operand& op, const float** lo_out, int64_t K, int64_t bi,
+                     int64_t bo, bool split, cudaStream_t st) {
+    const int64_t bytes = plane_bytes(op, K, bi, bo);
+    float* hi = ws.take(bytes);
+    float* lo = split ? ws.take(bytes) : nullptr;
+    if (!hi || (split && !lo)) {
+        char msg[160];
+        snprintf(msg, sizeof msg, "context workspace (%zu bytes) too small; this call needs more scratch", ws.cap);
+        return fail(TE_ERR_WORKSPACE, msg);
+    }
+    int rc = launch_pack(ctx, op, K, bi, bo, hi, lo, split, st);
+    if (rc) return rc;
+    const int64_t kp = round_up(K, 4);
+    const int64_t inner_n = (bi > 1 && op.stride_inner != 0) ? bi : 1;
+    Operand packed;
+    packed.ptr = hi;
+    packed.mn_major = false;
+    packed.rows = op.rows;
+    packed.ld = kp;
+    packed.stride_inner = (bi > 1 && op.stride_inner != 0) ? op.rows * kp : 0;
+    packed.stride_outer = (bo > 1 && op.stride_outer != 0) ? inner_n * op.rows * kp : 0;
+    op = packed;
+    if (lo_out) *lo_out = lo;
+    return TE_OK;
+}
+
+static int gemm_device(te_b200_ctx* ctx, const te_gemm_desc* d, cudaStream_t st) {
+    int rc = validate_desc(d);
+    if (rc) return rc;
+    if (d->M == 0 || d->N == 0) return TE_OK;
+    GemmProblem g;
+    g.M = d->M; g.N = d->N; g.K = d->K;
+    g.batch_inner = d->batch_inner; g.batch_outer = d->batch_outer;
+    operands_from_desc(d, g.a, g.b);
+    g.c = d->c; g.ldc = d->ldc; g.c_stride_inner = d->c_stride_inner; g.c_stride_outer = d->c_stride_outer;
+    g.preact = d->preact_out; g.bias = d->bias; g.alpha = d->alpha; g.scale_mode = d->scale_mode;
+    g.epilogue = d->epilogue;
+    Carver ws(ctx->workspace, ctx->workspace_bytes);
+    if (d->K > 0) {
+        if (d->precision == TE_PREC_3XTF32) {
+            if ((rc = pack_into(ctx, ws, g.a, &g.a_lo, d->K, d->batch_inner, d->batch_outer, true, st))) return rc;
+            if ((rc = pack_into(ctx, ws, g.b, &g.b_lo, d->K, d->batch_inner, d->batch_outer, true, st))) return rc;
+        } else {
+            if (!operand_tma_ok(g.a, d->batch_inner, d->batch_outer))
+                if ((rc = pack_into(ctx, ws, g.a, nullptr, d->K, d->batch_inner, d->batch_outer, false, st))) return rc;
+            if (!operand_tma_ok(g.b, d->batch_inner, d->batch_outer))
+                if ((rc = pack_into(ctx, ws, g.b, nullptr, d->K, d->batch_inner, d->batch_outer, false, st))) return rc;
+        }
+    } else {
+        // K == 0: the kernel issues no loads; give the tensor maps a valid dummy base.
+        g.a.ptr = g.b.ptr = reinterpret_cast<const float*>(ctx->workspace);
+        g.a.mn_major = g.b.mn_major = false;
+        g.a.ld = g.b.ld = 4;
+        g.a.stride_inner = g.a.stride_outer = g.b.stride_inner = g.b.stride_outer = 0;
+    }
+    return launch_gemm(ctx, g, st);
+}
+
+}  // namespace te
+
+using namespace te;
+
+extern "C" {
+
+const char* te_b200_status_string(int status) {
+    switch (status) {
+        case TE_OK: return "ok";
+        case TE_ERR_BAD_ARGUMENT: return "bad argument";
+        case TE_ERR_UNSUPPORTED_LAYOUT: return "CUDA matmul only supports row- or column-major 2D slices";
+        case TE_ERR_SHAPE_NDIM: return "Matmul requires tensors with at least 2 dimensions";
+        case TE_ERR_SHAPE_INNER: return "Inner dimensions must match for matmul";
+        case TE_ERR_SHAPE_BROADCAST: return "Batch dimensions are not broadcastable";
+        case TE_ERR_WORKSPACE: return "context workspace too small";
+        case TE_ERR_CUDA: return "CUDA call failed";
+        case TE_ERR_DEVICE_TIMEOUT: return "a bounded device-side wait gave up";
+        case TE_ERR_NO_DEVICE: return "no usable sm_100 GPU";
+        default: return "unknown status";
+    }
+}
+
+const char* te_b200_last_error(void) { return g_last_error.c_str(); }
+
+int te_b200_init(int device, size_t workspace_bytes, te_b200_ctx** out_ctx) {
+    if (!out_ctx) return fail(TE_ERR_BAD_ARGUMENT, "out_ctx is NULL");
+    *out_ctx = nullptr;
+    int count = 0;
+    cudaError_t e = cudaGetDeviceCount(&count);
+    if (e != cudaSuccess || count == 0) {
+        cudaGetLastError();
+        return fail(TE_ERR_NO_DEVICE, "no CUDA device is visible; this backend has no CPU path");
+    }
+    if (device < 0 || device >= count) return fail(TE_ERR_BAD_ARGUMENT, "device ordinal out of range");
+    cudaDeviceProp prop;
+    if ((e = cudaGetDeviceProperties(&prop, device)) != cudaSuccess) return cuda_fail(e, "cudaGetDeviceProperties");
+    if (prop.major != 10) {
+        char msg[160];
+        snprintf(msg, sizeof msg, "device %d is sm_%d%d; this backend is built for sm_100a only", device, prop.major, prop.minor);
+        return fail(TE_ERR_NO_DEVICE, msg);
+    }
+    int prev = 0;
+    cudaGetDevice(&prev);
+    if ((e = cudaSetDevice(device)) != cudaSuccess) return cuda_fail(e, "cudaSetDevice");
+    te_b200_ctx* ctx = new te_b200_ctx();
+    ctx->device = device;
+    ctx->sm_count = prop.multiProcessorCount;
+    int rc = TE_OK;
+    do {
+        cudaDriverEntryPointQueryResult q;
+        e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ctx->encode_tiled, cudaEnableDefault, &q);
+        if (e != cudaSuccess || q != cudaDriverEntryPointSuccess || !ctx->encode_tiled) {
+            rc = fail(TE_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+            break;
+        }
+        if ((e = cudaMalloc(&ctx->d_status, 256)) != cudaSuccess) { rc = cuda_fail(e, "cudaMalloc(status)"); break; }
+        if ((e = cudaMemset(ctx->d_status, 0, 256)) != cudaSuccess) { rc = cuda_fail(e, "cudaMemset(status)"); break; }
+        ctx->workspace_bytes = workspace_bytes < 4096 ? 4096 : workspace_bytes;
+        if ((e = cudaMalloc(&ctx->workspace, ctx->workspace_bytes)) != cudaSuccess) { rc = cuda_fail(e, "cudaMalloc(workspace)"); break; }
+    } while (0);
+    cudaSetDevice(prev);
+    if (rc) {
+        if (ctx->d_status) cudaFree(ctx->d_status);
+        if (ctx->workspace) cudaFree(ctx->workspace);
+        delete ctx;
+        return rc;
+    }
+    *out_ctx = ctx;
+    return TE_OK;
+}
+
+int te_b200_destroy(te_b200_ctx* ctx) {
+    if (!ctx) return TE_OK;
+    int prev = 0;
+    cudaGetDevice(&prev);
+    cudaSetDevice(ctx->device);
+    cudaFree(ctx->d_status);
+    cudaFree(ctx->workspace);
+    if (ctx->host_stage) cudaFree(ctx->host_stage);
+    cudaSetDevice(prev);
+    delete ctx;
+    return TE_OK;
+}
+
+int64_t te_b200_launch_count(const te_b200_ctx* ctx) { return ctx ? ctx->launches : 0; }
+
+int te_b200_check_device_status(te_b200_ctx* ctx) {
+    if (!ctx) return fail(TE_ERR_BAD_ARGUMENT, "ctx is NULL");
+    int h = 0;
+    cudaError_t e = cudaMemcpy(&h, ctx->d_status, sizeof(int), cudaMemcpyDeviceToHost);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaMemcpy(status)");
+    if (h != 0) {
+        cudaMemset(ctx->d_status, 0, sizeof(int));
+        char msg[128];
+        snprintf(msg, sizeof msg, "device-side bounded wait gave up (site code %d)", h);
+        return fail(TE_ERR_DEVICE_TIMEOUT, msg);
+    }
+    return TE_OK;
+}
+
+int te_b200_gemm_workspace_size(const te_gemm_desc* d, size_t* out_bytes) {
+    if (!out_bytes) return fail(TE_ERR_BAD_ARGUMENT, "out_bytes is NULL");
+    int rc = validate_desc(d);
+    if (rc) return rc;
+    *out_bytes = workspace_need(d);
+    return TE_OK;
+}
+
+int te_b200_gemm_f32(te_b200_ctx* ctx, const te_gemm_desc* d, te_stream_t stream) {
+    if (!ctx) return fail(TE_ERR_BAD_ARGUMENT, "ctx is NULL");
+    return gemm_device(ctx, d, static_cast<cudaStream_t>(stream));
+}
+
+int te_b200_matmul_nd(te_b200_ctx* ctx, const float* a, const int64_t* a_shape, const int64_t* a_strides, int a_ndim,
+                      const float* b, const int64_t* b_shape, const int64_t* b_strides, int b_ndim, float* c,
+                      int64_t* out_shape, int* out_ndim, int precision, te_stream_t stream) {
+    if (a_ndim < 2 || b_ndim < 2) return fail(TE_ERR_SHAPE_NDIM, te_b200_status_string(TE_ERR_SHAPE_NDIM));
+    if (a_ndim > 8 || b_ndim > 8) return fail(TE_ERR_BAD_ARGUMENT, "more than 8 dimensions");
+    if (!a_shape || !a_strides || !b_shape || !b_strides) return fail(TE_ERR_BAD_ARGUMENT, "shape/stride array is NULL");
+    const int64_t M = a_shape[a_ndim - 2], Ka = a_shape[a_ndim - 1];
+    const int64_t Kb = b_shape[b_ndim - 2], N = b_shape[b_ndim - 1];
+    if (Ka != Kb) return fail(TE_ERR_SHAPE_INNER, te_b200_status_string(TE_ERR_SHAPE_INNER));
+    // NumPy broadcasting of the batch dims, right-aligned (tensor.h:838-865).
+    const int nba = a_ndim - 2, nbb = b_ndim - 2, nb = nba > nbb ? nba : nbb;
+    std::vector<int64_t> ext(nb), sa(nb), sb(nb), sc(nb);
+    for (int i = 0; i < nb; ++i) {          // i counts from the right
+        const int64_t da = i < nba ? a_shape[nba - 1 - i] : 1;
+        const int64_t db = i < nbb ? b_shape[nbb - 1 - i] : 1;
+        if (da != db && da != 1 && db != 1)
+            return fail(TE_ERR_SHAPE_BROADCAST, te_b200_status_string(TE_ERR_SHAPE_BROADCAST));
+        const int idx = nb - 1 - i;
+        ext[idx] = da > db ? da : db;
+        // size-1 dims always index 0 (tensor.h:895-899): stride 0
+        sa[idx] = (i < nba && da != 1) ? a_strides[nba - 1 - i] : 0;
+        sb[idx] = (i < nbb && db != 1) ? b_strides[nbb - 1 - i] : 0;
+    }
+    int64_t run = M * N;
+    for (int i = nb - 1; i >= 0; --i) { sc[i] = run; run *= ext[i]; }
+    if (out_ndim) *out_ndim = nb + 2;
+    if (out_shape) {
+        for (int i = 0; i < nb; ++i) out_shape[i] = ext[i];
+        out_shape[nb] = M;
+        out_shape[nb + 1] = N;
+    }
+    if (!c) return TE_OK;   // shape query only
+    if (!ctx) return fail(TE_ERR_BAD_ARGUMENT, "ctx is NULL");
+
+    // Per-slice layout, the two cases cublas_params accepts (tensor.h:623-627).
+    auto slice_layout = [](int64_t s_row, int64_t s_col, int32_t& major, int64_t& ld) -> bool {
+        if (s_col == 1) { major = TE_ROW_MAJOR; ld = s_row; return true; }
+        if (s_row == 1) { major = TE_COL_MAJOR; ld = s_col; return true; }
+        return false;
+    };
+    te_gemm_desc d;
+    memset(&d, 0, sizeof d);
+    d.M = M; d.N = N; d.K = Ka;
+    if (!slice_layout(a_strides[a_ndim - 2], a_strides[a_ndim - 1], d.a_major, d.lda) ||
+        !slice_layout(b_strides[b_ndim - 2], b_strides[b_ndim - 1], d.b_major, d.ldb))
+        return fail(TE_ERR_UNSUPPORTED_LAYOUT, te_b200_status_string(TE_ERR_UNSUPPORTED_LAYOUT));
+    d.ldc = N;
+    d.precision = precision;
+    d.alpha = 1.0f;
+
+    // Drop unit dims, then merge neighbours that stride uniformly for A, B and C at once.
+    std::vector<int64_t> e2, a2, b2, c2;
+    for (int i = 0; i < nb; ++i) {
+        if (ext[i] == 0) return TE_OK;   // empty result
+        if (ext[i] == 1) continue;
+        if (!e2.empty() && a2.back() == sa[i] * ext[i] && b2.back() == sb[i] * ext[i] && c2.back() == sc[i] * ext[i]) {
+            e2.back() *= ext[i]; a2.back() = sa[i]; b2.back() = sb[i]; c2.back() = sc[i];
+        } else {
+            e2.push_back(ext[i]); a2.push_back(sa[i]); b2.push_back(sb[i]); c2.push_back(sc[i]);
+        }
+    }
+    const int levels = (int)e2.size();
+    const int loop_levels = levels > 2 ? levels - 2 : 0;
+    d.batch_outer = d.batch_inner = 1;
+    if (levels >= 1) {
+        const int li = levels - 1;
+        d.batch_inner = e2[li]; d.a_stride_inner = a2[li]; d.b_stride_inner = b2[li]; d.c_stride_inner = c2[li];
+    }
+    if (levels >= 2) {
+        const int lo = levels - 2;
+        d.batch_outer = e2[lo]; d.a_stride_outer = a2[lo]; d.b_stride_outer = b2[lo]; d.c_stride_outer = c2[lo];
+    }
+    int64_t loops = 1;
+    for (int i = 0; i < loop_levels; ++i) loops *= e2[i];
+    for (int64_t it = 0; it < loops; ++it) {
+        int64_t rem = it, oa = 0, ob = 0, oc = 0;
+        for (int i = loop_levels - 1; i >= 0; --i) {
+            const int64_t idx = rem % e2[i];
+            rem /= e2[i];
+            oa += idx * a2[i]; ob += idx * b2[i]; oc += idx * c2[i];
+        }
+        d.a = a + oa; d.b = b + ob; d.c = c + oc;
+        int rc = gemm_device(ctx, &d, static_cast<cudaStream_t>(stream));
+        if (rc) return rc;
+    }
+    return TE_OK;
+}
+
+int te_b200_gemm_f32_host(te_b200_ctx* ctx, const te_gemm_desc* h) {
+    if (!ctx) return fail(TE_ERR_BAD_ARGUMENT, "ctx is NULL");
+    int rc = validate_desc(h);
+    if (rc) return rc;
+    if (h->M == 0 || h->N == 0) return TE_OK;
+    auto span = [&](int64_t rows, int64_t cols, int64_t ld, int64_t so, int64_t si) -> int64_t {
+        // elements touched by a [rows, cols] slice with row pitch ld, over all batches
+        if (rows == 0 || cols == 0) return 0;
+        return (rows - 1) * ld + cols + (h->batch_outer - 1) * so + (h->batch_inner - 1) * si;
+    };
+    const int64_t a_el = h->a_major == TE_ROW_MAJOR ? span(h->M, h->K, h->lda, h->a_stride_outer, h->a_stride_inner)
+                                                    : span(h->K, h->M, h->lda, h->a_stride_outer, h->a_stride_inner);
+    const int64_t b_el = h->b_major == TE_ROW_MAJOR ? span(h->K, h->N, h->ldb, h->b_stride_outer, h->b_stride_inner)
+                                                    : span(h->N, h->K, h->ldb, h->b_stride_outer, h->b_stride_inner);
+    const int64_t c_el = span(h->M, h->N, h->ldc, h->c_stride_outer, h->c_stride_inner);
+    const int64_t bias_el = h->bias ? h->N : 0;
+    const int64_t pre_el = h->preact_out ? c_el : 0;
+    const size_t need = (size_t)(round_up(a_el * 4, 256) + round_up(b_el * 4, 256) + round_up(c_el * 4, 256) +
+                                 round_up(bias_el * 4, 256) + round_up(pre_el * 4, 256));
+    cudaError_t e;
+    if (need > ctx->host_stage_bytes) {   // grow-only device staging for host callers
+        if (ctx->host_stage) cudaFree(ctx->host_stage);
+        ctx->host_stage = nullptr;
+        ctx->host_stage_bytes = 0;
+        if ((e = cudaMalloc(&ctx->host_stage, need)) != cudaSuccess) return cuda_fail(e, "cudaMalloc(host staging)");
+        ctx->host_stage_bytes = need;
+    }
+    Carver st(ctx->host_stage, ctx->host_stage_bytes);
+    float* da = st.take(a_el * 4);
+    float* db = st.take(b_el * 4);
+    float* dc = st.take(c_el * 4);
+    float* dbias = bias_el ? st.take(bias_el * 4) : nullptr;
+    float* dpre = pre_el ? st.take(pre_el * 4) : nullptr;
+    cudaStream_t s = 0;
+    if (a_el && (e = cudaMemcpyAsync(da, h->a, a_el * 4, cudaMemcpyHostToDevice, s)) != cudaSuccess) return cuda_fail(e, "H2D A");
+    if (b_el && (e = cudaMemcpyAsync(db, h->b, b_el * 4, cudaMemcpyHostToDevice, s)) != cudaSuccess) return cuda_fail(e, "H2D B");
+    if (bias_el && (e = cudaMemcpyAsync(dbias, h->bias, bias_el * 4, cudaMemcpyHostToDevice, s)) != cudaSuccess) return cuda_fail(e, "H2D bias");
+    te_gemm_desc d = *h;
+    d.a = da; d.b = db; d.c = dc; d.bias = dbias; d.preact_out = dpre;
+    if ((rc = gemm_device(ctx, &d, s))) return rc;
+    if ((e = cudaMemcpyAsync(h->c, dc, c_el * 4, cudaMemcpyDeviceToHost, s)) != cudaSuccess) return cuda_fail(e, "D2H C");
+    if (pre_el && (e = cudaMemcpyAsync(h->preact_out, dpre, pre_el * 4, cudaMemcpyDeviceToHost, s)) != cudaSuccess) return cuda_fail(e, "D2H preact");
+    if ((e = cudaStreamSynchronize(s)) != cudaSuccess) return cuda_fail(e, "cudaStreamSynchronize");
+    return te_b200_check_device_status(ctx);
+}
+
+int te_b200_softmax_rows_f32(te_b200_ctx* ctx, const float* in, float* out, int64_t rows, int64_t cols, te_stream_t s) {
+    if (!ctx) return fail(TE_ERR_BAD_ARGUMENT, "ctx is NULL");
+    if (rows < 0 || cols < 0 || cols > INT32_MAX || ((rows && cols) && (!in || !out))) return fail(TE_ERR_BAD_ARGUMENT, "softmax: bad argument");
+    return launch_softmax_rows(ctx, in, out, rows, cols, static_cast<cudaStream_t>(s));
+}
+int te_b200_softmax_backward_rows_f32(te_b200_ctx* ctx, const float* sm, const float* dy, float* dx, int64_t rows,
+                                      int64_t cols, te_stream_t s) {
+    if (!ctx) return fail(TE_ERR_BAD_ARGUMENT, "ctx is NULL");
+    if (rows < 0 || cols < 0 || cols > INT32_MAX || ((rows && cols) && (!sm || !dy || !dx))) return fail(TE_ERR_BAD_ARGUMENT, "softmax backward: bad argument");
+    return launch_softmax_backward_rows(ctx, sm, dy, dx, rows, cols, static_cast<cudaStream_t>(s));
+}
+int te_b200_gelu_f32(te_b200_ctx* ctx, const float* x, float* y, int64_t n, te_stream_t s) {
+    if (!ctx) return fail(TE_ERR_BAD_ARGUMENT, "ctx is NULL");
+    if (n < 0 || (n && (!x || !y))) return fail(TE_ERR_BAD_ARGUMENT, "gelu: bad argument");
+    return launch_gelu(ctx, x, y, n, static_cast<cudaStream_t>(s));
+}
+int te_b200_gelu_backward_f32(te_b200_ctx* ctx, const float* x, const float* dy, float* dx, int64_t n, te_stream_t s) {
+    if (!ctx) return fail(TE_ERR_BAD_ARGUMENT, "ctx is NULL");
+    if (n < 0 || (n && (!x || !dy || !dx))) return fail(TE_ERR_BAD_ARGUMENT, "gelu backward: bad argument");
+    return launch_gelu_backward(ctx, x, dy, dx, n, static_cast<cudaStream_t>(s));
+}
+int te_b200_colsum_f32(te_b200_ctx* ctx, const float* in, int64_t rows, int64_t cols, int64_t ld, float* out, te_stream_t s) {
+    if (!ctx) return fail(TE_ERR_BAD_ARGUMENT, "ctx is NULL");
+    if (rows < 0 || cols < 0 || ld < cols || (cols && !out) || (rows && cols && !in)) return fail(TE_ERR_BAD_ARGUMENT, "colsum: bad argument");
+    return launch_colsum(ctx, in, rows, cols, ld, out, static_cast<cudaStream_t>(s));
+}
+
+int te_b200_linear_forward(te_b200_ctx* ctx, const float* x, const float* w, const float* bias, float* y, float* preact,
+                           int64_t rows, int64_t in_features, int64_t out_features, int gelu, int precision,
+                           te_stream_t stream) {
+    if (!ctx) return fail(TE_ERR_BAD_ARGUMENT, "ctx is NULL");
+    te_gemm_desc d;
+    memset(&d, 0, sizeof d);
+    d.M = rows; d.N = out_features; d.K = in_features;
+    d.a = x; d.lda = in_features; d.a_major = TE_ROW_MAJOR;
+    d.b = w; d.ldb = in_features; d.b_major = TE_COL_MAJOR;   // W[out,in] read as its transpose view [in,out]
+    d.c = y; d.ldc = out_features;
+    d.batch_outer = d.batch_inner = 1;
+    d.alpha = 1.0f;
+    d.bias = bias;
+    d.epilogue = gelu ? TE_EPI_BIAS_GELU : (bias ? TE_EPI_BIAS : TE_EPI_NONE);
+    d.preact_out = preact;
+    d.precision = precision;
+    return gemm_device(ctx, &d, static_cast<cudaStream_t>(stream));
+}
+
+int te_b200_linear_backward(te_b200_ctx* ctx, const float* x, const float* w, const float* dy, float* dx, float* dw,
+                            float* db, int64_t rows, int64_t in_features, int64_t out_features, int precision,
+                            te_stream_t stream) {
+    if (!ctx) return fail(TE_ERR_BAD_ARGUMENT, "ctx is NULL");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    int rc;
+    te_gemm_desc d;
+    if (dx) {   // dX[rows,in] = dY[rows,out] . W[out,in]
+        memset(&d, 0, sizeof d);
+        d.M = rows; d.N = in_features; d.K = out_features;
+        d.a = dy; d.lda = out_features; d.a_major = TE_ROW_MAJOR;
+        d.b = w; d.ldb = in_features; d.b_major = TE_ROW_MAJOR;
+        d.c = dx; d.ldc = in_features;
+        d.batch_outer = d.batch_inner = 1; d.alpha = 1.0f; d.precision = precision;
+        if ((rc = gemm_device(ctx, &d, st))) return rc;
+    }
+    if (dw) {   // dW[out,in] = dY^T[out,rows] . X[rows,in]
+        memset(&d, 0, sizeof d);
+        d.M = out_features; d.N = in_features; d.K = rows;
+        d.a = dy; d.lda = out_features; d.a_major = TE_COL_MAJOR;
+        d.b = x; d.ldb = in_features; d.b_major = TE_ROW_MAJOR;
+        d.c = dw; d.ldc = in_features;
+        d.batch_outer = d.batch_inner = 1; d.alpha = 1.0f; d.precision = precision;
+        if ((rc = gemm_device(ctx, &d, st))) return rc;
+    }
+    if (db) {
+        if ((rc = launch_colsum(ctx, dy, rows, out_features, out_features, db, st))) return rc;
+    }
+    return TE_OK;
+}
+
+int te_b200_attention_forward(te_b200_ctx* ctx, const te_attn_desc* t, te_stream_t stream) {
+    if (!ctx) return fail(TE_ERR_BAD_ARGUMENT, "ctx is NULL");
+    if (!t || t->B < 0 || t->H < 0 || t->T < 0 || t->d < 0) return fail(TE_ERR_BAD_ARGUMENT, "attention: bad extents");
+    if (t->B == 0 || t->H == 0 || t->T == 0) return TE_OK;
+    if (!t->q || !t->k || !t->v || !t->p_out || !t->o) return fail(TE_ERR_BAD_ARGUMENT, "attention: NULL pointer");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    te_gemm_desc d;
+    int rc;
+    // S = Q . K^T / sqrt(d)   (scaledot.cpp:13-22), written into p_out
+    memset(&d, 0, sizeof d);
+    d.M = t->T; d.N = t->T; d.K = t->d;
+    d.a = t->q; d.lda = t->q_strides[2]; d.a_major = TE_ROW_MAJOR;
+    d.b = t->k; d.ldb = t->k_strides[2]; d.b_major = TE_COL_MAJOR;
+    d.c = t->p_out; d.ldc = t->T;
+    d.batch_outer = t->B; d.batch_inner = t->H;
+    d.a_stride_outer = t->q_strides[0]; d.a_stride_inner = t->q_strides[1];
+    d.b_stride_outer = t->k_strides[0]; d.b_stride_inner = t->k_strides[1];
+    d.c_stride_outer = t->H * t->T * t->T; d.c_stride_inner = t->T * t->T;
+    d.alpha = sqrtf((float)t->d);
+    d.scale_mode = TE_SCALE_DIV;
+    d.precision = t->precision;
+    if ((rc = gemm_device(ctx, &d, st))) return rc;
+    // P = softmax(S) in place (scaledot.cpp:24)
+    if ((rc = launch_softmax_rows(ctx, t->p_out, t->p_out, t->B * t->H * t->T, t->T, st))) return rc;
+    // O = P . V
+    memset(&d, 0, sizeof d);
+    d.M = t->T; d.N = t->d; d.K = t->T;
+    d.a = t->p_out; d.lda = t->T; d.a_major = TE_ROW_MAJOR;
+    d.b = t->v; d.ldb = t->v_strides[2]; d.b_major = TE_ROW_MAJOR;
+    d.c = t->o; d.ldc = t->o_strides[2];
+    d.batch_outer = t->B; d.batch_inner = t->H;
+    d.a_stride_outer = t->H * t->T * t->T; d.a_stride_inner = t->T * t->T;
+    d.b_stride_outer = t->v_strides[0]; d.b_stride_inner = t->v_strides[1];
+    d.c_stride_outer = t->o_strides[0]; d.c_stride_inner = t->o_strides[1];
+    d.alpha = 1.0f;
+    d.precision = t->precision;
+    return gemm_device(ctx, &d, st);
+}
+
+int te_b200_shard_range(int64_t total, int world, int rank, int64_t align, int64_t* out_begin, int64_t* out_count) {
+    if (total < 0 || world < 1 || rank < 0 || rank >= world || align < 1 || !out_begin || !out_count)
+        return fail(TE_ERR_BAD_ARGUMENT, "shard_range: bad argument");
+    const int64_t units = (total + align - 1) / align;
+    const int64_t per = (units + world - 1) / world;
+    int64_t begin = (int64_t)rank * per * align;
+    if (begin > total) begin = total;
+    int64_t count = per * align;
+    if (begin + count > total) count = total - begin;
+    *out_begin = begin;
+    *out_count = count;
+    return TE_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,504 @@
+// FP32-in / FP32-out GEMM for sm_100a on the 5th-generation tensor cores.
+//
+//   C[b] = epilogue( scale( A[b] . B[b] ) ),  A: M x K,  B: K x N,  C: M x N row-major.
+//
+// One persistent CTA per SM walks a list of 128 x BN output tiles.  Inside a CTA the work is
+// split by warp role:
+//   warps 0-3  epilogue: tcgen05.ld the finished accumulator out of TMEM, apply scale / bias /
+//              GELU, store to global memory;
+//   warp  4    producer: one lane issues TMA loads (cp.async.bulk.tensor, 128-byte swizzle, no
+//              multicast) of the A and B k-blocks into a ring of shared-memory stages;
+//   warp  5    MMA: one lane issues tcgen05.mma kind::tf32 (128 x BN x 8 per instruction) from
+//              shared-memory descriptors into one of two TMEM accumulator buffers, so the
+//              epilogue of tile i overlaps the main loop of tile i+1.
+// Stage hand-off is by mbarriers (full: TMA bytes landed; empty: tcgen05.commit after the MMAs
+// that read the stage).  Every wait is bounded: after ~2 s a waiter records an error code in a
+// device status word, raises a CTA-wide abort flag, and all roles fall through to the teardown
+// that drains outstanding copies/MMAs and frees TMEM.
+//
+// Operands are either K-major (K contiguous: a row-major A, a column-major B) or MN-major (a
+// column-major A, a row-major B).  Both are read in place by TMA; ragged M/N/K edges rely on
+// TMA zero fill and a predicated epilogue.  In 3xTF32 mode each operand comes as two tf32 planes
+// (hi, lo) and every k-step issues lo.hi + hi.lo + hi.hi into the same accumulator.
+//
+// Where this sits in the reference: it is the device side of Tensor::cuda_matmul_impl_f32
+// (reference src/tensor/tensor.h:614-793), replacing cublasSgemm(/StridedBatched) and
+// matmul_kernel_double_buffered_cpasync (reference src/cuda/elementwise_cuda.cu:842-1005).
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+
+#include "ptx_sm100.cuh"
+#include "te_internal.h"
+
+namespace te {
+
+constexpr int BM = 128;
+constexpr int BK = 32;                       // floats per k-block = one 128-byte swizzle row
+constexpr int UMMA_K = 8;                    // tf32 K per tcgen05.mma
+constexpr int A_PLANE_BYTES = BM * BK * 4;   // 16 KiB
+constexpr int SMEM_RING_BUDGET = 192 * 1024;
+constexpr int SMEM_AUX_BYTES = 512;          // mbarriers, TMEM slot, abort flag
+constexpr int GROUP_M = 16;                  // raster: tiles advance down 16 m-blocks, then one n-block over
+constexpr uint64_t WAIT_LIMIT_NS = 2000000000ull;
+
+enum : int {  // where a bounded wait gave up (stored in the device status word)
+    WAIT_PRODUCER_EMPTY = 101,
+    WAIT_MMA_FULL = 102,
+    WAIT_MMA_TMEM_EMPTY = 103,
+    WAIT_EPI_TMEM_FULL = 104,
+    WAIT_TEARDOWN = 105
+};
+
+struct GemmParams {
+    int M, N, K;
+    int tiles_m, tiles_n;
+    int batch_inner, num_batches;
+    int a_mul_inner, a_mul_outer, b_mul_inner, b_mul_outer;  // 0 = broadcast, 1 = indexed
+    long long ldc, c_stride_inner, c_stride_outer;
+    float* c;
+    float* preact;
+    const float* bias;
+    float alpha;
+    int scale_mode;
+    int epilogue;
+    int* status;
+};
+
+template <int BN, int NPL>
+struct TileCfg {
+    static constexpr int B_PLANE_BYTES = BN * BK * 4;
+    static constexpr int STAGE_BYTES = NPL * (A_PLANE_BYTES + B_PLANE_BYTES);
+    static constexpr int STAGES = SMEM_RING_BUDGET / STAGE_BYTES;
+    static constexpr int TMEM_COLS = 2 * BN;  // two accumulator buffers of BN fp32 columns
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + SMEM_AUX_BYTES + 1024;  // +1024: manual alignment
+    static_assert(STAGES >= 2, "need at least a double buffer");
+    static_assert(TMEM_COLS >= 32 && TMEM_COLS <= 512 && (TMEM_COLS & (TMEM_COLS - 1)) == 0, "TMEM columns");
+};
+
+__device__ __forceinline__ bool wait_bounded(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                             int* status, int code) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const uint64_t t0 = global_timer_ns();
+    uint32_t polls = 0;
+    for (;;) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((++polls & 0x3F) == 0) {
+            if (*abort_flag) return false;
+            if (global_timer_ns() - t0 > WAIT_LIMIT_NS) {
+                *abort_flag = 1;
+                atomicCAS(status, 0, code);
+                return false;
+            }
+        }
+    }
+}
+
+__device__ __forceinline__ void tile_coords(int t, const GemmParams& p, int& batch, int& m_blk, int& n_blk) {
+    const int per_batch = p.tiles_m * p.tiles_n;
+    batch = t / per_batch;
+    const int r = t - batch * per_batch;
+    const int group_span = GROUP_M * p.tiles_n;
+    const int g = r / group_span;
+    const int first_m = g * GROUP_M;
+    const int gm = min(p.tiles_m - first_m, GROUP_M);
+    const int in_group = r - g * group_span;
+    m_blk = first_m + in_group % gm;
+    n_blk = in_group / gm;
+}
+
+__device__ __forceinline__ float gelu_tanh(float x) {
+    // Same expression as gelu_forward_kernel (reference src/cuda/elementwise_cuda.cu:2701-2707).
+    const float x3 = x * x * x;
+    return 0.5f * x * (1.0f + tanhf(0.7978845608f * (x + 0.044715f * x3)));
+}
+
+template <int BN, int NPL, bool A_MN, bool B_MN>
+__global__ void __launch_bounds__(192, 1)
+gemm_tf32_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_a_lo,
+                 const __grid_constant__ CUtensorMap tm_b, const __grid_constant__ CUtensorMap tm_b_lo,
+                 const GemmParams p) {
+    using Cfg = TileCfg<BN, NPL>;
+    constexpr int STAGES = Cfg::STAGES;
+    constexpr int B_PLANE_BYTES = Cfg::B_PLANE_BYTES;
+    constexpr int STAGE_BYTES = Cfg::STAGE_BYTES;
+    constexpr uint32_t IDESC = make_idesc_tf32(BM, BN, A_MN, B_MN);
+    // Descriptor geometry.
+    // K-major (TMA SWIZZLE_128B): rows of 128 B, 8-row groups 1024 B apart (SBO); one MMA advances 32 B along K.
+    // MN-major (TMA SWIZZLE_128B_ATOM_32B): every k index is a 128-byte row of 32 consecutive MN elements;
+    // 4-row groups are 512 B apart (SBO), 32-element MN chunks are BK*128 B apart (LBO); one MMA (8 k) advances 1024 B.
+    constexpr uint32_t MN_CHUNK_BYTES = BK * 128;
+    constexpr uint32_t A_LBO = A_MN ? MN_CHUNK_BYTES : 16, A_SBO = A_MN ? 512 : 1024, A_KSTEP = A_MN ? 1024 : UMMA_K * 4;
+    constexpr uint32_t B_LBO = B_MN ? MN_CHUNK_BYTES : 16, B_SBO = B_MN ? 512 : 1024, B_KSTEP = B_MN ? 1024 : UMMA_K * 4;
+    constexpr uint32_t A_LAYOUT = A_MN ? SMEM_LAYOUT_SW128_BASE32B : SMEM_LAYOUT_SW128;
+    constexpr uint32_t B_LAYOUT = B_MN ? SMEM_LAYOUT_SW128_BASE32B : SMEM_LAYOUT_SW128;
+
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw_addr = smem_u32(smem_raw);
+    const uint32_t ring = (raw_addr + 1023u) & ~1023u;           // 128B swizzle wants 1024-byte aligned tiles
+    uint8_t* aux = smem_raw + (ring - raw_addr) + STAGES * STAGE_BYTES;
+    const uint32_t aux_addr = ring + STAGES * STAGE_BYTES;
+    // aux layout (8-byte slots): full[STAGES] | empty[STAGES] | tmem_full[2] | tmem_empty[2] | teardown | slot | abort
+    const uint32_t bar_full = aux_addr;
+    const uint32_t bar_empty = bar_full + 8 * STAGES;
+    const uint32_t bar_tmem_full = bar_empty + 8 * STAGES;
+    const uint32_t bar_tmem_empty = bar_tmem_full + 16;
+    const uint32_t bar_teardown = bar_tmem_empty + 16;
+    const uint32_t tmem_slot_addr = bar_teardown + 8;
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(aux + (tmem_slot_addr - aux_addr));
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(aux + (tmem_slot_addr - aux_addr) + 4);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(bar_full + 8 * s, 1);
+            mbar_init(bar_empty + 8 * s, 1);
+        }
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(bar_tmem_full + 8 * i, 1);
+            mbar_init(bar_tmem_empty + 8 * i, 4);   // one arrival per epilogue warp
+        }
+        mbar_init(bar_teardown, 1);
+        *abort_flag = 0;
+        fence_barrier_init();
+        fence_proxy_async_smem();
+    }
+    if (warp == 4 && lane == 0) {
+        tma_prefetch_desc(&tm_a);
+        tma_prefetch_desc(&tm_b);
+        if (NPL == 2) {
+            tma_prefetch_desc(&tm_a_lo);
+            tma_prefetch_desc(&tm_b_lo);
+        }
+    }
+    if (warp == 5) {
+        tmem_alloc(tmem_slot_addr, Cfg::TMEM_COLS);
+        tmem_relinquish();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+
+    const int total_tiles = p.tiles_m * p.tiles_n * p.num_batches;
+    const int kblocks = (p.K + BK - 1) / BK;
+
+    if (warp == 4) {
+        // ------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            int issued = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+                int batch, m_blk, n_blk;
+                tile_coords(t, p, batch, m_blk, n_blk);
+                const int bo = batch / p.batch_inner, bi = batch - bo * p.batch_inner;
+                const int a_ci = bi * p.a_mul_inner, a_co = bo * p.a_mul_outer;
+                const int b_ci = bi * p.b_mul_inner, b_co = bo * p.b_mul_outer;
+                const int m0 = m_blk * BM, n0 = n_blk * BN;
+                for (int kb = 0; kb < kblocks; ++kb, ++issued) {
+                    const int s = issued % STAGES;
+                    const uint32_t phase = (issued / STAGES) & 1;
+                    if (!wait_bounded(bar_empty + 8 * s, phase ^ 1, abort_flag, p.status, WAIT_PRODUCER_EMPTY)) {
+                        ok = false;
+                        break;
+                    }
+                    const uint32_t full = bar_full + 8 * s;
+                    mbar_arrive_expect_tx(full, STAGE_BYTES);
+                    const uint32_t sa = ring + s * STAGE_BYTES;
+                    const uint32_t sb = sa + NPL * A_PLANE_BYTES;
+                    const int k0 = kb * BK;
+#pragma unroll
+                    for (int pl = 0; pl < NPL; ++pl) {
+                        const CUtensorMap* ma = pl ? &tm_a_lo : &tm_a;
+                        const CUtensorMap* mb = pl ? &tm_b_lo : &tm_b;
+                        if (A_MN) {
+#pragma unroll
+                            for (int c = 0; c < BM / 32; ++c)
+                                tma_load_4d(sa + pl * A_PLANE_BYTES + c * MN_CHUNK_BYTES, ma, full,
+                                            m0 + 32 * c, k0, a_ci, a_co);
+                        } else {
+                            tma_load_4d(sa + pl * A_PLANE_BYTES, ma, full, k0, m0, a_ci, a_co);
+                        }
+                        if (B_MN) {
+#pragma unroll
+                            for (int c = 0; c < BN / 32; ++c)
+                                tma_load_4d(sb + pl * B_PLANE_BYTES + c * MN_CHUNK_BYTES, mb, full,
+                                            n0 + 32 * c, k0, b_ci, b_co);
+                        } else {
+                            tma_load_4d(sb + pl * B_PLANE_BYTES, mb, full, k0, n0, b_ci, b_co);
+                        }
+                    }
+                }
+            }
+            if (!ok || *abort_flag) {
+                // Drain: copies already issued still write shared memory; wait (bounded) for them.
+                const int first = issued > STAGES ? issued - STAGES : 0;
+                for (int i = first; i < issued; ++i) {
+                    const uint64_t t0 = global_timer_ns();
+                    while (!mbar_try_wait(bar_full + 8 * (i % STAGES), (i / STAGES) & 1)) {
+                        if (global_timer_ns() - t0 > WAIT_LIMIT_NS) break;
+                    }
+                }
+            }
+        }
+    } else if (warp == 5) {
+        // ------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            int consumed = 0;
+            int local = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++local) {
+                const int buf = local & 1;
+                if (!wait_bounded(bar_tmem_empty + 8 * buf, ((local >> 1) & 1) ^ 1, abort_flag, p.status,
+                                  WAIT_MMA_TMEM_EMPTY)) {
+                    ok = false;
+                    break;
+                }
+                tc_fence_after_sync();
+                const uint32_t d_tmem = tmem_base + buf * BN;
+                for (int kb = 0; kb < kblocks; ++kb, ++consumed) {
+                    const int s = consumed % STAGES;
+                    if (!wait_bounded(bar_full + 8 * s, (consumed / STAGES) & 1, abort_flag, p.status,
+                                      WAIT_MMA_FULL)) {
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after_sync();
+                    const uint32_t sa = ring + s * STAGE_BYTES;
+                    const uint32_t sb = sa + NPL * A_PLANE_BYTES;
+#pragma unroll
+                    for (int j = 0; j < BK / UMMA_K; ++j) {
+                        const uint64_t a_hi = make_smem_desc(sa + j * A_KSTEP, A_LBO, A_SBO, A_LAYOUT);
+                        const uint64_t b_hi = make_smem_desc(sb + j * B_KSTEP, B_LBO, B_SBO, B_LAYOUT);
+                        const uint32_t acc0 = (kb | j) != 0;
+                        if (NPL == 2) {
+                            const uint64_t a_lo = make_smem_desc(sa + A_PLANE_BYTES + j * A_KSTEP, A_LBO, A_SBO, A_LAYOUT);
+                            const uint64_t b_lo = make_smem_desc(sb + B_PLANE_BYTES + j * B_KSTEP, B_LBO, B_SBO, B_LAYOUT);
+                            umma_tf32(d_tmem, a_lo, b_hi, IDESC, acc0);   // small terms first
+                            umma_tf32(d_tmem, a_hi, b_lo, IDESC, 1);
+                            umma_tf32(d_tmem, a_hi, b_hi, IDESC, 1);
+                        } else {
+                            umma_tf32(d_tmem, a_hi, b_hi, IDESC, acc0);
+                        }
+                    }
+                    umma_commit(bar_empty + 8 * s);   // stage reusable once these MMAs have read it
+                }
+                if (ok) umma_commit(bar_tmem_full + 8 * buf);
+            }
+            // All MMAs issued by this thread must be finished before TMEM is freed.
+            umma_commit(bar_teardown);
+            const uint64_t t0 = global_timer_ns();
+            while (!mbar_try_wait(bar_teardown, 0)) {
+                if (global_timer_ns() - t0 > WAIT_LIMIT_NS) {
+                    atomicCAS(p.status, 0, (int)WAIT_TEARDOWN);
+                    break;
+                }
+            }
+        }
+    } else {
+        // ------------------------------------------------------------ epilogue (warps 0-3)
+        int local = 0;
+        for (int t = blockIdx.x; t < total_tiles; t += gridDim.x, ++local) {
+            int batch, m_blk, n_blk;
+            tile_coords(t, p, batch, m_blk, n_blk);
+            const int bo = batch / p.batch_inner, bi = batch - bo * p.batch_inner;
+            const int buf = local & 1;
+            bool ok = wait_bounded(bar_tmem_full + 8 * buf, (local >> 1) & 1, abort_flag, p.status,
+                                   WAIT_EPI_TMEM_FULL);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            tc_fence_after_sync();
+
+            const int row = m_blk * BM + warp * 32 + lane;
+            const int n0 = n_blk * BN;
+            const long long batch_off = (long long)bo * p.c_stride_outer + (long long)bi * p.c_stride_inner;
+            const long long c_off = batch_off + (long long)row * p.ldc;
+            float* c_row = p.c + c_off;
+            float* pre_row = p.preact ? p.preact + c_off : nullptr;
+            const bool row_ok = row < p.M;
+            // 16-byte stores need every row start aligned: aligned batch base and ldc a multiple of 4.
+            const bool vec_ok = ((p.ldc & 3) == 0) && ((reinterpret_cast<uintptr_t>(p.c + batch_off) & 15) == 0) &&
+                                (!p.preact || (reinterpret_cast<uintptr_t>(p.preact + batch_off) & 15) == 0);
+            const uint32_t t_row = tmem_base + (uint32_t(warp * 32) << 16) + buf * BN;
+#pragma unroll 1
+            for (int cc = 0; cc < BN / 32; ++cc) {
+                const int col0 = n0 + cc * 32;
+                if (col0 >= p.N) break;   // warp-uniform
+                uint32_t r[32];
+                tmem_ld_32x32b_x32(t_row + cc * 32, r);
+                tmem_ld_wait();
+                float v[32];
+#pragma unroll
+                for (int j = 0; j < 32; ++j) {
+                    float x = p.K > 0 ? __uint_as_float(r[j]) : 0.0f;
+                    if (p.scale_mode == TE_SCALE_MUL) x *= p.alpha;
+                    else if (p.scale_mode == TE_SCALE_DIV) x = x / p.alpha;
+                    v[j] = x;
+                }
+                if (p.bias) {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j)
+                        if (col0 + j < p.N) v[j] += __ldg(p.bias + col0 + j);
+                }
+                const bool full_chunk = col0 + 32 <= p.N;
+                if (row_ok) {
+                    if (pre_row) {
+                        if (full_chunk && vec_ok) {
+#pragma unroll
+                            for (int j = 0; j < 32; j += 4)
+                                *reinterpret_cast<float4*>(pre_row + col0 + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 32; ++j)
+                                if (col0 + j < p.N) pre_row[col0 + j] = v[j];
+                        }
+                    }
+                    if (p.epilogue == TE_EPI_BIAS_GELU) {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) v[j] = gelu_tanh(v[j]);
+                    }
+                    if (full_chunk && vec_ok) {
+#pragma unroll
+                        for (int j = 0; j < 32; j += 4)
+                            *reinterpret_cast<float4*>(c_row + col0 + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j)
+                            if (col0 + j < p.N) c_row[col0 + j] = v[j];
+                    }
+                }
+            }
+            // Hand the accumulator buffer back to the MMA warp.
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_tmem_empty + 8 * buf);
+        }
+    }
+
+    __syncwarp();
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 5) {
+        tc_fence_after_sync();
+        tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+    }
+}
+
+// ------------------------------------------------------------------ host side ---
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                  CUtensorMapFloatOOBfill);
+
+bool operand_tma_ok(const Operand& op, int64_t batch_inner, int64_t batch_outer) {
+    if (reinterpret_cast<uintptr_t>(op.ptr) & 15) return false;
+    if (op.ld & 3) return false;
+    if (batch_inner > 1 && (op.stride_inner & 3)) return false;
+    if (batch_outer > 1 && (op.stride_outer & 3)) return false;
+    return true;
+}
+
+// 4-D map {contiguous index, strided index, batch_inner, batch_outer}.  Broadcast (stride 0) levels get
+// extent 1; the kernel multiplies their coordinate by 0.
+static int make_operand_map(te_b200_ctx* ctx, CUtensorMap* out, const float* ptr, const Operand& op,
+                            int64_t K, int box_rows, int64_t batch_inner, int64_t batch_outer) {
+    const int64_t k_extent = K > 0 ? K : 1;   // K == 0 issues no loads but the map must still be valid
+    const int64_t contiguous_extent = op.mn_major ? op.rows : k_extent;
+    const int64_t strided_extent = op.mn_major ? k_extent : op.rows;
+    const int64_t e2 = (batch_inner > 1 && op.stride_inner != 0) ? batch_inner : 1;
+    const int64_t e3 = (batch_outer > 1 && op.stride_outer != 0) ? batch_outer : 1;
+    cuuint64_t dims[4] = {(cuuint64_t)contiguous_extent, (cuuint64_t)strided_extent, (cuuint64_t)e2, (cuuint64_t)e3};
+    const cuuint64_t row_bytes = (cuuint64_t)op.ld * 4;
+    cuuint64_t strides[3] = {row_bytes,
+                             e2 > 1 ? (cuuint64_t)op.stride_inner * 4 : row_bytes,
+                             e3 > 1 ? (cuuint64_t)op.stride_outer * 4 : row_bytes};
+    cuuint32_t box[4] = {(cuuint32_t)BK, (cuuint32_t)(op.mn_major ? BK : box_rows), 1, 1};
+    cuuint32_t estr[4] = {1, 1, 1, 1};
+    EncodeTiledFn fn = reinterpret_cast<EncodeTiledFn>(ctx->encode_tiled);
+    CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<float*>(ptr), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE,
+                    op.mn_major ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
+                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        char msg[256];
+        snprintf(msg, sizeof msg,
+                 "cuTensorMapEncodeTiled failed (%d): dims {%llu,%llu,%llu,%llu} ld %lld ptr %p", (int)r,
+                 (unsigned long long)dims[0], (unsigned long long)dims[1], (unsigned long long)dims[2],
+                 (unsigned long long)dims[3], (long long)op.ld, (const void*)ptr);
+        set_error(msg);
+        return TE_ERR_CUDA;
+    }
+    return TE_OK;
+}
+
+template <int BN, int NPL, bool A_MN, bool B_MN>
+static int launch_variant(te_b200_ctx* ctx, const GemmProblem& g, cudaStream_t stream) {
+    using Cfg = TileCfg<BN, NPL>;
+    auto kernel = gemm_tf32_kernel<BN, NPL, A_MN, B_MN>;
+    static bool attr_done[16] = {};   // per device ordinal
+    if (ctx->device < 16 && !attr_done[ctx->device]) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
+        if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(max dynamic shared memory)");
+        attr_done[ctx->device] = true;
+    }
+    CUtensorMap ma, mal, mb, mbl;
+    int rc;
+    if ((rc = make_operand_map(ctx, &ma, g.a.ptr, g.a, g.K, BM, g.batch_inner, g.batch_outer))) return rc;
+    if ((rc = make_operand_map(ctx, &mb, g.b.ptr, g.b, g.K, BN, g.batch_inner, g.batch_outer))) return rc;
+    if (NPL == 2) {
+        if ((rc = make_operand_map(ctx, &mal, g.a_lo, g.a, g.K, BM, g.batch_inner, g.batch_outer))) return rc;
+        if ((rc = make_operand_map(ctx, &mbl, g.b_lo, g.b, g.K, BN, g.batch_inner, g.batch_outer))) return rc;
+    } else {
+        mal = ma;
+        mbl = mb;
+    }
+    GemmParams p;
+    p.M = (int)g.M; p.N = (int)g.N; p.K = (int)g.K;
+    p.tiles_m = (int)((g.M + BM - 1) / BM);
+    p.tiles_n = (int)((g.N + BN - 1) / BN);
+    p.batch_inner = (int)g.batch_inner;
+    p.num_batches = (int)(g.batch_inner * g.batch_outer);
+    p.a_mul_inner = (g.batch_inner > 1 && g.a.stride_inner != 0) ? 1 : 0;
+    p.a_mul_outer = (g.batch_outer > 1 && g.a.stride_outer != 0) ? 1 : 0;
+    p.b_mul_inner = (g.batch_inner > 1 && g.b.stride_inner != 0) ? 1 : 0;
+    p.b_mul_outer = (g.batch_outer > 1 && g.b.stride_outer != 0) ? 1 : 0;
+    p.ldc = g.ldc; p.c_stride_inner = g.c_stride_inner; p.c_stride_outer = g.c_stride_outer;
+    p.c = g.c; p.preact = g.preact; p.bias = g.bias;
+    p.alpha = g.alpha; p.scale_mode = g.scale_mode; p.epilogue = g.epilogue;
+    p.status = ctx->d_status;
+    const long long total = (long long)p.tiles_m * p.tiles_n * p.num_batches;
+    const int grid = (int)(total < ctx->sm_count ? total : ctx->sm_count);
+    kernel<<<grid, 192, Cfg::SMEM_BYTES, stream>>>(ma, mal, mb, mbl, p);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return cuda_fail(e, "gemm_tf32_kernel launch");
+    ctx->launches += 1;
+    return TE_OK;
+}
+
+template <int BN>
+static int launch_bn(te_b200_ctx* ctx, const GemmProblem& g, cudaStream_t stream) {
+    if (g.a_lo) {   // 3xTF32: planes are always packed K-major
+        return launch_variant<BN, 2, false, false>(ctx, g, stream);
+    }
+    if (!g.a.mn_major && !g.b.mn_major) return launch_variant<BN, 1, false, false>(ctx, g, stream);
+    if (!g.a.mn_major && g.b.mn_major) return launch_variant<BN, 1, false, true>(ctx, g, stream);
+    if (g.a.mn_major && !g.b.mn_major) return launch_variant<BN, 1, true, false>(ctx, g, stream);
+    return launch_variant<BN, 1, true, true>(ctx, g, stream);
+}
+
+int launch_gemm(te_b200_ctx* ctx, const GemmProblem& g, cudaStream_t stream) {
+    if (g.a_lo) {
+        if (g.N > 64) return launch_bn<128>(ctx, g, stream);
+        return launch_bn<64>(ctx, g, stream);
+    }
+    if (g.N > 128) return launch_bn<256>(ctx, g, stream);
+    if (g.N > 64) return launch_bn<128>(ctx, g, stream);
+    return launch_bn<64>(ctx, g, stream);
+}
+
+}  // namespace te

@@ -1,0 +1,102 @@
+// Operand packing pre-pass.
+//
+// Rewrites one GEMM operand (any of: row-/column-major, any leading dimension, two-level batch
+// strides) as dense K-major planes  dst[batch][row][kp]  with kp = K rounded up to 4 floats, so that
+// the TMA path of the GEMM kernel can always address it.  Two uses:
+//   * copy  - an operand whose base address or strides are not multiples of 16 bytes (for example
+//             the [tokens, 65] logits gradient of the language-model head);
+//   * split - 3xTF32: hi = round-to-nearest tf32(x), lo = round-to-nearest tf32(x - hi); both planes
+//             are exactly representable in tf32, so the tensor core consumes them unchanged.
+// Pure streaming work: bound by HBM bandwidth (reads 4 B, writes 4 or 8 B per element).
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "te_internal.h"
+
+namespace te {
+
+__device__ __forceinline__ float to_tf32_rn(float x) {
+    uint32_t u;
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(u) : "f"(x));
+    return __uint_as_float(u & 0xFFFFE000u);
+}
+
+struct PackParams {
+    const float* src;
+    float* dst_hi;
+    float* dst_lo;
+    long long rows, K, kp, ld;
+    long long stride_inner, stride_outer;   // source batch strides (elements)
+    int batch_inner;                         // packed batches are enumerated outer-major
+};
+
+template <bool MN_MAJOR, bool SPLIT>
+__global__ void __launch_bounds__(256) pack_operand_kernel(const PackParams p) {
+    __shared__ float tile[32][33];
+    const int tx = threadIdx.x, ty = threadIdx.y;          // 32 x 8
+    const long long k0 = (long long)blockIdx.x * 32;
+    const long long r0 = (long long)blockIdx.y * 32;
+    const int batch = blockIdx.z;
+    const int bo = batch / p.batch_inner, bi = batch - bo * p.batch_inner;
+    const float* src = p.src + bo * p.stride_outer + bi * p.stride_inner;
+    const long long plane = (long long)batch * p.rows * p.kp;
+
+    if (MN_MAJOR) {
+        // coalesced along the row index; transpose through shared memory
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const long long k = k0 + ty + 8 * i, r = r0 + tx;
+            tile[ty + 8 * i][tx] = (k < p.K && r < p.rows) ? src[k * p.ld + r] : 0.0f;
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const long long r = r0 + ty + 8 * i, k = k0 + tx;
+        if (r >= p.rows || k >= p.kp) continue;
+        float x;
+        if (MN_MAJOR) x = tile[tx][ty + 8 * i];
+        else x = (k < p.K) ? src[r * p.ld + k] : 0.0f;
+        const long long o = plane + r * p.kp + k;
+        if (SPLIT) {
+            const float hi = to_tf32_rn(x);
+            p.dst_hi[o] = hi;
+            p.dst_lo[o] = to_tf32_rn(x - hi);
+        } else {
+            p.dst_hi[o] = x;
+        }
+    }
+}
+
+int launch_pack(te_b200_ctx* ctx, const Operand& src, int64_t K, int64_t batch_inner, int64_t batch_outer,
+                float* dst_hi, float* dst_lo, bool split, cudaStream_t stream) {
+    // Broadcast levels are packed once.
+    const int64_t bi = (batch_inner > 1 && src.stride_inner != 0) ? batch_inner : 1;
+    const int64_t bo = (batch_outer > 1 && src.stride_outer != 0) ? batch_outer : 1;
+    PackParams p;
+    p.src = src.ptr; p.dst_hi = dst_hi; p.dst_lo = dst_lo;
+    p.rows = src.rows; p.K = K; p.kp = (K + 3) & ~int64_t(3); p.ld = src.ld;
+    p.stride_inner = src.stride_inner; p.stride_outer = src.stride_outer;
+    p.batch_inner = (int)bi;
+    if (src.rows == 0 || K == 0) return TE_OK;
+    const int64_t nb = bi * bo;
+    if (nb > 65535 || (src.rows + 31) / 32 > 65535) {
+        set_error("pack: operand has more than 65535 batches or row blocks");
+        return TE_ERR_BAD_ARGUMENT;
+    }
+    dim3 grid((unsigned)((p.kp + 31) / 32), (unsigned)((src.rows + 31) / 32), (unsigned)nb);
+    dim3 block(32, 8);
+    if (src.mn_major) {
+        if (split) pack_operand_kernel<true, true><<<grid, block, 0, stream>>>(p);
+        else pack_operand_kernel<true, false><<<grid, block, 0, stream>>>(p);
+    } else {
+        if (split) pack_operand_kernel<false, true><<<grid, block, 0, stream>>>(p);
+        else pack_operand_kernel<false, false><<<grid, block, 0, stream>>>(p);
+    }
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return cuda_fail(e, "pack_operand_kernel launch");
+    ctx->launches += 1;
+    return TE_OK;
+}
+
+}  // namespace te

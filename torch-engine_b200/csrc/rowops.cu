@@ -1,0 +1,200 @@
+// Row-wise and elementwise kernels that sit between / behind the GEMMs on the matmul path:
+// last-dim softmax (forward, backward), tanh-GELU (forward, backward) and the column sum that
+// produces a bias gradient.  All are HBM-bound streaming kernels: one warp per softmax row with the
+// row held in registers (one read, one write of the row), 16-byte accesses for the elementwise ones.
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "te_internal.h"
+
+namespace te {
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+// Softmax over the last dimension with max subtraction, as Tensor::softmax does
+// (reference src/tensor/tensor.cpp:1164-1296; CUDA kernel src/cuda/elementwise_cuda.cu:2424-2448).
+// ITEMS * 32 >= cols: the row lives in registers.  ITEMS == 0: generic three-pass loop.
+template <int ITEMS>
+__global__ void __launch_bounds__(256) softmax_rows_kernel(const float* __restrict__ in, float* __restrict__ out,
+                                                           long long rows, int cols) {
+    const int lane = threadIdx.x & 31;
+    const long long warps_per_grid = (long long)gridDim.x * (blockDim.x >> 5);
+    for (long long row = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); row < rows;
+         row += warps_per_grid) {
+        const float* x = in + row * cols;
+        float* y = out + row * cols;
+        if (ITEMS > 0) {
+            float v[ITEMS > 0 ? ITEMS : 1];
+            float m = -__int_as_float(0x7f800000);
+#pragma unroll
+            for (int i = 0; i < ITEMS; ++i) {
+                const int c = lane + 32 * i;
+                v[i] = c < cols ? x[c] : -__int_as_float(0x7f800000);
+                m = fmaxf(m, v[i]);
+            }
+            m = warp_max(m);
+            float s = 0.0f;
+#pragma unroll
+            for (int i = 0; i < ITEMS; ++i) {
+                const int c = lane + 32 * i;
+                v[i] = c < cols ? expf(v[i] - m) : 0.0f;
+                s += v[i];
+            }
+            s = warp_sum(s);
+#pragma unroll
+            for (int i = 0; i < ITEMS; ++i) {
+                const int c = lane + 32 * i;
+                if (c < cols) y[c] = v[i] / s;
+            }
+        } else {
+            float m = -__int_as_float(0x7f800000);
+            for (int c = lane; c < cols; c += 32) m = fmaxf(m, x[c]);
+            m = warp_max(m);
+            float s = 0.0f;
+            for (int c = lane; c < cols; c += 32) {
+                const float e = expf(x[c] - m);
+                y[c] = e;
+                s += e;
+            }
+            s = warp_sum(s);
+            for (int c = lane; c < cols; c += 32) y[c] = y[c] / s;
+        }
+    }
+}
+
+// dx = s * (dy - <dy, s>) per row (reference src/cuda/elementwise_cuda.cu:2450-2467).
+__global__ void __launch_bounds__(256) softmax_backward_rows_kernel(const float* __restrict__ s,
+                                                                    const float* __restrict__ dy,
+                                                                    float* __restrict__ dx, long long rows, int cols) {
+    const int lane = threadIdx.x & 31;
+    const long long warps_per_grid = (long long)gridDim.x * (blockDim.x >> 5);
+    for (long long row = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); row < rows;
+         row += warps_per_grid) {
+        const float* sr = s + row * cols;
+        const float* gr = dy + row * cols;
+        float* o = dx + row * cols;
+        float dot = 0.0f;
+        for (int c = lane; c < cols; c += 32) dot += gr[c] * sr[c];
+        dot = warp_sum(dot);
+        for (int c = lane; c < cols; c += 32) o[c] = sr[c] * (gr[c] - dot);
+    }
+}
+
+__device__ __forceinline__ float gelu_fwd(float x) {
+    const float x3 = x * x * x;
+    return 0.5f * x * (1.0f + tanhf(0.7978845608f * (x + 0.044715f * x3)));
+}
+// Derivative as written in gelu_backward_kernel (reference src/cuda/elementwise_cuda.cu:2709-2724).
+__device__ __forceinline__ float gelu_bwd(float x, float dy) {
+    const float c = 0.7978845608f, k = 0.044715f;
+    const float z = c * (x + k * x * x * x);
+    const float t = tanhf(z);
+    const float sech_sq = 1.0f - t * t;
+    const float inner = c * (1.0f + 3.0f * k * x * x);
+    return dy * (0.5f * (1.0f + t) * (1.0f + x * sech_sq * inner));
+}
+
+__global__ void __launch_bounds__(256) gelu_kernel(const float* __restrict__ x, float* __restrict__ y, long long n) {
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) y[i] = gelu_fwd(x[i]);
+}
+__global__ void __launch_bounds__(256) gelu_backward_kernel(const float* __restrict__ x, const float* __restrict__ dy,
+                                                            float* __restrict__ dx, long long n) {
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride)
+        dx[i] = gelu_bwd(x[i], dy[i]);
+}
+
+// out[j] = sum over rows of in[i*ld + j].  One block owns 32 columns; its 32 row-lanes stride the rows,
+// then a shared-memory tree adds the 32 partials in a fixed order (deterministic, unlike an atomicAdd).
+__global__ void __launch_bounds__(1024) colsum_kernel(const float* __restrict__ in, long long rows, long long cols,
+                                                      long long ld, float* __restrict__ out) {
+    __shared__ float part[32][33];
+    const int tx = threadIdx.x, ty = threadIdx.y;
+    const long long col = (long long)blockIdx.x * 32 + tx;
+    float acc = 0.0f;
+    if (col < cols)
+        for (long long r = ty; r < rows; r += 32) acc += in[r * ld + col];
+    part[ty][tx] = acc;
+    __syncthreads();
+    for (int h = 16; h > 0; h >>= 1) {
+        if (ty < h) part[ty][tx] += part[ty + h][tx];
+        __syncthreads();
+    }
+    if (ty == 0 && col < cols) out[col] = part[0][tx];
+}
+
+static int grid_for(long long work_items, int per_block, int sm_count) {
+    long long blocks = (work_items + per_block - 1) / per_block;
+    const long long cap = (long long)sm_count * 8;
+    if (blocks > cap) blocks = cap;
+    if (blocks < 1) blocks = 1;
+    return (int)blocks;
+}
+
+int launch_softmax_rows(te_b200_ctx* ctx, const float* in, float* out, int64_t rows, int64_t cols, cudaStream_t st) {
+    if (rows == 0 || cols == 0) return TE_OK;
+    const int grid = grid_for(rows, 8, ctx->sm_count);
+    const int c = (int)cols;
+    if (cols <= 32) softmax_rows_kernel<1><<<grid, 256, 0, st>>>(in, out, rows, c);
+    else if (cols <= 64) softmax_rows_kernel<2><<<grid, 256, 0, st>>>(in, out, rows, c);
+    else if (cols <= 128) softmax_rows_kernel<4><<<grid, 256, 0, st>>>(in, out, rows, c);
+    else if (cols <= 256) softmax_rows_kernel<8><<<grid, 256, 0, st>>>(in, out, rows, c);
+    else if (cols <= 512) softmax_rows_kernel<16><<<grid, 256, 0, st>>>(in, out, rows, c);
+    else if (cols <= 1024) softmax_rows_kernel<32><<<grid, 256, 0, st>>>(in, out, rows, c);
+    else softmax_rows_kernel<0><<<grid, 256, 0, st>>>(in, out, rows, c);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return cuda_fail(e, "softmax_rows_kernel launch");
+    ctx->launches += 1;
+    return TE_OK;
+}
+
+int launch_softmax_backward_rows(te_b200_ctx* ctx, const float* s, const float* dy, float* dx, int64_t rows,
+                                 int64_t cols, cudaStream_t st) {
+    if (rows == 0 || cols == 0) return TE_OK;
+    softmax_backward_rows_kernel<<<grid_for(rows, 8, ctx->sm_count), 256, 0, st>>>(s, dy, dx, rows, (int)cols);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return cuda_fail(e, "softmax_backward_rows_kernel launch");
+    ctx->launches += 1;
+    return TE_OK;
+}
+
+int launch_gelu(te_b200_ctx* ctx, const float* x, float* y, int64_t n, cudaStream_t st) {
+    if (n == 0) return TE_OK;
+    gelu_kernel<<<grid_for(n, 256, ctx->sm_count), 256, 0, st>>>(x, y, n);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return cuda_fail(e, "gelu_kernel launch");
+    ctx->launches += 1;
+    return TE_OK;
+}
+
+int launch_gelu_backward(te_b200_ctx* ctx, const float* x, const float* dy, float* dx, int64_t n, cudaStream_t st) {
+    if (n == 0) return TE_OK;
+    gelu_backward_kernel<<<grid_for(n, 256, ctx->sm_count), 256, 0, st>>>(x, dy, dx, n);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return cuda_fail(e, "gelu_backward_kernel launch");
+    ctx->launches += 1;
+    return TE_OK;
+}
+
+int launch_colsum(te_b200_ctx* ctx, const float* in, int64_t rows, int64_t cols, int64_t ld, float* out,
+                  cudaStream_t st) {
+    if (cols == 0) return TE_OK;
+    dim3 block(32, 32);
+    colsum_kernel<<<(unsigned)((cols + 31) / 32), block, 0, st>>>(in, rows, cols, ld, out);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return cuda_fail(e, "colsum_kernel launch");
+    ctx->launches += 1;
+    return TE_OK;
+}
+
+}  // namespace te

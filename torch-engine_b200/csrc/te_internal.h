@@ -1,0 +1,76 @@
+// Internal (C++) interfaces between the C-ABI layer and the CUDA translation units.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <string>
+#include "te_b200.h"
+
+namespace te {
+
+// One GEMM operand as the kernel sees it: logical [rows, K] where rows is the M (for A) or
+// N (for B) extent.  mn_major == false: K is the contiguous index (element (r,k) at r*ld + k).
+// mn_major == true: the row index is contiguous (element (r,k) at k*ld + r).
+struct Operand {
+    const float* ptr = nullptr;
+    bool mn_major = false;
+    int64_t rows = 0;
+    int64_t ld = 0;
+    int64_t stride_inner = 0, stride_outer = 0;  // elements; 0 = broadcast over that batch level
+};
+
+struct GemmProblem {
+    int64_t M = 0, N = 0, K = 0;
+    int64_t batch_inner = 1, batch_outer = 1;
+    Operand a, b;                 // raw fp32 (TF32 mode) or the tf32 "hi" planes (3xTF32)
+    const float* a_lo = nullptr;  // 3xTF32 only: "lo" planes with the geometry of a / b
+    const float* b_lo = nullptr;
+    float* c = nullptr;
+    int64_t ldc = 0, c_stride_inner = 0, c_stride_outer = 0;
+    float* preact = nullptr;
+    const float* bias = nullptr;
+    float alpha = 1.0f;
+    int scale_mode = TE_SCALE_NONE;
+    int epilogue = TE_EPI_NONE;
+};
+
+}  // namespace te
+
+struct te_b200_ctx {
+    int device = 0;
+    int sm_count = 0;
+    void* workspace = nullptr;
+    size_t workspace_bytes = 0;
+    int* d_status = nullptr;      // device word written by a kernel whose bounded wait gave up
+    int64_t launches = 0;
+    void* encode_tiled = nullptr; // cuTensorMapEncodeTiled, resolved through the runtime
+    void* host_stage = nullptr;   // grow-only device staging used by the host-buffer entry point
+    size_t host_stage_bytes = 0;
+};
+
+namespace te {
+
+void set_error(const std::string& msg);
+int cuda_fail(cudaError_t e, const char* what);
+
+// True when TMA can address the operand in place (16-byte aligned base, strides multiple of 16 B).
+bool operand_tma_ok(const Operand& op, int64_t batch_inner, int64_t batch_outer);
+
+// gemm_sm100.cu
+int launch_gemm(te_b200_ctx* ctx, const GemmProblem& p, cudaStream_t stream);
+
+// pack.cu: writes dense K-major planes [batch_outer][batch_inner][rows][kp] (kp = K rounded up to 4).
+// split == false: dst_hi receives a copy.  split == true: dst_hi / dst_lo receive the tf32 hi / lo parts.
+int launch_pack(te_b200_ctx* ctx, const Operand& src, int64_t K, int64_t batch_inner,
+                int64_t batch_outer, float* dst_hi, float* dst_lo, bool split, cudaStream_t stream);
+
+// rowops.cu
+int launch_softmax_rows(te_b200_ctx*, const float*, float*, int64_t rows, int64_t cols, cudaStream_t);
+int launch_softmax_backward_rows(te_b200_ctx*, const float* s, const float* dy, float* dx,
+                                 int64_t rows, int64_t cols, cudaStream_t);
+int launch_gelu(te_b200_ctx*, const float*, float*, int64_t n, cudaStream_t);
+int launch_gelu_backward(te_b200_ctx*, const float* x, const float* dy, float* dx, int64_t n,
+                         cudaStream_t);
+int launch_colsum(te_b200_ctx*, const float* in, int64_t rows, int64_t cols, int64_t ld, float* out,
+                  cudaStream_t);
+
+}  // namespace te

@@ -1,0 +1,203 @@
+"""Tensor-level host mirror of the reference operators on the matmul path.
+
+Each method corresponds to one reference call and forwards to the C ABI (lib.py); torch tensors are
+used only as device-memory holders (data_ptr, shape, stride) and for the current CUDA stream.
+
+    Backend.matmul          Tensor::matmul                        (reference src/tensor/tensor.cpp:761-785)
+    Backend.linear_forward  Linear::forward (+ FeedForward GELU)  (src/nn/linear.cpp:14-23, src/nn/ffn.cpp:12-16)
+    Backend.linear_backward MatMulBackward/AddBackward/TransposeBackward of that graph (src/core/grad_fn.cpp:93-139)
+    Backend.scaled_dot      ScaledDot::forward                    (src/nn/scaledot.cpp:8-27)
+    Backend.softmax / softmax_backward / gelu / gelu_backward / colsum: the kernels between the GEMMs.
+"""
+import ctypes as C
+
+import torch
+
+from . import lib as L
+
+_PREC = {"tf32": L.TE_PREC_TF32, "3xtf32": L.TE_PREC_3XTF32, L.TE_PREC_TF32: L.TE_PREC_TF32,
+         L.TE_PREC_3XTF32: L.TE_PREC_3XTF32}
+
+
+def _prec(p):
+    try:
+        return _PREC[p]
+    except KeyError:
+        raise ValueError("precision must be 'tf32' or '3xtf32'")
+
+
+def _ptr(t):
+    return None if t is None else C.c_void_p(t.data_ptr())
+
+
+def _i64(seq):
+    n = max(len(seq), 1)
+    return (C.c_int64 * n)(*seq)
+
+
+class Backend:
+    """One per device: owns the C context (workspace, status word).  Not thread-safe; calls that use the
+    workspace (3xTF32, operands TMA cannot address) must not overlap on different streams."""
+
+    def __init__(self, device=0, workspace_bytes=2 << 30):
+        self._lib = L.load()
+        self.device = int(device)
+        h = C.c_void_p()
+        L.check(self._lib.te_b200_init(self.device, workspace_bytes, C.byref(h)))
+        self._ctx = h
+        self.torch_device = torch.device("cuda", self.device)
+
+    def close(self):
+        if getattr(self, "_ctx", None):
+            self._lib.te_b200_destroy(self._ctx)
+            self._ctx = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    # ------------------------------------------------------------------ helpers
+    def _stream(self):
+        return C.c_void_p(torch.cuda.current_stream(self.torch_device).cuda_stream)
+
+    def _check_f32_cuda(self, *ts):
+        for t in ts:
+            if t is None:
+                continue
+            if t.dtype != torch.float32:
+                raise L.BackendError(L.TE_ERR_BAD_ARGUMENT, "CUDA matmul currently only supports Float32")
+            if not t.is_cuda:
+                raise L.BackendError(L.TE_ERR_BAD_ARGUMENT, "tensor is not on the GPU; this backend has no CPU path")
+
+    @property
+    def launches(self):
+        return int(self._lib.te_b200_launch_count(self._ctx))
+
+    def check_device_status(self):
+        """Synchronises and raises if a kernel gave up a bounded wait."""
+        torch.cuda.synchronize(self.torch_device)
+        L.check(self._lib.te_b200_check_device_status(self._ctx))
+
+    # ------------------------------------------------------------------ GEMM
+    def gemm(self, desc):
+        """Raw strided-batched GEMM from a filled lib.GemmDesc."""
+        L.check(self._lib.te_b200_gemm_f32(self._ctx, C.byref(desc), self._stream()))
+
+    def gemm_host(self, desc):
+        """Same with host pointers in the descriptor (copies in, runs, copies out, synchronises)."""
+        L.check(self._lib.te_b200_gemm_f32_host(self._ctx, C.byref(desc)))
+
+    def workspace_size(self, desc):
+        n = C.c_size_t()
+        L.check(self._lib.te_b200_gemm_workspace_size(C.byref(desc), C.byref(n)))
+        return n.value
+
+    def matmul(self, a, b, precision="tf32"):
+        """a.matmul(b) with NumPy batch broadcasting; a and b may be any strided views whose last two
+        dims form a row- or column-major slice.  Returns a fresh contiguous tensor."""
+        self._check_f32_cuda(a, b)
+        out_shape = L.matmul_shape(tuple(a.shape), tuple(a.stride()), tuple(b.shape), tuple(b.stride()))
+        c = torch.empty(out_shape, dtype=torch.float32, device=a.device)
+        L.check(self._lib.te_b200_matmul_nd(
+            self._ctx, _ptr(a), _i64(a.shape), _i64(a.stride()), a.dim(),
+            _ptr(b), _i64(b.shape), _i64(b.stride()), b.dim(),
+            _ptr(c), None, None, _prec(precision), self._stream()))
+        return c
+
+    # ------------------------------------------------------------------ Linear
+    def linear_forward(self, x, w, bias=None, gelu=False, want_preact=False, precision="tf32"):
+        """y = act(x . w^T + bias); x [..., in] contiguous, w [out, in].  Returns y or (y, preact)."""
+        self._check_f32_cuda(x, w, bias)
+        x = x.contiguous()
+        out_f, in_f = w.shape
+        rows = x.numel() // in_f if in_f else 0
+        y = torch.empty(x.shape[:-1] + (out_f,), dtype=torch.float32, device=x.device)
+        pre = torch.empty_like(y) if want_preact else None
+        L.check(self._lib.te_b200_linear_forward(self._ctx, _ptr(x), _ptr(w.contiguous()), _ptr(bias), _ptr(y),
+                                                 _ptr(pre), rows, in_f, out_f, int(bool(gelu)), _prec(precision),
+                                                 self._stream()))
+        return (y, pre) if want_preact else y
+
+    def linear_backward(self, x, w, dy, precision="tf32", need_dx=True, need_dw=True, need_db=True):
+        """(dx, dw[out,in], db[out]) for y = x . w^T + b given dy."""
+        self._check_f32_cuda(x, w, dy)
+        x = x.contiguous()
+        dy = dy.contiguous()
+        out_f, in_f = w.shape
+        rows = x.numel() // in_f if in_f else 0
+        dx = torch.empty_like(x) if need_dx else None
+        dw = torch.empty_like(w) if need_dw else None
+        db = torch.empty(out_f, dtype=torch.float32, device=x.device) if need_db else None
+        L.check(self._lib.te_b200_linear_backward(self._ctx, _ptr(x), _ptr(w.contiguous()), _ptr(dy), _ptr(dx),
+                                                  _ptr(dw), _ptr(db), rows, in_f, out_f, _prec(precision),
+                                                  self._stream()))
+        return dx, dw, db
+
+    # ------------------------------------------------------------------ attention
+    def scaled_dot(self, q, k, v, precision="tf32"):
+        """softmax(q . k^T / sqrt(d)) . v for [B,H,T,d] views with unit last-dim stride (for example the
+        MultiHeadAttention head views with strides [T*E, d, E, 1]).  Returns (o [B,H,T,d] contiguous, p)."""
+        self._check_f32_cuda(q, k, v)
+        if q.dim() != 4 or q.shape != k.shape or q.shape != v.shape:
+            raise L.BackendError(L.TE_ERR_BAD_ARGUMENT, "scaled_dot expects q, k, v of one [B,H,T,d] shape")
+        for t in (q, k, v):
+            if t.stride(3) != 1:
+                raise L.BackendError(L.TE_ERR_UNSUPPORTED_LAYOUT, L.status_string(L.TE_ERR_UNSUPPORTED_LAYOUT))
+        B, H, T, d = q.shape
+        p = torch.empty((B, H, T, T), dtype=torch.float32, device=q.device)
+        o = torch.empty((B, H, T, d), dtype=torch.float32, device=q.device)
+        desc = L.AttnDesc()
+        desc.B, desc.H, desc.T, desc.d = B, H, T, d
+        desc.q, desc.k, desc.v = q.data_ptr(), k.data_ptr(), v.data_ptr()
+        desc.q_strides = (C.c_int64 * 3)(*q.stride()[:3])
+        desc.k_strides = (C.c_int64 * 3)(*k.stride()[:3])
+        desc.v_strides = (C.c_int64 * 3)(*v.stride()[:3])
+        desc.p_out, desc.o = p.data_ptr(), o.data_ptr()
+        desc.o_strides = (C.c_int64 * 3)(*o.stride()[:3])
+        desc.precision = _prec(precision)
+        L.check(self._lib.te_b200_attention_forward(self._ctx, C.byref(desc), self._stream()))
+        return o, p
+
+    # ------------------------------------------------------------------ row / elementwise ops
+    def softmax(self, x):
+        self._check_f32_cuda(x)
+        x = x.contiguous()
+        y = torch.empty_like(x)
+        cols = x.shape[-1]
+        rows = x.numel() // cols if cols else 0
+        L.check(self._lib.te_b200_softmax_rows_f32(self._ctx, _ptr(x), _ptr(y), rows, cols, self._stream()))
+        return y
+
+    def softmax_backward(self, s, dy):
+        self._check_f32_cuda(s, dy)
+        s, dy = s.contiguous(), dy.contiguous()
+        dx = torch.empty_like(s)
+        cols = s.shape[-1]
+        rows = s.numel() // cols if cols else 0
+        L.check(self._lib.te_b200_softmax_backward_rows_f32(self._ctx, _ptr(s), _ptr(dy), _ptr(dx), rows, cols,
+                                                            self._stream()))
+        return dx
+
+    def gelu(self, x):
+        self._check_f32_cuda(x)
+        x = x.contiguous()
+        y = torch.empty_like(x)
+        L.check(self._lib.te_b200_gelu_f32(self._ctx, _ptr(x), _ptr(y), x.numel(), self._stream()))
+        return y
+
+    def gelu_backward(self, x, dy):
+        self._check_f32_cuda(x, dy)
+        x, dy = x.contiguous(), dy.contiguous()
+        dx = torch.empty_like(x)
+        L.check(self._lib.te_b200_gelu_backward_f32(self._ctx, _ptr(x), _ptr(dy), _ptr(dx), x.numel(), self._stream()))
+        return dx
+
+    def colsum(self, x2d):
+        self._check_f32_cuda(x2d)
+        x2d = x2d.contiguous()
+        rows, cols = x2d.shape
+        out = torch.empty(cols, dtype=torch.float32, device=x2d.device)
+        L.check(self._lib.te_b200_colsum_f32(self._ctx, _ptr(x2d), rows, cols, cols, _ptr(out), self._stream()))
+        return out
