@@ -164,12 +164,45 @@ class Oracle:
         return self.matmul(p, v), p
 
 
+class SeededRng:
+    """std::mt19937 / std::mt19937_64 streams with the C++ standard distributions, as the reference's
+    benchmarks and tests draw their inputs (seed 42, A first then B from the same generator)."""
+
+    def __init__(self, seed=42):
+        if not os.path.exists(ORACLE_PATH):
+            build()
+        self.lib = C.CDLL(ORACLE_PATH)
+        self.lib.oracle_rng_create.restype = C.c_void_p
+        self.h = C.c_void_p(self.lib.oracle_rng_create(C.c_uint64(seed)))
+
+    def __del__(self):
+        try:
+            self.lib.oracle_rng_destroy(self.h)
+        except Exception:
+            pass
+
+    def uniform(self, shape, lo=-1.0, hi=1.0):
+        out = np.empty(shape, dtype=np.float32)
+        self.lib.oracle_rng_uniform_f32(self.h, _fptr(out), C.c_int64(out.size), C.c_float(lo), C.c_float(hi))
+        return out
+
+    def normal(self, shape, mean=0.0, std=1.0):
+        out = np.empty(shape, dtype=np.float32)
+        self.lib.oracle_rng_normal_f32(self.h, _fptr(out), C.c_int64(out.size), C.c_float(mean), C.c_float(std))
+        return out
+
+    def tokens(self, shape, bound):
+        out = np.empty(shape, dtype=np.int64)
+        self.lib.oracle_rng_tokens_i64(self.h, _fptr(out), C.c_int64(out.size), C.c_int64(bound))
+        return out
+
+
 class RefView(C.Structure):
     _fields_ = [("ndim", C.c_int32), ("shape", C.c_int64 * 8), ("view_ndim", C.c_int32), ("view_shape", C.c_int64 * 8),
-                ("t1", C.c_int32), ("t2", C.c_int32)]
+                ("t1", C.c_int32), ("t2", C.c_int32), ("t3", C.c_int32), ("t4", C.c_int32)]
 
 
-def ref_view(shape, view=None, transpose=None):
+def ref_view(shape, view=None, transpose=None, transpose2=None):
     v = RefView()
     v.ndim = len(shape)
     for i, s in enumerate(shape):
@@ -178,6 +211,7 @@ def ref_view(shape, view=None, transpose=None):
     for i, s in enumerate(view or ()):
         v.view_shape[i] = s
     v.t1, v.t2 = transpose if transpose else (-1, -1)
+    v.t3, v.t4 = transpose2 if transpose2 else (-1, -1)
     return v
 
 

@@ -24,13 +24,15 @@ namespace {
 
 thread_local std::string g_err;
 
-// An operand recipe: contiguous base tensor -> optional view(new shape) -> optional transpose_view(t1, t2).
+// An operand recipe: contiguous base tensor -> optional view(new shape) -> optional transpose_view(t1, t2)
+// -> optional second transpose_view(t3, t4).
 struct RefView {
     int32_t ndim;
     int64_t shape[8];
     int32_t view_ndim;      // 0 = no view
     int64_t view_shape[8];
     int32_t t1, t2;         // -1 = no transpose
+    int32_t t3, t4;         // -1 = no second transpose
 };
 
 Tensor from_host(const float* data, const std::vector<int64_t>& shape) {
@@ -43,6 +45,7 @@ Tensor build(const float* data, const RefView& v) {
     Tensor t = from_host(data, std::vector<int64_t>(v.shape, v.shape + v.ndim));
     if (v.view_ndim > 0) t = t.view(std::vector<int64_t>(v.view_shape, v.view_shape + v.view_ndim));
     if (v.t1 >= 0) t = t.transpose_view((size_t)v.t1, (size_t)v.t2);
+    if (v.t3 >= 0) t = t.transpose_view((size_t)v.t3, (size_t)v.t4);
     return t;
 }
 
@@ -175,6 +178,7 @@ REF_API int ref_scaled_dot(const float* q, const RefView* vq, const float* k, co
         auto apply = [](Tensor t, const RefView& r) {
             if (r.view_ndim > 0) t = t.view(std::vector<int64_t>(r.view_shape, r.view_shape + r.view_ndim));
             if (r.t1 >= 0) t = t.transpose_view((size_t)r.t1, (size_t)r.t2);
+            if (r.t3 >= 0) t = t.transpose_view((size_t)r.t3, (size_t)r.t4);
             return t;
         };
         ScaledDot att;

@@ -1,0 +1,144 @@
+"""Host-side logic of the C-ABI library that needs no GPU: symbol export, shape/broadcast rules and error
+texts of Tensor::matmul, descriptor validation, workspace sizing, shard ranges, and the loud failure when
+no GPU is present."""
+import ctypes as C
+import os
+import re
+
+import numpy as np
+import pytest
+
+from torch_engine_b200 import lib as L
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_library_exports_every_declared_symbol():
+    header = open(os.path.join(ROOT, "include", "te_b200.h")).read()
+    declared = set(re.findall(r"TE_API\s+[\w\s\*]+?\b(te_b200_\w+)\s*\(", header))
+    assert len(declared) >= 19
+    lib = L.load()
+    for name in sorted(declared):
+        assert hasattr(lib, name), name
+    assert declared == set(L.SIGNATURES), declared ^ set(L.SIGNATURES)
+
+
+def test_struct_sizes_match_header_layout():
+    # 64-bit fields first, then the int32 pairs: no padding surprises between C and ctypes
+    assert C.sizeof(L.GemmDesc) == 8 * 3 + 8 * 3 + 8 * 3 + 4 * 2 + 8 * 2 + 8 * 6 + 4 * 3 + 4 + 8 * 2 + 4 * 2
+    assert C.sizeof(L.AttnDesc) == 8 * 4 + 8 * 3 + 8 * 9 + 8 * 2 + 8 * 3 + 8
+
+
+@pytest.mark.parametrize("a,b", [((2, 3), (3, 4)), ((2, 2, 3), (2, 3, 2)), ((1, 2, 3), (3, 3, 4)), ((2, 1, 4, 3), (5, 3, 6)),
+                                 ((4, 6, 8), (8, 10)), ((7, 1, 2, 5, 6), (3, 1, 6, 2))])
+def test_result_shape_matches_numpy_broadcasting(a, b):
+    def strides(s):
+        st, run = [], 1
+        for d in reversed(s):
+            st.append(run)
+            run *= d
+        return tuple(reversed(st))
+    assert L.matmul_shape(a, strides(a), b, strides(b)) == np.matmul(np.zeros(a), np.zeros(b)).shape
+
+
+@pytest.mark.parametrize("a,b,code,msg", [
+    ((3,), (3, 2), L.TE_ERR_SHAPE_NDIM, "Matmul requires tensors with at least 2 dimensions"),
+    ((2, 3), (2, 2), L.TE_ERR_SHAPE_INNER, "Inner dimensions must match for matmul"),
+    ((3, 2, 3), (2, 3, 4), L.TE_ERR_SHAPE_BROADCAST, "Batch dimensions are not broadcastable"),
+    ((2, 2, 3), (3, 3, 4), L.TE_ERR_SHAPE_BROADCAST, "Batch dimensions are not broadcastable"),
+])
+def test_shape_errors_repeat_the_reference_text(a, b, code, msg):
+    with pytest.raises(L.BackendError) as e:
+        L.matmul_shape(a, (1,) * len(a), b, (1,) * len(b))
+    assert e.value.status == code and str(e.value) == msg
+    assert L.status_string(code) == msg
+
+
+def test_unsupported_layout_text():
+    assert L.status_string(L.TE_ERR_UNSUPPORTED_LAYOUT) == "CUDA matmul only supports row- or column-major 2D slices"
+
+
+def _desc(**kw):
+    d = L.GemmDesc()
+    d.M, d.N, d.K = 64, 64, 64
+    d.a = d.b = d.c = 0x1000
+    d.lda = d.ldb = d.ldc = 64
+    d.batch_outer = d.batch_inner = 1
+    d.alpha = 1.0
+    for k, v in kw.items():
+        setattr(d, k, v)
+    return d
+
+
+def _ws(d):
+    n = C.c_size_t()
+    rc = L.load().te_b200_gemm_workspace_size(C.byref(d), C.byref(n))
+    return rc, n.value
+
+
+def test_descriptor_validation():
+    assert _ws(_desc())[0] == L.TE_OK
+    assert _ws(_desc(M=-1))[0] == L.TE_ERR_BAD_ARGUMENT
+    assert _ws(_desc(batch_inner=0))[0] == L.TE_ERR_BAD_ARGUMENT
+    assert _ws(_desc(a_major=2))[0] == L.TE_ERR_UNSUPPORTED_LAYOUT
+    assert _ws(_desc(lda=8))[0] == L.TE_ERR_UNSUPPORTED_LAYOUT       # ld smaller than the row
+    assert _ws(_desc(precision=7))[0] == L.TE_ERR_BAD_ARGUMENT
+    assert _ws(_desc(epilogue=L.TE_EPI_BIAS))[0] == L.TE_ERR_BAD_ARGUMENT   # bias epilogue without a bias
+    assert _ws(_desc(c=0))[0] == L.TE_ERR_BAD_ARGUMENT
+    assert _ws(_desc(a_stride_inner=-4))[0] == L.TE_ERR_BAD_ARGUMENT
+
+
+def test_workspace_sizing():
+    # aligned operands in TF32 mode are read in place
+    assert _ws(_desc()) == (L.TE_OK, 0)
+    # 3xTF32 packs hi+lo planes of both operands: 2 * 2 * 64*64*4 bytes
+    assert _ws(_desc(precision=L.TE_PREC_3XTF32)) == (L.TE_OK, 4 * 64 * 64 * 4)
+    # a leading dimension that is not a multiple of 4 floats cannot be addressed by TMA -> one packed copy of A
+    rc, n = _ws(_desc(M=64, K=65, N=64, lda=65, ldb=64))
+    assert rc == L.TE_OK and n == 64 * 68 * 4
+    # a misaligned base pointer likewise
+    assert _ws(_desc(b=0x1004))[1] == 64 * 64 * 4
+    # broadcast operands are packed once
+    rc, n = _ws(_desc(precision=L.TE_PREC_3XTF32, batch_inner=8, a_stride_inner=64 * 64, b_stride_inner=0,
+                      c_stride_inner=64 * 64))
+    assert n == 2 * (8 + 1) * 64 * 64 * 4
+    # empty problems need nothing
+    assert _ws(_desc(M=0))[1] == 0
+
+
+@pytest.mark.parametrize("total,world,align", [(8192, 8, 256), (8192, 4, 256), (65, 4, 1), (16, 8, 1), (16, 3, 1), (1000, 8, 128),
+                                               (5, 8, 1), (0, 2, 1)])
+def test_shard_ranges_partition_exactly(total, world, align):
+    covered = 0
+    for r in range(world):
+        b, n = L.shard_range(total, world, r, align)
+        assert b == covered and n >= 0
+        if n and b + n < total:
+            assert n % align == 0
+        covered += n
+    assert covered == total
+
+
+def test_shard_range_rejects_bad_arguments():
+    for args in [(-1, 2, 0, 1), (8, 0, 0, 1), (8, 2, 2, 1), (8, 2, 0, 0)]:
+        with pytest.raises(L.BackendError):
+            L.shard_range(*args)
+
+
+def test_init_fails_loudly_without_gpu():
+    import torch
+    if torch.cuda.is_available():
+        pytest.skip("a GPU is present")
+    h = C.c_void_p()
+    rc = L.load().te_b200_init(0, 1 << 20, C.byref(h))
+    assert rc == L.TE_ERR_NO_DEVICE and not h.value
+    assert b"no CPU path" in L.load().te_b200_last_error()
+    from torch_engine_b200 import ops
+    with pytest.raises(L.BackendError):
+        ops.Backend(0)
+
+
+def test_null_context_is_rejected():
+    d = _desc()
+    assert L.load().te_b200_gemm_f32(None, C.byref(d), None) == L.TE_ERR_BAD_ARGUMENT
+    assert L.load().te_b200_softmax_rows_f32(None, None, None, 1, 1, None) == L.TE_ERR_BAD_ARGUMENT

@@ -24,7 +24,8 @@ __device__ __forceinline__ float warp_sum(float v) {
 // (reference src/tensor/tensor.cpp:1164-1296; CUDA kernel src/cuda/elementwise_cuda.cu:2424-2448).
 // ITEMS * 32 >= cols: the row lives in registers.  ITEMS == 0: generic three-pass loop.
 template <int ITEMS>
-__global__ void __launch_bounds__(256) softmax_rows_kernel(const float* __restrict__ in, float* __restrict__ out,
+__global__ void __launch_bounds__(256) softmax_rows_kernel(const float* in, float* out,   // in may alias out
+                                                          
                                                            long long rows, int cols) {
     const int lane = threadIdx.x & 31;
     const long long warps_per_grid = (long long)gridDim.x * (blockDim.x >> 5);
