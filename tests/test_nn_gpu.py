@@ -11,6 +11,11 @@ from oracle import binding
 from tests import golden_cases as gc
 from tests.gpu_util import TOL_REL, assert_close, rel_err
 
+# Attention chains two GEMMs around an exp: a logit error e becomes a relative error ~e in the probabilities.
+# In TF32 mode the logits (|S| up to ~6 after scaling) carry ~7e-4*|QK^T|, so the composed tolerance is looser
+# than the single-GEMM 2e-3; in 3xTF32 mode the single-GEMM bound still holds with a small factor.
+ATTN_TOL = {"tf32": 1e-2, "3xtf32": 2e-5}
+
 pytestmark = pytest.mark.gpu
 GOLD = os.path.join(os.path.dirname(__file__), "golden")
 PRECS = ["tf32", "3xtf32"]
@@ -86,7 +91,7 @@ def test_linear_golden_forward_backward(backend, nn_gold, prec):
     dx2, dw2, db2 = backend.linear_backward(x, w, dpre, precision=prec)
     assert_close(dx2.cpu().numpy(), nn_gold["linear_gelu.dx"], prec, "dX through GELU")
     assert_close(dw2.cpu().numpy(), nn_gold["linear_gelu.dw"], prec, "dW through GELU")
-    assert np.abs(db2.cpu().numpy() - nn_gold["linear_gelu.db"]).max() <= 1e-3
+    assert_close(db2.cpu().numpy(), nn_gold["linear_gelu.db"], prec, "db through GELU")
     backend.check_device_status()
 
 
@@ -116,10 +121,10 @@ def test_scaled_dot_golden_contiguous_and_head_views(backend, nn_gold, prec):
     B, H, T, d = s["B"], s["H"], s["T"], s["d"]
     q, k, v = (dev(s[n]) for n in "qkv")
     o, p = backend.scaled_dot(q.view(B, H, T, d), k.view(B, H, T, d), v.view(B, H, T, d), precision=prec)
-    assert_close(o.cpu().numpy(), nn_gold["scaled_dot_contig.o"], prec, "contiguous")
+    assert rel_err(o.cpu().numpy(), nn_gold["scaled_dot_contig.o"]) <= ATTN_TOL[prec]
     heads = lambda t: t.view(B, T, H, d).transpose(1, 2)     # strides [T*E, d, E, 1]
     o2, _ = backend.scaled_dot(heads(q), heads(k), heads(v), precision=prec)
-    assert_close(o2.cpu().numpy(), nn_gold["scaled_dot_views.o"], prec, "head views")
+    assert rel_err(o2.cpu().numpy(), nn_gold["scaled_dot_views.o"]) <= ATTN_TOL[prec]
     assert np.abs(p.sum(dim=-1).cpu().numpy() - 1).max() <= 1e-5
 
 
@@ -133,7 +138,7 @@ def test_config2_attention_full_size(backend, oracle, prec):
     backend.check_device_status()
     sub = slice(0, 3)      # the oracle is single-threaded: check three batch entries (36 heads) in full
     o_ref, p_ref = oracle.scaled_dot(q[sub], k[sub], v[sub])
-    assert_close(o[sub].cpu().numpy(), o_ref, prec, "O")
+    assert rel_err(o[sub].cpu().numpy(), o_ref) <= ATTN_TOL[prec]
     # probabilities: softmax amplifies a logit error e to ~e*p; logits are O(10) here
     assert np.abs(p[sub].cpu().numpy() - p_ref).max() <= (3e-2 if prec == "tf32" else 2e-5)
     # batch-sharded evaluation (what each GPU does) equals the unsharded one

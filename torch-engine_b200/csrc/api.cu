@@ -93,9 +93,6 @@ static void operands_from_desc(const te_gemm_desc* d, Operand& a, Operand& b) {
     a.stride_inner = d->a_stride_inner; a.stride_outer = d->a_stride_outer;
     b.ptr = d->b; b.mn_major = (d->b_major == TE_ROW_MAJOR); b.rows = d->N; b.ld = d->ldb;
     b.stride_inner = d->b_stride_inner; b.stride_outer = d->b_stride_outer;
-    // A single row/column slice may legally carry any ld; give TMA a valid one.
-    if (a.ld < 4) a.ld = 4;
-    if (b.ld < 4) b.ld = 4;
 }
 
 static size_t workspace_need(const te_gemm_desc* d) {
@@ -107,9 +104,9 @@ static size_t workspace_need(const te_gemm_desc* d) {
         need += 2 * (size_t)plane_bytes(a, d->K, d->batch_inner, d->batch_outer);
         need += 2 * (size_t)plane_bytes(b, d->K, d->batch_inner, d->batch_outer);
     } else {
-        if (!operand_tma_ok(a, d->batch_inner, d->batch_outer))
+        if (!operand_tma_ok(a, d->K, d->batch_inner, d->batch_outer))
             need += (size_t)plane_bytes(a, d->K, d->batch_inner, d->batch_outer);
-        if (!operand_tma_ok(b, d->batch_inner, d->batch_outer))
+        if (!operand_tma_ok(b, d->K, d->batch_inner, d->batch_outer))
             need += (size_t)plane_bytes(b, d->K, d->batch_inner, d->batch_outer);
     }
     return need;
@@ -159,9 +156,9 @@ static int gemm_device(te_b200_ctx* ctx, const te_gemm_desc* d, cudaStream_t st)
             if ((rc = pack_into(ctx, ws, g.a, &g.a_lo, d->K, d->batch_inner, d->batch_outer, true, st))) return rc;
             if ((rc = pack_into(ctx, ws, g.b, &g.b_lo, d->K, d->batch_inner, d->batch_outer, true, st))) return rc;
         } else {
-            if (!operand_tma_ok(g.a, d->batch_inner, d->batch_outer))
+            if (!operand_tma_ok(g.a, d->K, d->batch_inner, d->batch_outer))
                 if ((rc = pack_into(ctx, ws, g.a, nullptr, d->K, d->batch_inner, d->batch_outer, false, st))) return rc;
-            if (!operand_tma_ok(g.b, d->batch_inner, d->batch_outer))
+            if (!operand_tma_ok(g.b, d->K, d->batch_inner, d->batch_outer))
                 if ((rc = pack_into(ctx, ws, g.b, nullptr, d->K, d->batch_inner, d->batch_outer, false, st))) return rc;
         }
     } else {

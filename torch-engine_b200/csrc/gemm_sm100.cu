@@ -19,7 +19,8 @@
 // Operands are either K-major (K contiguous: a row-major A, a column-major B) or MN-major (a
 // column-major A, a row-major B).  Both are read in place by TMA; ragged M/N/K edges rely on
 // TMA zero fill and a predicated epilogue.  In 3xTF32 mode each operand comes as two tf32 planes
-// (hi, lo) and every k-step issues lo.hi + hi.lo + hi.hi into the same accumulator.
+// (hi, lo) and every k-step issues lo.hi + hi.lo + hi.hi into the same accumulator; because the tensor
+// core's fp32 adder truncates, K is summed in chunks of 256 in TMEM and the chunks are added in registers.
 //
 // Where this sits in the reference: it is the device side of Tensor::cuda_matmul_impl_f32
 // (reference src/tensor/tensor.h:614-793), replacing cublasSgemm(/StridedBatched) and
@@ -114,6 +115,53 @@ __device__ __forceinline__ float gelu_tanh(float x) {
     return 0.5f * x * (1.0f + tanhf(0.7978845608f * (x + 0.044715f * x3)));
 }
 
+struct EpilogueRow {
+    float* c_row;      // start of this thread's output row
+    float* pre_row;    // same row of the optional pre-activation output
+    bool row_ok;       // row < M
+    bool vec_ok;       // 16-byte stores are legal
+};
+
+// scale -> (+bias) -> [store pre-activation] -> (GELU) -> store, for 32 consecutive columns of one row.
+__device__ __forceinline__ void epilogue_store32(float* v, int col0, const EpilogueRow& er, const GemmParams& p) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+        if (p.scale_mode == TE_SCALE_MUL) v[j] *= p.alpha;
+        else if (p.scale_mode == TE_SCALE_DIV) v[j] = v[j] / p.alpha;
+    }
+    if (p.bias) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+            if (col0 + j < p.N) v[j] += __ldg(p.bias + col0 + j);
+    }
+    if (!er.row_ok) return;
+    const bool full_chunk = col0 + 32 <= p.N;
+    if (er.pre_row) {
+        if (full_chunk && er.vec_ok) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 4)
+                *reinterpret_cast<float4*>(er.pre_row + col0 + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+        } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+                if (col0 + j < p.N) er.pre_row[col0 + j] = v[j];
+        }
+    }
+    if (p.epilogue == TE_EPI_BIAS_GELU) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = gelu_tanh(v[j]);
+    }
+    if (full_chunk && er.vec_ok) {
+#pragma unroll
+        for (int j = 0; j < 32; j += 4)
+            *reinterpret_cast<float4*>(er.c_row + col0 + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+    } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+            if (col0 + j < p.N) er.c_row[col0 + j] = v[j];
+    }
+}
+
 template <int BN, int NPL, bool A_MN, bool B_MN>
 __global__ void __launch_bounds__(192, 1)
 gemm_tf32_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_a_lo,
@@ -124,6 +172,9 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
     constexpr int B_PLANE_BYTES = Cfg::B_PLANE_BYTES;
     constexpr int STAGE_BYTES = Cfg::STAGE_BYTES;
     constexpr uint32_t IDESC = make_idesc_tf32(BM, BN, A_MN, B_MN);
+    constexpr bool CHUNKED = (NPL == 2);      // 3xTF32: sum K in chunks, add the chunks in registers
+    constexpr int CHUNK_KB = 8;               // k-blocks per chunk = 256 values of K
+    static_assert(!CHUNKED || BN <= 128, "chunked accumulation keeps BN floats per thread in registers");
     // Descriptor geometry.
     // K-major (TMA SWIZZLE_128B): rows of 128 B, 8-row groups 1024 B apart (SBO); one MMA advances 32 B along K.
     // MN-major (TMA SWIZZLE_128B_ATOM_32B): every k index is a 128-byte row of 32 consecutive MN elements;
@@ -248,45 +299,52 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
         // ------------------------------------------------------------ MMA issuer
         if (lane == 0) {
             int consumed = 0;
-            int local = 0;
+            int acc_idx = 0;   // accumulator hand-offs so far (one per tile, or one per K chunk when CHUNKED)
             bool ok = true;
-            for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++local) {
-                const int buf = local & 1;
-                if (!wait_bounded(bar_tmem_empty + 8 * buf, ((local >> 1) & 1) ^ 1, abort_flag, p.status,
-                                  WAIT_MMA_TMEM_EMPTY)) {
-                    ok = false;
-                    break;
-                }
-                tc_fence_after_sync();
-                const uint32_t d_tmem = tmem_base + buf * BN;
-                for (int kb = 0; kb < kblocks; ++kb, ++consumed) {
-                    const int s = consumed % STAGES;
-                    if (!wait_bounded(bar_full + 8 * s, (consumed / STAGES) & 1, abort_flag, p.status,
-                                      WAIT_MMA_FULL)) {
+            for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+                int kb = 0;
+                do {   // one pass per accumulator buffer: the whole K range, or one chunk of it
+                    const int kb_end = CHUNKED ? min(kb + CHUNK_KB, kblocks) : kblocks;
+                    const int buf = acc_idx & 1;
+                    if (!wait_bounded(bar_tmem_empty + 8 * buf, ((acc_idx >> 1) & 1) ^ 1, abort_flag, p.status,
+                                      WAIT_MMA_TMEM_EMPTY)) {
                         ok = false;
                         break;
                     }
                     tc_fence_after_sync();
-                    const uint32_t sa = ring + s * STAGE_BYTES;
-                    const uint32_t sb = sa + NPL * A_PLANE_BYTES;
-#pragma unroll
-                    for (int j = 0; j < BK / UMMA_K; ++j) {
-                        const uint64_t a_hi = make_smem_desc(sa + j * A_KSTEP, A_LBO, A_SBO, A_LAYOUT);
-                        const uint64_t b_hi = make_smem_desc(sb + j * B_KSTEP, B_LBO, B_SBO, B_LAYOUT);
-                        const uint32_t acc0 = (kb | j) != 0;
-                        if (NPL == 2) {
-                            const uint64_t a_lo = make_smem_desc(sa + A_PLANE_BYTES + j * A_KSTEP, A_LBO, A_SBO, A_LAYOUT);
-                            const uint64_t b_lo = make_smem_desc(sb + B_PLANE_BYTES + j * B_KSTEP, B_LBO, B_SBO, B_LAYOUT);
-                            umma_tf32(d_tmem, a_lo, b_hi, IDESC, acc0);   // small terms first
-                            umma_tf32(d_tmem, a_hi, b_lo, IDESC, 1);
-                            umma_tf32(d_tmem, a_hi, b_hi, IDESC, 1);
-                        } else {
-                            umma_tf32(d_tmem, a_hi, b_hi, IDESC, acc0);
+                    const uint32_t d_tmem = tmem_base + buf * BN;
+                    const int kb_first = kb;
+                    for (; kb < kb_end; ++kb, ++consumed) {
+                        const int s = consumed % STAGES;
+                        if (!wait_bounded(bar_full + 8 * s, (consumed / STAGES) & 1, abort_flag, p.status,
+                                          WAIT_MMA_FULL)) {
+                            ok = false;
+                            break;
                         }
+                        tc_fence_after_sync();
+                        const uint32_t sa = ring + s * STAGE_BYTES;
+                        const uint32_t sb = sa + NPL * A_PLANE_BYTES;
+#pragma unroll
+                        for (int j = 0; j < BK / UMMA_K; ++j) {
+                            const uint64_t a_hi = make_smem_desc(sa + j * A_KSTEP, A_LBO, A_SBO, A_LAYOUT);
+                            const uint64_t b_hi = make_smem_desc(sb + j * B_KSTEP, B_LBO, B_SBO, B_LAYOUT);
+                            const uint32_t acc0 = ((kb - kb_first) | j) != 0;
+                            if (NPL == 2) {
+                                const uint64_t a_lo = make_smem_desc(sa + A_PLANE_BYTES + j * A_KSTEP, A_LBO, A_SBO, A_LAYOUT);
+                                const uint64_t b_lo = make_smem_desc(sb + B_PLANE_BYTES + j * B_KSTEP, B_LBO, B_SBO, B_LAYOUT);
+                                umma_tf32(d_tmem, a_lo, b_hi, IDESC, acc0);   // small terms first
+                                umma_tf32(d_tmem, a_hi, b_lo, IDESC, 1);
+                                umma_tf32(d_tmem, a_hi, b_hi, IDESC, 1);
+                            } else {
+                                umma_tf32(d_tmem, a_hi, b_hi, IDESC, acc0);
+                            }
+                        }
+                        umma_commit(bar_empty + 8 * s);   // stage reusable once these MMAs have read it
                     }
-                    umma_commit(bar_empty + 8 * s);   // stage reusable once these MMAs have read it
-                }
-                if (ok) umma_commit(bar_tmem_full + 8 * buf);
+                    if (!ok) break;
+                    umma_commit(bar_tmem_full + 8 * buf);
+                    ++acc_idx;
+                } while (kb < kblocks);
             }
             // All MMAs issued by this thread must be finished before TMEM is freed.
             umma_commit(bar_teardown);
@@ -300,81 +358,88 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
         }
     } else {
         // ------------------------------------------------------------ epilogue (warps 0-3)
-        int local = 0;
-        for (int t = blockIdx.x; t < total_tiles; t += gridDim.x, ++local) {
+        int acc_idx = 0;
+        bool ok = true;
+        for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
             int batch, m_blk, n_blk;
             tile_coords(t, p, batch, m_blk, n_blk);
             const int bo = batch / p.batch_inner, bi = batch - bo * p.batch_inner;
-            const int buf = local & 1;
-            bool ok = wait_bounded(bar_tmem_full + 8 * buf, (local >> 1) & 1, abort_flag, p.status,
-                                   WAIT_EPI_TMEM_FULL);
-            ok = __all_sync(0xffffffffu, ok);
-            if (!ok) break;
-            tc_fence_after_sync();
-
             const int row = m_blk * BM + warp * 32 + lane;
             const int n0 = n_blk * BN;
             const long long batch_off = (long long)bo * p.c_stride_outer + (long long)bi * p.c_stride_inner;
-            const long long c_off = batch_off + (long long)row * p.ldc;
-            float* c_row = p.c + c_off;
-            float* pre_row = p.preact ? p.preact + c_off : nullptr;
-            const bool row_ok = row < p.M;
+            EpilogueRow er;
+            er.c_row = p.c + batch_off + (long long)row * p.ldc;
+            er.pre_row = p.preact ? p.preact + batch_off + (long long)row * p.ldc : nullptr;
+            er.row_ok = row < p.M;
             // 16-byte stores need every row start aligned: aligned batch base and ldc a multiple of 4.
-            const bool vec_ok = ((p.ldc & 3) == 0) && ((reinterpret_cast<uintptr_t>(p.c + batch_off) & 15) == 0) &&
-                                (!p.preact || (reinterpret_cast<uintptr_t>(p.preact + batch_off) & 15) == 0);
-            const uint32_t t_row = tmem_base + (uint32_t(warp * 32) << 16) + buf * BN;
-#pragma unroll 1
-            for (int cc = 0; cc < BN / 32; ++cc) {
-                const int col0 = n0 + cc * 32;
-                if (col0 >= p.N) break;   // warp-uniform
-                uint32_t r[32];
-                tmem_ld_32x32b_x32(t_row + cc * 32, r);
-                tmem_ld_wait();
-                float v[32];
+            er.vec_ok = ((p.ldc & 3) == 0) && ((reinterpret_cast<uintptr_t>(p.c + batch_off) & 15) == 0) &&
+                        (!p.preact || (reinterpret_cast<uintptr_t>(p.preact + batch_off) & 15) == 0);
+            if (CHUNKED) {
+                // Two-level accumulation: the tensor core sums CHUNK_KB k-blocks in TMEM (its fp32 adder
+                // truncates, which biases long sums), the partial sums are then added here in registers with
+                // round-to-nearest.  This keeps the 3xTF32 result at FP32 accuracy for any K.
+                constexpr int NACC = CHUNKED ? BN : 1;
+                float acc[NACC];
 #pragma unroll
-                for (int j = 0; j < 32; ++j) {
-                    float x = p.K > 0 ? __uint_as_float(r[j]) : 0.0f;
-                    if (p.scale_mode == TE_SCALE_MUL) x *= p.alpha;
-                    else if (p.scale_mode == TE_SCALE_DIV) x = x / p.alpha;
-                    v[j] = x;
-                }
-                if (p.bias) {
+                for (int j = 0; j < NACC; ++j) acc[j] = 0.0f;
+                const int chunks = kblocks > 0 ? (kblocks + CHUNK_KB - 1) / CHUNK_KB : 1;
+                for (int ch = 0; ch < chunks && ok; ++ch, ++acc_idx) {
+                    const int buf = acc_idx & 1;
+                    ok = wait_bounded(bar_tmem_full + 8 * buf, (acc_idx >> 1) & 1, abort_flag, p.status,
+                                      WAIT_EPI_TMEM_FULL);
+                    ok = __all_sync(0xffffffffu, ok);
+                    if (!ok) break;
+                    tc_fence_after_sync();
+                    const uint32_t t_row = tmem_base + (uint32_t(warp * 32) << 16) + buf * BN;
+                    if (p.K > 0) {
 #pragma unroll
-                    for (int j = 0; j < 32; ++j)
-                        if (col0 + j < p.N) v[j] += __ldg(p.bias + col0 + j);
-                }
-                const bool full_chunk = col0 + 32 <= p.N;
-                if (row_ok) {
-                    if (pre_row) {
-                        if (full_chunk && vec_ok) {
+                        for (int cc = 0; cc < NACC / 32; ++cc) {
+                            if (n0 + cc * 32 < p.N) {   // warp-uniform
+                                uint32_t r[32];
+                                tmem_ld_32x32b_x32(t_row + cc * 32, r);
+                                tmem_ld_wait();
 #pragma unroll
-                            for (int j = 0; j < 32; j += 4)
-                                *reinterpret_cast<float4*>(pre_row + col0 + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
-                        } else {
-#pragma unroll
-                            for (int j = 0; j < 32; ++j)
-                                if (col0 + j < p.N) pre_row[col0 + j] = v[j];
+                                for (int j = 0; j < 32; ++j) acc[cc * 32 + j] += __uint_as_float(r[j]);
+                            }
                         }
                     }
-                    if (p.epilogue == TE_EPI_BIAS_GELU) {
+                    tc_fence_before_sync();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(bar_tmem_empty + 8 * buf);
+                }
+                if (ok) {
 #pragma unroll
-                        for (int j = 0; j < 32; ++j) v[j] = gelu_tanh(v[j]);
-                    }
-                    if (full_chunk && vec_ok) {
-#pragma unroll
-                        for (int j = 0; j < 32; j += 4)
-                            *reinterpret_cast<float4*>(c_row + col0 + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
-                    } else {
-#pragma unroll
-                        for (int j = 0; j < 32; ++j)
-                            if (col0 + j < p.N) c_row[col0 + j] = v[j];
+                    for (int cc = 0; cc < NACC / 32; ++cc) {
+                        const int col0 = n0 + cc * 32;
+                        if (col0 < p.N) epilogue_store32(&acc[cc * 32], col0, er, p);
                     }
                 }
+            } else {
+                const int buf = acc_idx & 1;
+                ok = wait_bounded(bar_tmem_full + 8 * buf, (acc_idx >> 1) & 1, abort_flag, p.status,
+                                  WAIT_EPI_TMEM_FULL);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+                tc_fence_after_sync();
+                const uint32_t t_row = tmem_base + (uint32_t(warp * 32) << 16) + buf * BN;
+#pragma unroll 1
+                for (int cc = 0; cc < BN / 32; ++cc) {
+                    const int col0 = n0 + cc * 32;
+                    if (col0 >= p.N) break;   // warp-uniform
+                    uint32_t r[32];
+                    tmem_ld_32x32b_x32(t_row + cc * 32, r);
+                    tmem_ld_wait();
+                    float v[32];
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) v[j] = p.K > 0 ? __uint_as_float(r[j]) : 0.0f;
+                    epilogue_store32(v, col0, er, p);
+                }
+                // Hand the accumulator buffer back to the MMA warp.
+                tc_fence_before_sync();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar_tmem_empty + 8 * buf);
+                ++acc_idx;
             }
-            // Hand the accumulator buffer back to the MMA warp.
-            tc_fence_before_sync();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(bar_tmem_empty + 8 * buf);
         }
     }
 
@@ -394,9 +459,10 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
                                   CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
                                   CUtensorMapFloatOOBfill);
 
-bool operand_tma_ok(const Operand& op, int64_t batch_inner, int64_t batch_outer) {
+bool operand_tma_ok(const Operand& op, int64_t K, int64_t batch_inner, int64_t batch_outer) {
     if (reinterpret_cast<uintptr_t>(op.ptr) & 15) return false;
-    if (op.ld & 3) return false;
+    const int64_t strided_extent = op.mn_major ? K : op.rows;
+    if (strided_extent > 1 && (op.ld & 3)) return false;   // the pitch of a single-line slice is never used
     if (batch_inner > 1 && (op.stride_inner & 3)) return false;
     if (batch_outer > 1 && (op.stride_outer & 3)) return false;
     return true;
@@ -412,7 +478,9 @@ static int make_operand_map(te_b200_ctx* ctx, CUtensorMap* out, const float* ptr
     const int64_t e2 = (batch_inner > 1 && op.stride_inner != 0) ? batch_inner : 1;
     const int64_t e3 = (batch_outer > 1 && op.stride_outer != 0) ? batch_outer : 1;
     cuuint64_t dims[4] = {(cuuint64_t)contiguous_extent, (cuuint64_t)strided_extent, (cuuint64_t)e2, (cuuint64_t)e3};
-    const cuuint64_t row_bytes = (cuuint64_t)op.ld * 4;
+    // A slice with one line may carry any pitch; the map still needs a legal one.
+    const int64_t ld = strided_extent > 1 ? op.ld : ((contiguous_extent + 3) & ~int64_t(3));
+    const cuuint64_t row_bytes = (cuuint64_t)ld * 4;
     cuuint64_t strides[3] = {row_bytes,
                              e2 > 1 ? (cuuint64_t)op.stride_inner * 4 : row_bytes,
                              e3 > 1 ? (cuuint64_t)op.stride_outer * 4 : row_bytes};
@@ -483,7 +551,8 @@ static int launch_variant(te_b200_ctx* ctx, const GemmProblem& g, cudaStream_t s
 template <int BN>
 static int launch_bn(te_b200_ctx* ctx, const GemmProblem& g, cudaStream_t stream) {
     if (g.a_lo) {   // 3xTF32: planes are always packed K-major
-        return launch_variant<BN, 2, false, false>(ctx, g, stream);
+        if constexpr (BN <= 128) return launch_variant<BN, 2, false, false>(ctx, g, stream);
+        else return launch_variant<128, 2, false, false>(ctx, g, stream);
     }
     if (!g.a.mn_major && !g.b.mn_major) return launch_variant<BN, 1, false, false>(ctx, g, stream);
     if (!g.a.mn_major && g.b.mn_major) return launch_variant<BN, 1, false, true>(ctx, g, stream);

@@ -53,7 +53,7 @@ void set_error(const std::string& msg);
 int cuda_fail(cudaError_t e, const char* what);
 
 // True when TMA can address the operand in place (16-byte aligned base, strides multiple of 16 B).
-bool operand_tma_ok(const Operand& op, int64_t batch_inner, int64_t batch_outer);
+bool operand_tma_ok(const Operand& op, int64_t K, int64_t batch_inner, int64_t batch_outer);
 
 // gemm_sm100.cu
 int launch_gemm(te_b200_ctx* ctx, const GemmProblem& p, cudaStream_t stream);
