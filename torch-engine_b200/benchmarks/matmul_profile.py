@@ -1,0 +1,51 @@
+"""Profiling harness: one warm-up launch and a few profiled launches of the GEMM kernel on one shape, the
+role src/benchmarks/matmul_profile.cpp (:47-50, :149-187) plays for the reference's kernels under
+src/benchmarks/run_ncu_sweep.sh.  Meant to be run under `ncu -k regex:gemm_tf32`.
+
+    python torch-engine_b200/benchmarks/matmul_profile.py --m 4096 --n 4096 --k 4096 --precision tf32 --layout nn
+"""
+import argparse
+import os
+import sys
+
+ROOT = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+sys.path.insert(0, ROOT)
+
+import torch  # noqa: E402
+
+from torch_engine_b200 import ops  # noqa: E402
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--m", type=int, default=4096)
+    ap.add_argument("--n", type=int, default=4096)
+    ap.add_argument("--k", type=int, default=4096)
+    ap.add_argument("--precision", default="tf32", choices=["tf32", "3xtf32"])
+    ap.add_argument("--layout", default="nn", choices=["nn", "nt"], help="nn: row-major B; nt: column-major B (Linear weight)")
+    ap.add_argument("--launches", type=int, default=3)
+    args = ap.parse_args()
+    be = ops.Backend(0, workspace_bytes=2 << 30)
+    g = torch.Generator(device="cuda").manual_seed(42)
+    a = torch.rand(args.m, args.k, device="cuda", generator=g) * 2 - 1
+    if args.layout == "nn":
+        b = torch.rand(args.k, args.n, device="cuda", generator=g) * 2 - 1
+    else:
+        b = (torch.rand(args.n, args.k, device="cuda", generator=g) * 2 - 1).t()
+    be.matmul(a, b, precision=args.precision)          # warm-up
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.launches):
+        c = be.matmul(a, b, precision=args.precision)
+    e1.record()
+    torch.cuda.synchronize()
+    be.check_device_status()
+    ms = e0.elapsed_time(e1) / args.launches
+    print("%dx%dx%d %s %s: %.3f ms/launch, %.1f TFLOP/s, checksum %.6e" %
+          (args.m, args.n, args.k, args.precision, args.layout, ms, 2.0 * args.m * args.n * args.k / ms / 1e9,
+           float(c[::97, ::89].double().sum())))
+
+
+if __name__ == "__main__":
+    main()
