@@ -126,6 +126,24 @@ TE_API int te_b200_matmul_nd(te_b200_ctx* ctx,
                       float* c, int64_t* out_shape, int* out_ndim,
                       int precision, te_stream_t stream);
 
+/* The 3xTF32 GEMM for callers that may not allocate device memory.  No counterpart in the reference (its
+ * launchers allocate freely, src/cuda/elementwise_cuda.cu:2302-2346).  Some hosts cannot call cudaMalloc, or let
+ * a library call it for them: a plugin inside a framework whose allocator owns the device, a loop with a
+ * fixed memory budget, code that has already started capturing its streams.  For them this entry point
+ * needs no te_b200_ctx and allocates nothing: the tf32 hi/lo planes go into one fixed device array of
+ * TE_B200_STATIC_SCRATCH_BYTES that every GPU loading this library holds until the process exits.
+ *   - d->precision must be TE_PREC_3XTF32; the device that is current when called is used.
+ *   - A problem whose planes need more than TE_B200_STATIC_SCRATCH_BYTES (see te_b200_gemm_workspace_size)
+ *     is refused with TE_ERR_WORKSPACE; nothing is launched.
+ *   - The first call on a device also resolves the array's address and the kernel attributes: make it
+ *     before any stream capture begins.
+ *   - Calls share the array, which keeps the previous call's contents; each call rewrites what it reads
+ *     (planes, status word), but calls that overlap on the GPU race.  Serialise them on one stream.
+ *   - host_status (optional) receives, asynchronously on `stream`, 0 or the code of a device-side wait
+ *     that gave up; read it after synchronising the stream. */
+#define TE_B200_STATIC_SCRATCH_BYTES (64ll << 20)
+TE_API int te_b200_gemm_3xtf32_static(const te_gemm_desc* d, te_stream_t stream, int* host_status);
+
 /* Same GEMM with HOST buffers: copies A and B to the device, runs, copies C back and
  * synchronises.  This is the call a CPU-resident reference Tensor would make
  * (Tensor::toDevice + matmul + toDevice back, src/tensor/tensor.cpp:308-340). */

@@ -15,6 +15,7 @@ TE_ROW_MAJOR, TE_COL_MAJOR = 0, 1
 TE_PREC_TF32, TE_PREC_3XTF32 = 0, 1
 TE_EPI_NONE, TE_EPI_BIAS, TE_EPI_BIAS_GELU = 0, 1, 2
 TE_SCALE_NONE, TE_SCALE_MUL, TE_SCALE_DIV = 0, 1, 2
+TE_B200_STATIC_SCRATCH_BYTES = 64 << 20
 
 c_float_p = C.POINTER(C.c_float)
 c_i64_p = C.POINTER(C.c_int64)
@@ -62,6 +63,7 @@ SIGNATURES = {
                                     C.c_void_p, c_i64_p, c_i64_p, C.c_int,
                                     C.c_void_p, c_i64_p, C.POINTER(C.c_int), C.c_int, C.c_void_p]),
     "te_b200_gemm_f32_host": (C.c_int, [C.c_void_p, C.POINTER(GemmDesc)]),
+    "te_b200_gemm_3xtf32_static": (C.c_int, [C.POINTER(GemmDesc), C.c_void_p, C.POINTER(C.c_int)]),
     "te_b200_softmax_rows_f32": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_void_p]),
     "te_b200_softmax_backward_rows_f32": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64,
                                                     C.c_int64, C.c_void_p]),
