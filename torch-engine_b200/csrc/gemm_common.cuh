@@ -1,0 +1,150 @@
+// Device-side pieces shared by the GEMM kernels (single-CTA and CTA-pair forms): tile constants, kernel
+// parameters, the bounded mbarrier wait, the tile raster and the fused epilogue.
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "ptx_sm100.cuh"
+#include "te_internal.h"
+
+namespace te {
+
+constexpr int BM = 128;
+constexpr int BK = 32;                       // floats per k-block = one 128-byte swizzle row
+constexpr int UMMA_K = 8;                    // tf32 K per tcgen05.mma
+constexpr int A_PLANE_BYTES = BM * BK * 4;   // 16 KiB
+constexpr int SMEM_RING_BUDGET = 192 * 1024;
+constexpr int SMEM_AUX_BYTES = 512;          // mbarriers, TMEM slot, abort flag
+constexpr int GROUP_M = 16;                  // raster: tiles advance down 16 m-blocks, then one n-block over
+constexpr uint64_t WAIT_LIMIT_NS = 2000000000ull;
+
+enum : int {  // where a bounded wait gave up (stored in the device status word)
+    WAIT_PRODUCER_EMPTY = 101,
+    WAIT_MMA_FULL = 102,
+    WAIT_MMA_TMEM_EMPTY = 103,
+    WAIT_EPI_TMEM_FULL = 104,
+    WAIT_TEARDOWN = 105
+};
+
+struct GemmParams {
+    int M, N, K;
+    int tiles_m, tiles_n;
+    int batch_inner, num_batches;
+    int a_mul_inner, a_mul_outer, b_mul_inner, b_mul_outer;  // 0 = broadcast, 1 = indexed
+    long long ldc, c_stride_inner, c_stride_outer;
+    float* c;
+    float* preact;
+    const float* bias;
+    float alpha;
+    int scale_mode;
+    int epilogue;
+    int* status;
+};
+
+template <int BN, int NPL>
+struct TileCfg {
+    static constexpr int B_PLANE_BYTES = BN * BK * 4;
+    static constexpr int STAGE_BYTES = NPL * (A_PLANE_BYTES + B_PLANE_BYTES);
+    static constexpr int STAGES = SMEM_RING_BUDGET / STAGE_BYTES;
+    static constexpr int TMEM_COLS = 2 * BN;  // two accumulator buffers of BN fp32 columns
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + SMEM_AUX_BYTES + 1024;  // +1024: manual alignment
+    static_assert(STAGES >= 2, "need at least a double buffer");
+    static_assert(TMEM_COLS >= 32 && TMEM_COLS <= 512 && (TMEM_COLS & (TMEM_COLS - 1)) == 0, "TMEM columns");
+};
+
+__device__ __forceinline__ bool wait_bounded(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                             int* status, int code) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const uint64_t t0 = global_timer_ns();
+    uint32_t polls = 0;
+    for (;;) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((++polls & 0x3F) == 0) {
+            if (*abort_flag) return false;
+            if (global_timer_ns() - t0 > WAIT_LIMIT_NS) {
+                *abort_flag = 1;
+                atomicCAS(status, 0, code);
+                return false;
+            }
+        }
+    }
+}
+
+__device__ __forceinline__ void tile_coords(int t, const GemmParams& p, int& batch, int& m_blk, int& n_blk) {
+    const int per_batch = p.tiles_m * p.tiles_n;
+    batch = t / per_batch;
+    const int r = t - batch * per_batch;
+    const int group_span = GROUP_M * p.tiles_n;
+    const int g = r / group_span;
+    const int first_m = g * GROUP_M;
+    const int gm = min(p.tiles_m - first_m, GROUP_M);
+    const int in_group = r - g * group_span;
+    m_blk = first_m + in_group % gm;
+    n_blk = in_group / gm;
+}
+
+__device__ __forceinline__ float gelu_tanh(float x) {
+    // Same expression as gelu_forward_kernel (reference src/cuda/elementwise_cuda.cu:2701-2707).
+    const float x3 = x * x * x;
+    return 0.5f * x * (1.0f + tanhf(0.7978845608f * (x + 0.044715f * x3)));
+}
+
+struct EpilogueRow {
+    float* c_row;      // start of this thread's output row
+    float* pre_row;    // same row of the optional pre-activation output
+    bool row_ok;       // row < M
+    bool vec_ok;       // 16-byte stores are legal
+};
+
+// scale -> (+bias) -> [store pre-activation] -> (GELU) -> store, for 32 consecutive columns of one row.
+__device__ __forceinline__ void epilogue_store32(float* v, int col0, const EpilogueRow& er, const GemmParams& p) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+        if (p.scale_mode == TE_SCALE_MUL) v[j] *= p.alpha;
+        else if (p.scale_mode == TE_SCALE_DIV) v[j] = v[j] / p.alpha;
+    }
+    if (p.bias) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+            if (col0 + j < p.N) v[j] += __ldg(p.bias + col0 + j);
+    }
+    if (!er.row_ok) return;
+    const bool full_chunk = col0 + 32 <= p.N;
+    if (er.pre_row) {
+        if (full_chunk && er.vec_ok) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 4)
+                *reinterpret_cast<float4*>(er.pre_row + col0 + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+        } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+                if (col0 + j < p.N) er.pre_row[col0 + j] = v[j];
+        }
+    }
+    if (p.epilogue == TE_EPI_BIAS_GELU) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = gelu_tanh(v[j]);
+    }
+    if (full_chunk && er.vec_ok) {
+#pragma unroll
+        for (int j = 0; j < 32; j += 4)
+            *reinterpret_cast<float4*>(er.c_row + col0 + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+    } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+            if (col0 + j < p.N) er.c_row[col0 + j] = v[j];
+    }
+}
+
+// Host: 4-D tensor map {contiguous index, strided index, batch_inner, batch_outer} of one operand; box_rows is the
+// number of lines a K-major box carries (an MN-major box is always 32 x 32).
+int make_operand_map(te_b200_ctx* ctx, CUtensorMap* out, const float* ptr, const Operand& op, int64_t K,
+                     int box_rows, int64_t batch_inner, int64_t batch_outer);
+// Fills the kernel parameters that do not depend on the tile shape.
+void fill_common_params(GemmParams& p, const te_b200_ctx* ctx, const GemmProblem& g);
+
+// gemm_sm100_2cta.cu: the CTA-pair (cta_group::2) TF32 kernel, 256 x 256 tiles.
+int launch_gemm_2cta(te_b200_ctx* ctx, const GemmProblem& g, cudaStream_t stream);
+
+}  // namespace te

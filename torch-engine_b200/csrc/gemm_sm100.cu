@@ -6,8 +6,8 @@
 // split by warp role:
 //   warps 0-3  epilogue: tcgen05.ld the finished accumulator out of TMEM, apply scale / bias /
 //              GELU, store to global memory;
-//   warp  4    producer: one lane issues TMA loads (cp.async.bulk.tensor, 128-byte swizzle, no
-//              multicast) of the A and B k-blocks into a ring of shared-memory stages;
+//   warp  4    producer: one lane issues TMA tensor loads (128-byte swizzle, each CTA for itself) of the
+//              A and B k-blocks into a ring of shared-memory stages;
 //   warp  5    MMA: one lane issues tcgen05.mma kind::tf32 (128 x BN x 8 per instruction) from
 //              shared-memory descriptors into one of two TMEM accumulator buffers, so the
 //              epilogue of tile i overlaps the main loop of tile i+1.
@@ -29,138 +29,12 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 #include <stdio.h>
+#include <stdlib.h>
 
-#include "ptx_sm100.cuh"
-#include "te_internal.h"
+#include "gemm_common.cuh"
 
 namespace te {
 
-constexpr int BM = 128;
-constexpr int BK = 32;                       // floats per k-block = one 128-byte swizzle row
-constexpr int UMMA_K = 8;                    // tf32 K per tcgen05.mma
-constexpr int A_PLANE_BYTES = BM * BK * 4;   // 16 KiB
-constexpr int SMEM_RING_BUDGET = 192 * 1024;
-constexpr int SMEM_AUX_BYTES = 512;          // mbarriers, TMEM slot, abort flag
-constexpr int GROUP_M = 16;                  // raster: tiles advance down 16 m-blocks, then one n-block over
-constexpr uint64_t WAIT_LIMIT_NS = 2000000000ull;
-
-enum : int {  // where a bounded wait gave up (stored in the device status word)
-    WAIT_PRODUCER_EMPTY = 101,
-    WAIT_MMA_FULL = 102,
-    WAIT_MMA_TMEM_EMPTY = 103,
-    WAIT_EPI_TMEM_FULL = 104,
-    WAIT_TEARDOWN = 105
-};
-
-struct GemmParams {
-    int M, N, K;
-    int tiles_m, tiles_n;
-    int batch_inner, num_batches;
-    int a_mul_inner, a_mul_outer, b_mul_inner, b_mul_outer;  // 0 = broadcast, 1 = indexed
-    long long ldc, c_stride_inner, c_stride_outer;
-    float* c;
-    float* preact;
-    const float* bias;
-    float alpha;
-    int scale_mode;
-    int epilogue;
-    int* status;
-};
-
-template <int BN, int NPL>
-struct TileCfg {
-    static constexpr int B_PLANE_BYTES = BN * BK * 4;
-    static constexpr int STAGE_BYTES = NPL * (A_PLANE_BYTES + B_PLANE_BYTES);
-    static constexpr int STAGES = SMEM_RING_BUDGET / STAGE_BYTES;
-    static constexpr int TMEM_COLS = 2 * BN;  // two accumulator buffers of BN fp32 columns
-    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + SMEM_AUX_BYTES + 1024;  // +1024: manual alignment
-    static_assert(STAGES >= 2, "need at least a double buffer");
-    static_assert(TMEM_COLS >= 32 && TMEM_COLS <= 512 && (TMEM_COLS & (TMEM_COLS - 1)) == 0, "TMEM columns");
-};
-
-__device__ __forceinline__ bool wait_bounded(uint32_t bar, uint32_t parity, volatile int* abort_flag,
-                                             int* status, int code) {
-    if (mbar_try_wait(bar, parity)) return true;
-    const uint64_t t0 = global_timer_ns();
-    uint32_t polls = 0;
-    for (;;) {
-        if (mbar_try_wait(bar, parity)) return true;
-        if ((++polls & 0x3F) == 0) {
-            if (*abort_flag) return false;
-            if (global_timer_ns() - t0 > WAIT_LIMIT_NS) {
-                *abort_flag = 1;
-                atomicCAS(status, 0, code);
-                return false;
-            }
-        }
-    }
-}
-
-__device__ __forceinline__ void tile_coords(int t, const GemmParams& p, int& batch, int& m_blk, int& n_blk) {
-    const int per_batch = p.tiles_m * p.tiles_n;
-    batch = t / per_batch;
-    const int r = t - batch * per_batch;
-    const int group_span = GROUP_M * p.tiles_n;
-    const int g = r / group_span;
-    const int first_m = g * GROUP_M;
-    const int gm = min(p.tiles_m - first_m, GROUP_M);
-    const int in_group = r - g * group_span;
-    m_blk = first_m + in_group % gm;
-    n_blk = in_group / gm;
-}
-
-__device__ __forceinline__ float gelu_tanh(float x) {
-    // Same expression as gelu_forward_kernel (reference src/cuda/elementwise_cuda.cu:2701-2707).
-    const float x3 = x * x * x;
-    return 0.5f * x * (1.0f + tanhf(0.7978845608f * (x + 0.044715f * x3)));
-}
-
-struct EpilogueRow {
-    float* c_row;      // start of this thread's output row
-    float* pre_row;    // same row of the optional pre-activation output
-    bool row_ok;       // row < M
-    bool vec_ok;       // 16-byte stores are legal
-};
-
-// scale -> (+bias) -> [store pre-activation] -> (GELU) -> store, for 32 consecutive columns of one row.
-__device__ __forceinline__ void epilogue_store32(float* v, int col0, const EpilogueRow& er, const GemmParams& p) {
-#pragma unroll
-    for (int j = 0; j < 32; ++j) {
-        if (p.scale_mode == TE_SCALE_MUL) v[j] *= p.alpha;
-        else if (p.scale_mode == TE_SCALE_DIV) v[j] = v[j] / p.alpha;
-    }
-    if (p.bias) {
-#pragma unroll
-        for (int j = 0; j < 32; ++j)
-            if (col0 + j < p.N) v[j] += __ldg(p.bias + col0 + j);
-    }
-    if (!er.row_ok) return;
-    const bool full_chunk = col0 + 32 <= p.N;
-    if (er.pre_row) {
-        if (full_chunk && er.vec_ok) {
-#pragma unroll
-            for (int j = 0; j < 32; j += 4)
-                *reinterpret_cast<float4*>(er.pre_row + col0 + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
-        } else {
-#pragma unroll
-            for (int j = 0; j < 32; ++j)
-                if (col0 + j < p.N) er.pre_row[col0 + j] = v[j];
-        }
-    }
-    if (p.epilogue == TE_EPI_BIAS_GELU) {
-#pragma unroll
-        for (int j = 0; j < 32; ++j) v[j] = gelu_tanh(v[j]);
-    }
-    if (full_chunk && er.vec_ok) {
-#pragma unroll
-        for (int j = 0; j < 32; j += 4)
-            *reinterpret_cast<float4*>(er.c_row + col0 + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
-    } else {
-#pragma unroll
-        for (int j = 0; j < 32; ++j)
-            if (col0 + j < p.N) er.c_row[col0 + j] = v[j];
-    }
-}
 
 template <int BN, int NPL, bool A_MN, bool B_MN>
 __global__ void __launch_bounds__(192, 1)
@@ -470,7 +344,7 @@ bool operand_tma_ok(const Operand& op, int64_t K, int64_t batch_inner, int64_t b
 
 // 4-D map {contiguous index, strided index, batch_inner, batch_outer}.  Broadcast (stride 0) levels get
 // extent 1; the kernel multiplies their coordinate by 0.
-static int make_operand_map(te_b200_ctx* ctx, CUtensorMap* out, const float* ptr, const Operand& op,
+int make_operand_map(te_b200_ctx* ctx, CUtensorMap* out, const float* ptr, const Operand& op,
                             int64_t K, int box_rows, int64_t batch_inner, int64_t batch_outer) {
     const int64_t k_extent = K > 0 ? K : 1;   // K == 0 issues no loads but the map must still be valid
     const int64_t contiguous_extent = op.mn_major ? op.rows : k_extent;
@@ -504,6 +378,21 @@ static int make_operand_map(te_b200_ctx* ctx, CUtensorMap* out, const float* ptr
     return TE_OK;
 }
 
+void fill_common_params(GemmParams& p, const te_b200_ctx* ctx, const GemmProblem& g) {
+    p.M = (int)g.M; p.N = (int)g.N; p.K = (int)g.K;
+    p.tiles_m = p.tiles_n = 0;
+    p.batch_inner = (int)g.batch_inner;
+    p.num_batches = (int)(g.batch_inner * g.batch_outer);
+    p.a_mul_inner = (g.batch_inner > 1 && g.a.stride_inner != 0) ? 1 : 0;
+    p.a_mul_outer = (g.batch_outer > 1 && g.a.stride_outer != 0) ? 1 : 0;
+    p.b_mul_inner = (g.batch_inner > 1 && g.b.stride_inner != 0) ? 1 : 0;
+    p.b_mul_outer = (g.batch_outer > 1 && g.b.stride_outer != 0) ? 1 : 0;
+    p.ldc = g.ldc; p.c_stride_inner = g.c_stride_inner; p.c_stride_outer = g.c_stride_outer;
+    p.c = g.c; p.preact = g.preact; p.bias = g.bias;
+    p.alpha = g.alpha; p.scale_mode = g.scale_mode; p.epilogue = g.epilogue;
+    p.status = ctx->d_status;
+}
+
 template <int BN, int NPL, bool A_MN, bool B_MN>
 static int launch_variant(te_b200_ctx* ctx, const GemmProblem& g, cudaStream_t stream) {
     using Cfg = TileCfg<BN, NPL>;
@@ -526,19 +415,9 @@ static int launch_variant(te_b200_ctx* ctx, const GemmProblem& g, cudaStream_t s
         mbl = mb;
     }
     GemmParams p;
-    p.M = (int)g.M; p.N = (int)g.N; p.K = (int)g.K;
+    fill_common_params(p, ctx, g);
     p.tiles_m = (int)((g.M + BM - 1) / BM);
     p.tiles_n = (int)((g.N + BN - 1) / BN);
-    p.batch_inner = (int)g.batch_inner;
-    p.num_batches = (int)(g.batch_inner * g.batch_outer);
-    p.a_mul_inner = (g.batch_inner > 1 && g.a.stride_inner != 0) ? 1 : 0;
-    p.a_mul_outer = (g.batch_outer > 1 && g.a.stride_outer != 0) ? 1 : 0;
-    p.b_mul_inner = (g.batch_inner > 1 && g.b.stride_inner != 0) ? 1 : 0;
-    p.b_mul_outer = (g.batch_outer > 1 && g.b.stride_outer != 0) ? 1 : 0;
-    p.ldc = g.ldc; p.c_stride_inner = g.c_stride_inner; p.c_stride_outer = g.c_stride_outer;
-    p.c = g.c; p.preact = g.preact; p.bias = g.bias;
-    p.alpha = g.alpha; p.scale_mode = g.scale_mode; p.epilogue = g.epilogue;
-    p.status = ctx->d_status;
     const long long total = (long long)p.tiles_m * p.tiles_n * p.num_batches;
     const int grid = (int)(total < ctx->sm_count ? total : ctx->sm_count);
     kernel<<<grid, 192, Cfg::SMEM_BYTES, stream>>>(ma, mal, mb, mbl, p);
@@ -565,6 +444,8 @@ int launch_gemm(te_b200_ctx* ctx, const GemmProblem& g, cudaStream_t stream) {
         if (g.N > 64) return launch_bn<128>(ctx, g, stream);
         return launch_bn<64>(ctx, g, stream);
     }
+    if (!g.a_lo && g.M > 128 && g.N > 128 && !getenv("TE_DEBUG_NO_2CTA")) return launch_gemm_2cta(ctx, g, stream);
+    if (const char* f = getenv("TE_DEBUG_FORCE_BN")) { if (atoi(f) == 128) return launch_bn<128>(ctx, g, stream); if (atoi(f) == 64) return launch_bn<64>(ctx, g, stream); }
     if (g.N > 128) return launch_bn<256>(ctx, g, stream);
     if (g.N > 64) return launch_bn<128>(ctx, g, stream);
     return launch_bn<64>(ctx, g, stream);

@@ -1,0 +1,310 @@
+// CTA-pair form of the TF32 GEMM: two neighbouring SMs (a cluster of 2 CTAs) compute one 256 x 256 output tile
+// with tcgen05.mma.cta_group::2.
+//
+// Why: the single-CTA kernel streams (128 + 256) x 32 floats = 48 KB into shared memory for every 128x256x32
+// block of work and is limited by how fast shared memory can be filled, not by the tensor pipe.  In the pair form
+// each CTA loads its own 128 rows of A and only HALF of the B block (128 of the 256 columns); the instruction
+// reads both halves straight out of the two CTAs' shared memories.  Per CTA that is 32 KB for the same amount of
+// tensor work, and no load is broadcast between CTAs.
+//
+// Roles per CTA are as in the single-CTA kernel (warps 0-3 epilogue, warp 4 TMA producer, warp 5 MMA), with the
+// pair protocol on top:
+//   * "full" barriers live in the leader CTA (cluster rank 0): both producers post their byte counts there;
+//   * the leader's MMA lane issues for the pair and commits to the "empty" and "accumulator full" barriers of
+//     BOTH CTAs;
+//   * each CTA's epilogue drains its own 128 accumulator rows from its own TMEM and both report to the leader's
+//     "accumulator empty" barrier.
+// Every wait is bounded as in the single-CTA kernel; the CTAs leave together through a cluster barrier.
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+#include <stdlib.h>
+
+#include "gemm_common.cuh"
+
+namespace te {
+
+constexpr int PAIR_BM = 256;   // rows of one pair tile (128 per CTA)
+
+template <int BN>
+struct PairCfg {
+    static constexpr int B_HALF_BYTES = (BN / 2) * BK * 4;
+    static constexpr int STAGE_BYTES = A_PLANE_BYTES + B_HALF_BYTES;      // per CTA
+    static constexpr int STAGES = SMEM_RING_BUDGET / STAGE_BYTES;
+    static constexpr int TMEM_COLS = 2 * BN;
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + SMEM_AUX_BYTES + 1024;
+    static_assert(STAGES >= 2 && STAGES <= 12, "ring depth");
+    static_assert(TMEM_COLS <= 512, "TMEM columns");
+};
+
+__device__ __forceinline__ void pair_tile_coords(int t, const GemmParams& p, int& batch, int& m_blk, int& n_blk) {
+    tile_coords(t, p, batch, m_blk, n_blk);   // same raster; tiles_m counts 256-row blocks here
+}
+
+template <int BN, bool A_MN, bool B_MN>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
+gemm_tf32_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
+                      const GemmParams p) {
+    using Cfg = PairCfg<BN>;
+    constexpr int STAGES = Cfg::STAGES;
+    constexpr int STAGE_BYTES = Cfg::STAGE_BYTES;
+    constexpr int HALF_N = BN / 2;
+    constexpr uint32_t IDESC = make_idesc_tf32(PAIR_BM, BN, A_MN, B_MN);
+    constexpr uint32_t MN_CHUNK_BYTES = BK * 128;
+    constexpr uint32_t A_LBO = A_MN ? MN_CHUNK_BYTES : 16, A_SBO = A_MN ? 512 : 1024, A_KSTEP = A_MN ? 1024 : UMMA_K * 4;
+    constexpr uint32_t B_LBO = B_MN ? MN_CHUNK_BYTES : 16, B_SBO = B_MN ? 512 : 1024, B_KSTEP = B_MN ? 1024 : UMMA_K * 4;
+    constexpr uint32_t A_LAYOUT = A_MN ? SMEM_LAYOUT_SW128_BASE32B : SMEM_LAYOUT_SW128;
+    constexpr uint32_t B_LAYOUT = B_MN ? SMEM_LAYOUT_SW128_BASE32B : SMEM_LAYOUT_SW128;
+
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw_addr = smem_u32(smem_raw);
+    const uint32_t ring = (raw_addr + 1023u) & ~1023u;
+    uint8_t* aux = smem_raw + (ring - raw_addr) + STAGES * STAGE_BYTES;
+    const uint32_t aux_addr = ring + STAGES * STAGE_BYTES;
+    // aux: full[STAGES] | empty[STAGES] | tmem_full[2] | tmem_empty[2] | teardown | slot | abort
+    const uint32_t bar_full = aux_addr;
+    const uint32_t bar_empty = bar_full + 8 * STAGES;
+    const uint32_t bar_tmem_full = bar_empty + 8 * STAGES;
+    const uint32_t bar_tmem_empty = bar_tmem_full + 16;
+    const uint32_t bar_teardown = bar_tmem_empty + 16;
+    const uint32_t tmem_slot_addr = bar_teardown + 8;
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(aux + (tmem_slot_addr - aux_addr));
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(aux + (tmem_slot_addr - aux_addr) + 4);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_ctarank();          // 0 = leader
+    const bool leader = rank == 0;
+    const int pair = blockIdx.x >> 1;
+    const int num_pairs = gridDim.x >> 1;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(bar_full + 8 * s, 2);           // leader's copy is the one in use: one arrival per producer
+            mbar_init(bar_empty + 8 * s, 1);
+        }
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(bar_tmem_full + 8 * i, 1);
+            mbar_init(bar_tmem_empty + 8 * i, 8);     // leader's copy: 4 epilogue warps of each CTA
+        }
+        mbar_init(bar_teardown, 1);
+        *abort_flag = 0;
+        fence_barrier_init();
+        fence_proxy_async_smem();
+    }
+    if (warp == 4 && lane == 0) {
+        tma_prefetch_desc(&tm_a);
+        tma_prefetch_desc(&tm_b);
+    }
+    if (warp == 5) {
+        tmem_alloc_pair(tmem_slot_addr, Cfg::TMEM_COLS);
+        tmem_relinquish_pair();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    cluster_sync_all();                               // partner's barriers are initialised before anyone signals them
+    tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+
+    const int total_tiles = p.tiles_m * p.tiles_n * p.num_batches;
+    const int kblocks = (p.K + BK - 1) / BK;
+
+    if (warp == 4) {
+        // ------------------------------------------------------------ TMA producer (both CTAs)
+        if (lane == 0) {
+            int issued = 0;
+            bool ok = true;
+            for (int t = pair; t < total_tiles && ok; t += num_pairs) {
+                int batch, m_blk, n_blk;
+                pair_tile_coords(t, p, batch, m_blk, n_blk);
+                const int bo = batch / p.batch_inner, bi = batch - bo * p.batch_inner;
+                const int a_ci = bi * p.a_mul_inner, a_co = bo * p.a_mul_outer;
+                const int b_ci = bi * p.b_mul_inner, b_co = bo * p.b_mul_outer;
+                const int m0 = m_blk * PAIR_BM + (int)rank * BM;       // this CTA's 128 rows of A
+                const int n0 = n_blk * BN + (int)rank * HALF_N;        // this CTA's half of the B columns
+                for (int kb = 0; kb < kblocks; ++kb, ++issued) {
+                    const int s = issued % STAGES;
+                    const uint32_t phase = (issued / STAGES) & 1;
+                    if (!wait_bounded(bar_empty + 8 * s, phase ^ 1, abort_flag, p.status, WAIT_PRODUCER_EMPTY)) {
+                        ok = false;
+                        break;
+                    }
+                    const uint32_t full = map_to_cta(bar_full + 8 * s, 0);     // the leader's barrier
+                    mbar_arrive_expect_tx_cluster(full, STAGE_BYTES);
+                    const uint32_t sa = ring + s * STAGE_BYTES;
+                    const uint32_t sb = sa + A_PLANE_BYTES;
+                    const int k0 = kb * BK;
+                    if (A_MN) {
+#pragma unroll
+                        for (int c = 0; c < BM / 32; ++c)
+                            tma_load_4d_pair(sa + c * MN_CHUNK_BYTES, &tm_a, full, m0 + 32 * c, k0, a_ci, a_co);
+                    } else {
+                        tma_load_4d_pair(sa, &tm_a, full, k0, m0, a_ci, a_co);
+                    }
+                    if (B_MN) {
+#pragma unroll
+                        for (int c = 0; c < HALF_N / 32; ++c)
+                            tma_load_4d_pair(sb + c * MN_CHUNK_BYTES, &tm_b, full, n0 + 32 * c, k0, b_ci, b_co);
+                    } else {
+                        tma_load_4d_pair(sb, &tm_b, full, k0, n0, b_ci, b_co);
+                    }
+                }
+            }
+            if (!ok || *abort_flag) {
+                // Copies already issued still write this CTA's shared memory: give them time to land before leaving.
+                const uint64_t t0 = global_timer_ns();
+                while (global_timer_ns() - t0 < 200000ull) {
+                }
+            }
+        }
+    } else if (warp == 5) {
+        // ------------------------------------------------------------ MMA issuer (leader CTA only)
+        if (lane == 0 && leader) {
+            int consumed = 0;
+            int acc_idx = 0;
+            bool ok = true;
+            for (int t = pair; t < total_tiles && ok; t += num_pairs, ++acc_idx) {
+                const int buf = acc_idx & 1;
+                if (!wait_bounded(bar_tmem_empty + 8 * buf, ((acc_idx >> 1) & 1) ^ 1, abort_flag, p.status,
+                                  WAIT_MMA_TMEM_EMPTY)) {
+                    ok = false;
+                    break;
+                }
+                tc_fence_after_sync();
+                const uint32_t d_tmem = tmem_base + buf * BN;
+                for (int kb = 0; kb < kblocks; ++kb, ++consumed) {
+                    const int s = consumed % STAGES;
+                    if (!wait_bounded(bar_full + 8 * s, (consumed / STAGES) & 1, abort_flag, p.status, WAIT_MMA_FULL)) {
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after_sync();
+                    const uint32_t sa = ring + s * STAGE_BYTES;
+                    const uint32_t sb = sa + A_PLANE_BYTES;
+#pragma unroll
+                    for (int j = 0; j < BK / UMMA_K; ++j) {
+                        const uint64_t da = make_smem_desc(sa + j * A_KSTEP, A_LBO, A_SBO, A_LAYOUT);
+                        const uint64_t db = make_smem_desc(sb + j * B_KSTEP, B_LBO, B_SBO, B_LAYOUT);
+                        umma_tf32_pair(d_tmem, da, db, IDESC, (kb | j) != 0);
+                    }
+                    umma_commit_pair(bar_empty + 8 * s, 3);        // frees the stage in both CTAs
+                }
+                if (!ok) break;
+                umma_commit_pair(bar_tmem_full + 8 * buf, 3);      // accumulator ready in both CTAs
+            }
+            umma_commit_pair(bar_teardown, 1);
+            const uint64_t t0 = global_timer_ns();
+            while (!mbar_try_wait(bar_teardown, 0)) {
+                if (global_timer_ns() - t0 > WAIT_LIMIT_NS) {
+                    atomicCAS(p.status, 0, (int)WAIT_TEARDOWN);
+                    break;
+                }
+            }
+        }
+    } else {
+        // ------------------------------------------------------------ epilogue (warps 0-3, both CTAs)
+        int acc_idx = 0;
+        bool ok = true;
+        for (int t = pair; t < total_tiles && ok; t += num_pairs, ++acc_idx) {
+            int batch, m_blk, n_blk;
+            pair_tile_coords(t, p, batch, m_blk, n_blk);
+            const int bo = batch / p.batch_inner, bi = batch - bo * p.batch_inner;
+            const int row = m_blk * PAIR_BM + (int)rank * BM + warp * 32 + lane;
+            const int n0 = n_blk * BN;
+            const long long batch_off = (long long)bo * p.c_stride_outer + (long long)bi * p.c_stride_inner;
+            EpilogueRow er;
+            er.c_row = p.c + batch_off + (long long)row * p.ldc;
+            er.pre_row = p.preact ? p.preact + batch_off + (long long)row * p.ldc : nullptr;
+            er.row_ok = row < p.M;
+            er.vec_ok = ((p.ldc & 3) == 0) && ((reinterpret_cast<uintptr_t>(p.c + batch_off) & 15) == 0) &&
+                        (!p.preact || (reinterpret_cast<uintptr_t>(p.preact + batch_off) & 15) == 0);
+            const int buf = acc_idx & 1;
+            ok = wait_bounded(bar_tmem_full + 8 * buf, (acc_idx >> 1) & 1, abort_flag, p.status, WAIT_EPI_TMEM_FULL);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            tc_fence_after_sync();
+            const uint32_t t_row = tmem_base + (uint32_t(warp * 32) << 16) + buf * BN;
+#pragma unroll 1
+            for (int cc = 0; cc < BN / 32; ++cc) {
+                const int col0 = n0 + cc * 32;
+                if (col0 >= p.N) break;
+                uint32_t r[32];
+                tmem_ld_32x32b_x32(t_row + cc * 32, r);
+                tmem_ld_wait();
+                float v[32];
+#pragma unroll
+                for (int j = 0; j < 32; ++j) v[j] = p.K > 0 ? __uint_as_float(r[j]) : 0.0f;
+                epilogue_store32(v, col0, er, p);
+            }
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(map_to_cta(bar_tmem_empty + 8 * buf, 0));
+        }
+    }
+
+    __syncwarp();
+    tc_fence_before_sync();
+    __syncthreads();
+    cluster_sync_all();          // nobody leaves while the partner may still touch this CTA's memory or barriers
+    if (warp == 5) {
+        tc_fence_after_sync();
+        tmem_dealloc_pair(tmem_base, Cfg::TMEM_COLS);
+    }
+}
+
+template <int BN, bool A_MN, bool B_MN>
+static int launch_pair_variant(te_b200_ctx* ctx, const GemmProblem& g, cudaStream_t stream) {
+    using Cfg = PairCfg<BN>;
+    auto kernel = gemm_tf32_pair_kernel<BN, A_MN, B_MN>;
+    static bool attr_done[16] = {};
+    if (ctx->device < 16 && !attr_done[ctx->device]) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
+        if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(max dynamic shared memory)");
+        attr_done[ctx->device] = true;
+    }
+    CUtensorMap ma, mb;
+    int rc;
+    if ((rc = make_operand_map(ctx, &ma, g.a.ptr, g.a, g.K, BM, g.batch_inner, g.batch_outer))) return rc;
+    if ((rc = make_operand_map(ctx, &mb, g.b.ptr, g.b, g.K, BN / 2, g.batch_inner, g.batch_outer))) return rc;
+    GemmParams p;
+    fill_common_params(p, ctx, g);
+    p.tiles_m = (int)((g.M + PAIR_BM - 1) / PAIR_BM);
+    p.tiles_n = (int)((g.N + BN - 1) / BN);
+    const long long total = (long long)p.tiles_m * p.tiles_n * p.num_batches;
+    // How many CTA pairs can be resident at once (pairs must sit on neighbouring SMs, so this can be below SMs/2).
+    static int max_pairs_cached[16] = {};
+    int max_pairs = ctx->device < 16 ? max_pairs_cached[ctx->device] : 0;
+    if (max_pairs == 0) {
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(ctx->sm_count & ~1, 1, 1);
+        cfg.blockDim = dim3(192, 1, 1);
+        cfg.dynamicSmemBytes = Cfg::SMEM_BYTES;
+        cudaLaunchAttribute attr;
+        attr.id = cudaLaunchAttributeClusterDimension;
+        attr.val.clusterDim.x = 2; attr.val.clusterDim.y = 1; attr.val.clusterDim.z = 1;
+        cfg.attrs = &attr;
+        cfg.numAttrs = 1;
+        int n = 0;
+        cudaError_t eo = cudaOccupancyMaxActiveClusters(&n, kernel, &cfg);
+        if (eo != cudaSuccess || n < 1) { cudaGetLastError(); n = ctx->sm_count / 2; }
+        max_pairs = n;
+        if (ctx->device < 16) max_pairs_cached[ctx->device] = n;
+        if (getenv("TE_DEBUG_VERBOSE")) fprintf(stderr, "[te_b200] resident CTA pairs: %d\n", n);
+    }
+    const int pairs = (int)(total < max_pairs ? total : max_pairs);
+    kernel<<<2 * pairs, 192, Cfg::SMEM_BYTES, stream>>>(ma, mb, p);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return cuda_fail(e, "gemm_tf32_pair_kernel launch");
+    ctx->launches += 1;
+    return TE_OK;
+}
+
+int launch_gemm_2cta(te_b200_ctx* ctx, const GemmProblem& g, cudaStream_t stream) {
+    if (!g.a.mn_major && !g.b.mn_major) return launch_pair_variant<256, false, false>(ctx, g, stream);
+    if (!g.a.mn_major && g.b.mn_major) return launch_pair_variant<256, false, true>(ctx, g, stream);
+    if (g.a.mn_major && !g.b.mn_major) return launch_pair_variant<256, true, false>(ctx, g, stream);
+    return launch_pair_variant<256, true, true>(ctx, g, stream);
+}
+
+}  // namespace te
