@@ -112,3 +112,16 @@ def gpt_tiny_inputs(layout, seed=42):
     tokens = rng.tokens((cfg["batch"], cfg["seq"]), cfg["vocab"])
     targets = rng.tokens((cfg["batch"], cfg["seq"]), cfg["vocab"])
     return flat, tokens, targets
+
+
+# Benchmark config 4.  ffDim is 4*E, the ratio of every preset of the reference (scripts/run_benchmark_suite.py:22-26).
+GPT_C4 = dict(vocab=65, max_seq=256, E=384, H=6, L=6, ff=1536, batch=64, seq=256)
+
+
+def gpt_c4_inputs(layout, seed=42):
+    cfg = GPT_C4
+    rng = binding.SeededRng(seed)
+    flat = gpt_init_params(layout, cfg["L"], rng)
+    tokens = rng.tokens((cfg["batch"], cfg["seq"]), cfg["vocab"])
+    targets = rng.tokens((cfg["batch"], cfg["seq"]), cfg["vocab"])
+    return flat, tokens, targets

@@ -1,0 +1,134 @@
+"""The GPT training-step caller of the matmul path (reference src/benchmarks/gpt_benchmark_gpu.cpp:230-236 without
+the optimizer): GPT::forward (src/nn/gpt.cpp:26-86) -> crossEntropyLoss::forward_batched
+(src/loss/CrossEntropyLoss.cpp:47-127) -> backward.
+
+Every matmul of the step runs on this backend through the C ABI:
+  * Linear forward / backward (src/nn/linear.cpp:14-23, src/core/grad_fn.cpp:93-139) as the fused calls
+    te_b200_linear_forward / te_b200_linear_backward, the FeedForward GELU (src/nn/ffn.cpp:12-16) in the epilogue;
+  * ScaledDot::forward (src/nn/scaledot.cpp:8-27) on the head views of MultiHeadAttention::forward
+    (src/nn/multi_head_attention.cpp:19-42, strides [T*E, hd, E, 1], no copies, no mask), and its backward
+    (MatMulBackward x2, DivBackward, SoftmaxBackward) as four batched GEMMs and one softmax-backward kernel.
+What is not a matmul in the reference (embedding gather, sinusoidal position table, pre-LN LayerNorm, residual
+adds, the mean cross-entropy) stays outside the backend and is evaluated with stock torch ops, as those kernels
+stay with the reference.  Parameters come in GPT::parameters() order (src/nn/gpt.cpp:88-113).
+"""
+import math
+
+import torch
+
+
+class _Linear(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w, b, be, prec, gelu):
+        if gelu:
+            y, pre = be.linear_forward(x, w, b, gelu=True, want_preact=True, precision=prec)
+        else:
+            y, pre = be.linear_forward(x, w, b, precision=prec), None
+        ctx.save_for_backward(x, w, pre if pre is not None else x.new_empty(0))
+        ctx.be, ctx.prec, ctx.gelu = be, prec, gelu
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, w, pre = ctx.saved_tensors
+        be = ctx.be
+        dy = dy.contiguous()
+        if ctx.gelu:
+            dy = be.gelu_backward(pre, dy)       # GeluBackward consumes the pre-activation (grad_fn.cpp:169-204)
+        dx, dw, db = be.linear_backward(x, w, dy, precision=ctx.prec)
+        return dx, dw, db, None, None, None
+
+
+class _ScaledDot(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, q, k, v, be, prec):
+        o, p = be.scaled_dot(q, k, v, precision=prec)
+        ctx.save_for_backward(q, k, v, p)
+        ctx.be, ctx.prec = be, prec
+        return o
+
+    @staticmethod
+    def backward(ctx, d_o):
+        q, k, v, p = ctx.saved_tensors
+        be, prec = ctx.be, ctx.prec
+        d_o = d_o.contiguous()
+        scale = math.sqrt(q.shape[-1])
+        dv = be.matmul(p.transpose(-1, -2), d_o, precision=prec)          # P^T . dO
+        dp = be.matmul(d_o, v.transpose(-1, -2), precision=prec)          # dO . V^T
+        ds = be.softmax_backward(p, dp) / scale                            # SoftmaxBackward, then DivBackward
+        dq = be.matmul(ds, k, precision=prec)                              # dS . K
+        dk = be.matmul(ds.transpose(-1, -2), q, precision=prec)            # dS^T . Q
+        return dq, dk, dv, None, None
+
+
+def linear(be, x, w, b, prec, gelu=False):
+    return _Linear.apply(x, w, b, be, prec, gelu)
+
+
+def positional_table(seq_len, d_model, device):
+    """PositionalEmbedding::init_positional_embeddings (src/nn/positional_embedding.cpp:18-36): the exponent uses
+    the column index itself for even and odd columns alike."""
+    pos = torch.arange(seq_len, dtype=torch.float32).unsqueeze(1)
+    i = torch.arange(d_model, dtype=torch.float32).unsqueeze(0)
+    div = torch.exp(torch.log(torch.tensor(10000.0)) * (2.0 * (i / 2.0)) / float(d_model))
+    ang = pos / div
+    pe = torch.where((torch.arange(d_model) % 2 == 0).unsqueeze(0), torch.sin(ang), torch.cos(ang))
+    return pe.to(device)
+
+
+def layer_norm(x, g, b, eps=1e-5):
+    """LayerNorm::forward (src/nn/layernorm.cpp:19-77): biased variance, (x-mean)/sqrt(var+eps)*g+b."""
+    mean = x.mean(dim=-1, keepdim=True)
+    var = ((x - mean) ** 2).mean(dim=-1, keepdim=True)
+    return (x - mean) / torch.sqrt(var + eps) * g + b
+
+
+def split_params(flat, vocab, E, n_layers, ff):
+    """Views of a flat parameter vector in GPT::parameters() order, as leaf tensors that require grad."""
+    shapes = [(vocab, E)]
+    for _ in range(n_layers):
+        shapes += [(E,), (E,)] + [(E, E), (E,)] * 4 + [(E,), (E,)] + [(ff, E), (ff,), (E, ff), (E,)]
+    shapes += [(E,), (E,), (vocab, E), (vocab,)]
+    out, off = [], 0
+    for s in shapes:
+        n = 1
+        for d in s:
+            n *= d
+        out.append(flat[off:off + n].view(s).clone().requires_grad_(True))
+        off += n
+    assert off == flat.numel(), (off, flat.numel())
+    return out
+
+
+def gpt_forward(be, params, tokens, E, H, n_layers, prec="tf32"):
+    """Logits [B, T, vocab] of the pre-LN, unmasked GPT of the reference."""
+    B, T = tokens.shape
+    hd = E // H
+    it = iter(params)
+    emb = next(it)
+    x = emb[tokens] + positional_table(T, E, tokens.device).unsqueeze(0)          # gpt.cpp:29-68
+    for _ in range(n_layers):                                                     # transformer_block.cpp:15-35
+        g1, b1 = next(it), next(it)
+        wq, bq, wk, bk, wv, bv, wo, bo = (next(it) for _ in range(8))
+        g2, b2 = next(it), next(it)
+        w1, c1, w2, c2 = (next(it) for _ in range(4))
+        h = layer_norm(x, g1, b1)
+        heads = lambda t: t.view(B, T, H, hd).transpose(1, 2)                      # zero-copy head views
+        q, k, v = (heads(linear(be, h, w, b, prec)) for w, b in ((wq, bq), (wk, bk), (wv, bv)))
+        o = _ScaledDot.apply(q, k, v, be, prec)                                    # [B,H,T,hd]
+        o = o.transpose(1, 2).reshape(B, T, E)
+        x = x + linear(be, o, wo, bo, prec)
+        h = layer_norm(x, g2, b2)
+        x = x + linear(be, linear(be, h, w1, c1, prec, gelu=True), w2, c2, prec)
+    gf, bf, wh, bh = (next(it) for _ in range(4))
+    return linear(be, layer_norm(x, gf, bf), wh, bh, prec)
+
+
+def gpt_step(be, flat_params, tokens, targets, vocab, E, H, n_layers, ff, prec="tf32"):
+    """One forward + backward.  Returns (loss, logits, flat gradient in parameter order)."""
+    params = split_params(flat_params, vocab, E, n_layers, ff)
+    logits = gpt_forward(be, params, tokens, E, H, n_layers, prec)
+    loss = torch.nn.functional.cross_entropy(logits.reshape(-1, vocab), targets.reshape(-1))   # mean over B*T
+    loss.backward()
+    grads = torch.cat([p.grad.reshape(-1) for p in params])
+    return loss.detach(), logits.detach(), grads
