@@ -1,0 +1,157 @@
+"""Shape sweep of the matmul path, the counterpart of src/benchmarks/matmul_benchmark.cpp of the reference.
+
+Writes a JSON list with the reference's fields (kernel_name, dtype, M, K, N, time_ms, tflops, bandwidth_gb_s,
+pct_of_cublas, gpu_name; src/benchmarks/matmul_benchmark.cpp:342-362) plus mode, pct_of_tensor_peak,
+pct_of_hbm_peak, gpus, cpu_time_ms, cpu_cores.  Timing follows :53-94 there: CUDA events around `iters` launches
+after max(3, iters/5) warm-up launches, iters by problem size (raised to >= 20 for the large shapes), best and
+median of 7 trials.  FLOPs = 2*M*K*N, bytes = 4*(M*K + K*N + M*N) (:73-82).  Inputs: seed 42, uniform(-1, 1).
+
+    python torch-engine_b200/benchmarks/matmul_benchmark.py [out.json] [--cpu] [--quick]
+
+Cases: the square sweep 1024..16384 and the skinny shapes of the GEMM sweep configuration, the attention pair of
+batched products (B=16, H=12, T=256, d=64) with the softmax between them, and the MLP Linear forward (+GELU) and
+backward (X [4096,768], W [3072,768]).  `pct_of_cublas` compares with torch.matmul in TF32 mode (a cuBLAS call) as a
+comparator only.  With --cpu the reference's own CPU Tensor::matmul (single-threaded) is timed beside the small
+shapes and extrapolated, labelled as such, for the large ones.
+"""
+import argparse
+import json
+import os
+import statistics
+import sys
+import time
+
+ROOT = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+sys.path.insert(0, ROOT)
+
+import torch  # noqa: E402
+
+from torch_engine_b200 import ops  # noqa: E402
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        p = json.load(open(path))
+        return p["bf16_tflops"] / 2.0, p["hbm_gbs"], "measured"
+    return 1590.0 / 2.0, 6650.0, "fallback"
+
+
+def iters_for(flops):
+    if flops < 2 * 512 ** 3:
+        return 100
+    if flops < 2 * 2048 ** 3:
+        return 50
+    return 20
+
+
+def time_gpu(fn, iters, trials=7):
+    for _ in range(max(3, iters // 5)):
+        fn()
+    torch.cuda.synchronize()
+    out = []
+    for _ in range(trials):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(iters):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        out.append(e0.elapsed_time(e1) / iters)
+    return min(out), statistics.median(out)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("out", nargs="?", default=os.path.join(ROOT, "gpurun_out", "matmul_benchmark.json"))
+    ap.add_argument("--cpu", action="store_true", help="time the reference CPU matmul beside the GPU numbers")
+    ap.add_argument("--quick", action="store_true", help="skip 16384^3")
+    args = ap.parse_args()
+
+    be = ops.Backend(0, workspace_bytes=6 << 30)
+    tf32_peak, hbm_peak, peak_src = peaks()
+    gpu_name = torch.cuda.get_device_name(0)
+    torch.backends.cuda.matmul.allow_tf32 = True
+    gen = torch.Generator(device="cuda").manual_seed(42)
+    rnd = lambda *s: torch.rand(*s, device="cuda", generator=gen) * 2 - 1
+    results = []
+
+    cpu_rate = None
+    if args.cpu:
+        from oracle import binding
+        ref = binding.Reference() if binding.Reference.available() else None
+        rng = binding.SeededRng(42)
+        a, b = rng.uniform((1024, 1024)), rng.uniform((1024, 1024))
+        t0 = time.perf_counter()
+        if ref:
+            ref.matmul(a, binding.ref_view(a.shape), b, binding.ref_view(b.shape))
+        else:
+            binding.Oracle().matmul(a, b)
+        cpu_rate = 2.0 * 1024 ** 3 / (time.perf_counter() - t0)      # FLOP/s of one host core
+
+    def record(name, mode, M, K, N, batch, t_best, t_med, cublas_ms=None, extra_bytes=0):
+        flops = 2.0 * M * K * N * batch
+        byts = 4.0 * (M * K + K * N + M * N) * batch + extra_bytes
+        r = {"kernel_name": name, "dtype": "float32", "mode": mode, "M": M, "K": K, "N": N, "batch": batch,
+             "time_ms": t_med, "time_ms_best": t_best, "tflops": flops / t_med / 1e9,
+             "bandwidth_gb_s": byts / t_med / 1e6,
+             "pct_of_cublas": (100.0 * cublas_ms / t_med) if cublas_ms else None,
+             "pct_of_tensor_peak": 100.0 * flops / t_med / 1e9 / tf32_peak,
+             "pct_of_hbm_peak": 100.0 * byts / t_med / 1e6 / hbm_peak, "peak_source": peak_src,
+             "gpus": 1, "gpu_name": gpu_name}
+        if cpu_rate:
+            r["cpu_time_ms"] = flops / cpu_rate * 1e3
+            r["cpu_cores"] = 1
+            r["cpu_time_note"] = "extrapolated from the reference CPU matmul at 1024^3 (one core)"
+        results.append(r)
+        print("%-28s %-7s %6dx%6dx%6d b=%-4d %9.3f ms %8.1f TFLOP/s %8.1f GB/s %s" %
+              (name, mode, M, K, N, batch, t_med, r["tflops"], r["bandwidth_gb_s"],
+               ("%.0f%% of cuBLAS-TF32" % r["pct_of_cublas"]) if cublas_ms else ""), flush=True)
+
+    # ---- GEMM sweep: squares and skinny shapes, given as (M, K, N) like the reference ----
+    shapes = [(1024, 1024, 1024), (2048, 2048, 2048), (4096, 4096, 4096), (8192, 8192, 8192),
+              (8192, 512, 8192), (8192, 8192, 512), (16, 8192, 8192)]
+    if not args.quick:
+        shapes.append((16384, 16384, 16384))
+    for (M, K, N) in shapes:
+        a, b = rnd(M, K), rnd(K, N)
+        it = iters_for(2.0 * M * K * N)
+        it = max(it, 20) if M * K * N >= 4096 ** 3 else it
+        if M >= 16384:
+            it = 5
+        _, cub = time_gpu(lambda: torch.matmul(a, b), it, trials=3)
+        for mode in ("tf32", "3xtf32"):
+            tb, tm = time_gpu(lambda: be.matmul(a, b, precision=mode), it)
+            record("b200_tcgen05_gemm", mode, M, K, N, 1, tb, tm, cub)
+        del a, b
+        torch.cuda.empty_cache()
+
+    # ---- attention: S = Q.K^T / 8, softmax, O = P.V  over [16, 12, 256, 64] ----
+    q, k, v = (torch.randn(16, 12, 256, 64, device="cuda", generator=gen) for _ in range(3))
+    for mode in ("tf32", "3xtf32"):
+        tb, tm = time_gpu(lambda: be.scaled_dot(q, k, v, precision=mode), 50)
+        # algorithmic traffic of the unfused form: Q,K read, S written, softmax read+write, P read, V read, O written
+        record("b200_attention_qk_softmax_pv", mode, 256, 64, 256, 192 * 2, tb, tm, None)
+        results[-1]["bandwidth_gb_s"] = 251.7e6 / (tm * 1e-3) / 1e9
+        results[-1]["pct_of_hbm_peak"] = 100.0 * (251.7e6 / (tm * 1e-3) / 1e9) / hbm_peak
+        results[-1]["note"] = "two batched GEMMs + row softmax; bytes = 251.7 MB algorithmic (unfused)"
+
+    # ---- MLP Linear: X [4096,768], W [3072,768] ----
+    x, w, dy = torch.randn(4096, 768, device="cuda", generator=gen), torch.randn(3072, 768, device="cuda", generator=gen) * 0.02, \
+        torch.randn(4096, 3072, device="cuda", generator=gen)
+    bias = torch.zeros(3072, device="cuda")
+    _, cub = time_gpu(lambda: torch.nn.functional.linear(x, w, bias), 50, trials=3)
+    for mode in ("tf32", "3xtf32"):
+        tb, tm = time_gpu(lambda: be.linear_forward(x, w, bias, gelu=True, precision=mode), 50)
+        record("b200_linear_bias_gelu_fwd", mode, 4096, 768, 3072, 1, tb, tm, cub)
+        tb, tm = time_gpu(lambda: be.linear_backward(x, w, dy, precision=mode), 50)
+        record("b200_linear_bwd_dx_dw_db", mode, 4096, 3072, 768, 2, tb, tm, None)
+    be.check_device_status()
+    os.makedirs(os.path.dirname(args.out), exist_ok=True)
+    with open(args.out, "w") as f:
+        json.dump(results, f, indent=1)
+    print("wrote %d results to %s" % (len(results), args.out))
+
+
+if __name__ == "__main__":
+    main()

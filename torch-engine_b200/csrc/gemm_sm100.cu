@@ -4,11 +4,11 @@
 //
 // One persistent CTA per SM walks a list of 128 x BN output tiles.  Inside a CTA the work is
 // split by warp role:
-//   warps 0-3  epilogue: tcgen05.ld the finished accumulator out of TMEM, apply scale / bias /
+//   warps 0-7  epilogue: tcgen05.ld the finished accumulator out of TMEM, apply scale / bias /
 //              GELU, store to global memory;
-//   warp  4    producer: one lane issues TMA tensor loads (128-byte swizzle, each CTA for itself) of the
+//   warp  8    producer: one lane issues TMA tensor loads (128-byte swizzle, each CTA for itself) of the
 //              A and B k-blocks into a ring of shared-memory stages;
-//   warp  5    MMA: one lane issues tcgen05.mma kind::tf32 (128 x BN x 8 per instruction) from
+//   warp  9    MMA: one lane issues tcgen05.mma kind::tf32 (128 x BN x 8 per instruction) from
 //              shared-memory descriptors into one of two TMEM accumulator buffers, so the
 //              epilogue of tile i overlaps the main loop of tile i+1.
 // Stage hand-off is by mbarriers (full: TMA bytes landed; empty: tcgen05.commit after the MMAs
@@ -37,7 +37,7 @@ namespace te {
 
 
 template <int BN, int NPL, bool A_MN, bool B_MN>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(CTA_THREADS, 1)
 gemm_tf32_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_a_lo,
                  const __grid_constant__ CUtensorMap tm_b, const __grid_constant__ CUtensorMap tm_b_lo,
                  const GemmParams p) {
@@ -48,7 +48,7 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
     constexpr uint32_t IDESC = make_idesc_tf32(BM, BN, A_MN, B_MN);
     constexpr bool CHUNKED = (NPL == 2);      // 3xTF32: sum K in chunks, add the chunks in registers
     constexpr int CHUNK_KB = 8;               // k-blocks per chunk = 256 values of K
-    static_assert(!CHUNKED || BN <= 128, "chunked accumulation keeps BN floats per thread in registers");
+    static_assert(!CHUNKED || BN <= 256, "chunked accumulation keeps BN/2 floats per thread in registers");
     // Descriptor geometry.
     // K-major (TMA SWIZZLE_128B): rows of 128 B, 8-row groups 1024 B apart (SBO); one MMA advances 32 B along K.
     // MN-major (TMA SWIZZLE_128B_ATOM_32B): every k index is a 128-byte row of 32 consecutive MN elements;
@@ -84,14 +84,14 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
         }
         for (int i = 0; i < 2; ++i) {
             mbar_init(bar_tmem_full + 8 * i, 1);
-            mbar_init(bar_tmem_empty + 8 * i, 4);   // one arrival per epilogue warp
+            mbar_init(bar_tmem_empty + 8 * i, EPI_WARPS);   // one arrival per epilogue warp
         }
         mbar_init(bar_teardown, 1);
         *abort_flag = 0;
         fence_barrier_init();
         fence_proxy_async_smem();
     }
-    if (warp == 4 && lane == 0) {
+    if (warp == PRODUCER_WARP && lane == 0) {
         tma_prefetch_desc(&tm_a);
         tma_prefetch_desc(&tm_b);
         if (NPL == 2) {
@@ -99,7 +99,7 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
             tma_prefetch_desc(&tm_b_lo);
         }
     }
-    if (warp == 5) {
+    if (warp == MMA_WARP) {
         tmem_alloc(tmem_slot_addr, Cfg::TMEM_COLS);
         tmem_relinquish();
     }
@@ -111,7 +111,7 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
     const int total_tiles = p.tiles_m * p.tiles_n * p.num_batches;
     const int kblocks = (p.K + BK - 1) / BK;
 
-    if (warp == 4) {
+    if (warp == PRODUCER_WARP) {
         // ------------------------------------------------------------ TMA producer
         if (lane == 0) {
             int issued = 0;
@@ -169,7 +169,7 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                 }
             }
         }
-    } else if (warp == 5) {
+    } else if (warp == MMA_WARP) {
         // ------------------------------------------------------------ MMA issuer
         if (lane == 0) {
             int consumed = 0;
@@ -231,14 +231,14 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
             }
         }
     } else {
-        // ------------------------------------------------------------ epilogue (warps 0-3)
+        // ------------------------------------------------------------ epilogue (warps 0-7)
         int acc_idx = 0;
         bool ok = true;
         for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
             int batch, m_blk, n_blk;
             tile_coords(t, p, batch, m_blk, n_blk);
             const int bo = batch / p.batch_inner, bi = batch - bo * p.batch_inner;
-            const int row = m_blk * BM + warp * 32 + lane;
+            const int row = m_blk * BM + (warp & 3) * 32 + lane;
             const int n0 = n_blk * BN;
             const long long batch_off = (long long)bo * p.c_stride_outer + (long long)bi * p.c_stride_inner;
             EpilogueRow er;
@@ -252,7 +252,8 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                 // Two-level accumulation: the tensor core sums CHUNK_KB k-blocks in TMEM (its fp32 adder
                 // truncates, which biases long sums), the partial sums are then added here in registers with
                 // round-to-nearest.  This keeps the 3xTF32 result at FP32 accuracy for any K.
-                constexpr int NACC = CHUNKED ? BN : 1;
+                constexpr int NACC = CHUNKED ? BN / 2 : 1;     // this warp's half of the tile's columns
+                const int nh = n0 + (warp >> 2) * (BN / 2);
                 float acc[NACC];
 #pragma unroll
                 for (int j = 0; j < NACC; ++j) acc[j] = 0.0f;
@@ -264,13 +265,13 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                     ok = __all_sync(0xffffffffu, ok);
                     if (!ok) break;
                     tc_fence_after_sync();
-                    const uint32_t t_row = tmem_base + (uint32_t(warp * 32) << 16) + buf * BN;
+                    const uint32_t t_row = tmem_base + (uint32_t((warp & 3) * 32) << 16) + buf * BN;
                     if (p.K > 0) {
 #pragma unroll
                         for (int cc = 0; cc < NACC / 32; ++cc) {
-                            if (n0 + cc * 32 < p.N) {   // warp-uniform
+                            if (nh + cc * 32 < p.N) {   // warp-uniform
                                 uint32_t r[32];
-                                tmem_ld_32x32b_x32(t_row + cc * 32, r);
+                                tmem_ld_32x32b_x32(t_row + (warp >> 2) * (BN / 2) + cc * 32, r);
                                 tmem_ld_wait();
 #pragma unroll
                                 for (int j = 0; j < 32; ++j) acc[cc * 32 + j] += __uint_as_float(r[j]);
@@ -284,7 +285,7 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                 if (ok) {
 #pragma unroll
                     for (int cc = 0; cc < NACC / 32; ++cc) {
-                        const int col0 = n0 + cc * 32;
+                        const int col0 = nh + cc * 32;
                         if (col0 < p.N) epilogue_store32(&acc[cc * 32], col0, er, p);
                     }
                 }
@@ -295,9 +296,9 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
                 tc_fence_after_sync();
-                const uint32_t t_row = tmem_base + (uint32_t(warp * 32) << 16) + buf * BN;
+                const uint32_t t_row = tmem_base + (uint32_t((warp & 3) * 32) << 16) + buf * BN;
 #pragma unroll 1
-                for (int cc = 0; cc < BN / 32; ++cc) {
+                for (int cc = (warp >> 2) * (BN / 64); cc < ((warp >> 2) + 1) * (BN / 64); ++cc) {
                     const int col0 = n0 + cc * 32;
                     if (col0 >= p.N) break;   // warp-uniform
                     uint32_t r[32];
@@ -320,7 +321,7 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
     __syncwarp();
     tc_fence_before_sync();
     __syncthreads();
-    if (warp == 5) {
+    if (warp == MMA_WARP) {
         tc_fence_after_sync();
         tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
     }
@@ -420,7 +421,7 @@ static int launch_variant(te_b200_ctx* ctx, const GemmProblem& g, cudaStream_t s
     p.tiles_n = (int)((g.N + BN - 1) / BN);
     const long long total = (long long)p.tiles_m * p.tiles_n * p.num_batches;
     const int grid = (int)(total < ctx->sm_count ? total : ctx->sm_count);
-    kernel<<<grid, 192, Cfg::SMEM_BYTES, stream>>>(ma, mal, mb, mbl, p);
+    kernel<<<grid, CTA_THREADS, Cfg::SMEM_BYTES, stream>>>(ma, mal, mb, mbl, p);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return cuda_fail(e, "gemm_tf32_kernel launch");
     ctx->launches += 1;
@@ -439,15 +440,41 @@ static int launch_bn(te_b200_ctx* ctx, const GemmProblem& g, cudaStream_t stream
     return launch_variant<BN, 1, true, true>(ctx, g, stream);
 }
 
-int launch_gemm(te_b200_ctx* ctx, const GemmProblem& g, cudaStream_t stream) {
-    if (g.a_lo) {
-        if (g.N > 64) return launch_bn<128>(ctx, g, stream);
-        return launch_bn<64>(ctx, g, stream);
+// Tile-shape choice.  Larger tiles move fewer bytes into shared memory per flop (the pair tile least of all) but
+// give fewer tiles; with too few tiles most SMs idle.  The estimate below is waves x (k-blocks x time per k-block
+// + a fixed per-tile cost) with per-k-block times measured on 8192^3 for each shape (ns): they encode that the
+// small shapes are bound by filling shared memory, not by the tensor pipe.
+struct TileChoice { int bn; bool pair; };
+
+static TileChoice choose_tile(const te_b200_ctx* ctx, const GemmProblem& g) {
+    const double kblocks = (double)((g.K + BK - 1) / BK);
+    const double batches = (double)(g.batch_inner * g.batch_outer);
+    struct Cand { int bn; bool pair; double ns_per_kblock; double fixed_ns; };
+    const Cand cands[4] = {{256, true, 405.0, 3000.0}, {256, false, 432.0, 3000.0}, {128, false, 350.0, 2000.0},
+                           {64, false, 291.0, 1500.0}};
+    TileChoice best{64, false};
+    double best_t = 1e300;
+    for (const Cand& c : cands) {
+        if (c.pair && (g.M <= 128 || g.N <= 128 || g.a_lo)) continue;
+        if (g.a_lo && c.bn > 128) continue;                      // 3xTF32 keeps bn/2 accumulators per thread
+        if (c.bn > 64 && g.N <= c.bn / 2) continue;              // more than half of the tile would be padding
+        const double tm = (double)((g.M + (c.pair ? 255 : 127)) / (c.pair ? 256 : 128));
+        const double tn = (double)((g.N + c.bn - 1) / c.bn);
+        const double tiles = tm * tn * batches;
+        const double slots = c.pair ? ctx->sm_count / 2 : ctx->sm_count;
+        const double waves = (double)(long long)((tiles + slots - 1) / slots);
+        const double planes = g.a_lo ? 3.0 : 1.0;
+        const double t = waves * (kblocks * c.ns_per_kblock * planes + c.fixed_ns);
+        if (t < best_t) { best_t = t; best = TileChoice{c.bn, c.pair}; }
     }
-    if (!g.a_lo && g.M > 128 && g.N > 128 && !getenv("TE_DEBUG_NO_2CTA")) return launch_gemm_2cta(ctx, g, stream);
-    if (const char* f = getenv("TE_DEBUG_FORCE_BN")) { if (atoi(f) == 128) return launch_bn<128>(ctx, g, stream); if (atoi(f) == 64) return launch_bn<64>(ctx, g, stream); }
-    if (g.N > 128) return launch_bn<256>(ctx, g, stream);
-    if (g.N > 64) return launch_bn<128>(ctx, g, stream);
+    return best;
+}
+
+int launch_gemm(te_b200_ctx* ctx, const GemmProblem& g, cudaStream_t stream) {
+    const TileChoice c = choose_tile(ctx, g);
+    if (c.pair) return launch_gemm_2cta(ctx, g, stream);
+    if (c.bn == 256) return launch_bn<256>(ctx, g, stream);
+    if (c.bn == 128) return launch_bn<128>(ctx, g, stream);
     return launch_bn<64>(ctx, g, stream);
 }
 

@@ -7,7 +7,7 @@
 // reads both halves straight out of the two CTAs' shared memories.  Per CTA that is 32 KB for the same amount of
 // tensor work, and no load is broadcast between CTAs.
 //
-// Roles per CTA are as in the single-CTA kernel (warps 0-3 epilogue, warp 4 TMA producer, warp 5 MMA), with the
+// Roles per CTA are as in the single-CTA kernel (warps 0-7 epilogue, warp 8 TMA producer, warp 9 MMA), with the
 // pair protocol on top:
 //   * "full" barriers live in the leader CTA (cluster rank 0): both producers post their byte counts there;
 //   * the leader's MMA lane issues for the pair and commits to the "empty" and "accumulator full" barriers of
@@ -43,7 +43,7 @@ __device__ __forceinline__ void pair_tile_coords(int t, const GemmParams& p, int
 }
 
 template <int BN, bool A_MN, bool B_MN>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(CTA_THREADS, 1)
 gemm_tf32_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                       const GemmParams p) {
     using Cfg = PairCfg<BN>;
@@ -86,18 +86,18 @@ gemm_tf32_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
         }
         for (int i = 0; i < 2; ++i) {
             mbar_init(bar_tmem_full + 8 * i, 1);
-            mbar_init(bar_tmem_empty + 8 * i, 8);     // leader's copy: 4 epilogue warps of each CTA
+            mbar_init(bar_tmem_empty + 8 * i, 2 * EPI_WARPS);   // leader's copy: the epilogue warps of both CTAs
         }
         mbar_init(bar_teardown, 1);
         *abort_flag = 0;
         fence_barrier_init();
         fence_proxy_async_smem();
     }
-    if (warp == 4 && lane == 0) {
+    if (warp == PRODUCER_WARP && lane == 0) {
         tma_prefetch_desc(&tm_a);
         tma_prefetch_desc(&tm_b);
     }
-    if (warp == 5) {
+    if (warp == MMA_WARP) {
         tmem_alloc_pair(tmem_slot_addr, Cfg::TMEM_COLS);
         tmem_relinquish_pair();
     }
@@ -110,7 +110,7 @@ gemm_tf32_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
     const int total_tiles = p.tiles_m * p.tiles_n * p.num_batches;
     const int kblocks = (p.K + BK - 1) / BK;
 
-    if (warp == 4) {
+    if (warp == PRODUCER_WARP) {
         // ------------------------------------------------------------ TMA producer (both CTAs)
         if (lane == 0) {
             int issued = 0;
@@ -158,7 +158,7 @@ gemm_tf32_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
                 }
             }
         }
-    } else if (warp == 5) {
+    } else if (warp == MMA_WARP) {
         // ------------------------------------------------------------ MMA issuer (leader CTA only)
         if (lane == 0 && leader) {
             int consumed = 0;
@@ -203,14 +203,14 @@ gemm_tf32_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
             }
         }
     } else {
-        // ------------------------------------------------------------ epilogue (warps 0-3, both CTAs)
+        // ------------------------------------------------------------ epilogue (warps 0-7, both CTAs)
         int acc_idx = 0;
         bool ok = true;
         for (int t = pair; t < total_tiles && ok; t += num_pairs, ++acc_idx) {
             int batch, m_blk, n_blk;
             pair_tile_coords(t, p, batch, m_blk, n_blk);
             const int bo = batch / p.batch_inner, bi = batch - bo * p.batch_inner;
-            const int row = m_blk * PAIR_BM + (int)rank * BM + warp * 32 + lane;
+            const int row = m_blk * PAIR_BM + (int)rank * BM + (warp & 3) * 32 + lane;
             const int n0 = n_blk * BN;
             const long long batch_off = (long long)bo * p.c_stride_outer + (long long)bi * p.c_stride_inner;
             EpilogueRow er;
@@ -224,9 +224,9 @@ gemm_tf32_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             tc_fence_after_sync();
-            const uint32_t t_row = tmem_base + (uint32_t(warp * 32) << 16) + buf * BN;
+            const uint32_t t_row = tmem_base + (uint32_t((warp & 3) * 32) << 16) + buf * BN;
 #pragma unroll 1
-            for (int cc = 0; cc < BN / 32; ++cc) {
+            for (int cc = (warp >> 2) * (BN / 64); cc < ((warp >> 2) + 1) * (BN / 64); ++cc) {
                 const int col0 = n0 + cc * 32;
                 if (col0 >= p.N) break;
                 uint32_t r[32];
@@ -247,7 +247,7 @@ gemm_tf32_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
     tc_fence_before_sync();
     __syncthreads();
     cluster_sync_all();          // nobody leaves while the partner may still touch this CTA's memory or barriers
-    if (warp == 5) {
+    if (warp == MMA_WARP) {
         tc_fence_after_sync();
         tmem_dealloc_pair(tmem_base, Cfg::TMEM_COLS);
     }
@@ -278,7 +278,7 @@ static int launch_pair_variant(te_b200_ctx* ctx, const GemmProblem& g, cudaStrea
     if (max_pairs == 0) {
         cudaLaunchConfig_t cfg = {};
         cfg.gridDim = dim3(ctx->sm_count & ~1, 1, 1);
-        cfg.blockDim = dim3(192, 1, 1);
+        cfg.blockDim = dim3(CTA_THREADS, 1, 1);
         cfg.dynamicSmemBytes = Cfg::SMEM_BYTES;
         cudaLaunchAttribute attr;
         attr.id = cudaLaunchAttributeClusterDimension;
@@ -293,7 +293,7 @@ static int launch_pair_variant(te_b200_ctx* ctx, const GemmProblem& g, cudaStrea
         if (getenv("TE_DEBUG_VERBOSE")) fprintf(stderr, "[te_b200] resident CTA pairs: %d\n", n);
     }
     const int pairs = (int)(total < max_pairs ? total : max_pairs);
-    kernel<<<2 * pairs, 192, Cfg::SMEM_BYTES, stream>>>(ma, mb, p);
+    kernel<<<2 * pairs, CTA_THREADS, Cfg::SMEM_BYTES, stream>>>(ma, mb, p);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return cuda_fail(e, "gemm_tf32_pair_kernel launch");
     ctx->launches += 1;
