@@ -265,6 +265,22 @@ def test_host_buffer_entry_point(backend, oracle):
     d.precision = L.TE_PREC_3XTF32
     backend.gemm_host(d)
     assert_close(c, oracle.matmul(a, b), "3xtf32", "host entry")
+    # a tall product in TF32 mode takes the row-block pipeline (copy-in / multiply / copy-out overlapped)
+    M, K, N = 2500, 192, 520
+    a, b, bias = rng.uniform((M, K)), rng.uniform((K, N)), rng.uniform((N,))
+    c = np.full((M, N), np.nan, dtype=np.float32)
+    pre = np.full((M, N), np.nan, dtype=np.float32)
+    d = L.GemmDesc()
+    d.M, d.N, d.K = M, N, K
+    d.a, d.b, d.c = a.ctypes.data, b.ctypes.data, c.ctypes.data
+    d.lda, d.ldb, d.ldc = K, N, N
+    d.batch_outer = d.batch_inner = 1
+    d.precision = L.TE_PREC_TF32
+    d.epilogue, d.bias, d.preact_out = L.TE_EPI_BIAS_GELU, bias.ctypes.data, pre.ctypes.data
+    backend.gemm_host(d)
+    pre_ref = oracle.add_bias(oracle.matmul_2d_threads(a, b), bias)
+    assert_close(pre, pre_ref, "tf32", "pipelined host entry, pre-activation")
+    assert np.abs(c - oracle.gelu(pre)).max() <= 1e-5
 
 
 def test_launch_counter_moves(backend):

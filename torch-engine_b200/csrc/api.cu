@@ -250,6 +250,10 @@ int te_b200_destroy(te_b200_ctx* ctx) {
     cudaFree(ctx->d_status);
     cudaFree(ctx->workspace);
     if (ctx->host_stage) cudaFree(ctx->host_stage);
+    if (ctx->host_pipe_ready) {
+        for (int i = 0; i < 3; ++i) cudaStreamDestroy(ctx->host_streams[i]);
+        for (int i = 0; i < 33; ++i) cudaEventDestroy(ctx->host_events[i]);
+    }
     cudaSetDevice(prev);
     delete ctx;
     return TE_OK;
@@ -405,6 +409,50 @@ int te_b200_gemm_f32_host(te_b200_ctx* ctx, const te_gemm_desc* h) {
     float* dc = st.take(c_el * 4);
     float* dbias = bias_el ? st.take(bias_el * 4) : nullptr;
     float* dpre = pre_el ? st.take(pre_el * 4) : nullptr;
+    // Large single products with a row-major A are pipelined by row blocks: B goes in once, then block i of A is
+    // copied in while block i-1 is multiplied and block i-2 of C is copied out (PCIe runs in both directions).
+    const bool pipelined = h->batch_outer * h->batch_inner == 1 && h->a_major == TE_ROW_MAJOR && h->M >= 1024 &&
+                           h->K > 0 && h->precision == TE_PREC_TF32;
+    if (pipelined) {
+        if (!ctx->host_pipe_ready) {
+            for (int i = 0; i < 3; ++i)
+                if ((e = cudaStreamCreateWithFlags(&ctx->host_streams[i], cudaStreamNonBlocking)) != cudaSuccess)
+                    return cuda_fail(e, "cudaStreamCreateWithFlags");
+            for (int i = 0; i < 33; ++i)
+                if ((e = cudaEventCreateWithFlags(&ctx->host_events[i], cudaEventDisableTiming)) != cudaSuccess)
+                    return cuda_fail(e, "cudaEventCreateWithFlags");
+            ctx->host_pipe_ready = true;
+        }
+        cudaStream_t s_in = ctx->host_streams[0], s_mm = ctx->host_streams[1], s_out = ctx->host_streams[2];
+        constexpr int MAX_BLOCKS = 16;
+        int64_t rows_per = round_up((h->M + 7) / 8, 256);
+        int nblk = (int)((h->M + rows_per - 1) / rows_per);
+        if (nblk > MAX_BLOCKS) { rows_per = round_up((h->M + MAX_BLOCKS - 1) / MAX_BLOCKS, 256); nblk = (int)((h->M + rows_per - 1) / rows_per); }
+        if ((e = cudaMemcpyAsync(db, h->b, b_el * 4, cudaMemcpyHostToDevice, s_in)) != cudaSuccess) return cuda_fail(e, "H2D B");
+        if (bias_el && (e = cudaMemcpyAsync(dbias, h->bias, bias_el * 4, cudaMemcpyHostToDevice, s_in)) != cudaSuccess) return cuda_fail(e, "H2D bias");
+        cudaEventRecord(ctx->host_events[32], s_in);
+        cudaStreamWaitEvent(s_mm, ctx->host_events[32], 0);
+        for (int i = 0; i < nblk; ++i) {
+            const int64_t r0 = i * rows_per;
+            const int64_t rows = (r0 + rows_per <= h->M) ? rows_per : h->M - r0;
+            const int64_t a_cnt = (rows - 1) * h->lda + h->K, c_cnt = (rows - 1) * h->ldc + h->N;
+            if ((e = cudaMemcpyAsync(da + r0 * h->lda, h->a + r0 * h->lda, a_cnt * 4, cudaMemcpyHostToDevice, s_in)) != cudaSuccess) return cuda_fail(e, "H2D A block");
+            cudaEventRecord(ctx->host_events[i], s_in);
+            cudaStreamWaitEvent(s_mm, ctx->host_events[i], 0);
+            te_gemm_desc d = *h;
+            d.M = rows;
+            d.a = da + r0 * h->lda; d.b = db; d.c = dc + r0 * h->ldc; d.bias = dbias;
+            d.preact_out = dpre ? dpre + r0 * h->ldc : nullptr;
+            if ((rc = gemm_device(ctx, &d, s_mm))) return rc;
+            cudaEventRecord(ctx->host_events[16 + i], s_mm);
+            cudaStreamWaitEvent(s_out, ctx->host_events[16 + i], 0);
+            if ((e = cudaMemcpyAsync(h->c + r0 * h->ldc, dc + r0 * h->ldc, c_cnt * 4, cudaMemcpyDeviceToHost, s_out)) != cudaSuccess) return cuda_fail(e, "D2H C block");
+            if (dpre && (e = cudaMemcpyAsync(h->preact_out + r0 * h->ldc, dpre + r0 * h->ldc, c_cnt * 4, cudaMemcpyDeviceToHost, s_out)) != cudaSuccess) return cuda_fail(e, "D2H preact block");
+        }
+        if ((e = cudaStreamSynchronize(s_out)) != cudaSuccess) return cuda_fail(e, "cudaStreamSynchronize");
+        if ((e = cudaStreamSynchronize(s_mm)) != cudaSuccess) return cuda_fail(e, "cudaStreamSynchronize");
+        return te_b200_check_device_status(ctx);
+    }
     cudaStream_t s = 0;
     if (a_el && (e = cudaMemcpyAsync(da, h->a, a_el * 4, cudaMemcpyHostToDevice, s)) != cudaSuccess) return cuda_fail(e, "H2D A");
     if (b_el && (e = cudaMemcpyAsync(db, h->b, b_el * 4, cudaMemcpyHostToDevice, s)) != cudaSuccess) return cuda_fail(e, "H2D B");

@@ -45,6 +45,10 @@ struct te_b200_ctx {
     void* encode_tiled = nullptr; // cuTensorMapEncodeTiled, resolved through the runtime
     void* host_stage = nullptr;   // grow-only device staging used by the host-buffer entry point
     size_t host_stage_bytes = 0;
+    // host-buffer entry point: copy-in, compute and copy-out streams plus per-block events (created on first use)
+    cudaStream_t host_streams[3] = {nullptr, nullptr, nullptr};
+    cudaEvent_t host_events[33] = {};
+    bool host_pipe_ready = false;
 };
 
 namespace te {
