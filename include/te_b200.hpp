@@ -1,0 +1,231 @@
+// te_b200.hpp -- header-only C++17 host adapter over the C ABI of te_b200.h.
+//
+// It carries the names and calling conventions of the reference's host API for the matmul path, so that code
+// written against the reference reads the same here:
+//   te::Tensor          Tensor(shape, dtype=Float32, Device::CUDA), shape(), strides(), data(), view(),
+//                       transpose_view(d1, d2), matmul(other)        (reference src/tensor/tensor.h:92-130, :908)
+//   te::Linear          forward(x) = x.matmul(W.transpose_view(1,0)) + b   (reference src/nn/linear.cpp:14-23)
+//   te::FeedForward     Linear -> GELU -> Linear                           (reference src/nn/ffn.cpp:12-16)
+//   te::ScaledDot       softmax(Q.K^T / sqrt(d)).V                         (reference src/nn/scaledot.cpp:8-27)
+// Errors surface as std::runtime_error with the reference's texts (src/tensor/tensor.h:537, :547, :626, :858).
+// Tensors live on the GPU only: this backend has no CPU compute path.  Each Tensor owns (or shares) one
+// cudaMalloc'ed buffer, as the reference's CUDAAllocator does (src/core/allocators.h:35-52).
+#pragma once
+#include <cuda_runtime.h>
+
+#include <cmath>
+#include <cstdint>
+#include <memory>
+#include <stdexcept>
+#include <string>
+#include <vector>
+
+#include "te_b200.h"
+
+namespace te {
+
+inline void check(int rc) {
+    if (rc != TE_OK) {
+        const char* msg = te_b200_last_error();
+        throw std::runtime_error((msg && *msg) ? msg : te_b200_status_string(rc));
+    }
+}
+inline void cuda_check(cudaError_t e, const char* what) {
+    if (e != cudaSuccess) throw std::runtime_error(std::string(what) + ": " + cudaGetErrorString(e));
+}
+
+// One context per process and device, created on first use (the role of cuda_cublas_handle(),
+// reference src/core/cuda_utils.cpp:48-55).  TENSOR_GEMM_PRECISION=3xtf32 selects the FP32-accurate mode.
+class Backend {
+public:
+    static Backend& instance() {
+        static Backend b;
+        return b;
+    }
+    te_b200_ctx* ctx() const { return ctx_; }
+    int precision() const { return precision_; }
+    void set_precision(int p) { precision_ = p; }
+    void synchronize() {
+        cuda_check(cudaDeviceSynchronize(), "cudaDeviceSynchronize");
+        check(te_b200_check_device_status(ctx_));
+    }
+private:
+    Backend() {
+        check(te_b200_init(0, size_t(1) << 30, &ctx_));
+        const char* p = std::getenv("TENSOR_GEMM_PRECISION");
+        precision_ = (p && std::string(p) == "3xtf32") ? TE_PREC_3XTF32 : TE_PREC_TF32;
+    }
+    ~Backend() { te_b200_destroy(ctx_); }
+    te_b200_ctx* ctx_ = nullptr;
+    int precision_ = TE_PREC_TF32;
+};
+
+class Tensor {
+public:
+    Tensor() = default;
+    explicit Tensor(std::vector<int64_t> shape) : shape_(std::move(shape)) {
+        strides_.assign(shape_.size(), 1);
+        for (int i = (int)shape_.size() - 2; i >= 0; --i) strides_[i] = strides_[i + 1] * shape_[i + 1];
+        void* p = nullptr;
+        const size_t n = numel();
+        cuda_check(cudaMalloc(&p, (n ? n : 1) * sizeof(float)), "cudaMalloc");
+        storage_ = std::shared_ptr<void>(p, [](void* q) { cudaFree(q); });
+    }
+    static Tensor from_host(const std::vector<float>& v, std::vector<int64_t> shape) {
+        Tensor t(std::move(shape));
+        if (v.size() != t.numel()) throw std::runtime_error("from_host: element count does not match the shape");
+        cuda_check(cudaMemcpy(t.data(), v.data(), v.size() * sizeof(float), cudaMemcpyHostToDevice), "cudaMemcpy H2D");
+        return t;
+    }
+    // Row-major copy of the logical contents (views are gathered on the host side).
+    std::vector<float> to_host() const {
+        int64_t lo = 0, hi = 0;   // span of the view inside the storage, relative to offset_
+        for (size_t i = 0; i < shape_.size(); ++i)
+            if (shape_[i] > 0) (strides_[i] >= 0 ? hi : lo) += (shape_[i] - 1) * strides_[i];
+        std::vector<float> raw((size_t)(hi - lo + 1));
+        std::vector<float> out(numel());
+        if (out.empty()) return out;
+        cuda_check(cudaMemcpy(raw.data(), data() + lo, raw.size() * sizeof(float), cudaMemcpyDeviceToHost), "cudaMemcpy D2H");
+        std::vector<int64_t> idx(shape_.size(), 0);
+        for (size_t flat = 0; flat < out.size(); ++flat) {
+            int64_t off = -lo;
+            for (size_t d = 0; d < shape_.size(); ++d) off += idx[d] * strides_[d];
+            out[flat] = raw[(size_t)off];
+            for (int d = (int)shape_.size() - 1; d >= 0; --d) {
+                if (++idx[d] < shape_[d]) break;
+                idx[d] = 0;
+            }
+        }
+        return out;
+    }
+
+    size_t numel() const {
+        size_t n = 1;
+        for (int64_t d : shape_) n *= (size_t)d;
+        return n;
+    }
+    const std::vector<int64_t>& shape() const { return shape_; }
+    const std::vector<int64_t>& strides() const { return strides_; }   // in elements
+    float* data() const { return static_cast<float*>(storage_.get()) + offset_; }   // includes the view offset
+    bool is_contiguous() const {
+        int64_t run = 1;
+        for (int i = (int)shape_.size() - 1; i >= 0; --i) {
+            if (shape_[i] != 1 && strides_[i] != run) return false;
+            run *= shape_[i];
+        }
+        return true;
+    }
+
+    // Zero-copy stride swap (reference src/tensor/tensor.cpp:590-620).
+    Tensor transpose_view(size_t d1, size_t d2) const {
+        if (d1 >= shape_.size() || d2 >= shape_.size()) throw std::runtime_error("transpose_view: dimension out of range");
+        Tensor t = *this;
+        std::swap(t.shape_[d1], t.shape_[d2]);
+        std::swap(t.strides_[d1], t.strides_[d2]);
+        return t;
+    }
+    // Zero-copy reshape of a contiguous tensor (reference src/tensor/tensor.cpp:233-255).
+    Tensor view(const std::vector<int64_t>& new_shape) const {
+        if (!is_contiguous()) throw std::runtime_error("view requires a contiguous tensor");
+        size_t n = 1;
+        for (int64_t d : new_shape) n *= (size_t)d;
+        if (n != numel()) throw std::runtime_error("view: element count mismatch");
+        Tensor t = *this;
+        t.shape_ = new_shape;
+        t.strides_.assign(new_shape.size(), 1);
+        for (int i = (int)new_shape.size() - 2; i >= 0; --i) t.strides_[i] = t.strides_[i + 1] * new_shape[i + 1];
+        return t;
+    }
+
+    // Tensor::matmul (reference src/tensor/tensor.cpp:761-785): >= 2-D operands, NumPy batch broadcasting,
+    // fresh contiguous result; asynchronous on the legacy default stream like the reference's launches.
+    Tensor matmul(const Tensor& other) const {
+        int64_t out_shape[8];
+        int out_ndim = 0;
+        check(te_b200_matmul_nd(nullptr, nullptr, shape_.data(), strides_.data(), (int)shape_.size(), nullptr,
+                                other.shape_.data(), other.strides_.data(), (int)other.shape_.size(), nullptr, out_shape,
+                                &out_ndim, TE_PREC_TF32, nullptr));
+        Tensor result(std::vector<int64_t>(out_shape, out_shape + out_ndim));
+        Backend& be = Backend::instance();
+        check(te_b200_matmul_nd(be.ctx(), data(), shape_.data(), strides_.data(), (int)shape_.size(), other.data(),
+                                other.shape_.data(), other.strides_.data(), (int)other.shape_.size(), result.data(),
+                                nullptr, nullptr, be.precision(), nullptr));
+        return result;
+    }
+
+private:
+    std::shared_ptr<void> storage_;
+    std::vector<int64_t> shape_, strides_;
+    int64_t offset_ = 0;
+};
+
+// Linear::forward with the bias add (and optionally FeedForward's GELU) fused into the GEMM epilogue.
+class Linear {
+public:
+    Linear(int64_t in_features, int64_t out_features)
+        : in_(in_features), out_(out_features), weight_({out_features, in_features}), bias_({out_features}) {}
+    Tensor& weight() { return weight_; }   // [out, in], as in the reference
+    Tensor& bias() { return bias_; }
+    Tensor forward(const Tensor& x, bool gelu = false, Tensor* preact = nullptr) const {
+        if (x.shape().empty() || x.shape().back() != in_) throw std::runtime_error("Inner dimensions must match for matmul");
+        if (!x.is_contiguous()) throw std::runtime_error("Linear::forward expects a contiguous input");
+        std::vector<int64_t> ys = x.shape();
+        ys.back() = out_;
+        Tensor y(ys);
+        if (preact) *preact = Tensor(ys);
+        Backend& be = Backend::instance();
+        check(te_b200_linear_forward(be.ctx(), x.data(), weight_.data(), bias_.data(), y.data(),
+                                     preact ? preact->data() : nullptr, (int64_t)(x.numel() / (size_t)in_), in_, out_,
+                                     gelu ? 1 : 0, be.precision(), nullptr));
+        return y;
+    }
+    // {dX, dW[out,in], db[out]} in the order the reference's backward nodes produce them.
+    std::vector<Tensor> backward(const Tensor& x, const Tensor& dy) const {
+        Tensor dx(x.shape()), dw({out_, in_}), db({out_});
+        Backend& be = Backend::instance();
+        check(te_b200_linear_backward(be.ctx(), x.data(), weight_.data(), dy.data(), dx.data(), dw.data(), db.data(),
+                                      (int64_t)(x.numel() / (size_t)in_), in_, out_, be.precision(), nullptr));
+        return {dx, dw, db};
+    }
+private:
+    int64_t in_, out_;
+    Tensor weight_, bias_;
+};
+
+class FeedForward {
+public:
+    FeedForward(int64_t embed, int64_t ff) : linear1_(embed, ff), linear2_(ff, embed) {}
+    Linear& linear1() { return linear1_; }
+    Linear& linear2() { return linear2_; }
+    Tensor forward(const Tensor& x) const { return linear2_.forward(linear1_.forward(x, /*gelu=*/true)); }
+private:
+    Linear linear1_, linear2_;
+};
+
+class ScaledDot {
+public:
+    // Q, K, V: [B, H, T, d] tensors or views with unit last-dim stride (the MultiHeadAttention head views).
+    Tensor forward(const Tensor& Q, const Tensor& K, const Tensor& V, Tensor* probabilities = nullptr) const {
+        if (Q.shape().size() != 4 || Q.shape() != K.shape() || Q.shape() != V.shape())
+            throw std::runtime_error("ScaledDot expects Q, K, V of one [B,H,T,d] shape");
+        for (const Tensor* t : {&Q, &K, &V})
+            if (t->strides()[3] != 1) throw std::runtime_error(te_b200_status_string(TE_ERR_UNSUPPORTED_LAYOUT));
+        const int64_t B = Q.shape()[0], H = Q.shape()[1], T = Q.shape()[2], d = Q.shape()[3];
+        Tensor p({B, H, T, T}), o({B, H, T, d});
+        te_attn_desc a{};
+        a.B = B; a.H = H; a.T = T; a.d = d;
+        a.q = Q.data(); a.k = K.data(); a.v = V.data();
+        for (int i = 0; i < 3; ++i) {
+            a.q_strides[i] = Q.strides()[i]; a.k_strides[i] = K.strides()[i]; a.v_strides[i] = V.strides()[i];
+            a.o_strides[i] = o.strides()[i];
+        }
+        a.p_out = p.data(); a.o = o.data();
+        Backend& be = Backend::instance();
+        a.precision = be.precision();
+        check(te_b200_attention_forward(be.ctx(), &a, nullptr));
+        if (probabilities) *probabilities = p;
+        return o;
+    }
+};
+
+}  // namespace te

@@ -1,0 +1,98 @@
+// GPU check of the C++ host adapter (include/te_b200.hpp), laid out like the reference's own plain-main CUDA
+// check of Tensor::matmul (reference src/tests/cuda_matmul_tensor_test.cpp) and its throw / shape tests
+// (reference src/tests/tensor_test.cpp:597-725): same inputs, same expected values, exit code 0 on success.
+#include <cmath>
+#include <cstdio>
+#include <iostream>
+#include <numeric>
+#include <vector>
+
+#include "te_b200.hpp"
+
+using te::Tensor;
+
+static int failures = 0;
+
+static void expect_values(const char* what, const Tensor& t, const std::vector<float>& want, float tol) {
+    std::vector<float> got = t.to_host();
+    bool ok = got.size() == want.size();
+    for (size_t i = 0; ok && i < want.size(); ++i) ok = std::fabs(got[i] - want[i]) <= tol;
+    std::cout << (ok ? "ok   " : "FAIL ") << what << "\n";
+    if (!ok) ++failures;
+}
+
+template <typename F>
+static void expect_throw(const char* what, F&& f, const std::string& message) {
+    bool ok = false;
+    try {
+        f();
+    } catch (const std::runtime_error& e) {
+        ok = (message == e.what());
+        if (!ok) std::cout << "     got message: " << e.what() << "\n";
+    }
+    std::cout << (ok ? "ok   " : "FAIL ") << what << "\n";
+    if (!ok) ++failures;
+}
+
+static std::vector<float> iota(int n) {
+    std::vector<float> v(n);
+    std::iota(v.begin(), v.end(), 1.0f);
+    return v;
+}
+
+int main() {
+    try {
+        // 2-D: A 2x3 . B 3x4
+        Tensor a = Tensor::from_host(iota(6), {2, 3});
+        Tensor b = Tensor::from_host(iota(12), {3, 4});
+        expect_values("2x3 . 3x4", a.matmul(b), {38, 44, 50, 56, 83, 98, 113, 128}, 1e-5f);
+        // transposed-A view
+        Tensor a2 = Tensor::from_host(iota(6), {3, 2});
+        expect_values("transpose_view(0,1) . 3x4", a2.transpose_view(0, 1).matmul(b), {61, 70, 79, 88, 76, 88, 100, 112}, 1e-5f);
+        // batched 3-D
+        Tensor a3 = Tensor::from_host(iota(12), {2, 2, 3});
+        Tensor b3 = Tensor::from_host(iota(24), {2, 3, 4});
+        expect_values("batched 2x(2x3 . 3x4)", a3.matmul(b3),
+                      {38, 44, 50, 56, 83, 98, 113, 128, 416, 440, 464, 488, 569, 602, 635, 668}, 1e-4f);
+        // f32 2x3 . 3x2
+        expect_values("2x3 . 3x2", a.matmul(Tensor::from_host(iota(6), {3, 2})), {22, 28, 49, 64}, 0.0f);
+        // broadcast (1,2,3) @ (3,3,4) -> (3,2,4)
+        Tensor c = Tensor::from_host(iota(6), {1, 2, 3}).matmul(Tensor::from_host(iota(36), {3, 3, 4}));
+        const bool shape_ok = c.shape() == std::vector<int64_t>({3, 2, 4});
+        std::cout << (shape_ok ? "ok   " : "FAIL ") << "broadcast result shape\n";
+        if (!shape_ok) ++failures;
+        // the reference's throw cases, with its texts
+        expect_throw("inner dimension mismatch", [&] { Tensor({2, 3}).matmul(Tensor({2, 2})); },
+                     "Inner dimensions must match for matmul");
+        expect_throw("batch 3 vs 2", [&] { Tensor({3, 2, 3}).matmul(Tensor({2, 3, 4})); },
+                     "Batch dimensions are not broadcastable");
+        expect_throw("batch 2 vs 3", [&] { Tensor({2, 2, 3}).matmul(Tensor({3, 3, 4})); },
+                     "Batch dimensions are not broadcastable");
+        expect_throw("1-D operand", [&] { Tensor({3}).matmul(Tensor({3, 2})); },
+                     "Matmul requires tensors with at least 2 dimensions");
+        // Linear: y = x.W^T + b with W [out,in]
+        te::Linear lin(3, 2);
+        lin.weight() = Tensor::from_host({1, 0, -1, 2, 1, 0}, {2, 3});
+        lin.bias() = Tensor::from_host({0.5f, -1.0f}, {2});
+        expect_values("Linear forward", lin.forward(a), {1 - 3 + 0.5f, 2 + 2 - 1.0f, 4 - 6 + 0.5f, 8 + 5 - 1.0f}, 1e-5f);
+        // ScaledDot on MultiHeadAttention-style head views: uniform keys give the mean of V
+        const int64_t B = 2, T = 4, H = 2, hd = 8;
+        std::vector<float> q(B * T * H * hd, 0.0f), v(B * T * H * hd);
+        for (size_t i = 0; i < v.size(); ++i) v[i] = float(i % 7);
+        auto heads = [&](const std::vector<float>& x) { return Tensor::from_host(x, {B, T, H * hd}).view({B, T, H, hd}).transpose_view(1, 2); };
+        Tensor o = te::ScaledDot().forward(heads(q), heads(q), heads(v));
+        std::vector<float> want(B * H * T * hd);
+        for (int64_t bb = 0; bb < B; ++bb) for (int64_t h = 0; h < H; ++h) for (int64_t t = 0; t < T; ++t) for (int64_t e = 0; e < hd; ++e) {
+            float s = 0;
+            for (int64_t tt = 0; tt < T; ++tt) s += v[((bb * T + tt) * H + h) * hd + e];
+            want[((bb * H + h) * T + t) * hd + e] = s / T;
+        }
+        expect_values("ScaledDot on head views", o, want, 1e-2f);
+        te::Backend::instance().synchronize();
+    } catch (const std::exception& e) {
+        std::cout << "FAIL unexpected exception: " << e.what() << "\n";
+        return 1;
+    }
+    if (failures == 0) std::cout << "All C++ adapter checks passed.\n";
+    return failures == 0 ? 0 : 1;
+}

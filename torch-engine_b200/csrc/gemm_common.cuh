@@ -46,6 +46,7 @@ struct GemmParams {
     int scale_mode;
     int epilogue;
     int* status;
+    int tma_store;   // 1: outputs go through shared memory and TMA stores
 };
 
 template <int BN, int NPL>
@@ -54,8 +55,9 @@ struct TileCfg {
     static constexpr int STAGE_BYTES = NPL * (A_PLANE_BYTES + B_PLANE_BYTES);
     static constexpr int STAGES = SMEM_RING_BUDGET / STAGE_BYTES;
     static constexpr int TMEM_COLS = 2 * BN;  // two accumulator buffers of BN fp32 columns
-    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + SMEM_AUX_BYTES + 1024;  // +1024: manual alignment
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 8 * 32 * 128 + SMEM_AUX_BYTES + 1024;  // ring + 8 epilogue staging tiles + barriers + alignment slack
     static_assert(STAGES >= 2, "need at least a double buffer");
+    static_assert(SMEM_BYTES <= 232448, "exceeds the 227 KB of shared memory a CTA can have");
     static_assert(TMEM_COLS >= 32 && TMEM_COLS <= 512 && (TMEM_COLS & (TMEM_COLS - 1)) == 0, "TMEM columns");
 };
 
@@ -100,15 +102,46 @@ __device__ __forceinline__ float gelu_tanh(float x) {
     return 0.5f * x * (1.0f + t);
 }
 
+constexpr int EPI_STAGE_BYTES = 32 * 128;   // one warp's staging tile: 32 rows x 32 floats, 128-byte swizzled
+
 struct EpilogueRow {
     float* c_row;      // start of this thread's output row
     float* pre_row;    // same row of the optional pre-activation output
     bool row_ok;       // row < M
     bool vec_ok;       // 16-byte stores are legal
+    // TMA-store path (used when the output can be described by a tensor map)
+    bool tma_ok;
+    uint32_t stage;            // this warp's staging tile in shared memory
+    const CUtensorMap* tm_c;
+    const CUtensorMap* tm_pre;
+    int row0;                  // first of the 32 rows this warp owns
+    int bi, bo;                // batch coordinates
 };
 
+// The warp's 32 x 32 block goes through shared memory so that global memory is written in whole 128-byte lines by
+// the TMA unit instead of 32 scattered 16-byte pieces per store instruction.  Lane 0 owns the bulk group.
+__device__ __forceinline__ void stage_and_store32(const float* v, int col0, const EpilogueRow& er, const CUtensorMap* tm,
+                                                  int lane) {
+    if (lane == 0) bulk_wait_read_all();     // the previous store has finished reading the staging tile
+    __syncwarp();
+    const uint32_t row_addr = er.stage + lane * 128;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        const uint32_t unit = uint32_t(j) ^ (uint32_t(lane) & 7u);
+        asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(row_addr + unit * 16), "f"(v[4 * j]), "f"(v[4 * j + 1]),
+                     "f"(v[4 * j + 2]), "f"(v[4 * j + 3])
+                     : "memory");
+    }
+    fence_proxy_async_smem();
+    __syncwarp();
+    if (lane == 0) {
+        tma_store_4d(tm, er.stage, col0, er.row0, er.bi, er.bo);
+        bulk_commit_group();
+    }
+}
+
 // scale -> (+bias) -> [store pre-activation] -> (GELU) -> store, for 32 consecutive columns of one row.
-__device__ __forceinline__ void epilogue_store32(float* v, int col0, const EpilogueRow& er, const GemmParams& p) {
+__device__ __forceinline__ void epilogue_store32(float* v, int col0, const EpilogueRow& er, const GemmParams& p, int lane) {
 #pragma unroll
     for (int j = 0; j < 32; ++j) {
         if (p.scale_mode == TE_SCALE_MUL) v[j] *= p.alpha;
@@ -118,6 +151,16 @@ __device__ __forceinline__ void epilogue_store32(float* v, int col0, const Epilo
 #pragma unroll
         for (int j = 0; j < 32; ++j)
             if (col0 + j < p.N) v[j] += __ldg(p.bias + col0 + j);
+    }
+    if (er.tma_ok) {   // warp-uniform
+        if (er.row0 >= p.M) return;   // nothing of this warp's 32 rows exists: issue no store at all
+        if (p.preact) stage_and_store32(v, col0, er, er.tm_pre, lane);
+        if (p.epilogue == TE_EPI_BIAS_GELU) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = gelu_tanh(v[j]);
+        }
+        stage_and_store32(v, col0, er, er.tm_c, lane);
+        return;
     }
     if (!er.row_ok) return;
     const bool full_chunk = col0 + 32 <= p.N;
@@ -151,6 +194,10 @@ __device__ __forceinline__ void epilogue_store32(float* v, int col0, const Epilo
 // number of lines a K-major box carries (an MN-major box is always 32 x 32).
 int make_operand_map(te_b200_ctx* ctx, CUtensorMap* out, const float* ptr, const Operand& op, int64_t K,
                      int box_rows, int64_t batch_inner, int64_t batch_outer);
+// Host: tensor maps {column, row, batch_inner, batch_outer} of the output (and of the optional pre-activation
+// output) for the TMA-store epilogue.  Returns false when the output cannot be described (odd ldc, misaligned base);
+// the kernels then store directly.
+bool make_output_maps(te_b200_ctx* ctx, const GemmProblem& g, CUtensorMap* tm_c, CUtensorMap* tm_pre);
 // Fills the kernel parameters that do not depend on the tile shape.
 void fill_common_params(GemmParams& p, const te_b200_ctx* ctx, const GemmProblem& g);
 

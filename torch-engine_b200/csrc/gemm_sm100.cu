@@ -40,6 +40,7 @@ template <int BN, int NPL, bool A_MN, bool B_MN>
 __global__ void __launch_bounds__(CTA_THREADS, 1)
 gemm_tf32_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_a_lo,
                  const __grid_constant__ CUtensorMap tm_b, const __grid_constant__ CUtensorMap tm_b_lo,
+                 const __grid_constant__ CUtensorMap tm_c, const __grid_constant__ CUtensorMap tm_pre,
                  const GemmParams p) {
     using Cfg = TileCfg<BN, NPL>;
     constexpr int STAGES = Cfg::STAGES;
@@ -62,8 +63,9 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw_addr = smem_u32(smem_raw);
     const uint32_t ring = (raw_addr + 1023u) & ~1023u;           // 128B swizzle wants 1024-byte aligned tiles
-    uint8_t* aux = smem_raw + (ring - raw_addr) + STAGES * STAGE_BYTES;
-    const uint32_t aux_addr = ring + STAGES * STAGE_BYTES;
+    const uint32_t epi_stage = ring + STAGES * STAGE_BYTES;       // EPI_WARPS staging tiles, 1024-byte aligned
+    uint8_t* aux = smem_raw + (ring - raw_addr) + STAGES * STAGE_BYTES + EPI_WARPS * EPI_STAGE_BYTES;
+    const uint32_t aux_addr = epi_stage + EPI_WARPS * EPI_STAGE_BYTES;
     // aux layout (8-byte slots): full[STAGES] | empty[STAGES] | tmem_full[2] | tmem_empty[2] | teardown | slot | abort
     const uint32_t bar_full = aux_addr;
     const uint32_t bar_empty = bar_full + 8 * STAGES;
@@ -248,6 +250,13 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
             // 16-byte stores need every row start aligned: aligned batch base and ldc a multiple of 4.
             er.vec_ok = ((p.ldc & 3) == 0) && ((reinterpret_cast<uintptr_t>(p.c + batch_off) & 15) == 0) &&
                         (!p.preact || (reinterpret_cast<uintptr_t>(p.preact + batch_off) & 15) == 0);
+            er.tma_ok = p.tma_store != 0;
+            er.stage = epi_stage + warp * EPI_STAGE_BYTES;
+            er.tm_c = &tm_c;
+            er.tm_pre = &tm_pre;
+            er.row0 = m_blk * BM + (warp & 3) * 32;
+            er.bi = bi;
+            er.bo = bo;
             if (CHUNKED) {
                 // Two-level accumulation: the tensor core sums CHUNK_KB k-blocks in TMEM (its fp32 adder
                 // truncates, which biases long sums), the partial sums are then added here in registers with
@@ -286,7 +295,7 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
 #pragma unroll
                     for (int cc = 0; cc < NACC / 32; ++cc) {
                         const int col0 = nh + cc * 32;
-                        if (col0 < p.N) epilogue_store32(&acc[cc * 32], col0, er, p);
+                        if (col0 < p.N) epilogue_store32(&acc[cc * 32], col0, er, p, lane);
                     }
                 }
             } else {
@@ -307,7 +316,7 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                     float v[32];
 #pragma unroll
                     for (int j = 0; j < 32; ++j) v[j] = p.K > 0 ? __uint_as_float(r[j]) : 0.0f;
-                    epilogue_store32(v, col0, er, p);
+                    epilogue_store32(v, col0, er, p, lane);
                 }
                 // Hand the accumulator buffer back to the MMA warp.
                 tc_fence_before_sync();
@@ -318,6 +327,7 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
         }
     }
 
+    if (warp < EPI_WARPS && lane == 0) bulk_wait_all();   // this warp's output stores are complete
     __syncwarp();
     tc_fence_before_sync();
     __syncthreads();
@@ -379,7 +389,36 @@ int make_operand_map(te_b200_ctx* ctx, CUtensorMap* out, const float* ptr, const
     return TE_OK;
 }
 
+static bool make_one_output_map(te_b200_ctx* ctx, CUtensorMap* out, float* ptr, const GemmProblem& g) {
+    if (reinterpret_cast<uintptr_t>(ptr) & 15) return false;
+    if (g.N & 3) return false;   // the store unit clips a row at 16-byte granularity: a ragged last quad would spill past N
+    if (g.M > 1 && (g.ldc & 3)) return false;
+    if (g.batch_inner > 1 && ((g.c_stride_inner & 3) || g.c_stride_inner == 0)) return false;
+    if (g.batch_outer > 1 && ((g.c_stride_outer & 3) || g.c_stride_outer == 0)) return false;
+    const int64_t ld = g.M > 1 ? g.ldc : ((g.N + 3) & ~int64_t(3));
+    cuuint64_t dims[4] = {(cuuint64_t)g.N, (cuuint64_t)g.M, (cuuint64_t)g.batch_inner, (cuuint64_t)g.batch_outer};
+    const cuuint64_t row_bytes = (cuuint64_t)ld * 4;
+    cuuint64_t strides[3] = {row_bytes, g.batch_inner > 1 ? (cuuint64_t)g.c_stride_inner * 4 : row_bytes,
+                             g.batch_outer > 1 ? (cuuint64_t)g.c_stride_outer * 4 : row_bytes};
+    cuuint32_t box[4] = {32, 32, 1, 1};
+    cuuint32_t estr[4] = {1, 1, 1, 1};
+    EncodeTiledFn fn = reinterpret_cast<EncodeTiledFn>(ctx->encode_tiled);
+    return fn(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, ptr, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+bool make_output_maps(te_b200_ctx* ctx, const GemmProblem& g, CUtensorMap* tm_c, CUtensorMap* tm_pre) {
+    if (!make_one_output_map(ctx, tm_c, g.c, g)) return false;
+    if (g.preact) {
+        if (!make_one_output_map(ctx, tm_pre, g.preact, g)) return false;
+    } else {
+        *tm_pre = *tm_c;
+    }
+    return true;
+}
+
 void fill_common_params(GemmParams& p, const te_b200_ctx* ctx, const GemmProblem& g) {
+    p.tma_store = 0;
     p.M = (int)g.M; p.N = (int)g.N; p.K = (int)g.K;
     p.tiles_m = p.tiles_n = 0;
     p.batch_inner = (int)g.batch_inner;
@@ -417,11 +456,13 @@ static int launch_variant(te_b200_ctx* ctx, const GemmProblem& g, cudaStream_t s
     }
     GemmParams p;
     fill_common_params(p, ctx, g);
+    CUtensorMap mc, mpre;
+    p.tma_store = make_output_maps(ctx, g, &mc, &mpre) ? 1 : 0;
     p.tiles_m = (int)((g.M + BM - 1) / BM);
     p.tiles_n = (int)((g.N + BN - 1) / BN);
     const long long total = (long long)p.tiles_m * p.tiles_n * p.num_batches;
     const int grid = (int)(total < ctx->sm_count ? total : ctx->sm_count);
-    kernel<<<grid, CTA_THREADS, Cfg::SMEM_BYTES, stream>>>(ma, mal, mb, mbl, p);
+    kernel<<<grid, CTA_THREADS, Cfg::SMEM_BYTES, stream>>>(ma, mal, mb, mbl, mc, mpre, p);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return cuda_fail(e, "gemm_tf32_kernel launch");
     ctx->launches += 1;

@@ -33,9 +33,10 @@ struct PairCfg {
     static constexpr int STAGE_BYTES = A_PLANE_BYTES + B_HALF_BYTES;      // per CTA
     static constexpr int STAGES = SMEM_RING_BUDGET / STAGE_BYTES;
     static constexpr int TMEM_COLS = 2 * BN;
-    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + SMEM_AUX_BYTES + 1024;
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + EPI_WARPS * EPI_STAGE_BYTES + SMEM_AUX_BYTES + 1024;
     static_assert(STAGES >= 2 && STAGES <= 12, "ring depth");
     static_assert(TMEM_COLS <= 512, "TMEM columns");
+    static_assert(SMEM_BYTES <= 232448, "exceeds the 227 KB of shared memory a CTA can have");
 };
 
 __device__ __forceinline__ void pair_tile_coords(int t, const GemmParams& p, int& batch, int& m_blk, int& n_blk) {
@@ -45,6 +46,7 @@ __device__ __forceinline__ void pair_tile_coords(int t, const GemmParams& p, int
 template <int BN, bool A_MN, bool B_MN>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(CTA_THREADS, 1)
 gemm_tf32_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
+                      const __grid_constant__ CUtensorMap tm_c, const __grid_constant__ CUtensorMap tm_pre,
                       const GemmParams p) {
     using Cfg = PairCfg<BN>;
     constexpr int STAGES = Cfg::STAGES;
@@ -60,8 +62,9 @@ gemm_tf32_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw_addr = smem_u32(smem_raw);
     const uint32_t ring = (raw_addr + 1023u) & ~1023u;
-    uint8_t* aux = smem_raw + (ring - raw_addr) + STAGES * STAGE_BYTES;
-    const uint32_t aux_addr = ring + STAGES * STAGE_BYTES;
+    const uint32_t epi_stage = ring + STAGES * STAGE_BYTES;       // EPI_WARPS staging tiles, 1024-byte aligned
+    uint8_t* aux = smem_raw + (ring - raw_addr) + STAGES * STAGE_BYTES + EPI_WARPS * EPI_STAGE_BYTES;
+    const uint32_t aux_addr = epi_stage + EPI_WARPS * EPI_STAGE_BYTES;
     // aux: full[STAGES] | empty[STAGES] | tmem_full[2] | tmem_empty[2] | teardown | slot | abort
     const uint32_t bar_full = aux_addr;
     const uint32_t bar_empty = bar_full + 8 * STAGES;
@@ -219,6 +222,13 @@ gemm_tf32_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
             er.row_ok = row < p.M;
             er.vec_ok = ((p.ldc & 3) == 0) && ((reinterpret_cast<uintptr_t>(p.c + batch_off) & 15) == 0) &&
                         (!p.preact || (reinterpret_cast<uintptr_t>(p.preact + batch_off) & 15) == 0);
+            er.tma_ok = p.tma_store != 0;
+            er.stage = epi_stage + warp * EPI_STAGE_BYTES;
+            er.tm_c = &tm_c;
+            er.tm_pre = &tm_pre;
+            er.row0 = m_blk * PAIR_BM + (int)rank * BM + (warp & 3) * 32;
+            er.bi = bi;
+            er.bo = bo;
             const int buf = acc_idx & 1;
             ok = wait_bounded(bar_tmem_full + 8 * buf, (acc_idx >> 1) & 1, abort_flag, p.status, WAIT_EPI_TMEM_FULL);
             ok = __all_sync(0xffffffffu, ok);
@@ -235,7 +245,7 @@ gemm_tf32_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
                 float v[32];
 #pragma unroll
                 for (int j = 0; j < 32; ++j) v[j] = p.K > 0 ? __uint_as_float(r[j]) : 0.0f;
-                epilogue_store32(v, col0, er, p);
+                epilogue_store32(v, col0, er, p, lane);
             }
             tc_fence_before_sync();
             __syncwarp();
@@ -243,6 +253,7 @@ gemm_tf32_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
         }
     }
 
+    if (warp < EPI_WARPS && lane == 0) bulk_wait_all();   // this warp's output stores are complete
     __syncwarp();
     tc_fence_before_sync();
     __syncthreads();
@@ -269,6 +280,8 @@ static int launch_pair_variant(te_b200_ctx* ctx, const GemmProblem& g, cudaStrea
     if ((rc = make_operand_map(ctx, &mb, g.b.ptr, g.b, g.K, BN / 2, g.batch_inner, g.batch_outer))) return rc;
     GemmParams p;
     fill_common_params(p, ctx, g);
+    CUtensorMap mc, mpre;
+    p.tma_store = make_output_maps(ctx, g, &mc, &mpre) ? 1 : 0;
     p.tiles_m = (int)((g.M + PAIR_BM - 1) / PAIR_BM);
     p.tiles_n = (int)((g.N + BN - 1) / BN);
     const long long total = (long long)p.tiles_m * p.tiles_n * p.num_batches;
@@ -293,7 +306,7 @@ static int launch_pair_variant(te_b200_ctx* ctx, const GemmProblem& g, cudaStrea
         if (getenv("TE_DEBUG_VERBOSE")) fprintf(stderr, "[te_b200] resident CTA pairs: %d\n", n);
     }
     const int pairs = (int)(total < max_pairs ? total : max_pairs);
-    kernel<<<2 * pairs, CTA_THREADS, Cfg::SMEM_BYTES, stream>>>(ma, mb, p);
+    kernel<<<2 * pairs, CTA_THREADS, Cfg::SMEM_BYTES, stream>>>(ma, mb, mc, mpre, p);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return cuda_fail(e, "gemm_tf32_pair_kernel launch");
     ctx->launches += 1;
