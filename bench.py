@@ -154,6 +154,11 @@ def run_reference_arm(args, rank, world):
 
 
 def workload_config(args, world):
+    if getattr(args, "scaling", "weak") == "strong":
+        return {"workload": "gemm_fp32_8192x8192x8192_total", "M": M, "N_total": N_PER_GPU, "K": K,
+                "layout": "row-major A . row-major B", "precision_mode": args.precision,
+                "sharding": "N column blocks of 8192/world, no collective in the timed region", "world": world,
+                "l2": "operands larger than the 126 MB L2"}
     return {"workload": "gemm_fp32_8192x8192x8192_per_gpu", "M": M, "N_per_gpu": N_PER_GPU, "K": K,
             "layout": "row-major A . row-major B", "precision_mode": args.precision,
             "sharding": "N column blocks, one block per GPU, no collective in the timed region", "world": world,
@@ -168,6 +173,9 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--precision", default="tf32", choices=["tf32", "3xtf32"])
     ap.add_argument("--e2e-steps", type=int, default=5)
+    ap.add_argument("--scaling", default="weak", choices=["weak", "strong"],
+                    help="weak (default): every GPU multiplies its own 8192-column block; strong: one 8192^3 product "
+                         "split into N column blocks of 8192/N")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
 
@@ -191,8 +199,11 @@ def main():
     be = ops.Backend(local_rank, workspace_bytes=(3 << 30) if args.precision == "3xtf32" else (64 << 20))
 
     # This rank's column block of the [K, 8192*world] right-hand matrix, already local and contiguous.
-    n0, ncols = sharding.column_shard(N_PER_GPU * world, world, rank, N_PER_GPU)
-    assert ncols == N_PER_GPU
+    if args.scaling == "weak":
+        n0, ncols = sharding.column_shard(N_PER_GPU * world, world, rank, N_PER_GPU)
+        assert ncols == N_PER_GPU
+    else:
+        n0, ncols = sharding.column_shard(N_PER_GPU, world, rank, sharding.COLUMN_ALIGN)
     gen = torch.Generator(device="cuda").manual_seed(42 + rank)
     a = torch.rand(M, K, device="cuda", generator=gen) * 2 - 1
     b = torch.rand(K, ncols, device="cuda", generator=gen) * 2 - 1
@@ -243,7 +254,7 @@ def main():
         dist.all_reduce(ln, op=dist.ReduceOp.SUM)
     ms_total = float(t.item())
     ms_step = ms_total / args.steps
-    flops_step = 2.0 * M * ncols * K * world
+    flops_step = 2.0 * M * K * (N_PER_GPU * world if args.scaling == "weak" else N_PER_GPU)
     value = flops_step / (ms_step * 1e-3) / 1e12
 
     # ---- end to end: host buffers in pinned memory, H2D of A and B and D2H of C inside the timed region ----
@@ -281,7 +292,7 @@ def main():
         clocks["window"] = "timed region plus %.1f s of the same kernel untimed" % (t_wall2 - t_wall1)
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
-            "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
+            "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True, "scaling": args.scaling,
             "vs_baseline": None, "dtype": "tf32" if args.precision == "tf32" else "3xtf32", "data": "synthetic",
             "config": workload_config(args, world),
             "gpu_launches": int(ln.item()),
@@ -291,7 +302,10 @@ def main():
                          "frac": per_gpu_tflops / tf32_peak,
                          "peak_source": "%s bf16 burst %.1f TFLOP/s / 2 (tf32 runs at half the bf16 rate)" % (peaks["source"], peaks["bf16_burst"]),
                          "frac_of_nominal_1125": per_gpu_tflops / 1125.0,
-                         "traffic": None},
+                         # dram__bytes_read.sum + dram__bytes_write.sum of one 8192x8192x8192 launch, single-pass ncu
+                         # capture of this kernel (profiles/gemm_tf32_pair_8192_bench_launch_list.md)
+                         "traffic": 3459198464 if (ncols == N_PER_GPU and args.precision == "tf32") else None,
+                         "algorithmic_bytes": 4 * (M * K + K * ncols + M * ncols)},
             "clocks": clocks,
         }
         if not args.no_cpu_baseline:

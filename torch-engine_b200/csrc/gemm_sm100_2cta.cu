@@ -303,7 +303,6 @@ static int launch_pair_variant(te_b200_ctx* ctx, const GemmProblem& g, cudaStrea
         if (eo != cudaSuccess || n < 1) { cudaGetLastError(); n = ctx->sm_count / 2; }
         max_pairs = n;
         if (ctx->device < 16) max_pairs_cached[ctx->device] = n;
-        if (getenv("TE_DEBUG_VERBOSE")) fprintf(stderr, "[te_b200] resident CTA pairs: %d\n", n);
     }
     const int pairs = (int)(total < max_pairs ? total : max_pairs);
     kernel<<<2 * pairs, CTA_THREADS, Cfg::SMEM_BYTES, stream>>>(ma, mb, mc, mpre, p);
