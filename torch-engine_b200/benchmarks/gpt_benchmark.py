@@ -1,0 +1,72 @@
+"""GPT training-step timing with every matmul on this backend: the counterpart of
+src/benchmarks/gpt_benchmark_gpu.cpp of the reference (same JSON sections: model_config, training_config with
+gemm_backend, metrics with tokens_per_sec / time_per_step_ms / final_loss).  Forward + loss + backward per step on
+synthetic token ids (uniform in [0, vocab)); the optimizer update is not part of the matmul path and is left out,
+which the output states.  Environment variables as in the reference (:110-123): TENSOR_EMBED_DIM, TENSOR_NUM_HEADS,
+TENSOR_NUM_LAYERS, TENSOR_FF_DIM, TENSOR_BATCH_SIZE, TENSOR_SEQ_LEN, TENSOR_MEASURED_STEPS, TENSOR_WARMUP_STEPS,
+plus TENSOR_GEMM_PRECISION (tf32 | 3xtf32).  Defaults are benchmark configuration 4.
+
+    python torch-engine_b200/benchmarks/gpt_benchmark.py [out.json]
+"""
+import json
+import os
+import sys
+
+ROOT = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+sys.path.insert(0, ROOT)
+
+import torch  # noqa: E402
+
+from torch_engine_b200 import gpt, ops  # noqa: E402
+
+
+def env_int(name, default):
+    return int(os.environ.get(name, default))
+
+
+def main():
+    out_path = sys.argv[1] if len(sys.argv) > 1 else os.path.join(ROOT, "gpurun_out", "gpt_benchmark_b200.json")
+    E, H, L = env_int("TENSOR_EMBED_DIM", 384), env_int("TENSOR_NUM_HEADS", 6), env_int("TENSOR_NUM_LAYERS", 6)
+    ff = env_int("TENSOR_FF_DIM", 4 * E)
+    B, T = env_int("TENSOR_BATCH_SIZE", 64), env_int("TENSOR_SEQ_LEN", 256)
+    steps, warm = env_int("TENSOR_MEASURED_STEPS", 10), env_int("TENSOR_WARMUP_STEPS", 3)
+    vocab = 65
+    prec = os.environ.get("TENSOR_GEMM_PRECISION", "tf32")
+    be = ops.Backend(0, workspace_bytes=2 << 30)
+    g = torch.Generator(device="cuda").manual_seed(42)
+    n_params = vocab * E + L * (4 * E + 4 * (E * E + E) + 2 * E * ff + ff + E) + 2 * E + vocab * E + vocab
+    flat = torch.randn(n_params, device="cuda", generator=g) * 0.02
+    tokens = torch.randint(0, vocab, (B, T), device="cuda", generator=g)
+    targets = torch.randint(0, vocab, (B, T), device="cuda", generator=g)
+    loss = None
+    for _ in range(warm):
+        loss, _, _ = gpt.gpt_step(be, flat, tokens, targets, vocab, E, H, L, ff, prec)
+    torch.cuda.synchronize()
+    n0 = be.launches
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        loss, _, _ = gpt.gpt_step(be, flat, tokens, targets, vocab, E, H, L, ff, prec)
+    e1.record()
+    torch.cuda.synchronize()
+    be.check_device_status()
+    ms = e0.elapsed_time(e1) / steps
+    result = {
+        "framework": "TENSOR", "device": "CUDA",
+        "hardware": {"gpu": torch.cuda.get_device_name(0)},
+        "model_config": {"vocab_size": vocab, "max_seq_len": T, "embed_dim": E, "num_heads": H, "num_layers": L, "ff_dim": ff},
+        "training_config": {"batch_size": B, "seq_len": T, "measured_steps": steps, "dropout": 0.0,
+                            "gemm_backend": "b200", "gemm_precision": prec,
+                            "step": "forward + loss + backward (no optimizer update)"},
+        "metrics": {"timing_mode": "throughput", "total_time_s": ms * steps / 1e3, "total_tokens": B * T * steps,
+                    "tokens_per_sec": B * T / (ms / 1e3), "steps_per_sec": 1e3 / ms, "time_per_step_ms": ms,
+                    "final_loss": float(loss), "backend_kernel_launches_per_step": (be.launches - n0) / steps},
+    }
+    os.makedirs(os.path.dirname(out_path), exist_ok=True)
+    with open(out_path, "w") as f:
+        json.dump(result, f, indent=1)
+    print(json.dumps(result["metrics"]))
+
+
+if __name__ == "__main__":
+    main()
