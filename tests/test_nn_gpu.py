@@ -144,3 +144,29 @@ def test_config2_attention_full_size(backend, oracle, prec):
     # batch-sharded evaluation (what each GPU does) equals the unsharded one
     o_hi, _ = backend.scaled_dot(dev(q[8:]), dev(k[8:]), dev(v[8:]), precision=prec)
     assert torch.equal(o_hi, o[8:])
+
+
+@pytest.mark.parametrize("shape", [(2, 3, 100, 32), (1, 2, 200, 64), (2, 2, 256, 32), (1, 2, 64, 64), (1, 1, 4, 32),
+                                   (1, 1, 260, 64), (1, 2, 128, 48)])
+@pytest.mark.parametrize("prec", PRECS)
+def test_scaled_dot_shapes_fused_and_unfused(backend, oracle, shape, prec):
+    """Key counts up to 256 with head size 32 or 64 take the fused kernel in TF32 mode (ragged T included); the last two
+    shapes and the 3xTF32 mode take the two-GEMM path.  Both must agree with the reference composition."""
+    rng = binding.SeededRng(shape[2] * 7 + shape[3])
+    q, k, v = rng.normal(shape), rng.normal(shape), rng.normal(shape)
+    tq, tk, tv = dev(q), dev(k), dev(v)
+    n0 = backend.launches
+    o, p = backend.scaled_dot(tq, tk, tv, precision=prec)
+    launches = backend.launches - n0
+    backend.check_device_status()
+    fused = prec == "tf32" and shape[2] <= 256 and shape[2] % 4 == 0 and shape[3] in (32, 64)
+    assert launches == (1 if fused else (3 if prec == "tf32" else 7)), launches
+    o_ref, p_ref = oracle.scaled_dot(q, k, v)
+    assert rel_err(o.cpu().numpy(), o_ref) <= ATTN_TOL[prec]
+    assert np.abs(p.cpu().numpy() - p_ref).max() <= (3e-2 if prec == "tf32" else 2e-5)
+    assert np.abs(p.sum(dim=-1).cpu().numpy() - 1).max() <= 1e-5
+    # head views of a [B, T, H*d] projection, as MultiHeadAttention builds them
+    B, H, T, d = shape
+    heads = lambda x: torch.from_numpy(np.ascontiguousarray(np.swapaxes(x, 1, 2))).cuda().view(B, T, H * d).view(B, T, H, d).transpose(1, 2)
+    o2, _ = backend.scaled_dot(heads(q), heads(k), heads(v), precision=prec)
+    assert rel_err(o2.cpu().numpy(), o_ref) <= ATTN_TOL[prec]

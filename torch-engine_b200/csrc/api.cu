@@ -550,7 +550,8 @@ int te_b200_attention_forward(te_b200_ctx* ctx, const te_attn_desc* t, te_stream
     if (!t->q || !t->k || !t->v || !t->p_out || !t->o) return fail(TE_ERR_BAD_ARGUMENT, "attention: NULL pointer");
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     te_gemm_desc d;
-    int rc;
+    int rc = launch_attention_fused(ctx, t, st);     // one kernel when the problem fits it
+    if (rc != -1) return rc;
     // S = Q . K^T / sqrt(d)   (scaledot.cpp:13-22), written into p_out
     memset(&d, 0, sizeof d);
     d.M = t->T; d.N = t->T; d.K = t->d;

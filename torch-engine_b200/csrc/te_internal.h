@@ -62,6 +62,9 @@ bool operand_tma_ok(const Operand& op, int64_t K, int64_t batch_inner, int64_t b
 // gemm_sm100.cu
 int launch_gemm(te_b200_ctx* ctx, const GemmProblem& p, cudaStream_t stream);
 
+// attention_sm100.cu: fused QK^T -> softmax -> PV.  Returns -1 when the problem is outside the fused kernel's limits.
+int launch_attention_fused(te_b200_ctx* ctx, const te_attn_desc* t, cudaStream_t stream);
+
 // pack.cu: writes dense K-major planes [batch_outer][batch_inner][rows][kp] (kp = K rounded up to 4).
 // split == false: dst_hi receives a copy.  split == true: dst_hi / dst_lo receive the tf32 hi / lo parts.
 int launch_pack(te_b200_ctx* ctx, const Operand& src, int64_t K, int64_t batch_inner,
