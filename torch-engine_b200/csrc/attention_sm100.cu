@@ -56,8 +56,8 @@ attention_tf32_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
     const uint32_t q_smem = base;                                         // dchunks x [128 rows x 128 B]
     const uint32_t k_smem = q_smem + dchunks * (128 * 128);               // dchunks x [256 rows x 128 B]
     const uint32_t v_smem = k_smem + dchunks * (ATT_MAX_T * 128);         // dchunks x [256 key rows x 128 B], MN-major
-    const uint32_t stage_smem = v_smem + dchunks * (ATT_MAX_T * 128);     // 4 staging tiles
-    const uint32_t aux_addr = stage_smem + ATT_EPI_WARPS * EPI_STAGE_BYTES;
+    const uint32_t stage_smem = v_smem + dchunks * (ATT_MAX_T * 128);     // 2 staging tiles per softmax warp
+    const uint32_t aux_addr = stage_smem + 2 * ATT_EPI_WARPS * EPI_STAGE_BYTES;
     uint8_t* aux = smem_raw + (aux_addr - raw_addr);
     const uint32_t bar_qk = aux_addr, bar_v = aux_addr + 8, bar_s = aux_addr + 16, bar_p = aux_addr + 24,
                    bar_o = aux_addr + 32;
@@ -184,12 +184,13 @@ attention_tf32_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
 
             EpilogueRow er;
             er.c_row = nullptr; er.pre_row = nullptr; er.row_ok = true; er.vec_ok = false; er.tma_ok = true;
-            er.stage = stage_smem + warp * EPI_STAGE_BYTES;
+            er.stage = stage_smem + warp * 2 * EPI_STAGE_BYTES;
             er.tm_c = &tm_p; er.tm_pre = &tm_p;
             er.row0 = q0 + warp * 32;
             er.bi = h; er.bo = b;
             // pass 3: P = e / sum, written out once (runs while the tensor core computes P.V from the same columns)
             const float inv_sum = 1.0f / sum;
+            int stores = 0;   // staging tiles alternate over ALL stores of this warp, P and O alike
             if (er.row0 < p.T) {
                 for (int cc = 0; cc * 32 < p.T; ++cc) {
                     uint32_t r[32];
@@ -198,7 +199,7 @@ attention_tf32_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
                     float v[32];
 #pragma unroll
                     for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * inv_sum;
-                    stage_and_store32(v, cc * 32, er, &tm_p, lane);
+                    stage_and_store32(v, cc * 32, er, &tm_p, lane, true, (stores++) & 1);
                 }
             }
             ok = wait_bounded(bar_o, 0, abort_flag, p.status, WAIT_EPI_TMEM_FULL);
@@ -212,7 +213,7 @@ attention_tf32_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
                     float v[32];
 #pragma unroll
                     for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * inv_sum;
-                    stage_and_store32(v, cc * 32, er, &tm_o, lane);
+                    stage_and_store32(v, cc * 32, er, &tm_o, lane, true, (stores++) & 1);
                 }
             }
         }
@@ -279,7 +280,7 @@ int launch_attention_fused(te_b200_ctx* ctx, const te_attn_desc* t, cudaStream_t
     p.scale = sqrtf((float)t->d);
     p.status = ctx->d_status;
     const int dchunks = p.d / 32;
-    const int smem = 1024 + dchunks * (128 * 128 + 2 * ATT_MAX_T * 128) + ATT_EPI_WARPS * EPI_STAGE_BYTES + 128;
+    const int smem = 1024 + dchunks * (128 * 128 + 2 * ATT_MAX_T * 128) + 2 * ATT_EPI_WARPS * EPI_STAGE_BYTES + 128;
     static int attr_smem[16] = {};
     if (ctx->device < 16 && attr_smem[ctx->device] < smem) {
         cudaError_t e = cudaFuncSetAttribute(attention_tf32_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);

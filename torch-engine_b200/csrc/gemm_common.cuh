@@ -120,11 +120,17 @@ struct EpilogueRow {
 
 // The warp's 32 x 32 block goes through shared memory so that global memory is written in whole 128-byte lines by
 // the TMA unit instead of 32 scattered 16-byte pieces per store instruction.  Lane 0 owns the bulk group.
+// With `alternate` the caller switches between two staging tiles (er.stage and er.stage + EPI_STAGE_BYTES, chosen by
+// `which`), so only the store before the previous one has to have drained.
 __device__ __forceinline__ void stage_and_store32(const float* v, int col0, const EpilogueRow& er, const CUtensorMap* tm,
-                                                  int lane) {
-    if (lane == 0) bulk_wait_read_all();     // the previous store has finished reading the staging tile
+                                                  int lane, bool alternate = false, int which = 0) {
+    if (lane == 0) {
+        if (alternate) bulk_wait_read_all_but_one();
+        else bulk_wait_read_all();           // the previous store has finished reading the staging tile
+    }
     __syncwarp();
-    const uint32_t row_addr = er.stage + lane * 128;
+    const uint32_t stage = er.stage + (alternate ? which * EPI_STAGE_BYTES : 0);
+    const uint32_t row_addr = stage + lane * 128;
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
         const uint32_t unit = uint32_t(j) ^ (uint32_t(lane) & 7u);
@@ -135,7 +141,7 @@ __device__ __forceinline__ void stage_and_store32(const float* v, int col0, cons
     fence_proxy_async_smem();
     __syncwarp();
     if (lane == 0) {
-        tma_store_4d(tm, er.stage, col0, er.row0, er.bi, er.bo);
+        tma_store_4d(tm, stage, col0, er.row0, er.bi, er.bo);
         bulk_commit_group();
     }
 }

@@ -72,6 +72,8 @@ __device__ __forceinline__ void tma_store_4d(const void* tmap, uint32_t src_smem
 __device__ __forceinline__ void bulk_commit_group() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 // All earlier bulk groups of this thread have finished READING shared memory (the source may be reused).
 __device__ __forceinline__ void bulk_wait_read_all() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+// All but the most recent bulk group of this thread have finished reading shared memory.
+__device__ __forceinline__ void bulk_wait_read_all_but_one() { asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory"); }
 // All earlier bulk groups of this thread are complete.
 __device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 
