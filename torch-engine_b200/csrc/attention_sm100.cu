@@ -9,12 +9,14 @@
 // Why fused: unfused, the [B,H,T,T] score tensor crosses HBM four times (S written, softmax read + write, P read):
 // 200 of the 252 MB the attention configuration moves.  Here S never leaves the SM; only P is written, once.
 //
-// Per CTA (192 threads):
-//   warp 4      TMA loads of the Q block (128 x d), all keys K (T x d) and all values V (T x d) into shared memory;
-//   warp 5      S = Q.K^T with tcgen05.mma (both operands K-major) into TMEM columns [0, Tp); later O = P.V with
+// Per CTA (320 threads):
+//   warp 8      TMA loads of the Q block (128 x d), all keys K (T x d) and all values V (T x d) into shared memory;
+//   warp 9      S = Q.K^T with tcgen05.mma (both operands K-major) into TMEM columns [0, Tp); later O = P.V with
 //               the A operand read from TMEM (P, written back by the softmax warps) and V as an MN-major operand;
-//   warps 0-3   thread = one query row: row maximum, exp and row sum straight from TMEM, exp written back to TMEM
-//               as the PV operand, P = exp / sum and finally O / sum staged through shared memory and TMA-stored.
+//   warps 0-7   two warps per 32 query rows, each owning half of the key columns: row maximum, exp and row sum
+//               straight from TMEM (the halves exchange maxima and sums through shared memory), exp written back
+//               to TMEM as the PV operand, P = exp / sum and finally O / sum staged through shared memory and
+//               TMA-stored.
 // Limits of this form: TF32 mode, T <= 256 keys (one TMEM pass, no running rescale), d in {32, 64}; other problems
 // take the unfused path (two batched GEMMs + softmax kernel).  All waits are bounded as in the GEMM kernels.
 #include <cuda.h>
@@ -29,7 +31,7 @@ namespace te {
 
 constexpr int ATT_MAX_T = 256;
 constexpr int ATT_O_COL = 256;     // TMEM column where the output accumulator starts
-constexpr int ATT_EPI_WARPS = 4;
+constexpr int ATT_EPI_WARPS = 8;    // two warps per TMEM lane quadrant, each owning half of the columns
 
 __device__ __forceinline__ float ex2_approx(float x) {
     float y;
@@ -45,7 +47,7 @@ struct AttnParams {
     int* status;
 };
 
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(CTA_THREADS, 1)
 attention_tf32_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                       const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_p,
                       const __grid_constant__ CUtensorMap tm_o, const AttnParams p) {
@@ -61,6 +63,11 @@ attention_tf32_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
     uint8_t* aux = smem_raw + (aux_addr - raw_addr);
     const uint32_t bar_qk = aux_addr, bar_v = aux_addr + 8, bar_s = aux_addr + 16, bar_p = aux_addr + 24,
                    bar_o = aux_addr + 32;
+    const uint32_t bar_x1 = aux_addr + 56, bar_x2 = aux_addr + 64;
+    // The exchange arrays reuse the Q block's shared memory: Q is dead once the score MMAs have completed, and the
+    // softmax warps touch these arrays only after waiting for exactly that.
+    float* red_max = reinterpret_cast<float*>(smem_raw + (q_smem - raw_addr));          // [2 halves][128 rows]
+    float* red_sum = red_max + 256;                                                    // [2 halves][128 rows]
     const uint32_t tmem_slot_addr = aux_addr + 40;
     volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(aux + 40);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(aux + 44);
@@ -78,11 +85,13 @@ attention_tf32_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
         mbar_init(bar_p, ATT_EPI_WARPS);
         mbar_init(bar_o, 1);
         mbar_init(aux_addr + 48, 1);   // teardown: all MMAs of this CTA done
+        mbar_init(bar_x1, ATT_EPI_WARPS);   // row maxima of both column halves exchanged
+        mbar_init(bar_x2, ATT_EPI_WARPS);   // row sums exchanged
         *abort_flag = 0;
         fence_barrier_init();
         fence_proxy_async_smem();
     }
-    if (warp == 5) {
+    if (warp == MMA_WARP) {
         tmem_alloc(tmem_slot_addr, 512);
         tmem_relinquish();
     }
@@ -91,7 +100,7 @@ attention_tf32_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
     tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
 
-    if (warp == 4) {
+    if (warp == PRODUCER_WARP) {
         if (lane == 0) {
             tma_prefetch_desc(&tm_q);
             tma_prefetch_desc(&tm_k);
@@ -106,7 +115,7 @@ attention_tf32_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
                 for (int kb = 0; kb < ATT_MAX_T / 32; ++kb)
                     tma_load_4d(v_smem + c * (ATT_MAX_T * 128) + kb * (32 * 128), &tm_v, bar_v, 32 * c, 32 * kb, h, b);
         }
-    } else if (warp == 5) {
+    } else if (warp == MMA_WARP) {
         if (lane == 0) {
             bool ok = wait_bounded(bar_qk, 0, abort_flag, p.status, WAIT_MMA_FULL);
             if (ok) {
@@ -137,93 +146,130 @@ attention_tf32_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
             umma_commit(aux_addr + 48);
         }
     } else {
-        // ---------------------------------------------------------------- softmax + output (warps 0-3)
-        const uint32_t t_row = tmem_base + (uint32_t(warp * 32) << 16);
+        // ---------------------------------------------------------------- softmax + output (warps 0-7)
+        const int quad = warp & 3, half = warp >> 2;
+        const int rloc = quad * 32 + lane;                         // row inside the 128-row block = TMEM lane
+        const uint32_t t_row = tmem_base + (uint32_t(quad * 32) << 16);
         bool ok = wait_bounded(bar_s, 0, abort_flag, p.status, WAIT_EPI_TMEM_FULL);
         ok = __all_sync(0xffffffffu, ok);
         if (ok) {
             tc_fence_after_sync();
             const int nchunks = (p.t_pad + 31) / 32;
+            const int c_begin = half ? (nchunks + 1) / 2 : 0;      // this warp's share of the 32-column chunks
+            const int c_end = half ? nchunks : (nchunks + 1) / 2;
             // Scores are scaled by multiplying with 1/sqrt(d) and exponentiated with the ex2 unit: this kernel runs in
-            // TF32 mode only, where the scores carry ~1e-3 relative error already, and thread = row makes the
-            // per-element cost of the softmax the critical path of the CTA.
-            const float inv_scale = 1.0f / p.scale;
-            const float k2 = inv_scale * 1.4426950408889634f;     // log2(e) / sqrt(d)
+            // TF32 mode only, where the scores carry ~1e-3 relative error already, and the per-element cost of the
+            // softmax is the critical path of the CTA.
+            const float k2 = (1.0f / p.scale) * 1.4426950408889634f;     // log2(e) / sqrt(d)
             // pass 1: row maximum of the raw scores (the scale is positive, so the maximum commutes with it)
             float m = -INFINITY;
-            for (int cc = 0; cc < nchunks; ++cc) {
+            for (int cc = c_begin; cc < c_end; ++cc) {
                 uint32_t r[32];
                 tmem_ld_32x32b_x32(t_row + cc * 32, r);
                 tmem_ld_wait();
+                if ((cc + 1) * 32 <= p.T) {
 #pragma unroll
-                for (int j = 0; j < 32; ++j)
-                    if (cc * 32 + j < p.T) m = fmaxf(m, __uint_as_float(r[j]));
+                    for (int j = 0; j < 32; ++j) m = fmaxf(m, __uint_as_float(r[j]));
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j)
+                        if (cc * 32 + j < p.T) m = fmaxf(m, __uint_as_float(r[j]));
+                }
             }
+            red_max[half * 128 + rloc] = m;
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_x1);
+            ok = wait_bounded(bar_x1, 0, abort_flag, p.status, WAIT_EPI_TMEM_FULL);
+            ok = __all_sync(0xffffffffu, ok);
+        }
+        if (ok) {
+            const int nchunks = (p.t_pad + 31) / 32;
+            const int c_begin = half ? (nchunks + 1) / 2 : 0;
+            const int c_end = half ? nchunks : (nchunks + 1) / 2;
+            const float k2 = (1.0f / p.scale) * 1.4426950408889634f;
+            const float m = fmaxf(red_max[rloc], red_max[128 + rloc]);
             const float mk = m * k2;
             // pass 2: e = exp(s - m), row sum; e goes back to TMEM as the A operand of P.V
             float sum = 0.0f;
-            for (int cc = 0; cc < nchunks; ++cc) {
+            for (int cc = c_begin; cc < c_end; ++cc) {
                 uint32_t r[32];
                 tmem_ld_32x32b_x32(t_row + cc * 32, r);
                 tmem_ld_wait();
+                if ((cc + 1) * 32 <= p.T) {
 #pragma unroll
-                for (int j = 0; j < 32; ++j) {
-                    float e = 0.0f;
-                    if (cc * 32 + j < p.T) {
-                        e = ex2_approx(fmaf(__uint_as_float(r[j]), k2, -mk));
+                    for (int j = 0; j < 32; ++j) {
+                        const float e = ex2_approx(fmaf(__uint_as_float(r[j]), k2, -mk));
                         sum += e;
+                        r[j] = __float_as_uint(e);
                     }
-                    r[j] = __float_as_uint(e);
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        float e = 0.0f;
+                        if (cc * 32 + j < p.T) {
+                            e = ex2_approx(fmaf(__uint_as_float(r[j]), k2, -mk));
+                            sum += e;
+                        }
+                        r[j] = __float_as_uint(e);
+                    }
                 }
                 tmem_st_32x32b_x32(t_row + cc * 32, r);
             }
             tmem_st_wait();
             tc_fence_before_sync();
+            red_sum[half * 128 + rloc] = sum;
             __syncwarp();
-            if (lane == 0) mbar_arrive(bar_p);
-
-            EpilogueRow er;
-            er.c_row = nullptr; er.pre_row = nullptr; er.row_ok = true; er.vec_ok = false; er.tma_ok = true;
-            er.stage = stage_smem + warp * 2 * EPI_STAGE_BYTES;
-            er.tm_c = &tm_p; er.tm_pre = &tm_p;
-            er.row0 = q0 + warp * 32;
-            er.bi = h; er.bo = b;
-            // pass 3: P = e / sum, written out once (runs while the tensor core computes P.V from the same columns)
-            const float inv_sum = 1.0f / sum;
-            int stores = 0;   // staging tiles alternate over ALL stores of this warp, P and O alike
-            if (er.row0 < p.T) {
-                for (int cc = 0; cc * 32 < p.T; ++cc) {
-                    uint32_t r[32];
-                    tmem_ld_32x32b_x32(t_row + cc * 32, r);
-                    tmem_ld_wait();
-                    float v[32];
-#pragma unroll
-                    for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * inv_sum;
-                    stage_and_store32(v, cc * 32, er, &tm_p, lane, true, (stores++) & 1);
-                }
+            if (lane == 0) {
+                mbar_arrive(bar_p);      // this warp's part of the PV operand is in place
+                mbar_arrive(bar_x2);
             }
-            ok = wait_bounded(bar_o, 0, abort_flag, p.status, WAIT_EPI_TMEM_FULL);
+            ok = wait_bounded(bar_x2, 0, abort_flag, p.status, WAIT_EPI_TMEM_FULL);
             ok = __all_sync(0xffffffffu, ok);
-            if (ok && er.row0 < p.T) {
-                tc_fence_after_sync();
-                for (int cc = 0; cc < dchunks; ++cc) {
-                    uint32_t r[32];
-                    tmem_ld_32x32b_x32(t_row + ATT_O_COL + cc * 32, r);
-                    tmem_ld_wait();
-                    float v[32];
+            if (ok) {
+                const float inv_sum = 1.0f / (red_sum[rloc] + red_sum[128 + rloc]);
+                EpilogueRow er;
+                er.c_row = nullptr; er.pre_row = nullptr; er.row_ok = true; er.vec_ok = false; er.tma_ok = true;
+                er.stage = stage_smem + warp * 2 * EPI_STAGE_BYTES;
+                er.tm_c = &tm_p; er.tm_pre = &tm_p;
+                er.row0 = q0 + quad * 32;
+                er.bi = h; er.bo = b;
+                int stores = 0;   // staging tiles alternate over ALL stores of this warp, P and O alike
+                // pass 3: P = e / sum, written out once (while the tensor core computes P.V from the same columns)
+                if (er.row0 < p.T) {
+                    for (int cc = c_begin; cc < c_end && cc * 32 < p.T; ++cc) {
+                        uint32_t r[32];
+                        tmem_ld_32x32b_x32(t_row + cc * 32, r);
+                        tmem_ld_wait();
+                        float v[32];
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * inv_sum;
-                    stage_and_store32(v, cc * 32, er, &tm_o, lane, true, (stores++) & 1);
+                        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * inv_sum;
+                        stage_and_store32(v, cc * 32, er, &tm_p, lane, true, (stores++) & 1);
+                    }
+                }
+                ok = wait_bounded(bar_o, 0, abort_flag, p.status, WAIT_EPI_TMEM_FULL);
+                ok = __all_sync(0xffffffffu, ok);
+                if (ok && er.row0 < p.T) {
+                    tc_fence_after_sync();
+                    const int o_begin = half ? (dchunks + 1) / 2 : 0, o_end = half ? dchunks : (dchunks + 1) / 2;
+                    for (int cc = o_begin; cc < o_end; ++cc) {
+                        uint32_t r[32];
+                        tmem_ld_32x32b_x32(t_row + ATT_O_COL + cc * 32, r);
+                        tmem_ld_wait();
+                        float v[32];
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * inv_sum;
+                        stage_and_store32(v, cc * 32, er, &tm_o, lane, true, (stores++) & 1);
+                    }
                 }
             }
         }
-        if (lane == 0) bulk_wait_all();
+        if (lane == 0) bulk_wait_read_all();   // shared memory may go away once the stores have read it
     }
 
     __syncwarp();
     tc_fence_before_sync();
     __syncthreads();
-    if (warp == 5) {
+    if (warp == MMA_WARP) {
         if (lane == 0) {   // teardown barrier: every MMA of this CTA has completed
             const uint64_t t0 = global_timer_ns();
             while (!mbar_try_wait(aux_addr + 48, 0)) {
@@ -281,6 +327,7 @@ int launch_attention_fused(te_b200_ctx* ctx, const te_attn_desc* t, cudaStream_t
     p.status = ctx->d_status;
     const int dchunks = p.d / 32;
     const int smem = 1024 + dchunks * (128 * 128 + 2 * ATT_MAX_T * 128) + 2 * ATT_EPI_WARPS * EPI_STAGE_BYTES + 128;
+    if (smem > 232448) return -1;
     static int attr_smem[16] = {};
     if (ctx->device < 16 && attr_smem[ctx->device] < smem) {
         cudaError_t e = cudaFuncSetAttribute(attention_tf32_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
@@ -288,7 +335,7 @@ int launch_attention_fused(te_b200_ctx* ctx, const te_attn_desc* t, cudaStream_t
         attr_smem[ctx->device] = smem;
     }
     const int grid = (int)(t->B * t->H * p.tiles_q);
-    attention_tf32_kernel<<<grid, 192, smem, stream>>>(mq, mk, mv, mp, mo, p);
+    attention_tf32_kernel<<<grid, CTA_THREADS, smem, stream>>>(mq, mk, mv, mp, mo, p);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return cuda_fail(e, "attention_tf32_kernel launch");
     ctx->launches += 1;
