@@ -252,6 +252,31 @@ def test_skinny_sweep_shapes(backend, oracle, shape):
     backend.check_device_status()
 
 
+@pytest.mark.parametrize("prec", PRECS)
+def test_split_k_paths(backend, oracle, prec):
+    """Few output tiles and a long K: the launcher splits K over several work units per tile, the partial tiles go
+    to scratch and a reduction kernel adds them and applies the epilogue.  Covers the TMA-stored and the directly
+    stored partials (N not a multiple of 4), batches, the pair kernel (M, N > 128) and the fused epilogue."""
+    rng = binding.SeededRng(17)
+    for (B, M, K, N) in [(1, 96, 4096, 200), (1, 40, 3000, 198), (3, 64, 2048, 72), (1, 384, 8192, 320), (1, 16, 8192, 1024)]:
+        a = rng.normal((B, M, K)) if B > 1 else rng.normal((M, K))
+        b = rng.normal((K, N), 0.0, 0.1)
+        bias = rng.normal((N,), 0.0, 0.5)
+        ref = oracle.matmul(a, b) if B > 1 else oracle.matmul_2d_threads(a, b)
+        n0 = backend.launches
+        c = backend.matmul(dev(a), dev(b), precision=prec)
+        used = backend.launches - n0
+        assert used >= (2 if prec == "tf32" else 4), "expected the split-K path (GEMM + reduction)"
+        assert_close(c.cpu().numpy(), ref, prec, f"split-K {B}x{M}x{K}x{N}")
+        if B == 1:   # epilogue applied by the reduction kernel
+            y, pre = backend.linear_forward(dev(a), dev(np.ascontiguousarray(b.T)), dev(bias), gelu=True, want_preact=True,
+                                            precision=prec)
+            pre_ref = oracle.add_bias(ref, bias)
+            assert_close(pre.cpu().numpy(), pre_ref, prec, "split-K pre-activation")
+            assert np.abs(y.cpu().numpy() - oracle.gelu(pre.cpu().numpy())).max() <= 1e-5
+    backend.check_device_status()
+
+
 def test_host_buffer_entry_point(backend, oracle):
     rng = binding.SeededRng(42)
     M, K, N = 300, 128, 260

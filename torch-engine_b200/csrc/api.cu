@@ -168,6 +168,9 @@ static int gemm_device(te_b200_ctx* ctx, const te_gemm_desc* d, cudaStream_t st)
         g.a.ld = g.b.ld = 4;
         g.a.stride_inner = g.a.stride_outer = g.b.stride_inner = g.b.stride_outer = 0;
     }
+    // whatever the packing left of the workspace may hold split-K partial tiles
+    g.split_ws = reinterpret_cast<float*>(ws.base + ws.used);
+    g.split_ws_bytes = ws.cap - ws.used;
     return launch_gemm(ctx, g, st);
 }
 

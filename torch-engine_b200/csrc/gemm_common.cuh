@@ -47,7 +47,18 @@ struct GemmParams {
     int epilogue;
     int* status;
     int tma_store;   // 1: outputs go through shared memory and TMA stores
+    // Split K: every output tile is computed by k_splits work units, each over kb_per_split k-blocks, each writing
+    // its partial tile to slice `split` of a scratch buffer (split_stride elements apart); a reduction kernel adds
+    // the slices in order and applies the epilogue.  k_splits == 1: no scratch, kb_per_split = all k-blocks.
+    int k_splits, kb_per_split;
+    int batch_outer_n;          // number of outer batches (coordinate base of the split in the output tensor map)
+    long long split_stride;
 };
+
+struct WorkUnit {
+    int batch, m_blk, n_blk, split, kb0, kb1;
+};
+
 
 template <int BN, int NPL>
 struct TileCfg {
@@ -90,6 +101,14 @@ __device__ __forceinline__ void tile_coords(int t, const GemmParams& p, int& bat
     const int in_group = r - g * group_span;
     m_blk = first_m + in_group % gm;
     n_blk = in_group / gm;
+}
+
+__device__ __forceinline__ void decode_unit(int u, const GemmParams& p, int kblocks, WorkUnit& w) {
+    const int t = u / p.k_splits;
+    w.split = u - t * p.k_splits;
+    tile_coords(t, p, w.batch, w.m_blk, w.n_blk);
+    w.kb0 = w.split * p.kb_per_split;
+    w.kb1 = min(w.kb0 + p.kb_per_split, kblocks);
 }
 
 __device__ __forceinline__ float gelu_tanh(float x) {
@@ -203,11 +222,17 @@ int make_operand_map(te_b200_ctx* ctx, CUtensorMap* out, const float* ptr, const
 // Host: tensor maps {column, row, batch_inner, batch_outer} of the output (and of the optional pre-activation
 // output) for the TMA-store epilogue.  Returns false when the output cannot be described (odd ldc, misaligned base);
 // the kernels then store directly.
-bool make_output_maps(te_b200_ctx* ctx, const GemmProblem& g, CUtensorMap* tm_c, CUtensorMap* tm_pre);
+bool make_output_maps(te_b200_ctx* ctx, const GemmProblem& g, int k_splits, CUtensorMap* tm_c, CUtensorMap* tm_pre);
 // Fills the kernel parameters that do not depend on the tile shape.
 void fill_common_params(GemmParams& p, const te_b200_ctx* ctx, const GemmProblem& g);
 
 // gemm_sm100_2cta.cu: the CTA-pair (cta_group::2) TF32 kernel, 256 x 256 tiles.
-int launch_gemm_2cta(te_b200_ctx* ctx, const GemmProblem& g, cudaStream_t stream);
+int launch_gemm_2cta(te_b200_ctx* ctx, const GemmProblem& g, int k_splits, cudaStream_t stream);
+
+// Split-K plumbing shared by both kernels (gemm_sm100.cu).  prepare_split rewrites `kernel_problem` so that the GEMM
+// kernel writes raw partial tiles into the scratch of `g`, and fills the split fields of `p`; finish_split launches the
+// reduction that adds the slices and applies the epilogue of `g`.
+void prepare_split(const GemmProblem& g, int k_splits, GemmProblem& kernel_problem, GemmParams& p);
+int finish_split(te_b200_ctx* ctx, const GemmProblem& g, int k_splits, cudaStream_t stream);
 
 }  // namespace te

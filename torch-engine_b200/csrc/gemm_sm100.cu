@@ -110,7 +110,7 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
     tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
 
-    const int total_tiles = p.tiles_m * p.tiles_n * p.num_batches;
+    const int total_units = p.tiles_m * p.tiles_n * p.num_batches * p.k_splits;
     const int kblocks = (p.K + BK - 1) / BK;
 
     if (warp == PRODUCER_WARP) {
@@ -118,14 +118,15 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
         if (lane == 0) {
             int issued = 0;
             bool ok = true;
-            for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
-                int batch, m_blk, n_blk;
-                tile_coords(t, p, batch, m_blk, n_blk);
+            for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x) {
+                WorkUnit w;
+                decode_unit(u, p, kblocks, w);
+                const int batch = w.batch, m_blk = w.m_blk, n_blk = w.n_blk;
                 const int bo = batch / p.batch_inner, bi = batch - bo * p.batch_inner;
                 const int a_ci = bi * p.a_mul_inner, a_co = bo * p.a_mul_outer;
                 const int b_ci = bi * p.b_mul_inner, b_co = bo * p.b_mul_outer;
                 const int m0 = m_blk * BM, n0 = n_blk * BN;
-                for (int kb = 0; kb < kblocks; ++kb, ++issued) {
+                for (int kb = w.kb0; kb < w.kb1; ++kb, ++issued) {
                     const int s = issued % STAGES;
                     const uint32_t phase = (issued / STAGES) & 1;
                     if (!wait_bounded(bar_empty + 8 * s, phase ^ 1, abort_flag, p.status, WAIT_PRODUCER_EMPTY)) {
@@ -177,10 +178,12 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
             int consumed = 0;
             int acc_idx = 0;   // accumulator hand-offs so far (one per tile, or one per K chunk when CHUNKED)
             bool ok = true;
-            for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
-                int kb = 0;
-                do {   // one pass per accumulator buffer: the whole K range, or one chunk of it
-                    const int kb_end = CHUNKED ? min(kb + CHUNK_KB, kblocks) : kblocks;
+            for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x) {
+                WorkUnit w;
+                decode_unit(u, p, kblocks, w);
+                int kb = w.kb0;
+                do {   // one pass per accumulator buffer: this unit's whole K range, or one chunk of it
+                    const int kb_end = CHUNKED ? min(kb + CHUNK_KB, w.kb1) : w.kb1;
                     const int buf = acc_idx & 1;
                     if (!wait_bounded(bar_tmem_empty + 8 * buf, ((acc_idx >> 1) & 1) ^ 1, abort_flag, p.status,
                                       WAIT_MMA_TMEM_EMPTY)) {
@@ -220,7 +223,7 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                     if (!ok) break;
                     umma_commit(bar_tmem_full + 8 * buf);
                     ++acc_idx;
-                } while (kb < kblocks);
+                } while (kb < w.kb1);
             }
             // All MMAs issued by this thread must be finished before TMEM is freed.
             umma_commit(bar_teardown);
@@ -236,13 +239,15 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
         // ------------------------------------------------------------ epilogue (warps 0-7)
         int acc_idx = 0;
         bool ok = true;
-        for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
-            int batch, m_blk, n_blk;
-            tile_coords(t, p, batch, m_blk, n_blk);
+        for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x) {
+            WorkUnit w;
+            decode_unit(u, p, kblocks, w);
+            const int batch = w.batch, m_blk = w.m_blk, n_blk = w.n_blk;
             const int bo = batch / p.batch_inner, bi = batch - bo * p.batch_inner;
             const int row = m_blk * BM + (warp & 3) * 32 + lane;
             const int n0 = n_blk * BN;
-            const long long batch_off = (long long)bo * p.c_stride_outer + (long long)bi * p.c_stride_inner;
+            const long long batch_off = (long long)bo * p.c_stride_outer + (long long)bi * p.c_stride_inner +
+                                        (long long)w.split * p.split_stride;
             EpilogueRow er;
             er.c_row = p.c + batch_off + (long long)row * p.ldc;
             er.pre_row = p.preact ? p.preact + batch_off + (long long)row * p.ldc : nullptr;
@@ -256,7 +261,7 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
             er.tm_pre = &tm_pre;
             er.row0 = m_blk * BM + (warp & 3) * 32;
             er.bi = bi;
-            er.bo = bo;
+            er.bo = w.split * p.batch_outer_n + bo;
             if (CHUNKED) {
                 // Two-level accumulation: the tensor core sums CHUNK_KB k-blocks in TMEM (its fp32 adder
                 // truncates, which biases long sums), the partial sums are then added here in registers with
@@ -266,7 +271,7 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                 float acc[NACC];
 #pragma unroll
                 for (int j = 0; j < NACC; ++j) acc[j] = 0.0f;
-                const int chunks = kblocks > 0 ? (kblocks + CHUNK_KB - 1) / CHUNK_KB : 1;
+                const int chunks = w.kb1 > w.kb0 ? (w.kb1 - w.kb0 + CHUNK_KB - 1) / CHUNK_KB : 1;
                 for (int ch = 0; ch < chunks && ok; ++ch, ++acc_idx) {
                     const int buf = acc_idx & 1;
                     ok = wait_bounded(bar_tmem_full + 8 * buf, (acc_idx >> 1) & 1, abort_flag, p.status,
@@ -389,17 +394,19 @@ int make_operand_map(te_b200_ctx* ctx, CUtensorMap* out, const float* ptr, const
     return TE_OK;
 }
 
-static bool make_one_output_map(te_b200_ctx* ctx, CUtensorMap* out, float* ptr, const GemmProblem& g) {
+static bool make_one_output_map(te_b200_ctx* ctx, CUtensorMap* out, float* ptr, const GemmProblem& g, int k_splits) {
     if (reinterpret_cast<uintptr_t>(ptr) & 15) return false;
     if (g.N & 3) return false;   // the store unit clips a row at 16-byte granularity: a ragged last quad would spill past N
     if (g.M > 1 && (g.ldc & 3)) return false;
     if (g.batch_inner > 1 && ((g.c_stride_inner & 3) || g.c_stride_inner == 0)) return false;
-    if (g.batch_outer > 1 && ((g.c_stride_outer & 3) || g.c_stride_outer == 0)) return false;
+    if (g.batch_outer * k_splits > 1 && ((g.c_stride_outer & 3) || g.c_stride_outer == 0)) return false;
     const int64_t ld = g.M > 1 ? g.ldc : ((g.N + 3) & ~int64_t(3));
-    cuuint64_t dims[4] = {(cuuint64_t)g.N, (cuuint64_t)g.M, (cuuint64_t)g.batch_inner, (cuuint64_t)g.batch_outer};
+    // split-K scratch is laid out [split][outer][inner][M][N] dense, so splits extend the outer batch dimension
+    const int64_t outer_n = g.batch_outer * k_splits;
+    cuuint64_t dims[4] = {(cuuint64_t)g.N, (cuuint64_t)g.M, (cuuint64_t)g.batch_inner, (cuuint64_t)outer_n};
     const cuuint64_t row_bytes = (cuuint64_t)ld * 4;
     cuuint64_t strides[3] = {row_bytes, g.batch_inner > 1 ? (cuuint64_t)g.c_stride_inner * 4 : row_bytes,
-                             g.batch_outer > 1 ? (cuuint64_t)g.c_stride_outer * 4 : row_bytes};
+                             outer_n > 1 ? (cuuint64_t)g.c_stride_outer * 4 : row_bytes};
     cuuint32_t box[4] = {32, 32, 1, 1};
     cuuint32_t estr[4] = {1, 1, 1, 1};
     EncodeTiledFn fn = reinterpret_cast<EncodeTiledFn>(ctx->encode_tiled);
@@ -407,10 +414,10 @@ static bool make_one_output_map(te_b200_ctx* ctx, CUtensorMap* out, float* ptr, 
               CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-bool make_output_maps(te_b200_ctx* ctx, const GemmProblem& g, CUtensorMap* tm_c, CUtensorMap* tm_pre) {
-    if (!make_one_output_map(ctx, tm_c, g.c, g)) return false;
+bool make_output_maps(te_b200_ctx* ctx, const GemmProblem& g, int k_splits, CUtensorMap* tm_c, CUtensorMap* tm_pre) {
+    if (!make_one_output_map(ctx, tm_c, g.c, g, k_splits)) return false;
     if (g.preact) {
-        if (!make_one_output_map(ctx, tm_pre, g.preact, g)) return false;
+        if (!make_one_output_map(ctx, tm_pre, g.preact, g, k_splits)) return false;
     } else {
         *tm_pre = *tm_c;
     }
@@ -431,10 +438,79 @@ void fill_common_params(GemmParams& p, const te_b200_ctx* ctx, const GemmProblem
     p.c = g.c; p.preact = g.preact; p.bias = g.bias;
     p.alpha = g.alpha; p.scale_mode = g.scale_mode; p.epilogue = g.epilogue;
     p.status = ctx->d_status;
+    p.k_splits = 1;
+    p.kb_per_split = (int)((g.K + BK - 1) / BK);
+    p.batch_outer_n = (int)g.batch_outer;
+    p.split_stride = 0;
+}
+
+void prepare_split(const GemmProblem& g, int k_splits, GemmProblem& kp, GemmParams& p) {
+    if (k_splits <= 1) return;
+    const int kblocks = (int)((g.K + BK - 1) / BK);
+    const int64_t batches = g.batch_inner * g.batch_outer;
+    // the kernel writes raw sums into dense scratch [split][outer][inner][M][N]; the epilogue runs in the reduction
+    kp.c = g.split_ws;
+    kp.ldc = g.N;
+    kp.c_stride_inner = g.M * g.N;
+    kp.c_stride_outer = g.batch_inner * g.M * g.N;
+    kp.preact = nullptr; kp.bias = nullptr; kp.scale_mode = TE_SCALE_NONE; kp.epilogue = TE_EPI_NONE;
+    p.c = kp.c; p.ldc = kp.ldc; p.c_stride_inner = kp.c_stride_inner; p.c_stride_outer = kp.c_stride_outer;
+    p.preact = nullptr; p.bias = nullptr; p.scale_mode = TE_SCALE_NONE; p.epilogue = TE_EPI_NONE;
+    p.k_splits = k_splits;
+    p.kb_per_split = (kblocks + k_splits - 1) / k_splits;
+    p.split_stride = batches * g.M * g.N;
+}
+
+// out = epilogue( sum over splits, in split order, of the partial tiles ): deterministic, streaming, HBM-bound.
+struct SplitReduceParams {
+    const float* partial;
+    long long split_stride;
+    int k_splits;
+    long long M, N, batch_inner, total;       // total = batches * M * N
+    float* c; float* preact; const float* bias;
+    long long ldc, c_stride_inner, c_stride_outer;
+    float alpha; int scale_mode; int epilogue;
+};
+
+__global__ void __launch_bounds__(256) splitk_reduce_kernel(const SplitReduceParams r) {
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < r.total; i += stride) {
+        float v = 0.0f;
+        for (int s = 0; s < r.k_splits; ++s) v += r.partial[s * r.split_stride + i];
+        const long long n = i % r.N, row = (i / r.N) % r.M, batch = i / (r.N * r.M);
+        const long long bo = batch / r.batch_inner, bi = batch - bo * r.batch_inner;
+        if (r.scale_mode == TE_SCALE_MUL) v *= r.alpha;
+        else if (r.scale_mode == TE_SCALE_DIV) v = v / r.alpha;
+        if (r.bias) v += r.bias[n];
+        const long long o = bo * r.c_stride_outer + bi * r.c_stride_inner + row * r.ldc + n;
+        if (r.preact) r.preact[o] = v;
+        if (r.epilogue == TE_EPI_BIAS_GELU) v = gelu_tanh(v);
+        r.c[o] = v;
+    }
+}
+
+int finish_split(te_b200_ctx* ctx, const GemmProblem& g, int k_splits, cudaStream_t stream) {
+    SplitReduceParams r;
+    r.partial = g.split_ws;
+    r.M = g.M; r.N = g.N; r.batch_inner = g.batch_inner;
+    r.total = g.batch_inner * g.batch_outer * g.M * g.N;
+    r.split_stride = r.total;
+    r.k_splits = k_splits;
+    r.c = g.c; r.preact = g.preact; r.bias = g.bias;
+    r.ldc = g.ldc; r.c_stride_inner = g.c_stride_inner; r.c_stride_outer = g.c_stride_outer;
+    r.alpha = g.alpha; r.scale_mode = g.scale_mode; r.epilogue = g.epilogue;
+    long long blocks = (r.total + 255) / 256;
+    if (blocks > (long long)ctx->sm_count * 16) blocks = (long long)ctx->sm_count * 16;
+    splitk_reduce_kernel<<<(unsigned)blocks, 256, 0, stream>>>(r);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return cuda_fail(e, "splitk_reduce_kernel launch");
+    ctx->launches += 1;
+    return TE_OK;
 }
 
 template <int BN, int NPL, bool A_MN, bool B_MN>
-static int launch_variant(te_b200_ctx* ctx, const GemmProblem& g, cudaStream_t stream) {
+static int launch_variant(te_b200_ctx* ctx, const GemmProblem& g_in, int k_splits, cudaStream_t stream) {
+    GemmProblem g = g_in;
     using Cfg = TileCfg<BN, NPL>;
     auto kernel = gemm_tf32_kernel<BN, NPL, A_MN, B_MN>;
     static bool attr_done[16] = {};   // per device ordinal
@@ -456,44 +532,48 @@ static int launch_variant(te_b200_ctx* ctx, const GemmProblem& g, cudaStream_t s
     }
     GemmParams p;
     fill_common_params(p, ctx, g);
+    prepare_split(g_in, k_splits, g, p);       // with k_splits > 1 the kernel writes raw partial tiles to scratch
     CUtensorMap mc, mpre;
-    p.tma_store = make_output_maps(ctx, g, &mc, &mpre) ? 1 : 0;
+    p.tma_store = make_output_maps(ctx, g, k_splits, &mc, &mpre) ? 1 : 0;
     p.tiles_m = (int)((g.M + BM - 1) / BM);
     p.tiles_n = (int)((g.N + BN - 1) / BN);
-    const long long total = (long long)p.tiles_m * p.tiles_n * p.num_batches;
+    const long long total = (long long)p.tiles_m * p.tiles_n * p.num_batches * k_splits;
     const int grid = (int)(total < ctx->sm_count ? total : ctx->sm_count);
     kernel<<<grid, CTA_THREADS, Cfg::SMEM_BYTES, stream>>>(ma, mal, mb, mbl, mc, mpre, p);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return cuda_fail(e, "gemm_tf32_kernel launch");
     ctx->launches += 1;
-    return TE_OK;
+    return k_splits > 1 ? finish_split(ctx, g_in, k_splits, stream) : TE_OK;
 }
 
 template <int BN>
-static int launch_bn(te_b200_ctx* ctx, const GemmProblem& g, cudaStream_t stream) {
+static int launch_bn(te_b200_ctx* ctx, const GemmProblem& g, int k_splits, cudaStream_t stream) {
     if (g.a_lo) {   // 3xTF32: planes are always packed K-major
-        if constexpr (BN <= 128) return launch_variant<BN, 2, false, false>(ctx, g, stream);
-        else return launch_variant<128, 2, false, false>(ctx, g, stream);
+        if constexpr (BN <= 128) return launch_variant<BN, 2, false, false>(ctx, g, k_splits, stream);
+        else return launch_variant<128, 2, false, false>(ctx, g, k_splits, stream);
     }
-    if (!g.a.mn_major && !g.b.mn_major) return launch_variant<BN, 1, false, false>(ctx, g, stream);
-    if (!g.a.mn_major && g.b.mn_major) return launch_variant<BN, 1, false, true>(ctx, g, stream);
-    if (g.a.mn_major && !g.b.mn_major) return launch_variant<BN, 1, true, false>(ctx, g, stream);
-    return launch_variant<BN, 1, true, true>(ctx, g, stream);
+    if (!g.a.mn_major && !g.b.mn_major) return launch_variant<BN, 1, false, false>(ctx, g, k_splits, stream);
+    if (!g.a.mn_major && g.b.mn_major) return launch_variant<BN, 1, false, true>(ctx, g, k_splits, stream);
+    if (g.a.mn_major && !g.b.mn_major) return launch_variant<BN, 1, true, false>(ctx, g, k_splits, stream);
+    return launch_variant<BN, 1, true, true>(ctx, g, k_splits, stream);
 }
 
 // Tile-shape choice.  Larger tiles move fewer bytes into shared memory per flop (the pair tile least of all) but
 // give fewer tiles; with too few tiles most SMs idle.  The estimate below is waves x (k-blocks x time per k-block
 // + a fixed per-tile cost) with per-k-block times measured on 8192^3 for each shape (ns): they encode that the
-// small shapes are bound by filling shared memory, not by the tensor pipe.
-struct TileChoice { int bn; bool pair; };
+// small shapes are bound by filling shared memory, not by the tensor pipe.  When a problem has few tiles but a long
+// K (a thin M, a weight gradient over many tokens), K is additionally split over several work units per tile.
+struct TileChoice { int bn; bool pair; int k_splits; };
 
 static TileChoice choose_tile(const te_b200_ctx* ctx, const GemmProblem& g) {
-    const double kblocks = (double)((g.K + BK - 1) / BK);
+    const int kblocks = (int)((g.K + BK - 1) / BK);
     const double batches = (double)(g.batch_inner * g.batch_outer);
     struct Cand { int bn; bool pair; double ns_per_kblock; double fixed_ns; };
     const Cand cands[4] = {{256, true, 405.0, 3000.0}, {256, false, 432.0, 3000.0}, {128, false, 350.0, 2000.0},
                            {64, false, 291.0, 1500.0}};
-    TileChoice best{64, false};
+    const int split_options[8] = {1, 2, 3, 4, 6, 8, 12, 16};
+    const double out_bytes = batches * (double)g.M * (double)g.N * 4.0;
+    TileChoice best{64, false, 1};
     double best_t = 1e300;
     for (const Cand& c : cands) {
         if (c.pair && (g.M <= 128 || g.N <= 128 || g.a_lo)) continue;
@@ -503,20 +583,32 @@ static TileChoice choose_tile(const te_b200_ctx* ctx, const GemmProblem& g) {
         const double tn = (double)((g.N + c.bn - 1) / c.bn);
         const double tiles = tm * tn * batches;
         const double slots = c.pair ? ctx->sm_count / 2 : ctx->sm_count;
-        const double waves = (double)(long long)((tiles + slots - 1) / slots);
         const double planes = g.a_lo ? 3.0 : 1.0;
-        const double t = waves * (kblocks * c.ns_per_kblock * planes + c.fixed_ns);
-        if (t < best_t) { best_t = t; best = TileChoice{c.bn, c.pair}; }
+        for (int S : split_options) {
+            if (S > 1) {
+                // every split needs a few k-blocks of its own, the scratch must hold S copies of the output, and the
+                // last split must not be empty
+                if (kblocks < 4 * S || !g.split_ws || out_bytes * S > (double)g.split_ws_bytes) break;
+                const int per = (kblocks + S - 1) / S;
+                if ((S - 1) * per >= kblocks) continue;
+            }
+            const double units = tiles * S;
+            const double waves = (double)(long long)((units + slots - 1) / slots);
+            const double kb_unit = (double)((kblocks + S - 1) / S);
+            double t = waves * (kb_unit * c.ns_per_kblock * planes + c.fixed_ns);
+            if (S > 1) t += 4000.0 + out_bytes * (S + 1) / 4000.0;     // reduction: launch + (S reads + 1 write) at ~4 TB/s
+            if (t < best_t) { best_t = t; best = TileChoice{c.bn, c.pair, S}; }
+        }
     }
     return best;
 }
 
 int launch_gemm(te_b200_ctx* ctx, const GemmProblem& g, cudaStream_t stream) {
     const TileChoice c = choose_tile(ctx, g);
-    if (c.pair) return launch_gemm_2cta(ctx, g, stream);
-    if (c.bn == 256) return launch_bn<256>(ctx, g, stream);
-    if (c.bn == 128) return launch_bn<128>(ctx, g, stream);
-    return launch_bn<64>(ctx, g, stream);
+    if (c.pair) return launch_gemm_2cta(ctx, g, c.k_splits, stream);
+    if (c.bn == 256) return launch_bn<256>(ctx, g, c.k_splits, stream);
+    if (c.bn == 128) return launch_bn<128>(ctx, g, c.k_splits, stream);
+    return launch_bn<64>(ctx, g, c.k_splits, stream);
 }
 
 }  // namespace te

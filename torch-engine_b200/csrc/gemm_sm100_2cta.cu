@@ -39,10 +39,6 @@ struct PairCfg {
     static_assert(SMEM_BYTES <= 232448, "exceeds the 227 KB of shared memory a CTA can have");
 };
 
-__device__ __forceinline__ void pair_tile_coords(int t, const GemmParams& p, int& batch, int& m_blk, int& n_blk) {
-    tile_coords(t, p, batch, m_blk, n_blk);   // same raster; tiles_m counts 256-row blocks here
-}
-
 template <int BN, bool A_MN, bool B_MN>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(CTA_THREADS, 1)
 gemm_tf32_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
@@ -110,7 +106,7 @@ gemm_tf32_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
     tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
 
-    const int total_tiles = p.tiles_m * p.tiles_n * p.num_batches;
+    const int total_units = p.tiles_m * p.tiles_n * p.num_batches * p.k_splits;
     const int kblocks = (p.K + BK - 1) / BK;
 
     if (warp == PRODUCER_WARP) {
@@ -118,15 +114,16 @@ gemm_tf32_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
         if (lane == 0) {
             int issued = 0;
             bool ok = true;
-            for (int t = pair; t < total_tiles && ok; t += num_pairs) {
-                int batch, m_blk, n_blk;
-                pair_tile_coords(t, p, batch, m_blk, n_blk);
+            for (int u = pair; u < total_units && ok; u += num_pairs) {
+                WorkUnit w;
+                decode_unit(u, p, kblocks, w);
+                const int batch = w.batch, m_blk = w.m_blk, n_blk = w.n_blk;
                 const int bo = batch / p.batch_inner, bi = batch - bo * p.batch_inner;
                 const int a_ci = bi * p.a_mul_inner, a_co = bo * p.a_mul_outer;
                 const int b_ci = bi * p.b_mul_inner, b_co = bo * p.b_mul_outer;
                 const int m0 = m_blk * PAIR_BM + (int)rank * BM;       // this CTA's 128 rows of A
                 const int n0 = n_blk * BN + (int)rank * HALF_N;        // this CTA's half of the B columns
-                for (int kb = 0; kb < kblocks; ++kb, ++issued) {
+                for (int kb = w.kb0; kb < w.kb1; ++kb, ++issued) {
                     const int s = issued % STAGES;
                     const uint32_t phase = (issued / STAGES) & 1;
                     if (!wait_bounded(bar_empty + 8 * s, phase ^ 1, abort_flag, p.status, WAIT_PRODUCER_EMPTY)) {
@@ -167,7 +164,9 @@ gemm_tf32_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
             int consumed = 0;
             int acc_idx = 0;
             bool ok = true;
-            for (int t = pair; t < total_tiles && ok; t += num_pairs, ++acc_idx) {
+            for (int u = pair; u < total_units && ok; u += num_pairs, ++acc_idx) {
+                WorkUnit w;
+                decode_unit(u, p, kblocks, w);
                 const int buf = acc_idx & 1;
                 if (!wait_bounded(bar_tmem_empty + 8 * buf, ((acc_idx >> 1) & 1) ^ 1, abort_flag, p.status,
                                   WAIT_MMA_TMEM_EMPTY)) {
@@ -176,7 +175,7 @@ gemm_tf32_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
                 }
                 tc_fence_after_sync();
                 const uint32_t d_tmem = tmem_base + buf * BN;
-                for (int kb = 0; kb < kblocks; ++kb, ++consumed) {
+                for (int kb = w.kb0; kb < w.kb1; ++kb, ++consumed) {
                     const int s = consumed % STAGES;
                     if (!wait_bounded(bar_full + 8 * s, (consumed / STAGES) & 1, abort_flag, p.status, WAIT_MMA_FULL)) {
                         ok = false;
@@ -189,7 +188,7 @@ gemm_tf32_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
                     for (int j = 0; j < BK / UMMA_K; ++j) {
                         const uint64_t da = make_smem_desc(sa + j * A_KSTEP, A_LBO, A_SBO, A_LAYOUT);
                         const uint64_t db = make_smem_desc(sb + j * B_KSTEP, B_LBO, B_SBO, B_LAYOUT);
-                        umma_tf32_pair(d_tmem, da, db, IDESC, (kb | j) != 0);
+                        umma_tf32_pair(d_tmem, da, db, IDESC, ((kb - w.kb0) | j) != 0);
                     }
                     umma_commit_pair(bar_empty + 8 * s, 3);        // frees the stage in both CTAs
                 }
@@ -209,13 +208,15 @@ gemm_tf32_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
         // ------------------------------------------------------------ epilogue (warps 0-7, both CTAs)
         int acc_idx = 0;
         bool ok = true;
-        for (int t = pair; t < total_tiles && ok; t += num_pairs, ++acc_idx) {
-            int batch, m_blk, n_blk;
-            pair_tile_coords(t, p, batch, m_blk, n_blk);
+        for (int u = pair; u < total_units && ok; u += num_pairs, ++acc_idx) {
+            WorkUnit w;
+            decode_unit(u, p, kblocks, w);
+            const int batch = w.batch, m_blk = w.m_blk, n_blk = w.n_blk;
             const int bo = batch / p.batch_inner, bi = batch - bo * p.batch_inner;
             const int row = m_blk * PAIR_BM + (int)rank * BM + (warp & 3) * 32 + lane;
             const int n0 = n_blk * BN;
-            const long long batch_off = (long long)bo * p.c_stride_outer + (long long)bi * p.c_stride_inner;
+            const long long batch_off = (long long)bo * p.c_stride_outer + (long long)bi * p.c_stride_inner +
+                                        (long long)w.split * p.split_stride;
             EpilogueRow er;
             er.c_row = p.c + batch_off + (long long)row * p.ldc;
             er.pre_row = p.preact ? p.preact + batch_off + (long long)row * p.ldc : nullptr;
@@ -228,7 +229,7 @@ gemm_tf32_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
             er.tm_pre = &tm_pre;
             er.row0 = m_blk * PAIR_BM + (int)rank * BM + (warp & 3) * 32;
             er.bi = bi;
-            er.bo = bo;
+            er.bo = w.split * p.batch_outer_n + bo;
             const int buf = acc_idx & 1;
             ok = wait_bounded(bar_tmem_full + 8 * buf, (acc_idx >> 1) & 1, abort_flag, p.status, WAIT_EPI_TMEM_FULL);
             ok = __all_sync(0xffffffffu, ok);
@@ -265,7 +266,7 @@ gemm_tf32_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
 }
 
 template <int BN, bool A_MN, bool B_MN>
-static int launch_pair_variant(te_b200_ctx* ctx, const GemmProblem& g, cudaStream_t stream) {
+static int launch_pair_variant(te_b200_ctx* ctx, const GemmProblem& g_in, int k_splits, cudaStream_t stream) {
     using Cfg = PairCfg<BN>;
     auto kernel = gemm_tf32_pair_kernel<BN, A_MN, B_MN>;
     static bool attr_done[16] = {};
@@ -274,17 +275,19 @@ static int launch_pair_variant(te_b200_ctx* ctx, const GemmProblem& g, cudaStrea
         if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(max dynamic shared memory)");
         attr_done[ctx->device] = true;
     }
+    GemmProblem g = g_in;
     CUtensorMap ma, mb;
     int rc;
     if ((rc = make_operand_map(ctx, &ma, g.a.ptr, g.a, g.K, BM, g.batch_inner, g.batch_outer))) return rc;
     if ((rc = make_operand_map(ctx, &mb, g.b.ptr, g.b, g.K, BN / 2, g.batch_inner, g.batch_outer))) return rc;
     GemmParams p;
     fill_common_params(p, ctx, g);
+    prepare_split(g_in, k_splits, g, p);       // with k_splits > 1 the kernel writes raw partial tiles to scratch
     CUtensorMap mc, mpre;
-    p.tma_store = make_output_maps(ctx, g, &mc, &mpre) ? 1 : 0;
+    p.tma_store = make_output_maps(ctx, g, k_splits, &mc, &mpre) ? 1 : 0;
     p.tiles_m = (int)((g.M + PAIR_BM - 1) / PAIR_BM);
     p.tiles_n = (int)((g.N + BN - 1) / BN);
-    const long long total = (long long)p.tiles_m * p.tiles_n * p.num_batches;
+    const long long total = (long long)p.tiles_m * p.tiles_n * p.num_batches * k_splits;
     // How many CTA pairs can be resident at once (pairs must sit on neighbouring SMs, so this can be below SMs/2).
     static int max_pairs_cached[16] = {};
     int max_pairs = ctx->device < 16 ? max_pairs_cached[ctx->device] : 0;
@@ -309,14 +312,14 @@ static int launch_pair_variant(te_b200_ctx* ctx, const GemmProblem& g, cudaStrea
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return cuda_fail(e, "gemm_tf32_pair_kernel launch");
     ctx->launches += 1;
-    return TE_OK;
+    return k_splits > 1 ? finish_split(ctx, g_in, k_splits, stream) : TE_OK;
 }
 
-int launch_gemm_2cta(te_b200_ctx* ctx, const GemmProblem& g, cudaStream_t stream) {
-    if (!g.a.mn_major && !g.b.mn_major) return launch_pair_variant<256, false, false>(ctx, g, stream);
-    if (!g.a.mn_major && g.b.mn_major) return launch_pair_variant<256, false, true>(ctx, g, stream);
-    if (g.a.mn_major && !g.b.mn_major) return launch_pair_variant<256, true, false>(ctx, g, stream);
-    return launch_pair_variant<256, true, true>(ctx, g, stream);
+int launch_gemm_2cta(te_b200_ctx* ctx, const GemmProblem& g, int k_splits, cudaStream_t stream) {
+    if (!g.a.mn_major && !g.b.mn_major) return launch_pair_variant<256, false, false>(ctx, g, k_splits, stream);
+    if (!g.a.mn_major && g.b.mn_major) return launch_pair_variant<256, false, true>(ctx, g, k_splits, stream);
+    if (g.a.mn_major && !g.b.mn_major) return launch_pair_variant<256, true, false>(ctx, g, k_splits, stream);
+    return launch_pair_variant<256, true, true>(ctx, g, k_splits, stream);
 }
 
 }  // namespace te

@@ -31,6 +31,9 @@ struct GemmProblem {
     float alpha = 1.0f;
     int scale_mode = TE_SCALE_NONE;
     int epilogue = TE_EPI_NONE;
+    // scratch the launcher may use for split-K partial tiles (may be null / 0)
+    float* split_ws = nullptr;
+    size_t split_ws_bytes = 0;
 };
 
 }  // namespace te
