@@ -568,22 +568,26 @@ struct TileChoice { int bn; bool pair; int k_splits; };
 static TileChoice choose_tile(const te_b200_ctx* ctx, const GemmProblem& g) {
     const int kblocks = (int)((g.K + BK - 1) / BK);
     const double batches = (double)(g.batch_inner * g.batch_outer);
-    struct Cand { int bn; bool pair; double ns_per_kblock; double fixed_ns; };
-    const Cand cands[4] = {{256, true, 405.0, 3000.0}, {256, false, 432.0, 3000.0}, {128, false, 350.0, 2000.0},
-                           {64, false, 291.0, 1500.0}};
+    // ns per k-block of one tile in TF32 mode and in 3xTF32 mode (two planes per operand, three MMAs per k-step,
+    // fewer and larger pipeline stages), fixed ns per tile
+    struct Cand { int bn; bool pair; double ns_per_kblock; double ns_per_kblock_3x; double fixed_ns; };
+    const Cand cands[4] = {{256, true, 405.0, 1400.0, 3000.0}, {256, false, 432.0, 1e9, 3000.0},
+                           {128, false, 350.0, 804.0, 2000.0}, {64, false, 291.0, 520.0, 1500.0}};
     const int split_options[8] = {1, 2, 3, 4, 6, 8, 12, 16};
     const double out_bytes = batches * (double)g.M * (double)g.N * 4.0;
     TileChoice best{64, false, 1};
     double best_t = 1e300;
     for (const Cand& c : cands) {
-        if (c.pair && (g.M <= 128 || g.N <= 128 || g.a_lo)) continue;
-        if (g.a_lo && c.bn > 128) continue;                      // 3xTF32 keeps bn/2 accumulators per thread
+        if (c.pair && (g.M <= 128 || g.N <= 128)) continue;
+        if (c.pair && g.a_lo && kblocks < 160) continue;         // measured: the 3-stage pair form of 3xTF32 pays off from K ~ 5000
+        if (g.a_lo && !c.pair && c.bn > 128) continue;           // 3xTF32, single CTA: two 96 KB stages would be too few
         if (c.bn > 64 && g.N <= c.bn / 2) continue;              // more than half of the tile would be padding
         const double tm = (double)((g.M + (c.pair ? 255 : 127)) / (c.pair ? 256 : 128));
         const double tn = (double)((g.N + c.bn - 1) / c.bn);
         const double tiles = tm * tn * batches;
         const double slots = c.pair ? ctx->sm_count / 2 : ctx->sm_count;
-        const double planes = g.a_lo ? 3.0 : 1.0;
+        const double ns_kb = g.a_lo ? c.ns_per_kblock_3x : c.ns_per_kblock;
+        const double fixed = g.a_lo && c.pair ? 2.0 * c.fixed_ns : c.fixed_ns;
         for (int S : split_options) {
             if (S > 1) {
                 // every split needs a few k-blocks of its own, the scratch must hold S copies of the output, and the
@@ -595,7 +599,7 @@ static TileChoice choose_tile(const te_b200_ctx* ctx, const GemmProblem& g) {
             const double units = tiles * S;
             const double waves = (double)(long long)((units + slots - 1) / slots);
             const double kb_unit = (double)((kblocks + S - 1) / S);
-            double t = waves * (kb_unit * c.ns_per_kblock * planes + c.fixed_ns);
+            double t = waves * (kb_unit * ns_kb + fixed);
             if (S > 1) t += 4000.0 + out_bytes * (S + 1) / 4000.0;     // reduction: launch + (S reads + 1 write) at ~4 TB/s
             if (t < best_t) { best_t = t; best = TileChoice{c.bn, c.pair, S}; }
         }

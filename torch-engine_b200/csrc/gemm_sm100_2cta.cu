@@ -27,10 +27,10 @@ namespace te {
 
 constexpr int PAIR_BM = 256;   // rows of one pair tile (128 per CTA)
 
-template <int BN>
+template <int BN, int NPL>
 struct PairCfg {
     static constexpr int B_HALF_BYTES = (BN / 2) * BK * 4;
-    static constexpr int STAGE_BYTES = A_PLANE_BYTES + B_HALF_BYTES;      // per CTA
+    static constexpr int STAGE_BYTES = NPL * (A_PLANE_BYTES + B_HALF_BYTES);      // per CTA; NPL = 2: tf32 hi and lo planes
     static constexpr int STAGES = SMEM_RING_BUDGET / STAGE_BYTES;
     static constexpr int TMEM_COLS = 2 * BN;
     static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + EPI_WARPS * EPI_STAGE_BYTES + SMEM_AUX_BYTES + 1024;
@@ -39,12 +39,16 @@ struct PairCfg {
     static_assert(SMEM_BYTES <= 232448, "exceeds the 227 KB of shared memory a CTA can have");
 };
 
-template <int BN, bool A_MN, bool B_MN>
+template <int BN, int NPL, bool A_MN, bool B_MN>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(CTA_THREADS, 1)
-gemm_tf32_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
+gemm_tf32_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_a_lo,
+                      const __grid_constant__ CUtensorMap tm_b, const __grid_constant__ CUtensorMap tm_b_lo,
                       const __grid_constant__ CUtensorMap tm_c, const __grid_constant__ CUtensorMap tm_pre,
                       const GemmParams p) {
-    using Cfg = PairCfg<BN>;
+    using Cfg = PairCfg<BN, NPL>;
+    constexpr bool CHUNKED = (NPL == 2);      // 3xTF32: sum K in chunks in TMEM, add the chunks in registers
+    constexpr int CHUNK_KB = 8;
+    constexpr int B_HALF_BYTES = Cfg::B_HALF_BYTES;
     constexpr int STAGES = Cfg::STAGES;
     constexpr int STAGE_BYTES = Cfg::STAGE_BYTES;
     constexpr int HALF_N = BN / 2;
@@ -95,6 +99,10 @@ gemm_tf32_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
     if (warp == PRODUCER_WARP && lane == 0) {
         tma_prefetch_desc(&tm_a);
         tma_prefetch_desc(&tm_b);
+        if (NPL == 2) {
+            tma_prefetch_desc(&tm_a_lo);
+            tma_prefetch_desc(&tm_b_lo);
+        }
     }
     if (warp == MMA_WARP) {
         tmem_alloc_pair(tmem_slot_addr, Cfg::TMEM_COLS);
@@ -133,21 +141,27 @@ gemm_tf32_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
                     const uint32_t full = map_to_cta(bar_full + 8 * s, 0);     // the leader's barrier
                     mbar_arrive_expect_tx_cluster(full, STAGE_BYTES);
                     const uint32_t sa = ring + s * STAGE_BYTES;
-                    const uint32_t sb = sa + A_PLANE_BYTES;
+                    const uint32_t sb = sa + NPL * A_PLANE_BYTES;
                     const int k0 = kb * BK;
-                    if (A_MN) {
 #pragma unroll
-                        for (int c = 0; c < BM / 32; ++c)
-                            tma_load_4d_pair(sa + c * MN_CHUNK_BYTES, &tm_a, full, m0 + 32 * c, k0, a_ci, a_co);
-                    } else {
-                        tma_load_4d_pair(sa, &tm_a, full, k0, m0, a_ci, a_co);
-                    }
-                    if (B_MN) {
+                    for (int pl = 0; pl < NPL; ++pl) {
+                        const CUtensorMap* ma = pl ? &tm_a_lo : &tm_a;
+                        const CUtensorMap* mb = pl ? &tm_b_lo : &tm_b;
+                        const uint32_t pa = sa + pl * A_PLANE_BYTES, pb = sb + pl * B_HALF_BYTES;
+                        if (A_MN) {
 #pragma unroll
-                        for (int c = 0; c < HALF_N / 32; ++c)
-                            tma_load_4d_pair(sb + c * MN_CHUNK_BYTES, &tm_b, full, n0 + 32 * c, k0, b_ci, b_co);
-                    } else {
-                        tma_load_4d_pair(sb, &tm_b, full, k0, n0, b_ci, b_co);
+                            for (int c = 0; c < BM / 32; ++c)
+                                tma_load_4d_pair(pa + c * MN_CHUNK_BYTES, ma, full, m0 + 32 * c, k0, a_ci, a_co);
+                        } else {
+                            tma_load_4d_pair(pa, ma, full, k0, m0, a_ci, a_co);
+                        }
+                        if (B_MN) {
+#pragma unroll
+                            for (int c = 0; c < HALF_N / 32; ++c)
+                                tma_load_4d_pair(pb + c * MN_CHUNK_BYTES, mb, full, n0 + 32 * c, k0, b_ci, b_co);
+                        } else {
+                            tma_load_4d_pair(pb, mb, full, k0, n0, b_ci, b_co);
+                        }
                     }
                 }
             }
@@ -164,36 +178,51 @@ gemm_tf32_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
             int consumed = 0;
             int acc_idx = 0;
             bool ok = true;
-            for (int u = pair; u < total_units && ok; u += num_pairs, ++acc_idx) {
+            for (int u = pair; u < total_units && ok; u += num_pairs) {
                 WorkUnit w;
                 decode_unit(u, p, kblocks, w);
-                const int buf = acc_idx & 1;
-                if (!wait_bounded(bar_tmem_empty + 8 * buf, ((acc_idx >> 1) & 1) ^ 1, abort_flag, p.status,
-                                  WAIT_MMA_TMEM_EMPTY)) {
-                    ok = false;
-                    break;
-                }
-                tc_fence_after_sync();
-                const uint32_t d_tmem = tmem_base + buf * BN;
-                for (int kb = w.kb0; kb < w.kb1; ++kb, ++consumed) {
-                    const int s = consumed % STAGES;
-                    if (!wait_bounded(bar_full + 8 * s, (consumed / STAGES) & 1, abort_flag, p.status, WAIT_MMA_FULL)) {
+                int kb = w.kb0;
+                do {   // one pass per accumulator buffer: this unit's whole K range, or one chunk of it
+                    const int kb_end = CHUNKED ? min(kb + CHUNK_KB, w.kb1) : w.kb1;
+                    const int buf = acc_idx & 1;
+                    if (!wait_bounded(bar_tmem_empty + 8 * buf, ((acc_idx >> 1) & 1) ^ 1, abort_flag, p.status,
+                                      WAIT_MMA_TMEM_EMPTY)) {
                         ok = false;
                         break;
                     }
                     tc_fence_after_sync();
-                    const uint32_t sa = ring + s * STAGE_BYTES;
-                    const uint32_t sb = sa + A_PLANE_BYTES;
+                    const uint32_t d_tmem = tmem_base + buf * BN;
+                    const int kb_first = kb;
+                    for (; kb < kb_end; ++kb, ++consumed) {
+                        const int s = consumed % STAGES;
+                        if (!wait_bounded(bar_full + 8 * s, (consumed / STAGES) & 1, abort_flag, p.status, WAIT_MMA_FULL)) {
+                            ok = false;
+                            break;
+                        }
+                        tc_fence_after_sync();
+                        const uint32_t sa = ring + s * STAGE_BYTES;
+                        const uint32_t sb = sa + NPL * A_PLANE_BYTES;
 #pragma unroll
-                    for (int j = 0; j < BK / UMMA_K; ++j) {
-                        const uint64_t da = make_smem_desc(sa + j * A_KSTEP, A_LBO, A_SBO, A_LAYOUT);
-                        const uint64_t db = make_smem_desc(sb + j * B_KSTEP, B_LBO, B_SBO, B_LAYOUT);
-                        umma_tf32_pair(d_tmem, da, db, IDESC, ((kb - w.kb0) | j) != 0);
+                        for (int j = 0; j < BK / UMMA_K; ++j) {
+                            const uint64_t a_hi = make_smem_desc(sa + j * A_KSTEP, A_LBO, A_SBO, A_LAYOUT);
+                            const uint64_t b_hi = make_smem_desc(sb + j * B_KSTEP, B_LBO, B_SBO, B_LAYOUT);
+                            const uint32_t acc0 = ((kb - kb_first) | j) != 0;
+                            if (NPL == 2) {
+                                const uint64_t a_lo = make_smem_desc(sa + A_PLANE_BYTES + j * A_KSTEP, A_LBO, A_SBO, A_LAYOUT);
+                                const uint64_t b_lo = make_smem_desc(sb + B_HALF_BYTES + j * B_KSTEP, B_LBO, B_SBO, B_LAYOUT);
+                                umma_tf32_pair(d_tmem, a_lo, b_hi, IDESC, acc0);   // small terms first
+                                umma_tf32_pair(d_tmem, a_hi, b_lo, IDESC, 1);
+                                umma_tf32_pair(d_tmem, a_hi, b_hi, IDESC, 1);
+                            } else {
+                                umma_tf32_pair(d_tmem, a_hi, b_hi, IDESC, acc0);
+                            }
+                        }
+                        umma_commit_pair(bar_empty + 8 * s, 3);        // frees the stage in both CTAs
                     }
-                    umma_commit_pair(bar_empty + 8 * s, 3);        // frees the stage in both CTAs
-                }
-                if (!ok) break;
-                umma_commit_pair(bar_tmem_full + 8 * buf, 3);      // accumulator ready in both CTAs
+                    if (!ok) break;
+                    umma_commit_pair(bar_tmem_full + 8 * buf, 3);      // accumulator ready in both CTAs
+                    ++acc_idx;
+                } while (kb < w.kb1);
             }
             umma_commit_pair(bar_teardown, 1);
             const uint64_t t0 = global_timer_ns();
@@ -208,7 +237,7 @@ gemm_tf32_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
         // ------------------------------------------------------------ epilogue (warps 0-7, both CTAs)
         int acc_idx = 0;
         bool ok = true;
-        for (int u = pair; u < total_units && ok; u += num_pairs, ++acc_idx) {
+        for (int u = pair; u < total_units && ok; u += num_pairs) {
             WorkUnit w;
             decode_unit(u, p, kblocks, w);
             const int batch = w.batch, m_blk = w.m_blk, n_blk = w.n_blk;
@@ -230,27 +259,69 @@ gemm_tf32_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
             er.row0 = m_blk * PAIR_BM + (int)rank * BM + (warp & 3) * 32;
             er.bi = bi;
             er.bo = w.split * p.batch_outer_n + bo;
-            const int buf = acc_idx & 1;
-            ok = wait_bounded(bar_tmem_full + 8 * buf, (acc_idx >> 1) & 1, abort_flag, p.status, WAIT_EPI_TMEM_FULL);
-            ok = __all_sync(0xffffffffu, ok);
-            if (!ok) break;
-            tc_fence_after_sync();
-            const uint32_t t_row = tmem_base + (uint32_t((warp & 3) * 32) << 16) + buf * BN;
-#pragma unroll 1
-            for (int cc = (warp >> 2) * (BN / 64); cc < ((warp >> 2) + 1) * (BN / 64); ++cc) {
-                const int col0 = n0 + cc * 32;
-                if (col0 >= p.N) break;
-                uint32_t r[32];
-                tmem_ld_32x32b_x32(t_row + cc * 32, r);
-                tmem_ld_wait();
-                float v[32];
+            const uint32_t empty_leader = map_to_cta(bar_tmem_empty, 0);
+            if (CHUNKED) {
+                // Two-level accumulation (see the single-CTA kernel): chunk sums from TMEM are added in registers.
+                constexpr int NACC = CHUNKED ? BN / 2 : 1;     // this warp's half of the tile's columns
+                const int nh = n0 + (warp >> 2) * (BN / 2);
+                float acc[NACC];
 #pragma unroll
-                for (int j = 0; j < 32; ++j) v[j] = p.K > 0 ? __uint_as_float(r[j]) : 0.0f;
-                epilogue_store32(v, col0, er, p, lane);
+                for (int j = 0; j < NACC; ++j) acc[j] = 0.0f;
+                const int chunks = w.kb1 > w.kb0 ? (w.kb1 - w.kb0 + CHUNK_KB - 1) / CHUNK_KB : 1;
+                for (int ch = 0; ch < chunks && ok; ++ch, ++acc_idx) {
+                    const int buf = acc_idx & 1;
+                    ok = wait_bounded(bar_tmem_full + 8 * buf, (acc_idx >> 1) & 1, abort_flag, p.status, WAIT_EPI_TMEM_FULL);
+                    ok = __all_sync(0xffffffffu, ok);
+                    if (!ok) break;
+                    tc_fence_after_sync();
+                    const uint32_t t_row = tmem_base + (uint32_t((warp & 3) * 32) << 16) + buf * BN + (warp >> 2) * (BN / 2);
+                    if (p.K > 0) {
+#pragma unroll
+                        for (int cc = 0; cc < NACC / 32; ++cc) {
+                            if (nh + cc * 32 < p.N) {   // warp-uniform
+                                uint32_t r[32];
+                                tmem_ld_32x32b_x32(t_row + cc * 32, r);
+                                tmem_ld_wait();
+#pragma unroll
+                                for (int j = 0; j < 32; ++j) acc[cc * 32 + j] += __uint_as_float(r[j]);
+                            }
+                        }
+                    }
+                    tc_fence_before_sync();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive_cluster(empty_leader + 8 * buf);
+                }
+                if (ok) {
+#pragma unroll
+                    for (int cc = 0; cc < NACC / 32; ++cc) {
+                        const int col0 = nh + cc * 32;
+                        if (col0 < p.N) epilogue_store32(&acc[cc * 32], col0, er, p, lane);
+                    }
+                }
+            } else {
+                const int buf = acc_idx & 1;
+                ok = wait_bounded(bar_tmem_full + 8 * buf, (acc_idx >> 1) & 1, abort_flag, p.status, WAIT_EPI_TMEM_FULL);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+                tc_fence_after_sync();
+                const uint32_t t_row = tmem_base + (uint32_t((warp & 3) * 32) << 16) + buf * BN;
+#pragma unroll 1
+                for (int cc = (warp >> 2) * (BN / 64); cc < ((warp >> 2) + 1) * (BN / 64); ++cc) {
+                    const int col0 = n0 + cc * 32;
+                    if (col0 >= p.N) break;
+                    uint32_t r[32];
+                    tmem_ld_32x32b_x32(t_row + cc * 32, r);
+                    tmem_ld_wait();
+                    float v[32];
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) v[j] = p.K > 0 ? __uint_as_float(r[j]) : 0.0f;
+                    epilogue_store32(v, col0, er, p, lane);
+                }
+                tc_fence_before_sync();
+                __syncwarp();
+                if (lane == 0) mbar_arrive_cluster(empty_leader + 8 * buf);
+                ++acc_idx;
             }
-            tc_fence_before_sync();
-            __syncwarp();
-            if (lane == 0) mbar_arrive_cluster(map_to_cta(bar_tmem_empty + 8 * buf, 0));
         }
     }
 
@@ -265,10 +336,10 @@ gemm_tf32_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
     }
 }
 
-template <int BN, bool A_MN, bool B_MN>
+template <int BN, int NPL, bool A_MN, bool B_MN>
 static int launch_pair_variant(te_b200_ctx* ctx, const GemmProblem& g_in, int k_splits, cudaStream_t stream) {
-    using Cfg = PairCfg<BN>;
-    auto kernel = gemm_tf32_pair_kernel<BN, A_MN, B_MN>;
+    using Cfg = PairCfg<BN, NPL>;
+    auto kernel = gemm_tf32_pair_kernel<BN, NPL, A_MN, B_MN>;
     static bool attr_done[16] = {};
     if (ctx->device < 16 && !attr_done[ctx->device]) {
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
@@ -276,10 +347,17 @@ static int launch_pair_variant(te_b200_ctx* ctx, const GemmProblem& g_in, int k_
         attr_done[ctx->device] = true;
     }
     GemmProblem g = g_in;
-    CUtensorMap ma, mb;
+    CUtensorMap ma, mal, mb, mbl;
     int rc;
     if ((rc = make_operand_map(ctx, &ma, g.a.ptr, g.a, g.K, BM, g.batch_inner, g.batch_outer))) return rc;
     if ((rc = make_operand_map(ctx, &mb, g.b.ptr, g.b, g.K, BN / 2, g.batch_inner, g.batch_outer))) return rc;
+    if (NPL == 2) {
+        if ((rc = make_operand_map(ctx, &mal, g.a_lo, g.a, g.K, BM, g.batch_inner, g.batch_outer))) return rc;
+        if ((rc = make_operand_map(ctx, &mbl, g.b_lo, g.b, g.K, BN / 2, g.batch_inner, g.batch_outer))) return rc;
+    } else {
+        mal = ma;
+        mbl = mb;
+    }
     GemmParams p;
     fill_common_params(p, ctx, g);
     prepare_split(g_in, k_splits, g, p);       // with k_splits > 1 the kernel writes raw partial tiles to scratch
@@ -308,7 +386,7 @@ static int launch_pair_variant(te_b200_ctx* ctx, const GemmProblem& g_in, int k_
         if (ctx->device < 16) max_pairs_cached[ctx->device] = n;
     }
     const int pairs = (int)(total < max_pairs ? total : max_pairs);
-    kernel<<<2 * pairs, CTA_THREADS, Cfg::SMEM_BYTES, stream>>>(ma, mb, mc, mpre, p);
+    kernel<<<2 * pairs, CTA_THREADS, Cfg::SMEM_BYTES, stream>>>(ma, mal, mb, mbl, mc, mpre, p);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return cuda_fail(e, "gemm_tf32_pair_kernel launch");
     ctx->launches += 1;
@@ -316,10 +394,11 @@ static int launch_pair_variant(te_b200_ctx* ctx, const GemmProblem& g_in, int k_
 }
 
 int launch_gemm_2cta(te_b200_ctx* ctx, const GemmProblem& g, int k_splits, cudaStream_t stream) {
-    if (!g.a.mn_major && !g.b.mn_major) return launch_pair_variant<256, false, false>(ctx, g, k_splits, stream);
-    if (!g.a.mn_major && g.b.mn_major) return launch_pair_variant<256, false, true>(ctx, g, k_splits, stream);
-    if (g.a.mn_major && !g.b.mn_major) return launch_pair_variant<256, true, false>(ctx, g, k_splits, stream);
-    return launch_pair_variant<256, true, true>(ctx, g, k_splits, stream);
+    if (g.a_lo) return launch_pair_variant<256, 2, false, false>(ctx, g, k_splits, stream);   // 3xTF32: packed K-major planes
+    if (!g.a.mn_major && !g.b.mn_major) return launch_pair_variant<256, 1, false, false>(ctx, g, k_splits, stream);
+    if (!g.a.mn_major && g.b.mn_major) return launch_pair_variant<256, 1, false, true>(ctx, g, k_splits, stream);
+    if (g.a.mn_major && !g.b.mn_major) return launch_pair_variant<256, 1, true, false>(ctx, g, k_splits, stream);
+    return launch_pair_variant<256, 1, true, true>(ctx, g, k_splits, stream);
 }
 
 }  // namespace te

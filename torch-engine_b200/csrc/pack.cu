@@ -68,6 +68,39 @@ __global__ void __launch_bounds__(256) pack_operand_kernel(const PackParams p) {
     }
 }
 
+// K-major source whose rows are 16-byte aligned: no transpose needed, four k per thread with 16-byte accesses.
+template <bool SPLIT>
+__global__ void __launch_bounds__(256) pack_rows_vec4_kernel(const PackParams p, long long quads_per_row, long long total) {
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+        const long long q = i % quads_per_row;
+        const long long rb = i / quads_per_row;           // row index over all batches
+        const long long r = rb % p.rows;
+        const int batch = (int)(rb / p.rows);
+        const int bo = batch / p.batch_inner, bi = batch - bo * p.batch_inner;
+        const float* src = p.src + bo * p.stride_outer + bi * p.stride_inner + r * p.ld + 4 * q;
+        float4 x;
+        if (4 * q + 4 <= p.K) {
+            x = *reinterpret_cast<const float4*>(src);
+        } else {
+            x.x = 4 * q + 0 < p.K ? src[0] : 0.0f;
+            x.y = 4 * q + 1 < p.K ? src[1] : 0.0f;
+            x.z = 4 * q + 2 < p.K ? src[2] : 0.0f;
+            x.w = 0.0f;
+        }
+        const long long o = rb * p.kp + 4 * q;
+        if (SPLIT) {
+            float4 hi, lo;
+            hi.x = to_tf32_rn(x.x); hi.y = to_tf32_rn(x.y); hi.z = to_tf32_rn(x.z); hi.w = to_tf32_rn(x.w);
+            lo.x = to_tf32_rn(x.x - hi.x); lo.y = to_tf32_rn(x.y - hi.y); lo.z = to_tf32_rn(x.z - hi.z); lo.w = to_tf32_rn(x.w - hi.w);
+            *reinterpret_cast<float4*>(p.dst_hi + o) = hi;
+            *reinterpret_cast<float4*>(p.dst_lo + o) = lo;
+        } else {
+            *reinterpret_cast<float4*>(p.dst_hi + o) = x;
+        }
+    }
+}
+
 int launch_pack(te_b200_ctx* ctx, const Operand& src, int64_t K, int64_t batch_inner, int64_t batch_outer,
                 float* dst_hi, float* dst_lo, bool split, cudaStream_t stream) {
     // Broadcast levels are packed once.
@@ -83,6 +116,19 @@ int launch_pack(te_b200_ctx* ctx, const Operand& src, int64_t K, int64_t batch_i
     if (nb > 65535 || (src.rows + 31) / 32 > 65535) {
         set_error("pack: operand has more than 65535 batches or row blocks");
         return TE_ERR_BAD_ARGUMENT;
+    }
+    const bool rows_aligned = !src.mn_major && (reinterpret_cast<uintptr_t>(src.ptr) & 15) == 0 && (src.ld & 3) == 0 &&
+                              (bi == 1 || (src.stride_inner & 3) == 0) && (bo == 1 || (src.stride_outer & 3) == 0);
+    if (rows_aligned) {
+        const long long quads = p.kp / 4, total = quads * src.rows * nb;
+        long long blocks = (total + 255) / 256;
+        if (blocks > (long long)ctx->sm_count * 32) blocks = (long long)ctx->sm_count * 32;
+        if (split) pack_rows_vec4_kernel<true><<<(unsigned)blocks, 256, 0, stream>>>(p, quads, total);
+        else pack_rows_vec4_kernel<false><<<(unsigned)blocks, 256, 0, stream>>>(p, quads, total);
+        cudaError_t ev = cudaGetLastError();
+        if (ev != cudaSuccess) return cuda_fail(ev, "pack_rows_vec4_kernel launch");
+        ctx->launches += 1;
+        return TE_OK;
     }
     dim3 grid((unsigned)((p.kp + 31) / 32), (unsigned)((src.rows + 31) / 32), (unsigned)nb);
     dim3 block(32, 8);
