@@ -24,7 +24,7 @@ def backend():
     import torch
     from torch_engine_b200 import ops
     assert torch.cuda.is_available(), "GPU test run without a GPU"
-    be = ops.Backend(0, workspace_bytes=3 << 30)
+    be = ops.Backend(0, workspace_bytes=5 << 30)   # 16384^3 in 3xTF32 mode packs 4 GiB of planes
     yield be
     be.check_device_status()
     be.close()

@@ -238,6 +238,28 @@ def test_large_squares_sampled_rows(backend, oracle, n, rows, prec):
     assert rel_err(c2.cpu().numpy(), c.cpu().numpy()) <= 2 * TOL_REL[prec]
 
 
+def test_largest_sweep_square_16384(backend, oracle):
+    """16384^3 (1 GiB per operand): sampled rows against the float64 oracle in both modes, and two size-independent
+    properties: scaling A by a power of two scales C exactly, and the N-column-sharded evaluation (what each GPU of a
+    multi-GPU run computes) reproduces the unsharded columns bit for bit."""
+    n = 16384
+    g = torch.Generator(device="cuda").manual_seed(42)
+    a = torch.rand(n, n, device="cuda", generator=g) * 2 - 1
+    b = torch.rand(n, n, device="cuda", generator=g) * 2 - 1
+    pick = np.linspace(0, n - 1, 6).astype(int)
+    ref = oracle.matmul_f64(a[pick].cpu().numpy(), b.cpu().numpy())
+    c = backend.matmul(a, b, precision="tf32")
+    assert_close(c[pick].cpu().numpy(), ref, "tf32", "16384^3 tf32")
+    c4 = backend.matmul(a * 4.0, b, precision="tf32")
+    assert torch.equal(c4[pick], c[pick] * 4.0), "power-of-two scaling must be exact"
+    shard = backend.matmul(a, b[:, 4096:8192], precision="tf32")
+    assert torch.equal(shard, c[:, 4096:8192]), "column shard differs from the unsharded product"
+    del c4, shard
+    c3 = backend.matmul(a, b, precision="3xtf32")
+    assert_close(c3[pick].cpu().numpy(), ref, "3xtf32", "16384^3 3xtf32")
+    backend.check_device_status()
+
+
 @pytest.mark.parametrize("shape", [(8192, 512, 8192), (8192, 8192, 512), (16, 8192, 8192)])
 def test_skinny_sweep_shapes(backend, oracle, shape):
     M, K, N = shape
