@@ -163,6 +163,29 @@ def main():
         record("b200_linear_bias_gelu_fwd", mode, 4096, 768, 3072, 1, tb, tm, cub)
         tb, tm = time_gpu(lambda: be.linear_backward(x, w, dy, precision=mode), 50)
         record("b200_linear_bwd_dx_dw_db", mode, 4096, 3072, 768, 2, tb, tm, None)
+    # ---- HBM-bound helpers around the GEMMs: softmax rows, GELU, bias-gradient column sum, 3xTF32 packing ----
+    def record_stream(name, byts, tb, tm, shape):
+        r = {"kernel_name": name, "dtype": "float32", "mode": "-", "shape": shape, "time_ms": tm, "time_ms_best": tb,
+             "bandwidth_gb_s": byts / (tm * 1e-3) / 1e9, "pct_of_hbm_peak": 100.0 * byts / (tm * 1e-3) / 1e9 / hbm_peak,
+             "peak_source": peak_src, "gpus": 1, "gpu_name": gpu_name}
+        results.append(r)
+        print("%-28s %-24s %9.3f ms %8.1f GB/s  %5.1f%% of HBM peak" % (name, shape, tm, r["bandwidth_gb_s"], r["pct_of_hbm_peak"]), flush=True)
+
+    s_in = torch.randn(32 * 12 * 256, 256, device="cuda", generator=gen)          # 100.7 MB, larger than... read + write
+    tb, tm = time_gpu(lambda: be.softmax(s_in), 20)
+    record_stream("b200_softmax_rows", 2 * 4.0 * s_in.numel(), tb, tm, "98304x256")
+    dy_s = torch.randn_like(s_in)
+    p_s = be.softmax(s_in)
+    tb, tm = time_gpu(lambda: be.softmax_backward(p_s, dy_s), 20)
+    record_stream("b200_softmax_backward_rows", 3 * 4.0 * s_in.numel(), tb, tm, "98304x256")
+    act = torch.randn(16384, 3072, device="cuda", generator=gen)                   # 201 MB
+    tb, tm = time_gpu(lambda: be.gelu(act), 20)
+    record_stream("b200_gelu", 2 * 4.0 * act.numel(), tb, tm, "16384x3072")
+    dact = torch.randn_like(act)
+    tb, tm = time_gpu(lambda: be.gelu_backward(act, dact), 20)
+    record_stream("b200_gelu_backward", 3 * 4.0 * act.numel(), tb, tm, "16384x3072")
+    tb, tm = time_gpu(lambda: be.colsum(act), 20)
+    record_stream("b200_colsum", 4.0 * act.numel(), tb, tm, "16384x3072")
     be.check_device_status()
     os.makedirs(os.path.dirname(args.out), exist_ok=True)
     with open(args.out, "w") as f:

@@ -72,6 +72,40 @@ __global__ void __launch_bounds__(256) softmax_rows_kernel(const float* in, floa
     }
 }
 
+// Same softmax for rows of V4 * 128 floats that start on 16-byte boundaries: every lane moves whole float4s, which
+// keeps four times as many bytes in flight per instruction as the scalar form.
+template <int V4>
+__global__ void __launch_bounds__(256) softmax_rows_vec4_kernel(const float* in, float* out, long long rows) {
+    constexpr int cols = V4 * 128;
+    const int lane = threadIdx.x & 31;
+    const long long warps_per_grid = (long long)gridDim.x * (blockDim.x >> 5);
+    for (long long row = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); row < rows;
+         row += warps_per_grid) {
+        const float4* x = reinterpret_cast<const float4*>(in + row * cols);
+        float4* y = reinterpret_cast<float4*>(out + row * cols);
+        float4 v[V4];
+        float m = -__int_as_float(0x7f800000);
+#pragma unroll
+        for (int i = 0; i < V4; ++i) {
+            v[i] = x[lane + 32 * i];
+            m = fmaxf(m, fmaxf(fmaxf(v[i].x, v[i].y), fmaxf(v[i].z, v[i].w)));
+        }
+        m = warp_max(m);
+        float s = 0.0f;
+#pragma unroll
+        for (int i = 0; i < V4; ++i) {
+            v[i].x = expf(v[i].x - m); v[i].y = expf(v[i].y - m); v[i].z = expf(v[i].z - m); v[i].w = expf(v[i].w - m);
+            s += (v[i].x + v[i].y) + (v[i].z + v[i].w);
+        }
+        s = warp_sum(s);
+#pragma unroll
+        for (int i = 0; i < V4; ++i) {
+            v[i].x = v[i].x / s; v[i].y = v[i].y / s; v[i].z = v[i].z / s; v[i].w = v[i].w / s;
+            y[lane + 32 * i] = v[i];
+        }
+    }
+}
+
 // dx = s * (dy - <dy, s>) per row (reference src/cuda/elementwise_cuda.cu:2450-2467).
 __global__ void __launch_bounds__(256) softmax_backward_rows_kernel(const float* __restrict__ s,
                                                                     const float* __restrict__ dy,
@@ -134,6 +168,35 @@ __global__ void __launch_bounds__(1024) colsum_kernel(const float* __restrict__ 
     if (ty == 0 && col < cols) out[col] = part[0][tx];
 }
 
+// Two-phase form for tall inputs: slab s of the rows is summed into partial[s][col] (same thread layout as above),
+// then the slabs are added in order.  Deterministic, and enough blocks to pull the full HBM bandwidth.
+__global__ void __launch_bounds__(1024) colsum_slab_kernel(const float* __restrict__ in, long long rows, long long cols,
+                                                           long long ld, long long rows_per_slab, float* __restrict__ partial) {
+    __shared__ float part[32][33];
+    const int tx = threadIdx.x, ty = threadIdx.y;
+    const long long col = (long long)blockIdx.x * 32 + tx;
+    const long long r0 = (long long)blockIdx.y * rows_per_slab;
+    const long long r1 = r0 + rows_per_slab < rows ? r0 + rows_per_slab : rows;
+    float acc = 0.0f;
+    if (col < cols)
+        for (long long r = r0 + ty; r < r1; r += 32) acc += in[r * ld + col];
+    part[ty][tx] = acc;
+    __syncthreads();
+    for (int h = 16; h > 0; h >>= 1) {
+        if (ty < h) part[ty][tx] += part[ty + h][tx];
+        __syncthreads();
+    }
+    if (ty == 0 && col < cols) partial[(long long)blockIdx.y * cols + col] = part[0][tx];
+}
+__global__ void __launch_bounds__(256) colsum_finish_kernel(const float* __restrict__ partial, int slabs, long long cols,
+                                                            float* __restrict__ out) {
+    const long long col = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (col >= cols) return;
+    float acc = 0.0f;
+    for (int s = 0; s < slabs; ++s) acc += partial[(long long)s * cols + col];
+    out[col] = acc;
+}
+
 static int grid_for(long long work_items, int per_block, int sm_count) {
     long long blocks = (work_items + per_block - 1) / per_block;
     const long long cap = (long long)sm_count * 8;
@@ -146,7 +209,13 @@ int launch_softmax_rows(te_b200_ctx* ctx, const float* in, float* out, int64_t r
     if (rows == 0 || cols == 0) return TE_OK;
     const int grid = grid_for(rows, 8, ctx->sm_count);
     const int c = (int)cols;
-    if (cols <= 32) softmax_rows_kernel<1><<<grid, 256, 0, st>>>(in, out, rows, c);
+    const bool aligned = ((reinterpret_cast<uintptr_t>(in) | reinterpret_cast<uintptr_t>(out)) & 15) == 0;
+    if (aligned && (cols == 128 || cols == 256 || cols == 512 || cols == 1024)) {
+        if (cols == 128) softmax_rows_vec4_kernel<1><<<grid, 256, 0, st>>>(in, out, rows);
+        else if (cols == 256) softmax_rows_vec4_kernel<2><<<grid, 256, 0, st>>>(in, out, rows);
+        else if (cols == 512) softmax_rows_vec4_kernel<4><<<grid, 256, 0, st>>>(in, out, rows);
+        else softmax_rows_vec4_kernel<8><<<grid, 256, 0, st>>>(in, out, rows);
+    } else if (cols <= 32) softmax_rows_kernel<1><<<grid, 256, 0, st>>>(in, out, rows, c);
     else if (cols <= 64) softmax_rows_kernel<2><<<grid, 256, 0, st>>>(in, out, rows, c);
     else if (cols <= 128) softmax_rows_kernel<4><<<grid, 256, 0, st>>>(in, out, rows, c);
     else if (cols <= 256) softmax_rows_kernel<8><<<grid, 256, 0, st>>>(in, out, rows, c);
@@ -191,7 +260,22 @@ int launch_colsum(te_b200_ctx* ctx, const float* in, int64_t rows, int64_t cols,
                   cudaStream_t st) {
     if (cols == 0) return TE_OK;
     dim3 block(32, 32);
-    colsum_kernel<<<(unsigned)((cols + 31) / 32), block, 0, st>>>(in, rows, cols, ld, out);
+    const long long col_blocks = (cols + 31) / 32;
+    // enough (column block, row slab) pairs for ~4 blocks per SM, at least 256 rows per slab
+    long long slabs = ((long long)ctx->sm_count * 4 + col_blocks - 1) / col_blocks;
+    if (slabs > rows / 256) slabs = rows / 256;
+    if (slabs > 1 && (size_t)(slabs * cols * 4) <= ctx->workspace_bytes) {
+        const long long rows_per_slab = (rows + slabs - 1) / slabs;
+        slabs = (rows + rows_per_slab - 1) / rows_per_slab;
+        float* partial = static_cast<float*>(ctx->workspace);
+        colsum_slab_kernel<<<dim3((unsigned)col_blocks, (unsigned)slabs), block, 0, st>>>(in, rows, cols, ld, rows_per_slab, partial);
+        colsum_finish_kernel<<<(unsigned)((cols + 255) / 256), 256, 0, st>>>(partial, (int)slabs, cols, out);
+        cudaError_t e2 = cudaGetLastError();
+        if (e2 != cudaSuccess) return cuda_fail(e2, "colsum_slab_kernel launch");
+        ctx->launches += 2;
+        return TE_OK;
+    }
+    colsum_kernel<<<(unsigned)col_blocks, block, 0, st>>>(in, rows, cols, ld, out);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return cuda_fail(e, "colsum_kernel launch");
     ctx->launches += 1;
