@@ -173,9 +173,10 @@ __device__ __forceinline__ void epilogue_store32(float* v, int col0, const Epilo
         else if (p.scale_mode == TE_SCALE_DIV) v[j] = v[j] / p.alpha;
     }
     if (p.bias) {
+        // every thread of the warp needs the same 32 bias values: one coalesced load, then register shuffles
+        const float mine = (col0 + lane < p.N) ? __ldg(p.bias + col0 + lane) : 0.0f;
 #pragma unroll
-        for (int j = 0; j < 32; ++j)
-            if (col0 + j < p.N) v[j] += __ldg(p.bias + col0 + j);
+        for (int j = 0; j < 32; ++j) v[j] += __shfl_sync(0xffffffffu, mine, j);
     }
     if (er.tma_ok) {   // warp-uniform
         if (er.row0 >= p.M) return;   // nothing of this warp's 32 rows exists: issue no store at all
