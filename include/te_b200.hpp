@@ -14,6 +14,7 @@
 #include <cuda_runtime.h>
 
 #include <cmath>
+#include <cstdlib>
 #include <cstdint>
 #include <memory>
 #include <stdexcept>
@@ -157,6 +158,35 @@ private:
     std::shared_ptr<void> storage_;
     std::vector<int64_t> shape_, strides_;
     int64_t offset_ = 0;
+};
+
+// MatMulBackward::backward (reference src/core/grad_fn.cpp:126-139): for C = A.matmul(B) and upstream gradient dC,
+//   dA = dC . B^T,  dB = A^T . dC   (both through transpose_view, no copies),
+// each summed over the batch dimensions the operand was broadcast along (reduce_gradient, grad_fn.cpp:13-58).
+struct MatMulBackward {
+    Tensor a, b;   // the inputs of the forward call, held by value like GradFn::inputs
+    std::vector<Tensor> backward(const Tensor& dC) const {
+        const size_t na = a.shape().size(), nb = b.shape().size();
+        Tensor dA = dC.matmul(b.transpose_view(nb - 2, nb - 1));
+        Tensor dB = a.transpose_view(na - 2, na - 1).matmul(dC);
+        return {reduce_to(dA, a.shape()), reduce_to(dB, b.shape())};
+    }
+private:
+    // Sums the leading (broadcast) batch dimensions of `g` away so that it has `shape`.  Supports the cases the
+    // reference's callers produce: the operand had no batch dimensions, or all-ones batch dimensions.
+    static Tensor reduce_to(const Tensor& g, const std::vector<int64_t>& shape) {
+        if (g.shape() == shape) return g;
+        size_t target = 1;
+        for (int64_t d : shape) target *= (size_t)d;
+        if (target == 0 || g.numel() % target != 0) throw std::runtime_error("reduce_gradient: shapes are not broadcast-compatible");
+        const int64_t lead = (int64_t)(g.numel() / target);
+        for (size_t i = 0; i + 2 < shape.size(); ++i)
+            if (shape[i] != 1) throw std::runtime_error("reduce_gradient: only leading broadcast dimensions are supported");
+        Tensor out(shape);
+        // g is contiguous [lead, target]: the batch sum is a column sum over `lead` rows
+        check(te_b200_colsum_f32(Backend::instance().ctx(), g.data(), lead, (int64_t)target, (int64_t)target, out.data(), nullptr));
+        return out;
+    }
 };
 
 // Linear::forward with the bias add (and optionally FeedForward's GELU) fused into the GEMM epilogue.

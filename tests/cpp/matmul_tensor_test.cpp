@@ -70,6 +70,21 @@ int main() {
                      "Batch dimensions are not broadcastable");
         expect_throw("1-D operand", [&] { Tensor({3}).matmul(Tensor({3, 2})); },
                      "Matmul requires tensors with at least 2 dimensions");
+        // MatMulBackward with a broadcast weight: A [2,2,3] . B [3,2], dC = ones -> dA rows = row sums of B,
+        // dB = sum over both batches of A^T . ones (the reference reduces the [2,3,2] product over its batch dim)
+        {
+            Tensor A3 = Tensor::from_host(iota(12), {2, 2, 3});
+            Tensor B2 = Tensor::from_host({1, 2, 3, 4, 5, 6}, {3, 2});
+            Tensor dC = Tensor::from_host(std::vector<float>(8, 1.0f), {2, 2, 2});
+            te::MatMulBackward node{A3, B2};
+            std::vector<Tensor> g = node.backward(dC);
+            expect_values("MatMulBackward dA", g[0], {3, 7, 11, 3, 7, 11, 3, 7, 11, 3, 7, 11}, 1e-5f);
+            // column sums of A over all 4 rows: (1+4+7+10, 2+5+8+11, 3+6+9+12) = (22, 26, 30), repeated for both columns
+            expect_values("MatMulBackward dB (reduced over the broadcast batch)", g[1], {22, 22, 26, 26, 30, 30}, 1e-4f);
+            const bool shapes_ok = g[0].shape() == A3.shape() && g[1].shape() == B2.shape();
+            std::cout << (shapes_ok ? "ok   " : "FAIL ") << "MatMulBackward gradient shapes\n";
+            if (!shapes_ok) ++failures;
+        }
         // Linear: y = x.W^T + b with W [out,in]
         te::Linear lin(3, 2);
         lin.weight() = Tensor::from_host({1, 0, -1, 2, 1, 0}, {2, 3});
