@@ -43,6 +43,7 @@ struct AttnParams {
     int T, d, H, B;
     int t_pad;        // T rounded up to 16: N of the score MMA, K extent of the PV MMA
     int tiles_q;      // 128-row query blocks per head
+    int total_tiles;  // B * H * tiles_q
     float scale;      // sqrt(d)
     int* status;
 };
@@ -61,22 +62,22 @@ attention_tf32_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
     const uint32_t stage_smem = v_smem + dchunks * (ATT_MAX_T * 128);     // 2 staging tiles per softmax warp
     const uint32_t aux_addr = stage_smem + 2 * ATT_EPI_WARPS * EPI_STAGE_BYTES;
     uint8_t* aux = smem_raw + (aux_addr - raw_addr);
-    const uint32_t bar_qk = aux_addr, bar_v = aux_addr + 8, bar_s = aux_addr + 16, bar_p = aux_addr + 24,
-                   bar_o = aux_addr + 32;
-    const uint32_t bar_x1 = aux_addr + 56, bar_x2 = aux_addr + 64;
-    // The exchange arrays reuse the Q block's shared memory: Q is dead once the score MMAs have completed, and the
-    // softmax warps touch these arrays only after waiting for exactly that.
-    float* red_max = reinterpret_cast<float*>(smem_raw + (q_smem - raw_addr));          // [2 halves][128 rows]
-    float* red_sum = red_max + 256;                                                    // [2 halves][128 rows]
+    // One barrier per hand-off; tile i of this CTA completes phase i of each, so waits use parity i & 1.
+    const uint32_t bar_qk = aux_addr;          // Q and K of the tile have landed            (producer -> MMA)
+    const uint32_t bar_v = aux_addr + 8;       // V has landed                               (producer -> MMA)
+    const uint32_t bar_s = aux_addr + 16;      // score MMAs done: S readable, Q/K buffers reusable (MMA -> softmax, producer)
+    const uint32_t bar_p = aux_addr + 24;      // exponentials are in TMEM                   (8 softmax warps -> MMA)
+    const uint32_t bar_o = aux_addr + 32;      // PV MMAs done: O readable, V buffer reusable (MMA -> softmax, producer)
+    const uint32_t bar_td = aux_addr + 48;     // teardown
+    const uint32_t bar_x1 = aux_addr + 56;     // row maxima of both column halves written   (8 softmax warps)
+    const uint32_t bar_x2 = aux_addr + 64;     // row sums written                           (8 softmax warps)
+    const uint32_t bar_sfree = aux_addr + 72;  // S columns no longer read                   (8 softmax warps -> MMA)
+    const uint32_t bar_ofree = aux_addr + 80;  // O columns no longer read                   (8 softmax warps -> MMA)
     const uint32_t tmem_slot_addr = aux_addr + 40;
     volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(aux + 40);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(aux + 44);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int qb = blockIdx.x % p.tiles_q;
-    const int bh = blockIdx.x / p.tiles_q;
-    const int h = bh % p.H, b = bh / p.H;
-    const int q0 = qb * 128;
 
     if (threadIdx.x == 0) {
         mbar_init(bar_qk, 1);
@@ -84,9 +85,11 @@ attention_tf32_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
         mbar_init(bar_s, 1);
         mbar_init(bar_p, ATT_EPI_WARPS);
         mbar_init(bar_o, 1);
-        mbar_init(aux_addr + 48, 1);   // teardown: all MMAs of this CTA done
-        mbar_init(bar_x1, ATT_EPI_WARPS);   // row maxima of both column halves exchanged
-        mbar_init(bar_x2, ATT_EPI_WARPS);   // row sums exchanged
+        mbar_init(bar_td, 1);
+        mbar_init(bar_x1, ATT_EPI_WARPS);
+        mbar_init(bar_x2, ATT_EPI_WARPS);
+        mbar_init(bar_sfree, ATT_EPI_WARPS);
+        mbar_init(bar_ofree, ATT_EPI_WARPS);
         *abort_flag = 0;
         fence_barrier_init();
         fence_proxy_async_smem();
@@ -100,27 +103,42 @@ attention_tf32_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
     tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
 
+    // Persistent: this CTA handles tiles blockIdx.x, blockIdx.x + gridDim.x, ...  While the softmax of tile i runs,
+    // the producer already fetches Q and K of tile i+1 (their buffers are free once the score MMAs are done).
     if (warp == PRODUCER_WARP) {
         if (lane == 0) {
             tma_prefetch_desc(&tm_q);
             tma_prefetch_desc(&tm_k);
             tma_prefetch_desc(&tm_v);
-            mbar_arrive_expect_tx(bar_qk, dchunks * (128 * 128 + ATT_MAX_T * 128));
-            for (int c = 0; c < dchunks; ++c) {
-                tma_load_4d(q_smem + c * (128 * 128), &tm_q, bar_qk, 32 * c, q0, h, b);
-                tma_load_4d(k_smem + c * (ATT_MAX_T * 128), &tm_k, bar_qk, 32 * c, 0, h, b);
+            int i = 0;
+            for (int t = blockIdx.x; t < p.total_tiles; t += gridDim.x, ++i) {
+                const int qb = t % p.tiles_q, bh = t / p.tiles_q;
+                const int h = bh % p.H, b = bh / p.H, q0 = qb * 128;
+                if (i > 0 && !wait_bounded(bar_s, (i - 1) & 1, abort_flag, p.status, WAIT_PRODUCER_EMPTY)) break;
+                mbar_arrive_expect_tx(bar_qk, dchunks * (128 * 128 + ATT_MAX_T * 128));
+                for (int c = 0; c < dchunks; ++c) {
+                    tma_load_4d(q_smem + c * (128 * 128), &tm_q, bar_qk, 32 * c, q0, h, b);
+                    tma_load_4d(k_smem + c * (ATT_MAX_T * 128), &tm_k, bar_qk, 32 * c, 0, h, b);
+                }
+                if (i > 0 && !wait_bounded(bar_o, (i - 1) & 1, abort_flag, p.status, WAIT_PRODUCER_EMPTY)) break;
+                mbar_arrive_expect_tx(bar_v, dchunks * (ATT_MAX_T * 128));
+                for (int c = 0; c < dchunks; ++c)
+                    for (int kb = 0; kb < ATT_MAX_T / 32; ++kb)
+                        tma_load_4d(v_smem + c * (ATT_MAX_T * 128) + kb * (32 * 128), &tm_v, bar_v, 32 * c, 32 * kb, h, b);
             }
-            mbar_arrive_expect_tx(bar_v, dchunks * (ATT_MAX_T * 128));
-            for (int c = 0; c < dchunks; ++c)
-                for (int kb = 0; kb < ATT_MAX_T / 32; ++kb)
-                    tma_load_4d(v_smem + c * (ATT_MAX_T * 128) + kb * (32 * 128), &tm_v, bar_v, 32 * c, 32 * kb, h, b);
         }
     } else if (warp == MMA_WARP) {
         if (lane == 0) {
-            bool ok = wait_bounded(bar_qk, 0, abort_flag, p.status, WAIT_MMA_FULL);
-            if (ok) {
+            const uint32_t idesc_s = make_idesc_tf32(128, p.t_pad, false, false);
+            const uint32_t idesc_o = make_idesc_tf32(128, p.d, false, true);
+            int i = 0;
+            for (int t = blockIdx.x; t < p.total_tiles; t += gridDim.x, ++i) {
+                const uint32_t par = i & 1, prev = (i - 1) & 1;
+                // S columns: the previous tile's PV MMAs (which read them) and its probability pass must be over
+                if (i > 0 && !(wait_bounded(bar_o, prev, abort_flag, p.status, WAIT_MMA_TMEM_EMPTY) &&
+                               wait_bounded(bar_sfree, prev, abort_flag, p.status, WAIT_MMA_TMEM_EMPTY))) break;
+                if (!wait_bounded(bar_qk, par, abort_flag, p.status, WAIT_MMA_FULL)) break;
                 tc_fence_after_sync();
-                const uint32_t idesc_s = make_idesc_tf32(128, p.t_pad, false, false);
                 for (int c = 0; c < dchunks; ++c) {
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
@@ -130,37 +148,41 @@ attention_tf32_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
                     }
                 }
                 umma_commit(bar_s);
-                ok = wait_bounded(bar_p, 0, abort_flag, p.status, WAIT_MMA_TMEM_EMPTY) &&
-                     wait_bounded(bar_v, 0, abort_flag, p.status, WAIT_MMA_FULL);
-            }
-            if (ok) {
+                if (!(wait_bounded(bar_p, par, abort_flag, p.status, WAIT_MMA_TMEM_EMPTY) &&
+                      wait_bounded(bar_v, par, abort_flag, p.status, WAIT_MMA_FULL))) break;
+                // O columns: the previous tile's output must have been read out
+                if (i > 0 && !wait_bounded(bar_ofree, prev, abort_flag, p.status, WAIT_MMA_TMEM_EMPTY)) break;
                 tc_fence_after_sync();
-                const uint32_t idesc_o = make_idesc_tf32(128, p.d, false, true);
                 for (int kk = 0; kk < p.t_pad / 8; ++kk) {
                     const uint64_t dv = make_smem_desc(v_smem + kk * 1024, ATT_MAX_T * 128, 512, SMEM_LAYOUT_SW128_BASE32B);
                     umma_tf32_a_tmem(tmem_base + ATT_O_COL, tmem_base + kk * 8, dv, idesc_o, kk != 0);
                 }
                 umma_commit(bar_o);
             }
-            // nothing of this thread's MMAs may be in flight when TMEM is freed
-            umma_commit(aux_addr + 48);
+            umma_commit(bar_td);   // nothing of this thread's MMAs may be in flight when TMEM is freed
         }
     } else {
         // ---------------------------------------------------------------- softmax + output (warps 0-7)
         const int quad = warp & 3, half = warp >> 2;
-        const int rloc = quad * 32 + lane;                         // row inside the 128-row block = TMEM lane
         const uint32_t t_row = tmem_base + (uint32_t(quad * 32) << 16);
-        bool ok = wait_bounded(bar_s, 0, abort_flag, p.status, WAIT_EPI_TMEM_FULL);
-        ok = __all_sync(0xffffffffu, ok);
-        if (ok) {
+        const uint32_t x_col = t_row + ATT_O_COL + 64;             // 4 spare columns: max[half 0,1], sum[half 0,1]
+        const int nchunks = (p.t_pad + 31) / 32;
+        const int c_begin = half ? (nchunks + 1) / 2 : 0;          // this warp's share of the 32-column chunks
+        const int c_end = half ? nchunks : (nchunks + 1) / 2;
+        // Scores are scaled by multiplying with 1/sqrt(d) and exponentiated with the ex2 unit: this kernel runs in
+        // TF32 mode only, where the scores carry ~1e-3 relative error already, and the per-element cost of the
+        // softmax is on the critical path of the CTA.
+        const float k2 = (1.0f / p.scale) * 1.4426950408889634f;   // log2(e) / sqrt(d)
+        int stores = 0;   // staging tiles alternate over ALL stores of this warp
+        int i = 0;
+        for (int t = blockIdx.x; t < p.total_tiles; t += gridDim.x, ++i) {
+            const uint32_t par = i & 1;
+            const int qb = t % p.tiles_q, bh = t / p.tiles_q;
+            const int h = bh % p.H, b = bh / p.H, q0 = qb * 128;
+            bool ok = wait_bounded(bar_s, par, abort_flag, p.status, WAIT_EPI_TMEM_FULL);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
             tc_fence_after_sync();
-            const int nchunks = (p.t_pad + 31) / 32;
-            const int c_begin = half ? (nchunks + 1) / 2 : 0;      // this warp's share of the 32-column chunks
-            const int c_end = half ? nchunks : (nchunks + 1) / 2;
-            // Scores are scaled by multiplying with 1/sqrt(d) and exponentiated with the ex2 unit: this kernel runs in
-            // TF32 mode only, where the scores carry ~1e-3 relative error already, and the per-element cost of the
-            // softmax is the critical path of the CTA.
-            const float k2 = (1.0f / p.scale) * 1.4426950408889634f;     // log2(e) / sqrt(d)
             // pass 1: row maximum of the raw scores (the scale is positive, so the maximum commutes with it)
             float m = -INFINITY;
             for (int cc = c_begin; cc < c_end; ++cc) {
@@ -176,18 +198,18 @@ attention_tf32_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
                         if (cc * 32 + j < p.T) m = fmaxf(m, __uint_as_float(r[j]));
                 }
             }
-            red_max[half * 128 + rloc] = m;
+            // The two warps of a row group own the same TMEM lanes: they exchange through two spare columns.
+            tmem_st_32x32b_x1(x_col + half, __float_as_uint(m));
+            tmem_st_wait();
+            tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) mbar_arrive(bar_x1);
-            ok = wait_bounded(bar_x1, 0, abort_flag, p.status, WAIT_EPI_TMEM_FULL);
+            ok = wait_bounded(bar_x1, par, abort_flag, p.status, WAIT_EPI_TMEM_FULL);
             ok = __all_sync(0xffffffffu, ok);
-        }
-        if (ok) {
-            const int nchunks = (p.t_pad + 31) / 32;
-            const int c_begin = half ? (nchunks + 1) / 2 : 0;
-            const int c_end = half ? nchunks : (nchunks + 1) / 2;
-            const float k2 = (1.0f / p.scale) * 1.4426950408889634f;
-            const float m = fmaxf(red_max[rloc], red_max[128 + rloc]);
+            if (!ok) break;
+            tc_fence_after_sync();
+            m = fmaxf(m, __uint_as_float(tmem_ld_32x32b_x1(x_col + (half ^ 1))));
+            tmem_ld_wait();
             const float mk = m * k2;
             // pass 2: e = exp(s - m), row sum; e goes back to TMEM as the A operand of P.V
             float sum = 0.0f;
@@ -215,53 +237,61 @@ attention_tf32_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
                 }
                 tmem_st_32x32b_x32(t_row + cc * 32, r);
             }
+            tmem_st_32x32b_x1(x_col + 2 + half, __float_as_uint(sum));
             tmem_st_wait();
             tc_fence_before_sync();
-            red_sum[half * 128 + rloc] = sum;
             __syncwarp();
             if (lane == 0) {
                 mbar_arrive(bar_p);      // this warp's part of the PV operand is in place
                 mbar_arrive(bar_x2);
             }
-            ok = wait_bounded(bar_x2, 0, abort_flag, p.status, WAIT_EPI_TMEM_FULL);
+            ok = wait_bounded(bar_x2, par, abort_flag, p.status, WAIT_EPI_TMEM_FULL);
             ok = __all_sync(0xffffffffu, ok);
-            if (ok) {
-                const float inv_sum = 1.0f / (red_sum[rloc] + red_sum[128 + rloc]);
-                EpilogueRow er;
-                er.c_row = nullptr; er.pre_row = nullptr; er.row_ok = true; er.vec_ok = false; er.tma_ok = true;
-                er.stage = stage_smem + warp * 2 * EPI_STAGE_BYTES;
-                er.tm_c = &tm_p; er.tm_pre = &tm_p;
-                er.row0 = q0 + quad * 32;
-                er.bi = h; er.bo = b;
-                int stores = 0;   // staging tiles alternate over ALL stores of this warp, P and O alike
-                // pass 3: P = e / sum, written out once (while the tensor core computes P.V from the same columns)
+            if (!ok) break;
+            tc_fence_after_sync();
+            sum += __uint_as_float(tmem_ld_32x32b_x1(x_col + 2 + (half ^ 1)));
+            tmem_ld_wait();
+            const float inv_sum = 1.0f / sum;
+            EpilogueRow er;
+            er.c_row = nullptr; er.pre_row = nullptr; er.row_ok = true; er.vec_ok = false; er.tma_ok = true;
+            er.stage = stage_smem + warp * 2 * EPI_STAGE_BYTES;
+            er.tm_c = &tm_p; er.tm_pre = &tm_p;
+            er.row0 = q0 + quad * 32;
+            er.bi = h; er.bo = b;
+            // pass 3: P = e / sum, written out once (while the tensor core computes P.V from the same columns)
+            for (int cc = c_begin; cc < c_end && cc * 32 < p.T; ++cc) {
+                uint32_t r[32];
+                tmem_ld_32x32b_x32(t_row + cc * 32, r);
+                tmem_ld_wait();
                 if (er.row0 < p.T) {
-                    for (int cc = c_begin; cc < c_end && cc * 32 < p.T; ++cc) {
-                        uint32_t r[32];
-                        tmem_ld_32x32b_x32(t_row + cc * 32, r);
-                        tmem_ld_wait();
-                        float v[32];
+                    float v[32];
 #pragma unroll
-                        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * inv_sum;
-                        stage_and_store32(v, cc * 32, er, &tm_p, lane, true, (stores++) & 1);
-                    }
-                }
-                ok = wait_bounded(bar_o, 0, abort_flag, p.status, WAIT_EPI_TMEM_FULL);
-                ok = __all_sync(0xffffffffu, ok);
-                if (ok && er.row0 < p.T) {
-                    tc_fence_after_sync();
-                    const int o_begin = half ? (dchunks + 1) / 2 : 0, o_end = half ? dchunks : (dchunks + 1) / 2;
-                    for (int cc = o_begin; cc < o_end; ++cc) {
-                        uint32_t r[32];
-                        tmem_ld_32x32b_x32(t_row + ATT_O_COL + cc * 32, r);
-                        tmem_ld_wait();
-                        float v[32];
-#pragma unroll
-                        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * inv_sum;
-                        stage_and_store32(v, cc * 32, er, &tm_o, lane, true, (stores++) & 1);
-                    }
+                    for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * inv_sum;
+                    stage_and_store32(v, cc * 32, er, &tm_p, lane, true, (stores++) & 1);
                 }
             }
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_sfree);     // the S columns may be overwritten by the next tile's scores
+            ok = wait_bounded(bar_o, par, abort_flag, p.status, WAIT_EPI_TMEM_FULL);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            tc_fence_after_sync();
+            const int o_begin = half ? (dchunks + 1) / 2 : 0, o_end = half ? dchunks : (dchunks + 1) / 2;
+            for (int cc = o_begin; cc < o_end; ++cc) {
+                uint32_t r[32];
+                tmem_ld_32x32b_x32(t_row + ATT_O_COL + cc * 32, r);
+                tmem_ld_wait();
+                if (er.row0 < p.T) {
+                    float v[32];
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * inv_sum;
+                    stage_and_store32(v, cc * 32, er, &tm_o, lane, true, (stores++) & 1);
+                }
+            }
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_ofree);     // the O columns may be overwritten by the next tile's P.V
         }
         if (lane == 0) bulk_wait_read_all();   // shared memory may go away once the stores have read it
     }
@@ -272,7 +302,7 @@ attention_tf32_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
     if (warp == MMA_WARP) {
         if (lane == 0) {   // teardown barrier: every MMA of this CTA has completed
             const uint64_t t0 = global_timer_ns();
-            while (!mbar_try_wait(aux_addr + 48, 0)) {
+            while (!mbar_try_wait(bar_td, 0)) {
                 if (global_timer_ns() - t0 > WAIT_LIMIT_NS) {
                     atomicCAS(p.status, 0, (int)WAIT_TEARDOWN);
                     break;
@@ -334,7 +364,8 @@ int launch_attention_fused(te_b200_ctx* ctx, const te_attn_desc* t, cudaStream_t
         if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(attention)");
         attr_smem[ctx->device] = smem;
     }
-    const int grid = (int)(t->B * t->H * p.tiles_q);
+    p.total_tiles = (int)(t->B * t->H * p.tiles_q);
+    const int grid = p.total_tiles < ctx->sm_count ? p.total_tiles : ctx->sm_count;
     attention_tf32_kernel<<<grid, CTA_THREADS, smem, stream>>>(mq, mk, mv, mp, mo, p);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return cuda_fail(e, "attention_tf32_kernel launch");
