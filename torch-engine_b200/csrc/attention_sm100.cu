@@ -1,5 +1,6 @@
-// Fused scaled-dot attention forward for sm_100a:  O = softmax(Q.K^T / sqrt(d)) . V  for one (batch, head) and one
-// block of 128 query rows per CTA, with the score matrix kept in tensor memory.
+// Fused scaled-dot attention forward for sm_100a:  O = softmax(Q.K^T / sqrt(d)) . V, one tile = one (batch, head) and
+// one block of 128 query rows, with the score matrix kept in tensor memory.  Persistent: one CTA per SM walks the tiles
+// and fetches the next tile's operands while the current tile is in its softmax.
 //
 // Reference semantics: ScaledDot::forward (reference src/nn/scaledot.cpp:8-27): S = Q.K^T, S / sqrt(d) (a division),
 // softmax over the last dimension with max subtraction and division by the row sum (reference
@@ -9,12 +10,12 @@
 // Why fused: unfused, the [B,H,T,T] score tensor crosses HBM four times (S written, softmax read + write, P read):
 // 200 of the 252 MB the attention configuration moves.  Here S never leaves the SM; only P is written, once.
 //
-// Per CTA (320 threads):
+// Per CTA (320 threads), for every tile:
 //   warp 8      TMA loads of the Q block (128 x d), all keys K (T x d) and all values V (T x d) into shared memory;
 //   warp 9      S = Q.K^T with tcgen05.mma (both operands K-major) into TMEM columns [0, Tp); later O = P.V with
 //               the A operand read from TMEM (P, written back by the softmax warps) and V as an MN-major operand;
 //   warps 0-7   two warps per 32 query rows, each owning half of the key columns: row maximum, exp and row sum
-//               straight from TMEM (the halves exchange maxima and sums through shared memory), exp written back
+//               straight from TMEM (the halves exchange maxima and sums through four spare TMEM columns), exp written back
 //               to TMEM as the PV operand, P = exp / sum and finally O / sum staged through shared memory and
 //               TMA-stored.
 // Limits of this form: TF32 mode, T <= 256 keys (one TMEM pass, no running rescale), d in {32, 64}; other problems
