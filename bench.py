@@ -112,7 +112,7 @@ def cpu_reference_gemm(size, repeats=1):
     if binding.Reference.available():
         ref = binding.Reference()
         va, vb = binding.ref_view(a.shape), binding.ref_view(b.shape)
-        run = lambda: ref.matmul(a, va, b, vb)
+        run = lambda: ref.matmul(a, va, b, vb, out_shape=(size, size))
         kind = "reference"
     else:
         orc = binding.Oracle()

@@ -237,13 +237,16 @@ class Reference:
         self._check(self.lib.ref_view_strides(C.byref(view), shape, strides, C.byref(nd)))
         return tuple(shape[i] for i in range(nd.value)), tuple(strides[i] for i in range(nd.value))
 
-    def matmul(self, a, va, b, vb):
-        """a, b: dense base arrays; va, vb: recipes (ref_view).  Raises RuntimeError with the reference's text."""
+    def matmul(self, a, va, b, vb, out_shape=None):
+        """a, b: dense base arrays; va, vb: recipes (ref_view).  Raises RuntimeError with the reference's text.
+        Without out_shape the product is evaluated twice (once to learn the result shape); timed callers pass it."""
         a = np.ascontiguousarray(a, dtype=np.float32)
         b = np.ascontiguousarray(b, dtype=np.float32)
-        shape, nd = (C.c_int64 * 8)(), C.c_int32()
-        self._check(self.lib.ref_matmul(_fptr(a), C.byref(va), _fptr(b), C.byref(vb), None, shape, C.byref(nd)))
-        out = np.empty(tuple(shape[i] for i in range(nd.value)), dtype=np.float32)
+        if out_shape is None:
+            shape, nd = (C.c_int64 * 8)(), C.c_int32()
+            self._check(self.lib.ref_matmul(_fptr(a), C.byref(va), _fptr(b), C.byref(vb), None, shape, C.byref(nd)))
+            out_shape = tuple(shape[i] for i in range(nd.value))
+        out = np.empty(tuple(out_shape), dtype=np.float32)
         self._check(self.lib.ref_matmul(_fptr(a), C.byref(va), _fptr(b), C.byref(vb), _fptr(out), None, None))
         return out
 

@@ -98,7 +98,7 @@ def main():
         a, b = rng.uniform((1024, 1024)), rng.uniform((1024, 1024))
         t0 = time.perf_counter()
         if ref:
-            ref.matmul(a, binding.ref_view(a.shape), b, binding.ref_view(b.shape))
+            ref.matmul(a, binding.ref_view(a.shape), b, binding.ref_view(b.shape), out_shape=(1024, 1024))
         else:
             binding.Oracle().matmul(a, b)
         cpu_rate = 2.0 * 1024 ** 3 / (time.perf_counter() - t0)      # FLOP/s of one host core
