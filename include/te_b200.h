@@ -201,6 +201,36 @@ typedef struct te_attn_desc {
 } te_attn_desc;
 TE_API int te_b200_attention_forward(te_b200_ctx* ctx, const te_attn_desc* d, te_stream_t stream);
 
+/* Gradients of the call above given dO: the backward of ScaledDot::forward's graph
+ * (MatMulBackward of P.V and of Q.K^T, src/core/grad_fn.cpp:126-139; SoftmaxBackward,
+ * :569-665; DivBackward, :142-156) as one call:
+ *     dV = P^T.dO      dP = dO.V^T      dS = P o (dP - rowsum(P o dP)) / sqrt(d)
+ *     dQ = dS.K        dK = dS^T.Q
+ * p is the dense [B,H,T,T] probability tensor the forward call wrote; o its output (used for
+ * rowsum(P o dP) = rowsum(dO o O) by the fused kernel; may be NULL, which selects the unfused
+ * path).  q, k, v, o, d_o and the outputs dq, dk, dv are [B,H,T,d] views with element strides
+ * for B, H, T and unit stride over d.  The unfused path keeps dP/dS ([B,H,T,T] floats) in the
+ * context workspace. */
+typedef struct te_attn_bwd_desc {
+    int64_t B, H, T, d;
+    const float* q; const float* k; const float* v;
+    int64_t q_strides[3];
+    int64_t k_strides[3];
+    int64_t v_strides[3];
+    const float* p;         /* [B,H,T,T] dense */
+    const float* o;         /* forward output, optional */
+    int64_t o_strides[3];
+    const float* d_o;       /* gradient of the output */
+    int64_t d_o_strides[3];
+    float* dq; float* dk; float* dv;
+    int64_t dq_strides[3];
+    int64_t dk_strides[3];
+    int64_t dv_strides[3];
+    int32_t precision;
+    int32_t reserved;
+} te_attn_bwd_desc;
+TE_API int te_b200_attention_backward(te_b200_ctx* ctx, const te_attn_bwd_desc* d, te_stream_t stream);
+
 /* ---- sharding helpers (multi-GPU: one process per GPU) ----------------------- */
 
 /* Splits `total` units (N columns, or batch indices) over `world` ranks in blocks that are

@@ -1,7 +1,8 @@
-"""Profiling harness for the fused attention kernel: one warm-up call and a few profiled calls of
-ScaledDot::forward on [B, 12, 256, 64] operands, meant to be run under `ncu -k regex:attention`.
+"""Profiling harness for the fused attention kernels: one warm-up call and a few profiled calls of
+ScaledDot::forward (or, with --backward, of its backward) on [B, 12, 256, 64] operands, meant to be run under
+`ncu -k regex:attention`.
 
-    python torch-engine_b200/benchmarks/attention_profile.py --batch 32
+    python torch-engine_b200/benchmarks/attention_profile.py --batch 32 [--backward]
 """
 import argparse
 import os
@@ -22,12 +23,29 @@ def main():
     ap.add_argument("--seq", type=int, default=256)
     ap.add_argument("--head-dim", type=int, default=64)
     ap.add_argument("--calls", type=int, default=3)
+    ap.add_argument("--backward", action="store_true", help="profile the fused backward instead of the forward")
     args = ap.parse_args()
     be = ops.Backend(0, workspace_bytes=64 << 20)
     g = torch.Generator(device="cuda").manual_seed(42)
     shape = (args.batch, args.heads, args.seq, args.head_dim)
     q, k, v = (torch.randn(shape, device="cuda", generator=g) for _ in range(3))
-    be.scaled_dot(q, k, v)
+    o, p = be.scaled_dot(q, k, v)
+    if args.backward:
+        d_o = torch.randn(shape, device="cuda", generator=g)
+        be.scaled_dot_backward(q, k, v, p, d_o, o=o)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.calls):
+            dq, dk, dv = be.scaled_dot_backward(q, k, v, p, d_o, o=o)
+        e1.record()
+        torch.cuda.synchronize()
+        be.check_device_status()
+        ms = e0.elapsed_time(e1) / args.calls
+        byts = 4.0 * (8 * q.numel() + p.numel())      # Q, K, V, O, dO read, dQ, dK, dV written, P read
+        print("attention backward %s: %.3f ms/call, %.1f GB/s of %.1f MB algorithmic, checksum %.6e" %
+              (shape, ms, byts / ms / 1e6, byts / 1e6, float((dq + dk + dv)[::3, ::5, ::7].double().sum())))
+        return
     torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()

@@ -139,7 +139,8 @@ static int pack_into(te_b200_ctx* ctx, Carver& ws, Operand& op, const float** lo
     return TE_OK;
 }
 
-static int gemm_device(te_b200_ctx* ctx, const te_gemm_desc* d, cudaStream_t st) {
+// `reserve_tail` bytes at the end of the context workspace belong to the caller (scratch that outlives this GEMM).
+static int gemm_device(te_b200_ctx* ctx, const te_gemm_desc* d, cudaStream_t st, size_t reserve_tail = 0) {
     int rc = validate_desc(d);
     if (rc) return rc;
     if (d->M == 0 || d->N == 0) return TE_OK;
@@ -150,7 +151,7 @@ static int gemm_device(te_b200_ctx* ctx, const te_gemm_desc* d, cudaStream_t st)
     g.c = d->c; g.ldc = d->ldc; g.c_stride_inner = d->c_stride_inner; g.c_stride_outer = d->c_stride_outer;
     g.preact = d->preact_out; g.bias = d->bias; g.alpha = d->alpha; g.scale_mode = d->scale_mode;
     g.epilogue = d->epilogue;
-    Carver ws(ctx->workspace, ctx->workspace_bytes);
+    Carver ws(ctx->workspace, ctx->workspace_bytes - reserve_tail);
     if (d->K > 0) {
         if (d->precision == TE_PREC_3XTF32) {
             if ((rc = pack_into(ctx, ws, g.a, &g.a_lo, d->K, d->batch_inner, d->batch_outer, true, st))) return rc;
@@ -584,6 +585,80 @@ int te_b200_attention_forward(te_b200_ctx* ctx, const te_attn_desc* t, te_stream
     d.alpha = 1.0f;
     d.precision = t->precision;
     return gemm_device(ctx, &d, st);
+}
+
+int te_b200_attention_backward(te_b200_ctx* ctx, const te_attn_bwd_desc* t, te_stream_t stream) {
+    if (!ctx) return fail(TE_ERR_BAD_ARGUMENT, "ctx is NULL");
+    if (!t || t->B < 0 || t->H < 0 || t->T < 0 || t->d < 0) return fail(TE_ERR_BAD_ARGUMENT, "attention backward: bad extents");
+    if (t->B == 0 || t->H == 0 || t->T == 0 || t->d == 0) return TE_OK;
+    if (!t->q || !t->k || !t->v || !t->p || !t->d_o || !t->dq || !t->dk || !t->dv)
+        return fail(TE_ERR_BAD_ARGUMENT, "attention backward: NULL pointer");
+    if (t->precision != TE_PREC_TF32 && t->precision != TE_PREC_3XTF32)
+        return fail(TE_ERR_BAD_ARGUMENT, "precision must be TE_PREC_TF32 or TE_PREC_3XTF32");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    int rc = launch_attention_backward_fused(ctx, t, st);     // one kernel when the problem fits it
+    if (rc != -1) return rc;
+    // Unfused: dP / dS live at the end of the context workspace, the GEMMs use the front.
+    const int64_t BH = t->B * t->H;
+    const size_t tail = ((size_t)BH * t->T * t->T * sizeof(float) + 255) & ~size_t(255);
+    if (tail > ctx->workspace_bytes) {
+        char msg[160];
+        snprintf(msg, sizeof msg, "context workspace (%zu bytes) too small; attention backward needs %zu bytes for dP", ctx->workspace_bytes, tail);
+        return fail(TE_ERR_WORKSPACE, msg);
+    }
+    float* dp = reinterpret_cast<float*>(static_cast<char*>(ctx->workspace) + ctx->workspace_bytes - tail);
+    const int64_t sP_o = t->H * t->T * t->T, sP_i = t->T * t->T;
+    te_gemm_desc d;
+    // dV = P^T . dO   (MatMulBackward of P.V, grad_fn.cpp:131-134)
+    memset(&d, 0, sizeof d);
+    d.M = t->T; d.N = t->d; d.K = t->T;
+    d.a = t->p; d.lda = t->T; d.a_major = TE_COL_MAJOR;
+    d.b = t->d_o; d.ldb = t->d_o_strides[2]; d.b_major = TE_ROW_MAJOR;
+    d.c = t->dv; d.ldc = t->dv_strides[2];
+    d.batch_outer = t->B; d.batch_inner = t->H;
+    d.a_stride_outer = sP_o; d.a_stride_inner = sP_i;
+    d.b_stride_outer = t->d_o_strides[0]; d.b_stride_inner = t->d_o_strides[1];
+    d.c_stride_outer = t->dv_strides[0]; d.c_stride_inner = t->dv_strides[1];
+    d.alpha = 1.0f; d.precision = t->precision;
+    if ((rc = gemm_device(ctx, &d, st, tail))) return rc;
+    // dP = dO . V^T   (grad_fn.cpp:127-130)
+    memset(&d, 0, sizeof d);
+    d.M = t->T; d.N = t->T; d.K = t->d;
+    d.a = t->d_o; d.lda = t->d_o_strides[2]; d.a_major = TE_ROW_MAJOR;
+    d.b = t->v; d.ldb = t->v_strides[2]; d.b_major = TE_COL_MAJOR;
+    d.c = dp; d.ldc = t->T;
+    d.batch_outer = t->B; d.batch_inner = t->H;
+    d.a_stride_outer = t->d_o_strides[0]; d.a_stride_inner = t->d_o_strides[1];
+    d.b_stride_outer = t->v_strides[0]; d.b_stride_inner = t->v_strides[1];
+    d.c_stride_outer = sP_o; d.c_stride_inner = sP_i;
+    d.alpha = 1.0f; d.precision = t->precision;
+    if ((rc = gemm_device(ctx, &d, st, tail))) return rc;
+    // dS (before the division) = P o (dP - rowsum(P o dP)), in place   (SoftmaxBackward, grad_fn.cpp:569-665)
+    if ((rc = launch_softmax_backward_rows(ctx, t->p, dp, dp, BH * t->T, t->T, st))) return rc;
+    // dQ = (dS / sqrt(d)) . K  and  dK = (dS / sqrt(d))^T . Q : DivBackward (grad_fn.cpp:142-156) folded into the scale
+    const float scale = sqrtf((float)t->d);
+    memset(&d, 0, sizeof d);
+    d.M = t->T; d.N = t->d; d.K = t->T;
+    d.a = dp; d.lda = t->T; d.a_major = TE_ROW_MAJOR;
+    d.b = t->k; d.ldb = t->k_strides[2]; d.b_major = TE_ROW_MAJOR;
+    d.c = t->dq; d.ldc = t->dq_strides[2];
+    d.batch_outer = t->B; d.batch_inner = t->H;
+    d.a_stride_outer = sP_o; d.a_stride_inner = sP_i;
+    d.b_stride_outer = t->k_strides[0]; d.b_stride_inner = t->k_strides[1];
+    d.c_stride_outer = t->dq_strides[0]; d.c_stride_inner = t->dq_strides[1];
+    d.alpha = scale; d.scale_mode = TE_SCALE_DIV; d.precision = t->precision;
+    if ((rc = gemm_device(ctx, &d, st, tail))) return rc;
+    memset(&d, 0, sizeof d);
+    d.M = t->T; d.N = t->d; d.K = t->T;
+    d.a = dp; d.lda = t->T; d.a_major = TE_COL_MAJOR;
+    d.b = t->q; d.ldb = t->q_strides[2]; d.b_major = TE_ROW_MAJOR;
+    d.c = t->dk; d.ldc = t->dk_strides[2];
+    d.batch_outer = t->B; d.batch_inner = t->H;
+    d.a_stride_outer = sP_o; d.a_stride_inner = sP_i;
+    d.b_stride_outer = t->q_strides[0]; d.b_stride_inner = t->q_strides[1];
+    d.c_stride_outer = t->dk_strides[0]; d.c_stride_inner = t->dk_strides[1];
+    d.alpha = scale; d.scale_mode = TE_SCALE_DIV; d.precision = t->precision;
+    return gemm_device(ctx, &d, st, tail);
 }
 
 int te_b200_shard_range(int64_t total, int world, int rank, int64_t align, int64_t* out_begin, int64_t* out_count) {

@@ -321,7 +321,7 @@ typedef CUresult (*EncodeTiledFn4)(CUtensorMap*, CUtensorMapDataType, cuuint32_t
                                    CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
 // [B, H, T, cols] view with unit last-dim stride -> map {cols, T, H, B}.
-static bool make_bhtc_map(te_b200_ctx* ctx, CUtensorMap* out, const float* ptr, int64_t cols, int64_t T, int64_t H,
+bool make_bhtc_map(te_b200_ctx* ctx, CUtensorMap* out, const float* ptr, int64_t cols, int64_t T, int64_t H,
                           int64_t B, const int64_t* strides_bht, int box_cols, int box_rows, CUtensorMapSwizzle swz) {
     if (reinterpret_cast<uintptr_t>(ptr) & 15) return false;
     const int64_t sT = strides_bht[2], sH = strides_bht[1], sB = strides_bht[0];

@@ -227,6 +227,11 @@ bool make_output_maps(te_b200_ctx* ctx, const GemmProblem& g, int k_splits, CUte
 // Fills the kernel parameters that do not depend on the tile shape.
 void fill_common_params(GemmParams& p, const te_b200_ctx* ctx, const GemmProblem& g);
 
+// attention_sm100.cu.  Host: tensor map {cols, T, H, B} of a [B, H, T, cols] view with unit last-dim stride and element
+// strides strides_bht for B, H, T.  Returns false when TMA cannot address the view.
+bool make_bhtc_map(te_b200_ctx* ctx, CUtensorMap* out, const float* ptr, int64_t cols, int64_t T, int64_t H, int64_t B,
+                   const int64_t* strides_bht, int box_cols, int box_rows, CUtensorMapSwizzle swz);
+
 // gemm_sm100_2cta.cu: the CTA-pair (cta_group::2) TF32 kernel, 256 x 256 tiles.
 int launch_gemm_2cta(te_b200_ctx* ctx, const GemmProblem& g, int k_splits, cudaStream_t stream);
 

@@ -107,9 +107,9 @@ __global__ void __launch_bounds__(256) softmax_rows_vec4_kernel(const float* in,
 }
 
 // dx = s * (dy - <dy, s>) per row (reference src/cuda/elementwise_cuda.cu:2450-2467).
-__global__ void __launch_bounds__(256) softmax_backward_rows_kernel(const float* __restrict__ s,
-                                                                    const float* __restrict__ dy,
-                                                                    float* __restrict__ dx, long long rows, int cols) {
+// dx may be the same buffer as dy: every element is read and then written by the one lane that owns it.
+__global__ void __launch_bounds__(256) softmax_backward_rows_kernel(const float* __restrict__ s, const float* dy,
+                                                                    float* dx, long long rows, int cols) {
     const int lane = threadIdx.x & 31;
     const long long warps_per_grid = (long long)gridDim.x * (blockDim.x >> 5);
     for (long long row = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); row < rows;

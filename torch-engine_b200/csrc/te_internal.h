@@ -67,6 +67,8 @@ int launch_gemm(te_b200_ctx* ctx, const GemmProblem& p, cudaStream_t stream);
 
 // attention_sm100.cu: fused QK^T -> softmax -> PV.  Returns -1 when the problem is outside the fused kernel's limits.
 int launch_attention_fused(te_b200_ctx* ctx, const te_attn_desc* t, cudaStream_t stream);
+// attention_bwd_sm100.cu: fused backward of the same.  Returns -1 when the problem is outside the fused kernel's limits.
+int launch_attention_backward_fused(te_b200_ctx* ctx, const te_attn_bwd_desc* t, cudaStream_t stream);
 
 // pack.cu: writes dense K-major planes [batch_outer][batch_inner][rows][kp] (kp = K rounded up to 4).
 // split == false: dst_hi receives a copy.  split == true: dst_hi / dst_lo receive the tf32 hi / lo parts.

@@ -7,12 +7,11 @@ Every matmul of the step runs on this backend through the C ABI:
     te_b200_linear_forward / te_b200_linear_backward, the FeedForward GELU (src/nn/ffn.cpp:12-16) in the epilogue;
   * ScaledDot::forward (src/nn/scaledot.cpp:8-27) on the head views of MultiHeadAttention::forward
     (src/nn/multi_head_attention.cpp:19-42, strides [T*E, hd, E, 1], no copies, no mask), and its backward
-    (MatMulBackward x2, DivBackward, SoftmaxBackward) as four batched GEMMs and one softmax-backward kernel.
+    (MatMulBackward x2, DivBackward, SoftmaxBackward) as te_b200_attention_backward.
 What is not a matmul in the reference (embedding gather, sinusoidal position table, pre-LN LayerNorm, residual
 adds, the mean cross-entropy) stays outside the backend and is evaluated with stock torch ops, as those kernels
 stay with the reference.  Parameters come in GPT::parameters() order (src/nn/gpt.cpp:88-113).
 """
-import math
 
 import torch
 
@@ -43,21 +42,14 @@ class _ScaledDot(torch.autograd.Function):
     @staticmethod
     def forward(ctx, q, k, v, be, prec):
         o, p = be.scaled_dot(q, k, v, precision=prec)
-        ctx.save_for_backward(q, k, v, p)
+        ctx.save_for_backward(q, k, v, p, o)
         ctx.be, ctx.prec = be, prec
         return o
 
     @staticmethod
     def backward(ctx, d_o):
-        q, k, v, p = ctx.saved_tensors
-        be, prec = ctx.be, ctx.prec
-        d_o = d_o.contiguous()
-        scale = math.sqrt(q.shape[-1])
-        dv = be.matmul(p.transpose(-1, -2), d_o, precision=prec)          # P^T . dO
-        dp = be.matmul(d_o, v.transpose(-1, -2), precision=prec)          # dO . V^T
-        ds = be.softmax_backward(p, dp) / scale                            # SoftmaxBackward, then DivBackward
-        dq = be.matmul(ds, k, precision=prec)                              # dS . K
-        dk = be.matmul(ds.transpose(-1, -2), q, precision=prec)            # dS^T . Q
+        q, k, v, p, o = ctx.saved_tensors
+        dq, dk, dv = ctx.be.scaled_dot_backward(q, k, v, p, d_o, o=o, precision=ctx.prec)
         return dq, dk, dv, None, None
 
 

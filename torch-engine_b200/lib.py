@@ -49,6 +49,20 @@ class AttnDesc(C.Structure):
     ]
 
 
+class AttnBwdDesc(C.Structure):
+    """struct te_attn_bwd_desc"""
+    _fields_ = [
+        ("B", C.c_int64), ("H", C.c_int64), ("T", C.c_int64), ("d", C.c_int64),
+        ("q", C.c_void_p), ("k", C.c_void_p), ("v", C.c_void_p),
+        ("q_strides", C.c_int64 * 3), ("k_strides", C.c_int64 * 3), ("v_strides", C.c_int64 * 3),
+        ("p", C.c_void_p), ("o", C.c_void_p), ("o_strides", C.c_int64 * 3),
+        ("d_o", C.c_void_p), ("d_o_strides", C.c_int64 * 3),
+        ("dq", C.c_void_p), ("dk", C.c_void_p), ("dv", C.c_void_p),
+        ("dq_strides", C.c_int64 * 3), ("dk_strides", C.c_int64 * 3), ("dv_strides", C.c_int64 * 3),
+        ("precision", C.c_int32), ("reserved", C.c_int32),
+    ]
+
+
 # name -> (restype, argtypes); every symbol include/te_b200.h declares
 SIGNATURES = {
     "te_b200_init": (C.c_int, [C.c_int, C.c_size_t, C.POINTER(C.c_void_p)]),
@@ -75,6 +89,7 @@ SIGNATURES = {
     "te_b200_linear_backward": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
                                           C.c_void_p, C.c_int64, C.c_int64, C.c_int64, C.c_int, C.c_void_p]),
     "te_b200_attention_forward": (C.c_int, [C.c_void_p, C.POINTER(AttnDesc), C.c_void_p]),
+    "te_b200_attention_backward": (C.c_int, [C.c_void_p, C.POINTER(AttnBwdDesc), C.c_void_p]),
     "te_b200_shard_range": (C.c_int, [C.c_int64, C.c_int, C.c_int, C.c_int64, c_i64_p, c_i64_p]),
 }
 

@@ -7,6 +7,7 @@ used only as device-memory holders (data_ptr, shape, stride) and for the current
     Backend.linear_forward  Linear::forward (+ FeedForward GELU)  (src/nn/linear.cpp:14-23, src/nn/ffn.cpp:12-16)
     Backend.linear_backward MatMulBackward/AddBackward/TransposeBackward of that graph (src/core/grad_fn.cpp:93-139)
     Backend.scaled_dot      ScaledDot::forward                    (src/nn/scaledot.cpp:8-27)
+    Backend.scaled_dot_backward  its backward graph                (src/core/grad_fn.cpp:126-156, :569-665)
     Backend.softmax / softmax_backward / gelu / gelu_backward / colsum: the kernels between the GEMMs.
 """
 import ctypes as C
@@ -159,6 +160,39 @@ class Backend:
         desc.precision = _prec(precision)
         L.check(self._lib.te_b200_attention_forward(self._ctx, C.byref(desc), self._stream()))
         return o, p
+
+    def scaled_dot_backward(self, q, k, v, p, d_o, o=None, precision="tf32"):
+        """(dq, dk, dv) of scaled_dot given the gradient d_o of its output, the probabilities p it returned and
+        (optionally) its output o: MatMulBackward x2, SoftmaxBackward and DivBackward of the reference graph
+        (src/core/grad_fn.cpp:126-156, :569-665).  With o the fused kernel may run; without it the GEMM sequence."""
+        self._check_f32_cuda(q, k, v, p, d_o, o)
+        B, H, T, d = q.shape
+        if p.shape != (B, H, T, T) or not p.is_contiguous():
+            raise L.BackendError(L.TE_ERR_BAD_ARGUMENT, "scaled_dot_backward expects dense probabilities [B,H,T,T]")
+        if d_o.stride(3) != 1:
+            d_o = d_o.contiguous()
+        for t in (q, k, v) + ((o,) if o is not None else ()):
+            if t.shape != q.shape or t.stride(3) != 1:
+                raise L.BackendError(L.TE_ERR_UNSUPPORTED_LAYOUT, L.status_string(L.TE_ERR_UNSUPPORTED_LAYOUT))
+        dq, dk, dv = (torch.empty((B, H, T, d), dtype=torch.float32, device=q.device) for _ in range(3))
+        desc = L.AttnBwdDesc()
+        desc.B, desc.H, desc.T, desc.d = B, H, T, d
+        desc.q, desc.k, desc.v = q.data_ptr(), k.data_ptr(), v.data_ptr()
+        desc.q_strides = (C.c_int64 * 3)(*q.stride()[:3])
+        desc.k_strides = (C.c_int64 * 3)(*k.stride()[:3])
+        desc.v_strides = (C.c_int64 * 3)(*v.stride()[:3])
+        desc.p = p.data_ptr()
+        desc.o = o.data_ptr() if o is not None else None
+        desc.o_strides = (C.c_int64 * 3)(*(o.stride()[:3] if o is not None else (0, 0, 0)))
+        desc.d_o = d_o.data_ptr()
+        desc.d_o_strides = (C.c_int64 * 3)(*d_o.stride()[:3])
+        desc.dq, desc.dk, desc.dv = dq.data_ptr(), dk.data_ptr(), dv.data_ptr()
+        desc.dq_strides = (C.c_int64 * 3)(*dq.stride()[:3])
+        desc.dk_strides = (C.c_int64 * 3)(*dk.stride()[:3])
+        desc.dv_strides = (C.c_int64 * 3)(*dv.stride()[:3])
+        desc.precision = _prec(precision)
+        L.check(self._lib.te_b200_attention_backward(self._ctx, C.byref(desc), self._stream()))
+        return dq, dk, dv
 
     # ------------------------------------------------------------------ row / elementwise ops
     def softmax(self, x):
