@@ -6,7 +6,7 @@
 //                       transpose_view(d1, d2), matmul(other)        (reference src/tensor/tensor.h:92-130, :908)
 //   te::Linear          forward(x) = x.matmul(W.transpose_view(1,0)) + b   (reference src/nn/linear.cpp:14-23)
 //   te::FeedForward     Linear -> GELU -> Linear                           (reference src/nn/ffn.cpp:12-16)
-//   te::ScaledDot       softmax(Q.K^T / sqrt(d)).V                         (reference src/nn/scaledot.cpp:8-27)
+//   te::ScaledDot       softmax(Q.K^T / sqrt(d)).V and its backward        (reference src/nn/scaledot.cpp:8-27)
 // Errors surface as std::runtime_error with the reference's texts (src/tensor/tensor.h:537, :547, :626, :858).
 // Tensors live on the GPU only: this backend has no CPU compute path.  Each Tensor owns (or shares) one
 // cudaMalloc'ed buffer, as the reference's CUDAAllocator does (src/core/allocators.h:35-52).
@@ -255,6 +255,33 @@ public:
         check(te_b200_attention_forward(be.ctx(), &a, nullptr));
         if (probabilities) *probabilities = p;
         return o;
+    }
+
+    // Gradients {dQ, dK, dV} given dO, the probabilities and the output of forward(): the backward of its graph in one
+    // call (MatMulBackward x2, SoftmaxBackward, DivBackward; reference src/core/grad_fn.cpp:126-156, :569-665).
+    std::vector<Tensor> backward(const Tensor& Q, const Tensor& K, const Tensor& V, const Tensor& probabilities,
+                                 const Tensor& O, const Tensor& dO) const {
+        const int64_t B = Q.shape()[0], H = Q.shape()[1], T = Q.shape()[2], d = Q.shape()[3];
+        if (probabilities.shape() != std::vector<int64_t>{B, H, T, T} || !probabilities.is_contiguous())
+            throw std::runtime_error("ScaledDot backward expects dense probabilities [B,H,T,T]");
+        for (const Tensor* t : {&Q, &K, &V, &O, &dO})
+            if (t->shape() != Q.shape() || t->strides()[3] != 1)
+                throw std::runtime_error(te_b200_status_string(TE_ERR_UNSUPPORTED_LAYOUT));
+        Tensor dq({B, H, T, d}), dk({B, H, T, d}), dv({B, H, T, d});
+        te_attn_bwd_desc a{};
+        a.B = B; a.H = H; a.T = T; a.d = d;
+        a.q = Q.data(); a.k = K.data(); a.v = V.data();
+        a.p = probabilities.data(); a.o = O.data(); a.d_o = dO.data();
+        a.dq = dq.data(); a.dk = dk.data(); a.dv = dv.data();
+        for (int i = 0; i < 3; ++i) {
+            a.q_strides[i] = Q.strides()[i]; a.k_strides[i] = K.strides()[i]; a.v_strides[i] = V.strides()[i];
+            a.o_strides[i] = O.strides()[i]; a.d_o_strides[i] = dO.strides()[i];
+            a.dq_strides[i] = dq.strides()[i]; a.dk_strides[i] = dk.strides()[i]; a.dv_strides[i] = dv.strides()[i];
+        }
+        Backend& be = Backend::instance();
+        a.precision = be.precision();
+        check(te_b200_attention_backward(be.ctx(), &a, nullptr));
+        return {dq, dk, dv};
     }
 };
 

@@ -91,7 +91,8 @@ int main() {
         lin.bias() = Tensor::from_host({0.5f, -1.0f}, {2});
         expect_values("Linear forward", lin.forward(a), {1 - 3 + 0.5f, 2 + 2 - 1.0f, 4 - 6 + 0.5f, 8 + 5 - 1.0f}, 1e-5f);
         // ScaledDot on MultiHeadAttention-style head views: uniform keys give the mean of V
-        const int64_t B = 2, T = 4, H = 2, hd = 8;
+        for (const int64_t hd : {int64_t(8), int64_t(32)}) {     // 32: the fused kernels in TF32 mode; 8: the GEMM sequence
+        const int64_t B = 2, T = 4, H = 2;
         std::vector<float> q(B * T * H * hd, 0.0f), v(B * T * H * hd);
         for (size_t i = 0; i < v.size(); ++i) v[i] = float(i % 7);
         auto heads = [&](const std::vector<float>& x) { return Tensor::from_host(x, {B, T, H * hd}).view({B, T, H, hd}).transpose_view(1, 2); };
@@ -103,6 +104,24 @@ int main() {
             want[((bb * H + h) * T + t) * hd + e] = s / T;
         }
         expect_values("ScaledDot on head views", o, want, 1e-2f);
+        // Backward with zero queries and keys: P = 1/T everywhere, so dV is the mean of dO over the queries for every
+        // key, and dQ = dS.K and dK = dS^T.Q vanish with K and Q.
+        Tensor p_saved;
+        Tensor qh = heads(q), vh = heads(v);
+        Tensor o2 = te::ScaledDot().forward(qh, qh, vh, &p_saved);
+        std::vector<float> go(B * H * T * hd);
+        for (size_t i = 0; i < go.size(); ++i) go[i] = float(int(i % 5) - 2);
+        std::vector<Tensor> grads = te::ScaledDot().backward(qh, qh, vh, p_saved, o2, Tensor::from_host(go, {B, H, T, hd}));
+        std::vector<float> want_dv(B * H * T * hd), zeros(B * H * T * hd, 0.0f);
+        for (int64_t bh = 0; bh < B * H; ++bh) for (int64_t t = 0; t < T; ++t) for (int64_t e = 0; e < hd; ++e) {
+            float s = 0;
+            for (int64_t tt = 0; tt < T; ++tt) s += go[(bh * T + tt) * hd + e];
+            want_dv[(bh * T + t) * hd + e] = s / T;
+        }
+        expect_values("ScaledDot backward dV", grads[2], want_dv, 1e-2f);
+        expect_values("ScaledDot backward dQ", grads[0], zeros, 1e-6f);
+        expect_values("ScaledDot backward dK", grads[1], zeros, 1e-6f);
+        }
         te::Backend::instance().synchronize();
     } catch (const std::exception& e) {
         std::cout << "FAIL unexpected exception: " << e.what() << "\n";

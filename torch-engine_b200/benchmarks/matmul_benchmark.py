@@ -9,7 +9,7 @@ median of 7 trials.  FLOPs = 2*M*K*N, bytes = 4*(M*K + K*N + M*N) (:73-82).  Inp
     python torch-engine_b200/benchmarks/matmul_benchmark.py [out.json] [--cpu] [--quick]
 
 Cases: the square sweep 1024..16384 and the skinny shapes of the GEMM sweep configuration, the attention pair of
-batched products (B=16, H=12, T=256, d=64) with the softmax between them, and the MLP Linear forward (+GELU) and
+batched products (B=16, H=12, T=256, d=64) with the softmax between them and its backward, and the MLP Linear forward (+GELU) and
 backward (X [4096,768], W [3072,768]).  `pct_of_cublas` compares with torch.matmul in TF32 mode (a cuBLAS call) as a
 comparator only.  With --cpu the reference's own CPU Tensor::matmul (single-threaded) is timed beside the small
 shapes and extrapolated, labelled as such, for the large ones.
@@ -152,6 +152,21 @@ def main():
         results[-1]["pct_of_hbm_peak"] = 100.0 * (byts / (tm * 1e-3) / 1e9) / hbm_peak
         results[-1]["note"] = ("one fused kernel, S stays in tensor memory; bytes = 100.7 MB" if mode == "tf32" else
                                "two batched GEMMs + row softmax; bytes = 251.7 MB (unfused)")
+
+    # ---- attention backward: dQ, dK, dV from dO, P, O over the same [16, 12, 256, 64] operands ----
+    d_o = torch.randn(16, 12, 256, 64, device="cuda", generator=gen)
+    o_f, p_f = be.scaled_dot(q, k, v, precision="tf32")
+    for mode, o_arg in (("tf32", o_f), ("3xtf32", None)):
+        tb, tm = time_gpu(lambda: be.scaled_dot_backward(q, k, v, p_f, d_o, o=o_arg, precision=mode), 50)
+        # four products of 2*T*T*d FLOP per head (dV, dP, dQ, dK; S is not recomputed, P is read back)
+        record("b200_attention_backward", mode, 256, 64, 256, 192 * 4, tb, tm, None)
+        # algorithmic traffic, fused: P, Q, K, V, O, dO read once, dQ, dK, dV written once = 151.0 MB;
+        # unfused: P read twice, dP written, read and rewritten as dS, dS read twice (6 x 50.3 MB) + the [B,H,T,d] operands
+        byts = 151.0e6 if mode == "tf32" else 6 * 50.3e6 + 9 * 12.6e6
+        results[-1]["bandwidth_gb_s"] = byts / (tm * 1e-3) / 1e9
+        results[-1]["pct_of_hbm_peak"] = 100.0 * (byts / (tm * 1e-3) / 1e9) / hbm_peak
+        results[-1]["note"] = ("row-dot pre-pass + one fused kernel, dP and dS stay in tensor memory; bytes = 151.0 MB"
+                               if mode == "tf32" else "four batched GEMMs + softmax-backward kernel (unfused)")
 
     # ---- MLP Linear: X [4096,768], W [3072,768] ----
     x, w, dy = torch.randn(4096, 768, device="cuda", generator=gen), torch.randn(3072, 768, device="cuda", generator=gen) * 0.02, \

@@ -46,19 +46,49 @@ struct AttnBwdParams {
     int nblk;          // 128-row blocks per head (1 or 2)
     int total_tiles;   // B * H
     float inv_scale;   // 1 / sqrt(d)
-    const float* p;    // [B,H,T,T] dense
-    const float* o;
-    const float* d_o;
-    long long o_s[3], do_s[3];
+    int pbox;          // rows and columns of the P box: min(T, 128)
+    const float* dvec; // [B,H,T]: rowsum(dO o O), written by rowdot_bht_kernel
     int* status;
 };
+
+// D[b,h,t] = sum_c dO[b,h,t,c] * O[b,h,t,c] (= rowsum(P o dP), the inner product SoftmaxBackward subtracts).  A row is
+// d/4 float4 wide, so one warp instruction covers 32/(d/4) whole rows; partial dot products meet by shuffles.
+__global__ void __launch_bounds__(256) rowdot_bht_kernel(const float* __restrict__ x, long long xs0, long long xs1, long long xs2,
+                                                         const float* __restrict__ y, long long ys0, long long ys1, long long ys2,
+                                                         float* __restrict__ out, int H, int T, int d, long long rows) {
+    const int lane = threadIdx.x & 31;
+    const int f4 = d >> 2, rpi = 32 / f4;
+    const int sub = lane / f4, col = lane - sub * f4;
+    const long long warps = (long long)gridDim.x * (blockDim.x >> 5);
+    for (long long g = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); g * rpi < rows; g += warps) {
+        const long long r = g * rpi + sub;
+        float acc = 0.0f;
+        if (r < rows) {
+            const long long bh = r / T;
+            const int t = (int)(r - bh * T), h = (int)(bh % H);
+            const long long b = bh / H;
+            const float4 a = __ldg(reinterpret_cast<const float4*>(x + b * xs0 + h * xs1 + t * xs2) + col);
+            const float4 c = __ldg(reinterpret_cast<const float4*>(y + b * ys0 + h * ys1 + t * ys2) + col);
+            acc = a.x * c.x + a.y * c.y + a.z * c.z + a.w * c.w;
+        }
+        for (int off = f4 >> 1; off >= 1; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
+        if (col == 0 && r < rows) out[r] = acc;
+    }
+}
+
+// Asks the TMA unit to bring one box of a tensor into L2 (no shared-memory destination, nothing to wait for).
+__device__ __forceinline__ void tma_prefetch_l2_4d(const void* tmap, int c0, int c1, int c2, int c3) {
+    asm volatile("cp.async.bulk.prefetch.tensor.4d.L2.global.tile [%0, {%1, %2, %3, %4}];" ::"l"(reinterpret_cast<uint64_t>(tmap)),
+                 "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+                 : "memory");
+}
 
 __global__ void __launch_bounds__(CTA_THREADS, 1)
 attention_bwd_tf32_kernel(const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_k,
                           const __grid_constant__ CUtensorMap tm_dok, const __grid_constant__ CUtensorMap tm_dom,
                           const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_dq,
                           const __grid_constant__ CUtensorMap tm_dk, const __grid_constant__ CUtensorMap tm_dv,
-                          const AttnBwdParams p) {
+                          const __grid_constant__ CUtensorMap tm_p, const AttnBwdParams p) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw_addr = smem_u32(smem_raw);
     const uint32_t base = (raw_addr + 1023u) & ~1023u;
@@ -82,9 +112,11 @@ attention_bwd_tf32_kernel(const __grid_constant__ CUtensorMap tm_v, const __grid
     const uint32_t bar_free = aux_addr + 40;   // dV/dK (and at a tile's end dQ) read out          (8 warps -> MMA)
     const uint32_t bar_d = aux_addr + 48;      // D of the tile written                            (8 warps)
     const uint32_t bar_td = aux_addr + 56;     // teardown
-    const uint32_t tmem_slot_addr = aux_addr + 64;
-    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(aux + 64);
-    volatile int* abort_flag = reinterpret_cast<volatile int*>(aux + 68);
+    const uint32_t bar_p = aux_addr + 64;      // the step's block of P has landed in the dS^T region (producer -> warps)
+    const uint32_t bar_pr = aux_addr + 72;     // every warp has taken its P values: the region may be rewritten (8 warps)
+    const uint32_t tmem_slot_addr = aux_addr + 80;
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(aux + 80);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(aux + 84);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
@@ -97,6 +129,8 @@ attention_bwd_tf32_kernel(const __grid_constant__ CUtensorMap tm_v, const __grid
         mbar_init(bar_free, EPI_WARPS);
         mbar_init(bar_d, EPI_WARPS);
         mbar_init(bar_td, 1);
+        mbar_init(bar_p, 1);
+        mbar_init(bar_pr, EPI_WARPS);
         *abort_flag = 0;
         fence_barrier_init();
         fence_proxy_async_smem();
@@ -118,8 +152,13 @@ attention_bwd_tf32_kernel(const __grid_constant__ CUtensorMap tm_v, const __grid
             tma_prefetch_desc(&tm_dok);
             tma_prefetch_desc(&tm_dom);
             tma_prefetch_desc(&tm_q);
+            tma_prefetch_desc(&tm_p);
             int s = 0;   // steps issued by this CTA so far (phase of the per-step barriers)
+            int jc = 0;  // key blocks finished by this CTA so far (phase of bar_free)
             bool ok = true;
+            // The step's 128 x 128 block of P is copied into the (still unused) dS^T region, from where the element
+            // warps take it transposed; the block of the NEXT step is pulled into L2 a step ahead.
+            if ((int)blockIdx.x < p.total_tiles) tma_prefetch_l2_4d(&tm_p, 0, 0, blockIdx.x % p.H, blockIdx.x / p.H);
             for (int t = blockIdx.x; t < p.total_tiles && ok; t += gridDim.x) {
                 const int h = t % p.H, b = t / p.H;
                 for (int j = 0; j < nblk && ok; ++j) {
@@ -139,14 +178,40 @@ attention_bwd_tf32_kernel(const __grid_constant__ CUtensorMap tm_v, const __grid
                             ok = false;
                             break;
                         }
-                        mbar_arrive_expect_tx(bar_b, i == 0 ? 3 * opnd : 2 * opnd);
-                        for (int c = 0; c < dchunks; ++c) {
-                            for (int kb = 0; kb < 4; ++kb) {
-                                tma_load_4d(dom_smem + c * BWD_CHUNK + kb * 4096, &tm_dom, bar_b, 32 * c, 128 * i + 32 * kb, h, b);
-                                tma_load_4d(q_smem + c * BWD_CHUNK + kb * 4096, &tm_q, bar_b, 32 * c, 128 * i + 32 * kb, h, b);
-                                if (i == 0)
-                                    tma_load_4d(k_smem + c * BWD_CHUNK + kb * 4096, &tm_k, bar_b, 32 * c, 128 * j + 32 * kb, h, b);
+                        // The dS^T region takes the step's P block.  It is free once the previous step's MMA 4 is done
+                        // (waited for above) and, after a key block's last step, once the outputs staged in it have been
+                        // read by their stores.  The element warps need P first, so it goes ahead of the operands of
+                        // MMAs 2-4 unless it has to wait for those stores.
+                        const bool after_outputs = s > 0 && i == 0;
+                        for (int pass = 0; pass < 2; ++pass) {
+                            if ((pass == 0) != after_outputs) {
+                                if (after_outputs) {
+                                    if (!wait_bounded(bar_free, jc & 1, abort_flag, p.status, WAIT_PRODUCER_EMPTY)) {
+                                        ok = false;
+                                        break;
+                                    }
+                                    ++jc;
+                                }
+                                mbar_arrive_expect_tx(bar_p, p.pbox * p.pbox * 4);
+                                tma_load_4d(ds_smem, &tm_p, bar_p, 128 * j, 128 * i, h, b);
+                            } else {
+                                mbar_arrive_expect_tx(bar_b, i == 0 ? 3 * opnd : 2 * opnd);
+                                for (int c = 0; c < dchunks; ++c) {
+                                    for (int kb = 0; kb < 4; ++kb) {
+                                        tma_load_4d(dom_smem + c * BWD_CHUNK + kb * 4096, &tm_dom, bar_b, 32 * c, 128 * i + 32 * kb, h, b);
+                                        tma_load_4d(q_smem + c * BWD_CHUNK + kb * 4096, &tm_q, bar_b, 32 * c, 128 * i + 32 * kb, h, b);
+                                        if (i == 0)
+                                            tma_load_4d(k_smem + c * BWD_CHUNK + kb * 4096, &tm_k, bar_b, 32 * c, 128 * j + 32 * kb, h, b);
+                                    }
+                                }
                             }
+                        }
+                        if (!ok) break;
+                        {   // P block of the step after this one
+                            int ni = i + 1, nj = j, nt = t;
+                            if (ni == nblk) { ni = 0; ++nj; }
+                            if (nj == nblk) { nj = 0; nt += gridDim.x; }
+                            if (nt < p.total_tiles) tma_prefetch_l2_4d(&tm_p, 128 * nj, 128 * ni, nt % p.H, nt / p.H);
                         }
                     }
                 }
@@ -186,14 +251,17 @@ attention_bwd_tf32_kernel(const __grid_constant__ CUtensorMap tm_v, const __grid
                             break;
                         }
                         tc_fence_after_sync();
+#pragma unroll
                         for (int kk = 0; kk < 16; ++kk) {
                             const uint64_t db = make_smem_desc(dom_smem + kk * 1024, BWD_CHUNK, 512, SMEM_LAYOUT_SW128_BASE32B);
                             umma_tf32_a_tmem(tmem_base + BWD_COL_DV, tmem_base + BWD_COL_P + kk * 8, db, idesc_ta, (i | kk) != 0);
                         }
+#pragma unroll
                         for (int kk = 0; kk < 16; ++kk) {
                             const uint64_t db = make_smem_desc(q_smem + kk * 1024, BWD_CHUNK, 512, SMEM_LAYOUT_SW128_BASE32B);
                             umma_tf32_a_tmem(tmem_base + BWD_COL_DK, tmem_base + BWD_COL_DP + kk * 8, db, idesc_ta, (i | kk) != 0);
                         }
+#pragma unroll
                         for (int kk = 0; kk < 16; ++kk) {
                             const uint64_t da = make_smem_desc(ds_smem + kk * 1024, BWD_CHUNK, 512, SMEM_LAYOUT_SW128_BASE32B);
                             const uint64_t db = make_smem_desc(k_smem + kk * 1024, BWD_CHUNK, 512, SMEM_LAYOUT_SW128_BASE32B);
@@ -222,43 +290,41 @@ attention_bwd_tf32_kernel(const __grid_constant__ CUtensorMap tm_v, const __grid
         for (int t = blockIdx.x; t < p.total_tiles && ok; t += gridDim.x, ++tc) {
             const int h = t % p.H, b = t / p.H;
             er.bi = h; er.bo = b;
-            {   // D[r] = sum_c dO[r,c] * O[r,c] for this thread's query row
-                const int r = threadIdx.x;
-                float acc = 0.0f;
-                if (r < p.T) {
-                    const float4* go = reinterpret_cast<const float4*>(p.d_o + b * p.do_s[0] + h * p.do_s[1] + r * p.do_s[2]);
-                    const float4* oo = reinterpret_cast<const float4*>(p.o + b * p.o_s[0] + h * p.o_s[1] + r * p.o_s[2]);
-                    for (int c = 0; c < p.d / 4; ++c) {
-                        const float4 x = __ldg(go + c), y = __ldg(oo + c);
-                        acc += x.x * y.x + x.y * y.y + x.z * y.z + x.w * y.w;
-                    }
-                }
-                d_sm[r] = acc;
-                __syncwarp();
-                if (lane == 0) mbar_arrive(bar_d);
-                ok = wait_bounded(bar_d, tc & 1, abort_flag, p.status, WAIT_EPI_TMEM_FULL);
-                ok = __all_sync(0xffffffffu, ok);
-                if (!ok) break;
-            }
-            const float* p_head = p.p + (size_t)t * p.T * p.T;
+            // D of this head's queries: fetched now, published to the other warps just before its first use
+            const float d_mine = (int)threadIdx.x < p.T ? __ldg(p.dvec + (size_t)t * p.T + threadIdx.x) : 0.0f;
             for (int j = 0; j < nblk && ok; ++j, ++jc) {
-                const int key = j * 128 + krow;
                 for (int i = 0; i < nblk; ++i, ++s) {
-                    // P^T for this thread's key and its 64 queries, fetched before the wait so the loads overlap MMA 1
+                    // P^T for this thread's key and its 64 queries, out of the block the producer copied in
                     float pt[64];
+                    ok = wait_bounded(bar_p, s & 1, abort_flag, p.status, WAIT_EPI_TMEM_FULL);
+                    ok = __all_sync(0xffffffffu, ok);
+                    if (!ok) break;
                     {
-                        const int q0 = i * 128 + half * 64;
-                        const float* src = p_head + (size_t)q0 * p.T + key;
+                        const int q0 = half * 64;                // row of the block; rows and keys past T hold zeros or are skipped
+                        const uint32_t src = ds_smem + (uint32_t(q0) * p.pbox + krow) * 4;
 #pragma unroll
                         for (int c = 0; c < 64; ++c)
-                            pt[c] = (key < p.T && q0 + c < p.T) ? __ldg(src + (size_t)c * p.T) : 0.0f;
+                            pt[c] = (krow < p.pbox && q0 + c < p.pbox) ? ld_shared_f32(src + uint32_t(c) * p.pbox * 4) : 0.0f;
                     }
-                    if (lane == 0) bulk_wait_read_all();     // output stores staged in this warp's dS^T blocks have drained
                     __syncwarp();
+                    if (lane == 0) mbar_arrive(bar_pr);
+                    if ((i | j) == 0) {
+                        // every warp is past the previous tile's last element pass (its outputs were read after that
+                        // step's MMAs, which waited for all eight warps), so the D array may be rewritten
+                        d_sm[threadIdx.x] = d_mine;
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(bar_d);
+                        ok = wait_bounded(bar_d, tc & 1, abort_flag, p.status, WAIT_EPI_TMEM_FULL);
+                        ok = __all_sync(0xffffffffu, ok);
+                        if (!ok) break;
+                    }
                     ok = wait_bounded(bar_dp, s & 1, abort_flag, p.status, WAIT_EPI_TMEM_FULL);
                     ok = __all_sync(0xffffffffu, ok);
                     if (!ok) break;
                     tc_fence_after_sync();
+                    ok = wait_bounded(bar_pr, s & 1, abort_flag, p.status, WAIT_EPI_TMEM_FULL);   // nobody still reads P
+                    ok = __all_sync(0xffffffffu, ok);
+                    if (!ok) break;
 #pragma unroll
                     for (int c2 = 0; c2 < 2; ++c2) {
                         const int cc = half * 2 + c2;            // 32-query chunk of the block
@@ -318,6 +384,7 @@ attention_bwd_tf32_kernel(const __grid_constant__ CUtensorMap tm_v, const __grid
                         }
                     }
                     tc_fence_before_sync();
+                    if (lane == 0) bulk_wait_read_all();       // the staging blocks go back to the producer (next P block)
                     __syncwarp();
                     if (lane == 0) mbar_arrive(bar_free);
                 }
@@ -357,7 +424,7 @@ int launch_attention_backward_fused(te_b200_ctx* ctx, const te_attn_bwd_desc* t,
     if (t->B * t->H > INT32_MAX) return -1;
     if (!aligned16_view(t->o, t->o_strides) || !aligned16_view(t->d_o, t->d_o_strides)) return -1;
     if (reinterpret_cast<uintptr_t>(t->p) & 15) return -1;
-    CUtensorMap mv, mk, mdok, mdom, mq, mdq, mdk, mdv;
+    CUtensorMap mv, mk, mdok, mdom, mq, mdq, mdk, mdv, mp;
     const auto K_MAJOR = CU_TENSOR_MAP_SWIZZLE_128B, N_MAJOR = CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B;
     if (!make_bhtc_map(ctx, &mv, t->v, t->d, t->T, t->H, t->B, t->v_strides, 32, 128, K_MAJOR)) return -1;
     if (!make_bhtc_map(ctx, &mk, t->k, t->d, t->T, t->H, t->B, t->k_strides, 32, 32, N_MAJOR)) return -1;
@@ -367,14 +434,33 @@ int launch_attention_backward_fused(te_b200_ctx* ctx, const te_attn_bwd_desc* t,
     if (!make_bhtc_map(ctx, &mdq, t->dq, t->d, t->T, t->H, t->B, t->dq_strides, 32, 32, K_MAJOR)) return -1;
     if (!make_bhtc_map(ctx, &mdk, t->dk, t->d, t->T, t->H, t->B, t->dk_strides, 32, 32, K_MAJOR)) return -1;
     if (!make_bhtc_map(ctx, &mdv, t->dv, t->d, t->T, t->H, t->B, t->dv_strides, 32, 32, K_MAJOR)) return -1;
+    const int64_t p_strides[3] = {t->H * t->T * t->T, t->T * t->T, t->T};
+    if (!make_bhtc_map(ctx, &mp, t->p, t->T, t->T, t->H, t->B, p_strides, (int)(t->T < 128 ? t->T : 128),
+                       (int)(t->T < 128 ? t->T : 128), CU_TENSOR_MAP_SWIZZLE_NONE)) return -1;
     AttnBwdParams p;
     p.T = (int)t->T; p.d = (int)t->d; p.H = (int)t->H; p.B = (int)t->B;
     p.nblk = (int)((t->T + 127) / 128);
     p.total_tiles = (int)(t->B * t->H);
     p.inv_scale = 1.0f / sqrtf((float)t->d);
-    p.p = t->p; p.o = t->o; p.d_o = t->d_o;
-    for (int i = 0; i < 3; ++i) { p.o_s[i] = t->o_strides[i]; p.do_s[i] = t->d_o_strides[i]; }
+    p.pbox = (int)(t->T < 128 ? t->T : 128);
     p.status = ctx->d_status;
+    // D lives at the end of the context workspace
+    const long long rows = (long long)t->B * t->H * t->T;
+    const size_t d_bytes = ((size_t)rows * sizeof(float) + 255) & ~size_t(255);
+    if (d_bytes > ctx->workspace_bytes) return -1;
+    float* dvec = reinterpret_cast<float*>(static_cast<char*>(ctx->workspace) + ctx->workspace_bytes - d_bytes);
+    p.dvec = dvec;
+    {
+        const int rpi = 32 / ((int)t->d / 4);
+        long long blocks = (rows + 8 * rpi - 1) / (8 * rpi);
+        if (blocks > (long long)ctx->sm_count * 16) blocks = (long long)ctx->sm_count * 16;
+        rowdot_bht_kernel<<<(unsigned)blocks, 256, 0, stream>>>(t->d_o, t->d_o_strides[0], t->d_o_strides[1], t->d_o_strides[2],
+                                                                 t->o, t->o_strides[0], t->o_strides[1], t->o_strides[2], dvec,
+                                                                 (int)t->H, (int)t->T, (int)t->d, rows);
+        cudaError_t e = cudaGetLastError();
+        if (e != cudaSuccess) return cuda_fail(e, "rowdot_bht_kernel launch");
+        ctx->launches += 1;
+    }
     const int dchunks = p.d / 32;
     const int smem = 1024 + 5 * dchunks * BWD_CHUNK + 4 * BWD_CHUNK + 1024 + 128;
     if (smem > 232448) return -1;
@@ -385,7 +471,7 @@ int launch_attention_backward_fused(te_b200_ctx* ctx, const te_attn_bwd_desc* t,
         attr_smem[ctx->device] = smem;
     }
     const int grid = p.total_tiles < ctx->sm_count ? p.total_tiles : ctx->sm_count;
-    attention_bwd_tf32_kernel<<<grid, CTA_THREADS, smem, stream>>>(mv, mk, mdok, mdom, mq, mdq, mdk, mdv, p);
+    attention_bwd_tf32_kernel<<<grid, CTA_THREADS, smem, stream>>>(mv, mk, mdok, mdom, mq, mdq, mdk, mdv, mp, p);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return cuda_fail(e, "attention_bwd_tf32_kernel launch");
     ctx->launches += 1;

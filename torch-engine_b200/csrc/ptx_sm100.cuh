@@ -58,6 +58,11 @@ __device__ __forceinline__ void tma_load_4d(uint32_t dst_smem, const void* tmap,
         "r"(c2), "r"(c3)
         : "memory");
 }
+__device__ __forceinline__ float ld_shared_f32(uint32_t addr) {
+    float v;
+    asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(addr) : "memory");
+    return v;
+}
 __device__ __forceinline__ void tma_prefetch_desc(const void* tmap) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(tmap)) : "memory");
 }
