@@ -231,6 +231,45 @@ typedef struct te_attn_bwd_desc {
 } te_attn_bwd_desc;
 TE_API int te_b200_attention_backward(te_b200_ctx* ctx, const te_attn_bwd_desc* d, te_stream_t stream);
 
+/* ---- the GPT step's kernels around the matmuls ------------------------------- */
+/* Not matmuls, but what a training step of the reference's GPT runs between them; with the
+ * GEMMs and attention on this backend they were what bounded the step.  All reductions run in
+ * a fixed order (the reference's CUDA kernels use atomicAdd). */
+
+/* y = (x - mean) / sqrt(var + eps) * gamma + beta over the last dimension of x [rows, cols],
+ * biased variance.  LayerNorm::forward (src/nn/layernorm.cpp:19-82; kernel
+ * src/cuda/elementwise_cuda.cu:2497-2521).  cols <= 1024. */
+TE_API int te_b200_layernorm_forward(te_b200_ctx* ctx, const float* x, const float* gamma,
+                              const float* beta, float* y, int64_t rows, int64_t cols, float eps,
+                              te_stream_t stream);
+/* {dx, dgamma, dbeta} from x, gamma and the upstream gradient dy; mean and variance are
+ * recomputed from x as LayerNormBackward::backward does (src/core/grad_fn.cpp:405-538; kernel
+ * elementwise_cuda.cu:2523-2568).  dgamma / dbeta may be NULL.  Uses the context workspace. */
+TE_API int te_b200_layernorm_backward(te_b200_ctx* ctx, const float* x, const float* gamma,
+                               const float* dy, float* dx, float* dgamma, float* dbeta,
+                               int64_t rows, int64_t cols, float eps, te_stream_t stream);
+/* out[i][:] = table[tokens[i]][:] (+ pos[i % seq_len][:] when pos is not NULL) for n int64
+ * tokens: Embedding::forward (src/nn/embedding.cpp:18-60) with the positional sum of
+ * GPT::forward (src/nn/gpt.cpp:30-69) folded in.  An index outside [0, vocab) writes zeros and
+ * is reported by te_b200_check_device_status ("Embedding index out of range"). */
+TE_API int te_b200_embedding_forward(te_b200_ctx* ctx, const float* table, const int64_t* tokens,
+                              const float* pos, float* out, int64_t n, int64_t seq_len,
+                              int64_t dim, int64_t vocab, te_stream_t stream);
+/* dtable[v][:] = sum of dout[i][:] over the positions with tokens[i] == v, added in ascending i
+ * (the order of EmbeddingBackward's CPU loop, src/core/grad_fn.cpp:745-757); dtable is fully
+ * overwritten.  Cost grows with vocab * n: meant for the reference's small vocabularies. */
+TE_API int te_b200_embedding_backward(te_b200_ctx* ctx, const int64_t* tokens, const float* dout,
+                               float* dtable, int64_t n, int64_t dim, int64_t vocab,
+                               te_stream_t stream);
+/* Mean cross-entropy of logits [rows, vocab] against int64 targets [rows] into the device float
+ * *loss (may be NULL), and, when dlogits is not NULL, its gradient
+ * (softmax - one_hot) * upstream / rows.  crossEntropyLoss::forward_batched
+ * (src/loss/CrossEntropyLoss.cpp:47-127) and CrossEntropyBatchedBackward
+ * (src/core/grad_fn.cpp:271-346).  Uses the context workspace. */
+TE_API int te_b200_cross_entropy(te_b200_ctx* ctx, const float* logits, const int64_t* targets,
+                          float* loss, float* dlogits, float upstream, int64_t rows, int64_t vocab,
+                          te_stream_t stream);
+
 /* ---- sharding helpers (multi-GPU: one process per GPU) ----------------------- */
 
 /* Splits `total` units (N columns, or batch indices) over `world` ranks in blocks that are

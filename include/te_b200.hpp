@@ -8,15 +8,17 @@
 //   te::FeedForward     Linear -> GELU -> Linear                           (reference src/nn/ffn.cpp:12-16)
 //   te::ScaledDot       softmax(Q.K^T / sqrt(d)).V and its backward        (reference src/nn/scaledot.cpp:8-27)
 // Errors surface as std::runtime_error with the reference's texts (src/tensor/tensor.h:537, :547, :626, :858).
-// Tensors live on the GPU only: this backend has no CPU compute path.  Each Tensor owns (or shares) one
-// cudaMalloc'ed buffer, as the reference's CUDAAllocator does (src/core/allocators.h:35-52).
+// Tensors live on the GPU only: this backend has no CPU compute path.  Each Tensor owns (or shares) one device
+// buffer from te::CachingAllocator (the reference's CUDAAllocator calls cudaMalloc per tensor, src/core/allocators.h:35-52).
 #pragma once
 #include <cuda_runtime.h>
 
 #include <cmath>
 #include <cstdlib>
 #include <cstdint>
+#include <map>
 #include <memory>
+#include <mutex>
 #include <stdexcept>
 #include <string>
 #include <vector>
@@ -61,16 +63,78 @@ private:
     int precision_ = TE_PREC_TF32;
 };
 
+// Device memory for tensors, cached by block size.  The reference's CUDAAllocator calls cudaMalloc / cudaFree for every
+// tensor (src/core/allocators.h:35-52); both synchronise the device, and a training step creates hundreds of
+// temporaries.  Here a freed block goes to a free list of its (rounded) size and the next tensor of that size takes
+// it without touching the driver.  All work of this adapter is issued on the default stream, so a block handed out
+// again is only written by kernels that the stream orders after its last use.
+class CachingAllocator {
+public:
+    static CachingAllocator& instance() {
+        static CachingAllocator* a = new CachingAllocator();   // never destroyed: tensors with static lifetime may outlive any static
+        return *a;
+    }
+    static size_t rounded(size_t bytes) {
+        if (bytes < 512) return 512;
+        if (bytes < (size_t(1) << 20)) return (bytes + 511) & ~size_t(511);
+        return (bytes + (size_t(2) << 20) - 1) & ~((size_t(2) << 20) - 1);      // large blocks in 2 MiB steps
+    }
+    void* allocate(size_t bytes, size_t* block_bytes) {
+        const size_t n = rounded(bytes);
+        *block_bytes = n;
+        {
+            std::lock_guard<std::mutex> g(mu_);
+            auto it = free_.find(n);
+            if (it != free_.end()) {
+                void* p = it->second;
+                free_.erase(it);
+                ++hits_;
+                return p;
+            }
+        }
+        void* p = nullptr;
+        cudaError_t e = cudaMalloc(&p, n);
+        if (e != cudaSuccess) {          // out of memory: give the cached blocks back to the driver and retry once
+            cudaGetLastError();
+            empty_cache();
+            e = cudaMalloc(&p, n);
+        }
+        cuda_check(e, "cudaMalloc");
+        std::lock_guard<std::mutex> g(mu_);
+        ++device_mallocs_;
+        return p;
+    }
+    void release(void* p, size_t block_bytes) {
+        std::lock_guard<std::mutex> g(mu_);
+        free_.emplace(block_bytes, p);
+    }
+    void empty_cache() {
+        std::multimap<size_t, void*> blocks;
+        {
+            std::lock_guard<std::mutex> g(mu_);
+            blocks.swap(free_);
+        }
+        for (auto& kv : blocks) cudaFree(kv.second);
+    }
+    size_t device_mallocs() const { return device_mallocs_; }   // cudaMalloc calls so far
+    size_t cache_hits() const { return hits_; }
+private:
+    CachingAllocator() = default;
+    std::mutex mu_;
+    std::multimap<size_t, void*> free_;
+    size_t device_mallocs_ = 0, hits_ = 0;
+};
+
 class Tensor {
 public:
     Tensor() = default;
     explicit Tensor(std::vector<int64_t> shape) : shape_(std::move(shape)) {
         strides_.assign(shape_.size(), 1);
         for (int i = (int)shape_.size() - 2; i >= 0; --i) strides_[i] = strides_[i + 1] * shape_[i + 1];
-        void* p = nullptr;
         const size_t n = numel();
-        cuda_check(cudaMalloc(&p, (n ? n : 1) * sizeof(float)), "cudaMalloc");
-        storage_ = std::shared_ptr<void>(p, [](void* q) { cudaFree(q); });
+        size_t block = 0;
+        void* p = CachingAllocator::instance().allocate((n ? n : 1) * sizeof(float), &block);
+        storage_ = std::shared_ptr<void>(p, [block](void* q) { CachingAllocator::instance().release(q, block); });
     }
     static Tensor from_host(const std::vector<float>& v, std::vector<int64_t> shape) {
         Tensor t(std::move(shape));

@@ -150,6 +150,69 @@ class Oracle:
                                    C.c_int64(x2d.shape[1]), _fptr(out))
         return out
 
+    def layernorm(self, x, gamma, beta, eps=1e-5):
+        x = np.ascontiguousarray(x, dtype=np.float32)
+        y = np.empty_like(x)
+        D = x.shape[-1]
+        self.lib.oracle_layernorm_forward(_fptr(x), _fptr(np.ascontiguousarray(gamma, dtype=np.float32)),
+                                          _fptr(np.ascontiguousarray(beta, dtype=np.float32)), _fptr(y),
+                                          C.c_int64(x.size // D), C.c_int64(D), C.c_float(eps))
+        return y
+
+    def layernorm_backward(self, x, gamma, dy, eps=1e-5):
+        """(dx, dgamma, dbeta)."""
+        x = np.ascontiguousarray(x, dtype=np.float32)
+        dy = np.ascontiguousarray(dy, dtype=np.float32)
+        gamma = np.ascontiguousarray(gamma, dtype=np.float32)
+        D = x.shape[-1]
+        dx, dg, db, scratch = np.empty_like(x), np.empty(D, np.float32), np.empty(D, np.float32), np.empty(D, np.float32)
+        self.lib.oracle_layernorm_backward(_fptr(x), _fptr(gamma), _fptr(dy), _fptr(dx), _fptr(dg), _fptr(db),
+                                           _fptr(scratch), C.c_int64(x.size // D), C.c_int64(D), C.c_float(eps))
+        return dx, dg, db
+
+    def cross_entropy(self, logits, targets):
+        """Mean loss over the rows of logits [..., V] with int64 targets [...]."""
+        logits = np.ascontiguousarray(logits, dtype=np.float32)
+        targets = np.ascontiguousarray(targets, dtype=np.int64)
+        V = logits.shape[-1]
+        fn = self.lib.oracle_cross_entropy_forward
+        fn.restype = C.c_float
+        return np.float32(fn(_fptr(logits), targets.ctypes.data_as(C.c_void_p), C.c_int64(logits.size // V), C.c_int64(V)))
+
+    def cross_entropy_backward(self, logits, targets, upstream=1.0):
+        logits = np.ascontiguousarray(logits, dtype=np.float32)
+        targets = np.ascontiguousarray(targets, dtype=np.int64)
+        V = logits.shape[-1]
+        grad = np.empty_like(logits)
+        self.lib.oracle_cross_entropy_backward(_fptr(logits), targets.ctypes.data_as(C.c_void_p), C.c_float(upstream),
+                                               _fptr(grad), C.c_int64(logits.size // V), C.c_int64(V))
+        return grad
+
+    def embedding(self, table, tokens, pos=None):
+        """table[tokens] (+ pos[t] broadcast over the batch): tokens [B, T] -> [B, T, D]."""
+        table = np.ascontiguousarray(table, dtype=np.float32)
+        tokens = np.ascontiguousarray(tokens, dtype=np.int64)
+        vocab, D = table.shape
+        T = tokens.shape[-1]
+        out = np.empty(tokens.shape + (D,), dtype=np.float32)
+        pos_c = None if pos is None else np.ascontiguousarray(pos, dtype=np.float32)
+        fn = self.lib.oracle_embedding_forward
+        fn.restype = C.c_int
+        rc = fn(_fptr(table), tokens.ctypes.data_as(C.c_void_p), _fptr(pos_c) if pos_c is not None else None, _fptr(out),
+                C.c_int64(tokens.size), C.c_int64(T), C.c_int64(D), C.c_int64(vocab))
+        if rc:
+            raise OracleError(rc, "Embedding index out of range")
+        return out
+
+    def embedding_backward(self, tokens, dout, vocab):
+        tokens = np.ascontiguousarray(tokens, dtype=np.int64)
+        dout = np.ascontiguousarray(dout, dtype=np.float32)
+        D = dout.shape[-1]
+        dtable = np.empty((vocab, D), dtype=np.float32)
+        self.lib.oracle_embedding_backward(tokens.ctypes.data_as(C.c_void_p), _fptr(dout), _fptr(dtable),
+                                           C.c_int64(tokens.size), C.c_int64(D), C.c_int64(vocab))
+        return dtable
+
     # Compositions that follow the reference call sequence.
     def linear(self, x, w, bias, gelu=False):
         """Linear::forward (+ Tensor::gelu): x . w^T through the transposed view, then the broadcast bias add."""
@@ -273,6 +336,44 @@ class Reference:
         self._check(self.lib.ref_linear(_fptr(x), _i64(x.shape), x.ndim, _fptr(w), _fptr(bias), C.c_int64(in_f),
                                         C.c_int64(out_f), int(gelu), _fptr(dy) if dy is not None else None,
                                         p("y"), p("preact"), p("dx"), p("dw"), p("db")))
+        return res
+
+    def layernorm(self, x, gamma, beta, eps=1e-5, dy=None):
+        x = np.ascontiguousarray(x, dtype=np.float32)
+        gamma, beta = (np.ascontiguousarray(t, dtype=np.float32) for t in (gamma, beta))
+        D = x.shape[-1]
+        res = {"y": np.empty_like(x)}
+        if dy is not None:
+            dy = np.ascontiguousarray(dy, dtype=np.float32)
+            res.update(dx=np.empty_like(x), dgamma=np.empty_like(gamma), dbeta=np.empty_like(beta))
+        p = lambda k: _fptr(res[k]) if k in res else None
+        self._check(self.lib.ref_layernorm(_fptr(x), C.c_int64(x.size // D), C.c_int64(D), _fptr(gamma), _fptr(beta),
+                                           C.c_float(eps), _fptr(dy) if dy is not None else None, p("y"), p("dx"),
+                                           p("dgamma"), p("dbeta")))
+        return res
+
+    def cross_entropy(self, logits, targets, want_grad=True):
+        logits = np.ascontiguousarray(logits, dtype=np.float32)
+        targets = np.ascontiguousarray(targets, dtype=np.int64)
+        B, T, V = logits.shape
+        loss = C.c_float(0)
+        grad = np.empty_like(logits) if want_grad else None
+        self._check(self.lib.ref_cross_entropy(_fptr(logits), targets.ctypes.data_as(C.c_void_p), C.c_int64(B), C.c_int64(T),
+                                               C.c_int64(V), C.byref(loss), _fptr(grad) if want_grad else None))
+        return {"loss": np.float32(loss.value), "dlogits": grad}
+
+    def embedding(self, table, tokens, dout=None):
+        table = np.ascontiguousarray(table, dtype=np.float32)
+        tokens = np.ascontiguousarray(tokens, dtype=np.int64)
+        vocab, D = table.shape
+        B, T = tokens.shape
+        res = {"out": np.empty((B, T, D), dtype=np.float32)}
+        if dout is not None:
+            dout = np.ascontiguousarray(dout, dtype=np.float32)
+            res["dtable"] = np.empty_like(table)
+        self._check(self.lib.ref_embedding(_fptr(table), C.c_int64(vocab), C.c_int64(D), tokens.ctypes.data_as(C.c_void_p),
+                                           C.c_int64(B), C.c_int64(T), _fptr(dout) if dout is not None else None,
+                                           _fptr(res["out"]), _fptr(res["dtable"]) if dout is not None else None))
         return res
 
     def ffn(self, x, w1, b1, w2, b2, dy=None):

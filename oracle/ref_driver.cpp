@@ -16,6 +16,8 @@
 #include "nn/scaledot.h"
 #include "nn/multi_head_attention.h"
 #include "nn/gpt.h"
+#include "nn/layernorm.h"
+#include "nn/embedding.h"
 #include "loss/CrossEntropyLoss.h"
 
 #define REF_API extern "C" __attribute__((visibility("default")))
@@ -187,6 +189,63 @@ REF_API int ref_scaled_dot(const float* q, const RefView* vq, const float* k, co
         if (d_o) {
             backward_with(O, d_o);
             copy_grad(Qb, dq); copy_grad(Kb, dk); copy_grad(Vb, dv);
+        }
+    });
+}
+
+// LayerNorm::forward + LayerNormBackward over x [rows, D].  dy NULL -> forward only.
+REF_API int ref_layernorm(const float* x, int64_t rows, int64_t D, const float* gamma, const float* beta, float eps,
+                          const float* dy, float* y, float* dx, float* dgamma, float* dbeta) {
+    return guarded([&] {
+        LayerNorm ln(D, DType::Float32, eps);
+        auto p = ln.parameters();
+        std::memcpy(p[0].data(), gamma, sizeof(float) * D);
+        std::memcpy(p[1].data(), beta, sizeof(float) * D);
+        Tensor X = from_host(x, {rows, D});
+        X.setRequiresGrad(true);
+        Tensor Y = ln.forward(X);
+        if (y) copy_out(Y, y);
+        if (dy) {
+            backward_with(Y, dy);
+            copy_grad(X, dx);
+            copy_grad(p[0], dgamma);
+            copy_grad(p[1], dbeta);
+        }
+    });
+}
+
+// crossEntropyLoss::forward_batched over logits [B, T, V] and int64 targets [B, T], and its backward (seeded with 1).
+REF_API int ref_cross_entropy(const float* logits, const int64_t* targets, int64_t B, int64_t T, int64_t V, float* loss,
+                              float* dlogits) {
+    return guarded([&] {
+        Tensor L = from_host(logits, {B, T, V});
+        L.setRequiresGrad(true);
+        Tensor tg({B, T}, DType::Int64, Device::CPU);
+        std::memcpy(tg.data(), targets, sizeof(int64_t) * B * T);
+        crossEntropyLoss ce;
+        Tensor l = ce.forward_batched(L, tg);
+        if (loss) *loss = l.at<float>(0);
+        if (dlogits) {
+            l.backward();
+            copy_grad(L, dlogits);
+        }
+    });
+}
+
+// Embedding::forward over int64 tokens [B, T] (+ backward of an upstream gradient dout [B, T, D] into the table).
+REF_API int ref_embedding(const float* table, int64_t vocab, int64_t D, const int64_t* tokens, int64_t B, int64_t T,
+                          const float* dout, float* out, float* dtable) {
+    return guarded([&] {
+        Embedding emb(vocab, D, DType::Float32);
+        auto p = emb.parameters();
+        std::memcpy(p[0].data(), table, sizeof(float) * vocab * D);
+        Tensor tk({B, T}, DType::Int64, Device::CPU);
+        std::memcpy(tk.data(), tokens, sizeof(int64_t) * B * T);
+        Tensor Y = emb.forward(tk);
+        if (out) copy_out(Y, out);
+        if (dout) {
+            backward_with(Y, dout);
+            copy_grad(p[0], dtable);
         }
     });
 }

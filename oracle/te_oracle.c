@@ -181,3 +181,129 @@ ORACLE_API void oracle_colsum_f32(const float* in, int64_t rows, int64_t cols, i
     for (int64_t i = 0; i < rows; ++i)
         for (int64_t j = 0; j < cols; ++j) out[j] += in[i * ld + j];
 }
+
+/* ---- the GPT step's kernels around the matmuls (LayerNorm, embedding, cross-entropy) ------------------------- */
+
+/* LayerNorm::forward on the CPU (src/nn/layernorm.cpp:56-82): float mean, biased float variance, division by
+ * sqrt(var + eps), then * gamma + beta. */
+ORACLE_API void oracle_layernorm_forward(const float* x, const float* gamma, const float* beta, float* y,
+                                         int64_t rows, int64_t D, float eps) {
+    for (int64_t i = 0; i < rows; ++i) {
+        const float* xr = x + i * D;
+        float mean = 0.0f;
+        for (int64_t j = 0; j < D; ++j) mean += xr[j];
+        mean /= D;
+        float variance = 0.0f;
+        for (int64_t j = 0; j < D; ++j) {
+            const float diff = xr[j] - mean;
+            variance += diff * diff;
+        }
+        variance /= D;
+        const float std_dev = sqrtf(variance + eps);
+        for (int64_t j = 0; j < D; ++j) {
+            const float normalized = (xr[j] - mean) / std_dev;
+            y[i * D + j] = normalized * gamma[j] + beta[j];
+        }
+    }
+}
+
+/* LayerNormBackward::backward on the CPU (src/core/grad_fn.cpp:474-538): rows in ascending order accumulate
+ * d_gamma and d_beta in float; dx = (gamma*dy - mean(gamma*dy) - x_hat*mean(gamma*dy*x_hat)) / std. */
+ORACLE_API void oracle_layernorm_backward(const float* x, const float* gamma, const float* dy, float* dx,
+                                          float* dgamma, float* dbeta, float* x_hat_scratch, int64_t rows,
+                                          int64_t D, float eps) {
+    const float N = (float)D;
+    float* x_hat = x_hat_scratch;
+    for (int64_t j = 0; j < D; ++j) dgamma[j] = dbeta[j] = 0.0f;
+    for (int64_t b = 0; b < rows; ++b) {
+        const float* xr = x + b * D;
+        const float* dyr = dy + b * D;
+        float* dxr = dx + b * D;
+        float mean = 0.0f;
+        for (int64_t j = 0; j < D; ++j) mean += xr[j];
+        mean /= N;
+        float var = 0.0f;
+        for (int64_t j = 0; j < D; ++j) {
+            const float d = xr[j] - mean;
+            var += d * d;
+        }
+        var /= N;
+        const float std_val = sqrtf(var + eps);
+        for (int64_t j = 0; j < D; ++j) x_hat[j] = (xr[j] - mean) / std_val;
+        for (int64_t j = 0; j < D; ++j) {
+            dgamma[j] += dyr[j] * x_hat[j];
+            dbeta[j] += dyr[j];
+        }
+        float mean_g_dy = 0.0f, mean_g_dy_xhat = 0.0f;
+        for (int64_t j = 0; j < D; ++j) {
+            const float g_dy = gamma[j] * dyr[j];
+            mean_g_dy += g_dy;
+            mean_g_dy_xhat += g_dy * x_hat[j];
+        }
+        mean_g_dy /= N;
+        mean_g_dy_xhat /= N;
+        for (int64_t j = 0; j < D; ++j)
+            dxr[j] = (gamma[j] * dyr[j] - mean_g_dy - x_hat[j] * mean_g_dy_xhat) / std_val;
+    }
+}
+
+/* crossEntropyLoss::forward_batched on the CPU (src/loss/CrossEntropyLoss.cpp:100-124): per row float max, float
+ * sum of expf, the row losses added in double in row order, mean cast to float. */
+ORACLE_API float oracle_cross_entropy_forward(const float* logits, const int64_t* targets, int64_t rows, int64_t V) {
+    double total = 0.0;
+    for (int64_t n = 0; n < rows; ++n) {
+        const float* row = logits + n * V;
+        float max_logit = row[0];
+        for (int64_t v = 1; v < V; ++v) max_logit = row[v] > max_logit ? row[v] : max_logit;
+        float sum_exp = 0.0f;
+        for (int64_t v = 0; v < V; ++v) sum_exp += expf(row[v] - max_logit);
+        const float log_sum_exp = max_logit + logf(sum_exp);
+        total += (double)(-row[targets[n]] + log_sum_exp);
+    }
+    return (float)(total / (double)rows);
+}
+
+/* CrossEntropyBatchedBackward::backward on the CPU (src/core/grad_fn.cpp:295, :322-343):
+ * grad = (softmax - one_hot) * (upstream / rows). */
+ORACLE_API void oracle_cross_entropy_backward(const float* logits, const int64_t* targets, float upstream,
+                                              float* grad, int64_t rows, int64_t V) {
+    const float scale = upstream / (float)rows;
+    for (int64_t n = 0; n < rows; ++n) {
+        const float* row = logits + n * V;
+        float max_logit = row[0];
+        for (int64_t v = 1; v < V; ++v) max_logit = row[v] > max_logit ? row[v] : max_logit;
+        float sum_exp = 0.0f;
+        for (int64_t v = 0; v < V; ++v) sum_exp += expf(row[v] - max_logit);
+        for (int64_t v = 0; v < V; ++v) {
+            const float softmax_val = expf(row[v] - max_logit) / sum_exp;
+            const float one_hot = (v == targets[n]) ? 1.0f : 0.0f;
+            grad[n * V + v] = (softmax_val - one_hot) * scale;
+        }
+    }
+}
+
+/* Token embedding lookup plus the broadcast positional table, as GPT::forward composes them
+ * (src/nn/embedding.cpp:51-59, src/nn/gpt.cpp:30-69): out[i][j] = table[tokens[i]][j] + pos[i % T][j].
+ * pos may be NULL (plain Embedding::forward).  Returns non-zero for an index out of range. */
+ORACLE_API int oracle_embedding_forward(const float* table, const int64_t* tokens, const float* pos, float* out,
+                                        int64_t n, int64_t T, int64_t D, int64_t vocab) {
+    for (int64_t i = 0; i < n; ++i) {
+        const int64_t idx = tokens[i];
+        if (idx < 0 || idx >= vocab) return ORACLE_ERR_ARG;
+        for (int64_t j = 0; j < D; ++j)
+            out[i * D + j] = pos ? table[idx * D + j] + pos[(i % T) * D + j] : table[idx * D + j];
+    }
+    return ORACLE_OK;
+}
+
+/* EmbeddingBackward::backward on the CPU (src/core/grad_fn.cpp:745-757): rows of the upstream gradient are added
+ * into the table gradient in token order; out-of-range indices are skipped. */
+ORACLE_API void oracle_embedding_backward(const int64_t* tokens, const float* dout, float* dtable, int64_t n,
+                                          int64_t D, int64_t vocab) {
+    for (int64_t k = 0; k < vocab * D; ++k) dtable[k] = 0.0f;
+    for (int64_t i = 0; i < n; ++i) {
+        const int64_t idx = tokens[i];
+        if (idx < 0 || idx >= vocab) continue;
+        for (int64_t j = 0; j < D; ++j) dtable[idx * D + j] += dout[i * D + j];
+    }
+}

@@ -122,6 +122,25 @@ int main() {
         expect_values("ScaledDot backward dQ", grads[0], zeros, 1e-6f);
         expect_values("ScaledDot backward dK", grads[1], zeros, 1e-6f);
         }
+        // Temporaries of a repeated step come out of the allocator's cache: no further cudaMalloc after the first pass.
+        {
+            Tensor x = Tensor::from_host(std::vector<float>(64 * 48, 0.5f), {64, 48});
+            Tensor w = Tensor::from_host(std::vector<float>(48 * 32, 0.25f), {48, 32});
+            auto step = [&]() { Tensor y = x.matmul(w); Tensor z = y.matmul(w.transpose_view(0, 1)); return z.to_host()[0]; };
+            const float first = step();
+            const size_t mallocs = te::CachingAllocator::instance().device_mallocs();
+            const size_t hits = te::CachingAllocator::instance().cache_hits();
+            float last = first;
+            for (int it = 0; it < 10; ++it) last = step();
+            if (te::CachingAllocator::instance().device_mallocs() != mallocs || te::CachingAllocator::instance().cache_hits() < hits + 20 ||
+                last != first) {
+                std::cout << "FAIL caching allocator: " << te::CachingAllocator::instance().device_mallocs() - mallocs
+                          << " new cudaMalloc calls in 10 repeated steps\n";
+                ++failures;
+            } else {
+                std::cout << "ok   caching allocator reuses blocks\n";
+            }
+        }
         te::Backend::instance().synchronize();
     } catch (const std::exception& e) {
         std::cout << "FAIL unexpected exception: " << e.what() << "\n";

@@ -77,6 +77,24 @@ def nn_inputs(seed=42):
     return dict(linear=lin, ffn=ffn, scaled_dot=sd, mha=mha)
 
 
+def step_op_inputs(seed=7):
+    """Inputs of the LayerNorm / embedding / cross-entropy cases (the GPT step's kernels around the matmuls) and of
+    one attention backward case inside the fused kernel's limits."""
+    rng = binding.SeededRng(seed)
+    ln = {}
+    for tag, shape in (("ln48", (5, 7, 48)), ("ln50", (4, 6, 50)), ("ln384", (2, 5, 384))):
+        D = shape[-1]
+        ln[tag] = dict(x=rng.normal(shape, 0.3, 1.7), gamma=rng.normal((D,), 1.0, 0.3), beta=rng.normal((D,), 0.0, 0.2),
+                       dy=rng.normal(shape))
+    ce = dict(logits=rng.normal((3, 9, 65), 0.0, 2.5), targets=rng.tokens((3, 9), 65))
+    emb = dict(table=rng.normal((65, 24)), tokens=rng.tokens((4, 10), 65), dout=rng.normal((4, 10, 24)),
+               pos=rng.normal((10, 24)))
+    B, H, T, d = 1, 2, 64, 32
+    att = dict(B=B, H=H, T=T, d=d, q=rng.normal((B, H, T, d)), k=rng.normal((B, H, T, d)), v=rng.normal((B, H, T, d)),
+               d_o=rng.normal((B, H, T, d)))
+    return dict(ln=ln, ce=ce, emb=emb, att=att)
+
+
 GPT_TINY = dict(vocab=65, max_seq=16, E=32, H=4, L=2, ff=128, batch=3, seq=16)
 
 

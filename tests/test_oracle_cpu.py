@@ -147,3 +147,27 @@ def test_seeded_rng_matches_reference_first_values():
     r = binding.SeededRng(42)
     v = r.uniform((4,))
     assert np.allclose(v, [-0.25091976, 0.593086, 0.9014286, -0.63313043], atol=1e-7)
+
+
+def test_step_op_restatements_match_reference_golden(oracle):
+    """LayerNorm, embedding and cross-entropy restatements against outputs of the compiled reference
+    (tests/golden/step_ops.npz, written by tests/golden/make_golden_step_ops.py): bit for bit."""
+    g = np.load(os.path.join(GOLD, "step_ops.npz"))
+    inp = gc.step_op_inputs()
+    for tag, c in inp["ln"].items():
+        assert np.array_equal(oracle.layernorm(c["x"], c["gamma"], c["beta"]), g[f"{tag}.y"]), tag
+        dx, dg, db = oracle.layernorm_backward(c["x"], c["gamma"], c["dy"])
+        assert np.array_equal(dx, g[f"{tag}.dx"]) and np.array_equal(dg, g[f"{tag}.dgamma"]) and np.array_equal(db, g[f"{tag}.dbeta"]), tag
+    ce = inp["ce"]
+    assert oracle.cross_entropy(ce["logits"], ce["targets"]) == g["ce.loss"]
+    assert np.array_equal(oracle.cross_entropy_backward(ce["logits"], ce["targets"]), g["ce.dlogits"])
+    e = inp["emb"]
+    assert np.array_equal(oracle.embedding(e["table"], e["tokens"]), g["emb.out"])
+    assert np.array_equal(oracle.embedding_backward(e["tokens"], e["dout"], 65), g["emb.dtable"])
+    assert np.array_equal(oracle.embedding(e["table"], e["tokens"], pos=e["pos"]),
+                          (g["emb.out"] + e["pos"][None]).astype(np.float32))
+    with pytest.raises(binding.OracleError):
+        oracle.embedding(e["table"], np.array([[65]]))
+    a = inp["att"]
+    o, _ = oracle.scaled_dot(a["q"], a["k"], a["v"])
+    assert np.array_equal(o, g["att.o"])

@@ -201,6 +201,26 @@ def main():
     record_stream("b200_gelu_backward", 3 * 4.0 * act.numel(), tb, tm, "16384x3072")
     tb, tm = time_gpu(lambda: be.colsum(act), 20)
     record_stream("b200_colsum", 4.0 * act.numel(), tb, tm, "16384x3072")
+    # ---- the GPT step's kernels around the matmuls, at the GPT configuration's sizes scaled past L2 where it matters ----
+    xn = torch.randn(65536, 384, device="cuda", generator=gen)                      # 100.7 MB
+    gam, bet = torch.ones(384, device="cuda"), torch.zeros(384, device="cuda")
+    tb, tm = time_gpu(lambda: be.layernorm(xn, gam, bet), 20)
+    record_stream("b200_layernorm", 2 * 4.0 * xn.numel(), tb, tm, "65536x384")
+    dyn = torch.randn_like(xn)
+    tb, tm = time_gpu(lambda: be.layernorm_backward(xn, gam, dyn), 20)
+    record_stream("b200_layernorm_backward", 3 * 4.0 * xn.numel(), tb, tm, "65536x384")
+    lg = torch.randn(16384, 65, device="cuda", generator=gen)
+    tg = torch.randint(0, 65, (16384,), device="cuda", generator=gen)
+    tb, tm = time_gpu(lambda: be.cross_entropy(lg, tg), 50)
+    record_stream("b200_cross_entropy_fwd_bwd", 2 * 4.0 * lg.numel() + 8.0 * tg.numel(), tb, tm, "16384x65")
+    table = torch.randn(65, 384, device="cuda", generator=gen)
+    tok = torch.randint(0, 65, (64, 256), device="cuda", generator=gen)
+    pe = torch.randn(256, 384, device="cuda", generator=gen)
+    tb, tm = time_gpu(lambda: be.embedding(table, tok, pe), 50)
+    record_stream("b200_embedding_plus_pos", 4.0 * 16384 * 384 + 8.0 * 16384, tb, tm, "16384 tokens x 384")
+    d_emb = torch.randn(64, 256, 384, device="cuda", generator=gen)
+    tb, tm = time_gpu(lambda: be.embedding_backward(tok, d_emb, 65), 50)
+    record_stream("b200_embedding_backward", 4.0 * 16384 * 384 + 8.0 * 16384, tb, tm, "16384 tokens x 384, vocab 65")
     be.check_device_status()
     os.makedirs(os.path.dirname(args.out), exist_ok=True)
     with open(args.out, "w") as f:

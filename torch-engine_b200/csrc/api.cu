@@ -272,6 +272,7 @@ int te_b200_check_device_status(te_b200_ctx* ctx) {
     if (e != cudaSuccess) return cuda_fail(e, "cudaMemcpy(status)");
     if (h != 0) {
         cudaMemset(ctx->d_status, 0, sizeof(int));
+        if (h == 201) return fail(TE_ERR_BAD_ARGUMENT, "Embedding index out of range");   // src/nn/embedding.cpp:53-55
         char msg[128];
         snprintf(msg, sizeof msg, "device-side bounded wait gave up (site code %d)", h);
         return fail(TE_ERR_DEVICE_TIMEOUT, msg);
@@ -659,6 +660,52 @@ int te_b200_attention_backward(te_b200_ctx* ctx, const te_attn_bwd_desc* t, te_s
     d.c_stride_outer = t->dk_strides[0]; d.c_stride_inner = t->dk_strides[1];
     d.alpha = scale; d.scale_mode = TE_SCALE_DIV; d.precision = t->precision;
     return gemm_device(ctx, &d, st, tail);
+}
+
+int te_b200_layernorm_forward(te_b200_ctx* ctx, const float* x, const float* gamma, const float* beta, float* y,
+                              int64_t rows, int64_t cols, float eps, te_stream_t stream) {
+    if (!ctx) return fail(TE_ERR_BAD_ARGUMENT, "ctx is NULL");
+    if (rows < 0 || cols < 0) return fail(TE_ERR_BAD_ARGUMENT, "layernorm: negative extent");
+    if (rows == 0 || cols == 0) return TE_OK;
+    if (!x || !gamma || !beta || !y) return fail(TE_ERR_BAD_ARGUMENT, "layernorm: NULL pointer");
+    return launch_layernorm_forward(ctx, x, gamma, beta, y, rows, cols, eps, static_cast<cudaStream_t>(stream));
+}
+
+int te_b200_layernorm_backward(te_b200_ctx* ctx, const float* x, const float* gamma, const float* dy, float* dx,
+                               float* dgamma, float* dbeta, int64_t rows, int64_t cols, float eps, te_stream_t stream) {
+    if (!ctx) return fail(TE_ERR_BAD_ARGUMENT, "ctx is NULL");
+    if (rows < 0 || cols < 0) return fail(TE_ERR_BAD_ARGUMENT, "layernorm backward: negative extent");
+    if (cols == 0) return TE_OK;
+    if (rows > 0 && (!x || !dy || !dx)) return fail(TE_ERR_BAD_ARGUMENT, "layernorm backward: NULL pointer");
+    if (!gamma) return fail(TE_ERR_BAD_ARGUMENT, "layernorm backward: NULL pointer");
+    return launch_layernorm_backward(ctx, x, gamma, dy, dx, dgamma, dbeta, rows, cols, eps, static_cast<cudaStream_t>(stream));
+}
+
+int te_b200_embedding_forward(te_b200_ctx* ctx, const float* table, const int64_t* tokens, const float* pos, float* out,
+                              int64_t n, int64_t seq_len, int64_t dim, int64_t vocab, te_stream_t stream) {
+    if (!ctx) return fail(TE_ERR_BAD_ARGUMENT, "ctx is NULL");
+    if (n < 0 || dim < 0 || vocab < 0 || (pos && seq_len < 1)) return fail(TE_ERR_BAD_ARGUMENT, "embedding: bad extent");
+    if (n == 0 || dim == 0) return TE_OK;
+    if (!table || !tokens || !out) return fail(TE_ERR_BAD_ARGUMENT, "embedding: NULL pointer");
+    return launch_embedding_forward(ctx, table, tokens, pos, out, n, seq_len, dim, vocab, static_cast<cudaStream_t>(stream));
+}
+
+int te_b200_embedding_backward(te_b200_ctx* ctx, const int64_t* tokens, const float* dout, float* dtable, int64_t n,
+                               int64_t dim, int64_t vocab, te_stream_t stream) {
+    if (!ctx) return fail(TE_ERR_BAD_ARGUMENT, "ctx is NULL");
+    if (n < 0 || dim < 0 || vocab < 0) return fail(TE_ERR_BAD_ARGUMENT, "embedding backward: bad extent");
+    if (vocab == 0 || dim == 0) return TE_OK;
+    if (!dtable || (n > 0 && (!tokens || !dout))) return fail(TE_ERR_BAD_ARGUMENT, "embedding backward: NULL pointer");
+    return launch_embedding_backward(ctx, tokens, dout, dtable, n, dim, vocab, static_cast<cudaStream_t>(stream));
+}
+
+int te_b200_cross_entropy(te_b200_ctx* ctx, const float* logits, const int64_t* targets, float* loss, float* dlogits,
+                          float upstream, int64_t rows, int64_t vocab, te_stream_t stream) {
+    if (!ctx) return fail(TE_ERR_BAD_ARGUMENT, "ctx is NULL");
+    if (rows < 0 || vocab < 0) return fail(TE_ERR_BAD_ARGUMENT, "cross-entropy: negative extent");
+    if (rows == 0 || vocab == 0) return TE_OK;
+    if (!logits || !targets) return fail(TE_ERR_BAD_ARGUMENT, "cross-entropy: NULL pointer");
+    return launch_cross_entropy(ctx, logits, targets, loss, dlogits, upstream, rows, vocab, static_cast<cudaStream_t>(stream));
 }
 
 int te_b200_shard_range(int64_t total, int world, int rank, int64_t align, int64_t* out_begin, int64_t* out_count) {

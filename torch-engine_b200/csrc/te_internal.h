@@ -85,4 +85,16 @@ int launch_gelu_backward(te_b200_ctx*, const float* x, const float* dy, float* d
 int launch_colsum(te_b200_ctx*, const float* in, int64_t rows, int64_t cols, int64_t ld, float* out,
                   cudaStream_t);
 
+// norm_embed_loss.cu: the GPT step's kernels around the matmuls
+int launch_layernorm_forward(te_b200_ctx*, const float* x, const float* gamma, const float* beta, float* y, int64_t rows,
+                             int64_t cols, float eps, cudaStream_t);
+int launch_layernorm_backward(te_b200_ctx*, const float* x, const float* gamma, const float* dy, float* dx, float* dgamma,
+                              float* dbeta, int64_t rows, int64_t cols, float eps, cudaStream_t);
+int launch_embedding_forward(te_b200_ctx*, const float* table, const int64_t* tokens, const float* pos, float* out, int64_t n,
+                             int64_t T, int64_t D, int64_t vocab, cudaStream_t);
+int launch_embedding_backward(te_b200_ctx*, const int64_t* tokens, const float* dout, float* dtable, int64_t n, int64_t D,
+                              int64_t vocab, cudaStream_t);
+int launch_cross_entropy(te_b200_ctx*, const float* logits, const int64_t* targets, float* loss, float* grad, float upstream,
+                         int64_t rows, int64_t V, cudaStream_t);
+
 }  // namespace te

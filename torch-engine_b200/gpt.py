@@ -8,9 +8,11 @@ Every matmul of the step runs on this backend through the C ABI:
   * ScaledDot::forward (src/nn/scaledot.cpp:8-27) on the head views of MultiHeadAttention::forward
     (src/nn/multi_head_attention.cpp:19-42, strides [T*E, hd, E, 1], no copies, no mask), and its backward
     (MatMulBackward x2, DivBackward, SoftmaxBackward) as te_b200_attention_backward.
-What is not a matmul in the reference (embedding gather, sinusoidal position table, pre-LN LayerNorm, residual
-adds, the mean cross-entropy) stays outside the backend and is evaluated with stock torch ops, as those kernels
-stay with the reference.  Parameters come in GPT::parameters() order (src/nn/gpt.cpp:88-113).
+The step's kernels around the matmuls run on the backend as well: token embedding with the positional sum
+(src/nn/embedding.cpp:18-60, src/nn/gpt.cpp:30-69), pre-LN LayerNorm forward / backward (src/nn/layernorm.cpp:19-82,
+src/core/grad_fn.cpp:405-538) and the mean cross-entropy with its gradient (src/loss/CrossEntropyLoss.cpp:47-127,
+src/core/grad_fn.cpp:271-346).  Residual adds, the head merge copy and gradient accumulation stay stock torch ops.
+Parameters come in GPT::parameters() order (src/nn/gpt.cpp:88-113).
 """
 
 import torch
@@ -53,26 +55,76 @@ class _ScaledDot(torch.autograd.Function):
         return dq, dk, dv, None, None
 
 
+class _LayerNorm(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, g, b, be, eps):
+        ctx.save_for_backward(x, g)
+        ctx.be, ctx.eps = be, eps
+        return be.layernorm(x, g, b, eps)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, g = ctx.saved_tensors
+        dx, dg, db = ctx.be.layernorm_backward(x, g, dy, ctx.eps)
+        return dx, dg, db, None, None
+
+
+class _Embedding(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, table, tokens, pos, be):
+        ctx.save_for_backward(tokens)
+        ctx.be, ctx.vocab = be, table.shape[0]
+        return be.embedding(table, tokens, pos)
+
+    @staticmethod
+    def backward(ctx, dout):
+        (tokens,) = ctx.saved_tensors
+        return ctx.be.embedding_backward(tokens, dout, ctx.vocab), None, None, None
+
+
+class _CrossEntropy(torch.autograd.Function):
+    """Loss and gradient come out of one pass over the logits; backward scales the stored gradient by the upstream
+    value (1 for a plain loss.backward())."""
+    @staticmethod
+    def forward(ctx, logits, targets, be):
+        loss, grad = be.cross_entropy(logits, targets)
+        ctx.save_for_backward(grad)
+        return loss.reshape(())
+
+    @staticmethod
+    def backward(ctx, upstream):
+        (grad,) = ctx.saved_tensors
+        return grad * upstream, None, None
+
+
 def linear(be, x, w, b, prec, gelu=False):
     return _Linear.apply(x, w, b, be, prec, gelu)
 
 
+_POS_TABLES = {}
+
+
 def positional_table(seq_len, d_model, device):
     """PositionalEmbedding::init_positional_embeddings (src/nn/positional_embedding.cpp:18-36): the exponent uses
-    the column index itself for even and odd columns alike."""
+    the column index itself for even and odd columns alike.  Built once per (length, width, device), as the reference
+    builds it in the constructor."""
+    key = (seq_len, d_model, str(device))
+    if key not in _POS_TABLES:
+        _POS_TABLES[key] = _positional_table(seq_len, d_model).to(device)
+    return _POS_TABLES[key]
+
+
+def _positional_table(seq_len, d_model):
     pos = torch.arange(seq_len, dtype=torch.float32).unsqueeze(1)
     i = torch.arange(d_model, dtype=torch.float32).unsqueeze(0)
     div = torch.exp(torch.log(torch.tensor(10000.0)) * (2.0 * (i / 2.0)) / float(d_model))
     ang = pos / div
-    pe = torch.where((torch.arange(d_model) % 2 == 0).unsqueeze(0), torch.sin(ang), torch.cos(ang))
-    return pe.to(device)
+    return torch.where((torch.arange(d_model) % 2 == 0).unsqueeze(0), torch.sin(ang), torch.cos(ang))
 
 
-def layer_norm(x, g, b, eps=1e-5):
+def layer_norm(be, x, g, b, eps=1e-5):
     """LayerNorm::forward (src/nn/layernorm.cpp:19-77): biased variance, (x-mean)/sqrt(var+eps)*g+b."""
-    mean = x.mean(dim=-1, keepdim=True)
-    var = ((x - mean) ** 2).mean(dim=-1, keepdim=True)
-    return (x - mean) / torch.sqrt(var + eps) * g + b
+    return _LayerNorm.apply(x, g, b, be, eps)
 
 
 def split_params(flat, vocab, E, n_layers, ff):
@@ -98,29 +150,29 @@ def gpt_forward(be, params, tokens, E, H, n_layers, prec="tf32"):
     hd = E // H
     it = iter(params)
     emb = next(it)
-    x = emb[tokens] + positional_table(T, E, tokens.device).unsqueeze(0)          # gpt.cpp:29-68
+    x = _Embedding.apply(emb, tokens, positional_table(T, E, tokens.device), be)   # gpt.cpp:29-68
     for _ in range(n_layers):                                                     # transformer_block.cpp:15-35
         g1, b1 = next(it), next(it)
         wq, bq, wk, bk, wv, bv, wo, bo = (next(it) for _ in range(8))
         g2, b2 = next(it), next(it)
         w1, c1, w2, c2 = (next(it) for _ in range(4))
-        h = layer_norm(x, g1, b1)
+        h = layer_norm(be, x, g1, b1)
         heads = lambda t: t.view(B, T, H, hd).transpose(1, 2)                      # zero-copy head views
         q, k, v = (heads(linear(be, h, w, b, prec)) for w, b in ((wq, bq), (wk, bk), (wv, bv)))
         o = _ScaledDot.apply(q, k, v, be, prec)                                    # [B,H,T,hd]
         o = o.transpose(1, 2).reshape(B, T, E)
         x = x + linear(be, o, wo, bo, prec)
-        h = layer_norm(x, g2, b2)
+        h = layer_norm(be, x, g2, b2)
         x = x + linear(be, linear(be, h, w1, c1, prec, gelu=True), w2, c2, prec)
     gf, bf, wh, bh = (next(it) for _ in range(4))
-    return linear(be, layer_norm(x, gf, bf), wh, bh, prec)
+    return linear(be, layer_norm(be, x, gf, bf), wh, bh, prec)
 
 
 def gpt_step(be, flat_params, tokens, targets, vocab, E, H, n_layers, ff, prec="tf32"):
     """One forward + backward.  Returns (loss, logits, flat gradient in parameter order)."""
     params = split_params(flat_params, vocab, E, n_layers, ff)
     logits = gpt_forward(be, params, tokens, E, H, n_layers, prec)
-    loss = torch.nn.functional.cross_entropy(logits.reshape(-1, vocab), targets.reshape(-1))   # mean over B*T
+    loss = _CrossEntropy.apply(logits, targets, be)                                             # mean over B*T
     loss.backward()
     grads = torch.cat([p.grad.reshape(-1) for p in params])
     return loss.detach(), logits.detach(), grads

@@ -90,6 +90,11 @@ SIGNATURES = {
                                           C.c_void_p, C.c_int64, C.c_int64, C.c_int64, C.c_int, C.c_void_p]),
     "te_b200_attention_forward": (C.c_int, [C.c_void_p, C.POINTER(AttnDesc), C.c_void_p]),
     "te_b200_attention_backward": (C.c_int, [C.c_void_p, C.POINTER(AttnBwdDesc), C.c_void_p]),
+    "te_b200_layernorm_forward": (C.c_int, [C.c_void_p] + [C.c_void_p] * 4 + [C.c_int64, C.c_int64, C.c_float, C.c_void_p]),
+    "te_b200_layernorm_backward": (C.c_int, [C.c_void_p] + [C.c_void_p] * 6 + [C.c_int64, C.c_int64, C.c_float, C.c_void_p]),
+    "te_b200_embedding_forward": (C.c_int, [C.c_void_p] + [C.c_void_p] * 4 + [C.c_int64] * 4 + [C.c_void_p]),
+    "te_b200_embedding_backward": (C.c_int, [C.c_void_p] + [C.c_void_p] * 3 + [C.c_int64] * 3 + [C.c_void_p]),
+    "te_b200_cross_entropy": (C.c_int, [C.c_void_p] + [C.c_void_p] * 4 + [C.c_float, C.c_int64, C.c_int64, C.c_void_p]),
     "te_b200_shard_range": (C.c_int, [C.c_int64, C.c_int, C.c_int, C.c_int64, c_i64_p, c_i64_p]),
 }
 

@@ -9,6 +9,8 @@ used only as device-memory holders (data_ptr, shape, stride) and for the current
     Backend.scaled_dot      ScaledDot::forward                    (src/nn/scaledot.cpp:8-27)
     Backend.scaled_dot_backward  its backward graph                (src/core/grad_fn.cpp:126-156, :569-665)
     Backend.softmax / softmax_backward / gelu / gelu_backward / colsum: the kernels between the GEMMs.
+    Backend.layernorm / layernorm_backward / embedding / embedding_backward / cross_entropy: the GPT step's kernels
+        around the matmuls (src/nn/layernorm.cpp, src/nn/embedding.cpp, src/loss/CrossEntropyLoss.cpp).
 """
 import ctypes as C
 
@@ -193,6 +195,71 @@ class Backend:
         desc.precision = _prec(precision)
         L.check(self._lib.te_b200_attention_backward(self._ctx, C.byref(desc), self._stream()))
         return dq, dk, dv
+
+    # ------------------------------------------------------------------ the GPT step's kernels around the matmuls
+    def layernorm(self, x, gamma, beta, eps=1e-5):
+        """LayerNorm::forward over the last dimension (src/nn/layernorm.cpp:19-82)."""
+        self._check_f32_cuda(x, gamma, beta)
+        x = x.contiguous()
+        y = torch.empty_like(x)
+        cols = x.shape[-1]
+        rows = x.numel() // cols if cols else 0
+        L.check(self._lib.te_b200_layernorm_forward(self._ctx, _ptr(x), _ptr(gamma.contiguous()), _ptr(beta.contiguous()),
+                                                    _ptr(y), rows, cols, eps, self._stream()))
+        return y
+
+    def layernorm_backward(self, x, gamma, dy, eps=1e-5):
+        """(dx, dgamma, dbeta) of LayerNormBackward::backward (src/core/grad_fn.cpp:405-538)."""
+        self._check_f32_cuda(x, gamma, dy)
+        x, dy = x.contiguous(), dy.contiguous()
+        cols = x.shape[-1]
+        rows = x.numel() // cols if cols else 0
+        dx = torch.empty_like(x)
+        dg = torch.empty(cols, dtype=torch.float32, device=x.device)
+        db = torch.empty(cols, dtype=torch.float32, device=x.device)
+        L.check(self._lib.te_b200_layernorm_backward(self._ctx, _ptr(x), _ptr(gamma.contiguous()), _ptr(dy), _ptr(dx),
+                                                     _ptr(dg), _ptr(db), rows, cols, eps, self._stream()))
+        return dx, dg, db
+
+    def embedding(self, table, tokens, pos=None):
+        """table[tokens] (+ pos[t]) for int64 tokens [..., T]: Embedding::forward with GPT::forward's positional sum
+        (src/nn/embedding.cpp:18-60, src/nn/gpt.cpp:30-69)."""
+        self._check_f32_cuda(table, pos)
+        if tokens.dtype != torch.int64:
+            raise L.BackendError(L.TE_ERR_BAD_ARGUMENT, "Embedding input must be Int64")
+        tokens = tokens.contiguous()
+        table = table.contiguous()
+        vocab, dim = table.shape
+        out = torch.empty(tuple(tokens.shape) + (dim,), dtype=torch.float32, device=table.device)
+        T = tokens.shape[-1] if tokens.dim() else 1
+        L.check(self._lib.te_b200_embedding_forward(self._ctx, _ptr(table), _ptr(tokens), _ptr(pos.contiguous() if pos is not None else None),
+                                                    _ptr(out), tokens.numel(), T, dim, vocab, self._stream()))
+        return out
+
+    def embedding_backward(self, tokens, dout, vocab):
+        """Table gradient of EmbeddingBackward::backward (src/core/grad_fn.cpp:688-760), rows added in token order."""
+        self._check_f32_cuda(dout)
+        tokens, dout = tokens.contiguous(), dout.contiguous()
+        dim = dout.shape[-1]
+        dtable = torch.empty((vocab, dim), dtype=torch.float32, device=dout.device)
+        L.check(self._lib.te_b200_embedding_backward(self._ctx, _ptr(tokens), _ptr(dout), _ptr(dtable), tokens.numel(), dim,
+                                                     vocab, self._stream()))
+        return dtable
+
+    def cross_entropy(self, logits, targets, want_grad=True, upstream=1.0):
+        """(mean loss as a 1-element device tensor, dlogits or None): crossEntropyLoss::forward_batched and its
+        backward (src/loss/CrossEntropyLoss.cpp:47-127, src/core/grad_fn.cpp:271-346)."""
+        self._check_f32_cuda(logits)
+        if targets.dtype != torch.int64:
+            raise L.BackendError(L.TE_ERR_BAD_ARGUMENT, "cross-entropy targets must be Int64")
+        logits, targets = logits.contiguous(), targets.contiguous()
+        vocab = logits.shape[-1]
+        rows = logits.numel() // vocab if vocab else 0
+        loss = torch.zeros(1, dtype=torch.float32, device=logits.device)
+        grad = torch.empty_like(logits) if want_grad else None
+        L.check(self._lib.te_b200_cross_entropy(self._ctx, _ptr(logits), _ptr(targets), _ptr(loss), _ptr(grad), upstream, rows,
+                                                vocab, self._stream()))
+        return loss, grad
 
     # ------------------------------------------------------------------ row / elementwise ops
     def softmax(self, x):
