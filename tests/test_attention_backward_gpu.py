@@ -91,6 +91,21 @@ def test_fused_and_unfused_agree_and_many_tiles(backend):
     _check(plain, ref, "tf32", "unfused 40x6")
 
 
+def test_outputs_written_in_token_major_layout(backend):
+    """head_major_out=False: O, dQ, dK, dV land in [B,T,H,d] memory (the layout of the head-split views), values equal."""
+    shape = (3, 4, 256, 64)
+    q, k, v, p, o, d_o = _case(shape, 23, views=True)
+    for prec in ("tf32", "3xtf32"):
+        o1, p1 = backend.scaled_dot(q, k, v, precision=prec)
+        o2, p2 = backend.scaled_dot(q, k, v, precision=prec, head_major_out=False)
+        assert o2.transpose(1, 2).is_contiguous() and torch.equal(o1, o2) and torch.equal(p1, p2)
+        g1 = backend.scaled_dot_backward(q, k, v, p, d_o, o=o, precision=prec)
+        g2 = backend.scaled_dot_backward(q, k, v, p, d_o, o=o, precision=prec, head_major_out=False)
+        for a, b in zip(g1, g2):
+            assert b.transpose(1, 2).is_contiguous() and torch.equal(a, b)
+    backend.check_device_status()
+
+
 def test_backward_through_forward_outputs(backend):
     """The pair as a caller uses it: p and o come from this backend's own forward call."""
     shape = (4, 6, 256, 64)

@@ -161,17 +161,33 @@ __global__ void __launch_bounds__(256) layernorm_backward_kernel(const float* __
     block_sum(db, 1);
 }
 
+// One block per 32 columns: warp w adds the partial rows w, w + 8, ... in ascending order, then the eight warp sums
+// are added in warp order.
 __global__ void __launch_bounds__(256) layernorm_param_grad_kernel(const float* __restrict__ partial, int blocks, int cols,
                                                                    float* __restrict__ dgamma, float* __restrict__ dbeta) {
-    const int c = blockIdx.x * blockDim.x + threadIdx.x;
-    if (c >= cols) return;
+    __shared__ float red[2][8][32];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int c = blockIdx.x * 32 + lane;
     float a = 0.0f, b = 0.0f;
-    for (int i = 0; i < blocks; ++i) {
-        a += partial[((long long)i * 2) * cols + c];
-        b += partial[((long long)i * 2 + 1) * cols + c];
+    if (c < cols) {
+        for (int i = warp; i < blocks; i += 8) {
+            a += partial[((long long)i * 2) * cols + c];
+            b += partial[((long long)i * 2 + 1) * cols + c];
+        }
     }
-    if (dgamma) dgamma[c] = a;
-    if (dbeta) dbeta[c] = b;
+    red[0][warp][lane] = a;
+    red[1][warp][lane] = b;
+    __syncthreads();
+    if (warp == 0 && c < cols) {
+        float ta = 0.0f, tb = 0.0f;
+#pragma unroll
+        for (int w = 0; w < 8; ++w) {
+            ta += red[0][w][lane];
+            tb += red[1][w][lane];
+        }
+        if (dgamma) dgamma[c] = ta;
+        if (dbeta) dbeta[c] = tb;
+    }
 }
 
 // ------------------------------------------------------------------------------------------------ embedding
@@ -205,32 +221,58 @@ __global__ void __launch_bounds__(256) embedding_forward_kernel(const float* __r
 }
 
 // dtable[v][c] = sum over the positions i with tokens[i] == v, in ascending i, of dout[i][c]: one block per
-// (vocabulary row, 128 columns).  The block scans the token ids 128 at a time, each warp votes which of its 32
-// match, and the threads (one per column) add only the matching rows.  Suits the small vocabularies of the
-// reference's character-level models; the cost grows with vocab * n / 128.
+// (vocabulary row, 128 columns).  The block scans the token ids 128 at a time and appends the matching positions, in
+// order, to a list in shared memory (warp votes + prefix counts); whenever the list is full, and at the end, every
+// thread (one per column) adds the listed rows of dout, eight loads in flight at a time, strictly in list order.
+// Suits the small vocabularies of the reference's character-level models; the scan costs vocab * n / 128 block steps.
+constexpr int EMB_LIST = 1024;
+
 __global__ void __launch_bounds__(128) embedding_backward_kernel(const long long* __restrict__ tokens, const float* __restrict__ dout,
                                                                  float* __restrict__ dtable, long long n, int D) {
-    __shared__ unsigned match[4];
+    __shared__ int list[EMB_LIST + 128];
+    __shared__ int warp_count[4];
     const long long v = blockIdx.x;
     const int c = blockIdx.y * 128 + threadIdx.x;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     float acc = 0.0f;
+    int filled = 0;                                       // entries in the list (uniform over the block)
+    long long list_base = 0;                              // positions in the list are stored relative to this
+    auto consume = [&]() {
+        const float* col = dout + list_base * D + c;
+        int k = 0;
+        for (; k + 8 <= filled; k += 8) {
+            float x[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) x[u] = c < D ? __ldg(col + (long long)list[k + u] * D) : 0.0f;
+#pragma unroll
+            for (int u = 0; u < 8; ++u) acc += x[u];
+        }
+        for (; k < filled; ++k) acc += c < D ? __ldg(col + (long long)list[k] * D) : 0.0f;
+    };
     for (long long base = 0; base < n; base += 128) {
+        if (filled == 0) list_base = base;
         const long long i = base + threadIdx.x;
-        const unsigned m = __ballot_sync(0xffffffffu, i < n && tokens[i] == v);
-        __syncthreads();                       // the previous chunk's masks have been consumed
-        if (lane == 0) match[warp] = m;
+        const bool hit = i < n && tokens[i] == v;
+        const unsigned m = __ballot_sync(0xffffffffu, hit);
+        if (lane == 0) warp_count[warp] = __popc(m);
         __syncthreads();
+        int before = 0, total = 0;
 #pragma unroll
         for (int w = 0; w < 4; ++w) {
-            unsigned bits = match[w];
-            while (bits) {
-                const int k = __ffs(bits) - 1;
-                bits &= bits - 1;
-                if (c < D) acc += __ldg(dout + (base + w * 32 + k) * D + c);
-            }
+            const int cnt = warp_count[w];
+            if (w < warp) before += cnt;
+            total += cnt;
+        }
+        if (hit) list[filled + before + __popc(m & ((1u << lane) - 1u))] = (int)(i - list_base);
+        filled += total;
+        __syncthreads();                                  // list entries visible; warp_count may be rewritten
+        if (filled >= EMB_LIST) {
+            consume();
+            filled = 0;
+            __syncthreads();                              // everyone is done with the list before it is refilled
         }
     }
+    consume();
     if (c < D) dtable[v * D + c] = acc;
 }
 
@@ -347,7 +389,7 @@ int launch_layernorm_backward(te_b200_ctx* ctx, const float* x, const float* gam
 #undef CALL
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return cuda_fail(e, "layernorm_backward_kernel launch");
-    layernorm_param_grad_kernel<<<(cols + 255) / 256, 256, 0, st>>>(partial, grid, cols, dgamma, dbeta);
+    layernorm_param_grad_kernel<<<(cols + 31) / 32, 256, 0, st>>>(partial, grid, cols, dgamma, dbeta);
     e = cudaGetLastError();
     if (e != cudaSuccess) return cuda_fail(e, "layernorm_param_grad_kernel launch");
     ctx->launches += 2;

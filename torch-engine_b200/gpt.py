@@ -43,7 +43,7 @@ class _Linear(torch.autograd.Function):
 class _ScaledDot(torch.autograd.Function):
     @staticmethod
     def forward(ctx, q, k, v, be, prec):
-        o, p = be.scaled_dot(q, k, v, precision=prec)
+        o, p = be.scaled_dot(q, k, v, precision=prec, head_major_out=False)     # written as [B,T,H,hd]: the merge is a view
         ctx.save_for_backward(q, k, v, p, o)
         ctx.be, ctx.prec = be, prec
         return o
@@ -51,7 +51,7 @@ class _ScaledDot(torch.autograd.Function):
     @staticmethod
     def backward(ctx, d_o):
         q, k, v, p, o = ctx.saved_tensors
-        dq, dk, dv = ctx.be.scaled_dot_backward(q, k, v, p, d_o, o=o, precision=ctx.prec)
+        dq, dk, dv = ctx.be.scaled_dot_backward(q, k, v, p, d_o, o=o, precision=ctx.prec, head_major_out=False)
         return dq, dk, dv, None, None
 
 

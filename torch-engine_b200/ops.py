@@ -139,9 +139,11 @@ class Backend:
         return dx, dw, db
 
     # ------------------------------------------------------------------ attention
-    def scaled_dot(self, q, k, v, precision="tf32"):
+    def scaled_dot(self, q, k, v, precision="tf32", head_major_out=True):
         """softmax(q . k^T / sqrt(d)) . v for [B,H,T,d] views with unit last-dim stride (for example the
-        MultiHeadAttention head views with strides [T*E, d, E, 1]).  Returns (o [B,H,T,d] contiguous, p)."""
+        MultiHeadAttention head views with strides [T*E, d, E, 1]).  Returns (o [B,H,T,d], p).  o is contiguous, or with
+        head_major_out=False a view over [B,T,H,d] memory, so that the head merge of MultiHeadAttention::forward
+        (transpose + reshape, src/nn/multi_head_attention.cpp:36-38) needs no copy."""
         self._check_f32_cuda(q, k, v)
         if q.dim() != 4 or q.shape != k.shape or q.shape != v.shape:
             raise L.BackendError(L.TE_ERR_BAD_ARGUMENT, "scaled_dot expects q, k, v of one [B,H,T,d] shape")
@@ -150,7 +152,10 @@ class Backend:
                 raise L.BackendError(L.TE_ERR_UNSUPPORTED_LAYOUT, L.status_string(L.TE_ERR_UNSUPPORTED_LAYOUT))
         B, H, T, d = q.shape
         p = torch.empty((B, H, T, T), dtype=torch.float32, device=q.device)
-        o = torch.empty((B, H, T, d), dtype=torch.float32, device=q.device)
+        if head_major_out:
+            o = torch.empty((B, H, T, d), dtype=torch.float32, device=q.device)
+        else:
+            o = torch.empty((B, T, H, d), dtype=torch.float32, device=q.device).transpose(1, 2)
         desc = L.AttnDesc()
         desc.B, desc.H, desc.T, desc.d = B, H, T, d
         desc.q, desc.k, desc.v = q.data_ptr(), k.data_ptr(), v.data_ptr()
@@ -163,10 +168,11 @@ class Backend:
         L.check(self._lib.te_b200_attention_forward(self._ctx, C.byref(desc), self._stream()))
         return o, p
 
-    def scaled_dot_backward(self, q, k, v, p, d_o, o=None, precision="tf32"):
+    def scaled_dot_backward(self, q, k, v, p, d_o, o=None, precision="tf32", head_major_out=True):
         """(dq, dk, dv) of scaled_dot given the gradient d_o of its output, the probabilities p it returned and
         (optionally) its output o: MatMulBackward x2, SoftmaxBackward and DivBackward of the reference graph
-        (src/core/grad_fn.cpp:126-156, :569-665).  With o the fused kernel may run; without it the GEMM sequence."""
+        (src/core/grad_fn.cpp:126-156, :569-665).  With o the fused kernel may run; without it the GEMM sequence.
+        head_major_out=False returns views over [B,T,H,d] memory (the layout the head-split views came from)."""
         self._check_f32_cuda(q, k, v, p, d_o, o)
         B, H, T, d = q.shape
         if p.shape != (B, H, T, T) or not p.is_contiguous():
@@ -176,7 +182,10 @@ class Backend:
         for t in (q, k, v) + ((o,) if o is not None else ()):
             if t.shape != q.shape or t.stride(3) != 1:
                 raise L.BackendError(L.TE_ERR_UNSUPPORTED_LAYOUT, L.status_string(L.TE_ERR_UNSUPPORTED_LAYOUT))
-        dq, dk, dv = (torch.empty((B, H, T, d), dtype=torch.float32, device=q.device) for _ in range(3))
+        if head_major_out:
+            dq, dk, dv = (torch.empty((B, H, T, d), dtype=torch.float32, device=q.device) for _ in range(3))
+        else:
+            dq, dk, dv = (torch.empty((B, T, H, d), dtype=torch.float32, device=q.device).transpose(1, 2) for _ in range(3))
         desc = L.AttnBwdDesc()
         desc.B, desc.H, desc.T, desc.d = B, H, T, d
         desc.q, desc.k, desc.v = q.data_ptr(), k.data_ptr(), v.data_ptr()
