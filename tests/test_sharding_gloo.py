@@ -47,6 +47,14 @@ def _worker(rank, world, port, out_dir):
             full = sharding.all_gather_batches(o_loc, B, world, rank)
             assert torch.equal(full, sd(q, k, v)), B
             results[f"attn_{B}"] = (b0, cnt)
+        # data-parallel gradient averaging with unequal batch slices: rank r holds r + 1 rows whose per-row
+        # gradients are known, so the batch mean is known too
+        rows = rank + 1
+        per_row = [torch.full((5,), float(10 * r + i)) for r in range(world) for i in range(r + 1)]
+        mine = torch.stack([torch.full((5,), float(10 * rank + i)) for i in range(rows)]).mean(0)
+        total = sharding.all_reduce_batch_mean_(mine, rows)
+        assert total == sum(r + 1 for r in range(world))
+        assert torch.allclose(mine, torch.stack(per_row).mean(0))
         torch.save(results, os.path.join(out_dir, f"rank{rank}.pt"))
     finally:
         dist.destroy_process_group()

@@ -7,6 +7,10 @@ TENSOR_NUM_LAYERS, TENSOR_FF_DIM, TENSOR_BATCH_SIZE, TENSOR_SEQ_LEN, TENSOR_MEAS
 plus TENSOR_GEMM_PRECISION (tf32 | 3xtf32).  Defaults are benchmark configuration 4.
 
     python torch-engine_b200/benchmarks/gpt_benchmark.py [out.json]
+
+Under torchrun (one process per GPU) the step runs data-parallel: every rank takes TENSOR_BATCH_SIZE sequences of its
+own (weak scaling), the ranks exchange one all-reduce of the flat gradient per step (NCCL), time is the maximum over
+ranks and tokens/s the whole job's; rank 0 writes the result.
 """
 import json
 import os
@@ -17,7 +21,9 @@ sys.path.insert(0, ROOT)
 
 import torch  # noqa: E402
 
-from torch_engine_b200 import gpt, ops  # noqa: E402
+import torch.distributed as dist  # noqa: E402
+
+from torch_engine_b200 import gpt, ops, sharding  # noqa: E402
 
 
 def env_int(name, default):
@@ -32,31 +38,49 @@ def main():
     steps, warm = env_int("TENSOR_MEASURED_STEPS", 10), env_int("TENSOR_WARMUP_STEPS", 3)
     vocab = 65
     prec = os.environ.get("TENSOR_GEMM_PRECISION", "tf32")
-    be = ops.Backend(0, workspace_bytes=2 << 30)
+    world, rank, local = int(os.environ.get("WORLD_SIZE", 1)), int(os.environ.get("RANK", 0)), int(os.environ.get("LOCAL_RANK", 0))
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    sync = (lambda grads, rows: sharding.all_reduce_batch_mean_(grads, rows)) if world > 1 else None
+    be = ops.Backend(local, workspace_bytes=2 << 30)
     g = torch.Generator(device="cuda").manual_seed(42)
     n_params = vocab * E + L * (4 * E + 4 * (E * E + E) + 2 * E * ff + ff + E) + 2 * E + vocab * E + vocab
     flat = torch.randn(n_params, device="cuda", generator=g) * 0.02
+    g.manual_seed(1000 + rank)            # same parameters on every rank, different token batches
     tokens = torch.randint(0, vocab, (B, T), device="cuda", generator=g)
     targets = torch.randint(0, vocab, (B, T), device="cuda", generator=g)
     loss = None
     for _ in range(warm):
-        loss, _, _ = gpt.gpt_step(be, flat, tokens, targets, vocab, E, H, L, ff, prec)
+        loss, _, _ = gpt.gpt_step(be, flat, tokens, targets, vocab, E, H, L, ff, prec, grad_sync=sync)
     torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
     n0 = be.launches
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for _ in range(steps):
-        loss, _, _ = gpt.gpt_step(be, flat, tokens, targets, vocab, E, H, L, ff, prec)
+        loss, _, _ = gpt.gpt_step(be, flat, tokens, targets, vocab, E, H, L, ff, prec, grad_sync=sync)
     e1.record()
     torch.cuda.synchronize()
     be.check_device_status()
     ms = e0.elapsed_time(e1) / steps
+    if world > 1:
+        t = torch.tensor([ms], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+        dist.barrier()
+        dist.destroy_process_group()
+        if rank != 0:
+            return
+    B = B * world
     result = {
         "framework": "TENSOR", "device": "CUDA",
         "hardware": {"gpu": torch.cuda.get_device_name(0)},
         "model_config": {"vocab_size": vocab, "max_seq_len": T, "embed_dim": E, "num_heads": H, "num_layers": L, "ff_dim": ff},
         "training_config": {"batch_size": B, "seq_len": T, "measured_steps": steps, "dropout": 0.0,
-                            "gemm_backend": "b200", "gemm_precision": prec,
+                            "gemm_backend": "b200", "gemm_precision": prec, "gpus": world,
+                            "parallelism": "data-parallel, one gradient all-reduce per step" if world > 1 else "single GPU",
                             "step": "forward + loss + backward (no optimizer update)"},
         "metrics": {"timing_mode": "throughput", "total_time_s": ms * steps / 1e3, "total_tokens": B * T * steps,
                     "tokens_per_sec": B * T / (ms / 1e3), "steps_per_sec": 1e3 / ms, "time_per_step_ms": ms,

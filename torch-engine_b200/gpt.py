@@ -168,11 +168,15 @@ def gpt_forward(be, params, tokens, E, H, n_layers, prec="tf32"):
     return linear(be, layer_norm(be, x, gf, bf), wh, bh, prec)
 
 
-def gpt_step(be, flat_params, tokens, targets, vocab, E, H, n_layers, ff, prec="tf32"):
-    """One forward + backward.  Returns (loss, logits, flat gradient in parameter order)."""
+def gpt_step(be, flat_params, tokens, targets, vocab, E, H, n_layers, ff, prec="tf32", grad_sync=None):
+    """One forward + backward.  Returns (loss, logits, flat gradient in parameter order).  grad_sync, if given, is
+    called with (flat gradient, token rows of this rank) before returning: the data-parallel exchange
+    (sharding.all_reduce_batch_mean_)."""
     params = split_params(flat_params, vocab, E, n_layers, ff)
     logits = gpt_forward(be, params, tokens, E, H, n_layers, prec)
     loss = _CrossEntropy.apply(logits, targets, be)                                             # mean over B*T
     loss.backward()
     grads = torch.cat([p.grad.reshape(-1) for p in params])
+    if grad_sync is not None:
+        grad_sync(grads, tokens.numel())
     return loss.detach(), logits.detach(), grads

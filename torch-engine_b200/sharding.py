@@ -63,3 +63,18 @@ def all_gather_columns(c_local, n_total, world, rank, align=COLUMN_ALIGN, group=
 def all_gather_batches(o_local, b_total, world, rank, group=None):
     """Reassembles a batch-sharded result on every rank."""
     return _all_gather_padded(o_local, 0, b_total, world, rank, batch_shard, group)
+
+
+def all_reduce_batch_mean_(grads, local_rows, group=None):
+    """Data-parallel form of the GPT training step: every rank ran the step on its own slice of the batch (a mean loss
+    over `local_rows` token rows), and the gradient of the mean loss over the whole batch is the row-weighted average
+    of the ranks' gradients.  This is the step's one real exchange: a single all-reduce of the flat gradient (NCCL over
+    NVLink on GPUs, gloo in the CPU tests), in place.  Returns the total row count."""
+    world = dist.get_world_size(group)
+    total = torch.tensor([float(local_rows)], dtype=torch.float64, device=grads.device)
+    if world > 1:
+        grads.mul_(float(local_rows))
+        dist.all_reduce(grads, op=dist.ReduceOp.SUM, group=group)
+        dist.all_reduce(total, op=dist.ReduceOp.SUM, group=group)
+        grads.div_(float(total.item()))
+    return int(total.item())
