@@ -109,6 +109,10 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
+    // Everything above touched only this CTA's shared and tensor memory, so it may overlap the tail of the kernel
+    // ahead in the stream; from here on global memory is read and written.
+    griddep_launch_dependents();
+    griddep_wait();
 
     const int total_units = p.tiles_m * p.tiles_n * p.num_batches * p.k_splits;
     const int kblocks = (p.K + BK - 1) / BK;
@@ -539,8 +543,17 @@ static int launch_variant(te_b200_ctx* ctx, const GemmProblem& g_in, int k_split
     p.tiles_n = (int)((g.N + BN - 1) / BN);
     const long long total = (long long)p.tiles_m * p.tiles_n * p.num_batches * k_splits;
     const int grid = (int)(total < ctx->sm_count ? total : ctx->sm_count);
-    kernel<<<grid, CTA_THREADS, Cfg::SMEM_BYTES, stream>>>(ma, mal, mb, mbl, mc, mpre, p);
-    cudaError_t e = cudaGetLastError();
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)grid, 1, 1);
+    cfg.blockDim = dim3(CTA_THREADS, 1, 1);
+    cfg.dynamicSmemBytes = Cfg::SMEM_BYTES;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;    // the prologue may overlap the previous kernel's tail
+    attr.val.programmaticStreamSerializationAllowed = TE_PDL_ALLOWED;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, ma, mal, mb, mbl, mc, mpre, p);
     if (e != cudaSuccess) return cuda_fail(e, "gemm_tf32_kernel launch");
     ctx->launches += 1;
     return k_splits > 1 ? finish_split(ctx, g_in, k_splits, stream) : TE_OK;

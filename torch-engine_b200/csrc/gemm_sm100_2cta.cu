@@ -113,6 +113,10 @@ gemm_tf32_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
     cluster_sync_all();                               // partner's barriers are initialised before anyone signals them
     tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
+    // Everything above touched only the pair's shared and tensor memory, so it may overlap the tail of the kernel
+    // ahead in the stream; from here on global memory is read and written.
+    griddep_launch_dependents();
+    griddep_wait();
 
     const int total_units = p.tiles_m * p.tiles_n * p.num_batches * p.k_splits;
     const int kblocks = (p.K + BK - 1) / BK;
@@ -386,8 +390,17 @@ static int launch_pair_variant(te_b200_ctx* ctx, const GemmProblem& g_in, int k_
         if (ctx->device < 16) max_pairs_cached[ctx->device] = n;
     }
     const int pairs = (int)(total < max_pairs ? total : max_pairs);
-    kernel<<<2 * pairs, CTA_THREADS, Cfg::SMEM_BYTES, stream>>>(ma, mal, mb, mbl, mc, mpre, p);
-    cudaError_t e = cudaGetLastError();
+    cudaLaunchConfig_t lc = {};
+    lc.gridDim = dim3((unsigned)(2 * pairs), 1, 1);
+    lc.blockDim = dim3(CTA_THREADS, 1, 1);
+    lc.dynamicSmemBytes = Cfg::SMEM_BYTES;
+    lc.stream = stream;
+    cudaLaunchAttribute pdl;
+    pdl.id = cudaLaunchAttributeProgrammaticStreamSerialization;     // the prologue may overlap the previous kernel's tail
+    pdl.val.programmaticStreamSerializationAllowed = TE_PDL_ALLOWED;
+    lc.attrs = &pdl;
+    lc.numAttrs = 1;
+    cudaError_t e = cudaLaunchKernelEx(&lc, kernel, ma, mal, mb, mbl, mc, mpre, p);
     if (e != cudaSuccess) return cuda_fail(e, "gemm_tf32_pair_kernel launch");
     ctx->launches += 1;
     return k_splits > 1 ? finish_split(ctx, g_in, k_splits, stream) : TE_OK;
