@@ -56,6 +56,7 @@ struct AttnBwdParams {
 __global__ void __launch_bounds__(256) rowdot_bht_kernel(const float* __restrict__ x, long long xs0, long long xs1, long long xs2,
                                                          const float* __restrict__ y, long long ys0, long long ys1, long long ys2,
                                                          float* __restrict__ out, int H, int T, int d, long long rows) {
+    griddep_wait();
     const int lane = threadIdx.x & 31;
     const int f4 = d >> 2, rpi = 32 / f4;
     const int sub = lane / f4, col = lane - sub * f4;
@@ -143,6 +144,8 @@ attention_bwd_tf32_kernel(const __grid_constant__ CUtensorMap tm_v, const __grid
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
+    griddep_launch_dependents();   // persistent grid, every CTA resident: the next kernel may move in as CTAs exit
+    griddep_wait();                // the prologue above overlapped the previous kernel's tail; global memory from here on
     const int nblk = p.nblk;
 
     if (warp == PRODUCER_WARP) {
@@ -454,7 +457,7 @@ int launch_attention_backward_fused(te_b200_ctx* ctx, const te_attn_bwd_desc* t,
         const int rpi = 32 / ((int)t->d / 4);
         long long blocks = (rows + 8 * rpi - 1) / (8 * rpi);
         if (blocks > (long long)ctx->sm_count * 16) blocks = (long long)ctx->sm_count * 16;
-        rowdot_bht_kernel<<<(unsigned)blocks, 256, 0, stream>>>(t->d_o, t->d_o_strides[0], t->d_o_strides[1], t->d_o_strides[2],
+        launch_pdl(rowdot_bht_kernel, dim3((unsigned)blocks), dim3(256), 0, stream, t->d_o, t->d_o_strides[0], t->d_o_strides[1], t->d_o_strides[2],
                                                                  t->o, t->o_strides[0], t->o_strides[1], t->o_strides[2], dvec,
                                                                  (int)t->H, (int)t->T, (int)t->d, rows);
         cudaError_t e = cudaGetLastError();
@@ -471,7 +474,7 @@ int launch_attention_backward_fused(te_b200_ctx* ctx, const te_attn_bwd_desc* t,
         attr_smem[ctx->device] = smem;
     }
     const int grid = p.total_tiles < ctx->sm_count ? p.total_tiles : ctx->sm_count;
-    attention_bwd_tf32_kernel<<<grid, CTA_THREADS, smem, stream>>>(mv, mk, mdok, mdom, mq, mdq, mdk, mdv, mp, p);
+    launch_pdl(attention_bwd_tf32_kernel, dim3(grid), dim3(CTA_THREADS), smem, stream, mv, mk, mdok, mdom, mq, mdq, mdk, mdv, mp, p);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return cuda_fail(e, "attention_bwd_tf32_kernel launch");
     ctx->launches += 1;

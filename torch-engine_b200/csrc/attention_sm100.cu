@@ -103,6 +103,8 @@ attention_tf32_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
+    griddep_launch_dependents();   // persistent grid, every CTA resident: the next kernel may move in as CTAs exit
+    griddep_wait();                // the prologue above overlapped the previous kernel's tail; global memory from here on
 
     // Persistent: this CTA handles tiles blockIdx.x, blockIdx.x + gridDim.x, ...  While the softmax of tile i runs,
     // the producer already fetches Q and K of tile i+1 (their buffers are free once the score MMAs are done).
@@ -367,7 +369,7 @@ int launch_attention_fused(te_b200_ctx* ctx, const te_attn_desc* t, cudaStream_t
     }
     p.total_tiles = (int)(t->B * t->H * p.tiles_q);
     const int grid = p.total_tiles < ctx->sm_count ? p.total_tiles : ctx->sm_count;
-    attention_tf32_kernel<<<grid, CTA_THREADS, smem, stream>>>(mq, mk, mv, mp, mo, p);
+    launch_pdl(attention_tf32_kernel, dim3(grid), dim3(CTA_THREADS), smem, stream, mq, mk, mv, mp, mo, p);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return cuda_fail(e, "attention_tf32_kernel launch");
     ctx->launches += 1;

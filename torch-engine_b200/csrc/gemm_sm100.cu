@@ -477,6 +477,7 @@ struct SplitReduceParams {
 };
 
 __global__ void __launch_bounds__(256) splitk_reduce_kernel(const SplitReduceParams r) {
+    griddep_wait();
     const long long stride = (long long)gridDim.x * blockDim.x;
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < r.total; i += stride) {
         float v = 0.0f;
@@ -505,7 +506,7 @@ int finish_split(te_b200_ctx* ctx, const GemmProblem& g, int k_splits, cudaStrea
     r.alpha = g.alpha; r.scale_mode = g.scale_mode; r.epilogue = g.epilogue;
     long long blocks = (r.total + 255) / 256;
     if (blocks > (long long)ctx->sm_count * 16) blocks = (long long)ctx->sm_count * 16;
-    splitk_reduce_kernel<<<(unsigned)blocks, 256, 0, stream>>>(r);
+    launch_pdl(splitk_reduce_kernel, dim3((unsigned)blocks), dim3(256), 0, stream, r);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return cuda_fail(e, "splitk_reduce_kernel launch");
     ctx->launches += 1;
@@ -543,17 +544,7 @@ static int launch_variant(te_b200_ctx* ctx, const GemmProblem& g_in, int k_split
     p.tiles_n = (int)((g.N + BN - 1) / BN);
     const long long total = (long long)p.tiles_m * p.tiles_n * p.num_batches * k_splits;
     const int grid = (int)(total < ctx->sm_count ? total : ctx->sm_count);
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((unsigned)grid, 1, 1);
-    cfg.blockDim = dim3(CTA_THREADS, 1, 1);
-    cfg.dynamicSmemBytes = Cfg::SMEM_BYTES;
-    cfg.stream = stream;
-    cudaLaunchAttribute attr;
-    attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;    // the prologue may overlap the previous kernel's tail
-    attr.val.programmaticStreamSerializationAllowed = TE_PDL_ALLOWED;
-    cfg.attrs = &attr;
-    cfg.numAttrs = 1;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, ma, mal, mb, mbl, mc, mpre, p);
+    cudaError_t e = launch_pdl(kernel, dim3((unsigned)grid), dim3(CTA_THREADS), Cfg::SMEM_BYTES, stream, ma, mal, mb, mbl, mc, mpre, p);
     if (e != cudaSuccess) return cuda_fail(e, "gemm_tf32_kernel launch");
     ctx->launches += 1;
     return k_splits > 1 ? finish_split(ctx, g_in, k_splits, stream) : TE_OK;

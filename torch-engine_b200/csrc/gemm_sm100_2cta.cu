@@ -390,17 +390,7 @@ static int launch_pair_variant(te_b200_ctx* ctx, const GemmProblem& g_in, int k_
         if (ctx->device < 16) max_pairs_cached[ctx->device] = n;
     }
     const int pairs = (int)(total < max_pairs ? total : max_pairs);
-    cudaLaunchConfig_t lc = {};
-    lc.gridDim = dim3((unsigned)(2 * pairs), 1, 1);
-    lc.blockDim = dim3(CTA_THREADS, 1, 1);
-    lc.dynamicSmemBytes = Cfg::SMEM_BYTES;
-    lc.stream = stream;
-    cudaLaunchAttribute pdl;
-    pdl.id = cudaLaunchAttributeProgrammaticStreamSerialization;     // the prologue may overlap the previous kernel's tail
-    pdl.val.programmaticStreamSerializationAllowed = TE_PDL_ALLOWED;
-    lc.attrs = &pdl;
-    lc.numAttrs = 1;
-    cudaError_t e = cudaLaunchKernelEx(&lc, kernel, ma, mal, mb, mbl, mc, mpre, p);
+    cudaError_t e = launch_pdl(kernel, dim3((unsigned)(2 * pairs)), dim3(CTA_THREADS), Cfg::SMEM_BYTES, stream, ma, mal, mb, mbl, mc, mpre, p);
     if (e != cudaSuccess) return cuda_fail(e, "gemm_tf32_pair_kernel launch");
     ctx->launches += 1;
     return k_splits > 1 ? finish_split(ctx, g_in, k_splits, stream) : TE_OK;

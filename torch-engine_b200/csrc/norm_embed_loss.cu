@@ -13,6 +13,7 @@
 #include <math.h>
 #include <stdint.h>
 
+#include "pdl.cuh"
 #include "te_internal.h"
 
 namespace te {
@@ -64,6 +65,7 @@ template <int N, bool VEC>
 __global__ void __launch_bounds__(256) layernorm_forward_kernel(const float* __restrict__ x, const float* __restrict__ gamma,
                                                                 const float* __restrict__ beta, float* __restrict__ y,
                                                                 long long rows, int cols, float eps) {
+    griddep_wait();
     using R = RowRegs<N, VEC>;
     const int lane = threadIdx.x & 31;
     const long long warps = (long long)gridDim.x * (blockDim.x >> 5);
@@ -98,6 +100,7 @@ template <int N, bool VEC>
 __global__ void __launch_bounds__(256) layernorm_backward_kernel(const float* __restrict__ x, const float* __restrict__ gamma,
                                                                  const float* __restrict__ dy, float* __restrict__ dx,
                                                                  float* __restrict__ partial, long long rows, int cols, float eps) {
+    griddep_wait();
     using R = RowRegs<N, VEC>;
     extern __shared__ float red[];     // [8 warps][cols]
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -165,6 +168,7 @@ __global__ void __launch_bounds__(256) layernorm_backward_kernel(const float* __
 // are added in warp order.
 __global__ void __launch_bounds__(256) layernorm_param_grad_kernel(const float* __restrict__ partial, int blocks, int cols,
                                                                    float* __restrict__ dgamma, float* __restrict__ dbeta) {
+    griddep_wait();
     __shared__ float red[2][8][32];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int c = blockIdx.x * 32 + lane;
@@ -196,6 +200,7 @@ template <bool VEC>
 __global__ void __launch_bounds__(256) embedding_forward_kernel(const float* __restrict__ table, const long long* __restrict__ tokens,
                                                                 const float* __restrict__ pos, float* __restrict__ out, long long n,
                                                                 int T, int D, long long vocab, int* status) {
+    griddep_wait();
     const int per_row = VEC ? D / 4 : D;
     const long long total = n * per_row;
     const long long stride = (long long)gridDim.x * blockDim.x;
@@ -229,6 +234,7 @@ constexpr int EMB_LIST = 1024;
 
 __global__ void __launch_bounds__(128) embedding_backward_kernel(const long long* __restrict__ tokens, const float* __restrict__ dout,
                                                                  float* __restrict__ dtable, long long n, int D) {
+    griddep_wait();
     __shared__ int list[EMB_LIST + 128];
     __shared__ int warp_count[4];
     const long long v = blockIdx.x;
@@ -283,6 +289,7 @@ __global__ void __launch_bounds__(128) embedding_backward_kernel(const long long
 __global__ void __launch_bounds__(256) cross_entropy_rows_kernel(const float* __restrict__ logits, const long long* __restrict__ targets,
                                                                  float* __restrict__ grad, float scale, double* __restrict__ partial,
                                                                  long long rows, int V, int* status) {
+    griddep_wait();
     __shared__ double block_part[8];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const long long warps = (long long)gridDim.x * (blockDim.x >> 5);
@@ -320,6 +327,7 @@ __global__ void __launch_bounds__(256) cross_entropy_rows_kernel(const float* __
 }
 
 __global__ void cross_entropy_finish_kernel(const double* __restrict__ partial, int blocks, long long rows, float* __restrict__ loss) {
+    griddep_wait();
     if (threadIdx.x != 0 || blockIdx.x != 0) return;
     double t = 0.0;
     for (int i = 0; i < blocks; ++i) t += partial[i];
@@ -358,7 +366,7 @@ int launch_layernorm_forward(te_b200_ctx* ctx, const float* x, const float* gamm
     const int cols = (int)cols64;
     const bool vec = (cols & 3) == 0 && aligned16(x) && aligned16(y) && aligned16(gamma) && aligned16(beta);
     const int grid = row_grid(rows, ctx->sm_count, 8);
-#define CALL(N, V) layernorm_forward_kernel<N, V><<<grid, 256, 0, st>>>(x, gamma, beta, y, rows, cols, eps)
+#define CALL(N, V) launch_pdl(layernorm_forward_kernel<N, V>, dim3(grid), dim3(256), 0, st, x, gamma, beta, y, rows, cols, eps)
     TE_LN_DISPATCH(CALL)
 #undef CALL
     cudaError_t e = cudaGetLastError();
@@ -384,12 +392,12 @@ int launch_layernorm_backward(te_b200_ctx* ctx, const float* x, const float* gam
     }
     float* partial = static_cast<float*>(ctx->workspace);
     const size_t smem = (size_t)8 * cols * sizeof(float);
-#define CALL(N, V) layernorm_backward_kernel<N, V><<<grid, 256, smem, st>>>(x, gamma, dy, dx, partial, rows, cols, eps)
+#define CALL(N, V) launch_pdl(layernorm_backward_kernel<N, V>, dim3(grid), dim3(256), smem, st, x, gamma, dy, dx, partial, rows, cols, eps)
     TE_LN_DISPATCH(CALL)
 #undef CALL
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return cuda_fail(e, "layernorm_backward_kernel launch");
-    layernorm_param_grad_kernel<<<(cols + 31) / 32, 256, 0, st>>>(partial, grid, cols, dgamma, dbeta);
+    launch_pdl(layernorm_param_grad_kernel, dim3((cols + 31) / 32), dim3(256), 0, st, partial, grid, cols, dgamma, dbeta);
     e = cudaGetLastError();
     if (e != cudaSuccess) return cuda_fail(e, "layernorm_param_grad_kernel launch");
     ctx->launches += 2;
@@ -404,8 +412,8 @@ int launch_embedding_forward(te_b200_ctx* ctx, const float* table, const int64_t
     long long blocks = (total + 255) / 256;
     if (blocks > (long long)ctx->sm_count * 16) blocks = (long long)ctx->sm_count * 16;
     const long long* tk = reinterpret_cast<const long long*>(tokens);
-    if (vec) embedding_forward_kernel<true><<<(unsigned)blocks, 256, 0, st>>>(table, tk, pos, out, n, (int)(T > 0 ? T : 1), (int)D, vocab, ctx->d_status);
-    else embedding_forward_kernel<false><<<(unsigned)blocks, 256, 0, st>>>(table, tk, pos, out, n, (int)(T > 0 ? T : 1), (int)D, vocab, ctx->d_status);
+    if (vec) launch_pdl(embedding_forward_kernel<true>, dim3((unsigned)blocks), dim3(256), 0, st, table, tk, pos, out, n, (int)(T > 0 ? T : 1), (int)D, vocab, ctx->d_status);
+    else launch_pdl(embedding_forward_kernel<false>, dim3((unsigned)blocks), dim3(256), 0, st, table, tk, pos, out, n, (int)(T > 0 ? T : 1), (int)D, vocab, ctx->d_status);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return cuda_fail(e, "embedding_forward_kernel launch");
     ctx->launches += 1;
@@ -420,7 +428,7 @@ int launch_embedding_backward(te_b200_ctx* ctx, const int64_t* tokens, const flo
         return TE_ERR_BAD_ARGUMENT;
     }
     dim3 grid((unsigned)vocab, (unsigned)((D + 127) / 128));
-    embedding_backward_kernel<<<grid, 128, 0, st>>>(reinterpret_cast<const long long*>(tokens), dout, dtable, n, (int)D);
+    launch_pdl(embedding_backward_kernel, dim3(grid), dim3(128), 0, st, reinterpret_cast<const long long*>(tokens), dout, dtable, n, (int)D);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return cuda_fail(e, "embedding_backward_kernel launch");
     ctx->launches += 1;
@@ -441,13 +449,13 @@ int launch_cross_entropy(te_b200_ctx* ctx, const float* logits, const int64_t* t
     }
     double* partial = static_cast<double*>(ctx->workspace);
     const float scale = upstream / (float)rows;      // CrossEntropyBatchedBackward: upstream / N (grad_fn.cpp:295)
-    cross_entropy_rows_kernel<<<grid, 256, 0, st>>>(logits, reinterpret_cast<const long long*>(targets), grad, scale, partial,
+    launch_pdl(cross_entropy_rows_kernel, dim3(grid), dim3(256), 0, st, logits, reinterpret_cast<const long long*>(targets), grad, scale, partial,
                                                     rows, (int)V, ctx->d_status);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return cuda_fail(e, "cross_entropy_rows_kernel launch");
     ctx->launches += 1;
     if (loss) {
-        cross_entropy_finish_kernel<<<1, 32, 0, st>>>(partial, grid, rows, loss);
+        launch_pdl(cross_entropy_finish_kernel, dim3(1), dim3(32), 0, st, partial, grid, rows, loss);
         e = cudaGetLastError();
         if (e != cudaSuccess) return cuda_fail(e, "cross_entropy_finish_kernel launch");
         ctx->launches += 1;

@@ -11,6 +11,7 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include "pdl.cuh"
 #include "te_internal.h"
 
 namespace te {
@@ -32,6 +33,7 @@ struct PackParams {
 
 template <bool MN_MAJOR, bool SPLIT>
 __global__ void __launch_bounds__(256) pack_operand_kernel(const PackParams p) {
+    griddep_wait();
     __shared__ float tile[32][33];
     const int tx = threadIdx.x, ty = threadIdx.y;          // 32 x 8
     const long long k0 = (long long)blockIdx.x * 32;
@@ -71,6 +73,7 @@ __global__ void __launch_bounds__(256) pack_operand_kernel(const PackParams p) {
 // K-major source whose rows are 16-byte aligned: no transpose needed, four k per thread with 16-byte accesses.
 template <bool SPLIT>
 __global__ void __launch_bounds__(256) pack_rows_vec4_kernel(const PackParams p, long long quads_per_row, long long total) {
+    griddep_wait();
     const long long stride = (long long)gridDim.x * blockDim.x;
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
         const long long q = i % quads_per_row;
@@ -123,8 +126,8 @@ int launch_pack(te_b200_ctx* ctx, const Operand& src, int64_t K, int64_t batch_i
         const long long quads = p.kp / 4, total = quads * src.rows * nb;
         long long blocks = (total + 255) / 256;
         if (blocks > (long long)ctx->sm_count * 32) blocks = (long long)ctx->sm_count * 32;
-        if (split) pack_rows_vec4_kernel<true><<<(unsigned)blocks, 256, 0, stream>>>(p, quads, total);
-        else pack_rows_vec4_kernel<false><<<(unsigned)blocks, 256, 0, stream>>>(p, quads, total);
+        if (split) launch_pdl(pack_rows_vec4_kernel<true>, dim3((unsigned)blocks), dim3(256), 0, stream, p, quads, total);
+        else launch_pdl(pack_rows_vec4_kernel<false>, dim3((unsigned)blocks), dim3(256), 0, stream, p, quads, total);
         cudaError_t ev = cudaGetLastError();
         if (ev != cudaSuccess) return cuda_fail(ev, "pack_rows_vec4_kernel launch");
         ctx->launches += 1;
@@ -133,11 +136,11 @@ int launch_pack(te_b200_ctx* ctx, const Operand& src, int64_t K, int64_t batch_i
     dim3 grid((unsigned)((p.kp + 31) / 32), (unsigned)((src.rows + 31) / 32), (unsigned)nb);
     dim3 block(32, 8);
     if (src.mn_major) {
-        if (split) pack_operand_kernel<true, true><<<grid, block, 0, stream>>>(p);
-        else pack_operand_kernel<true, false><<<grid, block, 0, stream>>>(p);
+        if (split) launch_pdl(pack_operand_kernel<true, true>, dim3(grid), dim3(block), 0, stream, p);
+        else launch_pdl(pack_operand_kernel<true, false>, dim3(grid), dim3(block), 0, stream, p);
     } else {
-        if (split) pack_operand_kernel<false, true><<<grid, block, 0, stream>>>(p);
-        else pack_operand_kernel<false, false><<<grid, block, 0, stream>>>(p);
+        if (split) launch_pdl(pack_operand_kernel<false, true>, dim3(grid), dim3(block), 0, stream, p);
+        else launch_pdl(pack_operand_kernel<false, false>, dim3(grid), dim3(block), 0, stream, p);
     }
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return cuda_fail(e, "pack_operand_kernel launch");

@@ -2,6 +2,7 @@
 // mbarrier, TMA tensor loads (each CTA loads only for itself), thread-block-cluster helpers, tcgen05
 // (TMEM allocation, UMMA issue/commit, TMEM loads) and the descriptor encodings.
 #pragma once
+#include "pdl.cuh"
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -58,22 +59,6 @@ __device__ __forceinline__ void tma_load_4d(uint32_t dst_smem, const void* tmap,
         "r"(c2), "r"(c3)
         : "memory");
 }
-// Programmatic dependent launch.  A kernel launched with the programmatic-stream-serialization attribute may start
-// (allocate its resources, run its prologue) before the kernel ahead of it in the stream has finished;
-// griddep_wait() blocks until that kernel has completed and its memory is visible, and must precede every access to
-// global memory.  griddep_launch_dependents() lets the kernel BEHIND this one start as soon as every CTA of this grid
-// has issued it or exited; only grids whose CTAs are all resident at once may issue it before they are done.
-// Building with -DTE_NO_PDL turns both into no-ops and the launches into ordinary ones.
-#ifndef TE_NO_PDL
-__device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
-__device__ __forceinline__ void griddep_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
-constexpr int TE_PDL_ALLOWED = 1;
-#else
-__device__ __forceinline__ void griddep_wait() {}
-__device__ __forceinline__ void griddep_launch_dependents() {}
-constexpr int TE_PDL_ALLOWED = 0;
-#endif
-
 __device__ __forceinline__ float ld_shared_f32(uint32_t addr) {
     float v;
     asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(addr) : "memory");

@@ -5,6 +5,7 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include "pdl.cuh"
 #include "te_internal.h"
 
 namespace te {
@@ -27,6 +28,7 @@ template <int ITEMS>
 __global__ void __launch_bounds__(256) softmax_rows_kernel(const float* in, float* out,   // in may alias out
                                                           
                                                            long long rows, int cols) {
+    griddep_wait();
     const int lane = threadIdx.x & 31;
     const long long warps_per_grid = (long long)gridDim.x * (blockDim.x >> 5);
     for (long long row = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); row < rows;
@@ -76,6 +78,7 @@ __global__ void __launch_bounds__(256) softmax_rows_kernel(const float* in, floa
 // keeps four times as many bytes in flight per instruction as the scalar form.
 template <int V4>
 __global__ void __launch_bounds__(256) softmax_rows_vec4_kernel(const float* in, float* out, long long rows) {
+    griddep_wait();
     constexpr int cols = V4 * 128;
     const int lane = threadIdx.x & 31;
     const long long warps_per_grid = (long long)gridDim.x * (blockDim.x >> 5);
@@ -110,6 +113,7 @@ __global__ void __launch_bounds__(256) softmax_rows_vec4_kernel(const float* in,
 // dx may be the same buffer as dy: every element is read and then written by the one lane that owns it.
 __global__ void __launch_bounds__(256) softmax_backward_rows_kernel(const float* __restrict__ s, const float* dy,
                                                                     float* dx, long long rows, int cols) {
+    griddep_wait();
     const int lane = threadIdx.x & 31;
     const long long warps_per_grid = (long long)gridDim.x * (blockDim.x >> 5);
     for (long long row = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); row < rows;
@@ -139,11 +143,13 @@ __device__ __forceinline__ float gelu_bwd(float x, float dy) {
 }
 
 __global__ void __launch_bounds__(256) gelu_kernel(const float* __restrict__ x, float* __restrict__ y, long long n) {
+    griddep_wait();
     const long long stride = (long long)gridDim.x * blockDim.x;
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) y[i] = gelu_fwd(x[i]);
 }
 __global__ void __launch_bounds__(256) gelu_backward_kernel(const float* __restrict__ x, const float* __restrict__ dy,
                                                             float* __restrict__ dx, long long n) {
+    griddep_wait();
     const long long stride = (long long)gridDim.x * blockDim.x;
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride)
         dx[i] = gelu_bwd(x[i], dy[i]);
@@ -153,6 +159,7 @@ __global__ void __launch_bounds__(256) gelu_backward_kernel(const float* __restr
 // then a shared-memory tree adds the 32 partials in a fixed order (deterministic, unlike an atomicAdd).
 __global__ void __launch_bounds__(1024) colsum_kernel(const float* __restrict__ in, long long rows, long long cols,
                                                       long long ld, float* __restrict__ out) {
+    griddep_wait();
     __shared__ float part[32][33];
     const int tx = threadIdx.x, ty = threadIdx.y;
     const long long col = (long long)blockIdx.x * 32 + tx;
@@ -172,6 +179,7 @@ __global__ void __launch_bounds__(1024) colsum_kernel(const float* __restrict__ 
 // then the slabs are added in order.  Deterministic, and enough blocks to pull the full HBM bandwidth.
 __global__ void __launch_bounds__(1024) colsum_slab_kernel(const float* __restrict__ in, long long rows, long long cols,
                                                            long long ld, long long rows_per_slab, float* __restrict__ partial) {
+    griddep_wait();
     __shared__ float part[32][33];
     const int tx = threadIdx.x, ty = threadIdx.y;
     const long long col = (long long)blockIdx.x * 32 + tx;
@@ -190,6 +198,7 @@ __global__ void __launch_bounds__(1024) colsum_slab_kernel(const float* __restri
 }
 __global__ void __launch_bounds__(256) colsum_finish_kernel(const float* __restrict__ partial, int slabs, long long cols,
                                                             float* __restrict__ out) {
+    griddep_wait();
     const long long col = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (col >= cols) return;
     float acc = 0.0f;
@@ -211,17 +220,17 @@ int launch_softmax_rows(te_b200_ctx* ctx, const float* in, float* out, int64_t r
     const int c = (int)cols;
     const bool aligned = ((reinterpret_cast<uintptr_t>(in) | reinterpret_cast<uintptr_t>(out)) & 15) == 0;
     if (aligned && (cols == 128 || cols == 256 || cols == 512 || cols == 1024)) {
-        if (cols == 128) softmax_rows_vec4_kernel<1><<<grid, 256, 0, st>>>(in, out, rows);
-        else if (cols == 256) softmax_rows_vec4_kernel<2><<<grid, 256, 0, st>>>(in, out, rows);
-        else if (cols == 512) softmax_rows_vec4_kernel<4><<<grid, 256, 0, st>>>(in, out, rows);
-        else softmax_rows_vec4_kernel<8><<<grid, 256, 0, st>>>(in, out, rows);
-    } else if (cols <= 32) softmax_rows_kernel<1><<<grid, 256, 0, st>>>(in, out, rows, c);
-    else if (cols <= 64) softmax_rows_kernel<2><<<grid, 256, 0, st>>>(in, out, rows, c);
-    else if (cols <= 128) softmax_rows_kernel<4><<<grid, 256, 0, st>>>(in, out, rows, c);
-    else if (cols <= 256) softmax_rows_kernel<8><<<grid, 256, 0, st>>>(in, out, rows, c);
-    else if (cols <= 512) softmax_rows_kernel<16><<<grid, 256, 0, st>>>(in, out, rows, c);
-    else if (cols <= 1024) softmax_rows_kernel<32><<<grid, 256, 0, st>>>(in, out, rows, c);
-    else softmax_rows_kernel<0><<<grid, 256, 0, st>>>(in, out, rows, c);
+        if (cols == 128) launch_pdl(softmax_rows_vec4_kernel<1>, dim3(grid), dim3(256), 0, st, in, out, rows);
+        else if (cols == 256) launch_pdl(softmax_rows_vec4_kernel<2>, dim3(grid), dim3(256), 0, st, in, out, rows);
+        else if (cols == 512) launch_pdl(softmax_rows_vec4_kernel<4>, dim3(grid), dim3(256), 0, st, in, out, rows);
+        else launch_pdl(softmax_rows_vec4_kernel<8>, dim3(grid), dim3(256), 0, st, in, out, rows);
+    } else if (cols <= 32) launch_pdl(softmax_rows_kernel<1>, dim3(grid), dim3(256), 0, st, in, out, rows, c);
+    else if (cols <= 64) launch_pdl(softmax_rows_kernel<2>, dim3(grid), dim3(256), 0, st, in, out, rows, c);
+    else if (cols <= 128) launch_pdl(softmax_rows_kernel<4>, dim3(grid), dim3(256), 0, st, in, out, rows, c);
+    else if (cols <= 256) launch_pdl(softmax_rows_kernel<8>, dim3(grid), dim3(256), 0, st, in, out, rows, c);
+    else if (cols <= 512) launch_pdl(softmax_rows_kernel<16>, dim3(grid), dim3(256), 0, st, in, out, rows, c);
+    else if (cols <= 1024) launch_pdl(softmax_rows_kernel<32>, dim3(grid), dim3(256), 0, st, in, out, rows, c);
+    else launch_pdl(softmax_rows_kernel<0>, dim3(grid), dim3(256), 0, st, in, out, rows, c);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return cuda_fail(e, "softmax_rows_kernel launch");
     ctx->launches += 1;
@@ -231,7 +240,7 @@ int launch_softmax_rows(te_b200_ctx* ctx, const float* in, float* out, int64_t r
 int launch_softmax_backward_rows(te_b200_ctx* ctx, const float* s, const float* dy, float* dx, int64_t rows,
                                  int64_t cols, cudaStream_t st) {
     if (rows == 0 || cols == 0) return TE_OK;
-    softmax_backward_rows_kernel<<<grid_for(rows, 8, ctx->sm_count), 256, 0, st>>>(s, dy, dx, rows, (int)cols);
+    launch_pdl(softmax_backward_rows_kernel, dim3(grid_for(rows, 8, ctx->sm_count)), dim3(256), 0, st, s, dy, dx, rows, (int)cols);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return cuda_fail(e, "softmax_backward_rows_kernel launch");
     ctx->launches += 1;
@@ -240,7 +249,7 @@ int launch_softmax_backward_rows(te_b200_ctx* ctx, const float* s, const float* 
 
 int launch_gelu(te_b200_ctx* ctx, const float* x, float* y, int64_t n, cudaStream_t st) {
     if (n == 0) return TE_OK;
-    gelu_kernel<<<grid_for(n, 256, ctx->sm_count), 256, 0, st>>>(x, y, n);
+    launch_pdl(gelu_kernel, dim3(grid_for(n, 256, ctx->sm_count)), dim3(256), 0, st, x, y, n);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return cuda_fail(e, "gelu_kernel launch");
     ctx->launches += 1;
@@ -249,7 +258,7 @@ int launch_gelu(te_b200_ctx* ctx, const float* x, float* y, int64_t n, cudaStrea
 
 int launch_gelu_backward(te_b200_ctx* ctx, const float* x, const float* dy, float* dx, int64_t n, cudaStream_t st) {
     if (n == 0) return TE_OK;
-    gelu_backward_kernel<<<grid_for(n, 256, ctx->sm_count), 256, 0, st>>>(x, dy, dx, n);
+    launch_pdl(gelu_backward_kernel, dim3(grid_for(n, 256, ctx->sm_count)), dim3(256), 0, st, x, dy, dx, n);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return cuda_fail(e, "gelu_backward_kernel launch");
     ctx->launches += 1;
@@ -268,14 +277,14 @@ int launch_colsum(te_b200_ctx* ctx, const float* in, int64_t rows, int64_t cols,
         const long long rows_per_slab = (rows + slabs - 1) / slabs;
         slabs = (rows + rows_per_slab - 1) / rows_per_slab;
         float* partial = static_cast<float*>(ctx->workspace);
-        colsum_slab_kernel<<<dim3((unsigned)col_blocks, (unsigned)slabs), block, 0, st>>>(in, rows, cols, ld, rows_per_slab, partial);
-        colsum_finish_kernel<<<(unsigned)((cols + 255) / 256), 256, 0, st>>>(partial, (int)slabs, cols, out);
+        launch_pdl(colsum_slab_kernel, dim3(dim3((unsigned)col_blocks, (unsigned)slabs)), dim3(block), 0, st, in, rows, cols, ld, rows_per_slab, partial);
+        launch_pdl(colsum_finish_kernel, dim3((unsigned)((cols + 255) / 256)), dim3(256), 0, st, partial, (int)slabs, cols, out);
         cudaError_t e2 = cudaGetLastError();
         if (e2 != cudaSuccess) return cuda_fail(e2, "colsum_slab_kernel launch");
         ctx->launches += 2;
         return TE_OK;
     }
-    colsum_kernel<<<(unsigned)col_blocks, block, 0, st>>>(in, rows, cols, ld, out);
+    launch_pdl(colsum_kernel, dim3((unsigned)col_blocks), dim3(block), 0, st, in, rows, cols, ld, out);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return cuda_fail(e, "colsum_kernel launch");
     ctx->launches += 1;
