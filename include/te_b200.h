@@ -89,7 +89,10 @@ typedef struct te_gemm_desc {
 /* Creates the per-device context on `device` and reserves `workspace_bytes` of
  * device scratch (operand packing for 3xTF32 and for operands TMA cannot address).
  * Replaces the process-wide lazily created cuBLAS handle of
- * src/core/cuda_utils.cpp:48-55.  Returns TE_ERR_NO_DEVICE when no GPU is usable. */
+ * src/core/cuda_utils.cpp:48-55.  Returns TE_ERR_NO_DEVICE when no GPU is usable.
+ * Calls that take the context launch on the caller's stream: `device` must be the calling
+ * thread's current device then (they return TE_ERR_BAD_ARGUMENT otherwise).  A context is
+ * used by one thread and one stream at a time (its scratch is shared by its calls). */
 TE_API int te_b200_init(int device, size_t workspace_bytes, te_b200_ctx** out_ctx);
 TE_API int te_b200_destroy(te_b200_ctx* ctx);
 

@@ -179,6 +179,19 @@ static int gemm_device(te_b200_ctx* ctx, const te_gemm_desc* d, cudaStream_t st,
 
 using namespace te;
 
+// Every compute entry launches on the caller's stream, which belongs to the context's device: that device has to be
+// the calling thread's current one (as it is for the reference, which only ever uses device 0).
+static int check_ctx(const te_b200_ctx* ctx) {
+    if (!ctx) return fail(TE_ERR_BAD_ARGUMENT, "ctx is NULL");
+    int cur = -1;
+    if (cudaGetDevice(&cur) != cudaSuccess || cur != ctx->device) {
+        char msg[128];
+        snprintf(msg, sizeof msg, "the context was created for device %d but device %d is current", ctx->device, cur);
+        return fail(TE_ERR_BAD_ARGUMENT, msg);
+    }
+    return TE_OK;
+}
+
 extern "C" {
 
 const char* te_b200_status_string(int status) {
@@ -266,7 +279,7 @@ int te_b200_destroy(te_b200_ctx* ctx) {
 int64_t te_b200_launch_count(const te_b200_ctx* ctx) { return ctx ? ctx->launches : 0; }
 
 int te_b200_check_device_status(te_b200_ctx* ctx) {
-    if (!ctx) return fail(TE_ERR_BAD_ARGUMENT, "ctx is NULL");
+    if (int bad = check_ctx(ctx)) return bad;
     int h = 0;
     cudaError_t e = cudaMemcpy(&h, ctx->d_status, sizeof(int), cudaMemcpyDeviceToHost);
     if (e != cudaSuccess) return cuda_fail(e, "cudaMemcpy(status)");
@@ -289,7 +302,7 @@ int te_b200_gemm_workspace_size(const te_gemm_desc* d, size_t* out_bytes) {
 }
 
 int te_b200_gemm_f32(te_b200_ctx* ctx, const te_gemm_desc* d, te_stream_t stream) {
-    if (!ctx) return fail(TE_ERR_BAD_ARGUMENT, "ctx is NULL");
+    if (int bad = check_ctx(ctx)) return bad;
     return gemm_device(ctx, d, static_cast<cudaStream_t>(stream));
 }
 
@@ -325,7 +338,7 @@ int te_b200_matmul_nd(te_b200_ctx* ctx, const float* a, const int64_t* a_shape, 
         out_shape[nb + 1] = N;
     }
     if (!c) return TE_OK;   // shape query only
-    if (!ctx) return fail(TE_ERR_BAD_ARGUMENT, "ctx is NULL");
+    if (int bad = check_ctx(ctx)) return bad;
 
     // Per-slice layout, the two cases cublas_params accepts (tensor.h:623-627).
     auto slice_layout = [](int64_t s_row, int64_t s_col, int32_t& major, int64_t& ld) -> bool {
@@ -382,7 +395,7 @@ int te_b200_matmul_nd(te_b200_ctx* ctx, const float* a, const int64_t* a_shape, 
 }
 
 int te_b200_gemm_f32_host(te_b200_ctx* ctx, const te_gemm_desc* h) {
-    if (!ctx) return fail(TE_ERR_BAD_ARGUMENT, "ctx is NULL");
+    if (int bad = check_ctx(ctx)) return bad;
     int rc = validate_desc(h);
     if (rc) return rc;
     if (h->M == 0 || h->N == 0) return TE_OK;
@@ -472,28 +485,28 @@ int te_b200_gemm_f32_host(te_b200_ctx* ctx, const te_gemm_desc* h) {
 }
 
 int te_b200_softmax_rows_f32(te_b200_ctx* ctx, const float* in, float* out, int64_t rows, int64_t cols, te_stream_t s) {
-    if (!ctx) return fail(TE_ERR_BAD_ARGUMENT, "ctx is NULL");
+    if (int bad = check_ctx(ctx)) return bad;
     if (rows < 0 || cols < 0 || cols > INT32_MAX || ((rows && cols) && (!in || !out))) return fail(TE_ERR_BAD_ARGUMENT, "softmax: bad argument");
     return launch_softmax_rows(ctx, in, out, rows, cols, static_cast<cudaStream_t>(s));
 }
 int te_b200_softmax_backward_rows_f32(te_b200_ctx* ctx, const float* sm, const float* dy, float* dx, int64_t rows,
                                       int64_t cols, te_stream_t s) {
-    if (!ctx) return fail(TE_ERR_BAD_ARGUMENT, "ctx is NULL");
+    if (int bad = check_ctx(ctx)) return bad;
     if (rows < 0 || cols < 0 || cols > INT32_MAX || ((rows && cols) && (!sm || !dy || !dx))) return fail(TE_ERR_BAD_ARGUMENT, "softmax backward: bad argument");
     return launch_softmax_backward_rows(ctx, sm, dy, dx, rows, cols, static_cast<cudaStream_t>(s));
 }
 int te_b200_gelu_f32(te_b200_ctx* ctx, const float* x, float* y, int64_t n, te_stream_t s) {
-    if (!ctx) return fail(TE_ERR_BAD_ARGUMENT, "ctx is NULL");
+    if (int bad = check_ctx(ctx)) return bad;
     if (n < 0 || (n && (!x || !y))) return fail(TE_ERR_BAD_ARGUMENT, "gelu: bad argument");
     return launch_gelu(ctx, x, y, n, static_cast<cudaStream_t>(s));
 }
 int te_b200_gelu_backward_f32(te_b200_ctx* ctx, const float* x, const float* dy, float* dx, int64_t n, te_stream_t s) {
-    if (!ctx) return fail(TE_ERR_BAD_ARGUMENT, "ctx is NULL");
+    if (int bad = check_ctx(ctx)) return bad;
     if (n < 0 || (n && (!x || !dy || !dx))) return fail(TE_ERR_BAD_ARGUMENT, "gelu backward: bad argument");
     return launch_gelu_backward(ctx, x, dy, dx, n, static_cast<cudaStream_t>(s));
 }
 int te_b200_colsum_f32(te_b200_ctx* ctx, const float* in, int64_t rows, int64_t cols, int64_t ld, float* out, te_stream_t s) {
-    if (!ctx) return fail(TE_ERR_BAD_ARGUMENT, "ctx is NULL");
+    if (int bad = check_ctx(ctx)) return bad;
     if (rows < 0 || cols < 0 || ld < cols || (cols && !out) || (rows && cols && !in)) return fail(TE_ERR_BAD_ARGUMENT, "colsum: bad argument");
     return launch_colsum(ctx, in, rows, cols, ld, out, static_cast<cudaStream_t>(s));
 }
@@ -501,7 +514,7 @@ int te_b200_colsum_f32(te_b200_ctx* ctx, const float* in, int64_t rows, int64_t 
 int te_b200_linear_forward(te_b200_ctx* ctx, const float* x, const float* w, const float* bias, float* y, float* preact,
                            int64_t rows, int64_t in_features, int64_t out_features, int gelu, int precision,
                            te_stream_t stream) {
-    if (!ctx) return fail(TE_ERR_BAD_ARGUMENT, "ctx is NULL");
+    if (int bad = check_ctx(ctx)) return bad;
     te_gemm_desc d;
     memset(&d, 0, sizeof d);
     d.M = rows; d.N = out_features; d.K = in_features;
@@ -520,7 +533,7 @@ int te_b200_linear_forward(te_b200_ctx* ctx, const float* x, const float* w, con
 int te_b200_linear_backward(te_b200_ctx* ctx, const float* x, const float* w, const float* dy, float* dx, float* dw,
                             float* db, int64_t rows, int64_t in_features, int64_t out_features, int precision,
                             te_stream_t stream) {
-    if (!ctx) return fail(TE_ERR_BAD_ARGUMENT, "ctx is NULL");
+    if (int bad = check_ctx(ctx)) return bad;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     int rc;
     te_gemm_desc d;
@@ -549,7 +562,7 @@ int te_b200_linear_backward(te_b200_ctx* ctx, const float* x, const float* w, co
 }
 
 int te_b200_attention_forward(te_b200_ctx* ctx, const te_attn_desc* t, te_stream_t stream) {
-    if (!ctx) return fail(TE_ERR_BAD_ARGUMENT, "ctx is NULL");
+    if (int bad = check_ctx(ctx)) return bad;
     if (!t || t->B < 0 || t->H < 0 || t->T < 0 || t->d < 0) return fail(TE_ERR_BAD_ARGUMENT, "attention: bad extents");
     if (t->B == 0 || t->H == 0 || t->T == 0) return TE_OK;
     if (!t->q || !t->k || !t->v || !t->p_out || !t->o) return fail(TE_ERR_BAD_ARGUMENT, "attention: NULL pointer");
@@ -589,7 +602,7 @@ int te_b200_attention_forward(te_b200_ctx* ctx, const te_attn_desc* t, te_stream
 }
 
 int te_b200_attention_backward(te_b200_ctx* ctx, const te_attn_bwd_desc* t, te_stream_t stream) {
-    if (!ctx) return fail(TE_ERR_BAD_ARGUMENT, "ctx is NULL");
+    if (int bad = check_ctx(ctx)) return bad;
     if (!t || t->B < 0 || t->H < 0 || t->T < 0 || t->d < 0) return fail(TE_ERR_BAD_ARGUMENT, "attention backward: bad extents");
     if (t->B == 0 || t->H == 0 || t->T == 0 || t->d == 0) return TE_OK;
     if (!t->q || !t->k || !t->v || !t->p || !t->d_o || !t->dq || !t->dk || !t->dv)
@@ -664,7 +677,7 @@ int te_b200_attention_backward(te_b200_ctx* ctx, const te_attn_bwd_desc* t, te_s
 
 int te_b200_layernorm_forward(te_b200_ctx* ctx, const float* x, const float* gamma, const float* beta, float* y,
                               int64_t rows, int64_t cols, float eps, te_stream_t stream) {
-    if (!ctx) return fail(TE_ERR_BAD_ARGUMENT, "ctx is NULL");
+    if (int bad = check_ctx(ctx)) return bad;
     if (rows < 0 || cols < 0) return fail(TE_ERR_BAD_ARGUMENT, "layernorm: negative extent");
     if (rows == 0 || cols == 0) return TE_OK;
     if (!x || !gamma || !beta || !y) return fail(TE_ERR_BAD_ARGUMENT, "layernorm: NULL pointer");
@@ -673,7 +686,7 @@ int te_b200_layernorm_forward(te_b200_ctx* ctx, const float* x, const float* gam
 
 int te_b200_layernorm_backward(te_b200_ctx* ctx, const float* x, const float* gamma, const float* dy, float* dx,
                                float* dgamma, float* dbeta, int64_t rows, int64_t cols, float eps, te_stream_t stream) {
-    if (!ctx) return fail(TE_ERR_BAD_ARGUMENT, "ctx is NULL");
+    if (int bad = check_ctx(ctx)) return bad;
     if (rows < 0 || cols < 0) return fail(TE_ERR_BAD_ARGUMENT, "layernorm backward: negative extent");
     if (cols == 0) return TE_OK;
     if (rows > 0 && (!x || !dy || !dx)) return fail(TE_ERR_BAD_ARGUMENT, "layernorm backward: NULL pointer");
@@ -683,7 +696,7 @@ int te_b200_layernorm_backward(te_b200_ctx* ctx, const float* x, const float* ga
 
 int te_b200_embedding_forward(te_b200_ctx* ctx, const float* table, const int64_t* tokens, const float* pos, float* out,
                               int64_t n, int64_t seq_len, int64_t dim, int64_t vocab, te_stream_t stream) {
-    if (!ctx) return fail(TE_ERR_BAD_ARGUMENT, "ctx is NULL");
+    if (int bad = check_ctx(ctx)) return bad;
     if (n < 0 || dim < 0 || vocab < 0 || (pos && seq_len < 1)) return fail(TE_ERR_BAD_ARGUMENT, "embedding: bad extent");
     if (n == 0 || dim == 0) return TE_OK;
     if (!table || !tokens || !out) return fail(TE_ERR_BAD_ARGUMENT, "embedding: NULL pointer");
@@ -692,7 +705,7 @@ int te_b200_embedding_forward(te_b200_ctx* ctx, const float* table, const int64_
 
 int te_b200_embedding_backward(te_b200_ctx* ctx, const int64_t* tokens, const float* dout, float* dtable, int64_t n,
                                int64_t dim, int64_t vocab, te_stream_t stream) {
-    if (!ctx) return fail(TE_ERR_BAD_ARGUMENT, "ctx is NULL");
+    if (int bad = check_ctx(ctx)) return bad;
     if (n < 0 || dim < 0 || vocab < 0) return fail(TE_ERR_BAD_ARGUMENT, "embedding backward: bad extent");
     if (vocab == 0 || dim == 0) return TE_OK;
     if (!dtable || (n > 0 && (!tokens || !dout))) return fail(TE_ERR_BAD_ARGUMENT, "embedding backward: NULL pointer");
@@ -701,7 +714,7 @@ int te_b200_embedding_backward(te_b200_ctx* ctx, const int64_t* tokens, const fl
 
 int te_b200_cross_entropy(te_b200_ctx* ctx, const float* logits, const int64_t* targets, float* loss, float* dlogits,
                           float upstream, int64_t rows, int64_t vocab, te_stream_t stream) {
-    if (!ctx) return fail(TE_ERR_BAD_ARGUMENT, "ctx is NULL");
+    if (int bad = check_ctx(ctx)) return bad;
     if (rows < 0 || vocab < 0) return fail(TE_ERR_BAD_ARGUMENT, "cross-entropy: negative extent");
     if (rows == 0 || vocab == 0) return TE_OK;
     if (!logits || !targets) return fail(TE_ERR_BAD_ARGUMENT, "cross-entropy: NULL pointer");

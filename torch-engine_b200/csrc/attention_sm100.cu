@@ -362,10 +362,10 @@ int launch_attention_fused(te_b200_ctx* ctx, const te_attn_desc* t, cudaStream_t
     const int smem = 1024 + dchunks * (128 * 128 + 2 * ATT_MAX_T * 128) + 2 * ATT_EPI_WARPS * EPI_STAGE_BYTES + 128;
     if (smem > 232448) return -1;
     static int attr_smem[16] = {};
-    if (ctx->device < 16 && attr_smem[ctx->device] < smem) {
+    if (ctx->device >= 16 || attr_smem[ctx->device] < smem) {
         cudaError_t e = cudaFuncSetAttribute(attention_tf32_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(attention)");
-        attr_smem[ctx->device] = smem;
+        if (ctx->device < 16) attr_smem[ctx->device] = smem;
     }
     p.total_tiles = (int)(t->B * t->H * p.tiles_q);
     const int grid = p.total_tiles < ctx->sm_count ? p.total_tiles : ctx->sm_count;

@@ -519,10 +519,10 @@ static int launch_variant(te_b200_ctx* ctx, const GemmProblem& g_in, int k_split
     using Cfg = TileCfg<BN, NPL>;
     auto kernel = gemm_tf32_kernel<BN, NPL, A_MN, B_MN>;
     static bool attr_done[16] = {};   // per device ordinal
-    if (ctx->device < 16 && !attr_done[ctx->device]) {
+    if (ctx->device >= 16 || !attr_done[ctx->device]) {
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
         if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(max dynamic shared memory)");
-        attr_done[ctx->device] = true;
+        if (ctx->device < 16) attr_done[ctx->device] = true;
     }
     CUtensorMap ma, mal, mb, mbl;
     int rc;

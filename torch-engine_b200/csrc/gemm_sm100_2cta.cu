@@ -345,10 +345,10 @@ static int launch_pair_variant(te_b200_ctx* ctx, const GemmProblem& g_in, int k_
     using Cfg = PairCfg<BN, NPL>;
     auto kernel = gemm_tf32_pair_kernel<BN, NPL, A_MN, B_MN>;
     static bool attr_done[16] = {};
-    if (ctx->device < 16 && !attr_done[ctx->device]) {
+    if (ctx->device >= 16 || !attr_done[ctx->device]) {
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
         if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(max dynamic shared memory)");
-        attr_done[ctx->device] = true;
+        if (ctx->device < 16) attr_done[ctx->device] = true;
     }
     GemmProblem g = g_in;
     CUtensorMap ma, mal, mb, mbl;

@@ -264,7 +264,7 @@ class Backend:
         logits, targets = logits.contiguous(), targets.contiguous()
         vocab = logits.shape[-1]
         rows = logits.numel() // vocab if vocab else 0
-        loss = torch.zeros(1, dtype=torch.float32, device=logits.device)
+        loss = torch.empty(1, dtype=torch.float32, device=logits.device)
         grad = torch.empty_like(logits) if want_grad else None
         L.check(self._lib.te_b200_cross_entropy(self._ctx, _ptr(logits), _ptr(targets), _ptr(loss), _ptr(grad), upstream, rows,
                                                 vocab, self._stream()))
