@@ -336,3 +336,23 @@ def test_launch_counter_moves(backend):
     assert backend.launches == n0 + 1
     backend.matmul(torch.ones(8, 8, device="cuda"), torch.ones(8, 8, device="cuda"), precision="3xtf32")
     assert backend.launches == n0 + 4      # two packing passes + the GEMM
+
+
+def test_pair_tiles_192_wide(backend, oracle):
+    """N in (256, 384] with enough rows takes the 256 x 192 CTA-pair tile in TF32 mode (no quarter-empty 256-wide
+    tiles): all four layouts, ragged N and M, a long K, the fused Linear epilogue and a batched product."""
+    for M, K, N in [(1024, 384, 384), (600, 100, 330), (512, 2100, 384), (4096, 64, 260)]:
+        rng = binding.SeededRng(M + N)
+        a, b = rng.uniform((M, K)), rng.uniform((K, N))
+        ref = oracle.matmul_2d_threads(a, b)
+        for lay, (ta, tb) in _layouts(dev(a), dev(b)).items():
+            assert_close(backend.matmul(ta, tb, precision="tf32").cpu().numpy(), ref, "tf32", f"{M}x{K}x{N} {lay}")
+    rng = binding.SeededRng(17)
+    x, w, bias = rng.normal((2048, 96)), rng.normal((384, 96), 0.0, 0.2), rng.normal((384,), 0.0, 0.5)
+    y, pre = backend.linear_forward(dev(x), dev(w), dev(bias), gelu=True, want_preact=True, precision="tf32")
+    y_ref, pre_ref = oracle.linear(x, w, bias, gelu=True)
+    assert_close(pre.cpu().numpy(), pre_ref, "tf32", "Linear 96->384 pre-activation")
+    assert_close(y.cpu().numpy(), y_ref, "tf32", "Linear 96->384 + GELU")
+    a, b = rng.uniform((3, 512, 48)), rng.uniform((3, 48, 384))
+    assert_close(backend.matmul(dev(a), dev(b), precision="tf32").cpu().numpy(), oracle.matmul(a, b), "tf32", "batched 3x512x48x384")
+    backend.check_device_status()

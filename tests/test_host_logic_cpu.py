@@ -142,3 +142,34 @@ def test_null_context_is_rejected():
     d = _desc()
     assert L.load().te_b200_gemm_f32(None, C.byref(d), None) == L.TE_ERR_BAD_ARGUMENT
     assert L.load().te_b200_softmax_rows_f32(None, None, None, 1, 1, None) == L.TE_ERR_BAD_ARGUMENT
+
+
+def _plan(M, K, N, prec=None, batch=1, sm=148, scratch=1 << 30):
+    d = _desc(M=M, K=K, N=N, lda=K, ldb=N, ldc=N, batch_inner=batch, a_stride_inner=M * K, b_stride_inner=K * N,
+              c_stride_inner=M * N, precision=L.TE_PREC_TF32 if prec is None else prec)
+    bn, pair, splits = C.c_int(), C.c_int(), C.c_int()
+    rc = L.load().te_b200_gemm_plan(C.byref(d), sm, scratch, C.byref(bn), C.byref(pair), C.byref(splits))
+    assert rc == L.TE_OK
+    return bn.value, bool(pair.value), splits.value
+
+
+def test_tile_cost_model_choices():
+    """The tile choice is host arithmetic: pin the decisions the measurements behind it led to."""
+    assert _plan(8192, 8192, 8192) == (256, True, 1)                   # the headline shape: 256 x 256 CTA-pair tiles
+    assert _plan(16384, 384, 384) == (192, True, 1)                    # N = 384: two 192-wide tiles, not 256 + half-empty 256
+    assert _plan(16384, 384, 1536) == (256, True, 1)
+    assert _plan(4096, 768, 3072) == (256, True, 1)
+    bn, pair, splits = _plan(16, 8192, 8192)                           # thin M: single-CTA kernel, K split over several units
+    assert not pair and splits > 1
+    assert _plan(16, 8192, 8192, scratch=0)[2] == 1                    # no scratch, no split
+    bn, pair, splits = _plan(384, 16384, 384)                          # weight gradient: few tiles, long K
+    assert splits > 1
+    assert _plan(100, 64, 100)[1] is False                             # fits one 128-row tile: no pair
+    assert _plan(8192, 8192, 8192, prec=L.TE_PREC_3XTF32) == (256, True, 1)
+    bn, pair, splits = _plan(2048, 2048, 2048, prec=L.TE_PREC_3XTF32)  # 3xTF32 below K ~ 5000: single-CTA form, <= 128 wide
+    assert not pair and bn <= 128
+    for shape in [(1, 1, 1), (1000, 3, 7), (5, 100000, 5), (256, 512, 192)]:
+        bn, pair, splits = _plan(*shape)
+        assert bn in (64, 128, 192, 256) and splits >= 1
+    d = _desc(M=-1)
+    assert L.load().te_b200_gemm_plan(C.byref(d), 148, 0, None, None, None) == L.TE_ERR_BAD_ARGUMENT

@@ -721,6 +721,26 @@ int te_b200_cross_entropy(te_b200_ctx* ctx, const float* logits, const int64_t* 
     return launch_cross_entropy(ctx, logits, targets, loss, dlogits, upstream, rows, vocab, static_cast<cudaStream_t>(stream));
 }
 
+int te_b200_gemm_plan(const te_gemm_desc* d, int sm_count, size_t scratch_bytes, int* tile_n, int* cta_pair, int* k_splits) {
+    int rc = validate_desc(d);
+    if (rc) return rc;
+    if (sm_count < 1) return fail(TE_ERR_BAD_ARGUMENT, "gemm_plan: sm_count must be positive");
+    te_b200_ctx fake;
+    fake.sm_count = sm_count;
+    GemmProblem g;
+    g.M = d->M; g.N = d->N; g.K = d->K;
+    g.batch_inner = d->batch_inner; g.batch_outer = d->batch_outer;
+    static const float marker = 0.0f;
+    g.a_lo = d->precision == TE_PREC_3XTF32 ? &marker : nullptr;
+    g.split_ws = scratch_bytes ? const_cast<float*>(&marker) : nullptr;      // only tested for presence
+    g.split_ws_bytes = scratch_bytes;
+    const TileChoice c = choose_tile(&fake, g);
+    if (tile_n) *tile_n = c.bn;
+    if (cta_pair) *cta_pair = c.pair ? 1 : 0;
+    if (k_splits) *k_splits = c.k_splits;
+    return TE_OK;
+}
+
 int te_b200_shard_range(int64_t total, int world, int rank, int64_t align, int64_t* out_begin, int64_t* out_count) {
     if (total < 0 || world < 1 || rank < 0 || rank >= world || align < 1 || !out_begin || !out_count)
         return fail(TE_ERR_BAD_ARGUMENT, "shard_range: bad argument");

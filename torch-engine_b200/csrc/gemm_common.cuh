@@ -232,8 +232,8 @@ void fill_common_params(GemmParams& p, const te_b200_ctx* ctx, const GemmProblem
 bool make_bhtc_map(te_b200_ctx* ctx, CUtensorMap* out, const float* ptr, int64_t cols, int64_t T, int64_t H, int64_t B,
                    const int64_t* strides_bht, int box_cols, int box_rows, CUtensorMapSwizzle swz);
 
-// gemm_sm100_2cta.cu: the CTA-pair (cta_group::2) TF32 kernel, 256 x 256 tiles.
-int launch_gemm_2cta(te_b200_ctx* ctx, const GemmProblem& g, int k_splits, cudaStream_t stream);
+// gemm_sm100_2cta.cu: the CTA-pair (cta_group::2) TF32 kernel, tiles 256 x bn with bn in {128, 192, 256}.
+int launch_gemm_2cta(te_b200_ctx* ctx, const GemmProblem& g, int bn, int k_splits, cudaStream_t stream);
 
 // Split-K plumbing shared by both kernels (gemm_sm100.cu).  prepare_split rewrites `kernel_problem` so that the GEMM
 // kernel writes raw partial tiles into the scratch of `g`, and fills the split fields of `p`; finish_split launches the

@@ -567,15 +567,16 @@ static int launch_bn(te_b200_ctx* ctx, const GemmProblem& g, int k_splits, cudaS
 // + a fixed per-tile cost) with per-k-block times measured on 8192^3 for each shape (ns): they encode that the
 // small shapes are bound by filling shared memory, not by the tensor pipe.  When a problem has few tiles but a long
 // K (a thin M, a weight gradient over many tokens), K is additionally split over several work units per tile.
-struct TileChoice { int bn; bool pair; int k_splits; };
 
-static TileChoice choose_tile(const te_b200_ctx* ctx, const GemmProblem& g) {
+TileChoice choose_tile(const te_b200_ctx* ctx, const GemmProblem& g) {
     const int kblocks = (int)((g.K + BK - 1) / BK);
     const double batches = (double)(g.batch_inner * g.batch_outer);
     // ns per k-block of one tile in TF32 mode and in 3xTF32 mode (two planes per operand, three MMAs per k-step,
     // fewer and larger pipeline stages), fixed ns per tile
     struct Cand { int bn; bool pair; double ns_per_kblock; double ns_per_kblock_3x; double fixed_ns; };
-    const Cand cands[4] = {{256, true, 405.0, 1400.0, 3000.0}, {256, false, 432.0, 1e9, 3000.0},
+    // (the 256 x 192 pair tile exists for N = 384 and the like, where 256-wide tiles would be a quarter padding;
+    // measured on 16384x384x384: 16.3 us against 18.0 us)
+    const Cand cands[5] = {{256, true, 405.0, 1400.0, 3000.0}, {192, true, 355.0, 1e9, 3000.0}, {256, false, 432.0, 1e9, 3000.0},
                            {128, false, 350.0, 804.0, 2000.0}, {64, false, 291.0, 520.0, 1500.0}};
     const int split_options[8] = {1, 2, 3, 4, 6, 8, 12, 16};
     const double out_bytes = batches * (double)g.M * (double)g.N * 4.0;
@@ -585,6 +586,7 @@ static TileChoice choose_tile(const te_b200_ctx* ctx, const GemmProblem& g) {
         if (c.pair && (g.M <= 128 || g.N <= 128)) continue;
         if (c.pair && g.a_lo && kblocks < 160) continue;         // measured: the 3-stage pair form of 3xTF32 pays off from K ~ 5000
         if (g.a_lo && !c.pair && c.bn > 128) continue;           // 3xTF32, single CTA: two 96 KB stages would be too few
+        if (g.a_lo && c.pair && c.bn != 256) continue;           // 3xTF32 pair form exists for 256-wide tiles only
         if (c.bn > 64 && g.N <= c.bn / 2) continue;              // more than half of the tile would be padding
         const double tm = (double)((g.M + (c.pair ? 255 : 127)) / (c.pair ? 256 : 128));
         const double tn = (double)((g.N + c.bn - 1) / c.bn);
@@ -612,8 +614,14 @@ static TileChoice choose_tile(const te_b200_ctx* ctx, const GemmProblem& g) {
 }
 
 int launch_gemm(te_b200_ctx* ctx, const GemmProblem& g, cudaStream_t stream) {
-    const TileChoice c = choose_tile(ctx, g);
-    if (c.pair) return launch_gemm_2cta(ctx, g, c.k_splits, stream);
+    TileChoice c = choose_tile(ctx, g);
+#ifdef TE_TUNE
+    if (const char* f = getenv("TE_FORCE_TILE")) {     // "bn,pair,splits": tuning builds only
+        int bn = 0, pair = 0, sp = 1;
+        if (sscanf(f, "%d,%d,%d", &bn, &pair, &sp) == 3 && !g.a_lo) c = TileChoice{bn, pair != 0, g.split_ws ? sp : 1};
+    }
+#endif
+    if (c.pair) return launch_gemm_2cta(ctx, g, c.bn, c.k_splits, stream);
     if (c.bn == 256) return launch_bn<256>(ctx, g, c.k_splits, stream);
     if (c.bn == 128) return launch_bn<128>(ctx, g, c.k_splits, stream);
     return launch_bn<64>(ctx, g, c.k_splits, stream);

@@ -32,10 +32,10 @@ struct PairCfg {
     static constexpr int B_HALF_BYTES = (BN / 2) * BK * 4;
     static constexpr int STAGE_BYTES = NPL * (A_PLANE_BYTES + B_HALF_BYTES);      // per CTA; NPL = 2: tf32 hi and lo planes
     static constexpr int STAGES = SMEM_RING_BUDGET / STAGE_BYTES;
-    static constexpr int TMEM_COLS = 2 * BN;
+    static constexpr int TMEM_COLS = 2 * BN <= 256 ? 256 : 512;   // two accumulator buffers BN columns apart; allocations are powers of two
     static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + EPI_WARPS * EPI_STAGE_BYTES + SMEM_AUX_BYTES + 1024;
     static_assert(STAGES >= 2 && STAGES <= 12, "ring depth");
-    static_assert(TMEM_COLS <= 512, "TMEM columns");
+    static_assert(2 * BN <= TMEM_COLS && BN % 64 == 0, "TMEM columns");
     static_assert(SMEM_BYTES <= 232448, "exceeds the 227 KB of shared memory a CTA can have");
 };
 
@@ -396,12 +396,19 @@ static int launch_pair_variant(te_b200_ctx* ctx, const GemmProblem& g_in, int k_
     return k_splits > 1 ? finish_split(ctx, g_in, k_splits, stream) : TE_OK;
 }
 
-int launch_gemm_2cta(te_b200_ctx* ctx, const GemmProblem& g, int k_splits, cudaStream_t stream) {
+template <int BN>
+static int launch_pair_bn(te_b200_ctx* ctx, const GemmProblem& g, int k_splits, cudaStream_t stream) {
+    if (!g.a.mn_major && !g.b.mn_major) return launch_pair_variant<BN, 1, false, false>(ctx, g, k_splits, stream);
+    if (!g.a.mn_major && g.b.mn_major) return launch_pair_variant<BN, 1, false, true>(ctx, g, k_splits, stream);
+    if (g.a.mn_major && !g.b.mn_major) return launch_pair_variant<BN, 1, true, false>(ctx, g, k_splits, stream);
+    return launch_pair_variant<BN, 1, true, true>(ctx, g, k_splits, stream);
+}
+
+int launch_gemm_2cta(te_b200_ctx* ctx, const GemmProblem& g, int bn, int k_splits, cudaStream_t stream) {
     if (g.a_lo) return launch_pair_variant<256, 2, false, false>(ctx, g, k_splits, stream);   // 3xTF32: packed K-major planes
-    if (!g.a.mn_major && !g.b.mn_major) return launch_pair_variant<256, 1, false, false>(ctx, g, k_splits, stream);
-    if (!g.a.mn_major && g.b.mn_major) return launch_pair_variant<256, 1, false, true>(ctx, g, k_splits, stream);
-    if (g.a.mn_major && !g.b.mn_major) return launch_pair_variant<256, 1, true, false>(ctx, g, k_splits, stream);
-    return launch_pair_variant<256, 1, true, true>(ctx, g, k_splits, stream);
+    if (bn == 128) return launch_pair_bn<128>(ctx, g, k_splits, stream);
+    if (bn == 192) return launch_pair_bn<192>(ctx, g, k_splits, stream);
+    return launch_pair_bn<256>(ctx, g, k_splits, stream);
 }
 
 }  // namespace te

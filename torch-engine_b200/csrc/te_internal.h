@@ -64,6 +64,10 @@ bool operand_tma_ok(const Operand& op, int64_t K, int64_t batch_inner, int64_t b
 
 // gemm_sm100.cu
 int launch_gemm(te_b200_ctx* ctx, const GemmProblem& p, cudaStream_t stream);
+// The kernel form launch_gemm picks: tile width, CTA-pair or single-CTA kernel, K splits.  Uses only the extents, the
+// precision (a_lo set or not), the scratch size of `p` and ctx->sm_count; touches no device.
+struct TileChoice { int bn; bool pair; int k_splits; };
+TileChoice choose_tile(const te_b200_ctx* ctx, const GemmProblem& p);
 
 // attention_sm100.cu: fused QK^T -> softmax -> PV.  Returns -1 when the problem is outside the fused kernel's limits.
 int launch_attention_fused(te_b200_ctx* ctx, const te_attn_desc* t, cudaStream_t stream);

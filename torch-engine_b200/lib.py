@@ -88,6 +88,7 @@ SIGNATURES = {
                                          C.c_int64, C.c_int64, C.c_int64, C.c_int, C.c_int, C.c_void_p]),
     "te_b200_linear_backward": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
                                           C.c_void_p, C.c_int64, C.c_int64, C.c_int64, C.c_int, C.c_void_p]),
+    "te_b200_gemm_plan": (C.c_int, [C.POINTER(GemmDesc), C.c_int, C.c_size_t, C.POINTER(C.c_int), C.POINTER(C.c_int), C.POINTER(C.c_int)]),
     "te_b200_attention_forward": (C.c_int, [C.c_void_p, C.POINTER(AttnDesc), C.c_void_p]),
     "te_b200_attention_backward": (C.c_int, [C.c_void_p, C.POINTER(AttnBwdDesc), C.c_void_p]),
     "te_b200_layernorm_forward": (C.c_int, [C.c_void_p] + [C.c_void_p] * 4 + [C.c_int64, C.c_int64, C.c_float, C.c_void_p]),
