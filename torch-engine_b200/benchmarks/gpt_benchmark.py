@@ -4,7 +4,9 @@ gemm_backend, metrics with tokens_per_sec / time_per_step_ms / final_loss).  For
 synthetic token ids (uniform in [0, vocab)); the optimizer update is not part of the matmul path and is left out,
 which the output states.  Environment variables as in the reference (:110-123): TENSOR_EMBED_DIM, TENSOR_NUM_HEADS,
 TENSOR_NUM_LAYERS, TENSOR_FF_DIM, TENSOR_BATCH_SIZE, TENSOR_SEQ_LEN, TENSOR_MEASURED_STEPS, TENSOR_WARMUP_STEPS,
-plus TENSOR_GEMM_PRECISION (tf32 | 3xtf32).  Defaults are benchmark configuration 4.
+plus TENSOR_GEMM_PRECISION (tf32 | 3xtf32) and TENSOR_CUDA_GRAPH=1, which captures one whole step (forward, loss,
+backward: ~300 kernels of this backend and ~150 small torch kernels) into a CUDA graph and replays it, so that the
+host's per-launch cost drops out of the step time (single GPU only).  Defaults are benchmark configuration 4.
 
     python torch-engine_b200/benchmarks/gpt_benchmark.py [out.json]
 
@@ -50,6 +52,7 @@ def main():
     g.manual_seed(1000 + rank)            # same parameters on every rank, different token batches
     tokens = torch.randint(0, vocab, (B, T), device="cuda", generator=g)
     targets = torch.randint(0, vocab, (B, T), device="cuda", generator=g)
+    use_graph = os.environ.get("TENSOR_CUDA_GRAPH", "0") == "1" and world == 1
     loss = None
     for _ in range(warm):
         loss, _, _ = gpt.gpt_step(be, flat, tokens, targets, vocab, E, H, L, ff, prec, grad_sync=sync)
@@ -58,10 +61,28 @@ def main():
         dist.barrier()
     n0 = be.launches
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(steps):
-        loss, _, _ = gpt.gpt_step(be, flat, tokens, targets, vocab, E, H, L, ff, prec, grad_sync=sync)
-    e1.record()
+    if use_graph:
+        graph = torch.cuda.CUDAGraph()
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            gpt.gpt_step(be, flat, tokens, targets, vocab, E, H, L, ff, prec)        # allocator warm-up on this stream
+            with torch.cuda.graph(graph, stream=side):
+                loss, _, grads = gpt.gpt_step(be, flat, tokens, targets, vocab, E, H, L, ff, prec)
+        torch.cuda.synchronize()
+        launches_per_step = be.launches - n0 - (be.launches - n0) // 2                 # the captured pass only
+        graph.replay()
+        torch.cuda.synchronize()
+        e0.record()
+        for _ in range(steps):
+            graph.replay()
+        e1.record()
+    else:
+        e0.record()
+        for _ in range(steps):
+            loss, _, _ = gpt.gpt_step(be, flat, tokens, targets, vocab, E, H, L, ff, prec, grad_sync=sync)
+        e1.record()
+        launches_per_step = None
     torch.cuda.synchronize()
     be.check_device_status()
     ms = e0.elapsed_time(e1) / steps
@@ -84,7 +105,8 @@ def main():
                             "step": "forward + loss + backward (no optimizer update)"},
         "metrics": {"timing_mode": "throughput", "total_time_s": ms * steps / 1e3, "total_tokens": B * T * steps,
                     "tokens_per_sec": B * T / (ms / 1e3), "steps_per_sec": 1e3 / ms, "time_per_step_ms": ms,
-                    "final_loss": float(loss), "backend_kernel_launches_per_step": (be.launches - n0) / steps},
+                    "final_loss": float(loss), "backend_kernel_launches_per_step": launches_per_step if launches_per_step is not None else (be.launches - n0) / steps,
+                    "cuda_graph": bool(use_graph)},
     }
     os.makedirs(os.path.dirname(out_path), exist_ok=True)
     with open(out_path, "w") as f:

@@ -138,7 +138,7 @@ def split_params(flat, vocab, E, n_layers, ff):
         n = 1
         for d in s:
             n *= d
-        out.append(flat[off:off + n].view(s).clone().requires_grad_(True))
+        out.append(flat[off:off + n].view(s).detach().requires_grad_(True))     # a leaf over the same storage, no copy
         off += n
     assert off == flat.numel(), (off, flat.numel())
     return out
