@@ -287,9 +287,6 @@ attention_bwd_tf32_kernel(const __grid_constant__ CUtensorMap tm_v, const __grid
         int s = 0, jc = 0, tc = 0;
         bool ok = true;
         EpilogueRow er;
-#ifdef TE_EPI_LSU
-            er.lsu_base = nullptr;
-#endif
         er.c_row = nullptr; er.pre_row = nullptr; er.row_ok = true; er.vec_ok = false; er.tma_ok = true;
         er.tm_c = nullptr; er.tm_pre = nullptr;
         int stores = 0;

@@ -135,11 +135,6 @@ struct EpilogueRow {
     const CUtensorMap* tm_pre;
     int row0;                  // first of the 32 rows this warp owns
     int bi, bo;                // batch coordinates
-#ifdef TE_EPI_LSU
-    float* lsu_base;           // experiment: batch base of C for the ordinary-store path (NULL: TMA store)
-    long long lsu_ld;
-    int lsu_rows, lsu_cols;
-#endif
 };
 
 // The warp's 32 x 32 block goes through shared memory so that global memory is written in whole 128-byte lines by
@@ -162,23 +157,6 @@ __device__ __forceinline__ void stage_and_store32(const float* v, int col0, cons
                      "f"(v[4 * j + 2]), "f"(v[4 * j + 3])
                      : "memory");
     }
-#ifdef TE_EPI_LSU
-    // experiment: write the staged block out with ordinary coalesced stores (4 rows x 128 B per warp instruction)
-    __syncwarp();
-    if (er.lsu_base) {
-#pragma unroll
-        for (int it = 0; it < 8; ++it) {
-            const int row = it * 4 + (lane >> 3), u = lane & 7;
-            float4 v4;
-            asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v4.x), "=f"(v4.y), "=f"(v4.z), "=f"(v4.w)
-                         : "r"(stage + row * 128 + ((uint32_t(u) ^ (uint32_t(row) & 7u)) << 4)));
-            if (er.row0 + row < er.lsu_rows && col0 + u * 4 < er.lsu_cols)
-                *reinterpret_cast<float4*>(er.lsu_base + (long long)(er.row0 + row) * er.lsu_ld + col0 + u * 4) = v4;
-        }
-        __syncwarp();
-        return;
-    }
-#endif
     fence_proxy_async_smem();
     __syncwarp();
     if (lane == 0) {

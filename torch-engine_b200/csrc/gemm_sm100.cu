@@ -253,9 +253,6 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
             const long long batch_off = (long long)bo * p.c_stride_outer + (long long)bi * p.c_stride_inner +
                                         (long long)w.split * p.split_stride;
             EpilogueRow er;
-#ifdef TE_EPI_LSU
-            er.lsu_base = nullptr;
-#endif
             er.c_row = p.c + batch_off + (long long)row * p.ldc;
             er.pre_row = p.preact ? p.preact + batch_off + (long long)row * p.ldc : nullptr;
             er.row_ok = row < p.M;

@@ -263,10 +263,6 @@ gemm_tf32_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
             er.row0 = m_blk * PAIR_BM + (int)rank * BM + (warp & 3) * 32;
             er.bi = bi;
             er.bo = w.split * p.batch_outer_n + bo;
-#ifdef TE_EPI_LSU
-            er.lsu_base = (p.preact || kblocks > TE_EPI_LSU) ? nullptr : p.c + batch_off;
-            er.lsu_ld = p.ldc; er.lsu_rows = p.M; er.lsu_cols = p.N;
-#endif
             const uint32_t empty_leader = map_to_cta(bar_tmem_empty, 0);
             if (CHUNKED) {
                 // Two-level accumulation (see the single-CTA kernel): chunk sums from TMEM are added in registers.
