@@ -231,12 +231,13 @@ __global__ void __launch_bounds__(256) embedding_forward_kernel(const float* __r
 // thread (one per column) adds the listed rows of dout, eight loads in flight at a time, strictly in list order.
 // Suits the small vocabularies of the reference's character-level models; the scan costs vocab * n / 128 block steps.
 constexpr int EMB_LIST = 1024;
+constexpr int EMB_SUB = 4;               // sub-chunks of 128 token ids scanned per round (one barrier pair per round)
 
 __global__ void __launch_bounds__(128) embedding_backward_kernel(const long long* __restrict__ tokens, const float* __restrict__ dout,
                                                                  float* __restrict__ dtable, long long n, int D) {
     griddep_wait();
-    __shared__ int list[EMB_LIST + 128];
-    __shared__ int warp_count[4];
+    __shared__ int list[EMB_LIST + EMB_SUB * 128];
+    __shared__ int warp_count[EMB_SUB][4];
     const long long v = blockIdx.x;
     const int c = blockIdx.y * 128 + threadIdx.x;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -255,22 +256,35 @@ __global__ void __launch_bounds__(128) embedding_backward_kernel(const long long
         }
         for (; k < filled; ++k) acc += c < D ? __ldg(col + (long long)list[k] * D) : 0.0f;
     };
-    for (long long base = 0; base < n; base += 128) {
+    for (long long base = 0; base < n; base += EMB_SUB * 128) {
         if (filled == 0) list_base = base;
-        const long long i = base + threadIdx.x;
-        const bool hit = i < n && tokens[i] == v;
-        const unsigned m = __ballot_sync(0xffffffffu, hit);
-        if (lane == 0) warp_count[warp] = __popc(m);
-        __syncthreads();
-        int before = 0, total = 0;
+        bool hit[EMB_SUB];
+        unsigned m[EMB_SUB];
 #pragma unroll
-        for (int w = 0; w < 4; ++w) {
-            const int cnt = warp_count[w];
-            if (w < warp) before += cnt;
-            total += cnt;
+        for (int s = 0; s < EMB_SUB; ++s) {                 // the loads of a round are independent
+            const long long i = base + s * 128 + threadIdx.x;
+            hit[s] = i < n && tokens[i] == v;
         }
-        if (hit) list[filled + before + __popc(m & ((1u << lane) - 1u))] = (int)(i - list_base);
-        filled += total;
+#pragma unroll
+        for (int s = 0; s < EMB_SUB; ++s) {
+            m[s] = __ballot_sync(0xffffffffu, hit[s]);
+            if (lane == 0) warp_count[s][warp] = __popc(m[s]);
+        }
+        __syncthreads();
+        int offset = filled;
+#pragma unroll
+        for (int s = 0; s < EMB_SUB; ++s) {                 // positions are appended in ascending token order
+            int before = 0, total = 0;
+#pragma unroll
+            for (int w = 0; w < 4; ++w) {
+                const int cnt = warp_count[s][w];
+                if (w < warp) before += cnt;
+                total += cnt;
+            }
+            if (hit[s]) list[offset + before + __popc(m[s] & ((1u << lane) - 1u))] = (int)(base + s * 128 + threadIdx.x - list_base);
+            offset += total;
+        }
+        filled = offset;
         __syncthreads();                                  // list entries visible; warp_count may be rewritten
         if (filled >= EMB_LIST) {
             consume();
@@ -326,12 +340,16 @@ __global__ void __launch_bounds__(256) cross_entropy_rows_kernel(const float* __
     }
 }
 
+// One warp: lane l adds the block partials l, l + 32, ... in ascending order, then the 32 lane sums meet in a fixed
+// shuffle tree.
 __global__ void cross_entropy_finish_kernel(const double* __restrict__ partial, int blocks, long long rows, float* __restrict__ loss) {
     griddep_wait();
-    if (threadIdx.x != 0 || blockIdx.x != 0) return;
+    const int lane = threadIdx.x;
     double t = 0.0;
-    for (int i = 0; i < blocks; ++i) t += partial[i];
-    *loss = (float)(t / (double)rows);
+    for (int i = lane; i < blocks; i += 32) t += partial[i];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
+    if (lane == 0) *loss = (float)(t / (double)rows);
 }
 
 int row_grid(long long rows, int sm_count, int per_sm) {
@@ -442,7 +460,7 @@ int launch_cross_entropy(te_b200_ctx* ctx, const float* logits, const int64_t* t
         set_error("cross-entropy: vocabulary too large");
         return TE_ERR_BAD_ARGUMENT;
     }
-    const int grid = row_grid(rows, ctx->sm_count, 8);
+    const int grid = row_grid(rows, ctx->sm_count, 2);
     if ((size_t)grid * sizeof(double) > ctx->workspace_bytes) {
         set_error("context workspace too small for the cross-entropy partial sums");
         return TE_ERR_WORKSPACE;
