@@ -66,6 +66,14 @@ def test_colsum_and_elementwise_vs_oracle(backend, oracle):
     rng = binding.SeededRng(4)
     x = rng.normal((1000, 77))
     assert np.abs(backend.colsum(dev(x)).cpu().numpy() - oracle.colsum(x)).max() <= 1e-3
+    # the 16-byte-load form (column count a multiple of 4, tall input), the GPT configuration's bias gradients among
+    # them; ragged slab and column-block tails; against float64 sums (the float order differs from the oracle's)
+    for rows, cols in ((16384, 384), (16384, 1536), (4099, 260), (513, 4), (70000, 132)):
+        y = rng.normal((rows, cols))
+        got = backend.colsum(dev(y))
+        assert torch.equal(got, backend.colsum(dev(y))), "two runs differ"
+        ref64 = y.astype(np.float64).sum(0)
+        assert np.abs(got.cpu().numpy() - ref64).max() <= 2e-5 * np.abs(y).sum(0).max(), (rows, cols)
     v = rng.normal((12345,), 0.0, 2.0)
     assert np.abs(backend.gelu(dev(v)).cpu().numpy() - oracle.gelu(v)).max() <= 1e-5
     dy = rng.normal((12345,))

@@ -196,14 +196,68 @@ __global__ void __launch_bounds__(1024) colsum_slab_kernel(const float* __restri
     }
     if (ty == 0 && col < cols) partial[(long long)blockIdx.y * cols + col] = part[0][tx];
 }
+// The slabs are added by one block per 32 columns: warp w adds slabs w, w + 8, ... in ascending order, then the
+// eight warp sums are added in warp order.
 __global__ void __launch_bounds__(256) colsum_finish_kernel(const float* __restrict__ partial, int slabs, long long cols,
                                                             float* __restrict__ out) {
     griddep_wait();
-    const long long col = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-    if (col >= cols) return;
+    __shared__ float red[8][32];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const long long col = (long long)blockIdx.x * 32 + lane;
     float acc = 0.0f;
-    for (int s = 0; s < slabs; ++s) acc += partial[(long long)s * cols + col];
-    out[col] = acc;
+    if (col < cols)
+        for (int s = warp; s < slabs; s += 8) acc += partial[(long long)s * cols + col];
+    red[warp][lane] = acc;
+    __syncthreads();
+    if (warp == 0 && col < cols) {
+        float t = 0.0f;
+#pragma unroll
+        for (int w = 0; w < 8; ++w) t += red[w][lane];
+        out[col] = t;
+    }
+}
+
+// Slab sums with 16-byte loads (cols and ld multiples of 4, 16-byte aligned base): a block owns 128 columns, its eight
+// warps stride the rows of the slab four rows at a time (16 KB of loads in flight per block), every lane keeps four
+// column sums; the warps' sums are added in warp order through shared memory.
+__global__ void __launch_bounds__(256) colsum_slab_vec4_kernel(const float* __restrict__ in, long long rows, long long cols,
+                                                               long long ld, long long rows_per_slab, float* __restrict__ partial) {
+    griddep_wait();
+    __shared__ float4 red[8][32];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const long long col = (long long)blockIdx.x * 128 + lane * 4;
+    const long long r0 = (long long)blockIdx.y * rows_per_slab;
+    const long long r1 = r0 + rows_per_slab < rows ? r0 + rows_per_slab : rows;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (col < cols) {
+        const float* base = in + col;
+        long long r = r0 + warp;
+        for (; r + 24 < r1; r += 32) {
+            const float4 a = __ldg(reinterpret_cast<const float4*>(base + r * ld));
+            const float4 b = __ldg(reinterpret_cast<const float4*>(base + (r + 8) * ld));
+            const float4 c = __ldg(reinterpret_cast<const float4*>(base + (r + 16) * ld));
+            const float4 d = __ldg(reinterpret_cast<const float4*>(base + (r + 24) * ld));
+            acc.x += a.x; acc.y += a.y; acc.z += a.z; acc.w += a.w;
+            acc.x += b.x; acc.y += b.y; acc.z += b.z; acc.w += b.w;
+            acc.x += c.x; acc.y += c.y; acc.z += c.z; acc.w += c.w;
+            acc.x += d.x; acc.y += d.y; acc.z += d.z; acc.w += d.w;
+        }
+        for (; r < r1; r += 8) {
+            const float4 a = __ldg(reinterpret_cast<const float4*>(base + r * ld));
+            acc.x += a.x; acc.y += a.y; acc.z += a.z; acc.w += a.w;
+        }
+    }
+    red[warp][lane] = acc;
+    __syncthreads();
+    if (warp == 0 && col < cols) {
+        float4 t = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int w = 0; w < 8; ++w) {
+            const float4 x = red[w][lane];
+            t.x += x.x; t.y += x.y; t.z += x.z; t.w += x.w;
+        }
+        *reinterpret_cast<float4*>(partial + (long long)blockIdx.y * cols + col) = t;
+    }
 }
 
 static int grid_for(long long work_items, int per_block, int sm_count) {
@@ -269,6 +323,26 @@ int launch_colsum(te_b200_ctx* ctx, const float* in, int64_t rows, int64_t cols,
                   cudaStream_t st) {
     if (cols == 0) return TE_OK;
     dim3 block(32, 32);
+    const bool vec = (cols & 3) == 0 && (ld & 3) == 0 && (reinterpret_cast<uintptr_t>(in) & 15) == 0 && rows >= 512;
+    if (vec) {
+        // enough (column block, row slab) pairs for ~4 blocks per SM, at least 64 rows per slab
+        const long long cb = (cols + 127) / 128;
+        long long slabs = ((long long)ctx->sm_count * 4 + cb - 1) / cb;
+        if (slabs > rows / 64) slabs = rows / 64;
+        if (slabs < 1) slabs = 1;
+        if (slabs > 65535) slabs = 65535;
+        if ((size_t)(slabs * cols * 4) <= ctx->workspace_bytes) {
+            const long long rows_per_slab = (rows + slabs - 1) / slabs;
+            slabs = (rows + rows_per_slab - 1) / rows_per_slab;
+            float* partial = static_cast<float*>(ctx->workspace);
+            launch_pdl(colsum_slab_vec4_kernel, dim3((unsigned)cb, (unsigned)slabs), dim3(256), 0, st, in, rows, cols, ld, rows_per_slab, partial);
+            launch_pdl(colsum_finish_kernel, dim3((unsigned)((cols + 31) / 32)), dim3(256), 0, st, partial, (int)slabs, cols, out);
+            cudaError_t ev = cudaGetLastError();
+            if (ev != cudaSuccess) return cuda_fail(ev, "colsum_slab_vec4_kernel launch");
+            ctx->launches += 2;
+            return TE_OK;
+        }
+    }
     const long long col_blocks = (cols + 31) / 32;
     // enough (column block, row slab) pairs for ~4 blocks per SM, at least 256 rows per slab
     long long slabs = ((long long)ctx->sm_count * 4 + col_blocks - 1) / col_blocks;
@@ -278,7 +352,7 @@ int launch_colsum(te_b200_ctx* ctx, const float* in, int64_t rows, int64_t cols,
         slabs = (rows + rows_per_slab - 1) / rows_per_slab;
         float* partial = static_cast<float*>(ctx->workspace);
         launch_pdl(colsum_slab_kernel, dim3(dim3((unsigned)col_blocks, (unsigned)slabs)), dim3(block), 0, st, in, rows, cols, ld, rows_per_slab, partial);
-        launch_pdl(colsum_finish_kernel, dim3((unsigned)((cols + 255) / 256)), dim3(256), 0, st, partial, (int)slabs, cols, out);
+        launch_pdl(colsum_finish_kernel, dim3((unsigned)((cols + 31) / 32)), dim3(256), 0, st, partial, (int)slabs, cols, out);
         cudaError_t e2 = cudaGetLastError();
         if (e2 != cudaSuccess) return cuda_fail(e2, "colsum_slab_kernel launch");
         ctx->launches += 2;
