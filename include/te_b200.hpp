@@ -7,6 +7,8 @@
 //   te::Linear          forward(x) = x.matmul(W.transpose_view(1,0)) + b   (reference src/nn/linear.cpp:14-23)
 //   te::FeedForward     Linear -> GELU -> Linear                           (reference src/nn/ffn.cpp:12-16)
 //   te::ScaledDot       softmax(Q.K^T / sqrt(d)).V and its backward        (reference src/nn/scaledot.cpp:8-27)
+//   te::LayerNorm, te::Embedding, te::cross_entropy: the GPT step's kernels around the matmuls
+//                       (reference src/nn/layernorm.cpp, src/nn/embedding.cpp, src/loss/CrossEntropyLoss.cpp)
 // Errors surface as std::runtime_error with the reference's texts (src/tensor/tensor.h:537, :547, :626, :858).
 // Tensors live on the GPU only: this backend has no CPU compute path.  Each Tensor owns (or shares) one device
 // buffer from te::CachingAllocator (the reference's CUDAAllocator calls cudaMalloc per tensor, src/core/allocators.h:35-52).
@@ -348,5 +350,98 @@ public:
         return {dq, dk, dv};
     }
 };
+
+// Int64 device array for token ids and class targets (the reference keeps them in Int64 tensors).
+class IndexArray {
+public:
+    explicit IndexArray(const std::vector<int64_t>& host) : n_(host.size()) {
+        size_t block = 0;
+        void* p = CachingAllocator::instance().allocate((n_ ? n_ : 1) * sizeof(int64_t), &block);
+        storage_ = std::shared_ptr<void>(p, [block](void* q) { CachingAllocator::instance().release(q, block); });
+        cuda_check(cudaMemcpy(p, host.data(), n_ * sizeof(int64_t), cudaMemcpyHostToDevice), "cudaMemcpy H2D");
+    }
+    const int64_t* data() const { return static_cast<const int64_t*>(storage_.get()); }
+    size_t size() const { return n_; }
+private:
+    std::shared_ptr<void> storage_;
+    size_t n_;
+};
+
+// LayerNorm over the last dimension (reference src/nn/layernorm.cpp:19-82); backward returns {dx, dgamma, dbeta} in the
+// order LayerNormBackward does (src/core/grad_fn.cpp:405-538).
+class LayerNorm {
+public:
+    explicit LayerNorm(int64_t normalized_shape, float eps = 1e-5f)
+        : dim_(normalized_shape), eps_(eps),
+          weight_(Tensor::from_host(std::vector<float>((size_t)normalized_shape, 1.0f), {normalized_shape})),
+          bias_(Tensor::from_host(std::vector<float>((size_t)normalized_shape, 0.0f), {normalized_shape})) {}
+    Tensor& weight() { return weight_; }
+    Tensor& bias() { return bias_; }
+    Tensor forward(const Tensor& x) const {
+        if (x.shape().empty() || x.shape().back() != dim_)
+            throw std::runtime_error("Last dimension of input must match normalized_shape");
+        if (!x.is_contiguous()) throw std::runtime_error("LayerNorm requires a contiguous input");
+        Tensor y(x.shape());
+        Backend& be = Backend::instance();
+        check(te_b200_layernorm_forward(be.ctx(), x.data(), weight_.data(), bias_.data(), y.data(),
+                                        (int64_t)(x.numel() / (size_t)dim_), dim_, eps_, nullptr));
+        return y;
+    }
+    std::vector<Tensor> backward(const Tensor& x, const Tensor& dy) const {
+        if (!x.is_contiguous() || !dy.is_contiguous() || x.shape() != dy.shape())
+            throw std::runtime_error("CUDA LayerNormBackward requires contiguous x and pathDownGrad");
+        Tensor dx(x.shape()), dg({dim_}), db({dim_});
+        Backend& be = Backend::instance();
+        check(te_b200_layernorm_backward(be.ctx(), x.data(), weight_.data(), dy.data(), dx.data(), dg.data(), db.data(),
+                                         (int64_t)(x.numel() / (size_t)dim_), dim_, eps_, nullptr));
+        return {dx, dg, db};
+    }
+private:
+    int64_t dim_;
+    float eps_;
+    Tensor weight_, bias_;
+};
+
+// Embedding lookup (reference src/nn/embedding.cpp:18-60) with the optional positional table that GPT::forward adds
+// (src/nn/gpt.cpp:30-69), and the table gradient of EmbeddingBackward (src/core/grad_fn.cpp:688-760).
+class Embedding {
+public:
+    Embedding(int64_t num_embeddings, int64_t dim) : vocab_(num_embeddings), dim_(dim), weight_({num_embeddings, dim}) {}
+    Tensor& weight() { return weight_; }
+    // tokens: batch * seq_len ids; result [batch, seq_len, dim]
+    Tensor forward(const IndexArray& tokens, int64_t batch, int64_t seq_len, const Tensor* positional = nullptr) const {
+        if ((int64_t)tokens.size() != batch * seq_len) throw std::runtime_error("Embedding: token count does not match the shape");
+        Tensor out({batch, seq_len, dim_});
+        Backend& be = Backend::instance();
+        check(te_b200_embedding_forward(be.ctx(), weight_.data(), tokens.data(), positional ? positional->data() : nullptr,
+                                        out.data(), batch * seq_len, seq_len, dim_, vocab_, nullptr));
+        return out;
+    }
+    Tensor backward(const IndexArray& tokens, const Tensor& dout) const {
+        Tensor dw({vocab_, dim_});
+        Backend& be = Backend::instance();
+        check(te_b200_embedding_backward(be.ctx(), tokens.data(), dout.data(), dw.data(), (int64_t)tokens.size(), dim_, vocab_, nullptr));
+        return dw;
+    }
+private:
+    int64_t vocab_, dim_;
+    Tensor weight_;
+};
+
+// crossEntropyLoss::forward_batched over logits [B, T, V] (reference src/loss/CrossEntropyLoss.cpp:47-127): returns the
+// mean loss as a 1-element tensor and, when asked, the gradient CrossEntropyBatchedBackward would produce for an upstream
+// gradient of 1 (src/core/grad_fn.cpp:271-346).
+inline Tensor cross_entropy(const Tensor& logits, const IndexArray& targets, Tensor* dlogits = nullptr) {
+    if (logits.shape().size() != 3) throw std::runtime_error("forward_batched expects 3D logits [B, T, V]");
+    if (!logits.is_contiguous()) throw std::runtime_error("cross_entropy requires contiguous logits");
+    const int64_t V = logits.shape()[2], rows = logits.shape()[0] * logits.shape()[1];
+    if ((int64_t)targets.size() != rows) throw std::runtime_error("forward_batched expects 2D targets [B, T]");
+    Tensor loss({1});
+    Tensor grad = dlogits ? Tensor(logits.shape()) : Tensor();
+    Backend& be = Backend::instance();
+    check(te_b200_cross_entropy(be.ctx(), logits.data(), targets.data(), loss.data(), dlogits ? grad.data() : nullptr, 1.0f, rows, V, nullptr));
+    if (dlogits) *dlogits = grad;
+    return loss;
+}
 
 }  // namespace te

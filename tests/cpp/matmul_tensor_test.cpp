@@ -122,6 +122,47 @@ int main() {
         expect_values("ScaledDot backward dQ", grads[0], zeros, 1e-6f);
         expect_values("ScaledDot backward dK", grads[1], zeros, 1e-6f);
         }
+        // LayerNorm: a row of 1..8 normalises to (j - 4.5) / sqrt(5.25 + eps); with gain 2 and shift 1 on top
+        {
+            te::LayerNorm ln(8);
+            ln.weight() = Tensor::from_host(std::vector<float>(8, 2.0f), {8});
+            ln.bias() = Tensor::from_host(std::vector<float>(8, 1.0f), {8});
+            std::vector<float> xs(16), want(16);
+            for (int r = 0; r < 2; ++r) for (int j = 0; j < 8; ++j) {
+                xs[r * 8 + j] = float(j + 1) * float(r + 1);
+                want[r * 8 + j] = 2.0f * (float(j) - 3.5f) / std::sqrt(5.25f + 1e-5f / float((r + 1) * (r + 1))) + 1.0f;
+            }
+            Tensor x = Tensor::from_host(xs, {2, 8});
+            expect_values("LayerNorm forward", ln.forward(x), want, 1e-4f);
+            // dy = 1 everywhere: dbeta = number of rows, dgamma = column sums of x_hat, dx = 0 (a constant shift of y)
+            std::vector<Tensor> g = ln.backward(x, Tensor::from_host(std::vector<float>(16, 1.0f), {2, 8}));
+            expect_values("LayerNorm backward dx", g[0], std::vector<float>(16, 0.0f), 1e-5f);
+            expect_values("LayerNorm backward dbeta", g[2], std::vector<float>(8, 2.0f), 1e-6f);
+            std::vector<float> want_dg(8);
+            for (int j = 0; j < 8; ++j) want_dg[j] = (want[j] - 1.0f) / 2.0f + (want[8 + j] - 1.0f) / 2.0f;
+            expect_values("LayerNorm backward dgamma", g[1], want_dg, 1e-4f);
+        }
+        // Embedding lookup + positional sum, its table gradient, and the mean cross-entropy of uniform logits (= log V)
+        {
+            te::Embedding emb(5, 4);
+            std::vector<float> table(20);
+            for (int i = 0; i < 20; ++i) table[i] = float(i);
+            emb.weight() = Tensor::from_host(table, {5, 4});
+            te::IndexArray tok({4, 0, 4, 2, 1, 1});                    // batch 2, seq_len 3
+            Tensor pos = Tensor::from_host({100, 100, 100, 100, 200, 200, 200, 200, 300, 300, 300, 300}, {3, 4});
+            std::vector<float> want;
+            const int ids[6] = {4, 0, 4, 2, 1, 1};
+            for (int i = 0; i < 6; ++i) for (int j = 0; j < 4; ++j) want.push_back(table[ids[i] * 4 + j] + 100.0f * float(i % 3 + 1));
+            expect_values("Embedding + positions", emb.forward(tok, 2, 3, &pos), want, 0.0f);
+            Tensor dw = emb.backward(tok, Tensor::from_host(std::vector<float>(24, 1.0f), {2, 3, 4}));
+            expect_values("Embedding backward", dw, {1, 1, 1, 1, 2, 2, 2, 2, 1, 1, 1, 1, 0, 0, 0, 0, 2, 2, 2, 2}, 0.0f);
+            Tensor dlogits;
+            Tensor loss = te::cross_entropy(Tensor::from_host(std::vector<float>(2 * 3 * 5, 0.25f), {2, 3, 5}), tok, &dlogits);
+            expect_values("cross-entropy of uniform logits", loss, {std::log(5.0f)}, 1e-6f);
+            std::vector<float> want_g(30, 0.2f / 6.0f);
+            for (int i = 0; i < 6; ++i) want_g[i * 5 + ids[i]] = (0.2f - 1.0f) / 6.0f;
+            expect_values("cross-entropy gradient", dlogits, want_g, 1e-7f);
+        }
         // Temporaries of a repeated step come out of the allocator's cache: no further cudaMalloc after the first pass.
         {
             Tensor x = Tensor::from_host(std::vector<float>(64 * 48, 0.5f), {64, 48});
