@@ -81,6 +81,25 @@ def test_colsum_and_elementwise_vs_oracle(backend, oracle):
 
 
 @pytest.mark.parametrize("prec", PRECS)
+@pytest.mark.parametrize("rows,in_f,out_f", [(4096, 1536, 384), (300, 100, 40), (257, 77, 33), (64, 8, 4)])
+def test_linear_backward_with_gelu_backward_epilogue(backend, oracle, prec, rows, in_f, out_f):
+    """The second Linear of FeedForward: dx comes back as the gradient of the GELU's pre-activation.  Reference
+    composition: dH = dY . W (MatMulBackward), then GeluBackward on the pre-activation (grad_fn.cpp:169-204)."""
+    rng = binding.SeededRng(rows + in_f)
+    pre, w, dy = rng.normal((rows, in_f)), rng.normal((out_f, in_f), 0.0, 0.2), rng.normal((rows, out_f))
+    h = oracle.gelu(pre)
+    d_pre, dw, db = backend.linear_backward(dev(h), dev(w), dev(dy), precision=prec, gelu_preact=dev(pre))
+    want = oracle.gelu_backward(pre, oracle.matmul_2d_threads(dy, w))
+    assert_close(d_pre.cpu().numpy(), want, prec, "gradient of the pre-activation")
+    plain_dx, dw2, db2 = backend.linear_backward(dev(h), dev(w), dev(dy), precision=prec)
+    assert torch.equal(dw, dw2) and torch.equal(db, db2)
+    # the unfused sequence of this backend agrees to the rounding of the fast tanh
+    two_step = backend.gelu_backward(dev(pre), plain_dx)
+    assert rel_err(d_pre.cpu().numpy(), two_step.cpu().numpy()) <= 1e-5
+    backend.check_device_status()
+
+
+@pytest.mark.parametrize("prec", PRECS)
 def test_linear_golden_forward_backward(backend, nn_gold, prec):
     lin = gc.nn_inputs()["linear"]
     x, w, b, dy = (dev(lin[k]) for k in ("x", "w", "b", "dy"))

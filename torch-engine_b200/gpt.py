@@ -40,6 +40,28 @@ class _Linear(torch.autograd.Function):
         return dx, dw, db, None, None, None
 
 
+class _FeedForward(torch.autograd.Function):
+    """FeedForward::forward (src/nn/ffn.cpp:12-16): Linear -> GELU -> Linear.  Forward keeps the pre-activation of the
+    GELU; backward folds GeluBackward into the dX product of the second Linear, so the gradient of the hidden
+    activation is never written."""
+    @staticmethod
+    def forward(ctx, x, w1, c1, w2, c2, be, prec):
+        h, pre = be.linear_forward(x, w1, c1, gelu=True, want_preact=True, precision=prec)
+        y = be.linear_forward(h, w2, c2, precision=prec)
+        ctx.save_for_backward(x, w1, w2, h, pre)
+        ctx.be, ctx.prec = be, prec
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, w1, w2, h, pre = ctx.saved_tensors
+        be, prec = ctx.be, ctx.prec
+        dy = dy.contiguous()
+        d_pre, dw2, dc2 = be.linear_backward(h, w2, dy, precision=prec, gelu_preact=pre)
+        dx, dw1, dc1 = be.linear_backward(x, w1, d_pre, precision=prec)
+        return dx, dw1, dc1, dw2, dc2, None, None
+
+
 class _ScaledDot(torch.autograd.Function):
     @staticmethod
     def forward(ctx, q, k, v, be, prec):
@@ -163,7 +185,7 @@ def gpt_forward(be, params, tokens, E, H, n_layers, prec="tf32"):
         o = o.transpose(1, 2).reshape(B, T, E)
         x = x + linear(be, o, wo, bo, prec)
         h = layer_norm(be, x, g2, b2)
-        x = x + linear(be, linear(be, h, w1, c1, prec, gelu=True), w2, c2, prec)
+        x = x + _FeedForward.apply(h, w1, c1, w2, c2, be, prec)
     gf, bf, wh, bh = (next(it) for _ in range(4))
     return linear(be, layer_norm(be, x, gf, bf), wh, bh, prec)
 

@@ -123,9 +123,10 @@ class Backend:
                                                  self._stream()))
         return (y, pre) if want_preact else y
 
-    def linear_backward(self, x, w, dy, precision="tf32", need_dx=True, need_dw=True, need_db=True):
-        """(dx, dw[out,in], db[out]) for y = x . w^T + b given dy."""
-        self._check_f32_cuda(x, w, dy)
+    def linear_backward(self, x, w, dy, precision="tf32", need_dx=True, need_dw=True, need_db=True, gelu_preact=None):
+        """(dx, dw[out,in], db[out]) for y = x . w^T + b given dy.  With gelu_preact (x = gelu(gelu_preact), the second
+        Linear of FeedForward) dx is the gradient of that pre-activation: GeluBackward in the epilogue of the dX product."""
+        self._check_f32_cuda(x, w, dy, gelu_preact)
         x = x.contiguous()
         dy = dy.contiguous()
         out_f, in_f = w.shape
@@ -133,9 +134,11 @@ class Backend:
         dx = torch.empty_like(x) if need_dx else None
         dw = torch.empty_like(w) if need_dw else None
         db = torch.empty(out_f, dtype=torch.float32, device=x.device) if need_db else None
-        L.check(self._lib.te_b200_linear_backward(self._ctx, _ptr(x), _ptr(w.contiguous()), _ptr(dy), _ptr(dx),
-                                                  _ptr(dw), _ptr(db), rows, in_f, out_f, _prec(precision),
-                                                  self._stream()))
+        if gelu_preact is not None and (gelu_preact.shape != x.shape or not gelu_preact.is_contiguous()):
+            raise L.BackendError(L.TE_ERR_BAD_ARGUMENT, "gelu_preact must be contiguous and shaped like x")
+        L.check(self._lib.te_b200_linear_backward_gelu(self._ctx, _ptr(x), _ptr(gelu_preact), _ptr(w.contiguous()), _ptr(dy),
+                                                       _ptr(dx), _ptr(dw), _ptr(db), rows, in_f, out_f, _prec(precision),
+                                                       self._stream()))
         return dx, dw, db
 
     # ------------------------------------------------------------------ attention
