@@ -289,7 +289,7 @@ TE_API int te_b200_cross_entropy(te_b200_ctx* ctx, const float* logits, const in
 
 /* Which kernel form te_b200_gemm_f32 would use for this problem on a GPU with `sm_count` SMs
  * and `scratch_bytes` of context workspace left for split-K partials: tile width (64, 128,
- * 192 or 256 columns), whether the CTA-pair (cta_group::2, 256-row tiles) or the single-CTA
+ * 192, 256, 384 or 512 columns), whether the CTA-pair (cta_group::2, 256-row tiles) or the single-CTA
  * (128-row tiles) kernel runs, and into how many work units K is split.  Pure host
  * arithmetic (the tile cost model); needs no GPU and no context.  No reference counterpart:
  * the reference's dispatcher has one kernel per backend (src/tensor/tensor.h:652-698). */

@@ -356,3 +356,27 @@ def test_pair_tiles_192_wide(backend, oracle):
     a, b = rng.uniform((3, 512, 48)), rng.uniform((3, 48, 384))
     assert_close(backend.matmul(dev(a), dev(b), precision="tf32").cpu().numpy(), oracle.matmul(a, b), "tf32", "batched 3x512x48x384")
     backend.check_device_status()
+
+
+def test_wide_pair_tiles(backend, oracle):
+    """Long K with enough tiles takes the wide CTA-pair tiles in TF32 mode (256 x 512 or 256 x 384: two accumulators side
+    by side, one accumulator buffer): all four layouts, ragged M and N (a second tile that is mostly padding, a tile
+    whose second half is empty), the fused Linear epilogue, a batched product, and bit-reproducibility."""
+    # 256 x 512 tiles: (3000, 1100, 3000), (4000, 1040, 2000), (6000, 1040, 1300); 256 x 384 tiles: (3000, 1040, 2304), (4000, 1100, 1300)
+    for M, K, N in [(3000, 1100, 3000), (4000, 1040, 2000), (6000, 1040, 1300), (3000, 1040, 2304), (4000, 1100, 1300)]:
+        rng = binding.SeededRng(M + N + 1)
+        a, b = rng.uniform((M, K)), rng.uniform((K, N))
+        ref = oracle.matmul_2d_threads(a, b)
+        for lay, (ta, tb) in _layouts(dev(a), dev(b)).items():
+            c = backend.matmul(ta, tb, precision="tf32")
+            assert_close(c.cpu().numpy(), ref, "tf32", f"{M}x{K}x{N} {lay}")
+            assert torch.equal(c, backend.matmul(ta, tb, precision="tf32")), "two runs differ"
+    rng = binding.SeededRng(23)
+    x, w, bias = rng.normal((4096, 1024)), rng.normal((2048, 1024), 0.0, 0.05), rng.normal((2048,), 0.0, 0.5)
+    y, pre = backend.linear_forward(dev(x), dev(w), dev(bias), gelu=True, want_preact=True, precision="tf32")
+    y_ref, pre_ref = oracle.linear(x, w, bias, gelu=True)
+    assert_close(pre.cpu().numpy(), pre_ref, "tf32", "Linear 1024->2048 pre-activation")
+    assert_close(y.cpu().numpy(), y_ref, "tf32", "Linear 1024->2048 + GELU")
+    a, b = rng.uniform((3, 2048, 1024)), rng.uniform((3, 1024, 2048))
+    assert_close(backend.matmul(dev(a), dev(b), precision="tf32").cpu().numpy(), oracle.matmul(a, b), "tf32", "batched 3x2048x1024x2048")
+    backend.check_device_status()

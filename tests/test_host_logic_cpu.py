@@ -158,7 +158,10 @@ def _plan(M, K, N, prec=None, batch=1, sm=148, scratch=1 << 30):
 
 def test_tile_cost_model_choices():
     """The tile choice is host arithmetic: pin the decisions the measurements behind it led to."""
-    assert _plan(8192, 8192, 8192) == (256, True, 1)                   # the headline shape: 256 x 256 CTA-pair tiles
+    assert _plan(8192, 8192, 8192) == (512, True, 1)                   # the headline shape: wide 256 x 512 CTA-pair tiles
+    assert _plan(2048, 2048, 2048) == (256, True, 1)                   # too few tiles for the wide form to pay
+    assert _plan(8192, 512, 8192) == (256, True, 1)                    # short K: the wide form's exposed epilogue loses
+    assert _plan(16384, 1536, 384) == (384, True, 1)                   # one wave of 256 x 384 tiles
     assert _plan(16384, 384, 384) == (192, True, 1)                    # N = 384: two 192-wide tiles, not 256 + half-empty 256
     assert _plan(16384, 384, 1536) == (256, True, 1)
     assert _plan(4096, 768, 3072) == (256, True, 1)
@@ -173,6 +176,6 @@ def test_tile_cost_model_choices():
     assert not pair and bn <= 128
     for shape in [(1, 1, 1), (1000, 3, 7), (5, 100000, 5), (256, 512, 192)]:
         bn, pair, splits = _plan(*shape)
-        assert bn in (64, 128, 192, 256) and splits >= 1
+        assert bn in (64, 128, 192, 256, 384, 512) and splits >= 1
     d = _desc(M=-1)
     assert L.load().te_b200_gemm_plan(C.byref(d), 148, 0, None, None, None) == L.TE_ERR_BAD_ARGUMENT

@@ -577,8 +577,12 @@ TileChoice choose_tile(const te_b200_ctx* ctx, const GemmProblem& g) {
     // fewer and larger pipeline stages), fixed ns per tile
     struct Cand { int bn; bool pair; double ns_per_kblock; double ns_per_kblock_3x; double fixed_ns; };
     // (the 256 x 192 pair tile exists for N = 384 and the like, where 256-wide tiles would be a quarter padding;
-    // measured on 16384x384x384: 16.3 us against 18.0 us)
-    const Cand cands[5] = {{256, true, 405.0, 1400.0, 3000.0}, {192, true, 355.0, 1e9, 3000.0}, {256, false, 432.0, 1e9, 3000.0},
+    // measured on 16384x384x384: 16.3 us against 18.0 us.  The wide pair tiles -- 256 x 512 and 256 x 384, two
+    // accumulators side by side, A fetched once for both -- move a third fewer bytes per flop into shared memory but
+    // cannot overlap the epilogue with the next tile: 8192^3 1.55 ms against 1.78 ms, 4096^3 0.190 against 0.214 ms,
+    // 8192x512x8192 0.169 against 0.140 ms; their figures below are fitted to those ratios.)
+    const Cand cands[7] = {{256, true, 405.0, 1400.0, 3000.0}, {512, true, 695.0, 1e9, 8300.0}, {384, true, 618.0, 1e9, 8300.0},
+                           {192, true, 355.0, 1e9, 3000.0}, {256, false, 432.0, 1e9, 3000.0},
                            {128, false, 350.0, 804.0, 2000.0}, {64, false, 291.0, 520.0, 1500.0}};
     const int split_options[8] = {1, 2, 3, 4, 6, 8, 12, 16};
     const double out_bytes = batches * (double)g.M * (double)g.N * 4.0;
@@ -589,6 +593,7 @@ TileChoice choose_tile(const te_b200_ctx* ctx, const GemmProblem& g) {
         if (c.pair && g.a_lo && kblocks < 160) continue;         // measured: the 3-stage pair form of 3xTF32 pays off from K ~ 5000
         if (g.a_lo && !c.pair && c.bn > 128) continue;           // 3xTF32, single CTA: two 96 KB stages would be too few
         if (g.a_lo && c.pair && c.bn != 256) continue;           // 3xTF32 pair form exists for 256-wide tiles only
+        if (c.bn > 256 && kblocks < 32) continue;                // wide tiles: the exposed epilogue needs a long main loop to pay
         if (c.bn > 64 && g.N <= c.bn / 2) continue;              // more than half of the tile would be padding
         const double tm = (double)((g.M + (c.pair ? 255 : 127)) / (c.pair ? 256 : 128));
         const double tn = (double)((g.N + c.bn - 1) / c.bn);

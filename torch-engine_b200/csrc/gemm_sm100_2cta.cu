@@ -27,25 +27,33 @@ namespace te {
 
 constexpr int PAIR_BM = 256;   // rows of one pair tile (128 per CTA)
 
-template <int BN, int NPL>
+// NW = 1: the tile is 256 x BN and tensor memory holds two accumulator buffers, so the epilogue of one tile overlaps
+// the main loop of the next.  NW = 2 ("wide"): the tile is 256 x 2 BN, computed by two MMAs per k-step into two
+// accumulators side by side; A is fetched once for twice the columns (a third fewer bytes per flop into shared
+// memory), at the price of a single accumulator buffer: the next tile's MMAs wait for the epilogue.
+template <int BN, int NPL, int NW = 1>
 struct PairCfg {
-    static constexpr int B_HALF_BYTES = (BN / 2) * BK * 4;
+    static constexpr int TILE_N = NW * BN;
+    static constexpr int B_HALF_BYTES = (TILE_N / 2) * BK * 4;
     static constexpr int STAGE_BYTES = NPL * (A_PLANE_BYTES + B_HALF_BYTES);      // per CTA; NPL = 2: tf32 hi and lo planes
     static constexpr int STAGES = SMEM_RING_BUDGET / STAGE_BYTES;
-    static constexpr int TMEM_COLS = 2 * BN <= 256 ? 256 : 512;   // two accumulator buffers BN columns apart; allocations are powers of two
+    static constexpr int ACC_BUFS = NW == 1 ? 2 : 1;
+    static constexpr int TMEM_COLS = ACC_BUFS * TILE_N <= 256 ? 256 : 512;   // allocations are powers of two
     static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + EPI_WARPS * EPI_STAGE_BYTES + SMEM_AUX_BYTES + 1024;
     static_assert(STAGES >= 2 && STAGES <= 12, "ring depth");
-    static_assert(2 * BN <= TMEM_COLS && BN % 64 == 0, "TMEM columns");
+    static_assert(ACC_BUFS * TILE_N <= TMEM_COLS && BN % 64 == 0 && (NW == 1 || NPL == 1), "TMEM columns");
     static_assert(SMEM_BYTES <= 232448, "exceeds the 227 KB of shared memory a CTA can have");
 };
 
-template <int BN, int NPL, bool A_MN, bool B_MN>
+template <int BN, int NPL, bool A_MN, bool B_MN, int NW = 1>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(CTA_THREADS, 1)
 gemm_tf32_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_a_lo,
                       const __grid_constant__ CUtensorMap tm_b, const __grid_constant__ CUtensorMap tm_b_lo,
                       const __grid_constant__ CUtensorMap tm_c, const __grid_constant__ CUtensorMap tm_pre,
                       const GemmParams p) {
-    using Cfg = PairCfg<BN, NPL>;
+    using Cfg = PairCfg<BN, NPL, NW>;
+    constexpr int TN = Cfg::TILE_N;           // columns of one tile
+    constexpr int ACC_BUFS = Cfg::ACC_BUFS;
     constexpr bool CHUNKED = (NPL == 2);      // 3xTF32: sum K in chunks in TMEM, add the chunks in registers
     constexpr int CHUNK_KB = 8;
     constexpr int B_HALF_BYTES = Cfg::B_HALF_BYTES;
@@ -134,7 +142,7 @@ gemm_tf32_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
                 const int a_ci = bi * p.a_mul_inner, a_co = bo * p.a_mul_outer;
                 const int b_ci = bi * p.b_mul_inner, b_co = bo * p.b_mul_outer;
                 const int m0 = m_blk * PAIR_BM + (int)rank * BM;       // this CTA's 128 rows of A
-                const int n0 = n_blk * BN + (int)rank * HALF_N;        // this CTA's half of the B columns
+                const int n0 = n_blk * TN + (int)rank * HALF_N;        // this CTA's half of the B columns (of every sub-tile)
                 for (int kb = w.kb0; kb < w.kb1; ++kb, ++issued) {
                     const int s = issued % STAGES;
                     const uint32_t phase = (issued / STAGES) & 1;
@@ -159,12 +167,15 @@ gemm_tf32_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
                         } else {
                             tma_load_4d_pair(pa, ma, full, k0, m0, a_ci, a_co);
                         }
-                        if (B_MN) {
 #pragma unroll
-                            for (int c = 0; c < HALF_N / 32; ++c)
-                                tma_load_4d_pair(pb + c * MN_CHUNK_BYTES, mb, full, n0 + 32 * c, k0, b_ci, b_co);
-                        } else {
-                            tma_load_4d_pair(pb, mb, full, k0, n0, b_ci, b_co);
+                        for (int sub = 0; sub < NW; ++sub) {      // sub-tile `sub` takes columns n0 + sub * BN ..
+                            if (B_MN) {
+#pragma unroll
+                                for (int c = 0; c < HALF_N / 32; ++c)
+                                    tma_load_4d_pair(pb + (sub * (HALF_N / 32) + c) * MN_CHUNK_BYTES, mb, full, n0 + sub * BN + 32 * c, k0, b_ci, b_co);
+                            } else {
+                                tma_load_4d_pair(pb + sub * (HALF_N * BK * 4), mb, full, k0, n0 + sub * BN, b_ci, b_co);
+                            }
                         }
                     }
                 }
@@ -188,14 +199,15 @@ gemm_tf32_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
                 int kb = w.kb0;
                 do {   // one pass per accumulator buffer: this unit's whole K range, or one chunk of it
                     const int kb_end = CHUNKED ? min(kb + CHUNK_KB, w.kb1) : w.kb1;
-                    const int buf = acc_idx & 1;
-                    if (!wait_bounded(bar_tmem_empty + 8 * buf, ((acc_idx >> 1) & 1) ^ 1, abort_flag, p.status,
+                    const int buf = ACC_BUFS == 2 ? (acc_idx & 1) : 0;
+                    const uint32_t acc_phase = ACC_BUFS == 2 ? ((acc_idx >> 1) & 1) : (acc_idx & 1);
+                    if (!wait_bounded(bar_tmem_empty + 8 * buf, acc_phase ^ 1, abort_flag, p.status,
                                       WAIT_MMA_TMEM_EMPTY)) {
                         ok = false;
                         break;
                     }
                     tc_fence_after_sync();
-                    const uint32_t d_tmem = tmem_base + buf * BN;
+                    const uint32_t d_tmem = tmem_base + buf * TN;
                     const int kb_first = kb;
                     for (; kb < kb_end; ++kb, ++consumed) {
                         const int s = consumed % STAGES;
@@ -219,6 +231,11 @@ gemm_tf32_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
                                 umma_tf32_pair(d_tmem, a_hi, b_hi, IDESC, 1);
                             } else {
                                 umma_tf32_pair(d_tmem, a_hi, b_hi, IDESC, acc0);
+                                if (NW == 2) {     // second sub-tile: the other half of this CTA pair's B rows, next BN columns
+                                    constexpr uint32_t SUB = B_MN ? (HALF_N / 32) * MN_CHUNK_BYTES : HALF_N * BK * 4;
+                                    const uint64_t b2 = make_smem_desc(sb + SUB + j * B_KSTEP, B_LBO, B_SBO, B_LAYOUT);
+                                    umma_tf32_pair(d_tmem + BN, a_hi, b2, IDESC, acc0);
+                                }
                             }
                         }
                         umma_commit_pair(bar_empty + 8 * s, 3);        // frees the stage in both CTAs
@@ -247,7 +264,7 @@ gemm_tf32_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
             const int batch = w.batch, m_blk = w.m_blk, n_blk = w.n_blk;
             const int bo = batch / p.batch_inner, bi = batch - bo * p.batch_inner;
             const int row = m_blk * PAIR_BM + (int)rank * BM + (warp & 3) * 32 + lane;
-            const int n0 = n_blk * BN;
+            const int n0 = n_blk * TN;
             const long long batch_off = (long long)bo * p.c_stride_outer + (long long)bi * p.c_stride_inner +
                                         (long long)w.split * p.split_stride;
             EpilogueRow er;
@@ -305,14 +322,15 @@ gemm_tf32_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
                     }
                 }
             } else {
-                const int buf = acc_idx & 1;
-                ok = wait_bounded(bar_tmem_full + 8 * buf, (acc_idx >> 1) & 1, abort_flag, p.status, WAIT_EPI_TMEM_FULL);
+                const int buf = ACC_BUFS == 2 ? (acc_idx & 1) : 0;
+                const uint32_t acc_phase = ACC_BUFS == 2 ? ((acc_idx >> 1) & 1) : (acc_idx & 1);
+                ok = wait_bounded(bar_tmem_full + 8 * buf, acc_phase, abort_flag, p.status, WAIT_EPI_TMEM_FULL);
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
                 tc_fence_after_sync();
-                const uint32_t t_row = tmem_base + (uint32_t((warp & 3) * 32) << 16) + buf * BN;
+                const uint32_t t_row = tmem_base + (uint32_t((warp & 3) * 32) << 16) + buf * TN;
 #pragma unroll 1
-                for (int cc = (warp >> 2) * (BN / 64); cc < ((warp >> 2) + 1) * (BN / 64); ++cc) {
+                for (int cc = (warp >> 2) * (TN / 64); cc < ((warp >> 2) + 1) * (TN / 64); ++cc) {
                     const int col0 = n0 + cc * 32;
                     if (col0 >= p.N) break;
                     uint32_t r[32];
@@ -342,10 +360,10 @@ gemm_tf32_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
     }
 }
 
-template <int BN, int NPL, bool A_MN, bool B_MN>
+template <int BN, int NPL, bool A_MN, bool B_MN, int NW = 1>
 static int launch_pair_variant(te_b200_ctx* ctx, const GemmProblem& g_in, int k_splits, cudaStream_t stream) {
-    using Cfg = PairCfg<BN, NPL>;
-    auto kernel = gemm_tf32_pair_kernel<BN, NPL, A_MN, B_MN>;
+    using Cfg = PairCfg<BN, NPL, NW>;
+    auto kernel = gemm_tf32_pair_kernel<BN, NPL, A_MN, B_MN, NW>;
     static bool attr_done[16] = {};
     if (ctx->device >= 16 || !attr_done[ctx->device]) {
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
@@ -370,7 +388,7 @@ static int launch_pair_variant(te_b200_ctx* ctx, const GemmProblem& g_in, int k_
     CUtensorMap mc, mpre;
     p.tma_store = make_output_maps(ctx, g, k_splits, &mc, &mpre) ? 1 : 0;
     p.tiles_m = (int)((g.M + PAIR_BM - 1) / PAIR_BM);
-    p.tiles_n = (int)((g.N + BN - 1) / BN);
+    p.tiles_n = (int)((g.N + Cfg::TILE_N - 1) / Cfg::TILE_N);
     const long long total = (long long)p.tiles_m * p.tiles_n * p.num_batches * k_splits;
     // How many CTA pairs can be resident at once (pairs must sit on neighbouring SMs, so this can be below SMs/2).
     static int max_pairs_cached[16] = {};
@@ -398,18 +416,20 @@ static int launch_pair_variant(te_b200_ctx* ctx, const GemmProblem& g_in, int k_
     return k_splits > 1 ? finish_split(ctx, g_in, k_splits, stream) : TE_OK;
 }
 
-template <int BN>
+template <int BN, int NW = 1>
 static int launch_pair_bn(te_b200_ctx* ctx, const GemmProblem& g, int k_splits, cudaStream_t stream) {
-    if (!g.a.mn_major && !g.b.mn_major) return launch_pair_variant<BN, 1, false, false>(ctx, g, k_splits, stream);
-    if (!g.a.mn_major && g.b.mn_major) return launch_pair_variant<BN, 1, false, true>(ctx, g, k_splits, stream);
-    if (g.a.mn_major && !g.b.mn_major) return launch_pair_variant<BN, 1, true, false>(ctx, g, k_splits, stream);
-    return launch_pair_variant<BN, 1, true, true>(ctx, g, k_splits, stream);
+    if (!g.a.mn_major && !g.b.mn_major) return launch_pair_variant<BN, 1, false, false, NW>(ctx, g, k_splits, stream);
+    if (!g.a.mn_major && g.b.mn_major) return launch_pair_variant<BN, 1, false, true, NW>(ctx, g, k_splits, stream);
+    if (g.a.mn_major && !g.b.mn_major) return launch_pair_variant<BN, 1, true, false, NW>(ctx, g, k_splits, stream);
+    return launch_pair_variant<BN, 1, true, true, NW>(ctx, g, k_splits, stream);
 }
 
 int launch_gemm_2cta(te_b200_ctx* ctx, const GemmProblem& g, int bn, int k_splits, cudaStream_t stream) {
     if (g.a_lo) return launch_pair_variant<256, 2, false, false>(ctx, g, k_splits, stream);   // 3xTF32: packed K-major planes
     if (bn == 128) return launch_pair_bn<128>(ctx, g, k_splits, stream);
     if (bn == 192) return launch_pair_bn<192>(ctx, g, k_splits, stream);
+    if (bn == 384) return launch_pair_bn<192, 2>(ctx, g, k_splits, stream);   // wide tiles: two accumulators side by side
+    if (bn == 512) return launch_pair_bn<256, 2>(ctx, g, k_splits, stream);
     return launch_pair_bn<256>(ctx, g, k_splits, stream);
 }
 
