@@ -362,8 +362,9 @@ def test_wide_pair_tiles(backend, oracle):
     """Long K with enough tiles takes the wide CTA-pair tiles in TF32 mode (256 x 512 or 256 x 384: two accumulators side
     by side, one accumulator buffer): all four layouts, ragged M and N (a second tile that is mostly padding, a tile
     whose second half is empty), the fused Linear epilogue, a batched product, and bit-reproducibility."""
-    # 256 x 512 tiles: (3000, 1100, 3000), (4000, 1040, 2000), (6000, 1040, 1300); 256 x 384 tiles: (3000, 1040, 2304), (4000, 1100, 1300)
-    for M, K, N in [(3000, 1100, 3000), (4000, 1040, 2000), (6000, 1040, 1300), (3000, 1040, 2304), (4000, 1100, 1300)]:
+    # 256 x 512 tiles: (3000, 2100, 3000), (4000, 2048, 2000), (6000, 2048, 1300); 256 x 384 tiles: (3000, 2080, 2304),
+    # (4000, 2100, 1300) and, as a single wave from 32 k-blocks on, (16384, 1536, 384)
+    for M, K, N in [(3000, 2100, 3000), (4000, 2048, 2000), (6000, 2048, 1300), (3000, 2080, 2304), (4000, 2100, 1300), (16384, 1536, 384)]:
         rng = binding.SeededRng(M + N + 1)
         a, b = rng.uniform((M, K)), rng.uniform((K, N))
         ref = oracle.matmul_2d_threads(a, b)
@@ -372,11 +373,11 @@ def test_wide_pair_tiles(backend, oracle):
             assert_close(c.cpu().numpy(), ref, "tf32", f"{M}x{K}x{N} {lay}")
             assert torch.equal(c, backend.matmul(ta, tb, precision="tf32")), "two runs differ"
     rng = binding.SeededRng(23)
-    x, w, bias = rng.normal((4096, 1024)), rng.normal((2048, 1024), 0.0, 0.05), rng.normal((2048,), 0.0, 0.5)
+    x, w, bias = rng.normal((4096, 2048)), rng.normal((2048, 2048), 0.0, 0.05), rng.normal((2048,), 0.0, 0.5)
     y, pre = backend.linear_forward(dev(x), dev(w), dev(bias), gelu=True, want_preact=True, precision="tf32")
     y_ref, pre_ref = oracle.linear(x, w, bias, gelu=True)
-    assert_close(pre.cpu().numpy(), pre_ref, "tf32", "Linear 1024->2048 pre-activation")
-    assert_close(y.cpu().numpy(), y_ref, "tf32", "Linear 1024->2048 + GELU")
-    a, b = rng.uniform((3, 2048, 1024)), rng.uniform((3, 1024, 2048))
-    assert_close(backend.matmul(dev(a), dev(b), precision="tf32").cpu().numpy(), oracle.matmul(a, b), "tf32", "batched 3x2048x1024x2048")
+    assert_close(pre.cpu().numpy(), pre_ref, "tf32", "Linear 2048->2048 pre-activation")
+    assert_close(y.cpu().numpy(), y_ref, "tf32", "Linear 2048->2048 + GELU")
+    a, b = rng.uniform((2, 4096, 2048)), rng.uniform((2, 2048, 2048))     # 2 x 64 wide tiles
+    assert_close(backend.matmul(dev(a), dev(b), precision="tf32").cpu().numpy(), oracle.matmul(a, b), "tf32", "batched 2x4096x2048x2048")
     backend.check_device_status()

@@ -162,6 +162,7 @@ def test_tile_cost_model_choices():
     assert _plan(2048, 2048, 2048) == (256, True, 1)                   # too few tiles for the wide form to pay
     assert _plan(8192, 512, 8192) == (256, True, 1)                    # short K: the wide form's exposed epilogue loses
     assert _plan(16384, 1536, 384) == (384, True, 1)                   # one wave of 256 x 384 tiles
+    assert _plan(8192, 1024, 8192) == (256, True, 1)                   # 32 k-blocks: too short for the wide form
     assert _plan(16384, 384, 384) == (192, True, 1)                    # N = 384: two 192-wide tiles, not 256 + half-empty 256
     assert _plan(16384, 384, 1536) == (256, True, 1)
     assert _plan(4096, 768, 3072) == (256, True, 1)

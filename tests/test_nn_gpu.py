@@ -81,7 +81,7 @@ def test_colsum_and_elementwise_vs_oracle(backend, oracle):
 
 
 @pytest.mark.parametrize("prec", PRECS)
-@pytest.mark.parametrize("rows,in_f,out_f", [(4096, 1536, 384), (300, 100, 40), (257, 77, 33), (64, 8, 4)])
+@pytest.mark.parametrize("rows,in_f,out_f", [(4096, 1536, 384), (4096, 2048, 2048), (300, 100, 40), (257, 77, 33), (64, 8, 4)])
 def test_linear_backward_with_gelu_backward_epilogue(backend, oracle, prec, rows, in_f, out_f):
     """The second Linear of FeedForward: dx comes back as the gradient of the GELU's pre-activation.  Reference
     composition: dH = dY . W (MatMulBackward), then GeluBackward on the pre-activation (grad_fn.cpp:169-204)."""

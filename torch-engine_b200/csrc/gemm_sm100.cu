@@ -593,7 +593,14 @@ TileChoice choose_tile(const te_b200_ctx* ctx, const GemmProblem& g) {
         if (c.pair && g.a_lo && kblocks < 160) continue;         // measured: the 3-stage pair form of 3xTF32 pays off from K ~ 5000
         if (g.a_lo && !c.pair && c.bn > 128) continue;           // 3xTF32, single CTA: two 96 KB stages would be too few
         if (g.a_lo && c.pair && c.bn != 256) continue;           // 3xTF32 pair form exists for 256-wide tiles only
-        if (c.bn > 256 && kblocks < 32) continue;                // wide tiles: the exposed epilogue needs a long main loop to pay
+        // wide tiles: the exposed epilogue needs a long main loop to pay (measured: 8192x1024x8192 and 16384x1024x4096
+        // lose 4-20 % with them, 4096x2048x4096 gains 20 %, everything from K = 4096 on gains 13-30 %)
+        if (c.bn > 256 && kblocks < 64) {
+            // ... except a single wave of 256 x 384 tiles, whose epilogue is exposed only once (16384x1536x384: 37.5 us
+            // against 40.7 us with 192-wide tiles)
+            const long long wide_tiles = ((g.M + 255) / 256) * ((g.N + c.bn - 1) / c.bn) * (long long)batches;
+            if (!(c.bn == 384 && kblocks >= 32 && wide_tiles <= ctx->sm_count / 2)) continue;
+        }
         if (c.bn > 64 && g.N <= c.bn / 2) continue;              // more than half of the tile would be padding
         const double tm = (double)((g.M + (c.pair ? 255 : 127)) / (c.pair ? 256 : 128));
         const double tn = (double)((g.N + c.bn - 1) / c.bn);
