@@ -26,7 +26,24 @@ sys.path.insert(0, ROOT)
 
 import torch  # noqa: E402
 
-from torch_engine_b200 import ops  # noqa: E402
+import ctypes as C  # noqa: E402
+
+from torch_engine_b200 import lib as L, ops  # noqa: E402
+
+
+def plan(M, K, N, mode, sm_count=148, scratch=4 << 30):
+    """(tile width, CTA pair?, K splits) the backend's cost model picks for a dense row-major product."""
+    d = L.GemmDesc()
+    d.M, d.N, d.K = M, N, K
+    d.a = d.b = d.c = 0x1000
+    d.lda, d.ldb, d.ldc = K, N, N
+    d.batch_outer = d.batch_inner = 1
+    d.alpha = 1.0
+    d.precision = L.TE_PREC_3XTF32 if mode == "3xtf32" else L.TE_PREC_TF32
+    bn, pair, sp = C.c_int(), C.c_int(), C.c_int()
+    if L.load().te_b200_gemm_plan(C.byref(d), sm_count, scratch, C.byref(bn), C.byref(pair), C.byref(sp)) != L.TE_OK:
+        return None
+    return {"tile_n": bn.value, "cta_pair": bool(pair.value), "k_splits": sp.value}
 
 
 def peaks():
@@ -137,6 +154,7 @@ def main():
         for mode in ("tf32", "3xtf32"):
             tb, tm = time_gpu(lambda: be.matmul(a, b, precision=mode), it)
             record("b200_tcgen05_gemm", mode, M, K, N, 1, tb, tm, cub)
+            results[-1]["kernel_form"] = plan(M, K, N, mode)
         del a, b
         torch.cuda.empty_cache()
 
