@@ -113,13 +113,13 @@ __device__ __forceinline__ void decode_unit(int u, const GemmParams& p, int kblo
 }
 
 __device__ __forceinline__ float gelu_tanh(float x) {
-    // Same expression as gelu_forward_kernel (reference src/cuda/elementwise_cuda.cu:2701-2707).
-    // tanh(z) = 1 - 2 / (exp(2z) + 1): two fast-math instructions instead of the tanhf routine, absolute error
-    // ~1e-7 (the epilogue evaluates this for every output element, so it has to stay cheaper than the main loop).
-    const float x3 = x * x * x;
-    const float z = 0.7978845608f * (x + 0.044715f * x3);
-    const float t = 1.0f - __fdividef(2.0f, __expf(2.0f * z) + 1.0f);
-    return 0.5f * x * (1.0f + t);
+    // Same function as gelu_forward_kernel (reference src/cuda/elementwise_cuda.cu:2701-2707), 0.5 x (1 + tanh(z)) with
+    // z = 0.79788456 (x + 0.044715 x^3).  Since 0.5 (1 + tanh(z)) = 1 / (1 + exp(-2z)), one fast exponential and one
+    // fast division do it (absolute error ~1e-7; the epilogue evaluates this for every output element, so it has to
+    // stay cheaper than the main loop).
+    const float u = x * x;
+    const float m2z = x * fmaf(u, -2.0f * 0.7978845608f * 0.044715f, -2.0f * 0.7978845608f);    // -2z
+    return __fdividef(x, 1.0f + __expf(m2z));
 }
 
 // d/dx of the tanh-form GELU times the upstream value, the expression of gelu_backward_kernel (reference
