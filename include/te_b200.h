@@ -45,7 +45,7 @@ enum {
 
 enum { TE_ROW_MAJOR = 0, TE_COL_MAJOR = 1 };
 enum { TE_PREC_TF32 = 0, TE_PREC_3XTF32 = 1 };
-enum { TE_EPI_NONE = 0, TE_EPI_BIAS = 1, TE_EPI_BIAS_GELU = 2, TE_EPI_GELU_BACKWARD = 3 };
+enum { TE_EPI_NONE = 0, TE_EPI_BIAS = 1, TE_EPI_BIAS_GELU = 2 };
 enum { TE_SCALE_NONE = 0, TE_SCALE_MUL = 1, TE_SCALE_DIV = 2 };
 
 typedef struct te_b200_ctx te_b200_ctx;   /* one per device; owns the workspace   */
@@ -82,10 +82,6 @@ typedef struct te_gemm_desc {
                                   src/core/grad_fn.cpp:169); same layout as c; NULL to skip */
     int32_t precision;         /* TE_PREC_* */
     int32_t reserved;
-    const float* epilogue_in;  /* TE_EPI_GELU_BACKWARD: the pre-activation x of a GELU, laid out like c; the
-                                  product is multiplied by gelu'(x) on its way out, which is GeluBackward
-                                  (src/core/grad_fn.cpp:169-204) applied to a gradient that never reaches
-                                  memory in between.  NULL otherwise */
 } te_gemm_desc;
 
 /* ---- context --------------------------------------------------------------- */
@@ -191,8 +187,11 @@ TE_API int te_b200_linear_backward(te_b200_ctx* ctx, const float* x, const float
                             int64_t out_features, int precision, te_stream_t stream);
 /* The same when x is the output of a GELU whose pre-activation is x_preact [rows,in] (the second
  * Linear of FeedForward, src/nn/ffn.cpp:12-16): dx receives the gradient with respect to the
- * PRE-activation, dX o gelu'(x_preact), GeluBackward (src/core/grad_fn.cpp:169-204) applied in the
- * epilogue of the dX product.  x_preact == NULL: identical to te_b200_linear_backward. */
+ * PRE-activation, dX o gelu'(x_preact): the dX product followed by GeluBackward
+ * (src/core/grad_fn.cpp:169-204) in place, one call for both.  (Folding GeluBackward into the
+ * product's epilogue was built and measured: the extra loads sit on the epilogue's critical path and
+ * the added code slowed every other epilogue, so the two-kernel form is the faster one.)
+ * x_preact == NULL: identical to te_b200_linear_backward. */
 TE_API int te_b200_linear_backward_gelu(te_b200_ctx* ctx, const float* x, const float* x_preact,
                                  const float* w, const float* dy, float* dx, float* dw, float* db,
                                  int64_t rows, int64_t in_features, int64_t out_features,

@@ -68,9 +68,7 @@ static int validate_desc(const te_gemm_desc* d) {
         return fail(TE_ERR_UNSUPPORTED_LAYOUT, te_b200_status_string(TE_ERR_UNSUPPORTED_LAYOUT));
     if (d->precision != TE_PREC_TF32 && d->precision != TE_PREC_3XTF32)
         return fail(TE_ERR_BAD_ARGUMENT, "precision must be TE_PREC_TF32 or TE_PREC_3XTF32");
-    if (d->epilogue < TE_EPI_NONE || d->epilogue > TE_EPI_GELU_BACKWARD) return fail(TE_ERR_BAD_ARGUMENT, "bad epilogue");
-    if (d->epilogue == TE_EPI_GELU_BACKWARD && !d->epilogue_in)
-        return fail(TE_ERR_BAD_ARGUMENT, "TE_EPI_GELU_BACKWARD needs the pre-activation in epilogue_in");
+    if (d->epilogue < TE_EPI_NONE || d->epilogue > TE_EPI_BIAS_GELU) return fail(TE_ERR_BAD_ARGUMENT, "bad epilogue");
     if (d->scale_mode < TE_SCALE_NONE || d->scale_mode > TE_SCALE_DIV) return fail(TE_ERR_BAD_ARGUMENT, "bad scale_mode");
     if (d->epilogue == TE_EPI_BIAS && !d->bias) return fail(TE_ERR_BAD_ARGUMENT, "TE_EPI_BIAS needs a bias pointer");
     if (d->M == 0 || d->N == 0) return TE_OK;
@@ -153,7 +151,6 @@ static int gemm_device(te_b200_ctx* ctx, const te_gemm_desc* d, cudaStream_t st,
     g.c = d->c; g.ldc = d->ldc; g.c_stride_inner = d->c_stride_inner; g.c_stride_outer = d->c_stride_outer;
     g.preact = d->preact_out; g.bias = d->bias; g.alpha = d->alpha; g.scale_mode = d->scale_mode;
     g.epilogue = d->epilogue;
-    g.epi_in = d->epilogue == TE_EPI_GELU_BACKWARD ? d->epilogue_in : nullptr;
     Carver ws(ctx->workspace, ctx->workspace_bytes - reserve_tail);
     if (d->K > 0) {
         if (d->precision == TE_PREC_3XTF32) {
@@ -553,11 +550,9 @@ int te_b200_linear_backward_gelu(te_b200_ctx* ctx, const float* x, const float* 
         d.b = w; d.ldb = in_features; d.b_major = TE_ROW_MAJOR;
         d.c = dx; d.ldc = in_features;
         d.batch_outer = d.batch_inner = 1; d.alpha = 1.0f; d.precision = precision;
-        if (x_preact) {     // x = gelu(x_preact): hand back the gradient of the pre-activation
-            d.epilogue = TE_EPI_GELU_BACKWARD;
-            d.epilogue_in = x_preact;
-        }
         if ((rc = gemm_device(ctx, &d, st))) return rc;
+        // x = gelu(x_preact): hand back the gradient of the pre-activation (GeluBackward, in place)
+        if (x_preact && (rc = launch_gelu_backward(ctx, x_preact, dx, dx, rows * in_features, st))) return rc;
     }
     if (dw) {   // dW[out,in] = dY^T[out,rows] . X[rows,in]
         memset(&d, 0, sizeof d);

@@ -41,7 +41,6 @@ struct GemmParams {
     long long ldc, c_stride_inner, c_stride_outer;
     float* c;
     float* preact;
-    const float* epi_in;   // TE_EPI_GELU_BACKWARD: pre-activation whose GELU derivative multiplies the product
     const float* bias;
     float alpha;
     int scale_mode;
@@ -122,24 +121,11 @@ __device__ __forceinline__ float gelu_tanh(float x) {
     return __fdividef(x, 1.0f + __expf(m2z));
 }
 
-// d/dx of the tanh-form GELU times the upstream value, the expression of gelu_backward_kernel (reference
-// src/cuda/elementwise_cuda.cu:2709-2724), with the same fast tanh as gelu_tanh above.
-__device__ __forceinline__ float gelu_tanh_backward(float x, float dy) {
-    const float c = 0.7978845608f, k = 0.044715f;
-    const float z = c * (x + k * x * x * x);
-    const float t = 1.0f - __fdividef(2.0f, __expf(2.0f * z) + 1.0f);
-    const float sech_sq = 1.0f - t * t;
-    const float inner = c * (1.0f + 3.0f * k * x * x);
-    return dy * (0.5f * (1.0f + t) * (1.0f + x * sech_sq * inner));
-}
-
 constexpr int EPI_STAGE_BYTES = 32 * 128;   // one warp's staging tile: 32 rows x 32 floats, 128-byte swizzled
 
 struct EpilogueRow {
     float* c_row;      // start of this thread's output row
     float* pre_row;    // same row of the optional pre-activation output
-    const float* in_row;   // same row of the GELU-backward input (valid when row_ok)
-    bool in_vec_ok;        // ... and 16-byte loads from it are legal
     bool row_ok;       // row < M
     bool vec_ok;       // 16-byte stores are legal
     // TMA-store path (used when the output can be described by a tensor map)
@@ -191,26 +177,6 @@ __device__ __forceinline__ void epilogue_store32(float* v, int col0, const Epilo
         const float mine = (col0 + lane < p.N) ? __ldg(p.bias + col0 + lane) : 0.0f;
 #pragma unroll
         for (int j = 0; j < 32; ++j) v[j] += __shfl_sync(0xffffffffu, mine, j);
-    }
-    if (p.epilogue == TE_EPI_GELU_BACKWARD && er.row_ok) {
-        // This thread's 32 pre-activation values sit next to each other in its row.  (Bringing the block in with
-        // coalesced loads through the staging tile was measured and is slower: it adds a store-drain wait and two warp
-        // barriers to every block, 121 us against 99 us on the 16384 x 384 x 1536 dX product.)
-        const float* a = er.in_row + col0;
-        if (col0 + 32 <= p.N && er.in_vec_ok) {
-#pragma unroll
-            for (int j = 0; j < 32; j += 4) {
-                const float4 x = __ldg(reinterpret_cast<const float4*>(a + j));
-                v[j] = gelu_tanh_backward(x.x, v[j]);
-                v[j + 1] = gelu_tanh_backward(x.y, v[j + 1]);
-                v[j + 2] = gelu_tanh_backward(x.z, v[j + 2]);
-                v[j + 3] = gelu_tanh_backward(x.w, v[j + 3]);
-            }
-        } else {
-#pragma unroll
-            for (int j = 0; j < 32; ++j)
-                if (col0 + j < p.N) v[j] = gelu_tanh_backward(__ldg(a + j), v[j]);
-        }
     }
     if (er.tma_ok) {   // warp-uniform
         if (er.row0 >= p.M) return;   // nothing of this warp's 32 rows exists: issue no store at all

@@ -255,8 +255,6 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
             EpilogueRow er;
             er.c_row = p.c + batch_off + (long long)row * p.ldc;
             er.pre_row = p.preact ? p.preact + batch_off + (long long)row * p.ldc : nullptr;
-            er.in_row = p.epi_in ? p.epi_in + batch_off + (long long)row * p.ldc : nullptr;
-            er.in_vec_ok = p.epi_in && ((p.ldc & 3) == 0) && ((reinterpret_cast<uintptr_t>(p.epi_in + batch_off) & 15) == 0);
             er.row_ok = row < p.M;
             // 16-byte stores need every row start aligned: aligned batch base and ldc a multiple of 4.
             er.vec_ok = ((p.ldc & 3) == 0) && ((reinterpret_cast<uintptr_t>(p.c + batch_off) & 15) == 0) &&
@@ -441,7 +439,7 @@ void fill_common_params(GemmParams& p, const te_b200_ctx* ctx, const GemmProblem
     p.b_mul_inner = (g.batch_inner > 1 && g.b.stride_inner != 0) ? 1 : 0;
     p.b_mul_outer = (g.batch_outer > 1 && g.b.stride_outer != 0) ? 1 : 0;
     p.ldc = g.ldc; p.c_stride_inner = g.c_stride_inner; p.c_stride_outer = g.c_stride_outer;
-    p.c = g.c; p.preact = g.preact; p.bias = g.bias; p.epi_in = g.epi_in;
+    p.c = g.c; p.preact = g.preact; p.bias = g.bias;
     p.alpha = g.alpha; p.scale_mode = g.scale_mode; p.epilogue = g.epilogue;
     p.status = ctx->d_status;
     p.k_splits = 1;
@@ -459,9 +457,9 @@ void prepare_split(const GemmProblem& g, int k_splits, GemmProblem& kp, GemmPara
     kp.ldc = g.N;
     kp.c_stride_inner = g.M * g.N;
     kp.c_stride_outer = g.batch_inner * g.M * g.N;
-    kp.preact = nullptr; kp.bias = nullptr; kp.epi_in = nullptr; kp.scale_mode = TE_SCALE_NONE; kp.epilogue = TE_EPI_NONE;
+    kp.preact = nullptr; kp.bias = nullptr; kp.scale_mode = TE_SCALE_NONE; kp.epilogue = TE_EPI_NONE;
     p.c = kp.c; p.ldc = kp.ldc; p.c_stride_inner = kp.c_stride_inner; p.c_stride_outer = kp.c_stride_outer;
-    p.preact = nullptr; p.bias = nullptr; p.epi_in = nullptr; p.scale_mode = TE_SCALE_NONE; p.epilogue = TE_EPI_NONE;
+    p.preact = nullptr; p.bias = nullptr; p.scale_mode = TE_SCALE_NONE; p.epilogue = TE_EPI_NONE;
     p.k_splits = k_splits;
     p.kb_per_split = (kblocks + k_splits - 1) / k_splits;
     p.split_stride = batches * g.M * g.N;
@@ -609,7 +607,6 @@ TileChoice choose_tile(const te_b200_ctx* ctx, const GemmProblem& g) {
         const double ns_kb = g.a_lo ? c.ns_per_kblock_3x : c.ns_per_kblock;
         const double fixed = g.a_lo && c.pair ? 2.0 * c.fixed_ns : c.fixed_ns;
         for (int S : split_options) {
-            if (S > 1 && g.epilogue == TE_EPI_GELU_BACKWARD) break;     // that epilogue lives in the GEMM kernels only
             if (S > 1) {
                 // every split needs a few k-blocks of its own, the scratch must hold S copies of the output, and the
                 // last split must not be empty

@@ -270,8 +270,6 @@ gemm_tf32_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
             EpilogueRow er;
             er.c_row = p.c + batch_off + (long long)row * p.ldc;
             er.pre_row = p.preact ? p.preact + batch_off + (long long)row * p.ldc : nullptr;
-            er.in_row = p.epi_in ? p.epi_in + batch_off + (long long)row * p.ldc : nullptr;
-            er.in_vec_ok = p.epi_in && ((p.ldc & 3) == 0) && ((reinterpret_cast<uintptr_t>(p.epi_in + batch_off) & 15) == 0);
             er.row_ok = row < p.M;
             er.vec_ok = ((p.ldc & 3) == 0) && ((reinterpret_cast<uintptr_t>(p.c + batch_off) & 15) == 0) &&
                         (!p.preact || (reinterpret_cast<uintptr_t>(p.preact + batch_off) & 15) == 0);

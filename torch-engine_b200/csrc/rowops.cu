@@ -147,8 +147,8 @@ __global__ void __launch_bounds__(256) gelu_kernel(const float* __restrict__ x, 
     const long long stride = (long long)gridDim.x * blockDim.x;
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) y[i] = gelu_fwd(x[i]);
 }
-__global__ void __launch_bounds__(256) gelu_backward_kernel(const float* __restrict__ x, const float* __restrict__ dy,
-                                                            float* __restrict__ dx, long long n) {
+// dx may be the same buffer as dy (each element is read, then written, by one thread).
+__global__ void __launch_bounds__(256) gelu_backward_kernel(const float* __restrict__ x, const float* dy, float* dx, long long n) {
     griddep_wait();
     const long long stride = (long long)gridDim.x * blockDim.x;
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride)

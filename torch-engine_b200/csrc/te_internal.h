@@ -27,7 +27,6 @@ struct GemmProblem {
     float* c = nullptr;
     int64_t ldc = 0, c_stride_inner = 0, c_stride_outer = 0;
     float* preact = nullptr;
-    const float* epi_in = nullptr;     // TE_EPI_GELU_BACKWARD: pre-activation, laid out like c
     const float* bias = nullptr;
     float alpha = 1.0f;
     int scale_mode = TE_SCALE_NONE;

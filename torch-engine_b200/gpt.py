@@ -42,8 +42,8 @@ class _Linear(torch.autograd.Function):
 
 class _FeedForward(torch.autograd.Function):
     """FeedForward::forward (src/nn/ffn.cpp:12-16): Linear -> GELU -> Linear.  Forward keeps the pre-activation of the
-    GELU; backward folds GeluBackward into the dX product of the second Linear, so the gradient of the hidden
-    activation is never written."""
+    GELU; backward asks the second Linear for the gradient of that pre-activation directly (one call: dX product, then
+    GeluBackward in place)."""
     @staticmethod
     def forward(ctx, x, w1, c1, w2, c2, be, prec):
         h, pre = be.linear_forward(x, w1, c1, gelu=True, want_preact=True, precision=prec)

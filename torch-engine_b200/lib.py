@@ -13,7 +13,7 @@ TE_ERR_BAD_ARGUMENT, TE_ERR_UNSUPPORTED_LAYOUT, TE_ERR_SHAPE_NDIM, TE_ERR_SHAPE_
 TE_ERR_SHAPE_BROADCAST, TE_ERR_WORKSPACE, TE_ERR_CUDA, TE_ERR_DEVICE_TIMEOUT, TE_ERR_NO_DEVICE = 5, 6, 7, 8, 9
 TE_ROW_MAJOR, TE_COL_MAJOR = 0, 1
 TE_PREC_TF32, TE_PREC_3XTF32 = 0, 1
-TE_EPI_NONE, TE_EPI_BIAS, TE_EPI_BIAS_GELU, TE_EPI_GELU_BACKWARD = 0, 1, 2, 3
+TE_EPI_NONE, TE_EPI_BIAS, TE_EPI_BIAS_GELU = 0, 1, 2
 TE_SCALE_NONE, TE_SCALE_MUL, TE_SCALE_DIV = 0, 1, 2
 TE_B200_STATIC_SCRATCH_BYTES = 64 << 20
 
@@ -35,7 +35,6 @@ class GemmDesc(C.Structure):
         ("alpha", C.c_float), ("scale_mode", C.c_int32), ("epilogue", C.c_int32),
         ("bias", C.c_void_p), ("preact_out", C.c_void_p),
         ("precision", C.c_int32), ("reserved", C.c_int32),
-        ("epilogue_in", C.c_void_p),
     ]
 
 

@@ -125,7 +125,7 @@ class Backend:
 
     def linear_backward(self, x, w, dy, precision="tf32", need_dx=True, need_dw=True, need_db=True, gelu_preact=None):
         """(dx, dw[out,in], db[out]) for y = x . w^T + b given dy.  With gelu_preact (x = gelu(gelu_preact), the second
-        Linear of FeedForward) dx is the gradient of that pre-activation: GeluBackward in the epilogue of the dX product."""
+        Linear of FeedForward) dx is the gradient of that pre-activation: the dX product, then GeluBackward in place."""
         self._check_f32_cuda(x, w, dy, gelu_preact)
         x = x.contiguous()
         dy = dy.contiguous()
