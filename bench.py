@@ -304,7 +304,7 @@ def main():
                          "frac_of_nominal_1125": per_gpu_tflops / 1125.0,
                          # dram__bytes_read.sum + dram__bytes_write.sum of one 8192x8192x8192 launch, single-pass ncu
                          # capture of this kernel (profiles/gemm_tf32_pair_8192_bench_launch_list.md)
-                         "traffic": 1949022208 if (ncols == N_PER_GPU and args.precision == "tf32") else None,
+                         "traffic": 2412997888 if (ncols == N_PER_GPU and args.precision == "tf32") else None,
                          "algorithmic_bytes": 4 * (M * K + K * ncols + M * ncols)},
             "clocks": clocks,
         }
