@@ -36,7 +36,9 @@
 namespace te {
 
 
-template <int BN, int NPL, bool A_MN, bool B_MN>
+// PLAIN: the output is the bare product going out through TMA stores (no scale, bias, pre-activation output or GELU);
+// the general epilogue's code costs registers and drain time even when none of its branches is taken.
+template <int BN, int NPL, bool A_MN, bool B_MN, bool PLAIN = false>
 __global__ void __launch_bounds__(CTA_THREADS, 1)
 gemm_tf32_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_a_lo,
                  const __grid_constant__ CUtensorMap tm_b, const __grid_constant__ CUtensorMap tm_b_lo,
@@ -304,7 +306,13 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
 #pragma unroll
                     for (int cc = 0; cc < NACC / 32; ++cc) {
                         const int col0 = nh + cc * 32;
-                        if (col0 < p.N) epilogue_store32(&acc[cc * 32], col0, er, p, lane);
+                        if (col0 < p.N) {
+                            if constexpr (PLAIN) {
+                                if (er.row0 < p.M) stage_and_store32(&acc[cc * 32], col0, er, er.tm_c, lane);
+                            } else {
+                                epilogue_store32(&acc[cc * 32], col0, er, p, lane);
+                            }
+                        }
                     }
                 }
             } else {
@@ -325,7 +333,11 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                     float v[32];
 #pragma unroll
                     for (int j = 0; j < 32; ++j) v[j] = p.K > 0 ? __uint_as_float(r[j]) : 0.0f;
-                    epilogue_store32(v, col0, er, p, lane);
+                    if constexpr (PLAIN) {
+                        if (er.row0 < p.M) stage_and_store32(v, col0, er, er.tm_c, lane);
+                    } else {
+                        epilogue_store32(v, col0, er, p, lane);
+                    }
                 }
                 // Hand the accumulator buffer back to the MMA warp.
                 tc_fence_before_sync();
@@ -517,10 +529,13 @@ template <int BN, int NPL, bool A_MN, bool B_MN>
 static int launch_variant(te_b200_ctx* ctx, const GemmProblem& g_in, int k_splits, cudaStream_t stream) {
     GemmProblem g = g_in;
     using Cfg = TileCfg<BN, NPL>;
-    auto kernel = gemm_tf32_kernel<BN, NPL, A_MN, B_MN>;
     static bool attr_done[16] = {};   // per device ordinal
     if (ctx->device >= 16 || !attr_done[ctx->device]) {
-        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
+        cudaError_t e = cudaFuncSetAttribute(gemm_tf32_kernel<BN, NPL, A_MN, B_MN, false>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
+        if (e == cudaSuccess && NPL == 1)
+            e = cudaFuncSetAttribute(gemm_tf32_kernel<BN, 1, A_MN, B_MN, true>,
+                                     cudaFuncAttributeMaxDynamicSharedMemorySize, TileCfg<BN, 1>::SMEM_BYTES);
         if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(max dynamic shared memory)");
         if (ctx->device < 16) attr_done[ctx->device] = true;
     }
@@ -544,6 +559,14 @@ static int launch_variant(te_b200_ctx* ctx, const GemmProblem& g_in, int k_split
     p.tiles_n = (int)((g.N + BN - 1) / BN);
     const long long total = (long long)p.tiles_m * p.tiles_n * p.num_batches * k_splits;
     const int grid = (int)(total < ctx->sm_count ? total : ctx->sm_count);
+    // The bare-product kernel serves the calls whose output a tensor map describes and that ask for nothing but the
+    // product (split-K partial tiles included).
+    const bool bare = NPL == 1 && p.tma_store &&
+                      (k_splits > 1 || (!g.bias && !g.preact && g.scale_mode == TE_SCALE_NONE && g.epilogue == TE_EPI_NONE));
+    auto kernel = gemm_tf32_kernel<BN, NPL, A_MN, B_MN, false>;
+    if constexpr (NPL == 1) {
+        if (bare) kernel = gemm_tf32_kernel<BN, 1, A_MN, B_MN, true>;
+    }
     cudaError_t e = launch_pdl(kernel, dim3((unsigned)grid), dim3(CTA_THREADS), Cfg::SMEM_BYTES, stream, ma, mal, mb, mbl, mc, mpre, p);
     if (e != cudaSuccess) return cuda_fail(e, "gemm_tf32_kernel launch");
     ctx->launches += 1;
