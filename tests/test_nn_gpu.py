@@ -78,6 +78,12 @@ def test_colsum_and_elementwise_vs_oracle(backend, oracle):
     assert np.abs(backend.gelu(dev(v)).cpu().numpy() - oracle.gelu(v)).max() <= 1e-5
     dy = rng.normal((12345,))
     assert np.abs(backend.gelu_backward(dev(v), dev(dy)).cpu().numpy() - oracle.gelu_backward(v, dy)).max() <= 1e-5
+    # lengths that take the vector kernels: a ragged last round of a small grid, and more vectors than one round of
+    # the capped grid covers
+    for n in (4 * 100003, 4 * 5000003):
+        v, dy = rng.normal((n,), 0.0, 2.0), rng.normal((n,))
+        assert np.abs(backend.gelu(dev(v)).cpu().numpy() - oracle.gelu(v)).max() <= 1e-5, n
+        assert np.abs(backend.gelu_backward(dev(v), dev(dy)).cpu().numpy() - oracle.gelu_backward(v, dy)).max() <= 1e-5, n
 
 
 @pytest.mark.parametrize("prec", PRECS)

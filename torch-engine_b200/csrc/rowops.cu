@@ -147,12 +147,57 @@ __global__ void __launch_bounds__(256) gelu_kernel(const float* __restrict__ x, 
     const long long stride = (long long)gridDim.x * blockDim.x;
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) y[i] = gelu_fwd(x[i]);
 }
+// 16-byte aligned buffers, n4 = n / 4 vectors, four vectors in flight per thread.
+constexpr int GELU_UNROLL = 4;
+__global__ void __launch_bounds__(256) gelu_vec4_kernel(const float4* __restrict__ x, float4* __restrict__ y, long long n4) {
+    griddep_wait();
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    for (long long i0 = (long long)blockIdx.x * blockDim.x + threadIdx.x; i0 < n4; i0 += stride * GELU_UNROLL) {
+        float4 xv[GELU_UNROLL];
+#pragma unroll
+        for (int u = 0; u < GELU_UNROLL; ++u) {
+            const long long i = i0 + u * stride;
+            if (i < n4) xv[u] = x[i];
+        }
+#pragma unroll
+        for (int u = 0; u < GELU_UNROLL; ++u) {
+            const long long i = i0 + u * stride;
+            if (i < n4) y[i] = make_float4(gelu_fwd(xv[u].x), gelu_fwd(xv[u].y), gelu_fwd(xv[u].z), gelu_fwd(xv[u].w));
+        }
+    }
+}
 // dx may be the same buffer as dy (each element is read, then written, by one thread).
 __global__ void __launch_bounds__(256) gelu_backward_kernel(const float* __restrict__ x, const float* dy, float* dx, long long n) {
     griddep_wait();
     const long long stride = (long long)gridDim.x * blockDim.x;
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride)
         dx[i] = gelu_bwd(x[i], dy[i]);
+}
+// The same for 16-byte aligned buffers, n4 = n / 4 vectors: because dx may alias dy the compiler cannot move loads
+// above stores by itself, so each thread first loads the operands of GELU_BWD_UNROLL vectors and then writes them --
+// enough loads in flight to reach the HBM rate, and still every element is read before it is written.
+constexpr int GELU_BWD_UNROLL = 4;
+__global__ void __launch_bounds__(256) gelu_backward_vec4_kernel(const float4* __restrict__ x, const float4* dy, float4* dx, long long n4) {
+    griddep_wait();
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    for (long long i0 = (long long)blockIdx.x * blockDim.x + threadIdx.x; i0 < n4; i0 += stride * GELU_BWD_UNROLL) {
+        float4 xv[GELU_BWD_UNROLL], gv[GELU_BWD_UNROLL];
+#pragma unroll
+        for (int u = 0; u < GELU_BWD_UNROLL; ++u) {
+            const long long i = i0 + u * stride;
+            if (i < n4) { xv[u] = x[i]; gv[u] = dy[i]; }
+        }
+#pragma unroll
+        for (int u = 0; u < GELU_BWD_UNROLL; ++u) {
+            const long long i = i0 + u * stride;
+            if (i < n4) {
+                float4 r;
+                r.x = gelu_bwd(xv[u].x, gv[u].x); r.y = gelu_bwd(xv[u].y, gv[u].y);
+                r.z = gelu_bwd(xv[u].z, gv[u].z); r.w = gelu_bwd(xv[u].w, gv[u].w);
+                dx[i] = r;
+            }
+        }
+    }
 }
 
 // out[j] = sum over rows of in[i*ld + j].  One block owns 32 columns; its 32 row-lanes stride the rows,
@@ -303,7 +348,11 @@ int launch_softmax_backward_rows(te_b200_ctx* ctx, const float* s, const float* 
 
 int launch_gelu(te_b200_ctx* ctx, const float* x, float* y, int64_t n, cudaStream_t st) {
     if (n == 0) return TE_OK;
-    launch_pdl(gelu_kernel, dim3(grid_for(n, 256, ctx->sm_count)), dim3(256), 0, st, x, y, n);
+    if ((n & 3) == 0 && ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y)) & 15) == 0)
+        launch_pdl(gelu_vec4_kernel, dim3(grid_for(n / 4 / GELU_UNROLL + 1, 256, ctx->sm_count)), dim3(256), 0, st,
+                   reinterpret_cast<const float4*>(x), reinterpret_cast<float4*>(y), (long long)(n / 4));
+    else
+        launch_pdl(gelu_kernel, dim3(grid_for(n, 256, ctx->sm_count)), dim3(256), 0, st, x, y, n);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return cuda_fail(e, "gelu_kernel launch");
     ctx->launches += 1;
@@ -312,7 +361,14 @@ int launch_gelu(te_b200_ctx* ctx, const float* x, float* y, int64_t n, cudaStrea
 
 int launch_gelu_backward(te_b200_ctx* ctx, const float* x, const float* dy, float* dx, int64_t n, cudaStream_t st) {
     if (n == 0) return TE_OK;
-    launch_pdl(gelu_backward_kernel, dim3(grid_for(n, 256, ctx->sm_count)), dim3(256), 0, st, x, dy, dx, n);
+    const bool vec = (n & 3) == 0 && ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(dy) |
+                                        reinterpret_cast<uintptr_t>(dx)) & 15) == 0;
+    if (vec)
+        launch_pdl(gelu_backward_vec4_kernel, dim3(grid_for(n / 4 / GELU_BWD_UNROLL + 1, 256, ctx->sm_count)), dim3(256), 0, st,
+                   reinterpret_cast<const float4*>(x), reinterpret_cast<const float4*>(dy), reinterpret_cast<float4*>(dx),
+                   (long long)(n / 4));
+    else
+        launch_pdl(gelu_backward_kernel, dim3(grid_for(n, 256, ctx->sm_count)), dim3(256), 0, st, x, dy, dx, n);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return cuda_fail(e, "gelu_backward_kernel launch");
     ctx->launches += 1;
