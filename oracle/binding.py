@@ -3,6 +3,9 @@
 `Oracle`    - liboracle.so, the plain-C restatement (te_oracle.c); built by `make -C oracle`.
 `Reference` - _ref/libref_cpu.so, the reference's own CPU path compiled from its sources (ref_driver.cpp).
               Present only where it was built; it travels as a prebuilt file.
+`ReferenceCuda` - _ref_cuda/libref_cuda.so, the reference's CUDA path built for sm_100a with the
+              TENSOR_GEMM_BACKEND=b200 binding applied (same driver, USE_CUDA): the reference's own Tensor / nn /
+              autograd code on the GPU under its cuBLAS, `custom` or `b200` GEMM backend.  Needs a GPU to run.
 Only tests/, the smoke check and the benchmark's CPU legs may import this module.
 """
 import ctypes as C
@@ -14,13 +17,16 @@ import numpy as np
 _HERE = os.path.dirname(os.path.abspath(__file__))
 ORACLE_PATH = os.path.join(_HERE, "liboracle.so")
 REF_PATH = os.path.join(_HERE, "_ref", "libref_cpu.so")
+REF_CUDA_PATH = os.path.join(_HERE, "_ref_cuda", "libref_cuda.so")
+REF_CUDA_MATMUL_TEST = os.path.join(_HERE, "_ref_cuda", "cuda_matmul_tensor_test")
 
 _f32p = np.ctypeslib.ndpointer(dtype=np.float32, flags="C_CONTIGUOUS")
 
 
 def build(reference_root="/root/reference"):
-    """Runs the Makefile: liboracle.so always, _ref/libref_cpu.so when the reference sources are present."""
-    subprocess.run(["make", "-s", "-C", _HERE, "-j8", "REF=" + reference_root], check=True)
+    """Runs the Makefile: liboracle.so always; _ref/libref_cpu.so and (once libte_b200.so exists) the patched CUDA
+    build _ref_cuda/ when the reference sources are present."""
+    subprocess.run(["make", "-s", "-C", _HERE, "-j8", "REF=" + reference_root, "all", "ref_cuda"], check=True)
 
 
 def _i64(seq):
@@ -285,11 +291,17 @@ class Reference:
     def available():
         return os.path.exists(REF_PATH)
 
+    PATH = REF_PATH
+    prefix = "ref_"       # ReferenceCuda switches to "ref_fused_" for the module-level calls
+
     def __init__(self):
-        if not os.path.exists(REF_PATH):
-            raise RuntimeError("reference CPU library not built (needs the reference sources): " + REF_PATH)
-        self.lib = C.CDLL(REF_PATH)
+        if not os.path.exists(self.PATH):
+            raise RuntimeError("reference library not built (needs the reference sources): " + self.PATH)
+        self.lib = C.CDLL(self.PATH)
         self.lib.ref_last_error.restype = C.c_char_p
+
+    def _fn(self, name):
+        return getattr(self.lib, self.prefix + name)
 
     def _check(self, rc):
         if rc:
@@ -333,7 +345,7 @@ class Reference:
             dy = np.ascontiguousarray(dy, dtype=np.float32)
             res.update(dx=np.empty_like(x), dw=np.empty_like(w), db=np.empty_like(bias))
         p = lambda k: _fptr(res[k]) if k in res else None
-        self._check(self.lib.ref_linear(_fptr(x), _i64(x.shape), x.ndim, _fptr(w), _fptr(bias), C.c_int64(in_f),
+        self._check(self._fn("linear")(_fptr(x), _i64(x.shape), x.ndim, _fptr(w), _fptr(bias), C.c_int64(in_f),
                                         C.c_int64(out_f), int(gelu), _fptr(dy) if dy is not None else None,
                                         p("y"), p("preact"), p("dx"), p("dw"), p("db")))
         return res
@@ -386,7 +398,7 @@ class Reference:
             res.update(dx=np.empty_like(x), dw1=np.empty_like(w1), db1=np.empty_like(b1), dw2=np.empty_like(w2),
                        db2=np.empty_like(b2))
         p = lambda k: _fptr(res[k]) if k in res else None
-        self._check(self.lib.ref_ffn(_fptr(x), _i64(x.shape), x.ndim, C.c_int64(embed), C.c_int64(ff), _fptr(w1),
+        self._check(self._fn("ffn")(_fptr(x), _i64(x.shape), x.ndim, C.c_int64(embed), C.c_int64(ff), _fptr(w1),
                                      _fptr(b1), _fptr(w2), _fptr(b2), _fptr(dy) if dy is not None else None, p("y"),
                                      p("dx"), p("dw1"), p("db1"), p("dw2"), p("db2")))
         return res
@@ -398,7 +410,7 @@ class Reference:
             d_o = np.ascontiguousarray(d_o, dtype=np.float32)
             res.update(dq=np.empty_like(q), dk=np.empty_like(k), dv=np.empty_like(v))
         p = lambda n: _fptr(res[n]) if n in res else None
-        self._check(self.lib.ref_scaled_dot(_fptr(q), C.byref(vq), _fptr(k), C.byref(vk), _fptr(v), C.byref(vv),
+        self._check(self._fn("scaled_dot")(_fptr(q), C.byref(vq), _fptr(k), C.byref(vk), _fptr(v), C.byref(vv),
                                             _fptr(d_o) if d_o is not None else None, p("o"), p("dq"), p("dk"), p("dv")))
         return res
 
@@ -414,7 +426,7 @@ class Reference:
             res["dx"] = np.empty_like(x)
             res["dparams"] = [np.empty_like(t) for t in params]
             dpp = (C.c_void_p * 8)(*[t.ctypes.data for t in res["dparams"]])
-        self._check(self.lib.ref_mha(_fptr(x), C.c_int64(B), C.c_int64(T), C.c_int64(E), C.c_int64(H), pp,
+        self._check(self._fn("mha")(_fptr(x), C.c_int64(B), C.c_int64(T), C.c_int64(E), C.c_int64(H), pp,
                                      _fptr(dy) if dy is not None else None, _fptr(res["y"]),
                                      _fptr(res["dx"]) if dy is not None else None, dpp))
         return res
@@ -440,3 +452,54 @@ class Reference:
                                           _fptr(logits) if want_logits else None,
                                           _fptr(grads) if want_grads else None))
         return loss.value, logits, grads
+
+
+class ReferenceCuda(Reference):
+    """The reference's CUDA path (sm_100a build with the b200 binding).  `backend` is the value of
+    TENSOR_GEMM_BACKEND the reference reads on every matmul: None (cuBLAS FP32), "custom", or "b200";
+    `precision` is TENSOR_GEMM_PRECISION for the b200 backend ("tf32" / "3xtf32").  With fused=True the
+    module-level calls (linear, ffn, scaled_dot, mha) go through include/torchengine/te_b200_modules.h, i.e. the
+    fused C-ABI calls with their own GradFn nodes inside the reference's autograd engine."""
+    PATH = REF_CUDA_PATH
+
+    @staticmethod
+    def available():
+        return os.path.exists(REF_CUDA_PATH)
+
+    def __init__(self, backend=None, precision="tf32", fused=False):
+        super().__init__()
+        self.configure(backend, precision, fused)
+        self._check(self.lib.ref_use_cuda(1))
+
+    def configure(self, backend=None, precision="tf32", fused=False):
+        if backend is None:
+            os.environ.pop("TENSOR_GEMM_BACKEND", None)
+        else:
+            os.environ["TENSOR_GEMM_BACKEND"] = backend
+        os.environ["TENSOR_GEMM_PRECISION"] = precision
+        self.prefix = "ref_fused_" if fused else "ref_"
+        return self
+
+    def cublas_tf32(self, on):
+        self._check(self.lib.ref_cuda_cublas_tf32(int(on)))
+
+    def time_matmul(self, M, K, N, warmup=3, iters=10, want_result=False):
+        """(ms per call, last product or None) of Tensor::matmul on mt19937(42) uniform(-1,1) operands."""
+        ms = C.c_double()
+        out = np.empty((M, N), dtype=np.float32) if want_result else None
+        self._check(self.lib.ref_cuda_time_matmul(C.c_int64(M), C.c_int64(K), C.c_int64(N), C.c_int32(warmup),
+                                                  C.c_int32(iters), C.byref(ms), _fptr(out) if want_result else None))
+        return ms.value, out
+
+    def gpt_bench(self, vocab, max_seq, E, H, Lyr, ff, flat_params, tokens, targets, warmup=1, steps=3):
+        """(ms per forward+loss+backward step, last loss) of the reference's own GPT on the GPU."""
+        flat_params = np.ascontiguousarray(flat_params, dtype=np.float32)
+        tokens = np.ascontiguousarray(tokens, dtype=np.int64)
+        targets = np.ascontiguousarray(targets, dtype=np.int64)
+        batch, seq = tokens.shape
+        ms, loss = C.c_double(), C.c_float()
+        self._check(self.lib.ref_cuda_gpt_bench(C.c_int64(vocab), C.c_int64(max_seq), C.c_int64(E), C.c_int64(H),
+                                                C.c_int64(Lyr), C.c_int64(ff), C.c_int64(batch), C.c_int64(seq),
+                                                _fptr(flat_params), _fptr(tokens), _fptr(targets), C.c_int32(warmup),
+                                                C.c_int32(steps), C.byref(ms), C.byref(loss)))
+        return ms.value, loss.value

@@ -3,6 +3,12 @@
 // the golden fixtures under tests/golden/, and serves as the timed CPU reference in the benchmark.
 // Everything here goes through the reference's public API: Tensor, transpose_view/view, matmul,
 // Linear, FeedForward, ScaledDot, MultiHeadAttention, GPT, crossEntropyLoss, backward().
+//
+// The file is compiled twice (see Makefile): without USE_CUDA into _ref/libref_cpu.so, and with USE_CUDA, against
+// the reference tree with the TENSOR_GEMM_BACKEND=b200 binding applied, into _ref_cuda/libref_cuda.so.  In the CUDA
+// build ref_use_cuda(1) makes every entry point place its tensors and modules on the GPU, so that the same calls
+// run the reference's CUDA path with whichever GEMM backend the environment selects (cuBLAS, custom, b200).
+#include <chrono>
 #include <cstdint>
 #include <cstring>
 #include <random>
@@ -25,6 +31,29 @@
 namespace {
 
 thread_local std::string g_err;
+bool g_cuda = false;   // place tensors and modules on the GPU (CUDA build only)
+
+Tensor on_device(const Tensor& t) {
+#ifdef USE_CUDA
+    if (g_cuda) return t.toDevice(Device::CUDA);
+#endif
+    return t;
+}
+
+// Overwrites a module's parameters (on the host, where the constructors create them) and then moves the module.
+template <typename M>
+std::vector<Tensor> load_params(M& m, const std::vector<const float*>& values) {
+    auto p = m.parameters();
+    for (size_t i = 0; i < p.size() && i < values.size(); ++i)
+        std::memcpy(p[i].data(), values[i], p[i].numel() * sizeof(float));
+#ifdef USE_CUDA
+    if (g_cuda) {
+        m.to_cuda();
+        p = m.parameters();
+    }
+#endif
+    return p;
+}
 
 // An operand recipe: contiguous base tensor -> optional view(new shape) -> optional transpose_view(t1, t2)
 // -> optional second transpose_view(t3, t4).
@@ -40,7 +69,13 @@ struct RefView {
 Tensor from_host(const float* data, const std::vector<int64_t>& shape) {
     Tensor t(shape, DType::Float32, Device::CPU);
     std::memcpy(t.data(), data, t.numel() * sizeof(float));
-    return t;
+    return on_device(t);
+}
+
+Tensor tokens_from_host(const int64_t* data, const std::vector<int64_t>& shape) {
+    Tensor t(shape, DType::Int64, Device::CPU);
+    std::memcpy(t.data(), data, t.numel() * sizeof(int64_t));
+    return on_device(t);
 }
 
 Tensor build(const float* data, const RefView& v) {
@@ -52,7 +87,7 @@ Tensor build(const float* data, const RefView& v) {
 }
 
 void copy_out(const Tensor& t, float* dst) {
-    Tensor c = t.contiguous();
+    Tensor c = t.contiguous().toDevice(Device::CPU);
     std::memcpy(dst, c.data(), c.numel() * sizeof(float));
 }
 
@@ -84,6 +119,17 @@ int guarded(F&& f) {
 }  // namespace
 
 REF_API const char* ref_last_error() { return g_err.c_str(); }
+
+// 1: run on the GPU from now on (fails in the build without USE_CUDA); 0: on the host.
+REF_API int ref_use_cuda(int on) {
+#ifdef USE_CUDA
+    g_cuda = on != 0;
+    return 0;
+#else
+    if (on) { g_err = "this build of the reference has no CUDA path"; return 1; }
+    return 0;
+#endif
+}
 
 // Tensor::matmul on the reference CPU path.  out may be NULL to query the shape / the thrown message only.
 REF_API int ref_matmul(const float* a, const RefView* va, const float* b, const RefView* vb, float* out,
@@ -127,9 +173,7 @@ REF_API int ref_linear(const float* x, const int64_t* x_shape, int32_t x_ndim, c
                        float* dx, float* dw, float* db) {
     return guarded([&] {
         Linear lin(in_f, out_f, DType::Float32);
-        auto params = lin.parameters();
-        std::memcpy(params[0].data(), w, sizeof(float) * in_f * out_f);
-        std::memcpy(params[1].data(), bias, sizeof(float) * out_f);
+        auto params = load_params(lin, {w, bias});
         Tensor X = from_host(x, std::vector<int64_t>(x_shape, x_shape + x_ndim));
         X.setRequiresGrad(true);
         Tensor pre = lin.forward(X);
@@ -151,11 +195,7 @@ REF_API int ref_ffn(const float* x, const int64_t* x_shape, int32_t x_ndim, int6
                     float* dx, float* dw1, float* db1, float* dw2, float* db2) {
     return guarded([&] {
         FeedForward ffn(embed, ff, DType::Float32);
-        auto p = ffn.parameters();
-        std::memcpy(p[0].data(), w1, sizeof(float) * embed * ff);
-        std::memcpy(p[1].data(), b1, sizeof(float) * ff);
-        std::memcpy(p[2].data(), w2, sizeof(float) * embed * ff);
-        std::memcpy(p[3].data(), b2, sizeof(float) * embed);
+        auto p = load_params(ffn, {w1, b1, w2, b2});
         Tensor X = from_host(x, std::vector<int64_t>(x_shape, x_shape + x_ndim));
         X.setRequiresGrad(true);
         Tensor Y = ffn.forward(X);
@@ -198,9 +238,7 @@ REF_API int ref_layernorm(const float* x, int64_t rows, int64_t D, const float* 
                           const float* dy, float* y, float* dx, float* dgamma, float* dbeta) {
     return guarded([&] {
         LayerNorm ln(D, DType::Float32, eps);
-        auto p = ln.parameters();
-        std::memcpy(p[0].data(), gamma, sizeof(float) * D);
-        std::memcpy(p[1].data(), beta, sizeof(float) * D);
+        auto p = load_params(ln, {gamma, beta});
         Tensor X = from_host(x, {rows, D});
         X.setRequiresGrad(true);
         Tensor Y = ln.forward(X);
@@ -220,11 +258,10 @@ REF_API int ref_cross_entropy(const float* logits, const int64_t* targets, int64
     return guarded([&] {
         Tensor L = from_host(logits, {B, T, V});
         L.setRequiresGrad(true);
-        Tensor tg({B, T}, DType::Int64, Device::CPU);
-        std::memcpy(tg.data(), targets, sizeof(int64_t) * B * T);
+        Tensor tg = tokens_from_host(targets, {B, T});
         crossEntropyLoss ce;
         Tensor l = ce.forward_batched(L, tg);
-        if (loss) *loss = l.at<float>(0);
+        if (loss) copy_out(l, loss);
         if (dlogits) {
             l.backward();
             copy_grad(L, dlogits);
@@ -237,10 +274,8 @@ REF_API int ref_embedding(const float* table, int64_t vocab, int64_t D, const in
                           const float* dout, float* out, float* dtable) {
     return guarded([&] {
         Embedding emb(vocab, D, DType::Float32);
-        auto p = emb.parameters();
-        std::memcpy(p[0].data(), table, sizeof(float) * vocab * D);
-        Tensor tk({B, T}, DType::Int64, Device::CPU);
-        std::memcpy(tk.data(), tokens, sizeof(int64_t) * B * T);
+        auto p = load_params(emb, {table});
+        Tensor tk = tokens_from_host(tokens, {B, T});
         Tensor Y = emb.forward(tk);
         if (out) copy_out(Y, out);
         if (dout) {
@@ -255,8 +290,7 @@ REF_API int ref_mha(const float* x, int64_t B, int64_t T, int64_t E, int64_t H, 
                     const float* dy, float* y, float* dx, float* const* dparams) {
     return guarded([&] {
         MultiHeadAttention mha(E, H, DType::Float32);
-        auto p = mha.parameters();
-        for (size_t i = 0; i < p.size(); ++i) std::memcpy(p[i].data(), params[i], p[i].numel() * sizeof(float));
+        auto p = load_params(mha, std::vector<const float*>(params, params + 8));
         Tensor X = from_host(x, {B, T, E});
         X.setRequiresGrad(true);
         Tensor Y = mha.forward(X);
@@ -286,21 +320,20 @@ REF_API int ref_gpt_step(int64_t vocab, int64_t max_seq, int64_t E, int64_t H, i
                          float* loss_out, float* logits_out, float* flat_grads) {
     return guarded([&] {
         GPT model(vocab, max_seq, E, H, L, ff, DType::Float32, 0.0f);
-        auto p = model.parameters();
+        std::vector<const float*> values;
         size_t off = 0;
-        for (auto& t : p) {
-            std::memcpy(t.data(), flat_params + off, t.numel() * sizeof(float));
+        for (auto& t : model.parameters()) {
+            values.push_back(flat_params + off);
             off += t.numel();
         }
-        Tensor tok({batch, seq}, DType::Int64, Device::CPU), tgt({batch, seq}, DType::Int64, Device::CPU);
-        std::memcpy(tok.data(), tokens, sizeof(int64_t) * batch * seq);
-        std::memcpy(tgt.data(), targets, sizeof(int64_t) * batch * seq);
+        auto p = load_params(model, values);
+        Tensor tok = tokens_from_host(tokens, {batch, seq}), tgt = tokens_from_host(targets, {batch, seq});
         model.zero_grad();
         Tensor logits = model.forward(tok);
         if (logits_out) copy_out(logits, logits_out);
         crossEntropyLoss ce;
         Tensor loss = ce.forward_batched(logits, tgt);
-        *loss_out = static_cast<float*>(loss.data())[0];
+        copy_out(loss, loss_out);
         if (flat_grads) {
             loss.backward();
             off = 0;
@@ -311,3 +344,181 @@ REF_API int ref_gpt_step(int64_t vocab, int64_t max_seq, int64_t E, int64_t H, i
         }
     });
 }
+
+#ifdef USE_CUDA
+// ------------------------------------------------------------------------------------------------------------------
+// CUDA build only (_ref_cuda/libref_cuda.so).  Timing of the reference's own Tensor::matmul / GPT step on the GPU under
+// the backend the environment selects, and the same module-level calls as above routed through the fused adapter
+// (include/torchengine/te_b200_modules.h) so that its GradFn nodes run inside the reference's autograd engine.
+#include <cuda_runtime.h>
+#include "core/cuda_utils.h"
+#include "torchengine/te_b200_modules.h"
+
+// cuBLAS math mode of the reference's process-wide handle: 0 = default FP32 (what the reference runs),
+// 1 = TF32 tensor-op math (a comparator the reference never enables).
+REF_API int ref_cuda_cublas_tf32(int on) {
+    return guarded([&] {
+        cublas_check_error(cublasSetMathMode(cuda_cublas_handle(), on ? CUBLAS_TF32_TENSOR_OP_MATH : CUBLAS_DEFAULT_MATH),
+                           "cublasSetMathMode");
+    });
+}
+
+// C = A.B for row-major [M,K].[K,N] through Tensor::matmul on the GPU with the reference benchmark's inputs
+// (std::mt19937(42), uniform(-1,1), A filled first; src/benchmarks/matmul_benchmark.cpp:107-110).  Times `iters`
+// calls with CUDA events after `warmup` calls; results are kept alive until after the timing because the reference
+// frees each result with cudaFree, which synchronises the device.  out (optional, host) receives the last product.
+REF_API int ref_cuda_time_matmul(int64_t M, int64_t K, int64_t N, int32_t warmup, int32_t iters, double* ms_per_call, float* out) {
+    return guarded([&] {
+        std::mt19937 gen(42);
+        std::uniform_real_distribution<float> dist(-1.0f, 1.0f);
+        std::vector<float> ha((size_t)M * K), hb((size_t)K * N);
+        for (auto& v : ha) v = dist(gen);
+        for (auto& v : hb) v = dist(gen);
+        Tensor A = from_host(ha.data(), {M, K}).toDevice(Device::CUDA);
+        Tensor B = from_host(hb.data(), {K, N}).toDevice(Device::CUDA);
+        for (int i = 0; i < warmup; ++i) Tensor C = A.matmul(B);
+        cuda_check_error(cudaDeviceSynchronize(), "sync");
+        cudaEvent_t e0, e1;
+        cudaEventCreate(&e0);
+        cudaEventCreate(&e1);
+        {
+            std::vector<Tensor> keep;
+            keep.reserve(iters);
+            cudaEventRecord(e0, 0);
+            for (int i = 0; i < iters; ++i) keep.push_back(A.matmul(B));
+            cudaEventRecord(e1, 0);
+            cuda_check_error(cudaEventSynchronize(e1), "event sync");
+            float ms = 0.0f;
+            cudaEventElapsedTime(&ms, e0, e1);
+            if (ms_per_call) *ms_per_call = (double)ms / (iters > 0 ? iters : 1);
+            if (out && !keep.empty()) copy_out(keep.back(), out);
+        }
+        cudaEventDestroy(e0);
+        cudaEventDestroy(e1);
+    });
+}
+
+// The reference's GPT forward + loss + backward on the GPU (src/benchmarks/gpt_benchmark_gpu.cpp:230-236 without the
+// optimizer), `steps` times after `warmup`, wall clock around device synchronisation.
+REF_API int ref_cuda_gpt_bench(int64_t vocab, int64_t max_seq, int64_t E, int64_t H, int64_t L, int64_t ff, int64_t batch,
+                               int64_t seq, const float* flat_params, const int64_t* tokens, const int64_t* targets,
+                               int32_t warmup, int32_t steps, double* ms_per_step, float* loss_out) {
+    return guarded([&] {
+        const bool was = g_cuda;
+        g_cuda = true;
+        GPT model(vocab, max_seq, E, H, L, ff, DType::Float32, 0.0f);
+        std::vector<const float*> values;
+        size_t off = 0;
+        for (auto& t : model.parameters()) { values.push_back(flat_params + off); off += t.numel(); }
+        load_params(model, values);
+        Tensor tok = tokens_from_host(tokens, {batch, seq}), tgt = tokens_from_host(targets, {batch, seq});
+        g_cuda = was;
+        crossEntropyLoss ce;
+        auto one = [&] {
+            model.zero_grad();
+            Tensor logits = model.forward(tok);
+            Tensor loss = ce.forward_batched(logits, tgt);
+            loss.backward();
+            return loss;
+        };
+        for (int i = 0; i < warmup; ++i) one();
+        cuda_check_error(cudaDeviceSynchronize(), "sync");
+        const auto t0 = std::chrono::steady_clock::now();
+        for (int i = 0; i < steps; ++i) {
+            Tensor loss = one();
+            if (i == steps - 1 && loss_out) copy_out(loss, loss_out);
+        }
+        cuda_check_error(cudaDeviceSynchronize(), "sync");
+        const auto t1 = std::chrono::steady_clock::now();
+        if (ms_per_step) *ms_per_step = std::chrono::duration<double, std::milli>(t1 - t0).count() / (steps > 0 ? steps : 1);
+    });
+}
+
+// --- the fused adapter inside the reference's autograd --------------------------------------------------------------
+
+REF_API int ref_fused_linear(const float* x, const int64_t* x_shape, int32_t x_ndim, const float* w, const float* bias,
+                             int64_t in_f, int64_t out_f, int32_t gelu, const float* dy, float* y, float* /*preact: not
+                             returned by the fused call*/, float* dx, float* dw, float* db) {
+    return guarded([&] {
+        const bool was = g_cuda;
+        g_cuda = true;
+        te_b200::FusedLinear lin(in_f, out_f, DType::Float32);
+        auto p = load_params(lin, {w, bias});
+        Tensor X = from_host(x, std::vector<int64_t>(x_shape, x_shape + x_ndim));
+        X.setRequiresGrad(true);
+        Tensor Y = gelu ? te_b200::linear_gelu(X, p[0], p[1]) : lin.forward(X);
+        if (y) copy_out(Y, y);
+        if (dy) {
+            backward_with(Y, dy);
+            copy_grad(X, dx); copy_grad(p[0], dw); copy_grad(p[1], db);
+        }
+        g_cuda = was;
+    });
+}
+
+REF_API int ref_fused_ffn(const float* x, const int64_t* x_shape, int32_t x_ndim, int64_t embed, int64_t ff,
+                          const float* w1, const float* b1, const float* w2, const float* b2, const float* dy, float* y,
+                          float* dx, float* dw1, float* db1, float* dw2, float* db2) {
+    return guarded([&] {
+        const bool was = g_cuda;
+        g_cuda = true;
+        te_b200::FusedFeedForward ffn(embed, ff, DType::Float32);
+        auto p = load_params(ffn, {w1, b1, w2, b2});
+        Tensor X = from_host(x, std::vector<int64_t>(x_shape, x_shape + x_ndim));
+        X.setRequiresGrad(true);
+        Tensor Y = ffn.forward(X);
+        if (y) copy_out(Y, y);
+        if (dy) {
+            backward_with(Y, dy);
+            copy_grad(X, dx);
+            copy_grad(p[0], dw1); copy_grad(p[1], db1); copy_grad(p[2], dw2); copy_grad(p[3], db2);
+        }
+        g_cuda = was;
+    });
+}
+
+REF_API int ref_fused_scaled_dot(const float* q, const RefView* vq, const float* k, const RefView* vk, const float* v,
+                                 const RefView* vv, const float* d_o, float* o, float* dq, float* dk, float* dv) {
+    return guarded([&] {
+        const bool was = g_cuda;
+        g_cuda = true;
+        Tensor Qb = from_host(q, std::vector<int64_t>(vq->shape, vq->shape + vq->ndim));
+        Tensor Kb = from_host(k, std::vector<int64_t>(vk->shape, vk->shape + vk->ndim));
+        Tensor Vb = from_host(v, std::vector<int64_t>(vv->shape, vv->shape + vv->ndim));
+        Qb.setRequiresGrad(true); Kb.setRequiresGrad(true); Vb.setRequiresGrad(true);
+        auto apply = [](Tensor t, const RefView& r) {
+            if (r.view_ndim > 0) t = t.view(std::vector<int64_t>(r.view_shape, r.view_shape + r.view_ndim));
+            if (r.t1 >= 0) t = t.transpose_view((size_t)r.t1, (size_t)r.t2);
+            if (r.t3 >= 0) t = t.transpose_view((size_t)r.t3, (size_t)r.t4);
+            return t;
+        };
+        Tensor O = te_b200::scaled_dot(apply(Qb, *vq), apply(Kb, *vk), apply(Vb, *vv));
+        if (o) copy_out(O, o);
+        if (d_o) {
+            backward_with(O, d_o);
+            copy_grad(Qb, dq); copy_grad(Kb, dk); copy_grad(Vb, dv);
+        }
+        g_cuda = was;
+    });
+}
+
+REF_API int ref_fused_mha(const float* x, int64_t B, int64_t T, int64_t E, int64_t H, const float* const* params,
+                          const float* dy, float* y, float* dx, float* const* dparams) {
+    return guarded([&] {
+        const bool was = g_cuda;
+        g_cuda = true;
+        te_b200::FusedMultiHeadAttention mha(E, H, DType::Float32);
+        auto p = load_params(mha, std::vector<const float*>(params, params + 8));
+        Tensor X = from_host(x, {B, T, E});
+        X.setRequiresGrad(true);
+        Tensor Y = mha.forward(X);
+        if (y) copy_out(Y, y);
+        if (dy) {
+            backward_with(Y, dy);
+            copy_grad(X, dx);
+            if (dparams) for (size_t i = 0; i < p.size(); ++i) copy_grad(p[i], dparams[i]);
+        }
+        g_cuda = was;
+    });
+}
+#endif  // USE_CUDA

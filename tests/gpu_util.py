@@ -17,3 +17,15 @@ def assert_close(c, ref, precision, what=""):
     e = rel_err(c, ref)
     assert e <= TOL_REL[precision], f"{what}: relative error {e:.3e} > {TOL_REL[precision]:.0e} ({precision})"
     return e
+
+
+def elementwise_rel_err(c, ref, floor=1e-2):
+    """max |C - Cref| / |Cref| over the entries with |Cref| >= floor * rms(Cref): the stricter of the two readings of
+    "relative error" for products of uniform(-1,1) operands, whose entries come arbitrarily close to zero."""
+    ref = np.asarray(ref, dtype=np.float64)
+    c = np.asarray(c, dtype=np.float64)
+    rms = float(np.sqrt(np.mean(ref * ref)))
+    mask = np.abs(ref) >= floor * rms
+    if not mask.any():
+        return 0.0
+    return float((np.abs(c - ref)[mask] / np.abs(ref)[mask]).max())
