@@ -52,7 +52,7 @@ typedef struct te_b200_ctx te_b200_ctx;   /* one per device; owns the workspace 
 typedef void* te_stream_t;                /* a cudaStream_t; NULL = legacy default */
 
 /*
- * One (optionally strided-batched) GEMM:  C[b] = epi( scale( A[b] . B[b] ) ).
+ * One (optionally strided-batched) GEMM:  C[b] = epi( scale( A[b] . B[b] ) ) [+ R[b]].
  * A[b] is M x K, B[b] is K x N, C[b] is M x N row-major with leading dim ldc.
  * Replaces the argument lists of cublasSgemm / cublasSgemmStridedBatched as the
  * reference issues them (src/tensor/tensor.h:690-698, :756-765) and of
@@ -80,6 +80,11 @@ typedef struct te_gemm_desc {
     const float* bias;         /* device or NULL */
     float*  preact_out;        /* optional: value before GELU (what GeluBackward needs,
                                   src/core/grad_fn.cpp:169); same layout as c; NULL to skip */
+    const float* residual;     /* optional, same layout as c (ldc and the c batch strides), added last:
+                                  c = act(scale(A.B) + bias) + residual.  The `x + sublayer(x)` adds of
+                                  src/nn/transformer_block.cpp:15-35, and, with residual == c, the gradient
+                                  accumulation `*grad = *grad + g` of src/tensor/tensor.cpp:1138-1142.
+                                  May alias c (each element is read before it is written); NULL to skip */
     int32_t precision;         /* TE_PREC_* */
     int32_t reserved;
 } te_gemm_desc;
@@ -111,6 +116,17 @@ TE_API const char* te_b200_status_string(int status);
  * launched through ctx gave up a bounded wait since the last call, else TE_OK. */
 TE_API int te_b200_check_device_status(te_b200_ctx* ctx);
 
+/* Every wait inside a kernel of this library (on an mbarrier that a copy, the tensor core or another warp
+ * completes) is bounded: when it runs out the kernel records where, winds down and returns, and
+ * te_b200_check_device_status reports TE_ERR_DEVICE_TIMEOUT.  This sets the bound for kernels launched through ctx
+ * afterwards (0 = the default of two seconds).  Synchronises `stream`.  No reference counterpart: the reference's
+ * kernels contain no waits (src/cuda/elementwise_cuda.cu). */
+TE_API int te_b200_set_wait_limit_ns(te_b200_ctx* ctx, uint64_t limit_ns, te_stream_t stream);
+/* Launches a one-warp kernel that waits, with that bound, on a barrier nothing arrives at: after synchronising,
+ * te_b200_check_device_status returns TE_ERR_DEVICE_TIMEOUT ("... site code 901") and the context works as before.
+ * The kernel returns by itself; nothing traps, faults or hangs.  Proves the failure path of the waits end to end. */
+TE_API int te_b200_selftest_wait_timeout(te_b200_ctx* ctx, te_stream_t stream);
+
 /* ---- GEMM ------------------------------------------------------------------ */
 
 /* Asynchronous on `stream`.  Replaces the body of Tensor::cuda_matmul_impl_f32
@@ -133,17 +149,22 @@ TE_API int te_b200_matmul_nd(te_b200_ctx* ctx,
  * launchers allocate freely, src/cuda/elementwise_cuda.cu:2302-2346).  Some hosts cannot call cudaMalloc, or let
  * a library call it for them: a plugin inside a framework whose allocator owns the device, a loop with a
  * fixed memory budget, code that has already started capturing its streams.  For them this entry point
- * needs no te_b200_ctx and allocates nothing: the tf32 hi/lo planes go into one fixed device array of
- * TE_B200_STATIC_SCRATCH_BYTES that every GPU loading this library holds until the process exits.
+ * needs no te_b200_ctx and calls no allocator: the tf32 hi/lo planes go into one fixed device array of
+ * TE_B200_STATIC_SCRATCH_BYTES inside the library image.  The CUDA runtime reserves that array on a GPU when it
+ * loads this part of the library there, which (with the default lazy loading) is during the first call on that
+ * device; from then on the GPU holds it until the process exits.
  *   - d->precision must be TE_PREC_3XTF32; the device that is current when called is used.
  *   - A problem whose planes need more than TE_B200_STATIC_SCRATCH_BYTES (see te_b200_gemm_workspace_size)
  *     is refused with TE_ERR_WORKSPACE; nothing is launched.
- *   - The first call on a device also resolves the array's address and the kernel attributes: make it
- *     before any stream capture begins.
+ *   - The first successful call on a device does all one-time work (the load above, the array's address, and the
+ *     attributes of every kernel any problem shape can reach): make it before any stream capture begins and while
+ *     the device still has the array's size free.  If it fails, the next call tries again.
  *   - Calls share the array, which keeps the previous call's contents; each call rewrites what it reads
  *     (planes, status word), but calls that overlap on the GPU race.  Serialise them on one stream.
  *   - host_status (optional) receives, asynchronously on `stream`, 0 or the code of a device-side wait
- *     that gave up; read it after synchronising the stream. */
+ *     that gave up; read it after synchronising the stream.  It is the target of a device-to-host copy: use pinned
+ *     memory, and it must be pinned (or NULL) if the stream is being captured.  An empty problem (M or N zero)
+ *     launches nothing and stores 0 at once. */
 #define TE_B200_STATIC_SCRATCH_BYTES (64ll << 20)
 TE_API int te_b200_gemm_3xtf32_static(const te_gemm_desc* d, te_stream_t stream, int* host_status);
 
@@ -197,6 +218,17 @@ TE_API int te_b200_linear_backward_gelu(te_b200_ctx* ctx, const float* x, const 
                                  int64_t rows, int64_t in_features, int64_t out_features,
                                  int precision, te_stream_t stream);
 
+/* The general form of the two calls above.  dx_residual (optional, [rows,in]) is added into dx: the gradient that
+ * reaches the Linear's input over a parallel branch (the `x + sublayer(x)` of src/nn/transformer_block.cpp:15-35);
+ * it may be dx itself, which chains the input gradients of several Linears reading the same x.  accumulate != 0
+ * adds dW and db to the buffers' contents instead of overwriting them -- the `*grad = *grad + g` of the autograd
+ * engine (src/tensor/tensor.cpp:1138-1142) folded into the producing kernels.  x_preact as in _gelu (it excludes
+ * dx_residual). */
+TE_API int te_b200_linear_backward_ex(te_b200_ctx* ctx, const float* x, const float* x_preact, const float* w,
+                               const float* dy, float* dx, const float* dx_residual, float* dw, float* db,
+                               int accumulate, int64_t rows, int64_t in_features, int64_t out_features,
+                               int precision, te_stream_t stream);
+
 /* O = softmax(Q.K^T / sqrt(d)) . V for Q,K,V viewed as [B,H,T,d] with explicit element
  * strides (last-dim stride must be 1).  ScaledDot::forward (src/nn/scaledot.cpp:8-27).
  * p_out is a dense [B,H,T,T] buffer that receives the probabilities (SoftmaxBackward and
@@ -245,6 +277,45 @@ typedef struct te_attn_bwd_desc {
 } te_attn_bwd_desc;
 TE_API int te_b200_attention_backward(te_b200_ctx* ctx, const te_attn_bwd_desc* d, te_stream_t stream);
 
+/* MultiHeadAttention::forward (src/nn/multi_head_attention.cpp:19-42) as one call: the three input projections
+ * (bias in the GEMM epilogue), scaled-dot attention on the head views [B,H,T,E/H] of the [B,T,E] projections
+ * (strides [T*E, E/H, E]: no copy), the head outputs written straight back in merged [B,T,E] order, and the output
+ * projection, optionally with the block's residual input added (src/nn/transformer_block.cpp:20-24).
+ * Weights are [E,E] as Linear stores them ([out,in], src/nn/linear.cpp:7); biases [E] or NULL.  q, k, v, p, attn are
+ * caller-owned buffers the backward call needs again. */
+typedef struct te_mha_desc {
+    int64_t B, T, E, H;
+    const float* x;                                  /* [B,T,E] */
+    const float *wq, *bq, *wk, *bk, *wv, *bv, *wo, *bo;
+    float *q, *k, *v;                                /* [B,T,E] each: the projections */
+    float* p;                                        /* [B,H,T,T] attention probabilities */
+    float* attn;                                     /* [B,T,E] merged head outputs (input of the out projection) */
+    float* y;                                        /* [B,T,E] result */
+    const float* residual;                           /* optional [B,T,E], added to y */
+    int32_t precision;
+    int32_t reserved;
+} te_mha_desc;
+TE_API int te_b200_mha_forward(te_b200_ctx* ctx, const te_mha_desc* d, te_stream_t stream);
+
+/* Backward of the call above: the graph MatMulBackward/AddBackward of four Linears, TransposeBackward and
+ * ReshapeBackward of the head split and merge, and the attention core (src/core/grad_fn.cpp:93-156, :397-403,
+ * :559-665).  dq, dk, dv, dattn are caller-owned [B,T,E] scratch.  dx = dx_residual + dq.Wq + dk.Wk + dv.Wv.
+ * Parameter gradients are [E,E] / [E] like the parameters; NULL skips one; accumulate != 0 adds to their contents. */
+typedef struct te_mha_bwd_desc {
+    int64_t B, T, E, H;
+    const float* x;
+    const float *wq, *wk, *wv, *wo;
+    const float *q, *k, *v, *p, *attn;               /* as the forward call left them */
+    const float* dy;                                 /* [B,T,E] */
+    float* dx;                                       /* [B,T,E] */
+    const float* dx_residual;                        /* optional [B,T,E] */
+    float *dwq, *dbq, *dwk, *dbk, *dwv, *dbv, *dwo, *dbo;
+    float *dq, *dk, *dv, *dattn;                     /* scratch */
+    int32_t accumulate;
+    int32_t precision;
+} te_mha_bwd_desc;
+TE_API int te_b200_mha_backward(te_b200_ctx* ctx, const te_mha_bwd_desc* d, te_stream_t stream);
+
 /* ---- the GPT step's kernels around the matmuls ------------------------------- */
 /* Not matmuls, but what a training step of the reference's GPT runs between them; with the
  * GEMMs and attention on this backend they were what bounded the step.  All reductions run in
@@ -262,6 +333,12 @@ TE_API int te_b200_layernorm_forward(te_b200_ctx* ctx, const float* x, const flo
 TE_API int te_b200_layernorm_backward(te_b200_ctx* ctx, const float* x, const float* gamma,
                                const float* dy, float* dx, float* dgamma, float* dbeta,
                                int64_t rows, int64_t cols, float eps, te_stream_t stream);
+/* The same with dx_residual ([rows, cols], optional) added into dx: in a pre-LN block the gradient of the block's
+ * input is the LayerNorm's dx plus the gradient that bypasses it over the residual branch
+ * (src/nn/transformer_block.cpp:15-35; AddBackward, src/core/grad_fn.cpp:93-102).  May be dx itself. */
+TE_API int te_b200_layernorm_backward_ex(te_b200_ctx* ctx, const float* x, const float* gamma,
+                                  const float* dy, float* dx, const float* dx_residual, float* dgamma,
+                                  float* dbeta, int64_t rows, int64_t cols, float eps, te_stream_t stream);
 /* out[i][:] = table[tokens[i]][:] (+ pos[i % seq_len][:] when pos is not NULL) for n int64
  * tokens: Embedding::forward (src/nn/embedding.cpp:18-60) with the positional sum of
  * GPT::forward (src/nn/gpt.cpp:30-69) folded in.  An index outside [0, vocab) writes zeros and
@@ -302,6 +379,35 @@ TE_API int te_b200_gemm_plan(const te_gemm_desc* d, int sm_count, size_t scratch
  * the reference has no multi-device code (README.md:47). */
 TE_API int te_b200_shard_range(int64_t total, int world, int rank, int64_t align,
                         int64_t* out_begin, int64_t* out_count);
+
+/* ---- multi-GPU driver (one process per GPU, NCCL over NVLink) -------------------- */
+/* None of this has a counterpart in the reference (no multi-device code, README.md:47).  Computing a shard needs no
+ * exchange; these calls move data AROUND the products.  NCCL is bound at run time (libnccl.so.2). */
+typedef struct te_b200_comm te_b200_comm;
+
+/* 128 bytes identifying a new communicator: rank 0 creates them, the caller hands them to every rank (a file, a
+ * socket, torch.distributed's store ...). */
+#define TE_B200_COMM_ID_BYTES 128
+TE_API int te_b200_comm_unique_id(void* out_id);
+/* Joins rank `rank` of `world` (collective: every rank calls it); ctx's device must be current. */
+TE_API int te_b200_comm_init(te_b200_ctx* ctx, const void* id, int world, int rank, te_b200_comm** out_comm);
+TE_API int te_b200_comm_destroy(te_b200_comm* comm);
+TE_API int te_b200_comm_rank(const te_b200_comm* comm, int* world, int* rank);
+
+/* Reassembles C [M,N] (row-major, pitch ld_full) on every rank from the ranks' column blocks as
+ * te_b200_shard_range(N, world, r, align) assigns them.  c_local is this rank's dense [M, n_local] block; staging
+ * holds M*N floats.  One all-gather of the blocks as they are, then one re-tile kernel.  Asynchronous on `stream`. */
+TE_API int te_b200_all_gather_columns(te_b200_comm* comm, const float* c_local, int64_t M, int64_t N, int64_t align,
+                               float* staging, float* c_full, int64_t ld_full, te_stream_t stream);
+/* The same for row blocks of a dense [rows, cols] matrix, in place: this rank's rows
+ * (te_b200_shard_range(rows, world, rank, align)) are already at their position inside `full`. */
+TE_API int te_b200_all_gather_rows(te_b200_comm* comm, float* full, int64_t rows, int64_t cols, int64_t align,
+                            te_stream_t stream);
+/* te_b200_gemm_f32_host for `world` ranks that all hold the same HOST operands (row-major A [M,K] and B [K,N]): each
+ * rank copies 1/world of A's rows and its column block of B (te_b200_shard_range(N, world, rank, column_align)) to
+ * its GPU, the ranks replicate A over NVLink, each multiplies and copies its columns of C back into its host C.
+ * Per GPU, PCIe carries 1/world of the bytes.  Collective; synchronises before returning. */
+TE_API int te_b200_gemm_f32_host_sharded(te_b200_comm* comm, const te_gemm_desc* d_host, int64_t column_align);
 
 #ifdef __cplusplus
 }

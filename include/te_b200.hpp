@@ -351,6 +351,76 @@ public:
     }
 };
 
+// MultiHeadAttention (reference src/nn/multi_head_attention.cpp:19-42) as the two fused calls te_b200_mha_forward /
+// te_b200_mha_backward: four Linears, the head split and merge as strides, attention on the head views.
+class MultiHeadAttention {
+public:
+    MultiHeadAttention(int64_t embed_dim, int64_t num_heads)
+        : embed_(embed_dim), heads_(num_heads), q_(embed_dim, embed_dim), k_(embed_dim, embed_dim), v_(embed_dim, embed_dim),
+          out_(embed_dim, embed_dim) {
+        if (num_heads < 1 || embed_dim % num_heads != 0) throw std::runtime_error("embedDim must be divisible by numHeads");
+    }
+    // in MultiHeadAttention::parameters() order: q, k, v, out projections
+    Linear& q_proj() { return q_; }
+    Linear& k_proj() { return k_; }
+    Linear& v_proj() { return v_; }
+    Linear& out_proj() { return out_; }
+
+    // What forward() keeps for backward(): the projections, the probabilities and the merged head outputs.
+    struct Saved { Tensor x, q, k, v, p, attn; };
+
+    // x: [B, T, E] contiguous.  residual (optional, [B, T, E]) is added to the result: x + MHA(...) of a transformer block.
+    Tensor forward(const Tensor& x, Saved* saved = nullptr, const Tensor* residual = nullptr) {
+        if (x.shape().size() != 3 || x.shape()[2] != embed_) throw std::runtime_error("Inner dimensions must match for matmul");
+        if (!x.is_contiguous()) throw std::runtime_error("MultiHeadAttention::forward expects a contiguous input");
+        const int64_t B = x.shape()[0], T = x.shape()[1];
+        Saved s{x, Tensor(x.shape()), Tensor(x.shape()), Tensor(x.shape()), Tensor({B, heads_, T, T}), Tensor(x.shape())};
+        Tensor y(x.shape());
+        te_mha_desc m{};
+        m.B = B; m.T = T; m.E = embed_; m.H = heads_;
+        m.x = x.data();
+        m.wq = q_.weight().data(); m.bq = q_.bias().data(); m.wk = k_.weight().data(); m.bk = k_.bias().data();
+        m.wv = v_.weight().data(); m.bv = v_.bias().data(); m.wo = out_.weight().data(); m.bo = out_.bias().data();
+        m.q = s.q.data(); m.k = s.k.data(); m.v = s.v.data(); m.p = s.p.data(); m.attn = s.attn.data();
+        m.y = y.data();
+        m.residual = residual ? residual->data() : nullptr;
+        Backend& be = Backend::instance();
+        m.precision = be.precision();
+        check(te_b200_mha_forward(be.ctx(), &m, nullptr));
+        if (saved) *saved = s;
+        return y;
+    }
+
+    // {dX, dWq, dbq, dWk, dbk, dWv, dbv, dWo, dbo}: the input gradient followed by the parameter gradients in
+    // parameters() order, as the reference's backward nodes deliver them.
+    std::vector<Tensor> backward(const Saved& s, const Tensor& dy) {
+        const int64_t B = s.x.shape()[0], T = s.x.shape()[1];
+        if (dy.shape() != s.x.shape() || !dy.is_contiguous()) throw std::runtime_error("MultiHeadAttention backward expects a contiguous [B,T,E] gradient");
+        std::vector<Tensor> g = {Tensor(s.x.shape())};
+        for (int i = 0; i < 4; ++i) {
+            g.emplace_back(std::vector<int64_t>{embed_, embed_});
+            g.emplace_back(std::vector<int64_t>{embed_});
+        }
+        Tensor dq(s.x.shape()), dk(s.x.shape()), dv(s.x.shape()), dattn(s.x.shape());
+        te_mha_bwd_desc m{};
+        m.B = B; m.T = T; m.E = embed_; m.H = heads_;
+        m.x = s.x.data();
+        m.wq = q_.weight().data(); m.wk = k_.weight().data(); m.wv = v_.weight().data(); m.wo = out_.weight().data();
+        m.q = s.q.data(); m.k = s.k.data(); m.v = s.v.data(); m.p = s.p.data(); m.attn = s.attn.data();
+        m.dy = dy.data(); m.dx = g[0].data();
+        m.dwq = g[1].data(); m.dbq = g[2].data(); m.dwk = g[3].data(); m.dbk = g[4].data();
+        m.dwv = g[5].data(); m.dbv = g[6].data(); m.dwo = g[7].data(); m.dbo = g[8].data();
+        m.dq = dq.data(); m.dk = dk.data(); m.dv = dv.data(); m.dattn = dattn.data();
+        Backend& be = Backend::instance();
+        m.precision = be.precision();
+        check(te_b200_mha_backward(be.ctx(), &m, nullptr));
+        return g;
+    }
+private:
+    int64_t embed_, heads_;
+    Linear q_, k_, v_, out_;
+};
+
 // Int64 device array for token ids and class targets (the reference keeps them in Int64 tensors).
 class IndexArray {
 public:

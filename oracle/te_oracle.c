@@ -6,7 +6,7 @@
  *
  * Parity status: PINNED.  Each function below follows the reference lines it cites, is checked
  * bit-for-bit against the reference's own CPU code compiled from its sources (ref_driver.cpp ->
- * _ref/libref_cpu.so, see pin_oracle.py) and against the known-answer vectors of the reference's
+ * _ref/libref_cpu.so, by tests/test_oracle_cpu.py) and against the known-answer vectors of the reference's
  * tests (tests/golden/reference_known_answers.json).
  *
  * Arithmetic notes that make bit-exactness possible: the reference accumulates C[i][j] in memory

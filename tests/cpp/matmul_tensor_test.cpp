@@ -122,6 +122,35 @@ int main() {
         expect_values("ScaledDot backward dQ", grads[0], zeros, 1e-6f);
         expect_values("ScaledDot backward dK", grads[1], zeros, 1e-6f);
         }
+        // MultiHeadAttention with zero query/key projections (uniform attention) and identity value/output projections:
+        // every position receives the mean of x over its sequence; with a residual input, x is added on top.
+        for (const int64_t E : {int64_t(16), int64_t(64)}) {      // head size 8: GEMM sequence; 32: the fused kernels (TF32 mode)
+            const int64_t B = 2, T = 4, H = 2;
+            te::MultiHeadAttention mha(E, H);
+            std::vector<float> zero_w(E * E, 0.0f), eye(E * E, 0.0f), zero_b(E, 0.0f);
+            for (int64_t i = 0; i < E; ++i) eye[i * E + i] = 1.0f;
+            mha.q_proj().weight() = Tensor::from_host(zero_w, {E, E});  mha.q_proj().bias() = Tensor::from_host(zero_b, {E});
+            mha.k_proj().weight() = Tensor::from_host(zero_w, {E, E});  mha.k_proj().bias() = Tensor::from_host(zero_b, {E});
+            mha.v_proj().weight() = Tensor::from_host(eye, {E, E});     mha.v_proj().bias() = Tensor::from_host(zero_b, {E});
+            mha.out_proj().weight() = Tensor::from_host(eye, {E, E});   mha.out_proj().bias() = Tensor::from_host(zero_b, {E});
+            std::vector<float> xs(B * T * E);
+            for (size_t i = 0; i < xs.size(); ++i) xs[i] = float(int(i % 11) - 5);
+            Tensor x = Tensor::from_host(xs, {B, T, E});
+            std::vector<float> want(xs.size());
+            for (int64_t b = 0; b < B; ++b) for (int64_t e = 0; e < E; ++e) {
+                float m = 0;
+                for (int64_t t = 0; t < T; ++t) m += xs[(b * T + t) * E + e];
+                for (int64_t t = 0; t < T; ++t) want[(b * T + t) * E + e] = m / T + xs[(b * T + t) * E + e];
+            }
+            te::MultiHeadAttention::Saved saved;
+            expect_values("MultiHeadAttention forward + residual", mha.forward(x, &saved, &x), want, 2e-2f);
+            // dy = 1: the out projection (identity) passes it on, every key gets T * (1/T) of it, the value projection
+            // (identity) passes that on: dx = 1; query and key paths vanish with Q = K = 0.  dbo = B*T.
+            std::vector<Tensor> g = mha.backward(saved, Tensor::from_host(std::vector<float>(xs.size(), 1.0f), {B, T, E}));
+            expect_values("MultiHeadAttention backward dx", g[0], std::vector<float>(xs.size(), 1.0f), 1e-2f);
+            expect_values("MultiHeadAttention backward dbo", g[8], std::vector<float>(E, float(B * T)), 1e-4f);
+            expect_values("MultiHeadAttention backward dbq", g[2], std::vector<float>(E, 0.0f), 1e-5f);
+        }
         // LayerNorm: a row of 1..8 normalises to (j - 4.5) / sqrt(5.25 + eps); with gain 2 and shift 1 on top
         {
             te::LayerNorm ln(8);

@@ -23,10 +23,32 @@ def test_library_exports_every_declared_symbol():
     assert declared == set(L.SIGNATURES), declared ^ set(L.SIGNATURES)
 
 
-def test_struct_sizes_match_header_layout():
-    # 64-bit fields first, then the int32 pairs: no padding surprises between C and ctypes
-    assert C.sizeof(L.GemmDesc) == 8 * 3 + 8 * 3 + 8 * 3 + 4 * 2 + 8 * 2 + 8 * 6 + 4 * 3 + 4 + 8 * 2 + 4 * 2
-    assert C.sizeof(L.AttnDesc) == 8 * 4 + 8 * 3 + 8 * 9 + 8 * 2 + 8 * 3 + 8
+def test_struct_sizes_match_header_layout(tmp_path):
+    """sizeof and the offset of the last field of every descriptor, as a C compiler lays include/te_b200.h out,
+    against the ctypes mirrors in lib.py."""
+    import subprocess
+    src = tmp_path / "sizes.c"
+    src.write_text("""
+#include <stdio.h>
+#include <stddef.h>
+#include "te_b200.h"
+int main(void) {
+    printf("%zu %zu\\n", sizeof(te_gemm_desc), offsetof(te_gemm_desc, precision));
+    printf("%zu %zu\\n", sizeof(te_attn_desc), offsetof(te_attn_desc, precision));
+    printf("%zu %zu\\n", sizeof(te_attn_bwd_desc), offsetof(te_attn_bwd_desc, precision));
+    printf("%zu %zu\\n", sizeof(te_mha_desc), offsetof(te_mha_desc, precision));
+    printf("%zu %zu\\n", sizeof(te_mha_bwd_desc), offsetof(te_mha_bwd_desc, precision));
+    return 0;
+}
+""")
+    exe = tmp_path / "sizes"
+    subprocess.run(["gcc", "-I", os.path.join(ROOT, "include"), str(src), "-o", str(exe)], check=True)
+    rows = [tuple(int(v) for v in line.split()) for line in subprocess.run([str(exe)], capture_output=True, text=True, check=True).stdout.split("\n") if line]
+    mirrors = [L.GemmDesc, L.AttnDesc, L.AttnBwdDesc, L.MhaDesc, L.MhaBwdDesc]
+    assert len(rows) == len(mirrors)
+    for (size, off), m in zip(rows, mirrors):
+        assert C.sizeof(m) == size, m.__name__
+        assert getattr(m, "precision").offset == off, m.__name__
 
 
 @pytest.mark.parametrize("a,b", [((2, 3), (3, 4)), ((2, 2, 3), (2, 3, 2)), ((1, 2, 3), (3, 3, 4)), ((2, 1, 4, 3), (5, 3, 6)),

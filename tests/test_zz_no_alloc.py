@@ -49,6 +49,40 @@ def test_static_scratch_entry_matches_context_entry(backend):
     backend.check_device_status()
 
 
+def test_static_scratch_entry_allocates_nothing_after_its_first_call():
+    """The first call on a device loads the library's device code (which reserves the scratch array) and configures
+    every kernel variant; from the second call on, the free device memory must not move, whatever the shape: a thin
+    product (split K), a 64-wide tile, a 128-wide tile, and a long-K product that takes the CTA-pair form."""
+    lib = L.load()
+    g = torch.Generator(device="cuda").manual_seed(5)
+    stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    shapes = [(64, 64, 64), (16, 4096, 256), (200, 300, 100), (512, 512, 512), (512, 5120, 512)]
+    ops = []
+    for (M, K, N) in shapes:
+        a = torch.rand(M, K, device="cuda", generator=g) * 2 - 1
+        b = torch.rand(K, N, device="cuda", generator=g) * 2 - 1
+        ops.append((a, b, torch.empty(M, N, device="cuda")))
+    status = torch.zeros(1, dtype=torch.int32).pin_memory()
+    sp = C.cast(status.data_ptr(), C.POINTER(C.c_int))
+    a, b, c = ops[0]
+    L.check(lib.te_b200_gemm_3xtf32_static(C.byref(_desc(a, b, c)), stream, sp))   # first call: one-time work
+    torch.cuda.synchronize()
+    for a, b, c in ops[1:]:
+        free_before = torch.cuda.mem_get_info()[0]     # taken per call: torch's own allocator may grow in between
+        L.check(lib.te_b200_gemm_3xtf32_static(C.byref(_desc(a, b, c)), stream, sp))
+        torch.cuda.synchronize()
+        assert int(status[0]) == 0
+        assert torch.cuda.mem_get_info()[0] == free_before
+        ref = (a.double() @ b.double()).cpu().numpy()
+        assert rel_err(c.cpu().numpy(), ref) <= TOL_REL["3xtf32"]
+    # an empty problem launches nothing and reports 0 at once
+    flag = C.c_int(-1)
+    d = _desc(ops[0][0], ops[0][1], ops[0][2])
+    d.M = 0
+    L.check(lib.te_b200_gemm_3xtf32_static(C.byref(d), stream, C.byref(flag)))
+    assert flag.value == 0
+
+
 def test_static_scratch_entry_refuses_what_does_not_fit():
     lib = L.load()
     a = torch.zeros(16, 16, device="cuda")

@@ -33,7 +33,7 @@ def env_int(name, default):
 
 
 def main():
-    out_path = sys.argv[1] if len(sys.argv) > 1 else os.path.join(ROOT, "gpurun_out", "gpt_benchmark_b200.json")
+    out_path = sys.argv[1] if len(sys.argv) > 1 else "gpt_benchmark_b200.json"   # beside the caller, like the reference's benchmark
     E, H, L = env_int("TENSOR_EMBED_DIM", 384), env_int("TENSOR_NUM_HEADS", 6), env_int("TENSOR_NUM_LAYERS", 6)
     ff = env_int("TENSOR_FF_DIM", 4 * E)
     B, T = env_int("TENSOR_BATCH_SIZE", 64), env_int("TENSOR_SEQ_LEN", 256)
@@ -108,7 +108,7 @@ def main():
                     "final_loss": float(loss), "backend_kernel_launches_per_step": launches_per_step if launches_per_step is not None else (be.launches - n0) / steps,
                     "cuda_graph": bool(use_graph)},
     }
-    os.makedirs(os.path.dirname(out_path), exist_ok=True)
+    os.makedirs(os.path.dirname(os.path.abspath(out_path)), exist_ok=True)
     with open(out_path, "w") as f:
         json.dump(result, f, indent=1)
     print(json.dumps(result["metrics"]))

@@ -94,7 +94,7 @@ def time_gpu(fn, iters, trials=7):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("out", nargs="?", default=os.path.join(ROOT, "gpurun_out", "matmul_benchmark.json"))
+    ap.add_argument("out", nargs="?", default="matmul_benchmark.json", help="output JSON (default: in the current directory)")
     ap.add_argument("--cpu", action="store_true", help="time the reference CPU matmul beside the GPU numbers")
     ap.add_argument("--quick", action="store_true", help="skip 16384^3")
     args = ap.parse_args()
@@ -240,7 +240,7 @@ def main():
     tb, tm = time_gpu(lambda: be.embedding_backward(tok, d_emb, 65), 50)
     record_stream("b200_embedding_backward", 4.0 * 16384 * 384 + 8.0 * 16384, tb, tm, "16384 tokens x 384, vocab 65")
     be.check_device_status()
-    os.makedirs(os.path.dirname(args.out), exist_ok=True)
+    os.makedirs(os.path.dirname(os.path.abspath(args.out)), exist_ok=True)
     with open(args.out, "w") as f:
         json.dump(results, f, indent=1)
     print("wrote %d results to %s" % (len(results), args.out))

@@ -149,7 +149,7 @@ static int gemm_device(te_b200_ctx* ctx, const te_gemm_desc* d, cudaStream_t st,
     g.batch_inner = d->batch_inner; g.batch_outer = d->batch_outer;
     operands_from_desc(d, g.a, g.b);
     g.c = d->c; g.ldc = d->ldc; g.c_stride_inner = d->c_stride_inner; g.c_stride_outer = d->c_stride_outer;
-    g.preact = d->preact_out; g.bias = d->bias; g.alpha = d->alpha; g.scale_mode = d->scale_mode;
+    g.preact = d->preact_out; g.bias = d->bias; g.residual = d->residual; g.alpha = d->alpha; g.scale_mode = d->scale_mode;
     g.epilogue = d->epilogue;
     Carver ws(ctx->workspace, ctx->workspace_bytes - reserve_tail);
     if (d->K > 0) {
@@ -243,8 +243,8 @@ int te_b200_init(int device, size_t workspace_bytes, te_b200_ctx** out_ctx) {
             rc = fail(TE_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
             break;
         }
-        if ((e = cudaMalloc(&ctx->d_status, 256)) != cudaSuccess) { rc = cuda_fail(e, "cudaMalloc(status)"); break; }
-        if ((e = cudaMemset(ctx->d_status, 0, 256)) != cudaSuccess) { rc = cuda_fail(e, "cudaMemset(status)"); break; }
+        if ((e = cudaMalloc(&ctx->d_status, STATUS_AREA_BYTES)) != cudaSuccess) { rc = cuda_fail(e, "cudaMalloc(status)"); break; }
+        if ((e = cudaMemset(ctx->d_status, 0, STATUS_AREA_BYTES)) != cudaSuccess) { rc = cuda_fail(e, "cudaMemset(status)"); break; }
         ctx->workspace_bytes = workspace_bytes < 4096 ? 4096 : workspace_bytes;
         if ((e = cudaMalloc(&ctx->workspace, ctx->workspace_bytes)) != cudaSuccess) { rc = cuda_fail(e, "cudaMalloc(workspace)"); break; }
     } while (0);
@@ -285,12 +285,29 @@ int te_b200_check_device_status(te_b200_ctx* ctx) {
     if (e != cudaSuccess) return cuda_fail(e, "cudaMemcpy(status)");
     if (h != 0) {
         cudaMemset(ctx->d_status, 0, sizeof(int));
-        if (h == 201) return fail(TE_ERR_BAD_ARGUMENT, "Embedding index out of range");   // src/nn/embedding.cpp:53-55
+        if (h == STATUS_BAD_EMBEDDING_INDEX) return fail(TE_ERR_BAD_ARGUMENT, "Embedding index out of range");   // src/nn/embedding.cpp:53-55
+        if (h == STATUS_BAD_TARGET_INDEX) return fail(TE_ERR_BAD_ARGUMENT, "Cross-entropy target index out of range");
         char msg[128];
         snprintf(msg, sizeof msg, "device-side bounded wait gave up (site code %d)", h);
         return fail(TE_ERR_DEVICE_TIMEOUT, msg);
     }
     return TE_OK;
+}
+
+int te_b200_set_wait_limit_ns(te_b200_ctx* ctx, uint64_t limit_ns, te_stream_t stream) {
+    if (int bad = check_ctx(ctx)) return bad;
+    ctx->wait_limit_ns = limit_ns;
+    // stream-ordered, from a field of the context (it must stay valid until the copy has run)
+    cudaError_t e = cudaMemcpyAsync(reinterpret_cast<char*>(ctx->d_status) + 8, &ctx->wait_limit_ns, sizeof(uint64_t),
+                                    cudaMemcpyHostToDevice, static_cast<cudaStream_t>(stream));
+    if (e != cudaSuccess) return cuda_fail(e, "cudaMemcpyAsync(wait limit)");
+    if ((e = cudaStreamSynchronize(static_cast<cudaStream_t>(stream))) != cudaSuccess) return cuda_fail(e, "cudaStreamSynchronize");
+    return TE_OK;
+}
+
+int te_b200_selftest_wait_timeout(te_b200_ctx* ctx, te_stream_t stream) {
+    if (int bad = check_ctx(ctx)) return bad;
+    return launch_wait_selftest(ctx, static_cast<cudaStream_t>(stream));
 }
 
 int te_b200_gemm_workspace_size(const te_gemm_desc* d, size_t* out_bytes) {
@@ -398,6 +415,7 @@ int te_b200_gemm_f32_host(te_b200_ctx* ctx, const te_gemm_desc* h) {
     if (int bad = check_ctx(ctx)) return bad;
     int rc = validate_desc(h);
     if (rc) return rc;
+    if (h->residual) return fail(TE_ERR_BAD_ARGUMENT, "the host-buffer entry takes no residual input");
     if (h->M == 0 || h->N == 0) return TE_OK;
     auto span = [&](int64_t rows, int64_t cols, int64_t ld, int64_t so, int64_t si) -> int64_t {
         // elements touched by a [rows, cols] slice with row pitch ld, over all batches
@@ -442,30 +460,50 @@ int te_b200_gemm_f32_host(te_b200_ctx* ctx, const te_gemm_desc* h) {
             ctx->host_pipe_ready = true;
         }
         cudaStream_t s_in = ctx->host_streams[0], s_mm = ctx->host_streams[1], s_out = ctx->host_streams[2];
+        // An error in the middle leaves copies in flight on the caller's buffers and on the staging area: drain the
+        // three streams before reporting it.
+        auto drained = [&](int code) {
+            cudaStreamSynchronize(s_in);
+            cudaStreamSynchronize(s_mm);
+            cudaStreamSynchronize(s_out);
+            return code;
+        };
+        // what the product itself would refuse (a workspace too small for a repacked operand) is found before any copy
+        {
+            te_gemm_desc full = *h;
+            full.a = da; full.b = db; full.c = dc; full.bias = dbias; full.preact_out = dpre;
+            const size_t ws_need = workspace_need(&full);
+            if (ws_need > ctx->workspace_bytes) {
+                char msg[160];
+                snprintf(msg, sizeof msg, "context workspace (%zu bytes) too small; this call needs %zu bytes of scratch",
+                         ctx->workspace_bytes, ws_need);
+                return fail(TE_ERR_WORKSPACE, msg);
+            }
+        }
         constexpr int MAX_BLOCKS = 16;
         int64_t rows_per = round_up((h->M + 7) / 8, 256);
         int nblk = (int)((h->M + rows_per - 1) / rows_per);
         if (nblk > MAX_BLOCKS) { rows_per = round_up((h->M + MAX_BLOCKS - 1) / MAX_BLOCKS, 256); nblk = (int)((h->M + rows_per - 1) / rows_per); }
-        if ((e = cudaMemcpyAsync(db, h->b, b_el * 4, cudaMemcpyHostToDevice, s_in)) != cudaSuccess) return cuda_fail(e, "H2D B");
-        if (bias_el && (e = cudaMemcpyAsync(dbias, h->bias, bias_el * 4, cudaMemcpyHostToDevice, s_in)) != cudaSuccess) return cuda_fail(e, "H2D bias");
+        if ((e = cudaMemcpyAsync(db, h->b, b_el * 4, cudaMemcpyHostToDevice, s_in)) != cudaSuccess) return drained(cuda_fail(e, "H2D B"));
+        if (bias_el && (e = cudaMemcpyAsync(dbias, h->bias, bias_el * 4, cudaMemcpyHostToDevice, s_in)) != cudaSuccess) return drained(cuda_fail(e, "H2D bias"));
         cudaEventRecord(ctx->host_events[32], s_in);
         cudaStreamWaitEvent(s_mm, ctx->host_events[32], 0);
         for (int i = 0; i < nblk; ++i) {
             const int64_t r0 = i * rows_per;
             const int64_t rows = (r0 + rows_per <= h->M) ? rows_per : h->M - r0;
             const int64_t a_cnt = (rows - 1) * h->lda + h->K, c_cnt = (rows - 1) * h->ldc + h->N;
-            if ((e = cudaMemcpyAsync(da + r0 * h->lda, h->a + r0 * h->lda, a_cnt * 4, cudaMemcpyHostToDevice, s_in)) != cudaSuccess) return cuda_fail(e, "H2D A block");
+            if ((e = cudaMemcpyAsync(da + r0 * h->lda, h->a + r0 * h->lda, a_cnt * 4, cudaMemcpyHostToDevice, s_in)) != cudaSuccess) return drained(cuda_fail(e, "H2D A block"));
             cudaEventRecord(ctx->host_events[i], s_in);
             cudaStreamWaitEvent(s_mm, ctx->host_events[i], 0);
             te_gemm_desc d = *h;
             d.M = rows;
             d.a = da + r0 * h->lda; d.b = db; d.c = dc + r0 * h->ldc; d.bias = dbias;
             d.preact_out = dpre ? dpre + r0 * h->ldc : nullptr;
-            if ((rc = gemm_device(ctx, &d, s_mm))) return rc;
+            if ((rc = gemm_device(ctx, &d, s_mm))) return drained(rc);
             cudaEventRecord(ctx->host_events[16 + i], s_mm);
             cudaStreamWaitEvent(s_out, ctx->host_events[16 + i], 0);
-            if ((e = cudaMemcpyAsync(h->c + r0 * h->ldc, dc + r0 * h->ldc, c_cnt * 4, cudaMemcpyDeviceToHost, s_out)) != cudaSuccess) return cuda_fail(e, "D2H C block");
-            if (dpre && (e = cudaMemcpyAsync(h->preact_out + r0 * h->ldc, dpre + r0 * h->ldc, c_cnt * 4, cudaMemcpyDeviceToHost, s_out)) != cudaSuccess) return cuda_fail(e, "D2H preact block");
+            if ((e = cudaMemcpyAsync(h->c + r0 * h->ldc, dc + r0 * h->ldc, c_cnt * 4, cudaMemcpyDeviceToHost, s_out)) != cudaSuccess) return drained(cuda_fail(e, "D2H C block"));
+            if (dpre && (e = cudaMemcpyAsync(h->preact_out + r0 * h->ldc, dpre + r0 * h->ldc, c_cnt * 4, cudaMemcpyDeviceToHost, s_out)) != cudaSuccess) return drained(cuda_fail(e, "D2H preact block"));
         }
         if ((e = cudaStreamSynchronize(s_out)) != cudaSuccess) return cuda_fail(e, "cudaStreamSynchronize");
         if ((e = cudaStreamSynchronize(s_mm)) != cudaSuccess) return cuda_fail(e, "cudaStreamSynchronize");
@@ -508,7 +546,7 @@ int te_b200_gelu_backward_f32(te_b200_ctx* ctx, const float* x, const float* dy,
 int te_b200_colsum_f32(te_b200_ctx* ctx, const float* in, int64_t rows, int64_t cols, int64_t ld, float* out, te_stream_t s) {
     if (int bad = check_ctx(ctx)) return bad;
     if (rows < 0 || cols < 0 || ld < cols || (cols && !out) || (rows && cols && !in)) return fail(TE_ERR_BAD_ARGUMENT, "colsum: bad argument");
-    return launch_colsum(ctx, in, rows, cols, ld, out, static_cast<cudaStream_t>(s));
+    return launch_colsum(ctx, in, rows, cols, ld, out, false, static_cast<cudaStream_t>(s));
 }
 
 int te_b200_linear_forward(te_b200_ctx* ctx, const float* x, const float* w, const float* bias, float* y, float* preact,
@@ -533,40 +571,130 @@ int te_b200_linear_forward(te_b200_ctx* ctx, const float* x, const float* w, con
 int te_b200_linear_backward(te_b200_ctx* ctx, const float* x, const float* w, const float* dy, float* dx, float* dw,
                             float* db, int64_t rows, int64_t in_features, int64_t out_features, int precision,
                             te_stream_t stream) {
-    return te_b200_linear_backward_gelu(ctx, x, nullptr, w, dy, dx, dw, db, rows, in_features, out_features, precision, stream);
+    return te_b200_linear_backward_ex(ctx, x, nullptr, w, dy, dx, nullptr, dw, db, 0, rows, in_features, out_features, precision, stream);
 }
 
 int te_b200_linear_backward_gelu(te_b200_ctx* ctx, const float* x, const float* x_preact, const float* w, const float* dy,
                                  float* dx, float* dw, float* db, int64_t rows, int64_t in_features, int64_t out_features,
                                  int precision, te_stream_t stream) {
+    return te_b200_linear_backward_ex(ctx, x, x_preact, w, dy, dx, nullptr, dw, db, 0, rows, in_features, out_features, precision, stream);
+}
+
+int te_b200_linear_backward_ex(te_b200_ctx* ctx, const float* x, const float* x_preact, const float* w, const float* dy,
+                               float* dx, const float* dx_residual, float* dw, float* db, int accumulate, int64_t rows,
+                               int64_t in_features, int64_t out_features, int precision, te_stream_t stream) {
     if (int bad = check_ctx(ctx)) return bad;
+    if (x_preact && dx_residual) return fail(TE_ERR_BAD_ARGUMENT, "linear backward: x_preact and dx_residual exclude each other");
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     int rc;
     te_gemm_desc d;
-    if (dx) {   // dX[rows,in] = dY[rows,out] . W[out,in]
+    if (dx) {   // dX[rows,in] = dY[rows,out] . W[out,in]  (+ the gradient arriving over a residual branch)
         memset(&d, 0, sizeof d);
         d.M = rows; d.N = in_features; d.K = out_features;
         d.a = dy; d.lda = out_features; d.a_major = TE_ROW_MAJOR;
         d.b = w; d.ldb = in_features; d.b_major = TE_ROW_MAJOR;
         d.c = dx; d.ldc = in_features;
+        d.residual = dx_residual;
         d.batch_outer = d.batch_inner = 1; d.alpha = 1.0f; d.precision = precision;
         if ((rc = gemm_device(ctx, &d, st))) return rc;
         // x = gelu(x_preact): hand back the gradient of the pre-activation (GeluBackward, in place)
         if (x_preact && (rc = launch_gelu_backward(ctx, x_preact, dx, dx, rows * in_features, st))) return rc;
     }
-    if (dw) {   // dW[out,in] = dY^T[out,rows] . X[rows,in]
+    if (dw) {   // dW[out,in] (+)= dY^T[out,rows] . X[rows,in]
         memset(&d, 0, sizeof d);
         d.M = out_features; d.N = in_features; d.K = rows;
         d.a = dy; d.lda = out_features; d.a_major = TE_COL_MAJOR;
         d.b = x; d.ldb = in_features; d.b_major = TE_ROW_MAJOR;
         d.c = dw; d.ldc = in_features;
+        d.residual = accumulate ? dw : nullptr;
         d.batch_outer = d.batch_inner = 1; d.alpha = 1.0f; d.precision = precision;
         if ((rc = gemm_device(ctx, &d, st))) return rc;
     }
     if (db) {
-        if ((rc = launch_colsum(ctx, dy, rows, out_features, out_features, db, st))) return rc;
+        if ((rc = launch_colsum(ctx, dy, rows, out_features, out_features, db, accumulate != 0, st))) return rc;
     }
     return TE_OK;
+}
+
+// ---- MultiHeadAttention ----------------------------------------------------------------------------------------
+
+static int validate_mha(int64_t B, int64_t T, int64_t E, int64_t H) {
+    if (B < 0 || T < 0 || E < 0 || H < 1) return fail(TE_ERR_BAD_ARGUMENT, "multi-head attention: bad extents");
+    if (E % H != 0) return fail(TE_ERR_BAD_ARGUMENT, "embedDim must be divisible by numHeads");   // multi_head_attention.cpp:13-15
+    return TE_OK;
+}
+
+int te_b200_mha_forward(te_b200_ctx* ctx, const te_mha_desc* m, te_stream_t stream) {
+    if (int bad = check_ctx(ctx)) return bad;
+    if (!m) return fail(TE_ERR_BAD_ARGUMENT, "multi-head attention: descriptor is NULL");
+    if (int bad = validate_mha(m->B, m->T, m->E, m->H)) return bad;
+    if (m->B == 0 || m->T == 0 || m->E == 0) return TE_OK;
+    if (!m->x || !m->wq || !m->wk || !m->wv || !m->wo || !m->q || !m->k || !m->v || !m->p || !m->attn || !m->y)
+        return fail(TE_ERR_BAD_ARGUMENT, "multi-head attention: NULL pointer");
+    const int64_t rows = m->B * m->T, E = m->E, hd = E / m->H;
+    int rc;
+    // Q, K, V = Linear(x)  (multi_head_attention.cpp:20-22), bias in the epilogue
+    if ((rc = te_b200_linear_forward(ctx, m->x, m->wq, m->bq, m->q, nullptr, rows, E, E, 0, m->precision, stream))) return rc;
+    if ((rc = te_b200_linear_forward(ctx, m->x, m->wk, m->bk, m->k, nullptr, rows, E, E, 0, m->precision, stream))) return rc;
+    if ((rc = te_b200_linear_forward(ctx, m->x, m->wv, m->bv, m->v, nullptr, rows, E, E, 0, m->precision, stream))) return rc;
+    // heads are views [B,H,T,hd] with strides [T*E, hd, E] of the [B,T,E] projections (:27-32); the attention output is
+    // written with the same strides, i.e. already merged back to [B,T,E] (:37-39 without the gather copy)
+    te_attn_desc a;
+    memset(&a, 0, sizeof a);
+    a.B = m->B; a.H = m->H; a.T = m->T; a.d = hd;
+    a.q = m->q; a.k = m->k; a.v = m->v; a.p_out = m->p; a.o = m->attn;
+    const int64_t hs[3] = {m->T * E, hd, E};
+    for (int i = 0; i < 3; ++i) a.q_strides[i] = a.k_strides[i] = a.v_strides[i] = a.o_strides[i] = hs[i];
+    a.precision = m->precision;
+    if ((rc = te_b200_attention_forward(ctx, &a, stream))) return rc;
+    // y = Linear(attn) [+ residual]  (:41)
+    te_gemm_desc d;
+    memset(&d, 0, sizeof d);
+    d.M = rows; d.N = E; d.K = E;
+    d.a = m->attn; d.lda = E; d.a_major = TE_ROW_MAJOR;
+    d.b = m->wo; d.ldb = E; d.b_major = TE_COL_MAJOR;
+    d.c = m->y; d.ldc = E;
+    d.batch_outer = d.batch_inner = 1; d.alpha = 1.0f;
+    d.bias = m->bo; d.epilogue = m->bo ? TE_EPI_BIAS : TE_EPI_NONE;
+    d.residual = m->residual;
+    d.precision = m->precision;
+    return gemm_device(ctx, &d, static_cast<cudaStream_t>(stream));
+}
+
+int te_b200_mha_backward(te_b200_ctx* ctx, const te_mha_bwd_desc* m, te_stream_t stream) {
+    if (int bad = check_ctx(ctx)) return bad;
+    if (!m) return fail(TE_ERR_BAD_ARGUMENT, "multi-head attention backward: descriptor is NULL");
+    if (int bad = validate_mha(m->B, m->T, m->E, m->H)) return bad;
+    if (m->B == 0 || m->T == 0 || m->E == 0) return TE_OK;
+    if (!m->x || !m->wq || !m->wk || !m->wv || !m->wo || !m->q || !m->k || !m->v || !m->p || !m->attn || !m->dy || !m->dx ||
+        !m->dq || !m->dk || !m->dv || !m->dattn)
+        return fail(TE_ERR_BAD_ARGUMENT, "multi-head attention backward: NULL pointer");
+    const int64_t rows = m->B * m->T, E = m->E, hd = E / m->H;
+    const int acc = m->accumulate;
+    int rc;
+    // out projection: d_attn = dY . Wo, dWo = dY^T . attn, dbo = colsum(dY)
+    if ((rc = te_b200_linear_backward_ex(ctx, m->attn, nullptr, m->wo, m->dy, m->dattn, nullptr, m->dwo, m->dbo, acc, rows, E, E,
+                                         m->precision, stream))) return rc;
+    // attention core on head views of the [B,T,E] buffers
+    te_attn_bwd_desc a;
+    memset(&a, 0, sizeof a);
+    a.B = m->B; a.H = m->H; a.T = m->T; a.d = hd;
+    a.q = m->q; a.k = m->k; a.v = m->v; a.p = m->p; a.o = m->attn; a.d_o = m->dattn;
+    a.dq = m->dq; a.dk = m->dk; a.dv = m->dv;
+    const int64_t hs[3] = {m->T * E, hd, E};
+    for (int i = 0; i < 3; ++i)
+        a.q_strides[i] = a.k_strides[i] = a.v_strides[i] = a.o_strides[i] = a.d_o_strides[i] = a.dq_strides[i] =
+            a.dk_strides[i] = a.dv_strides[i] = hs[i];
+    a.precision = m->precision;
+    if ((rc = te_b200_attention_backward(ctx, &a, stream))) return rc;
+    // the three input projections; their dX contributions are chained through the residual input:
+    // dx = dx_residual + dq.Wq + dk.Wk + dv.Wv
+    if ((rc = te_b200_linear_backward_ex(ctx, m->x, nullptr, m->wq, m->dq, m->dx, m->dx_residual, m->dwq, m->dbq, acc, rows, E, E,
+                                         m->precision, stream))) return rc;
+    if ((rc = te_b200_linear_backward_ex(ctx, m->x, nullptr, m->wk, m->dk, m->dx, m->dx, m->dwk, m->dbk, acc, rows, E, E,
+                                         m->precision, stream))) return rc;
+    return te_b200_linear_backward_ex(ctx, m->x, nullptr, m->wv, m->dv, m->dx, m->dx, m->dwv, m->dbv, acc, rows, E, E,
+                                      m->precision, stream);
 }
 
 int te_b200_attention_forward(te_b200_ctx* ctx, const te_attn_desc* t, te_stream_t stream) {
@@ -694,12 +822,18 @@ int te_b200_layernorm_forward(te_b200_ctx* ctx, const float* x, const float* gam
 
 int te_b200_layernorm_backward(te_b200_ctx* ctx, const float* x, const float* gamma, const float* dy, float* dx,
                                float* dgamma, float* dbeta, int64_t rows, int64_t cols, float eps, te_stream_t stream) {
+    return te_b200_layernorm_backward_ex(ctx, x, gamma, dy, dx, nullptr, dgamma, dbeta, rows, cols, eps, stream);
+}
+
+int te_b200_layernorm_backward_ex(te_b200_ctx* ctx, const float* x, const float* gamma, const float* dy, float* dx,
+                                  const float* dx_residual, float* dgamma, float* dbeta, int64_t rows, int64_t cols,
+                                  float eps, te_stream_t stream) {
     if (int bad = check_ctx(ctx)) return bad;
     if (rows < 0 || cols < 0) return fail(TE_ERR_BAD_ARGUMENT, "layernorm backward: negative extent");
     if (cols == 0) return TE_OK;
     if (rows > 0 && (!x || !dy || !dx)) return fail(TE_ERR_BAD_ARGUMENT, "layernorm backward: NULL pointer");
     if (!gamma) return fail(TE_ERR_BAD_ARGUMENT, "layernorm backward: NULL pointer");
-    return launch_layernorm_backward(ctx, x, gamma, dy, dx, dgamma, dbeta, rows, cols, eps, static_cast<cudaStream_t>(stream));
+    return launch_layernorm_backward(ctx, x, gamma, dy, dx, dx_residual, dgamma, dbeta, rows, cols, eps, static_cast<cudaStream_t>(stream));
 }
 
 int te_b200_embedding_forward(te_b200_ctx* ctx, const float* table, const int64_t* tokens, const float* pos, float* out,

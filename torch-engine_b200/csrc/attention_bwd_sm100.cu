@@ -467,11 +467,11 @@ int launch_attention_backward_fused(te_b200_ctx* ctx, const te_attn_bwd_desc* t,
     const int dchunks = p.d / 32;
     const int smem = 1024 + 5 * dchunks * BWD_CHUNK + 4 * BWD_CHUNK + 1024 + 128;
     if (smem > 232448) return -1;
-    static int attr_smem[16] = {};
-    if (ctx->device >= 16 || attr_smem[ctx->device] < smem) {
+    int& attr_smem = ctx->kernel_state[reinterpret_cast<const void*>(attention_bwd_tf32_kernel)];
+    if (attr_smem < smem) {
         cudaError_t e = cudaFuncSetAttribute(attention_bwd_tf32_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(attention backward)");
-        if (ctx->device < 16) attr_smem[ctx->device] = smem;
+        attr_smem = smem;
     }
     const int grid = p.total_tiles < ctx->sm_count ? p.total_tiles : ctx->sm_count;
     launch_pdl(attention_bwd_tf32_kernel, dim3(grid), dim3(CTA_THREADS), smem, stream, mv, mk, mdok, mdom, mq, mdq, mdk, mdv, mp, p);

@@ -318,10 +318,6 @@ attention_tf32_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
     }
 }
 
-typedef CUresult (*EncodeTiledFn4)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
 // [B, H, T, cols] view with unit last-dim stride -> map {cols, T, H, B}.
 bool make_bhtc_map(te_b200_ctx* ctx, CUtensorMap* out, const float* ptr, int64_t cols, int64_t T, int64_t H,
                           int64_t B, const int64_t* strides_bht, int box_cols, int box_rows, CUtensorMapSwizzle swz) {
@@ -329,14 +325,10 @@ bool make_bhtc_map(te_b200_ctx* ctx, CUtensorMap* out, const float* ptr, int64_t
     const int64_t sT = strides_bht[2], sH = strides_bht[1], sB = strides_bht[0];
     if ((T > 1 && ((sT & 3) || sT < cols)) || (H > 1 && ((sH & 3) || sH == 0)) || (B > 1 && ((sB & 3) || sB == 0))) return false;
     const cuuint64_t row_bytes = (cuuint64_t)(T > 1 ? sT : ((cols + 3) & ~int64_t(3))) * 4;
-    cuuint64_t dims[4] = {(cuuint64_t)cols, (cuuint64_t)T, (cuuint64_t)H, (cuuint64_t)B};
-    cuuint64_t strides[3] = {row_bytes, H > 1 ? (cuuint64_t)sH * 4 : row_bytes, B > 1 ? (cuuint64_t)sB * 4 : row_bytes};
-    cuuint32_t box[4] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows, 1, 1};
-    cuuint32_t estr[4] = {1, 1, 1, 1};
-    EncodeTiledFn4 fn = reinterpret_cast<EncodeTiledFn4>(ctx->encode_tiled);
-    return fn(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<float*>(ptr), dims, strides, box, estr,
-              CU_TENSOR_MAP_INTERLEAVE_NONE, swz, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+    const uint64_t dims[4] = {(uint64_t)cols, (uint64_t)T, (uint64_t)H, (uint64_t)B};
+    const uint64_t strides[3] = {row_bytes, H > 1 ? (uint64_t)sH * 4 : row_bytes, B > 1 ? (uint64_t)sB * 4 : row_bytes};
+    const uint32_t box[4] = {(uint32_t)box_cols, (uint32_t)box_rows, 1, 1};
+    return encode_tiled_cached(ctx, out, ptr, dims, strides, box, (int)swz, (int)CU_TENSOR_MAP_L2_PROMOTION_L2_256B) == 0;
 }
 
 // Returns TE_OK when the fused kernel was launched, -1 when this problem is outside its limits (the caller then
@@ -361,11 +353,11 @@ int launch_attention_fused(te_b200_ctx* ctx, const te_attn_desc* t, cudaStream_t
     const int dchunks = p.d / 32;
     const int smem = 1024 + dchunks * (128 * 128 + 2 * ATT_MAX_T * 128) + 2 * ATT_EPI_WARPS * EPI_STAGE_BYTES + 128;
     if (smem > 232448) return -1;
-    static int attr_smem[16] = {};
-    if (ctx->device >= 16 || attr_smem[ctx->device] < smem) {
+    int& attr_smem = ctx->kernel_state[reinterpret_cast<const void*>(attention_tf32_kernel)];
+    if (attr_smem < smem) {
         cudaError_t e = cudaFuncSetAttribute(attention_tf32_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(attention)");
-        if (ctx->device < 16) attr_smem[ctx->device] = smem;
+        attr_smem = smem;
     }
     p.total_tiles = (int)(t->B * t->H * p.tiles_q);
     const int grid = p.total_tiles < ctx->sm_count ? p.total_tiles : ctx->sm_count;

@@ -17,7 +17,7 @@ constexpr int A_PLANE_BYTES = BM * BK * 4;   // 16 KiB
 constexpr int SMEM_RING_BUDGET = 192 * 1024;
 constexpr int SMEM_AUX_BYTES = 512;          // mbarriers, TMEM slot, abort flag
 constexpr int GROUP_M = 16;                  // raster: tiles advance down 16 m-blocks, then one n-block over
-constexpr uint64_t WAIT_LIMIT_NS = 2000000000ull;
+constexpr uint64_t WAIT_LIMIT_NS = 2000000000ull;   // default limit of a bounded wait; a context may set another
 // Warp roles: warps 0-7 drain accumulators (warp w reads TMEM lanes 32*(w%4).., columns of half w/4),
 // warp 8 issues TMA loads, warp 9 allocates TMEM and issues MMAs.
 constexpr int EPI_WARPS = 8;
@@ -33,6 +33,11 @@ enum : int {  // where a bounded wait gave up (stored in the device status word)
     WAIT_TEARDOWN = 105
 };
 
+// Epilogue forms a GEMM kernel is compiled for.  The bare product (EPI_PLAIN) and the residual form are separate
+// instances because epilogue code that is present but not taken still costs registers and drain time on products
+// whose epilogue is not hidden behind a long main loop.
+enum : int { EPI_GENERAL = 0, EPI_PLAIN = 1, EPI_RESIDUAL = 2 };
+
 struct GemmParams {
     int M, N, K;
     int tiles_m, tiles_n;
@@ -42,6 +47,7 @@ struct GemmParams {
     float* c;
     float* preact;
     const float* bias;
+    const float* residual;   // optional, same layout as c: added last (may alias c: accumulation)
     float alpha;
     int scale_mode;
     int epilogue;
@@ -76,12 +82,16 @@ __device__ __forceinline__ bool wait_bounded(uint32_t bar, uint32_t parity, vola
                                              int* status, int code) {
     if (mbar_try_wait(bar, parity)) return true;
     const uint64_t t0 = global_timer_ns();
+    // The limit lives next to the status word (bytes 8..15 of the status area); 0 means the default.  Only this slow
+    // path reads it.
+    const uint64_t set_limit = *reinterpret_cast<const volatile unsigned long long*>(status + 2);
+    const uint64_t limit = set_limit ? set_limit : WAIT_LIMIT_NS;
     uint32_t polls = 0;
     for (;;) {
         if (mbar_try_wait(bar, parity)) return true;
         if ((++polls & 0x3F) == 0) {
             if (*abort_flag) return false;
-            if (global_timer_ns() - t0 > WAIT_LIMIT_NS) {
+            if (global_timer_ns() - t0 > limit) {
                 *abort_flag = 1;
                 atomicCAS(status, 0, code);
                 return false;
@@ -126,6 +136,7 @@ constexpr int EPI_STAGE_BYTES = 32 * 128;   // one warp's staging tile: 32 rows 
 struct EpilogueRow {
     float* c_row;      // start of this thread's output row
     float* pre_row;    // same row of the optional pre-activation output
+    const float* res_row;   // same row of the optional residual input
     bool row_ok;       // row < M
     bool vec_ok;       // 16-byte stores are legal
     // TMA-store path (used when the output can be described by a tensor map)
@@ -165,8 +176,33 @@ __device__ __forceinline__ void stage_and_store32(const float* v, int col0, cons
     }
 }
 
-// scale -> (+bias) -> [store pre-activation] -> (GELU) -> store, for 32 consecutive columns of one row.
+// This thread's 32 residual values (its row, columns col0 .. col0+31); zeros outside the matrix.
+__device__ __forceinline__ void load_residual32(float* r, int col0, const EpilogueRow& er, const GemmParams& p) {
+    if (er.row_ok && er.vec_ok && col0 + 32 <= p.N) {
+#pragma unroll
+        for (int j = 0; j < 32; j += 4) {
+            const float4 t = *reinterpret_cast<const float4*>(er.res_row + col0 + j);
+            r[j] = t.x; r[j + 1] = t.y; r[j + 2] = t.z; r[j + 3] = t.w;
+        }
+    } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) r[j] = (er.row_ok && col0 + j < p.N) ? er.res_row[col0 + j] : 0.0f;
+    }
+}
+
+// scale -> (+bias) -> [store pre-activation] -> (GELU) -> (+residual) -> store, for 32 consecutive columns of one row.
+template <bool RES = false>
 __device__ __forceinline__ void epilogue_store32(float* v, int col0, const EpilogueRow& er, const GemmParams& p, int lane) {
+    float res[RES ? 32 : 1];
+    if constexpr (RES) {
+        // issued first so that the loads are in flight during the arithmetic below (the residual may alias the
+        // output: every element is read here, by the thread that writes it later)
+        if (p.residual) load_residual32(res, col0, er, p);
+        else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) res[j] = 0.0f;
+        }
+    }
 #pragma unroll
     for (int j = 0; j < 32; ++j) {
         if (p.scale_mode == TE_SCALE_MUL) v[j] *= p.alpha;
@@ -184,6 +220,10 @@ __device__ __forceinline__ void epilogue_store32(float* v, int col0, const Epilo
         if (p.epilogue == TE_EPI_BIAS_GELU) {
 #pragma unroll
             for (int j = 0; j < 32; ++j) v[j] = gelu_tanh(v[j]);
+        }
+        if constexpr (RES) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] += res[j];
         }
         stage_and_store32(v, col0, er, er.tm_c, lane);
         return;
@@ -204,6 +244,10 @@ __device__ __forceinline__ void epilogue_store32(float* v, int col0, const Epilo
     if (p.epilogue == TE_EPI_BIAS_GELU) {
 #pragma unroll
         for (int j = 0; j < 32; ++j) v[j] = gelu_tanh(v[j]);
+    }
+    if constexpr (RES) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] += res[j];
     }
     if (full_chunk && er.vec_ok) {
 #pragma unroll

@@ -30,15 +30,17 @@
 #include <stdint.h>
 #include <stdio.h>
 #include <stdlib.h>
+#include <string.h>
 
 #include "gemm_common.cuh"
 
 namespace te {
 
 
-// PLAIN: the output is the bare product going out through TMA stores (no scale, bias, pre-activation output or GELU);
-// the general epilogue's code costs registers and drain time even when none of its branches is taken.
-template <int BN, int NPL, bool A_MN, bool B_MN, bool PLAIN = false>
+// EPI_PLAIN: the output is the bare product going out through TMA stores (no scale, bias, pre-activation output or
+// GELU); the general epilogue's code costs registers and drain time even when none of its branches is taken.
+// EPI_RESIDUAL: the general epilogue plus a residual input added last.
+template <int BN, int NPL, bool A_MN, bool B_MN, int EPI = EPI_GENERAL>
 __global__ void __launch_bounds__(CTA_THREADS, 1)
 gemm_tf32_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_a_lo,
                  const __grid_constant__ CUtensorMap tm_b, const __grid_constant__ CUtensorMap tm_b_lo,
@@ -257,10 +259,12 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
             EpilogueRow er;
             er.c_row = p.c + batch_off + (long long)row * p.ldc;
             er.pre_row = p.preact ? p.preact + batch_off + (long long)row * p.ldc : nullptr;
+            er.res_row = p.residual ? p.residual + batch_off + (long long)row * p.ldc : nullptr;
             er.row_ok = row < p.M;
             // 16-byte stores need every row start aligned: aligned batch base and ldc a multiple of 4.
             er.vec_ok = ((p.ldc & 3) == 0) && ((reinterpret_cast<uintptr_t>(p.c + batch_off) & 15) == 0) &&
-                        (!p.preact || (reinterpret_cast<uintptr_t>(p.preact + batch_off) & 15) == 0);
+                        (!p.preact || (reinterpret_cast<uintptr_t>(p.preact + batch_off) & 15) == 0) &&
+                        (!p.residual || (reinterpret_cast<uintptr_t>(p.residual + batch_off) & 15) == 0);
             er.tma_ok = p.tma_store != 0;
             er.stage = epi_stage + warp * EPI_STAGE_BYTES;
             er.tm_c = &tm_c;
@@ -307,10 +311,10 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                     for (int cc = 0; cc < NACC / 32; ++cc) {
                         const int col0 = nh + cc * 32;
                         if (col0 < p.N) {
-                            if constexpr (PLAIN) {
+                            if constexpr (EPI == EPI_PLAIN) {
                                 if (er.row0 < p.M) stage_and_store32(&acc[cc * 32], col0, er, er.tm_c, lane);
                             } else {
-                                epilogue_store32(&acc[cc * 32], col0, er, p, lane);
+                                epilogue_store32<EPI == EPI_RESIDUAL>(&acc[cc * 32], col0, er, p, lane);
                             }
                         }
                     }
@@ -333,10 +337,10 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                     float v[32];
 #pragma unroll
                     for (int j = 0; j < 32; ++j) v[j] = p.K > 0 ? __uint_as_float(r[j]) : 0.0f;
-                    if constexpr (PLAIN) {
+                    if constexpr (EPI == EPI_PLAIN) {
                         if (er.row0 < p.M) stage_and_store32(v, col0, er, er.tm_c, lane);
                     } else {
-                        epilogue_store32(v, col0, er, p, lane);
+                        epilogue_store32<EPI == EPI_RESIDUAL>(v, col0, er, p, lane);
                     }
                 }
                 // Hand the accumulator buffer back to the MMA warp.
@@ -365,6 +369,40 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
                                   CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
                                   CUtensorMapFloatOOBfill);
 
+// A training step encodes the same few hundred maps again every iteration (same pointers, shapes and strides); the
+// context keeps the last encodings in a small direct-mapped table so that a repeat costs a hash and a 128-byte copy
+// instead of a driver call.  The key holds every argument of the encoder, so a hit is exact.
+int encode_tiled_cached(te_b200_ctx* ctx, void* out_map, const void* ptr, const uint64_t dims[4], const uint64_t strides[3],
+                        const uint32_t box[4], int swizzle, int l2_promotion) {
+    uint64_t key[16] = {reinterpret_cast<uint64_t>(ptr), dims[0], dims[1], dims[2], dims[3], strides[0], strides[1], strides[2],
+                        (uint64_t)box[0] | ((uint64_t)box[1] << 32), (uint64_t)box[2] | ((uint64_t)box[3] << 32),
+                        (uint64_t)(uint32_t)swizzle | ((uint64_t)(uint32_t)l2_promotion << 32), 0, 0, 0, 0, 0};
+    uint64_t h = 0x9E3779B97F4A7C15ull;
+    for (int i = 0; i < 11; ++i) h = (h ^ key[i]) * 0xFF51AFD7ED558CCDull, h ^= h >> 29;
+    TensorMapCacheEntry& e = ctx->tmap_cache[h & 255];
+    if (e.valid && memcmp(e.key, key, sizeof key) == 0) {
+        memcpy(out_map, e.map, 128);
+        ctx->tmap_hits += 1;
+        return 0;
+    }
+    cuuint64_t d[4] = {dims[0], dims[1], dims[2], dims[3]};
+    cuuint64_t st[3] = {strides[0], strides[1], strides[2]};
+    cuuint32_t bx[4] = {box[0], box[1], box[2], box[3]};
+    cuuint32_t estr[4] = {1, 1, 1, 1};
+    CUtensorMap m;
+    EncodeTiledFn fn = reinterpret_cast<EncodeTiledFn>(ctx->encode_tiled);
+    CUresult r = fn(&m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<void*>(ptr), d, st, bx, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                    (CUtensorMapSwizzle)swizzle, (CUtensorMapL2promotion)l2_promotion, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return (int)r;
+    static_assert(sizeof(CUtensorMap) == 128, "tensor map size");
+    memcpy(out_map, &m, 128);
+    memcpy(e.key, key, sizeof key);
+    memcpy(e.map, &m, 128);
+    e.valid = true;
+    ctx->tmap_misses += 1;
+    return 0;
+}
+
 bool operand_tma_ok(const Operand& op, int64_t K, int64_t batch_inner, int64_t batch_outer) {
     if (reinterpret_cast<uintptr_t>(op.ptr) & 15) return false;
     const int64_t strided_extent = op.mn_major ? K : op.rows;
@@ -383,25 +421,21 @@ int make_operand_map(te_b200_ctx* ctx, CUtensorMap* out, const float* ptr, const
     const int64_t strided_extent = op.mn_major ? k_extent : op.rows;
     const int64_t e2 = (batch_inner > 1 && op.stride_inner != 0) ? batch_inner : 1;
     const int64_t e3 = (batch_outer > 1 && op.stride_outer != 0) ? batch_outer : 1;
-    cuuint64_t dims[4] = {(cuuint64_t)contiguous_extent, (cuuint64_t)strided_extent, (cuuint64_t)e2, (cuuint64_t)e3};
+    const uint64_t dims[4] = {(uint64_t)contiguous_extent, (uint64_t)strided_extent, (uint64_t)e2, (uint64_t)e3};
     // A slice with one line may carry any pitch; the map still needs a legal one.
     const int64_t ld = strided_extent > 1 ? op.ld : ((contiguous_extent + 3) & ~int64_t(3));
-    const cuuint64_t row_bytes = (cuuint64_t)ld * 4;
-    cuuint64_t strides[3] = {row_bytes,
-                             e2 > 1 ? (cuuint64_t)op.stride_inner * 4 : row_bytes,
-                             e3 > 1 ? (cuuint64_t)op.stride_outer * 4 : row_bytes};
-    cuuint32_t box[4] = {(cuuint32_t)BK, (cuuint32_t)(op.mn_major ? BK : box_rows), 1, 1};
-    cuuint32_t estr[4] = {1, 1, 1, 1};
-    EncodeTiledFn fn = reinterpret_cast<EncodeTiledFn>(ctx->encode_tiled);
-    CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<float*>(ptr), dims, strides, box, estr,
-                    CU_TENSOR_MAP_INTERLEAVE_NONE,
-                    op.mn_major ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
-                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) {
+    const uint64_t row_bytes = (uint64_t)ld * 4;
+    const uint64_t strides[3] = {row_bytes,
+                                 e2 > 1 ? (uint64_t)op.stride_inner * 4 : row_bytes,
+                                 e3 > 1 ? (uint64_t)op.stride_outer * 4 : row_bytes};
+    const uint32_t box[4] = {(uint32_t)BK, (uint32_t)(op.mn_major ? BK : box_rows), 1, 1};
+    const int r = encode_tiled_cached(ctx, out, ptr, dims, strides, box,
+                                      (int)(op.mn_major ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B),
+                                      (int)CU_TENSOR_MAP_L2_PROMOTION_L2_256B);
+    if (r != 0) {
         char msg[256];
         snprintf(msg, sizeof msg,
-                 "cuTensorMapEncodeTiled failed (%d): dims {%llu,%llu,%llu,%llu} ld %lld ptr %p", (int)r,
+                 "cuTensorMapEncodeTiled failed (%d): dims {%llu,%llu,%llu,%llu} ld %lld ptr %p", r,
                  (unsigned long long)dims[0], (unsigned long long)dims[1], (unsigned long long)dims[2],
                  (unsigned long long)dims[3], (long long)op.ld, (const void*)ptr);
         set_error(msg);
@@ -419,15 +453,13 @@ static bool make_one_output_map(te_b200_ctx* ctx, CUtensorMap* out, float* ptr, 
     const int64_t ld = g.M > 1 ? g.ldc : ((g.N + 3) & ~int64_t(3));
     // split-K scratch is laid out [split][outer][inner][M][N] dense, so splits extend the outer batch dimension
     const int64_t outer_n = g.batch_outer * k_splits;
-    cuuint64_t dims[4] = {(cuuint64_t)g.N, (cuuint64_t)g.M, (cuuint64_t)g.batch_inner, (cuuint64_t)outer_n};
-    const cuuint64_t row_bytes = (cuuint64_t)ld * 4;
-    cuuint64_t strides[3] = {row_bytes, g.batch_inner > 1 ? (cuuint64_t)g.c_stride_inner * 4 : row_bytes,
-                             outer_n > 1 ? (cuuint64_t)g.c_stride_outer * 4 : row_bytes};
-    cuuint32_t box[4] = {32, 32, 1, 1};
-    cuuint32_t estr[4] = {1, 1, 1, 1};
-    EncodeTiledFn fn = reinterpret_cast<EncodeTiledFn>(ctx->encode_tiled);
-    return fn(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, ptr, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+    const uint64_t dims[4] = {(uint64_t)g.N, (uint64_t)g.M, (uint64_t)g.batch_inner, (uint64_t)outer_n};
+    const uint64_t row_bytes = (uint64_t)ld * 4;
+    const uint64_t strides[3] = {row_bytes, g.batch_inner > 1 ? (uint64_t)g.c_stride_inner * 4 : row_bytes,
+                                 outer_n > 1 ? (uint64_t)g.c_stride_outer * 4 : row_bytes};
+    const uint32_t box[4] = {32, 32, 1, 1};
+    return encode_tiled_cached(ctx, out, ptr, dims, strides, box, (int)CU_TENSOR_MAP_SWIZZLE_128B,
+                               (int)CU_TENSOR_MAP_L2_PROMOTION_NONE) == 0;
 }
 
 bool make_output_maps(te_b200_ctx* ctx, const GemmProblem& g, int k_splits, CUtensorMap* tm_c, CUtensorMap* tm_pre) {
@@ -451,7 +483,7 @@ void fill_common_params(GemmParams& p, const te_b200_ctx* ctx, const GemmProblem
     p.b_mul_inner = (g.batch_inner > 1 && g.b.stride_inner != 0) ? 1 : 0;
     p.b_mul_outer = (g.batch_outer > 1 && g.b.stride_outer != 0) ? 1 : 0;
     p.ldc = g.ldc; p.c_stride_inner = g.c_stride_inner; p.c_stride_outer = g.c_stride_outer;
-    p.c = g.c; p.preact = g.preact; p.bias = g.bias;
+    p.c = g.c; p.preact = g.preact; p.bias = g.bias; p.residual = g.residual;
     p.alpha = g.alpha; p.scale_mode = g.scale_mode; p.epilogue = g.epilogue;
     p.status = ctx->d_status;
     p.k_splits = 1;
@@ -469,9 +501,9 @@ void prepare_split(const GemmProblem& g, int k_splits, GemmProblem& kp, GemmPara
     kp.ldc = g.N;
     kp.c_stride_inner = g.M * g.N;
     kp.c_stride_outer = g.batch_inner * g.M * g.N;
-    kp.preact = nullptr; kp.bias = nullptr; kp.scale_mode = TE_SCALE_NONE; kp.epilogue = TE_EPI_NONE;
+    kp.preact = nullptr; kp.bias = nullptr; kp.residual = nullptr; kp.scale_mode = TE_SCALE_NONE; kp.epilogue = TE_EPI_NONE;
     p.c = kp.c; p.ldc = kp.ldc; p.c_stride_inner = kp.c_stride_inner; p.c_stride_outer = kp.c_stride_outer;
-    p.preact = nullptr; p.bias = nullptr; p.scale_mode = TE_SCALE_NONE; p.epilogue = TE_EPI_NONE;
+    p.preact = nullptr; p.bias = nullptr; p.residual = nullptr; p.scale_mode = TE_SCALE_NONE; p.epilogue = TE_EPI_NONE;
     p.k_splits = k_splits;
     p.kb_per_split = (kblocks + k_splits - 1) / k_splits;
     p.split_stride = batches * g.M * g.N;
@@ -483,7 +515,7 @@ struct SplitReduceParams {
     long long split_stride;
     int k_splits;
     long long M, N, batch_inner, total;       // total = batches * M * N
-    float* c; float* preact; const float* bias;
+    float* c; float* preact; const float* bias; const float* residual;
     long long ldc, c_stride_inner, c_stride_outer;
     float alpha; int scale_mode; int epilogue;
 };
@@ -502,6 +534,7 @@ __global__ void __launch_bounds__(256) splitk_reduce_kernel(const SplitReducePar
         const long long o = bo * r.c_stride_outer + bi * r.c_stride_inner + row * r.ldc + n;
         if (r.preact) r.preact[o] = v;
         if (r.epilogue == TE_EPI_BIAS_GELU) v = gelu_tanh(v);
+        if (r.residual) v += r.residual[o];
         r.c[o] = v;
     }
 }
@@ -513,7 +546,7 @@ int finish_split(te_b200_ctx* ctx, const GemmProblem& g, int k_splits, cudaStrea
     r.total = g.batch_inner * g.batch_outer * g.M * g.N;
     r.split_stride = r.total;
     r.k_splits = k_splits;
-    r.c = g.c; r.preact = g.preact; r.bias = g.bias;
+    r.c = g.c; r.preact = g.preact; r.bias = g.bias; r.residual = g.residual;
     r.ldc = g.ldc; r.c_stride_inner = g.c_stride_inner; r.c_stride_outer = g.c_stride_outer;
     r.alpha = g.alpha; r.scale_mode = g.scale_mode; r.epilogue = g.epilogue;
     long long blocks = (r.total + 255) / 256;
@@ -525,20 +558,43 @@ int finish_split(te_b200_ctx* ctx, const GemmProblem& g, int k_splits, cudaStrea
     return TE_OK;
 }
 
+// One-time set-up of a kernel instance in this context: the dynamic shared memory limit (which also makes the
+// runtime load the kernel's module).
+template <int BN, int NPL, bool A_MN, bool B_MN>
+static int ensure_kernel_attributes(te_b200_ctx* ctx) {
+    using Cfg = TileCfg<BN, NPL>;
+    // 3xTF32 (NPL = 2) has one instance, which carries the residual input; TF32 has all three epilogue forms
+    int& attr_done = ctx->kernel_state[reinterpret_cast<const void*>(gemm_tf32_kernel<BN, NPL, A_MN, B_MN, EPI_RESIDUAL>)];
+    if (attr_done) return TE_OK;
+    cudaError_t e = cudaFuncSetAttribute(gemm_tf32_kernel<BN, NPL, A_MN, B_MN, EPI_RESIDUAL>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
+    if (e == cudaSuccess && NPL == 1)
+        e = cudaFuncSetAttribute(gemm_tf32_kernel<BN, 1, A_MN, B_MN, EPI_PLAIN>,
+                                 cudaFuncAttributeMaxDynamicSharedMemorySize, TileCfg<BN, 1>::SMEM_BYTES);
+    if (e == cudaSuccess && NPL == 1)
+        e = cudaFuncSetAttribute(gemm_tf32_kernel<BN, 1, A_MN, B_MN, EPI_GENERAL>,
+                                 cudaFuncAttributeMaxDynamicSharedMemorySize, TileCfg<BN, 1>::SMEM_BYTES);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(max dynamic shared memory)");
+    attr_done = 1;
+    return TE_OK;
+}
+
+int prepare_3xtf32_kernels(te_b200_ctx* ctx) {
+    int rc;
+    if ((rc = ensure_kernel_attributes<64, 2, false, false>(ctx))) return rc;
+    if ((rc = ensure_kernel_attributes<128, 2, false, false>(ctx))) return rc;
+    cudaFuncAttributes fa;
+    cudaError_t e = cudaFuncGetAttributes(&fa, splitk_reduce_kernel);      // loads the kernel
+    if (e != cudaSuccess) return cuda_fail(e, "cudaFuncGetAttributes(splitk_reduce_kernel)");
+    if ((rc = prepare_pair_3xtf32_kernel(ctx))) return rc;
+    return prepare_pack_kernels();
+}
+
 template <int BN, int NPL, bool A_MN, bool B_MN>
 static int launch_variant(te_b200_ctx* ctx, const GemmProblem& g_in, int k_splits, cudaStream_t stream) {
     GemmProblem g = g_in;
     using Cfg = TileCfg<BN, NPL>;
-    static bool attr_done[16] = {};   // per device ordinal
-    if (ctx->device >= 16 || !attr_done[ctx->device]) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_tf32_kernel<BN, NPL, A_MN, B_MN, false>,
-                                             cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
-        if (e == cudaSuccess && NPL == 1)
-            e = cudaFuncSetAttribute(gemm_tf32_kernel<BN, 1, A_MN, B_MN, true>,
-                                     cudaFuncAttributeMaxDynamicSharedMemorySize, TileCfg<BN, 1>::SMEM_BYTES);
-        if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(max dynamic shared memory)");
-        if (ctx->device < 16) attr_done[ctx->device] = true;
-    }
+    if (int rc0 = ensure_kernel_attributes<BN, NPL, A_MN, B_MN>(ctx)) return rc0;
     CUtensorMap ma, mal, mb, mbl;
     int rc;
     if ((rc = make_operand_map(ctx, &ma, g.a.ptr, g.a, g.K, BM, g.batch_inner, g.batch_outer))) return rc;
@@ -562,10 +618,11 @@ static int launch_variant(te_b200_ctx* ctx, const GemmProblem& g_in, int k_split
     // The bare-product kernel serves the calls whose output a tensor map describes and that ask for nothing but the
     // product (split-K partial tiles included).
     const bool bare = NPL == 1 && p.tma_store &&
-                      (k_splits > 1 || (!g.bias && !g.preact && g.scale_mode == TE_SCALE_NONE && g.epilogue == TE_EPI_NONE));
-    auto kernel = gemm_tf32_kernel<BN, NPL, A_MN, B_MN, false>;
+                      (k_splits > 1 || (!g.bias && !g.preact && !g.residual && g.scale_mode == TE_SCALE_NONE && g.epilogue == TE_EPI_NONE));
+    auto kernel = gemm_tf32_kernel<BN, NPL, A_MN, B_MN, EPI_RESIDUAL>;
     if constexpr (NPL == 1) {
-        if (bare) kernel = gemm_tf32_kernel<BN, 1, A_MN, B_MN, true>;
+        if (bare) kernel = gemm_tf32_kernel<BN, 1, A_MN, B_MN, EPI_PLAIN>;
+        else if (!p.residual) kernel = gemm_tf32_kernel<BN, 1, A_MN, B_MN, EPI_GENERAL>;
     }
     cudaError_t e = launch_pdl(kernel, dim3((unsigned)grid), dim3(CTA_THREADS), Cfg::SMEM_BYTES, stream, ma, mal, mb, mbl, mc, mpre, p);
     if (e != cudaSuccess) return cuda_fail(e, "gemm_tf32_kernel launch");
@@ -648,14 +705,30 @@ TileChoice choose_tile(const te_b200_ctx* ctx, const GemmProblem& g) {
     return best;
 }
 
-int launch_gemm(te_b200_ctx* ctx, const GemmProblem& g, cudaStream_t stream) {
-    TileChoice c = choose_tile(ctx, g);
-#ifdef TE_TUNE
-    if (const char* f = getenv("TE_FORCE_TILE")) {     // "bn,pair,splits": tuning builds only
-        int bn = 0, pair = 0, sp = 1;
-        if (sscanf(f, "%d,%d,%d", &bn, &pair, &sp) == 3 && !g.a_lo) c = TileChoice{bn, pair != 0, g.split_ws ? sp : 1};
+// Self-test of the bounded wait every kernel of the library uses: one warp initialises an mbarrier that nothing ever
+// arrives at and waits on it.  The wait runs out after the context's limit, records STATUS_SELFTEST_WAIT in the status
+// word and the kernel returns normally -- no trap, no fault, the context stays usable.
+__global__ void __launch_bounds__(32) wait_selftest_kernel(int* status) {
+    __shared__ __align__(8) unsigned long long bar;
+    __shared__ int abort_flag;
+    griddep_wait();
+    if (threadIdx.x == 0) {
+        mbar_init(smem_u32(&bar), 1);
+        abort_flag = 0;
+        fence_barrier_init();
+        wait_bounded(smem_u32(&bar), 0, &abort_flag, status, STATUS_SELFTEST_WAIT);
     }
-#endif
+}
+
+int launch_wait_selftest(te_b200_ctx* ctx, cudaStream_t stream) {
+    cudaError_t e = launch_pdl(wait_selftest_kernel, dim3(1), dim3(32), 0, stream, ctx->d_status);
+    if (e != cudaSuccess) return cuda_fail(e, "wait_selftest_kernel launch");
+    ctx->launches += 1;
+    return TE_OK;
+}
+
+int launch_gemm(te_b200_ctx* ctx, const GemmProblem& g, cudaStream_t stream) {
+    const TileChoice c = choose_tile(ctx, g);
     if (c.pair) return launch_gemm_2cta(ctx, g, c.bn, c.k_splits, stream);
     if (c.bn == 256) return launch_bn<256>(ctx, g, c.k_splits, stream);
     if (c.bn == 128) return launch_bn<128>(ctx, g, c.k_splits, stream);

@@ -45,10 +45,10 @@ struct PairCfg {
     static_assert(SMEM_BYTES <= 232448, "exceeds the 227 KB of shared memory a CTA can have");
 };
 
-// PLAIN: the output is the bare product going out through TMA stores (no scale, bias, pre-activation output or GELU).
+// EPI_PLAIN: the output is the bare product going out through TMA stores (no scale, bias, pre-activation output or GELU).
 // Compiling that case separately keeps the general epilogue's code out of it, which is worth 2-11 % on the products
 // whose epilogue is not hidden behind a long main loop (16384x384x384: 16.9 -> 15.1 us) and 2 % on 8192^3.
-template <int BN, int NPL, bool A_MN, bool B_MN, int NW = 1, bool PLAIN = false>
+template <int BN, int NPL, bool A_MN, bool B_MN, int NW = 1, int EPI = EPI_GENERAL>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(CTA_THREADS, 1)
 gemm_tf32_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_a_lo,
                       const __grid_constant__ CUtensorMap tm_b, const __grid_constant__ CUtensorMap tm_b_lo,
@@ -273,9 +273,11 @@ gemm_tf32_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
             EpilogueRow er;
             er.c_row = p.c + batch_off + (long long)row * p.ldc;
             er.pre_row = p.preact ? p.preact + batch_off + (long long)row * p.ldc : nullptr;
+            er.res_row = p.residual ? p.residual + batch_off + (long long)row * p.ldc : nullptr;
             er.row_ok = row < p.M;
             er.vec_ok = ((p.ldc & 3) == 0) && ((reinterpret_cast<uintptr_t>(p.c + batch_off) & 15) == 0) &&
-                        (!p.preact || (reinterpret_cast<uintptr_t>(p.preact + batch_off) & 15) == 0);
+                        (!p.preact || (reinterpret_cast<uintptr_t>(p.preact + batch_off) & 15) == 0) &&
+                        (!p.residual || (reinterpret_cast<uintptr_t>(p.residual + batch_off) & 15) == 0);
             er.tma_ok = p.tma_store != 0;
             er.stage = epi_stage + warp * EPI_STAGE_BYTES;
             er.tm_c = &tm_c;
@@ -320,10 +322,10 @@ gemm_tf32_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
                     for (int cc = 0; cc < NACC / 32; ++cc) {
                         const int col0 = nh + cc * 32;
                         if (col0 < p.N) {
-                            if constexpr (PLAIN) {
+                            if constexpr (EPI == EPI_PLAIN) {
                                 if (er.row0 < p.M) stage_and_store32(&acc[cc * 32], col0, er, er.tm_c, lane);
                             } else {
-                                epilogue_store32(&acc[cc * 32], col0, er, p, lane);
+                                epilogue_store32<EPI == EPI_RESIDUAL>(&acc[cc * 32], col0, er, p, lane);
                             }
                         }
                     }
@@ -346,10 +348,10 @@ gemm_tf32_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
                     float v[32];
 #pragma unroll
                     for (int j = 0; j < 32; ++j) v[j] = p.K > 0 ? __uint_as_float(r[j]) : 0.0f;
-                    if constexpr (PLAIN) {
+                    if constexpr (EPI == EPI_PLAIN) {
                         if (er.row0 < p.M) stage_and_store32(v, col0, er, er.tm_c, lane);
                     } else {
-                        epilogue_store32(v, col0, er, p, lane);
+                        epilogue_store32<EPI == EPI_RESIDUAL>(v, col0, er, p, lane);
                     }
                 }
                 tc_fence_before_sync();
@@ -371,36 +373,71 @@ gemm_tf32_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
     }
 }
 
-template <int BN, int NPL, bool A_MN, bool B_MN, int NW, bool PLAIN>
+// One-time set-up of a pair-kernel instance in this context; *out_pairs receives how many CTA pairs can be resident.
+template <int BN, int NPL, bool A_MN, bool B_MN, int NW, int EPI>
+static int ensure_pair_kernel(te_b200_ctx* ctx, int* out_pairs) {
+    using Cfg = PairCfg<BN, NPL, NW>;
+    auto kernel = gemm_tf32_pair_kernel<BN, NPL, A_MN, B_MN, NW, EPI>;
+    // kernel_state of a pair kernel: 0 = untouched, otherwise the number of CTA pairs that can be resident at once
+    int& max_pairs = ctx->kernel_state[reinterpret_cast<const void*>(kernel)];
+    if (max_pairs == 0) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
+        if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(max dynamic shared memory)");
+        // pairs must sit on neighbouring SMs, so the count can be below SMs / 2
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(ctx->sm_count & ~1, 1, 1);
+        cfg.blockDim = dim3(CTA_THREADS, 1, 1);
+        cfg.dynamicSmemBytes = Cfg::SMEM_BYTES;
+        cudaLaunchAttribute attr;
+        attr.id = cudaLaunchAttributeClusterDimension;
+        attr.val.clusterDim.x = 2; attr.val.clusterDim.y = 1; attr.val.clusterDim.z = 1;
+        cfg.attrs = &attr;
+        cfg.numAttrs = 1;
+        int n = 0;
+        cudaError_t eo = cudaOccupancyMaxActiveClusters(&n, kernel, &cfg);
+        if (eo != cudaSuccess || n < 1) { cudaGetLastError(); n = ctx->sm_count / 2; }
+        max_pairs = n;
+    }
+    *out_pairs = max_pairs;
+    return TE_OK;
+}
+
+int prepare_pair_3xtf32_kernel(te_b200_ctx* ctx) {
+    int pairs = 0;
+    return ensure_pair_kernel<256, 2, false, false, 1, EPI_RESIDUAL>(ctx, &pairs);
+}
+
+template <int BN, int NPL, bool A_MN, bool B_MN, int NW, int EPI>
 static int launch_pair_impl(te_b200_ctx* ctx, const GemmProblem& g_in, int k_splits, cudaStream_t stream);
 
 // The bare-product kernel serves the calls whose output a tensor map can describe and that ask for nothing but the
 // product (split-K partial tiles included); everything else takes the general one.
 template <int BN, int NPL, bool A_MN, bool B_MN, int NW = 1>
 static int launch_pair_variant(te_b200_ctx* ctx, const GemmProblem& g, int k_splits, cudaStream_t stream) {
-    const bool bare = k_splits > 1 || (!g.bias && !g.preact && g.scale_mode == TE_SCALE_NONE && g.epilogue == TE_EPI_NONE);
-    CUtensorMap probe_c, probe_pre;
+    const bool bare = k_splits > 1 || (!g.bias && !g.preact && !g.residual && g.scale_mode == TE_SCALE_NONE && g.epilogue == TE_EPI_NONE);
     if (NPL == 1 && bare) {
+        // does a tensor map describe the output?  (the encoding itself is cached in the context, so the launcher's own
+        // call below costs a table look-up)
         GemmProblem k = g;
         GemmParams scratch;
+        CUtensorMap probe_c, probe_pre;
         fill_common_params(scratch, ctx, g);
         prepare_split(g, k_splits, k, scratch);
         if (make_output_maps(ctx, k, k_splits, &probe_c, &probe_pre))
-            return launch_pair_impl<BN, NPL, A_MN, B_MN, NW, true>(ctx, g, k_splits, stream);
+            return launch_pair_impl<BN, NPL, A_MN, B_MN, NW, EPI_PLAIN>(ctx, g, k_splits, stream);
     }
-    return launch_pair_impl<BN, NPL, A_MN, B_MN, NW, false>(ctx, g, k_splits, stream);
+    // 3xTF32 (NPL = 2) has one instance, which carries the residual input
+    if (NPL == 2 || (g.residual && k_splits == 1)) return launch_pair_impl<BN, NPL, A_MN, B_MN, NW, EPI_RESIDUAL>(ctx, g, k_splits, stream);
+    if constexpr (NPL == 1) return launch_pair_impl<BN, NPL, A_MN, B_MN, NW, EPI_GENERAL>(ctx, g, k_splits, stream);
+    return TE_ERR_BAD_ARGUMENT;   // not reached
 }
 
-template <int BN, int NPL, bool A_MN, bool B_MN, int NW, bool PLAIN>
+template <int BN, int NPL, bool A_MN, bool B_MN, int NW, int EPI>
 static int launch_pair_impl(te_b200_ctx* ctx, const GemmProblem& g_in, int k_splits, cudaStream_t stream) {
     using Cfg = PairCfg<BN, NPL, NW>;
-    auto kernel = gemm_tf32_pair_kernel<BN, NPL, A_MN, B_MN, NW, PLAIN>;
-    static bool attr_done[16] = {};
-    if (ctx->device >= 16 || !attr_done[ctx->device]) {
-        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
-        if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(max dynamic shared memory)");
-        if (ctx->device < 16) attr_done[ctx->device] = true;
-    }
+    auto kernel = gemm_tf32_pair_kernel<BN, NPL, A_MN, B_MN, NW, EPI>;
+    int max_pairs = 0;
+    if (int rc0 = ensure_pair_kernel<BN, NPL, A_MN, B_MN, NW, EPI>(ctx, &max_pairs)) return rc0;
     GemmProblem g = g_in;
     CUtensorMap ma, mal, mb, mbl;
     int rc;
@@ -418,32 +455,13 @@ static int launch_pair_impl(te_b200_ctx* ctx, const GemmProblem& g_in, int k_spl
     prepare_split(g_in, k_splits, g, p);       // with k_splits > 1 the kernel writes raw partial tiles to scratch
     CUtensorMap mc, mpre;
     p.tma_store = make_output_maps(ctx, g, k_splits, &mc, &mpre) ? 1 : 0;
-    if (PLAIN && !p.tma_store) {
+    if (EPI == EPI_PLAIN && !p.tma_store) {
         set_error("internal: the bare-product kernel was chosen for an output no tensor map describes");
         return TE_ERR_BAD_ARGUMENT;
     }
     p.tiles_m = (int)((g.M + PAIR_BM - 1) / PAIR_BM);
     p.tiles_n = (int)((g.N + Cfg::TILE_N - 1) / Cfg::TILE_N);
     const long long total = (long long)p.tiles_m * p.tiles_n * p.num_batches * k_splits;
-    // How many CTA pairs can be resident at once (pairs must sit on neighbouring SMs, so this can be below SMs/2).
-    static int max_pairs_cached[16] = {};
-    int max_pairs = ctx->device < 16 ? max_pairs_cached[ctx->device] : 0;
-    if (max_pairs == 0) {
-        cudaLaunchConfig_t cfg = {};
-        cfg.gridDim = dim3(ctx->sm_count & ~1, 1, 1);
-        cfg.blockDim = dim3(CTA_THREADS, 1, 1);
-        cfg.dynamicSmemBytes = Cfg::SMEM_BYTES;
-        cudaLaunchAttribute attr;
-        attr.id = cudaLaunchAttributeClusterDimension;
-        attr.val.clusterDim.x = 2; attr.val.clusterDim.y = 1; attr.val.clusterDim.z = 1;
-        cfg.attrs = &attr;
-        cfg.numAttrs = 1;
-        int n = 0;
-        cudaError_t eo = cudaOccupancyMaxActiveClusters(&n, kernel, &cfg);
-        if (eo != cudaSuccess || n < 1) { cudaGetLastError(); n = ctx->sm_count / 2; }
-        max_pairs = n;
-        if (ctx->device < 16) max_pairs_cached[ctx->device] = n;
-    }
     const int pairs = (int)(total < max_pairs ? total : max_pairs);
     cudaError_t e = launch_pdl(kernel, dim3((unsigned)(2 * pairs)), dim3(CTA_THREADS), Cfg::SMEM_BYTES, stream, ma, mal, mb, mbl, mc, mpre, p);
     if (e != cudaSuccess) return cuda_fail(e, "gemm_tf32_pair_kernel launch");

@@ -20,7 +20,6 @@ namespace te {
 
 namespace {
 
-constexpr int STATUS_BAD_INDEX = 201;   // device status code: an embedding index was out of range
 
 __device__ __forceinline__ float warp_sum_f(float v) {
 #pragma unroll
@@ -98,7 +97,7 @@ __global__ void __launch_bounds__(256) layernorm_forward_kernel(const float* __r
 // partial row pair; layernorm_param_grad_kernel adds the partials of all blocks in block order.
 template <int N, bool VEC>
 __global__ void __launch_bounds__(256) layernorm_backward_kernel(const float* __restrict__ x, const float* __restrict__ gamma,
-                                                                 const float* __restrict__ dy, float* __restrict__ dx,
+                                                                 const float* __restrict__ dy, float* dx, const float* dx_residual,
                                                                  float* __restrict__ partial, long long rows, int cols, float eps) {
     griddep_wait();
     using R = RowRegs<N, VEC>;
@@ -142,6 +141,11 @@ __global__ void __launch_bounds__(256) layernorm_backward_kernel(const float* __
         m2 = warp_sum_f(m2) * inv_n;
 #pragma unroll
         for (int k = 0; k < N * R::W; ++k) xr.v[k] = (gy.v[k] - m1 - xr.v[k] * m2) * inv_std;
+        if (dx_residual) {     // the gradient arriving over the branch that bypasses this LayerNorm (may be dx itself)
+            gy.load(dx_residual + r * cols, cols, lane);
+#pragma unroll
+            for (int k = 0; k < N * R::W; ++k) xr.v[k] += gy.v[k];
+        }
         xr.store(dx + r * cols, cols, lane);
     }
     // block sums of the two column accumulators, warps added in warp order
@@ -209,7 +213,7 @@ __global__ void __launch_bounds__(256) embedding_forward_kernel(const float* __r
         const int j = (int)(idx - i * per_row);
         const long long tok = tokens[i];
         const bool ok = tok >= 0 && tok < vocab;
-        if (!ok && j == 0) atomicCAS(status, 0, STATUS_BAD_INDEX);
+        if (!ok && j == 0) atomicCAS(status, 0, te::STATUS_BAD_EMBEDDING_INDEX);
         if (VEC) {
             float4 v = ok ? __ldg(reinterpret_cast<const float4*>(table + tok * D) + j) : make_float4(0.f, 0.f, 0.f, 0.f);
             if (pos) {
@@ -312,7 +316,7 @@ __global__ void __launch_bounds__(256) cross_entropy_rows_kernel(const float* __
         const float* row = logits + r * V;
         long long tgt = targets[r];
         if (tgt < 0 || tgt >= V) {
-            if (lane == 0) atomicCAS(status, 0, STATUS_BAD_INDEX);
+            if (lane == 0) atomicCAS(status, 0, te::STATUS_BAD_TARGET_INDEX);
             tgt = 0;
         }
         float m = -INFINITY;
@@ -394,14 +398,16 @@ int launch_layernorm_forward(te_b200_ctx* ctx, const float* x, const float* gamm
 }
 
 int launch_layernorm_backward(te_b200_ctx* ctx, const float* x, const float* gamma, const float* dy, float* dx,
-                              float* dgamma, float* dbeta, int64_t rows, int64_t cols64, float eps, cudaStream_t st) {
+                              const float* dx_residual, float* dgamma, float* dbeta, int64_t rows, int64_t cols64, float eps,
+                              cudaStream_t st) {
     if (cols64 == 0) return TE_OK;
     if (cols64 > 1024) {
         set_error("LayerNorm rows longer than 1024 elements are not supported");
         return TE_ERR_BAD_ARGUMENT;
     }
     const int cols = (int)cols64;
-    const bool vec = (cols & 3) == 0 && aligned16(x) && aligned16(dy) && aligned16(dx) && aligned16(gamma);
+    const bool vec = (cols & 3) == 0 && aligned16(x) && aligned16(dy) && aligned16(dx) && aligned16(gamma) &&
+                     (!dx_residual || aligned16(dx_residual));
     const int grid = row_grid(rows, ctx->sm_count, 2);
     const size_t need = (size_t)grid * 2 * cols * sizeof(float);
     if (need > ctx->workspace_bytes) {
@@ -410,7 +416,7 @@ int launch_layernorm_backward(te_b200_ctx* ctx, const float* x, const float* gam
     }
     float* partial = static_cast<float*>(ctx->workspace);
     const size_t smem = (size_t)8 * cols * sizeof(float);
-#define CALL(N, V) launch_pdl(layernorm_backward_kernel<N, V>, dim3(grid), dim3(256), smem, st, x, gamma, dy, dx, partial, rows, cols, eps)
+#define CALL(N, V) launch_pdl(layernorm_backward_kernel<N, V>, dim3(grid), dim3(256), smem, st, x, gamma, dy, dx, dx_residual, partial, rows, cols, eps)
     TE_LN_DISPATCH(CALL)
 #undef CALL
     cudaError_t e = cudaGetLastError();

@@ -28,7 +28,7 @@ struct PackParams {
     float* dst_lo;
     long long rows, K, kp, ld;
     long long stride_inner, stride_outer;   // source batch strides (elements)
-    int batch_inner;                         // packed batches are enumerated outer-major
+    long long batch_inner, num_batches;     // packed batches are enumerated outer-major
 };
 
 template <bool MN_MAJOR, bool SPLIT>
@@ -37,35 +37,38 @@ __global__ void __launch_bounds__(256) pack_operand_kernel(const PackParams p) {
     __shared__ float tile[32][33];
     const int tx = threadIdx.x, ty = threadIdx.y;          // 32 x 8
     const long long k0 = (long long)blockIdx.x * 32;
-    const long long r0 = (long long)blockIdx.y * 32;
-    const int batch = blockIdx.z;
-    const int bo = batch / p.batch_inner, bi = batch - bo * p.batch_inner;
-    const float* src = p.src + bo * p.stride_outer + bi * p.stride_inner;
-    const long long plane = (long long)batch * p.rows * p.kp;
-
-    if (MN_MAJOR) {
-        // coalesced along the row index; transpose through shared memory
+    // grid.y / grid.z are capped at 65535: blocks walk the remaining row blocks and batches (block-uniform loops)
+    for (long long batch = blockIdx.z; batch < p.num_batches; batch += gridDim.z) {
+        const long long bo = batch / p.batch_inner, bi = batch - bo * p.batch_inner;
+        const float* src = p.src + bo * p.stride_outer + bi * p.stride_inner;
+        const long long plane = batch * p.rows * p.kp;
+        for (long long r0 = (long long)blockIdx.y * 32; r0 < p.rows; r0 += (long long)gridDim.y * 32) {
+            if (MN_MAJOR) {
+                // coalesced along the row index; transpose through shared memory
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            const long long k = k0 + ty + 8 * i, r = r0 + tx;
-            tile[ty + 8 * i][tx] = (k < p.K && r < p.rows) ? src[k * p.ld + r] : 0.0f;
-        }
-        __syncthreads();
-    }
+                for (int i = 0; i < 4; ++i) {
+                    const long long k = k0 + ty + 8 * i, r = r0 + tx;
+                    tile[ty + 8 * i][tx] = (k < p.K && r < p.rows) ? src[k * p.ld + r] : 0.0f;
+                }
+                __syncthreads();
+            }
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        const long long r = r0 + ty + 8 * i, k = k0 + tx;
-        if (r >= p.rows || k >= p.kp) continue;
-        float x;
-        if (MN_MAJOR) x = tile[tx][ty + 8 * i];
-        else x = (k < p.K) ? src[r * p.ld + k] : 0.0f;
-        const long long o = plane + r * p.kp + k;
-        if (SPLIT) {
-            const float hi = to_tf32_rn(x);
-            p.dst_hi[o] = hi;
-            p.dst_lo[o] = to_tf32_rn(x - hi);
-        } else {
-            p.dst_hi[o] = x;
+            for (int i = 0; i < 4; ++i) {
+                const long long r = r0 + ty + 8 * i, k = k0 + tx;
+                if (r >= p.rows || k >= p.kp) continue;
+                float x;
+                if (MN_MAJOR) x = tile[tx][ty + 8 * i];
+                else x = (k < p.K) ? src[r * p.ld + k] : 0.0f;
+                const long long o = plane + r * p.kp + k;
+                if (SPLIT) {
+                    const float hi = to_tf32_rn(x);
+                    p.dst_hi[o] = hi;
+                    p.dst_lo[o] = to_tf32_rn(x - hi);
+                } else {
+                    p.dst_hi[o] = x;
+                }
+            }
+            if (MN_MAJOR) __syncthreads();   // the tile is rewritten by the next iteration
         }
     }
 }
@@ -79,8 +82,8 @@ __global__ void __launch_bounds__(256) pack_rows_vec4_kernel(const PackParams p,
         const long long q = i % quads_per_row;
         const long long rb = i / quads_per_row;           // row index over all batches
         const long long r = rb % p.rows;
-        const int batch = (int)(rb / p.rows);
-        const int bo = batch / p.batch_inner, bi = batch - bo * p.batch_inner;
+        const long long batch = rb / p.rows;
+        const long long bo = batch / p.batch_inner, bi = batch - bo * p.batch_inner;
         const float* src = p.src + bo * p.stride_outer + bi * p.stride_inner + r * p.ld + 4 * q;
         float4 x;
         if (4 * q + 4 <= p.K) {
@@ -104,6 +107,16 @@ __global__ void __launch_bounds__(256) pack_rows_vec4_kernel(const PackParams p,
     }
 }
 
+// Makes the runtime load the packing kernels now (a first launch would otherwise do it).
+int prepare_pack_kernels() {
+    cudaFuncAttributes fa;
+    cudaError_t e = cudaFuncGetAttributes(&fa, pack_rows_vec4_kernel<true>);
+    if (e == cudaSuccess) e = cudaFuncGetAttributes(&fa, pack_operand_kernel<true, true>);
+    if (e == cudaSuccess) e = cudaFuncGetAttributes(&fa, pack_operand_kernel<false, true>);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaFuncGetAttributes(pack kernels)");
+    return TE_OK;
+}
+
 int launch_pack(te_b200_ctx* ctx, const Operand& src, int64_t K, int64_t batch_inner, int64_t batch_outer,
                 float* dst_hi, float* dst_lo, bool split, cudaStream_t stream) {
     // Broadcast levels are packed once.
@@ -113,13 +126,10 @@ int launch_pack(te_b200_ctx* ctx, const Operand& src, int64_t K, int64_t batch_i
     p.src = src.ptr; p.dst_hi = dst_hi; p.dst_lo = dst_lo;
     p.rows = src.rows; p.K = K; p.kp = (K + 3) & ~int64_t(3); p.ld = src.ld;
     p.stride_inner = src.stride_inner; p.stride_outer = src.stride_outer;
-    p.batch_inner = (int)bi;
+    p.batch_inner = bi;
+    p.num_batches = bi * bo;
     if (src.rows == 0 || K == 0) return TE_OK;
     const int64_t nb = bi * bo;
-    if (nb > 65535 || (src.rows + 31) / 32 > 65535) {
-        set_error("pack: operand has more than 65535 batches or row blocks");
-        return TE_ERR_BAD_ARGUMENT;
-    }
     const bool rows_aligned = !src.mn_major && (reinterpret_cast<uintptr_t>(src.ptr) & 15) == 0 && (src.ld & 3) == 0 &&
                               (bi == 1 || (src.stride_inner & 3) == 0) && (bo == 1 || (src.stride_outer & 3) == 0);
     if (rows_aligned) {
@@ -133,7 +143,8 @@ int launch_pack(te_b200_ctx* ctx, const Operand& src, int64_t K, int64_t batch_i
         ctx->launches += 1;
         return TE_OK;
     }
-    dim3 grid((unsigned)((p.kp + 31) / 32), (unsigned)((src.rows + 31) / 32), (unsigned)nb);
+    const int64_t row_blocks = (src.rows + 31) / 32;
+    dim3 grid((unsigned)((p.kp + 31) / 32), (unsigned)(row_blocks < 65535 ? row_blocks : 65535), (unsigned)(nb < 65535 ? nb : 65535));
     dim3 block(32, 8);
     if (src.mn_major) {
         if (split) launch_pdl(pack_operand_kernel<true, true>, dim3(grid), dim3(block), 0, stream, p);

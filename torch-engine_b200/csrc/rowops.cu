@@ -203,7 +203,7 @@ __global__ void __launch_bounds__(256) gelu_backward_vec4_kernel(const float4* _
 // out[j] = sum over rows of in[i*ld + j].  One block owns 32 columns; its 32 row-lanes stride the rows,
 // then a shared-memory tree adds the 32 partials in a fixed order (deterministic, unlike an atomicAdd).
 __global__ void __launch_bounds__(1024) colsum_kernel(const float* __restrict__ in, long long rows, long long cols,
-                                                      long long ld, float* __restrict__ out) {
+                                                      long long ld, float* out, int accumulate) {
     griddep_wait();
     __shared__ float part[32][33];
     const int tx = threadIdx.x, ty = threadIdx.y;
@@ -217,13 +217,30 @@ __global__ void __launch_bounds__(1024) colsum_kernel(const float* __restrict__ 
         if (ty < h) part[ty][tx] += part[ty + h][tx];
         __syncthreads();
     }
-    if (ty == 0 && col < cols) out[col] = part[0][tx];
+    if (ty == 0 && col < cols) out[col] = accumulate ? out[col] + part[0][tx] : part[0][tx];
 }
 
-// Two-phase form for tall inputs: slab s of the rows is summed into partial[s][col] (same thread layout as above),
-// then the slabs are added in order.  Deterministic, and enough blocks to pull the full HBM bandwidth.
+// Form for tall inputs: slab s of the rows is summed into partial[s][col] (same thread layout as above), then the
+// slabs are added in order.  Deterministic, and enough blocks to pull the full HBM bandwidth.
+// The block that finishes a column block last (counted through `counters`, one zero-initialised word per column block,
+// reset to zero by that block) adds the slabs' partial sums in a fixed order: warp w adds slabs w, w + 8, ... ascending,
+// then the eight warp sums are added in warp order.  One launch, and the same result bits on every run.
+__device__ __forceinline__ bool colsum_is_last_block(unsigned* counter, unsigned slabs, bool* flag_smem) {
+    __threadfence();                 // this thread's partial sums are visible before the count goes up
+    __syncthreads();
+    if (threadIdx.x == 0 && threadIdx.y == 0) {
+        const unsigned prev = atomicAdd(counter, 1u);
+        *flag_smem = (prev == slabs - 1);
+        if (prev == slabs - 1) *counter = 0;      // ready for the next call
+    }
+    __syncthreads();
+    if (*flag_smem) __threadfence();
+    return *flag_smem;
+}
+
 __global__ void __launch_bounds__(1024) colsum_slab_kernel(const float* __restrict__ in, long long rows, long long cols,
-                                                           long long ld, long long rows_per_slab, float* __restrict__ partial) {
+                                                           long long ld, long long rows_per_slab, float* __restrict__ partial,
+                                                           int slabs, unsigned* counters, float* out, int accumulate) {
     griddep_wait();
     __shared__ float part[32][33];
     const int tx = threadIdx.x, ty = threadIdx.y;
@@ -240,33 +257,29 @@ __global__ void __launch_bounds__(1024) colsum_slab_kernel(const float* __restri
         __syncthreads();
     }
     if (ty == 0 && col < cols) partial[(long long)blockIdx.y * cols + col] = part[0][tx];
-}
-// The slabs are added by one block per 32 columns: warp w adds slabs w, w + 8, ... in ascending order, then the
-// eight warp sums are added in warp order.
-__global__ void __launch_bounds__(256) colsum_finish_kernel(const float* __restrict__ partial, int slabs, long long cols,
-                                                            float* __restrict__ out) {
-    griddep_wait();
-    __shared__ float red[8][32];
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const long long col = (long long)blockIdx.x * 32 + lane;
-    float acc = 0.0f;
-    if (col < cols)
-        for (int s = warp; s < slabs; s += 8) acc += partial[(long long)s * cols + col];
-    red[warp][lane] = acc;
+    __shared__ bool last;
+    if (!colsum_is_last_block(counters + blockIdx.x, (unsigned)slabs, &last)) return;
+    // warps 0-7 add the slabs (warp w: w, w + 8, ...), then the eight sums are added in warp order
+    if (ty < 8) {
+        float t = 0.0f;
+        if (col < cols)
+            for (int sl = ty; sl < slabs; sl += 8) t += __ldcg(partial + (long long)sl * cols + col);
+        part[ty][tx] = t;
+    }
     __syncthreads();
-    if (warp == 0 && col < cols) {
+    if (ty == 0 && col < cols) {
         float t = 0.0f;
 #pragma unroll
-        for (int w = 0; w < 8; ++w) t += red[w][lane];
-        out[col] = t;
+        for (int w = 0; w < 8; ++w) t += part[w][tx];
+        out[col] = accumulate ? out[col] + t : t;
     }
 }
-
 // Slab sums with 16-byte loads (cols and ld multiples of 4, 16-byte aligned base): a block owns 128 columns, its eight
 // warps stride the rows of the slab four rows at a time (16 KB of loads in flight per block), every lane keeps four
 // column sums; the warps' sums are added in warp order through shared memory.
 __global__ void __launch_bounds__(256) colsum_slab_vec4_kernel(const float* __restrict__ in, long long rows, long long cols,
-                                                               long long ld, long long rows_per_slab, float* __restrict__ partial) {
+                                                               long long ld, long long rows_per_slab, float* __restrict__ partial,
+                                                               int slabs, unsigned* counters, float* out, int accumulate) {
     griddep_wait();
     __shared__ float4 red[8][32];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -302,6 +315,31 @@ __global__ void __launch_bounds__(256) colsum_slab_vec4_kernel(const float* __re
             t.x += x.x; t.y += x.y; t.z += x.z; t.w += x.w;
         }
         *reinterpret_cast<float4*>(partial + (long long)blockIdx.y * cols + col) = t;
+    }
+    __shared__ bool last;
+    if (!colsum_is_last_block(counters + blockIdx.x, (unsigned)slabs, &last)) return;
+    float4 s4 = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (col < cols)
+        for (int sl = warp; sl < slabs; sl += 8) {
+            const float4 x = __ldcg(reinterpret_cast<const float4*>(partial + (long long)sl * cols + col));
+            s4.x += x.x; s4.y += x.y; s4.z += x.z; s4.w += x.w;
+        }
+    __syncthreads();                 // red[] is reused
+    red[warp][lane] = s4;
+    __syncthreads();
+    if (warp == 0 && col < cols) {
+        float4 t = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int w = 0; w < 8; ++w) {
+            const float4 x = red[w][lane];
+            t.x += x.x; t.y += x.y; t.z += x.z; t.w += x.w;
+        }
+        float4* o = reinterpret_cast<float4*>(out + col);
+        if (accumulate) {
+            const float4 prev = *o;
+            t.x += prev.x; t.y += prev.y; t.z += prev.z; t.w += prev.w;
+        }
+        *o = t;
     }
 }
 
@@ -375,11 +413,13 @@ int launch_gelu_backward(te_b200_ctx* ctx, const float* x, const float* dy, floa
     return TE_OK;
 }
 
-int launch_colsum(te_b200_ctx* ctx, const float* in, int64_t rows, int64_t cols, int64_t ld, float* out,
+int launch_colsum(te_b200_ctx* ctx, const float* in, int64_t rows, int64_t cols, int64_t ld, float* out, bool accumulate,
                   cudaStream_t st) {
     if (cols == 0) return TE_OK;
     dim3 block(32, 32);
-    const bool vec = (cols & 3) == 0 && (ld & 3) == 0 && (reinterpret_cast<uintptr_t>(in) & 15) == 0 && rows >= 512;
+    unsigned* counters = reinterpret_cast<unsigned*>(ctx->d_status) + STATUS_COUNTER_WORD;
+    const bool vec = (cols & 3) == 0 && (ld & 3) == 0 && (reinterpret_cast<uintptr_t>(in) & 15) == 0 &&
+                     (reinterpret_cast<uintptr_t>(out) & 15) == 0 && rows >= 512;
     if (vec) {
         // enough (column block, row slab) pairs for ~4 blocks per SM, at least 64 rows per slab
         const long long cb = (cols + 127) / 128;
@@ -387,15 +427,15 @@ int launch_colsum(te_b200_ctx* ctx, const float* in, int64_t rows, int64_t cols,
         if (slabs > rows / 64) slabs = rows / 64;
         if (slabs < 1) slabs = 1;
         if (slabs > 65535) slabs = 65535;
-        if ((size_t)(slabs * cols * 4) <= ctx->workspace_bytes) {
+        if ((size_t)(slabs * cols * 4) <= ctx->workspace_bytes && cb <= STATUS_COUNTER_WORDS) {
             const long long rows_per_slab = (rows + slabs - 1) / slabs;
             slabs = (rows + rows_per_slab - 1) / rows_per_slab;
             float* partial = static_cast<float*>(ctx->workspace);
-            launch_pdl(colsum_slab_vec4_kernel, dim3((unsigned)cb, (unsigned)slabs), dim3(256), 0, st, in, rows, cols, ld, rows_per_slab, partial);
-            launch_pdl(colsum_finish_kernel, dim3((unsigned)((cols + 31) / 32)), dim3(256), 0, st, partial, (int)slabs, cols, out);
+            launch_pdl(colsum_slab_vec4_kernel, dim3((unsigned)cb, (unsigned)slabs), dim3(256), 0, st, in, rows, cols, ld,
+                       rows_per_slab, partial, (int)slabs, counters, out, accumulate ? 1 : 0);
             cudaError_t ev = cudaGetLastError();
             if (ev != cudaSuccess) return cuda_fail(ev, "colsum_slab_vec4_kernel launch");
-            ctx->launches += 2;
+            ctx->launches += 1;
             return TE_OK;
         }
     }
@@ -403,18 +443,19 @@ int launch_colsum(te_b200_ctx* ctx, const float* in, int64_t rows, int64_t cols,
     // enough (column block, row slab) pairs for ~4 blocks per SM, at least 256 rows per slab
     long long slabs = ((long long)ctx->sm_count * 4 + col_blocks - 1) / col_blocks;
     if (slabs > rows / 256) slabs = rows / 256;
-    if (slabs > 1 && (size_t)(slabs * cols * 4) <= ctx->workspace_bytes) {
+    if (slabs > 65535) slabs = 65535;
+    if (slabs > 1 && (size_t)(slabs * cols * 4) <= ctx->workspace_bytes && col_blocks <= STATUS_COUNTER_WORDS) {
         const long long rows_per_slab = (rows + slabs - 1) / slabs;
         slabs = (rows + rows_per_slab - 1) / rows_per_slab;
         float* partial = static_cast<float*>(ctx->workspace);
-        launch_pdl(colsum_slab_kernel, dim3(dim3((unsigned)col_blocks, (unsigned)slabs)), dim3(block), 0, st, in, rows, cols, ld, rows_per_slab, partial);
-        launch_pdl(colsum_finish_kernel, dim3((unsigned)((cols + 31) / 32)), dim3(256), 0, st, partial, (int)slabs, cols, out);
+        launch_pdl(colsum_slab_kernel, dim3(dim3((unsigned)col_blocks, (unsigned)slabs)), dim3(block), 0, st, in, rows, cols, ld,
+                   rows_per_slab, partial, (int)slabs, counters, out, accumulate ? 1 : 0);
         cudaError_t e2 = cudaGetLastError();
         if (e2 != cudaSuccess) return cuda_fail(e2, "colsum_slab_kernel launch");
-        ctx->launches += 2;
+        ctx->launches += 1;
         return TE_OK;
     }
-    launch_pdl(colsum_kernel, dim3((unsigned)col_blocks), dim3(block), 0, st, in, rows, cols, ld, out);
+    launch_pdl(colsum_kernel, dim3((unsigned)col_blocks), dim3(block), 0, st, in, rows, cols, ld, out, accumulate ? 1 : 0);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return cuda_fail(e, "colsum_kernel launch");
     ctx->launches += 1;

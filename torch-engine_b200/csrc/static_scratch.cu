@@ -8,14 +8,20 @@
 // breaks their accounting.
 //
 // What it does instead: the tf32 hi/lo planes that the 3xTF32 kernel reads are written into ONE fixed
-// array in device global memory that is part of this library's image.  Every GPU that loads the library
-// holds those TE_B200_STATIC_SCRATCH_BYTES until the process exits, whether or not this entry point is used.
-// Nothing here calls cudaMalloc, cudaFree, or any routine that allocates (no torch, no cuBLAS).
+// array in device global memory that is part of this library's image.  Nothing here calls cudaMalloc,
+// cudaFree, or any routine that allocates (no torch, no cuBLAS).  The array is not free, though: the CUDA
+// runtime loads a library's device code lazily, and loading the part that holds the array is what reserves
+// its TE_B200_STATIC_SCRATCH_BYTES (plus the code of the kernels) on that GPU, until the process exits.
+// That load happens inside the FIRST call on each device (or earlier, if the process runs with
+// CUDA_MODULE_LOADING=EAGER); it is the one moment at which this entry point needs free device memory,
+// and on a device that has none left it fails with TE_ERR_CUDA -- the next call tries again.
 //
 // Rules for the caller:
-//   * The first call on each device resolves the array's device address (cudaGetSymbolAddress with that
-//     device current), the driver's tensor-map encoder and the kernel attributes.  Make that first call
-//     outside any stream capture.
+//   * The first successful call on each device does all one-time work: it resolves the array's device
+//     address (cudaGetSymbolAddress with that device current), the driver's tensor-map encoder, and loads
+//     and configures every kernel any later problem shape can reach (both single-CTA tile widths, the
+//     CTA-pair form, the split-K reduction, the packing kernels).  Make that first call outside any
+//     stream capture; later calls, whatever their shape, do no first-use work.
 //   * All calls on one device share the array; it keeps whatever the previous call left.  Everything a call
 //     reads from it is rewritten by that call first (the planes by the packing pass, the status word by a
 //     memset on the stream), but two calls that overlap on the GPU (different streams) race on it.
@@ -37,43 +43,45 @@ namespace {
 constexpr int MAX_DEVICES = 16;
 
 struct DeviceSlot {
-    std::once_flag once;
-    int rc = TE_ERR_CUDA;          // result of the one-time set-up
+    std::mutex lock;
+    bool ready = false;            // set once the set-up has succeeded; a failed set-up is retried by the next call
     unsigned char* base = nullptr; // DEVICE address of g_static_scratch on this device
-    te_b200_ctx ctx;               // host-side bookkeeping only; nothing in it is allocated
+    te_b200_ctx ctx;               // host-side bookkeeping only; nothing in it is allocated on the device
 };
 DeviceSlot g_slots[MAX_DEVICES];
 
 inline int64_t round_up(int64_t x, int64_t a) { return (x + a - 1) / a * a; }
 
-void setup_device(int dev, DeviceSlot* slot) {
+int setup_device(int dev, DeviceSlot* slot) {
     cudaDeviceProp prop;
     cudaError_t e = cudaGetDeviceProperties(&prop, dev);
-    if (e != cudaSuccess) { slot->rc = te::cuda_fail(e, "cudaGetDeviceProperties"); return; }
+    if (e != cudaSuccess) return te::cuda_fail(e, "cudaGetDeviceProperties");
     if (prop.major != 10) {
         te::set_error("this backend is built for sm_100a only");
-        slot->rc = TE_ERR_NO_DEVICE;
-        return;
+        return TE_ERR_NO_DEVICE;
     }
     // In host code `g_static_scratch` names a host-side shadow, not device memory: ask the runtime for the
     // address the array has on the device that is current right now.
     void* dptr = nullptr;
     e = cudaGetSymbolAddress(&dptr, g_static_scratch);
-    if (e != cudaSuccess || !dptr) { slot->rc = te::cuda_fail(e, "cudaGetSymbolAddress(static scratch)"); return; }
+    if (e != cudaSuccess || !dptr) {
+        cudaGetLastError();
+        return te::cuda_fail(e, "cudaGetSymbolAddress(static scratch; loading it reserves the array on this device)");
+    }
     slot->base = static_cast<unsigned char*>(dptr);
     cudaDriverEntryPointQueryResult q;
     e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &slot->ctx.encode_tiled, cudaEnableDefault, &q);
     if (e != cudaSuccess || q != cudaDriverEntryPointSuccess || !slot->ctx.encode_tiled) {
         te::set_error("cuTensorMapEncodeTiled is not available from this driver");
-        slot->rc = TE_ERR_CUDA;
-        return;
+        return TE_ERR_CUDA;
     }
     slot->ctx.device = dev;
     slot->ctx.sm_count = prop.multiProcessorCount;
     slot->ctx.d_status = reinterpret_cast<int*>(slot->base);
     slot->ctx.workspace = slot->base + 256;
     slot->ctx.workspace_bytes = TE_B200_STATIC_SCRATCH_BYTES;
-    slot->rc = TE_OK;
+    // Load and configure every kernel a later call may launch, so that none of them does first-use work.
+    return te::prepare_3xtf32_kernels(&slot->ctx);
 }
 
 }  // namespace
@@ -94,7 +102,10 @@ extern "C" int te_b200_gemm_3xtf32_static(const te_gemm_desc* d, te_stream_t str
         set_error(msg);
         return TE_ERR_WORKSPACE;
     }
-    if (d->M == 0 || d->N == 0) return TE_OK;
+    if (d->M == 0 || d->N == 0) {
+        if (host_status) *host_status = 0;    // nothing was launched, so nothing can have timed out
+        return TE_OK;
+    }
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) {
@@ -107,8 +118,13 @@ extern "C" int te_b200_gemm_3xtf32_static(const te_gemm_desc* d, te_stream_t str
         return TE_ERR_BAD_ARGUMENT;
     }
     DeviceSlot* slot = &g_slots[dev];
-    std::call_once(slot->once, setup_device, dev, slot);
-    if (slot->rc) return slot->rc;
+    {
+        std::lock_guard<std::mutex> guard(slot->lock);
+        if (!slot->ready) {
+            if ((rc = setup_device(dev, slot))) return rc;     // not latched: the next call tries again
+            slot->ready = true;
+        }
+    }
     te_b200_ctx* ctx = &slot->ctx;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
 
@@ -123,7 +139,7 @@ extern "C" int te_b200_gemm_3xtf32_static(const te_gemm_desc* d, te_stream_t str
     g.b.ptr = d->b; g.b.mn_major = (d->b_major == TE_ROW_MAJOR); g.b.rows = d->N; g.b.ld = d->ldb;
     g.b.stride_inner = d->b_stride_inner; g.b.stride_outer = d->b_stride_outer;
     g.c = d->c; g.ldc = d->ldc; g.c_stride_inner = d->c_stride_inner; g.c_stride_outer = d->c_stride_outer;
-    g.preact = d->preact_out; g.bias = d->bias; g.alpha = d->alpha; g.scale_mode = d->scale_mode;
+    g.preact = d->preact_out; g.bias = d->bias; g.residual = d->residual; g.alpha = d->alpha; g.scale_mode = d->scale_mode;
     g.epilogue = d->epilogue;
 
     unsigned char* cursor = static_cast<unsigned char*>(ctx->workspace);

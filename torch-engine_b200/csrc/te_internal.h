@@ -3,6 +3,7 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 #include <string>
+#include <unordered_map>
 #include "te_b200.h"
 
 namespace te {
@@ -28,6 +29,7 @@ struct GemmProblem {
     int64_t ldc = 0, c_stride_inner = 0, c_stride_outer = 0;
     float* preact = nullptr;
     const float* bias = nullptr;
+    const float* residual = nullptr;   // optional, layout of c; added last; may alias c
     float alpha = 1.0f;
     int scale_mode = TE_SCALE_NONE;
     int epilogue = TE_EPI_NONE;
@@ -38,13 +40,31 @@ struct GemmProblem {
 
 }  // namespace te
 
+// One encoded tensor map and the arguments it was encoded from (context-local cache, see encode_tiled_cached).
+struct TensorMapCacheEntry {
+    uint64_t key[16];
+    unsigned char map[128];
+    bool valid = false;
+};
+
 struct te_b200_ctx {
     int device = 0;
     int sm_count = 0;
     void* workspace = nullptr;
     size_t workspace_bytes = 0;
-    int* d_status = nullptr;      // device word written by a kernel whose bounded wait gave up
+    // Device status area (STATUS_AREA_BYTES; the static-scratch entry point has the first 256 bytes only).  Word 0: code
+    // written by a kernel whose bounded wait gave up (or that met a bad index).  Bytes 8..15: the wait limit in
+    // nanoseconds every bounded wait reads on its slow path (0 = default).  Words STATUS_COUNTER_WORD..: arrival
+    // counters of the column-sum kernel, zero between launches.
+    int* d_status = nullptr;
     int64_t launches = 0;
+    uint64_t wait_limit_ns = 0;   // host copy of the limit stored in the status area (0 = default)
+    // Per-kernel one-time state of THIS context, keyed by the kernel's address: 1 once its attributes are set; for
+    // the CTA-pair kernels the number of pairs that can be resident at once.
+    std::unordered_map<const void*, int> kernel_state;
+    // Recently encoded tensor maps: a repeated step (same pointers, shapes and strides) skips the driver's encoder.
+    TensorMapCacheEntry tmap_cache[256];
+    int64_t tmap_hits = 0, tmap_misses = 0;
     void* encode_tiled = nullptr; // cuTensorMapEncodeTiled, resolved through the runtime
     void* host_stage = nullptr;   // grow-only device staging used by the host-buffer entry point
     size_t host_stage_bytes = 0;
@@ -59,11 +79,30 @@ namespace te {
 void set_error(const std::string& msg);
 int cuda_fail(cudaError_t e, const char* what);
 
+// cuTensorMapEncodeTiled for a 4-D fp32 tensor through the context's cache.  Returns the driver's CUresult (0 = ok).
+int encode_tiled_cached(te_b200_ctx* ctx, void* out_map, const void* ptr, const uint64_t dims[4], const uint64_t strides[3],
+                        const uint32_t box[4], int swizzle, int l2_promotion);
+
+constexpr int STATUS_AREA_BYTES = 8192;
+constexpr int STATUS_COUNTER_WORD = 16;
+constexpr int STATUS_COUNTER_WORDS = STATUS_AREA_BYTES / 4 - STATUS_COUNTER_WORD;
+
+// Device status codes that are not wait sites.
+constexpr int STATUS_BAD_EMBEDDING_INDEX = 201;   // "Embedding index out of range" (src/nn/embedding.cpp:53-55)
+constexpr int STATUS_BAD_TARGET_INDEX = 202;      // cross-entropy target outside [0, vocab)
+constexpr int STATUS_SELFTEST_WAIT = 901;         // the wait self-test's barrier, which nobody arrives at
+
 // True when TMA can address the operand in place (16-byte aligned base, strides multiple of 16 B).
 bool operand_tma_ok(const Operand& op, int64_t K, int64_t batch_inner, int64_t batch_outer);
 
 // gemm_sm100.cu
 int launch_gemm(te_b200_ctx* ctx, const GemmProblem& p, cudaStream_t stream);
+int launch_wait_selftest(te_b200_ctx* ctx, cudaStream_t stream);
+// Loads every kernel a 3xTF32 GEMM can reach (both single-CTA tile widths, the CTA-pair form, the split-K reduction,
+// the packing kernels) and sets their attributes in this context, so that no later call does first-use work.
+int prepare_3xtf32_kernels(te_b200_ctx* ctx);
+int prepare_pair_3xtf32_kernel(te_b200_ctx* ctx);   // gemm_sm100_2cta.cu
+int prepare_pack_kernels();                         // pack.cu
 // The kernel form launch_gemm picks: tile width, CTA-pair or single-CTA kernel, K splits.  Uses only the extents, the
 // precision (a_lo set or not), the scratch size of `p` and ctx->sm_count; touches no device.
 struct TileChoice { int bn; bool pair; int k_splits; };
@@ -86,14 +125,15 @@ int launch_softmax_backward_rows(te_b200_ctx*, const float* s, const float* dy, 
 int launch_gelu(te_b200_ctx*, const float*, float*, int64_t n, cudaStream_t);
 int launch_gelu_backward(te_b200_ctx*, const float* x, const float* dy, float* dx, int64_t n,
                          cudaStream_t);
-int launch_colsum(te_b200_ctx*, const float* in, int64_t rows, int64_t cols, int64_t ld, float* out,
+int launch_colsum(te_b200_ctx*, const float* in, int64_t rows, int64_t cols, int64_t ld, float* out, bool accumulate,
                   cudaStream_t);
 
 // norm_embed_loss.cu: the GPT step's kernels around the matmuls
 int launch_layernorm_forward(te_b200_ctx*, const float* x, const float* gamma, const float* beta, float* y, int64_t rows,
                              int64_t cols, float eps, cudaStream_t);
-int launch_layernorm_backward(te_b200_ctx*, const float* x, const float* gamma, const float* dy, float* dx, float* dgamma,
-                              float* dbeta, int64_t rows, int64_t cols, float eps, cudaStream_t);
+int launch_layernorm_backward(te_b200_ctx*, const float* x, const float* gamma, const float* dy, float* dx,
+                              const float* dx_residual, float* dgamma, float* dbeta, int64_t rows, int64_t cols, float eps,
+                              cudaStream_t);
 int launch_embedding_forward(te_b200_ctx*, const float* table, const int64_t* tokens, const float* pos, float* out, int64_t n,
                              int64_t T, int64_t D, int64_t vocab, cudaStream_t);
 int launch_embedding_backward(te_b200_ctx*, const int64_t* tokens, const float* dout, float* dtable, int64_t n, int64_t D,

@@ -2,126 +2,27 @@
 the optimizer): GPT::forward (src/nn/gpt.cpp:26-86) -> crossEntropyLoss::forward_batched
 (src/loss/CrossEntropyLoss.cpp:47-127) -> backward.
 
-Every matmul of the step runs on this backend through the C ABI:
-  * Linear forward / backward (src/nn/linear.cpp:14-23, src/core/grad_fn.cpp:93-139) as the fused calls
-    te_b200_linear_forward / te_b200_linear_backward, the FeedForward GELU (src/nn/ffn.cpp:12-16) in the epilogue;
-  * ScaledDot::forward (src/nn/scaledot.cpp:8-27) on the head views of MultiHeadAttention::forward
-    (src/nn/multi_head_attention.cpp:19-42, strides [T*E, hd, E, 1], no copies, no mask), and its backward
-    (MatMulBackward x2, DivBackward, SoftmaxBackward) as te_b200_attention_backward.
-The step's kernels around the matmuls run on the backend as well: token embedding with the positional sum
-(src/nn/embedding.cpp:18-60, src/nn/gpt.cpp:30-69), pre-LN LayerNorm forward / backward (src/nn/layernorm.cpp:19-82,
-src/core/grad_fn.cpp:405-538) and the mean cross-entropy with its gradient (src/loss/CrossEntropyLoss.cpp:47-127,
-src/core/grad_fn.cpp:271-346).  Residual adds, the head merge copy and gradient accumulation stay stock torch ops.
-Parameters come in GPT::parameters() order (src/nn/gpt.cpp:88-113).
+The step is an explicit schedule of C-ABI calls over buffers allocated once per configuration: nothing in it is a
+torch operator, torch only owns the memory.  Per pre-LN block (src/nn/transformer_block.cpp:15-35):
+
+  forward   LayerNorm -> te_b200_mha_forward (three projections, attention on head views, out projection, the block's
+            residual input added in the last GEMM's epilogue) -> LayerNorm -> Linear+GELU (pre-activation kept) ->
+            Linear with the second residual in its epilogue;
+  backward  te_b200_linear_backward_ex twice (the first hands back the gradient of the GELU's pre-activation),
+            te_b200_layernorm_backward_ex (adds the gradient that bypasses the LayerNorm over the residual branch),
+            te_b200_mha_backward, te_b200_layernorm_backward_ex.
+
+Every parameter is used once per step, so each gradient is written once, straight into its slice of one flat
+gradient vector in GPT::parameters() order (src/nn/gpt.cpp:88-113): no accumulation pass and no concatenation.
+Token embedding with the positional sum (src/nn/embedding.cpp:18-60, src/nn/gpt.cpp:30-69), the mean cross-entropy with
+its gradient and the embedding gradient are backend kernels as well.
 """
+import ctypes as C
 
 import torch
 
-
-class _Linear(torch.autograd.Function):
-    @staticmethod
-    def forward(ctx, x, w, b, be, prec, gelu):
-        if gelu:
-            y, pre = be.linear_forward(x, w, b, gelu=True, want_preact=True, precision=prec)
-        else:
-            y, pre = be.linear_forward(x, w, b, precision=prec), None
-        ctx.save_for_backward(x, w, pre if pre is not None else x.new_empty(0))
-        ctx.be, ctx.prec, ctx.gelu = be, prec, gelu
-        return y
-
-    @staticmethod
-    def backward(ctx, dy):
-        x, w, pre = ctx.saved_tensors
-        be = ctx.be
-        dy = dy.contiguous()
-        if ctx.gelu:
-            dy = be.gelu_backward(pre, dy)       # GeluBackward consumes the pre-activation (grad_fn.cpp:169-204)
-        dx, dw, db = be.linear_backward(x, w, dy, precision=ctx.prec)
-        return dx, dw, db, None, None, None
-
-
-class _FeedForward(torch.autograd.Function):
-    """FeedForward::forward (src/nn/ffn.cpp:12-16): Linear -> GELU -> Linear.  Forward keeps the pre-activation of the
-    GELU; backward asks the second Linear for the gradient of that pre-activation directly (one call: dX product, then
-    GeluBackward in place)."""
-    @staticmethod
-    def forward(ctx, x, w1, c1, w2, c2, be, prec):
-        h, pre = be.linear_forward(x, w1, c1, gelu=True, want_preact=True, precision=prec)
-        y = be.linear_forward(h, w2, c2, precision=prec)
-        ctx.save_for_backward(x, w1, w2, h, pre)
-        ctx.be, ctx.prec = be, prec
-        return y
-
-    @staticmethod
-    def backward(ctx, dy):
-        x, w1, w2, h, pre = ctx.saved_tensors
-        be, prec = ctx.be, ctx.prec
-        dy = dy.contiguous()
-        d_pre, dw2, dc2 = be.linear_backward(h, w2, dy, precision=prec, gelu_preact=pre)
-        dx, dw1, dc1 = be.linear_backward(x, w1, d_pre, precision=prec)
-        return dx, dw1, dc1, dw2, dc2, None, None
-
-
-class _ScaledDot(torch.autograd.Function):
-    @staticmethod
-    def forward(ctx, q, k, v, be, prec):
-        o, p = be.scaled_dot(q, k, v, precision=prec, head_major_out=False)     # written as [B,T,H,hd]: the merge is a view
-        ctx.save_for_backward(q, k, v, p, o)
-        ctx.be, ctx.prec = be, prec
-        return o
-
-    @staticmethod
-    def backward(ctx, d_o):
-        q, k, v, p, o = ctx.saved_tensors
-        dq, dk, dv = ctx.be.scaled_dot_backward(q, k, v, p, d_o, o=o, precision=ctx.prec, head_major_out=False)
-        return dq, dk, dv, None, None
-
-
-class _LayerNorm(torch.autograd.Function):
-    @staticmethod
-    def forward(ctx, x, g, b, be, eps):
-        ctx.save_for_backward(x, g)
-        ctx.be, ctx.eps = be, eps
-        return be.layernorm(x, g, b, eps)
-
-    @staticmethod
-    def backward(ctx, dy):
-        x, g = ctx.saved_tensors
-        dx, dg, db = ctx.be.layernorm_backward(x, g, dy, ctx.eps)
-        return dx, dg, db, None, None
-
-
-class _Embedding(torch.autograd.Function):
-    @staticmethod
-    def forward(ctx, table, tokens, pos, be):
-        ctx.save_for_backward(tokens)
-        ctx.be, ctx.vocab = be, table.shape[0]
-        return be.embedding(table, tokens, pos)
-
-    @staticmethod
-    def backward(ctx, dout):
-        (tokens,) = ctx.saved_tensors
-        return ctx.be.embedding_backward(tokens, dout, ctx.vocab), None, None, None
-
-
-class _CrossEntropy(torch.autograd.Function):
-    """Loss and gradient come out of one pass over the logits; backward scales the stored gradient by the upstream
-    value (1 for a plain loss.backward())."""
-    @staticmethod
-    def forward(ctx, logits, targets, be):
-        loss, grad = be.cross_entropy(logits, targets)
-        ctx.save_for_backward(grad)
-        return loss.reshape(())
-
-    @staticmethod
-    def backward(ctx, upstream):
-        (grad,) = ctx.saved_tensors
-        return grad * upstream, None, None
-
-
-def linear(be, x, w, b, prec, gelu=False):
-    return _Linear.apply(x, w, b, be, prec, gelu)
-
+from . import lib as L
+from .ops import _prec
 
 _POS_TABLES = {}
 
@@ -144,61 +45,148 @@ def _positional_table(seq_len, d_model):
     return torch.where((torch.arange(d_model) % 2 == 0).unsqueeze(0), torch.sin(ang), torch.cos(ang))
 
 
-def layer_norm(be, x, g, b, eps=1e-5):
-    """LayerNorm::forward (src/nn/layernorm.cpp:19-77): biased variance, (x-mean)/sqrt(var+eps)*g+b."""
-    return _LayerNorm.apply(x, g, b, be, eps)
-
-
-def split_params(flat, vocab, E, n_layers, ff):
-    """Views of a flat parameter vector in GPT::parameters() order, as leaf tensors that require grad."""
+def param_shapes(vocab, E, n_layers, ff):
+    """Shapes of GPT::parameters() in order: token table, per block {ln1 g/b, q/k/v/out Linear w/b, ln2 g/b, ffn w1/b1/w2/b2},
+    final LayerNorm g/b, head w/b."""
     shapes = [(vocab, E)]
     for _ in range(n_layers):
         shapes += [(E,), (E,)] + [(E, E), (E,)] * 4 + [(E,), (E,)] + [(ff, E), (ff,), (E, ff), (E,)]
     shapes += [(E,), (E,), (vocab, E), (vocab,)]
-    out, off = [], 0
-    for s in shapes:
-        n = 1
-        for d in s:
-            n *= d
-        out.append(flat[off:off + n].view(s).detach().requires_grad_(True))     # a leaf over the same storage, no copy
-        off += n
-    assert off == flat.numel(), (off, flat.numel())
-    return out
+    return shapes
 
 
-def gpt_forward(be, params, tokens, E, H, n_layers, prec="tf32"):
-    """Logits [B, T, vocab] of the pre-LN, unmasked GPT of the reference."""
-    B, T = tokens.shape
-    hd = E // H
-    it = iter(params)
-    emb = next(it)
-    x = _Embedding.apply(emb, tokens, positional_table(T, E, tokens.device), be)   # gpt.cpp:29-68
-    for _ in range(n_layers):                                                     # transformer_block.cpp:15-35
-        g1, b1 = next(it), next(it)
-        wq, bq, wk, bk, wv, bv, wo, bo = (next(it) for _ in range(8))
-        g2, b2 = next(it), next(it)
-        w1, c1, w2, c2 = (next(it) for _ in range(4))
-        h = layer_norm(be, x, g1, b1)
-        heads = lambda t: t.view(B, T, H, hd).transpose(1, 2)                      # zero-copy head views
-        q, k, v = (heads(linear(be, h, w, b, prec)) for w, b in ((wq, bq), (wk, bk), (wv, bv)))
-        o = _ScaledDot.apply(q, k, v, be, prec)                                    # [B,H,T,hd]
-        o = o.transpose(1, 2).reshape(B, T, E)
-        x = x + linear(be, o, wo, bo, prec)
-        h = layer_norm(be, x, g2, b2)
-        x = x + _FeedForward.apply(h, w1, c1, w2, c2, be, prec)
-    gf, bf, wh, bh = (next(it) for _ in range(4))
-    return linear(be, layer_norm(be, x, gf, bf), wh, bh, prec)
+def _numel(shape):
+    n = 1
+    for d in shape:
+        n *= d
+    return n
+
+
+class GptStep:
+    """Buffers and call schedule of one forward + loss + backward for a fixed (model, batch, sequence) configuration."""
+
+    def __init__(self, be, vocab, E, H, n_layers, ff, B, T, prec="tf32"):
+        self.be, self.cfg = be, (vocab, E, H, n_layers, ff, B, T, prec)
+        self.prec = _prec(prec)
+        dev = be.torch_device
+        f32 = dict(dtype=torch.float32, device=dev)
+        self.shapes = param_shapes(vocab, E, n_layers, ff)
+        self.offsets, off = [], 0
+        for s in self.shapes:
+            self.offsets.append(off)
+            off += _numel(s)
+        self.n_params = off
+        self.grads = torch.empty(off, **f32)
+        bte = lambda: torch.empty(B, T, E, **f32)
+        self.x = [bte() for _ in range(n_layers + 1)]          # block inputs; x[0] is the embedding output
+        self.layers = []
+        for _ in range(n_layers):
+            self.layers.append(dict(h1=bte(), q=bte(), k=bte(), v=bte(), attn=bte(), y1=bte(), h2=bte(),
+                                    p=torch.empty(B, H, T, T, **f32), pre=torch.empty(B, T, ff, **f32),
+                                    f=torch.empty(B, T, ff, **f32)))
+        self.hf = bte()
+        self.logits = torch.empty(B, T, vocab, **f32)
+        self.dlogits = torch.empty(B, T, vocab, **f32)
+        self.loss = torch.empty(1, **f32)
+        # backward scratch
+        self.dxa, self.dxb, self.dh = bte(), bte(), bte()
+        self.dq, self.dk, self.dv, self.dattn = bte(), bte(), bte(), bte()
+        self.dpre = torch.empty(B, T, ff, **f32)
+        self.pos = positional_table(T, E, dev)
+
+    def _p(self, flat, i):
+        return flat.data_ptr() + 4 * self.offsets[i]
+
+    def _g(self, i):
+        return self.grads.data_ptr() + 4 * self.offsets[i]
+
+    def run(self, flat_params, tokens, targets):
+        """Returns (loss [1], logits [B,T,vocab], flat gradient); all three are buffers of this object."""
+        vocab, E, H, n_layers, ff, B, T, _ = self.cfg
+        be, lib, ctx, prec = self.be, self.be._lib, self.be._ctx, self.prec
+        st = be._stream()
+        rows = B * T
+        ptr = lambda t: C.c_void_p(t.data_ptr())
+        P = lambda i: C.c_void_p(self._p(flat_params, i))
+        G = lambda i: C.c_void_p(self._g(i))
+        eps = 1e-5
+        assert flat_params.numel() == self.n_params and flat_params.is_contiguous()
+        assert tokens.shape == (B, T) and tokens.dtype == torch.int64 and targets.dtype == torch.int64
+        tokens, targets = tokens.contiguous(), targets.contiguous()
+
+        # ---- forward ----------------------------------------------------------------------------------------
+        L.check(lib.te_b200_embedding_forward(ctx, P(0), ptr(tokens), ptr(self.pos), ptr(self.x[0]), rows, T, E, vocab, st))
+        for l, a in enumerate(self.layers):
+            i = 1 + 16 * l          # ln1 g,b | wq,bq,wk,bk,wv,bv,wo,bo | ln2 g,b | w1,c1,w2,c2
+            L.check(lib.te_b200_layernorm_forward(ctx, ptr(self.x[l]), P(i), P(i + 1), ptr(a["h1"]), rows, E, eps, st))
+            m = L.MhaDesc()
+            m.B, m.T, m.E, m.H = B, T, E, H
+            m.x = a["h1"].data_ptr()
+            for n, j in zip(("wq", "bq", "wk", "bk", "wv", "bv", "wo", "bo"), range(i + 2, i + 10)):
+                setattr(m, n, self._p(flat_params, j))
+            m.q, m.k, m.v, m.p, m.attn = (a[n].data_ptr() for n in ("q", "k", "v", "p", "attn"))
+            m.y, m.residual, m.precision = a["y1"].data_ptr(), self.x[l].data_ptr(), prec
+            L.check(lib.te_b200_mha_forward(ctx, C.byref(m), st))                       # y1 = x + MHA(LN1(x))
+            L.check(lib.te_b200_layernorm_forward(ctx, ptr(a["y1"]), P(i + 10), P(i + 11), ptr(a["h2"]), rows, E, eps, st))
+            L.check(lib.te_b200_linear_forward(ctx, ptr(a["h2"]), P(i + 12), P(i + 13), ptr(a["f"]), ptr(a["pre"]), rows, E, ff,
+                                               1, prec, st))                           # f = gelu(h2.W1^T + c1)
+            d = L.GemmDesc()                                                            # x' = y1 + f.W2^T + c2
+            d.M, d.N, d.K = rows, E, ff
+            d.a, d.lda, d.a_major = a["f"].data_ptr(), ff, L.TE_ROW_MAJOR
+            d.b, d.ldb, d.b_major = self._p(flat_params, i + 14), ff, L.TE_COL_MAJOR
+            d.c, d.ldc = self.x[l + 1].data_ptr(), E
+            d.batch_outer = d.batch_inner = 1
+            d.alpha, d.bias, d.epilogue = 1.0, self._p(flat_params, i + 15), L.TE_EPI_BIAS
+            d.residual, d.precision = a["y1"].data_ptr(), prec
+            L.check(lib.te_b200_gemm_f32(ctx, C.byref(d), st))
+        i = 1 + 16 * n_layers      # final ln g,b | head w,b
+        L.check(lib.te_b200_layernorm_forward(ctx, ptr(self.x[n_layers]), P(i), P(i + 1), ptr(self.hf), rows, E, eps, st))
+        L.check(lib.te_b200_linear_forward(ctx, ptr(self.hf), P(i + 2), P(i + 3), ptr(self.logits), None, rows, E, vocab, 0, prec, st))
+        L.check(lib.te_b200_cross_entropy(ctx, ptr(self.logits), ptr(targets), ptr(self.loss), ptr(self.dlogits), 1.0, rows,
+                                          vocab, st))                                  # mean over B*T, gradient in the same pass
+
+        # ---- backward ---------------------------------------------------------------------------------------
+        L.check(lib.te_b200_linear_backward_ex(ctx, ptr(self.hf), None, P(i + 2), ptr(self.dlogits), ptr(self.dh), None, G(i + 2),
+                                               G(i + 3), 0, rows, E, vocab, prec, st))
+        L.check(lib.te_b200_layernorm_backward_ex(ctx, ptr(self.x[n_layers]), P(i), ptr(self.dh), ptr(self.dxa), None, G(i),
+                                                  G(i + 1), rows, E, eps, st))
+        for l in range(n_layers - 1, -1, -1):      # dxa holds the gradient of x[l+1]
+            a = self.layers[l]
+            i = 1 + 16 * l
+            L.check(lib.te_b200_linear_backward_ex(ctx, ptr(a["f"]), ptr(a["pre"]), P(i + 14), ptr(self.dxa), ptr(self.dpre), None,
+                                                   G(i + 14), G(i + 15), 0, rows, ff, E, prec, st))
+            L.check(lib.te_b200_linear_backward_ex(ctx, ptr(a["h2"]), None, P(i + 12), ptr(self.dpre), ptr(self.dh), None,
+                                                   G(i + 12), G(i + 13), 0, rows, E, ff, prec, st))
+            L.check(lib.te_b200_layernorm_backward_ex(ctx, ptr(a["y1"]), P(i + 10), ptr(self.dh), ptr(self.dxb), ptr(self.dxa),
+                                                      G(i + 10), G(i + 11), rows, E, eps, st))      # gradient of y1
+            m = L.MhaBwdDesc()
+            m.B, m.T, m.E, m.H = B, T, E, H
+            m.x = a["h1"].data_ptr()
+            m.wq, m.wk, m.wv, m.wo = (self._p(flat_params, j) for j in (i + 2, i + 4, i + 6, i + 8))
+            m.q, m.k, m.v, m.p, m.attn = (a[n].data_ptr() for n in ("q", "k", "v", "p", "attn"))
+            m.dy, m.dx, m.dx_residual = self.dxb.data_ptr(), self.dh.data_ptr(), None
+            for n, j in zip(("dwq", "dbq", "dwk", "dbk", "dwv", "dbv", "dwo", "dbo"), range(i + 2, i + 10)):
+                setattr(m, n, self._g(j))
+            m.dq, m.dk, m.dv, m.dattn = (t.data_ptr() for t in (self.dq, self.dk, self.dv, self.dattn))
+            m.accumulate, m.precision = 0, prec
+            L.check(lib.te_b200_mha_backward(ctx, C.byref(m), st))                     # gradient of LN1's output
+            L.check(lib.te_b200_layernorm_backward_ex(ctx, ptr(self.x[l]), P(i), ptr(self.dh), ptr(self.dxa), ptr(self.dxb), G(i),
+                                                      G(i + 1), rows, E, eps, st))                   # gradient of x[l]
+        L.check(lib.te_b200_embedding_backward(ctx, ptr(tokens), ptr(self.dxa), G(0), rows, E, vocab, st))
+        return self.loss, self.logits, self.grads
 
 
 def gpt_step(be, flat_params, tokens, targets, vocab, E, H, n_layers, ff, prec="tf32", grad_sync=None):
     """One forward + backward.  Returns (loss, logits, flat gradient in parameter order).  grad_sync, if given, is
     called with (flat gradient, token rows of this rank) before returning: the data-parallel exchange
-    (sharding.all_reduce_batch_mean_)."""
-    params = split_params(flat_params, vocab, E, n_layers, ff)
-    logits = gpt_forward(be, params, tokens, E, H, n_layers, prec)
-    loss = _CrossEntropy.apply(logits, targets, be)                                             # mean over B*T
-    loss.backward()
-    grads = torch.cat([p.grad.reshape(-1) for p in params])
+    (sharding.all_reduce_batch_mean_).  The buffers belong to a GptStep kept on the backend per configuration, so
+    the results of one call are overwritten by the next call with the same configuration."""
+    B, T = tokens.shape
+    key = (vocab, E, H, n_layers, ff, B, T, prec)
+    plans = be.__dict__.setdefault("_gpt_steps", {})
+    if key not in plans:
+        plans[key] = GptStep(be, vocab, E, H, n_layers, ff, B, T, prec)
+    loss, logits, grads = plans[key].run(flat_params, tokens, targets)
     if grad_sync is not None:
         grad_sync(grads, tokens.numel())
-    return loss.detach(), logits.detach(), grads
+    return loss.reshape(()), logits, grads

@@ -33,7 +33,7 @@ class GemmDesc(C.Structure):
         ("b_stride_outer", C.c_int64), ("b_stride_inner", C.c_int64),
         ("c_stride_outer", C.c_int64), ("c_stride_inner", C.c_int64),
         ("alpha", C.c_float), ("scale_mode", C.c_int32), ("epilogue", C.c_int32),
-        ("bias", C.c_void_p), ("preact_out", C.c_void_p),
+        ("bias", C.c_void_p), ("preact_out", C.c_void_p), ("residual", C.c_void_p),
         ("precision", C.c_int32), ("reserved", C.c_int32),
     ]
 
@@ -63,6 +63,21 @@ class AttnBwdDesc(C.Structure):
     ]
 
 
+class MhaDesc(C.Structure):
+    """struct te_mha_desc"""
+    _fields_ = [("B", C.c_int64), ("T", C.c_int64), ("E", C.c_int64), ("H", C.c_int64), ("x", C.c_void_p)] + \
+               [(n, C.c_void_p) for n in ("wq", "bq", "wk", "bk", "wv", "bv", "wo", "bo", "q", "k", "v", "p", "attn", "y",
+                                          "residual")] + [("precision", C.c_int32), ("reserved", C.c_int32)]
+
+
+class MhaBwdDesc(C.Structure):
+    """struct te_mha_bwd_desc"""
+    _fields_ = [("B", C.c_int64), ("T", C.c_int64), ("E", C.c_int64), ("H", C.c_int64)] + \
+               [(n, C.c_void_p) for n in ("x", "wq", "wk", "wv", "wo", "q", "k", "v", "p", "attn", "dy", "dx", "dx_residual",
+                                          "dwq", "dbq", "dwk", "dbk", "dwv", "dbv", "dwo", "dbo", "dq", "dk", "dv",
+                                          "dattn")] + [("accumulate", C.c_int32), ("precision", C.c_int32)]
+
+
 # name -> (restype, argtypes); every symbol include/te_b200.h declares
 SIGNATURES = {
     "te_b200_init": (C.c_int, [C.c_int, C.c_size_t, C.POINTER(C.c_void_p)]),
@@ -89,14 +104,28 @@ SIGNATURES = {
     "te_b200_linear_backward": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
                                           C.c_void_p, C.c_int64, C.c_int64, C.c_int64, C.c_int, C.c_void_p]),
     "te_b200_linear_backward_gelu": (C.c_int, [C.c_void_p] + [C.c_void_p] * 7 + [C.c_int64, C.c_int64, C.c_int64, C.c_int, C.c_void_p]),
+    "te_b200_linear_backward_ex": (C.c_int, [C.c_void_p] + [C.c_void_p] * 8 + [C.c_int, C.c_int64, C.c_int64, C.c_int64, C.c_int, C.c_void_p]),
+    "te_b200_mha_forward": (C.c_int, [C.c_void_p, C.POINTER(MhaDesc), C.c_void_p]),
+    "te_b200_mha_backward": (C.c_int, [C.c_void_p, C.POINTER(MhaBwdDesc), C.c_void_p]),
+    "te_b200_set_wait_limit_ns": (C.c_int, [C.c_void_p, C.c_uint64, C.c_void_p]),
+    "te_b200_selftest_wait_timeout": (C.c_int, [C.c_void_p, C.c_void_p]),
     "te_b200_gemm_plan": (C.c_int, [C.POINTER(GemmDesc), C.c_int, C.c_size_t, C.POINTER(C.c_int), C.POINTER(C.c_int), C.POINTER(C.c_int)]),
     "te_b200_attention_forward": (C.c_int, [C.c_void_p, C.POINTER(AttnDesc), C.c_void_p]),
     "te_b200_attention_backward": (C.c_int, [C.c_void_p, C.POINTER(AttnBwdDesc), C.c_void_p]),
     "te_b200_layernorm_forward": (C.c_int, [C.c_void_p] + [C.c_void_p] * 4 + [C.c_int64, C.c_int64, C.c_float, C.c_void_p]),
     "te_b200_layernorm_backward": (C.c_int, [C.c_void_p] + [C.c_void_p] * 6 + [C.c_int64, C.c_int64, C.c_float, C.c_void_p]),
+    "te_b200_layernorm_backward_ex": (C.c_int, [C.c_void_p] + [C.c_void_p] * 7 + [C.c_int64, C.c_int64, C.c_float, C.c_void_p]),
     "te_b200_embedding_forward": (C.c_int, [C.c_void_p] + [C.c_void_p] * 4 + [C.c_int64] * 4 + [C.c_void_p]),
     "te_b200_embedding_backward": (C.c_int, [C.c_void_p] + [C.c_void_p] * 3 + [C.c_int64] * 3 + [C.c_void_p]),
     "te_b200_cross_entropy": (C.c_int, [C.c_void_p] + [C.c_void_p] * 4 + [C.c_float, C.c_int64, C.c_int64, C.c_void_p]),
+    "te_b200_comm_unique_id": (C.c_int, [C.c_void_p]),
+    "te_b200_comm_init": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.POINTER(C.c_void_p)]),
+    "te_b200_comm_destroy": (C.c_int, [C.c_void_p]),
+    "te_b200_comm_rank": (C.c_int, [C.c_void_p, C.POINTER(C.c_int), C.POINTER(C.c_int)]),
+    "te_b200_all_gather_columns": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_int64, C.c_void_p, C.c_void_p,
+                                              C.c_int64, C.c_void_p]),
+    "te_b200_all_gather_rows": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_int64, C.c_void_p]),
+    "te_b200_gemm_f32_host_sharded": (C.c_int, [C.c_void_p, C.POINTER(GemmDesc), C.c_int64]),
     "te_b200_shard_range": (C.c_int, [C.c_int64, C.c_int, C.c_int, C.c_int64, c_i64_p, c_i64_p]),
 }
 

@@ -8,6 +8,8 @@ used only as device-memory holders (data_ptr, shape, stride) and for the current
     Backend.linear_backward MatMulBackward/AddBackward/TransposeBackward of that graph (src/core/grad_fn.cpp:93-139)
     Backend.scaled_dot      ScaledDot::forward                    (src/nn/scaledot.cpp:8-27)
     Backend.scaled_dot_backward  its backward graph                (src/core/grad_fn.cpp:126-156, :569-665)
+    Backend.mha_forward / mha_backward  MultiHeadAttention::forward and its backward graph
+                                                                  (src/nn/multi_head_attention.cpp:19-42)
     Backend.softmax / softmax_backward / gelu / gelu_backward / colsum: the kernels between the GEMMs.
     Backend.layernorm / layernorm_backward / embedding / embedding_backward / cross_entropy: the GPT step's kernels
         around the matmuls (src/nn/layernorm.cpp, src/nn/embedding.cpp, src/loss/CrossEntropyLoss.cpp).
@@ -83,6 +85,15 @@ class Backend:
         torch.cuda.synchronize(self.torch_device)
         L.check(self._lib.te_b200_check_device_status(self._ctx))
 
+    def set_wait_limit_ns(self, limit_ns):
+        """Bound of every device-side wait of kernels launched through this context from now on (0 = default, 2 s)."""
+        L.check(self._lib.te_b200_set_wait_limit_ns(self._ctx, int(limit_ns), self._stream()))
+
+    def selftest_wait_timeout(self):
+        """Launches the kernel whose bounded wait is meant to run out; check_device_status() then raises
+        BackendError with status TE_ERR_DEVICE_TIMEOUT."""
+        L.check(self._lib.te_b200_selftest_wait_timeout(self._ctx, self._stream()))
+
     # ------------------------------------------------------------------ GEMM
     def gemm(self, desc):
         """Raw strided-batched GEMM from a filled lib.GemmDesc."""
@@ -123,23 +134,81 @@ class Backend:
                                                  self._stream()))
         return (y, pre) if want_preact else y
 
-    def linear_backward(self, x, w, dy, precision="tf32", need_dx=True, need_dw=True, need_db=True, gelu_preact=None):
+    def linear_backward(self, x, w, dy, precision="tf32", need_dx=True, need_dw=True, need_db=True, gelu_preact=None,
+                        dx_residual=None, accumulate_into=None):
         """(dx, dw[out,in], db[out]) for y = x . w^T + b given dy.  With gelu_preact (x = gelu(gelu_preact), the second
-        Linear of FeedForward) dx is the gradient of that pre-activation: the dX product, then GeluBackward in place."""
-        self._check_f32_cuda(x, w, dy, gelu_preact)
+        Linear of FeedForward) dx is the gradient of that pre-activation: the dX product, then GeluBackward in place.
+        dx_residual ([rows, in]) is added into dx.  accumulate_into = (dw, db) adds the parameter gradients to those
+        tensors in place (and returns them) instead of writing fresh ones."""
+        self._check_f32_cuda(x, w, dy, gelu_preact, dx_residual)
         x = x.contiguous()
         dy = dy.contiguous()
         out_f, in_f = w.shape
         rows = x.numel() // in_f if in_f else 0
         dx = torch.empty_like(x) if need_dx else None
-        dw = torch.empty_like(w) if need_dw else None
-        db = torch.empty(out_f, dtype=torch.float32, device=x.device) if need_db else None
+        if accumulate_into is not None:
+            dw, db = accumulate_into
+            self._check_f32_cuda(dw, db)
+        else:
+            dw = torch.empty_like(w) if need_dw else None
+            db = torch.empty(out_f, dtype=torch.float32, device=x.device) if need_db else None
         if gelu_preact is not None and (gelu_preact.shape != x.shape or not gelu_preact.is_contiguous()):
             raise L.BackendError(L.TE_ERR_BAD_ARGUMENT, "gelu_preact must be contiguous and shaped like x")
-        L.check(self._lib.te_b200_linear_backward_gelu(self._ctx, _ptr(x), _ptr(gelu_preact), _ptr(w.contiguous()), _ptr(dy),
-                                                       _ptr(dx), _ptr(dw), _ptr(db), rows, in_f, out_f, _prec(precision),
-                                                       self._stream()))
+        if dx_residual is not None and (dx_residual.shape != x.shape or not dx_residual.is_contiguous()):
+            raise L.BackendError(L.TE_ERR_BAD_ARGUMENT, "dx_residual must be contiguous and shaped like x")
+        L.check(self._lib.te_b200_linear_backward_ex(self._ctx, _ptr(x), _ptr(gelu_preact), _ptr(w.contiguous()), _ptr(dy),
+                                                     _ptr(dx), _ptr(dx_residual), _ptr(dw), _ptr(db),
+                                                     int(accumulate_into is not None), rows, in_f, out_f, _prec(precision),
+                                                     self._stream()))
         return dx, dw, db
+
+    # ------------------------------------------------------------------ multi-head attention
+    def mha_forward(self, x, params, heads, residual=None, precision="tf32"):
+        """MultiHeadAttention::forward for x [B,T,E]; params in parameters() order (wq,bq,wk,bk,wv,bv,wo,bo).
+        Returns (y, saved) where saved holds what mha_backward needs."""
+        self._check_f32_cuda(x, residual, *params)
+        x = x.contiguous()
+        B, T, E = x.shape
+        new = lambda *shape: torch.empty(shape, dtype=torch.float32, device=x.device)
+        saved = dict(x=x, q=new(B, T, E), k=new(B, T, E), v=new(B, T, E), p=new(B, heads, T, T), attn=new(B, T, E),
+                     params=[t.contiguous() for t in params], heads=heads)
+        y = new(B, T, E)
+        m = L.MhaDesc()
+        m.B, m.T, m.E, m.H = B, T, E, heads
+        m.x = x.data_ptr()
+        for n, t in zip(("wq", "bq", "wk", "bk", "wv", "bv", "wo", "bo"), saved["params"]):
+            setattr(m, n, t.data_ptr())
+        for n in ("q", "k", "v", "p", "attn"):
+            setattr(m, n, saved[n].data_ptr())
+        m.y = y.data_ptr()
+        m.residual = residual.contiguous().data_ptr() if residual is not None else None
+        m.precision = _prec(precision)
+        L.check(self._lib.te_b200_mha_forward(self._ctx, C.byref(m), self._stream()))
+        return y, saved
+
+    def mha_backward(self, saved, dy, dx_residual=None, precision="tf32"):
+        """(dx, [dwq, dbq, dwk, dbk, dwv, dbv, dwo, dbo]) for the call that produced `saved`."""
+        self._check_f32_cuda(dy, dx_residual)
+        x = saved["x"]
+        dy = dy.contiguous()
+        B, T, E = x.shape
+        dx = torch.empty_like(x)
+        grads = [torch.empty_like(t) for t in saved["params"]]
+        scratch = [torch.empty_like(x) for _ in range(4)]
+        m = L.MhaBwdDesc()
+        m.B, m.T, m.E, m.H = B, T, E, saved["heads"]
+        m.x = x.data_ptr()
+        m.wq, m.wk, m.wv, m.wo = (saved["params"][i].data_ptr() for i in (0, 2, 4, 6))
+        for n in ("q", "k", "v", "p", "attn"):
+            setattr(m, n, saved[n].data_ptr())
+        m.dy, m.dx = dy.data_ptr(), dx.data_ptr()
+        m.dx_residual = dx_residual.contiguous().data_ptr() if dx_residual is not None else None
+        for n, t in zip(("dwq", "dbq", "dwk", "dbk", "dwv", "dbv", "dwo", "dbo"), grads):
+            setattr(m, n, t.data_ptr())
+        m.dq, m.dk, m.dv, m.dattn = (t.data_ptr() for t in scratch)
+        m.accumulate, m.precision = 0, _prec(precision)
+        L.check(self._lib.te_b200_mha_backward(self._ctx, C.byref(m), self._stream()))
+        return dx, grads
 
     # ------------------------------------------------------------------ attention
     def scaled_dot(self, q, k, v, precision="tf32", head_major_out=True):
@@ -220,17 +289,18 @@ class Backend:
                                                     _ptr(y), rows, cols, eps, self._stream()))
         return y
 
-    def layernorm_backward(self, x, gamma, dy, eps=1e-5):
-        """(dx, dgamma, dbeta) of LayerNormBackward::backward (src/core/grad_fn.cpp:405-538)."""
-        self._check_f32_cuda(x, gamma, dy)
+    def layernorm_backward(self, x, gamma, dy, eps=1e-5, dx_residual=None):
+        """(dx, dgamma, dbeta) of LayerNormBackward::backward (src/core/grad_fn.cpp:405-538); dx_residual is added to dx."""
+        self._check_f32_cuda(x, gamma, dy, dx_residual)
         x, dy = x.contiguous(), dy.contiguous()
         cols = x.shape[-1]
         rows = x.numel() // cols if cols else 0
         dx = torch.empty_like(x)
         dg = torch.empty(cols, dtype=torch.float32, device=x.device)
         db = torch.empty(cols, dtype=torch.float32, device=x.device)
-        L.check(self._lib.te_b200_layernorm_backward(self._ctx, _ptr(x), _ptr(gamma.contiguous()), _ptr(dy), _ptr(dx),
-                                                     _ptr(dg), _ptr(db), rows, cols, eps, self._stream()))
+        L.check(self._lib.te_b200_layernorm_backward_ex(self._ctx, _ptr(x), _ptr(gamma.contiguous()), _ptr(dy), _ptr(dx),
+                                                        _ptr(dx_residual.contiguous() if dx_residual is not None else None),
+                                                        _ptr(dg), _ptr(db), rows, cols, eps, self._stream()))
         return dx, dg, db
 
     def embedding(self, table, tokens, pos=None):

@@ -7,6 +7,8 @@ whole result on every rank is one all-gather issued (NCCL over NVLink on GPUs, g
 The reference has no multi-device code at all (its README lists distributed training as planned), so this
 layer has no counterpart there; it wraps whatever matmul callable it is given.
 """
+import ctypes as C
+
 import torch
 import torch.distributed as dist
 
@@ -78,3 +80,52 @@ def all_reduce_batch_mean_(grads, local_rows, group=None):
         dist.all_reduce(total, op=dist.ReduceOp.SUM, group=group)
         grads.div_(float(total.item()))
     return int(total.item())
+
+
+class Communicator:
+    """The library's own NCCL communicator for one rank (csrc/dist.cu): the all-gathers of the data plane and the
+    sharded host-buffer GEMM run through the C ABI, not through torch.  torch.distributed is used once, to hand rank 0's
+    communicator id to the other ranks."""
+
+    def __init__(self, backend, world, rank, group=None):
+        self.be, self.world, self.rank = backend, world, rank
+        self._lib = backend._lib
+        ident = torch.zeros(128, dtype=torch.uint8)
+        if rank == 0:
+            buf = (C.c_ubyte * 128)()
+            L.check(self._lib.te_b200_comm_unique_id(buf))
+            ident = torch.tensor(list(buf), dtype=torch.uint8)
+        if world > 1:
+            ident = ident.to(backend.torch_device) if dist.get_backend(group) == "nccl" else ident
+            dist.broadcast(ident, src=0, group=group)
+        raw = (C.c_ubyte * 128)(*ident.cpu().tolist())
+        h = C.c_void_p()
+        L.check(self._lib.te_b200_comm_init(backend._ctx, raw, world, rank, C.byref(h)))
+        self._comm = h
+
+    def close(self):
+        if getattr(self, "_comm", None):
+            self._lib.te_b200_comm_destroy(self._comm)
+            self._comm = None
+
+    def all_gather_columns(self, c_local, n_total, align=COLUMN_ALIGN, out=None, staging=None):
+        """[M, N] on every rank from the ranks' dense [M, n_r] column blocks: one NCCL all-gather + one re-tile kernel."""
+        M = c_local.shape[0]
+        c_local = c_local.contiguous()
+        out = out if out is not None else torch.empty(M, n_total, dtype=torch.float32, device=c_local.device)
+        staging = staging if staging is not None else torch.empty(M * n_total, dtype=torch.float32, device=c_local.device)
+        L.check(self._lib.te_b200_all_gather_columns(self._comm, C.c_void_p(c_local.data_ptr()), M, n_total, align,
+                                                     C.c_void_p(staging.data_ptr()), C.c_void_p(out.data_ptr()), out.stride(0),
+                                                     self.be._stream()))
+        return out
+
+    def all_gather_rows(self, full, align=1):
+        """In place: every rank filled its own row block of the dense [rows, cols] tensor `full`."""
+        rows = full.shape[0]
+        cols = full.numel() // rows if rows else 0
+        L.check(self._lib.te_b200_all_gather_rows(self._comm, C.c_void_p(full.data_ptr()), rows, cols, align, self.be._stream()))
+        return full
+
+    def gemm_host_sharded(self, desc, align=COLUMN_ALIGN):
+        """te_b200_gemm_f32_host_sharded on a descriptor holding HOST pointers; collective."""
+        L.check(self._lib.te_b200_gemm_f32_host_sharded(self._comm, C.byref(desc), align))
