@@ -1,7 +1,8 @@
 """The GPT training-step caller with every matmul on the CUDA backend, against the reference's own CPU step.
 Tiny configuration: full logits and all gradients from tests/golden/gpt_tiny.npz.  Benchmark configuration 4
-(6 layers, d_model 384, 6 heads, context 256, vocab 65, batch 64): loss, norms and sampled entries from
-tests/golden/gpt_c4.npz (one reference CPU run, tests/golden/make_golden_c4.py)."""
+(6 layers, d_model 384, 6 heads, context 256, vocab 65, batch 64): loss, norms and sampled entries of every gradient from
+tests/golden/gpt_c4.npz, and the COMPLETE gradient tensors of the token embedding, the final LayerNorm, the head and block 2
+from tests/golden/gpt_c4_full.npz (one reference CPU run of 12 minutes, tests/golden/make_golden_c4.py)."""
 import os
 
 import numpy as np
@@ -86,3 +87,13 @@ def test_config4_gpt_step_matches_reference(backend, prec):
         norm = np.linalg.norm(seg.astype(np.float64))
         assert abs(norm - g["grad_norm"][t]) <= GRAD_TOL[prec] * max(g["grad_norm"][t], floor * np.sqrt(size)), f"gradient norm {t}"
         off += size
+    # complete tensors: embedding, block 2 (LayerNorms, query / output projections, every bias, 32 rows of the second
+    # FeedForward weight), final LayerNorm and head
+    full = np.load(os.path.join(GOLD, "gpt_c4_full.npz"))
+    starts = np.concatenate([[0], np.cumsum([size for size, _ in layout])])
+    for t in full["tensors"].tolist():
+        want = full["grad_%d" % t]
+        first = int(full["first_%d" % t])
+        got = gr[starts[t] + first:starts[t] + first + want.size]
+        scale = max(float(g["grad_absmax"][t]), floor)
+        assert np.abs(got - want).max() <= GRAD_TOL[prec] * scale, f"complete gradient tensor {t}"

@@ -287,7 +287,7 @@ attention_bwd_tf32_kernel(const __grid_constant__ CUtensorMap tm_v, const __grid
         int s = 0, jc = 0, tc = 0;
         bool ok = true;
         EpilogueRow er;
-        er.c_row = nullptr; er.pre_row = nullptr; er.row_ok = true; er.vec_ok = false; er.tma_ok = true;
+        er.c_row = nullptr; er.pre_row = nullptr; er.res_row = nullptr; er.row_ok = true; er.vec_ok = false; er.tma_ok = true; er.sector_ok = false;
         er.tm_c = nullptr; er.tm_pre = nullptr;
         int stores = 0;
         for (int t = blockIdx.x; t < p.total_tiles && ok; t += gridDim.x, ++tc) {

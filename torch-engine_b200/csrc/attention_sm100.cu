@@ -256,7 +256,7 @@ attention_tf32_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
             tmem_ld_wait();
             const float inv_sum = 1.0f / sum;
             EpilogueRow er;
-            er.c_row = nullptr; er.pre_row = nullptr; er.row_ok = true; er.vec_ok = false; er.tma_ok = true;
+            er.c_row = nullptr; er.pre_row = nullptr; er.res_row = nullptr; er.row_ok = true; er.vec_ok = false; er.tma_ok = true; er.sector_ok = false;
             er.stage = stage_smem + warp * 2 * EPI_STAGE_BYTES;
             er.tm_c = &tm_p; er.tm_pre = &tm_p;
             er.row0 = q0 + quad * 32;

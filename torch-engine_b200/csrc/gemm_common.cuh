@@ -33,6 +33,14 @@ enum : int {  // where a bounded wait gave up (stored in the device status word)
     WAIT_TEARDOWN = 105
 };
 
+// How an epilogue thread's 32 consecutive columns of one row reach global memory.
+//   STORE_DIRECT  16-byte or scalar stores: any leading dimension, alignment and ragged N;
+//   STORE_TMA     the warp's 32 x 32 block is staged in shared memory and leaves as one TMA tensor store;
+//   STORE_SECTOR  each thread writes its row piece with 32-byte stores (st.global.v8.f32), one whole L2 sector per
+//                 store: no shared-memory staging, no proxy fence, no wait for a staging tile to drain.  Needs 32-byte
+//                 aligned rows (base, ldc and batch strides multiples of 8 floats) and N a multiple of 8.
+enum : int { STORE_DIRECT = 0, STORE_TMA = 1, STORE_SECTOR = 2 };
+
 // Epilogue forms a GEMM kernel is compiled for.  The bare product (EPI_PLAIN) and the residual form are separate
 // instances because epilogue code that is present but not taken still costs registers and drain time on products
 // whose epilogue is not hidden behind a long main loop.
@@ -52,7 +60,7 @@ struct GemmParams {
     int scale_mode;
     int epilogue;
     int* status;
-    int tma_store;   // 1: outputs go through shared memory and TMA stores
+    int tma_store;   // how outputs leave: STORE_DIRECT (any layout), STORE_TMA (staged in shared memory), STORE_SECTOR
     // Split K: every output tile is computed by k_splits work units, each over kb_per_split k-blocks, each writing
     // its partial tile to slice `split` of a scratch buffer (split_stride elements apart); a reduction kernel adds
     // the slices in order and applies the epilogue.  k_splits == 1: no scratch, kb_per_split = all k-blocks.
@@ -139,6 +147,7 @@ struct EpilogueRow {
     const float* res_row;   // same row of the optional residual input
     bool row_ok;       // row < M
     bool vec_ok;       // 16-byte stores are legal
+    bool sector_ok;    // STORE_SECTOR: 32-byte stores straight from registers
     // TMA-store path (used when the output can be described by a tensor map)
     bool tma_ok;
     uint32_t stage;            // this warp's staging tile in shared memory
@@ -173,6 +182,26 @@ __device__ __forceinline__ void stage_and_store32(const float* v, int col0, cons
     if (lane == 0) {
         tma_store_4d(tm, stage, col0, er.row0, er.bi, er.bo);
         bulk_commit_group();
+    }
+}
+
+// 32 consecutive floats of one row, 32-byte aligned, as whole sectors; `left` = columns up to N (a multiple of 8).
+__device__ __forceinline__ void store_row32_sectors(float* dst, const float* v, int left) {
+#pragma unroll
+    for (int j = 0; j < 32; j += 8) {
+        if (j < left)
+            asm volatile("st.global.v8.f32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(dst + j), "f"(v[j]), "f"(v[j + 1]),
+                         "f"(v[j + 2]), "f"(v[j + 3]), "f"(v[j + 4]), "f"(v[j + 5]), "f"(v[j + 6]), "f"(v[j + 7])
+                         : "memory");
+    }
+}
+
+// The bare product's way out: sector stores from registers, or the staged TMA store.
+__device__ __forceinline__ void plain_store32(const float* v, int col0, const EpilogueRow& er, const GemmParams& p, int lane) {
+    if (er.sector_ok) {
+        if (er.row_ok) store_row32_sectors(er.c_row + col0, v, p.N - col0);
+    } else if (er.row0 < p.M) {
+        stage_and_store32(v, col0, er, er.tm_c, lane);
     }
 }
 
@@ -213,6 +242,20 @@ __device__ __forceinline__ void epilogue_store32(float* v, int col0, const Epilo
         const float mine = (col0 + lane < p.N) ? __ldg(p.bias + col0 + lane) : 0.0f;
 #pragma unroll
         for (int j = 0; j < 32; ++j) v[j] += __shfl_sync(0xffffffffu, mine, j);
+    }
+    if (er.sector_ok) {   // warp-uniform
+        if (!er.row_ok) return;
+        if (er.pre_row) store_row32_sectors(er.pre_row + col0, v, p.N - col0);
+        if (p.epilogue == TE_EPI_BIAS_GELU) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = gelu_tanh(v[j]);
+        }
+        if constexpr (RES) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] += res[j];
+        }
+        store_row32_sectors(er.c_row + col0, v, p.N - col0);
+        return;
     }
     if (er.tma_ok) {   // warp-uniform
         if (er.row0 >= p.M) return;   // nothing of this warp's 32 rows exists: issue no store at all
@@ -268,6 +311,8 @@ int make_operand_map(te_b200_ctx* ctx, CUtensorMap* out, const float* ptr, const
 // output) for the TMA-store epilogue.  Returns false when the output cannot be described (odd ldc, misaligned base);
 // the kernels then store directly.
 bool make_output_maps(te_b200_ctx* ctx, const GemmProblem& g, int k_splits, CUtensorMap* tm_c, CUtensorMap* tm_pre);
+// Host: the store mode for this output (fills the tensor maps when it is STORE_TMA; they are valid dummies otherwise).
+int choose_store_mode(te_b200_ctx* ctx, const GemmProblem& g, int k_splits, CUtensorMap* tm_c, CUtensorMap* tm_pre);
 // Fills the kernel parameters that do not depend on the tile shape.
 void fill_common_params(GemmParams& p, const te_b200_ctx* ctx, const GemmProblem& g);
 

@@ -265,7 +265,8 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
             er.vec_ok = ((p.ldc & 3) == 0) && ((reinterpret_cast<uintptr_t>(p.c + batch_off) & 15) == 0) &&
                         (!p.preact || (reinterpret_cast<uintptr_t>(p.preact + batch_off) & 15) == 0) &&
                         (!p.residual || (reinterpret_cast<uintptr_t>(p.residual + batch_off) & 15) == 0);
-            er.tma_ok = p.tma_store != 0;
+            er.tma_ok = p.tma_store == STORE_TMA;
+            er.sector_ok = p.tma_store == STORE_SECTOR;
             er.stage = epi_stage + warp * EPI_STAGE_BYTES;
             er.tm_c = &tm_c;
             er.tm_pre = &tm_pre;
@@ -312,7 +313,7 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                         const int col0 = nh + cc * 32;
                         if (col0 < p.N) {
                             if constexpr (EPI == EPI_PLAIN) {
-                                if (er.row0 < p.M) stage_and_store32(&acc[cc * 32], col0, er, er.tm_c, lane);
+                                plain_store32(&acc[cc * 32], col0, er, p, lane);
                             } else {
                                 epilogue_store32<EPI == EPI_RESIDUAL>(&acc[cc * 32], col0, er, p, lane);
                             }
@@ -338,7 +339,7 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
 #pragma unroll
                     for (int j = 0; j < 32; ++j) v[j] = p.K > 0 ? __uint_as_float(r[j]) : 0.0f;
                     if constexpr (EPI == EPI_PLAIN) {
-                        if (er.row0 < p.M) stage_and_store32(v, col0, er, er.tm_c, lane);
+                        plain_store32(v, col0, er, p, lane);
                     } else {
                         epilogue_store32<EPI == EPI_RESIDUAL>(v, col0, er, p, lane);
                     }
@@ -470,6 +471,32 @@ bool make_output_maps(te_b200_ctx* ctx, const GemmProblem& g, int k_splits, CUte
         *tm_pre = *tm_c;
     }
     return true;
+}
+
+// 32-byte stores need every row start on a sector boundary.
+static bool sector_store_ok(const GemmProblem& g, int k_splits) {
+    auto ok_ptr = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 31) == 0; };
+    if ((g.N & 7) || !ok_ptr(g.c) || (g.preact && !ok_ptr(g.preact))) return false;
+    if (g.M > 1 && (g.ldc & 7)) return false;
+    if (g.batch_inner > 1 && (g.c_stride_inner & 7)) return false;
+    if (g.batch_outer * k_splits > 1 && (g.c_stride_outer & 7)) return false;
+    return true;
+}
+
+#ifndef TE_PREFER_SECTOR_STORES
+#define TE_PREFER_SECTOR_STORES 0
+#endif
+
+int choose_store_mode(te_b200_ctx* ctx, const GemmProblem& g, int k_splits, CUtensorMap* tm_c, CUtensorMap* tm_pre) {
+    const bool tma = make_output_maps(ctx, g, k_splits, tm_c, tm_pre);
+    const bool sector = sector_store_ok(g, k_splits);
+    if (!tma) {
+        // the kernels take tensor maps as parameters whether they use them or not
+        memset(tm_c, 0, sizeof(CUtensorMap));
+        memset(tm_pre, 0, sizeof(CUtensorMap));
+    }
+    if (sector && (TE_PREFER_SECTOR_STORES || !tma)) return STORE_SECTOR;
+    return tma ? STORE_TMA : STORE_DIRECT;
 }
 
 void fill_common_params(GemmParams& p, const te_b200_ctx* ctx, const GemmProblem& g) {
@@ -610,7 +637,7 @@ static int launch_variant(te_b200_ctx* ctx, const GemmProblem& g_in, int k_split
     fill_common_params(p, ctx, g);
     prepare_split(g_in, k_splits, g, p);       // with k_splits > 1 the kernel writes raw partial tiles to scratch
     CUtensorMap mc, mpre;
-    p.tma_store = make_output_maps(ctx, g, k_splits, &mc, &mpre) ? 1 : 0;
+    p.tma_store = choose_store_mode(ctx, g, k_splits, &mc, &mpre);
     p.tiles_m = (int)((g.M + BM - 1) / BM);
     p.tiles_n = (int)((g.N + BN - 1) / BN);
     const long long total = (long long)p.tiles_m * p.tiles_n * p.num_batches * k_splits;

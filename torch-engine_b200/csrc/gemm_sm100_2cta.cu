@@ -278,7 +278,8 @@ gemm_tf32_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
             er.vec_ok = ((p.ldc & 3) == 0) && ((reinterpret_cast<uintptr_t>(p.c + batch_off) & 15) == 0) &&
                         (!p.preact || (reinterpret_cast<uintptr_t>(p.preact + batch_off) & 15) == 0) &&
                         (!p.residual || (reinterpret_cast<uintptr_t>(p.residual + batch_off) & 15) == 0);
-            er.tma_ok = p.tma_store != 0;
+            er.tma_ok = p.tma_store == STORE_TMA;
+            er.sector_ok = p.tma_store == STORE_SECTOR;
             er.stage = epi_stage + warp * EPI_STAGE_BYTES;
             er.tm_c = &tm_c;
             er.tm_pre = &tm_pre;
@@ -323,7 +324,7 @@ gemm_tf32_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
                         const int col0 = nh + cc * 32;
                         if (col0 < p.N) {
                             if constexpr (EPI == EPI_PLAIN) {
-                                if (er.row0 < p.M) stage_and_store32(&acc[cc * 32], col0, er, er.tm_c, lane);
+                                plain_store32(&acc[cc * 32], col0, er, p, lane);
                             } else {
                                 epilogue_store32<EPI == EPI_RESIDUAL>(&acc[cc * 32], col0, er, p, lane);
                             }
@@ -349,7 +350,7 @@ gemm_tf32_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
 #pragma unroll
                     for (int j = 0; j < 32; ++j) v[j] = p.K > 0 ? __uint_as_float(r[j]) : 0.0f;
                     if constexpr (EPI == EPI_PLAIN) {
-                        if (er.row0 < p.M) stage_and_store32(v, col0, er, er.tm_c, lane);
+                        plain_store32(v, col0, er, p, lane);
                     } else {
                         epilogue_store32<EPI == EPI_RESIDUAL>(v, col0, er, p, lane);
                     }
@@ -454,7 +455,7 @@ static int launch_pair_impl(te_b200_ctx* ctx, const GemmProblem& g_in, int k_spl
     fill_common_params(p, ctx, g);
     prepare_split(g_in, k_splits, g, p);       // with k_splits > 1 the kernel writes raw partial tiles to scratch
     CUtensorMap mc, mpre;
-    p.tma_store = make_output_maps(ctx, g, k_splits, &mc, &mpre) ? 1 : 0;
+    p.tma_store = choose_store_mode(ctx, g, k_splits, &mc, &mpre);
     if (EPI == EPI_PLAIN && !p.tma_store) {
         set_error("internal: the bare-product kernel was chosen for an output no tensor map describes");
         return TE_ERR_BAD_ARGUMENT;
