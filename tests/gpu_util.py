@@ -29,3 +29,11 @@ def elementwise_rel_err(c, ref, floor=1e-2):
     if not mask.any():
         return 0.0
     return float((np.abs(c - ref)[mask] / np.abs(ref)[mask]).max())
+
+
+def rel_err_floored(c, ref, floor):
+    """rel_err with the scale floored: for gradients that are zero in exact arithmetic (the key-projection bias of an
+    attention layer: softmax ignores a constant added to every key score) and hold only rounding noise in any
+    implementation, the reference's included."""
+    ref = np.asarray(ref, dtype=np.float64)
+    return float(np.abs(np.asarray(c, dtype=np.float64) - ref).max() / max(float(np.abs(ref).max()), floor))

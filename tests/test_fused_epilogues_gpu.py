@@ -12,7 +12,7 @@ import torch
 
 from oracle import binding
 from tests import golden_cases as gc
-from tests.gpu_util import TOL_REL, rel_err
+from tests.gpu_util import TOL_REL, rel_err, rel_err_floored
 from torch_engine_b200 import lib as L
 
 pytestmark = pytest.mark.gpu
@@ -115,8 +115,12 @@ def test_multi_head_attention_goldens(backend, prec):
     assert rel_err(y.cpu().numpy(), gold["mha.y"]) <= ATTN_TOL[prec]
     dx, grads = backend.mha_backward(saved, dy, precision=prec)
     assert rel_err(dx.cpu().numpy(), gold["mha.dx"]) <= CHAIN_TOL[prec]
+    # the key-projection bias gradient is zero in exact arithmetic: what any implementation returns there is rounding
+    # noise of sums of O(1) terms, so it is measured against the scale of the other gradients
+    gmax = max(float(np.abs(gold[f"mha.dparam{i}"]).max()) for i in range(8))
     for i, g in enumerate(grads):
-        assert rel_err(g.cpu().numpy(), gold[f"mha.dparam{i}"]) <= CHAIN_TOL[prec], i
+        floor = gmax if float(np.abs(gold[f"mha.dparam{i}"]).max()) < 1e-3 * gmax else 0.0
+        assert rel_err_floored(g.cpu().numpy(), gold[f"mha.dparam{i}"], floor) <= CHAIN_TOL[prec], i
     # with the block's residual input and the gradient of the bypassing branch
     y2, saved2 = backend.mha_forward(x, params, m["H"], residual=x, precision=prec)
     assert rel_err((y2 - x).cpu().numpy(), gold["mha.y"]) <= ATTN_TOL[prec]

@@ -335,7 +335,11 @@ def test_launch_counter_moves(backend):
     backend.matmul(torch.ones(8, 8, device="cuda"), torch.ones(8, 8, device="cuda"))
     assert backend.launches == n0 + 1
     backend.matmul(torch.ones(8, 8, device="cuda"), torch.ones(8, 8, device="cuda"), precision="3xtf32")
-    assert backend.launches == n0 + 4      # two packing passes + the GEMM
+    assert backend.launches == n0 + 2      # the 3xTF32 mode splits hi / lo inside the kernel: one launch as well
+    big = torch.ones(256, 5120, device="cuda")
+    n1 = backend.launches
+    backend.matmul(big, big.t().contiguous(), precision="3xtf32")
+    assert backend.launches == n1 + 3      # long K, large M and N: the CTA-pair form behind two packing passes
 
 
 def test_pair_tiles_192_wide(backend, oracle):

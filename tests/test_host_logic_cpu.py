@@ -114,17 +114,22 @@ def test_descriptor_validation():
 def test_workspace_sizing():
     # aligned operands in TF32 mode are read in place
     assert _ws(_desc()) == (L.TE_OK, 0)
-    # 3xTF32 packs hi+lo planes of both operands: 2 * 2 * 64*64*4 bytes
-    assert _ws(_desc(precision=L.TE_PREC_3XTF32)) == (L.TE_OK, 4 * 64 * 64 * 4)
+    # 3xTF32 splits hi / lo inside the kernel: no plane storage ...
+    assert _ws(_desc(precision=L.TE_PREC_3XTF32)) == (L.TE_OK, 0)
+    # ... except where the CTA-pair form can be chosen (M, N > 128 and K >= 5120), which reads packed hi+lo planes of
+    # both operands: 2 * 2 * 256*5120*4 bytes
+    big = dict(M=256, N=256, K=5120, lda=5120, ldb=256, ldc=256, precision=L.TE_PREC_3XTF32)
+    assert _ws(_desc(**big)) == (L.TE_OK, 4 * 256 * 5120 * 4)
+    # an operand TMA cannot address is still copied once (not split) in 3xTF32 mode
+    assert _ws(_desc(M=64, K=65, N=64, lda=65, ldb=64, precision=L.TE_PREC_3XTF32))[1] == 64 * 68 * 4
     # a leading dimension that is not a multiple of 4 floats cannot be addressed by TMA -> one packed copy of A
     rc, n = _ws(_desc(M=64, K=65, N=64, lda=65, ldb=64))
     assert rc == L.TE_OK and n == 64 * 68 * 4
     # a misaligned base pointer likewise
     assert _ws(_desc(b=0x1004))[1] == 64 * 64 * 4
     # broadcast operands are packed once
-    rc, n = _ws(_desc(precision=L.TE_PREC_3XTF32, batch_inner=8, a_stride_inner=64 * 64, b_stride_inner=0,
-                      c_stride_inner=64 * 64))
-    assert n == 2 * (8 + 1) * 64 * 64 * 4
+    rc, n = _ws(_desc(batch_inner=8, a=0x1004, a_stride_inner=64 * 64, b=0x2004, b_stride_inner=0, c_stride_inner=64 * 64))
+    assert n == (8 + 1) * 64 * 64 * 4
     # empty problems need nothing
     assert _ws(_desc(M=0))[1] == 0
 

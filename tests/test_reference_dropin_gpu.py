@@ -23,7 +23,7 @@ import pytest
 
 from oracle import binding
 from tests import golden_cases as gc
-from tests.gpu_util import TOL_REL, elementwise_rel_err, rel_err
+from tests.gpu_util import TOL_REL, elementwise_rel_err, rel_err, rel_err_floored
 
 pytestmark = pytest.mark.gpu
 GOLD = os.path.join(os.path.dirname(__file__), "golden")
@@ -124,8 +124,12 @@ def test_scaled_dot_and_mha_through_reference_autograd(refcuda, nn_gold, prec, f
     r = refcuda.mha(m["x"], m["params"], m["H"], dy=m["dy"])
     assert rel_err(r["y"], nn_gold["mha.y"]) <= ATTN_TOL[prec]
     assert rel_err(r["dx"], nn_gold["mha.dx"]) <= CHAIN_TOL[prec]
+    # the key-projection bias gradient is zero in exact arithmetic: what any implementation returns there is rounding
+    # noise of sums of O(1) terms, so it is measured against the scale of the other gradients
+    gmax = max(float(np.abs(nn_gold[f"mha.dparam{i}"]).max()) for i in range(8))
     for i, g in enumerate(r["dparams"]):
-        assert rel_err(g, nn_gold[f"mha.dparam{i}"]) <= CHAIN_TOL[prec], i
+        floor = gmax if float(np.abs(nn_gold[f"mha.dparam{i}"]).max()) < 1e-3 * gmax else 0.0
+        assert rel_err_floored(g, nn_gold[f"mha.dparam{i}"], floor) <= CHAIN_TOL[prec], i
 
 
 @pytest.mark.parametrize("prec", PRECS)
@@ -142,10 +146,11 @@ def test_reference_gpt_step_with_every_matmul_on_b200(refcuda, prec):
     assert abs(loss - float(g["loss"])) <= (2e-3 if prec == "tf32" else 1e-4)
     assert rel_err(logits, g["logits"]) <= ATTN_TOL[prec]
     off = 0
+    gmax = float(np.abs(g["grads"]).max())       # key-projection bias gradients are zero in exact arithmetic: see the MHA test
     for size, _rank in layout:
         ref_g = g["grads"][off:off + size]
-        if np.abs(ref_g).max() > 0:
-            assert rel_err(grads[off:off + size], ref_g) <= (3e-2 if prec == "tf32" else 5e-4), off
+        floor = gmax if float(np.abs(ref_g).max()) < 1e-3 * gmax else 0.0
+        assert rel_err_floored(grads[off:off + size], ref_g, floor) <= (3e-2 if prec == "tf32" else 5e-4), off
         off += size
 
 

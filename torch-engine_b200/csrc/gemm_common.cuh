@@ -24,13 +24,15 @@ constexpr int EPI_WARPS = 8;
 constexpr int PRODUCER_WARP = 8;
 constexpr int MMA_WARP = 9;
 constexpr int CTA_THREADS = 320;
+constexpr int CONVERTER_THREADS = 128;       // warps 10-13 of the kernels that split fp32 into tf32 hi/lo in shared memory
 
 enum : int {  // where a bounded wait gave up (stored in the device status word)
     WAIT_PRODUCER_EMPTY = 101,
     WAIT_MMA_FULL = 102,
     WAIT_MMA_TMEM_EMPTY = 103,
     WAIT_EPI_TMEM_FULL = 104,
-    WAIT_TEARDOWN = 105
+    WAIT_TEARDOWN = 105,
+    WAIT_CONVERTER_FULL = 106
 };
 
 // How an epilogue thread's 32 consecutive columns of one row reach global memory.
@@ -85,6 +87,13 @@ struct TileCfg {
     static_assert(SMEM_BYTES <= 232448, "exceeds the 227 KB of shared memory a CTA can have");
     static_assert(TMEM_COLS >= 32 && TMEM_COLS <= 512 && (TMEM_COLS & (TMEM_COLS - 1)) == 0, "TMEM columns");
 };
+
+// round-to-nearest (ties away) fp32 -> tf32, low 13 mantissa bits cleared: exactly representable on the tensor core
+__device__ __forceinline__ float to_tf32_rn(float x) {
+    uint32_t u;
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(u) : "f"(x));
+    return __uint_as_float(u & 0xFFFFE000u);
+}
 
 __device__ __forceinline__ bool wait_bounded(uint32_t bar, uint32_t parity, volatile int* abort_flag,
                                              int* status, int code) {
@@ -238,10 +247,19 @@ __device__ __forceinline__ void epilogue_store32(float* v, int col0, const Epilo
         else if (p.scale_mode == TE_SCALE_DIV) v[j] = v[j] / p.alpha;
     }
     if (p.bias) {
-        // every thread of the warp needs the same 32 bias values: one coalesced load, then register shuffles
-        const float mine = (col0 + lane < p.N) ? __ldg(p.bias + col0 + lane) : 0.0f;
+        // every thread of the warp needs the same 32 bias values: eight 16-byte loads from one address per
+        // instruction (a broadcast out of L1), instead of a shuffle per output element
+        const float* bp = p.bias + col0;
+        if (col0 + 32 <= p.N && (reinterpret_cast<uintptr_t>(bp) & 15) == 0) {
 #pragma unroll
-        for (int j = 0; j < 32; ++j) v[j] += __shfl_sync(0xffffffffu, mine, j);
+            for (int j = 0; j < 32; j += 4) {
+                const float4 t = __ldg(reinterpret_cast<const float4*>(bp + j));
+                v[j] += t.x; v[j + 1] += t.y; v[j + 2] += t.z; v[j + 3] += t.w;
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] += (col0 + j < p.N) ? __ldg(bp + j) : 0.0f;
+        }
     }
     if (er.sector_ok) {   // warp-uniform
         if (!er.row_ok) return;

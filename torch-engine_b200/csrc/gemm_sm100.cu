@@ -40,8 +40,12 @@ namespace te {
 // EPI_PLAIN: the output is the bare product going out through TMA stores (no scale, bias, pre-activation output or
 // GELU); the general epilogue's code costs registers and drain time even when none of its branches is taken.
 // EPI_RESIDUAL: the general epilogue plus a residual input added last.
-template <int BN, int NPL, bool A_MN, bool B_MN, int EPI = EPI_GENERAL>
-__global__ void __launch_bounds__(CTA_THREADS, 1)
+// SPLIT (3xTF32 only): the operands arrive as they are in memory; TMA fills the first plane of a stage with the raw
+// fp32 tile and four converter warps (warps 10-13) rewrite it in place as hi = round-to-nearest tf32(x) and write
+// lo = round-to-nearest tf32(x - hi) into the second plane, then hand the stage to the MMA warp.  Same numbers as the
+// packing pre-pass, without its workspace and without its extra pass over global memory.
+template <int BN, int NPL, bool A_MN, bool B_MN, int EPI = EPI_GENERAL, bool SPLIT = false>
+__global__ void __launch_bounds__(SPLIT ? CTA_THREADS + CONVERTER_THREADS : CTA_THREADS, 1)
 gemm_tf32_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_a_lo,
                  const __grid_constant__ CUtensorMap tm_b, const __grid_constant__ CUtensorMap tm_b_lo,
                  const __grid_constant__ CUtensorMap tm_c, const __grid_constant__ CUtensorMap tm_pre,
@@ -54,6 +58,7 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
     constexpr bool CHUNKED = (NPL == 2);      // 3xTF32: sum K in chunks, add the chunks in registers
     constexpr int CHUNK_KB = 8;               // k-blocks per chunk = 256 values of K
     static_assert(!CHUNKED || BN <= 256, "chunked accumulation keeps BN/2 floats per thread in registers");
+    static_assert(!SPLIT || NPL == 2, "the in-kernel split produces the second plane of a two-plane stage");
     // Descriptor geometry.
     // K-major (TMA SWIZZLE_128B): rows of 128 B, 8-row groups 1024 B apart (SBO); one MMA advances 32 B along K.
     // MN-major (TMA SWIZZLE_128B_ATOM_32B): every k index is a 128-byte row of 32 consecutive MN elements;
@@ -70,10 +75,11 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
     const uint32_t epi_stage = ring + STAGES * STAGE_BYTES;       // EPI_WARPS staging tiles, 1024-byte aligned
     uint8_t* aux = smem_raw + (ring - raw_addr) + STAGES * STAGE_BYTES + EPI_WARPS * EPI_STAGE_BYTES;
     const uint32_t aux_addr = epi_stage + EPI_WARPS * EPI_STAGE_BYTES;
-    // aux layout (8-byte slots): full[STAGES] | empty[STAGES] | tmem_full[2] | tmem_empty[2] | teardown | slot | abort
+    // aux layout (8-byte slots): full[STAGES] | empty[STAGES] | conv[STAGES] | tmem_full[2] | tmem_empty[2] | teardown | slot | abort
     const uint32_t bar_full = aux_addr;
     const uint32_t bar_empty = bar_full + 8 * STAGES;
-    const uint32_t bar_tmem_full = bar_empty + 8 * STAGES;
+    const uint32_t bar_conv = bar_empty + 8 * STAGES;          // SPLIT: the converter warps have produced hi and lo
+    const uint32_t bar_tmem_full = bar_conv + 8 * STAGES;
     const uint32_t bar_tmem_empty = bar_tmem_full + 16;
     const uint32_t bar_teardown = bar_tmem_empty + 16;
     const uint32_t tmem_slot_addr = bar_teardown + 8;
@@ -87,6 +93,7 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
         for (int s = 0; s < STAGES; ++s) {
             mbar_init(bar_full + 8 * s, 1);
             mbar_init(bar_empty + 8 * s, 1);
+            mbar_init(bar_conv + 8 * s, CONVERTER_THREADS / 32);   // one arrival per converter warp
         }
         for (int i = 0; i < 2; ++i) {
             mbar_init(bar_tmem_full + 8 * i, 1);
@@ -142,12 +149,12 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                         break;
                     }
                     const uint32_t full = bar_full + 8 * s;
-                    mbar_arrive_expect_tx(full, STAGE_BYTES);
+                    mbar_arrive_expect_tx(full, SPLIT ? STAGE_BYTES / 2 : STAGE_BYTES);
                     const uint32_t sa = ring + s * STAGE_BYTES;
                     const uint32_t sb = sa + NPL * A_PLANE_BYTES;
                     const int k0 = kb * BK;
 #pragma unroll
-                    for (int pl = 0; pl < NPL; ++pl) {
+                    for (int pl = 0; pl < (SPLIT ? 1 : NPL); ++pl) {
                         const CUtensorMap* ma = pl ? &tm_a_lo : &tm_a;
                         const CUtensorMap* mb = pl ? &tm_b_lo : &tm_b;
                         if (A_MN) {
@@ -203,7 +210,7 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                     const int kb_first = kb;
                     for (; kb < kb_end; ++kb, ++consumed) {
                         const int s = consumed % STAGES;
-                        if (!wait_bounded(bar_full + 8 * s, (consumed / STAGES) & 1, abort_flag, p.status,
+                        if (!wait_bounded((SPLIT ? bar_conv : bar_full) + 8 * s, (consumed / STAGES) & 1, abort_flag, p.status,
                                           WAIT_MMA_FULL)) {
                             ok = false;
                             break;
@@ -241,6 +248,41 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                     atomicCAS(p.status, 0, (int)WAIT_TEARDOWN);
                     break;
                 }
+            }
+        }
+    } else if (SPLIT && warp > MMA_WARP) {
+        // ------------------------------------------------------------ converters (warps 10-13, SPLIT only)
+        // A stage is [A raw->hi | A lo | B raw->hi | B lo]; whatever the operand's layout, the lo plane mirrors the hi
+        // plane byte for byte, so the conversion walks both planes as flat arrays of 16-byte pieces.
+        const int ct = threadIdx.x - (MMA_WARP + 1) * 32;
+        int converted = 0;
+        bool ok = true;
+        for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x) {
+            WorkUnit w;
+            decode_unit(u, p, kblocks, w);
+            for (int kb = w.kb0; kb < w.kb1 && ok; ++kb, ++converted) {
+                const int s = converted % STAGES;
+                ok = wait_bounded(bar_full + 8 * s, (converted / STAGES) & 1, abort_flag, p.status, WAIT_CONVERTER_FULL);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+                const uint32_t sa = ring + s * STAGE_BYTES;
+                const uint32_t sb = sa + 2 * A_PLANE_BYTES;
+#pragma unroll 4
+                for (int i = ct; i < (A_PLANE_BYTES + B_PLANE_BYTES) / 16; i += CONVERTER_THREADS) {
+                    const bool in_a = i < A_PLANE_BYTES / 16;
+                    const uint32_t src = in_a ? sa + 16 * i : sb + 16 * (i - A_PLANE_BYTES / 16);
+                    const uint32_t dst = src + (in_a ? A_PLANE_BYTES : B_PLANE_BYTES);
+                    float4 x;
+                    asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(x.x), "=f"(x.y), "=f"(x.z), "=f"(x.w) : "r"(src) : "memory");
+                    float4 hi, lo;
+                    hi.x = to_tf32_rn(x.x); hi.y = to_tf32_rn(x.y); hi.z = to_tf32_rn(x.z); hi.w = to_tf32_rn(x.w);
+                    lo.x = to_tf32_rn(x.x - hi.x); lo.y = to_tf32_rn(x.y - hi.y); lo.z = to_tf32_rn(x.z - hi.z); lo.w = to_tf32_rn(x.w - hi.w);
+                    asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(src), "f"(hi.x), "f"(hi.y), "f"(hi.z), "f"(hi.w) : "memory");
+                    asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "f"(lo.x), "f"(lo.y), "f"(lo.z), "f"(lo.w) : "memory");
+                }
+                fence_proxy_async_smem();      // the tensor core reads these planes through the async proxy
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar_conv + 8 * s);
             }
         }
     } else {
@@ -587,13 +629,13 @@ int finish_split(te_b200_ctx* ctx, const GemmProblem& g, int k_splits, cudaStrea
 
 // One-time set-up of a kernel instance in this context: the dynamic shared memory limit (which also makes the
 // runtime load the kernel's module).
-template <int BN, int NPL, bool A_MN, bool B_MN>
+template <int BN, int NPL, bool A_MN, bool B_MN, bool SPLIT = false>
 static int ensure_kernel_attributes(te_b200_ctx* ctx) {
     using Cfg = TileCfg<BN, NPL>;
     // 3xTF32 (NPL = 2) has one instance, which carries the residual input; TF32 has all three epilogue forms
-    int& attr_done = ctx->kernel_state[reinterpret_cast<const void*>(gemm_tf32_kernel<BN, NPL, A_MN, B_MN, EPI_RESIDUAL>)];
+    int& attr_done = ctx->kernel_state[reinterpret_cast<const void*>(gemm_tf32_kernel<BN, NPL, A_MN, B_MN, EPI_RESIDUAL, SPLIT>)];
     if (attr_done) return TE_OK;
-    cudaError_t e = cudaFuncSetAttribute(gemm_tf32_kernel<BN, NPL, A_MN, B_MN, EPI_RESIDUAL>,
+    cudaError_t e = cudaFuncSetAttribute(gemm_tf32_kernel<BN, NPL, A_MN, B_MN, EPI_RESIDUAL, SPLIT>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
     if (e == cudaSuccess && NPL == 1)
         e = cudaFuncSetAttribute(gemm_tf32_kernel<BN, 1, A_MN, B_MN, EPI_PLAIN>,
@@ -617,16 +659,16 @@ int prepare_3xtf32_kernels(te_b200_ctx* ctx) {
     return prepare_pack_kernels();
 }
 
-template <int BN, int NPL, bool A_MN, bool B_MN>
+template <int BN, int NPL, bool A_MN, bool B_MN, bool SPLIT = false>
 static int launch_variant(te_b200_ctx* ctx, const GemmProblem& g_in, int k_splits, cudaStream_t stream) {
     GemmProblem g = g_in;
     using Cfg = TileCfg<BN, NPL>;
-    if (int rc0 = ensure_kernel_attributes<BN, NPL, A_MN, B_MN>(ctx)) return rc0;
+    if (int rc0 = ensure_kernel_attributes<BN, NPL, A_MN, B_MN, SPLIT>(ctx)) return rc0;
     CUtensorMap ma, mal, mb, mbl;
     int rc;
     if ((rc = make_operand_map(ctx, &ma, g.a.ptr, g.a, g.K, BM, g.batch_inner, g.batch_outer))) return rc;
     if ((rc = make_operand_map(ctx, &mb, g.b.ptr, g.b, g.K, BN, g.batch_inner, g.batch_outer))) return rc;
-    if (NPL == 2) {
+    if (NPL == 2 && !SPLIT) {
         if ((rc = make_operand_map(ctx, &mal, g.a_lo, g.a, g.K, BM, g.batch_inner, g.batch_outer))) return rc;
         if ((rc = make_operand_map(ctx, &mbl, g.b_lo, g.b, g.K, BN, g.batch_inner, g.batch_outer))) return rc;
     } else {
@@ -646,12 +688,13 @@ static int launch_variant(te_b200_ctx* ctx, const GemmProblem& g_in, int k_split
     // product (split-K partial tiles included).
     const bool bare = NPL == 1 && p.tma_store &&
                       (k_splits > 1 || (!g.bias && !g.preact && !g.residual && g.scale_mode == TE_SCALE_NONE && g.epilogue == TE_EPI_NONE));
-    auto kernel = gemm_tf32_kernel<BN, NPL, A_MN, B_MN, EPI_RESIDUAL>;
+    auto kernel = gemm_tf32_kernel<BN, NPL, A_MN, B_MN, EPI_RESIDUAL, SPLIT>;
     if constexpr (NPL == 1) {
         if (bare) kernel = gemm_tf32_kernel<BN, 1, A_MN, B_MN, EPI_PLAIN>;
         else if (!p.residual) kernel = gemm_tf32_kernel<BN, 1, A_MN, B_MN, EPI_GENERAL>;
     }
-    cudaError_t e = launch_pdl(kernel, dim3((unsigned)grid), dim3(CTA_THREADS), Cfg::SMEM_BYTES, stream, ma, mal, mb, mbl, mc, mpre, p);
+    const int threads = SPLIT ? CTA_THREADS + CONVERTER_THREADS : CTA_THREADS;
+    cudaError_t e = launch_pdl(kernel, dim3((unsigned)grid), dim3(threads), Cfg::SMEM_BYTES, stream, ma, mal, mb, mbl, mc, mpre, p);
     if (e != cudaSuccess) return cuda_fail(e, "gemm_tf32_kernel launch");
     ctx->launches += 1;
     return k_splits > 1 ? finish_split(ctx, g_in, k_splits, stream) : TE_OK;
@@ -659,7 +702,14 @@ static int launch_variant(te_b200_ctx* ctx, const GemmProblem& g_in, int k_split
 
 template <int BN>
 static int launch_bn(te_b200_ctx* ctx, const GemmProblem& g, int k_splits, cudaStream_t stream) {
-    if (g.a_lo) {   // 3xTF32: planes are always packed K-major
+    if (g.split_in_kernel) {   // 3xTF32 on the operands as they are: the kernel splits hi / lo in shared memory
+        constexpr int B2 = BN <= 128 ? BN : 128;
+        if (!g.a.mn_major && !g.b.mn_major) return launch_variant<B2, 2, false, false, true>(ctx, g, k_splits, stream);
+        if (!g.a.mn_major && g.b.mn_major) return launch_variant<B2, 2, false, true, true>(ctx, g, k_splits, stream);
+        if (g.a.mn_major && !g.b.mn_major) return launch_variant<B2, 2, true, false, true>(ctx, g, k_splits, stream);
+        return launch_variant<B2, 2, true, true, true>(ctx, g, k_splits, stream);
+    }
+    if (g.a_lo) {   // 3xTF32 on packed planes (always K-major)
         if constexpr (BN <= 128) return launch_variant<BN, 2, false, false>(ctx, g, k_splits, stream);
         else return launch_variant<128, 2, false, false>(ctx, g, k_splits, stream);
     }
@@ -675,7 +725,12 @@ static int launch_bn(te_b200_ctx* ctx, const GemmProblem& g, int k_splits, cudaS
 // small shapes are bound by filling shared memory, not by the tensor pipe.  When a problem has few tiles but a long
 // K (a thin M, a weight gradient over many tokens), K is additionally split over several work units per tile.
 
-TileChoice choose_tile(const te_b200_ctx* ctx, const GemmProblem& g) {
+TileChoice choose_tile(const te_b200_ctx* ctx, const GemmProblem& g_in) {
+    // 3xTF32 is recognised by its lo planes; a problem that is split inside the kernel has none but is costed the same
+    // way and is limited to the single-CTA kernel
+    GemmProblem g = g_in;
+    static const float three_x_marker = 0.0f;
+    if (g.split_in_kernel) g.a_lo = &three_x_marker;
     const int kblocks = (int)((g.K + BK - 1) / BK);
     const double batches = (double)(g.batch_inner * g.batch_outer);
     // ns per k-block of one tile in TF32 mode and in 3xTF32 mode (two planes per operand, three MMAs per k-step,
@@ -694,7 +749,7 @@ TileChoice choose_tile(const te_b200_ctx* ctx, const GemmProblem& g) {
     TileChoice best{64, false, 1};
     double best_t = 1e300;
     for (const Cand& c : cands) {
-        if (c.pair && (g.M <= 128 || g.N <= 128)) continue;
+        if (c.pair && (g.M <= 128 || g.N <= 128 || g.split_in_kernel)) continue;
         if (c.pair && g.a_lo && kblocks < 160) continue;         // measured: the 3-stage pair form of 3xTF32 pays off from K ~ 5000
         if (g.a_lo && !c.pair && c.bn > 128) continue;           // 3xTF32, single CTA: two 96 KB stages would be too few
         if (g.a_lo && c.pair && c.bn != 256) continue;           // 3xTF32 pair form exists for 256-wide tiles only

@@ -11,16 +11,11 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include "gemm_common.cuh"
 #include "pdl.cuh"
 #include "te_internal.h"
 
 namespace te {
-
-__device__ __forceinline__ float to_tf32_rn(float x) {
-    uint32_t u;
-    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(u) : "f"(x));
-    return __uint_as_float(u & 0xFFFFE000u);
-}
 
 struct PackParams {
     const float* src;

@@ -23,8 +23,9 @@ struct GemmProblem {
     int64_t M = 0, N = 0, K = 0;
     int64_t batch_inner = 1, batch_outer = 1;
     Operand a, b;                 // raw fp32 (TF32 mode) or the tf32 "hi" planes (3xTF32)
-    const float* a_lo = nullptr;  // 3xTF32 only: "lo" planes with the geometry of a / b
+    const float* a_lo = nullptr;  // 3xTF32 on packed planes: "lo" planes with the geometry of a / b
     const float* b_lo = nullptr;
+    bool split_in_kernel = false; // 3xTF32 on raw operands: the kernel derives hi / lo itself (single-CTA kernel only)
     float* c = nullptr;
     int64_t ldc = 0, c_stride_inner = 0, c_stride_outer = 0;
     float* preact = nullptr;
@@ -106,6 +107,9 @@ int prepare_pack_kernels();                         // pack.cu
 // The kernel form launch_gemm picks: tile width, CTA-pair or single-CTA kernel, K splits.  Uses only the extents, the
 // precision (a_lo set or not), the scratch size of `p` and ctx->sm_count; touches no device.
 struct TileChoice { int bn; bool pair; int k_splits; };
+// 3xTF32: true when the CTA-pair form (which reads packed hi / lo planes) can be the choice for these extents; everything
+// else is split inside the single-CTA kernel and needs no plane storage.
+inline bool three_x_pair_possible(int64_t M, int64_t N, int64_t K) { return M > 128 && N > 128 && (K + 31) / 32 >= 160; }
 TileChoice choose_tile(const te_b200_ctx* ctx, const GemmProblem& p);
 
 // attention_sm100.cu: fused QK^T -> softmax -> PV.  Returns -1 when the problem is outside the fused kernel's limits.
