@@ -288,7 +288,7 @@ def test_split_k_paths(backend, oracle, prec):
         n0 = backend.launches
         c = backend.matmul(dev(a), dev(b), precision=prec)
         used = backend.launches - n0
-        assert used >= (2 if prec == "tf32" else 4), "expected the split-K path (GEMM + reduction)"
+        assert used >= 2, "expected the split-K path (GEMM + reduction)"
         assert_close(c.cpu().numpy(), ref, prec, f"split-K {B}x{M}x{K}x{N}")
         if B == 1:   # epilogue applied by the reduction kernel
             y, pre = backend.linear_forward(dev(a), dev(np.ascontiguousarray(b.T)), dev(bias), gelu=True, want_preact=True,
@@ -336,7 +336,7 @@ def test_launch_counter_moves(backend):
     assert backend.launches == n0 + 1
     backend.matmul(torch.ones(8, 8, device="cuda"), torch.ones(8, 8, device="cuda"), precision="3xtf32")
     assert backend.launches == n0 + 2      # the 3xTF32 mode splits hi / lo inside the kernel: one launch as well
-    big = torch.ones(256, 5120, device="cuda")
+    big = torch.ones(2048, 8192, device="cuda")
     n1 = backend.launches
     backend.matmul(big, big.t().contiguous(), precision="3xtf32")
     assert backend.launches == n1 + 3      # long K, large M and N: the CTA-pair form behind two packing passes

@@ -114,12 +114,13 @@ def test_descriptor_validation():
 def test_workspace_sizing():
     # aligned operands in TF32 mode are read in place
     assert _ws(_desc()) == (L.TE_OK, 0)
-    # 3xTF32 splits hi / lo inside the kernel: no plane storage ...
+    # 3xTF32 splits hi / lo inside the kernel for thin and small products: no plane storage ...
     assert _ws(_desc(precision=L.TE_PREC_3XTF32)) == (L.TE_OK, 0)
-    # ... except where the CTA-pair form can be chosen (M, N > 128 and K >= 5120), which reads packed hi+lo planes of
-    # both operands: 2 * 2 * 256*5120*4 bytes
-    big = dict(M=256, N=256, K=5120, lda=5120, ldb=256, ldc=256, precision=L.TE_PREC_3XTF32)
-    assert _ws(_desc(**big)) == (L.TE_OK, 4 * 256 * 5120 * 4)
+    thin = dict(M=16, N=8192, K=8192, lda=8192, ldb=8192, ldc=8192, precision=L.TE_PREC_3XTF32)
+    assert _ws(_desc(**thin)) == (L.TE_OK, 0)
+    # ... large ones read packed hi+lo planes of both operands: 2 * 2 * 2048*2048*4 bytes
+    big = dict(M=2048, N=2048, K=2048, lda=2048, ldb=2048, ldc=2048, precision=L.TE_PREC_3XTF32)
+    assert _ws(_desc(**big)) == (L.TE_OK, 4 * 2048 * 2048 * 4)
     # an operand TMA cannot address is still copied once (not split) in 3xTF32 mode
     assert _ws(_desc(M=64, K=65, N=64, lda=65, ldb=64, precision=L.TE_PREC_3XTF32))[1] == 64 * 68 * 4
     # a leading dimension that is not a multiple of 4 floats cannot be addressed by TMA -> one packed copy of A

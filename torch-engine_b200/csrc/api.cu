@@ -100,8 +100,8 @@ static size_t workspace_need(const te_gemm_desc* d) {
     Operand a, b;
     operands_from_desc(d, a, b);
     size_t need = 0;
-    if (d->precision == TE_PREC_3XTF32 && three_x_pair_possible(d->M, d->N, d->K)) {
-        // the CTA-pair form reads hi / lo planes written by the packing pass
+    if (d->precision == TE_PREC_3XTF32 && !three_x_split_in_kernel(d->M, d->N, d->K)) {
+        // large products read hi / lo planes written by the packing pass
         need += 2 * (size_t)plane_bytes(a, d->K, d->batch_inner, d->batch_outer);
         need += 2 * (size_t)plane_bytes(b, d->K, d->batch_inner, d->batch_outer);
     } else {
@@ -154,17 +154,9 @@ static int gemm_device(te_b200_ctx* ctx, const te_gemm_desc* d, cudaStream_t st,
     g.epilogue = d->epilogue;
     Carver ws(ctx->workspace, ctx->workspace_bytes - reserve_tail);
     if (d->K > 0) {
-        bool packed_3x = false;
-        if (d->precision == TE_PREC_3XTF32) {
-            // The CTA-pair form (long K, large M and N) reads packed hi / lo planes; every other problem is split inside
-            // the single-CTA kernel from the operands as they are, without plane storage.
-            GemmProblem probe = g;
-            static const float marker = 0.0f;
-            probe.a_lo = &marker;
-            probe.split_ws = reinterpret_cast<float*>(ws.base);
-            probe.split_ws_bytes = ws.cap;
-            packed_3x = three_x_pair_possible(d->M, d->N, d->K) && choose_tile(ctx, probe).pair;
-        }
+        // 3xTF32: thin and small products are split inside the kernel from the operands as they are; large ones read
+        // hi / lo planes written by the packing pass (see three_x_split_in_kernel)
+        const bool packed_3x = d->precision == TE_PREC_3XTF32 && !three_x_split_in_kernel(d->M, d->N, d->K);
         if (packed_3x) {
             if ((rc = pack_into(ctx, ws, g.a, &g.a_lo, d->K, d->batch_inner, d->batch_outer, true, st))) return rc;
             if ((rc = pack_into(ctx, ws, g.b, &g.b_lo, d->K, d->batch_inner, d->batch_outer, true, st))) return rc;

@@ -32,6 +32,8 @@
 #include <stdlib.h>
 #include <string.h>
 
+#include <type_traits>
+
 #include "gemm_common.cuh"
 
 namespace te {
@@ -265,21 +267,27 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                 ok = wait_bounded(bar_full + 8 * s, (converted / STAGES) & 1, abort_flag, p.status, WAIT_CONVERTER_FULL);
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
-                const uint32_t sa = ring + s * STAGE_BYTES;
-                const uint32_t sb = sa + 2 * A_PLANE_BYTES;
-#pragma unroll 4
-                for (int i = ct; i < (A_PLANE_BYTES + B_PLANE_BYTES) / 16; i += CONVERTER_THREADS) {
-                    const bool in_a = i < A_PLANE_BYTES / 16;
-                    const uint32_t src = in_a ? sa + 16 * i : sb + 16 * (i - A_PLANE_BYTES / 16);
-                    const uint32_t dst = src + (in_a ? A_PLANE_BYTES : B_PLANE_BYTES);
-                    float4 x;
-                    asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(x.x), "=f"(x.y), "=f"(x.z), "=f"(x.w) : "r"(src) : "memory");
-                    float4 hi, lo;
-                    hi.x = to_tf32_rn(x.x); hi.y = to_tf32_rn(x.y); hi.z = to_tf32_rn(x.z); hi.w = to_tf32_rn(x.w);
-                    lo.x = to_tf32_rn(x.x - hi.x); lo.y = to_tf32_rn(x.y - hi.y); lo.z = to_tf32_rn(x.z - hi.z); lo.w = to_tf32_rn(x.w - hi.w);
-                    asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(src), "f"(hi.x), "f"(hi.y), "f"(hi.z), "f"(hi.w) : "memory");
-                    asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "f"(lo.x), "f"(lo.y), "f"(lo.z), "f"(lo.w) : "memory");
-                }
+                // all loads of a plane are issued before the first conversion, so that their latencies overlap
+                float4* a_hi = reinterpret_cast<float4*>(smem_raw + (ring - raw_addr) + s * STAGE_BYTES);
+                float4* b_hi = a_hi + 2 * (A_PLANE_BYTES / 16);
+                auto split_plane = [&](float4* hi_plane, auto pieces_tag) {
+                    constexpr int PIECES = decltype(pieces_tag)::value;      // 16-byte pieces per thread
+                    float4* lo_plane = hi_plane + PIECES * CONVERTER_THREADS;
+                    float4 x[PIECES];
+#pragma unroll
+                    for (int i = 0; i < PIECES; ++i) x[i] = hi_plane[ct + i * CONVERTER_THREADS];
+#pragma unroll
+                    for (int i = 0; i < PIECES; ++i) {
+                        float4 hi, lo;
+                        hi.x = to_tf32_rn(x[i].x); hi.y = to_tf32_rn(x[i].y); hi.z = to_tf32_rn(x[i].z); hi.w = to_tf32_rn(x[i].w);
+                        lo.x = to_tf32_rn(x[i].x - hi.x); lo.y = to_tf32_rn(x[i].y - hi.y);
+                        lo.z = to_tf32_rn(x[i].z - hi.z); lo.w = to_tf32_rn(x[i].w - hi.w);
+                        hi_plane[ct + i * CONVERTER_THREADS] = hi;
+                        lo_plane[ct + i * CONVERTER_THREADS] = lo;
+                    }
+                };
+                split_plane(a_hi, std::integral_constant<int, A_PLANE_BYTES / 16 / CONVERTER_THREADS>{});
+                split_plane(b_hi, std::integral_constant<int, B_PLANE_BYTES / 16 / CONVERTER_THREADS>{});
                 fence_proxy_async_smem();      // the tensor core reads these planes through the async proxy
                 __syncwarp();
                 if (lane == 0) mbar_arrive(bar_conv + 8 * s);

@@ -107,9 +107,16 @@ int prepare_pack_kernels();                         // pack.cu
 // The kernel form launch_gemm picks: tile width, CTA-pair or single-CTA kernel, K splits.  Uses only the extents, the
 // precision (a_lo set or not), the scratch size of `p` and ctx->sm_count; touches no device.
 struct TileChoice { int bn; bool pair; int k_splits; };
-// 3xTF32: true when the CTA-pair form (which reads packed hi / lo planes) can be the choice for these extents; everything
-// else is split inside the single-CTA kernel and needs no plane storage.
-inline bool three_x_pair_possible(int64_t M, int64_t N, int64_t K) { return M > 128 && N > 128 && (K + 31) / 32 >= 160; }
+// 3xTF32: where the tf32 hi / lo parts of the operands come from.  Splitting inside the kernel (converter warps rewrite
+// every landed stage in shared memory) needs no plane storage and no extra pass over global memory, but a tile of A is
+// converted again for every tile of N it meets (and B for every tile of M), and the conversion shares the shared-memory
+// bandwidth the tensor core feeds from.  Measured: it wins where one extent is thin (16x8192x8192: 0.138 against
+// 0.275 ms) and on small problems (no two extra launches); the packing pre-pass wins on large squares (4096^3: 0.72
+// against 0.96 ms).
+inline bool three_x_split_in_kernel(int64_t M, int64_t N, int64_t K) {
+    const int64_t thin = M < N ? M : N;
+    return thin <= 256 || (double)M * (double)N * (double)K <= 2147483648.0;
+}
 TileChoice choose_tile(const te_b200_ctx* ctx, const GemmProblem& p);
 
 // attention_sm100.cu: fused QK^T -> softmax -> PV.  Returns -1 when the problem is outside the fused kernel's limits.
