@@ -223,11 +223,13 @@ TE_API int te_b200_linear_backward_gelu(te_b200_ctx* ctx, const float* x, const 
  * it may be dx itself, which chains the input gradients of several Linears reading the same x.  accumulate != 0
  * adds dW and db to the buffers' contents instead of overwriting them -- the `*grad = *grad + g` of the autograd
  * engine (src/tensor/tensor.cpp:1138-1142) folded into the producing kernels.  x_preact as in _gelu (it excludes
- * dx_residual). */
+ * dx_residual).  dx_colsum (optional, [in]) receives the column sums of the returned dx: the bias gradient of the
+ * Linear whose output x (or x_preact) is, i.e. what its AddBackward would obtain through reduce_gradient
+ * (src/core/grad_fn.cpp:13-58, :93-102); with x_preact it comes out of the GeluBackward pass itself. */
 TE_API int te_b200_linear_backward_ex(te_b200_ctx* ctx, const float* x, const float* x_preact, const float* w,
-                               const float* dy, float* dx, const float* dx_residual, float* dw, float* db,
-                               int accumulate, int64_t rows, int64_t in_features, int64_t out_features,
-                               int precision, te_stream_t stream);
+                               const float* dy, float* dx, const float* dx_residual, float* dx_colsum, float* dw,
+                               float* db, int accumulate, int64_t rows, int64_t in_features,
+                               int64_t out_features, int precision, te_stream_t stream);
 
 /* O = softmax(Q.K^T / sqrt(d)) . V for Q,K,V viewed as [B,H,T,d] with explicit element
  * strides (last-dim stride must be 1).  ScaledDot::forward (src/nn/scaledot.cpp:8-27).
@@ -335,10 +337,13 @@ TE_API int te_b200_layernorm_backward(te_b200_ctx* ctx, const float* x, const fl
                                int64_t rows, int64_t cols, float eps, te_stream_t stream);
 /* The same with dx_residual ([rows, cols], optional) added into dx: in a pre-LN block the gradient of the block's
  * input is the LayerNorm's dx plus the gradient that bypasses it over the residual branch
- * (src/nn/transformer_block.cpp:15-35; AddBackward, src/core/grad_fn.cpp:93-102).  May be dx itself. */
+ * (src/nn/transformer_block.cpp:15-35; AddBackward, src/core/grad_fn.cpp:93-102).  May be dx itself.
+ * dx_colsum (optional, [cols]) receives the column sums of the returned dx -- the bias gradient of the Linear whose
+ * output feeds the residual stream at this point -- accumulated beside dgamma and dbeta in the same pass. */
 TE_API int te_b200_layernorm_backward_ex(te_b200_ctx* ctx, const float* x, const float* gamma,
                                   const float* dy, float* dx, const float* dx_residual, float* dgamma,
-                                  float* dbeta, int64_t rows, int64_t cols, float eps, te_stream_t stream);
+                                  float* dbeta, float* dx_colsum, int64_t rows, int64_t cols, float eps,
+                                  te_stream_t stream);
 /* out[i][:] = table[tokens[i]][:] (+ pos[i % seq_len][:] when pos is not NULL) for n int64
  * tokens: Embedding::forward (src/nn/embedding.cpp:18-60) with the positional sum of
  * GPT::forward (src/nn/gpt.cpp:30-69) folded in.  An index outside [0, vocab) writes zeros and

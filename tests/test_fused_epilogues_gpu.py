@@ -101,6 +101,10 @@ def test_feed_forward_goldens(backend, prec):
     dx, dw1, db1 = backend.linear_backward(x, w1, d_pre, precision=prec)
     for got, name in ((dx, "dx"), (dw1, "dw1"), (db1, "db1"), (dw2, "dw2"), (db2, "db2")):
         assert rel_err(got.cpu().numpy(), gold[f"ffn.{name}"]) <= 3 * TOL_REL[prec], name
+    # the first Linear's bias gradient as a by-product of the GeluBackward pass (column sums of d_pre)
+    d_pre2, _, _, db1_fused = backend.linear_backward(h, w2, dy, precision=prec, gelu_preact=pre, want_dx_colsum=True)
+    assert torch.equal(d_pre2, d_pre)
+    assert rel_err(db1_fused.cpu().numpy(), gold["ffn.db1"]) <= 3 * TOL_REL[prec]
     backend.check_device_status()
 
 
@@ -157,6 +161,11 @@ def test_layernorm_backward_adds_the_bypassing_gradient(backend, oracle):
     assert float((dx1 - (dx0 + branch)).abs().max()) <= 1e-6
     dx_ref, _, _ = oracle.layernorm_backward(c["x"], c["gamma"], c["dy"])
     assert np.abs(dx0.cpu().numpy() - dx_ref).max() <= 2e-5
+    # column sums of the result (the bias gradient of the Linear feeding the residual stream) out of the same pass
+    dx2, dg2, db2, sums = backend.layernorm_backward(x, gamma, dy, dx_residual=branch, want_dx_colsum=True)
+    assert torch.equal(dx2, dx1) and torch.equal(dg2, dg1) and torch.equal(db2, db1)
+    want = dx1.double().reshape(-1, dx1.shape[-1]).sum(dim=0)
+    assert float((sums.double() - want).abs().max()) <= 1e-5 * max(1.0, float(want.abs().max()))
     backend.check_device_status()
 
 

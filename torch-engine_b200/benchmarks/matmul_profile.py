@@ -24,6 +24,8 @@ def main():
     ap.add_argument("--precision", default="tf32", choices=["tf32", "3xtf32"])
     ap.add_argument("--layout", default="nn", choices=["nn", "nt"], help="nn: row-major B; nt: column-major B (Linear weight)")
     ap.add_argument("--launches", type=int, default=3)
+    ap.add_argument("--epilogue", default="none", choices=["none", "bias", "bias_gelu"],
+                    help="with --layout nt: run the product as Linear::forward with the bias (and GELU) in the GEMM epilogue")
     args = ap.parse_args()
     be = ops.Backend(0, workspace_bytes=2 << 30)
     g = torch.Generator(device="cuda").manual_seed(42)
@@ -32,12 +34,18 @@ def main():
         b = torch.rand(args.k, args.n, device="cuda", generator=g) * 2 - 1
     else:
         b = (torch.rand(args.n, args.k, device="cuda", generator=g) * 2 - 1).t()
-    be.matmul(a, b, precision=args.precision)          # warm-up
+    if args.epilogue != "none":
+        assert args.layout == "nt", "--epilogue runs Linear::forward, whose weight is the nt layout"
+        w, bias = b.t(), torch.rand(args.n, device="cuda", generator=g)
+        run = lambda: be.linear_forward(a, w, bias, gelu=args.epilogue == "bias_gelu", precision=args.precision)
+    else:
+        run = lambda: be.matmul(a, b, precision=args.precision)
+    run()          # warm-up
     torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for _ in range(args.launches):
-        c = be.matmul(a, b, precision=args.precision)
+        c = run()
     e1.record()
     torch.cuda.synchronize()
     be.check_device_status()

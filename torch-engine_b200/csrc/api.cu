@@ -576,20 +576,21 @@ int te_b200_linear_forward(te_b200_ctx* ctx, const float* x, const float* w, con
 int te_b200_linear_backward(te_b200_ctx* ctx, const float* x, const float* w, const float* dy, float* dx, float* dw,
                             float* db, int64_t rows, int64_t in_features, int64_t out_features, int precision,
                             te_stream_t stream) {
-    return te_b200_linear_backward_ex(ctx, x, nullptr, w, dy, dx, nullptr, dw, db, 0, rows, in_features, out_features, precision, stream);
+    return te_b200_linear_backward_ex(ctx, x, nullptr, w, dy, dx, nullptr, nullptr, dw, db, 0, rows, in_features, out_features, precision, stream);
 }
 
 int te_b200_linear_backward_gelu(te_b200_ctx* ctx, const float* x, const float* x_preact, const float* w, const float* dy,
                                  float* dx, float* dw, float* db, int64_t rows, int64_t in_features, int64_t out_features,
                                  int precision, te_stream_t stream) {
-    return te_b200_linear_backward_ex(ctx, x, x_preact, w, dy, dx, nullptr, dw, db, 0, rows, in_features, out_features, precision, stream);
+    return te_b200_linear_backward_ex(ctx, x, x_preact, w, dy, dx, nullptr, nullptr, dw, db, 0, rows, in_features, out_features, precision, stream);
 }
 
 int te_b200_linear_backward_ex(te_b200_ctx* ctx, const float* x, const float* x_preact, const float* w, const float* dy,
-                               float* dx, const float* dx_residual, float* dw, float* db, int accumulate, int64_t rows,
-                               int64_t in_features, int64_t out_features, int precision, te_stream_t stream) {
+                               float* dx, const float* dx_residual, float* dx_colsum, float* dw, float* db, int accumulate,
+                               int64_t rows, int64_t in_features, int64_t out_features, int precision, te_stream_t stream) {
     if (int bad = check_ctx(ctx)) return bad;
     if (x_preact && dx_residual) return fail(TE_ERR_BAD_ARGUMENT, "linear backward: x_preact and dx_residual exclude each other");
+    if (dx_colsum && !dx) return fail(TE_ERR_BAD_ARGUMENT, "linear backward: dx_colsum needs dx");
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     int rc;
     te_gemm_desc d;
@@ -602,8 +603,14 @@ int te_b200_linear_backward_ex(te_b200_ctx* ctx, const float* x, const float* x_
         d.residual = dx_residual;
         d.batch_outer = d.batch_inner = 1; d.alpha = 1.0f; d.precision = precision;
         if ((rc = gemm_device(ctx, &d, st))) return rc;
-        // x = gelu(x_preact): hand back the gradient of the pre-activation (GeluBackward, in place)
-        if (x_preact && (rc = launch_gelu_backward(ctx, x_preact, dx, dx, rows * in_features, st))) return rc;
+        // x = gelu(x_preact): hand back the gradient of the pre-activation (GeluBackward, in place), and its column sums
+        // (the bias gradient of the Linear before the GELU) out of the same pass when asked for
+        if (x_preact && dx_colsum) {
+            if ((rc = launch_gelu_backward_colsum(ctx, x_preact, dx, dx, rows, in_features, dx_colsum, st))) return rc;
+        } else {
+            if (x_preact && (rc = launch_gelu_backward(ctx, x_preact, dx, dx, rows * in_features, st))) return rc;
+            if (dx_colsum && (rc = launch_colsum(ctx, dx, rows, in_features, in_features, dx_colsum, false, st))) return rc;
+        }
     }
     if (dw) {   // dW[out,in] (+)= dY^T[out,rows] . X[rows,in]
         memset(&d, 0, sizeof d);
@@ -678,7 +685,7 @@ int te_b200_mha_backward(te_b200_ctx* ctx, const te_mha_bwd_desc* m, te_stream_t
     const int acc = m->accumulate;
     int rc;
     // out projection: d_attn = dY . Wo, dWo = dY^T . attn, dbo = colsum(dY)
-    if ((rc = te_b200_linear_backward_ex(ctx, m->attn, nullptr, m->wo, m->dy, m->dattn, nullptr, m->dwo, m->dbo, acc, rows, E, E,
+    if ((rc = te_b200_linear_backward_ex(ctx, m->attn, nullptr, m->wo, m->dy, m->dattn, nullptr, nullptr, m->dwo, m->dbo, acc, rows, E, E,
                                          m->precision, stream))) return rc;
     // attention core on head views of the [B,T,E] buffers
     te_attn_bwd_desc a;
@@ -694,11 +701,11 @@ int te_b200_mha_backward(te_b200_ctx* ctx, const te_mha_bwd_desc* m, te_stream_t
     if ((rc = te_b200_attention_backward(ctx, &a, stream))) return rc;
     // the three input projections; their dX contributions are chained through the residual input:
     // dx = dx_residual + dq.Wq + dk.Wk + dv.Wv
-    if ((rc = te_b200_linear_backward_ex(ctx, m->x, nullptr, m->wq, m->dq, m->dx, m->dx_residual, m->dwq, m->dbq, acc, rows, E, E,
+    if ((rc = te_b200_linear_backward_ex(ctx, m->x, nullptr, m->wq, m->dq, m->dx, m->dx_residual, nullptr, m->dwq, m->dbq, acc, rows, E, E,
                                          m->precision, stream))) return rc;
-    if ((rc = te_b200_linear_backward_ex(ctx, m->x, nullptr, m->wk, m->dk, m->dx, m->dx, m->dwk, m->dbk, acc, rows, E, E,
+    if ((rc = te_b200_linear_backward_ex(ctx, m->x, nullptr, m->wk, m->dk, m->dx, m->dx, nullptr, m->dwk, m->dbk, acc, rows, E, E,
                                          m->precision, stream))) return rc;
-    return te_b200_linear_backward_ex(ctx, m->x, nullptr, m->wv, m->dv, m->dx, m->dx, m->dwv, m->dbv, acc, rows, E, E,
+    return te_b200_linear_backward_ex(ctx, m->x, nullptr, m->wv, m->dv, m->dx, m->dx, nullptr, m->dwv, m->dbv, acc, rows, E, E,
                                       m->precision, stream);
 }
 
@@ -827,18 +834,18 @@ int te_b200_layernorm_forward(te_b200_ctx* ctx, const float* x, const float* gam
 
 int te_b200_layernorm_backward(te_b200_ctx* ctx, const float* x, const float* gamma, const float* dy, float* dx,
                                float* dgamma, float* dbeta, int64_t rows, int64_t cols, float eps, te_stream_t stream) {
-    return te_b200_layernorm_backward_ex(ctx, x, gamma, dy, dx, nullptr, dgamma, dbeta, rows, cols, eps, stream);
+    return te_b200_layernorm_backward_ex(ctx, x, gamma, dy, dx, nullptr, dgamma, dbeta, nullptr, rows, cols, eps, stream);
 }
 
 int te_b200_layernorm_backward_ex(te_b200_ctx* ctx, const float* x, const float* gamma, const float* dy, float* dx,
-                                  const float* dx_residual, float* dgamma, float* dbeta, int64_t rows, int64_t cols,
-                                  float eps, te_stream_t stream) {
+                                  const float* dx_residual, float* dgamma, float* dbeta, float* dx_colsum, int64_t rows,
+                                  int64_t cols, float eps, te_stream_t stream) {
     if (int bad = check_ctx(ctx)) return bad;
     if (rows < 0 || cols < 0) return fail(TE_ERR_BAD_ARGUMENT, "layernorm backward: negative extent");
     if (cols == 0) return TE_OK;
     if (rows > 0 && (!x || !dy || !dx)) return fail(TE_ERR_BAD_ARGUMENT, "layernorm backward: NULL pointer");
     if (!gamma) return fail(TE_ERR_BAD_ARGUMENT, "layernorm backward: NULL pointer");
-    return launch_layernorm_backward(ctx, x, gamma, dy, dx, dx_residual, dgamma, dbeta, rows, cols, eps, static_cast<cudaStream_t>(stream));
+    return launch_layernorm_backward(ctx, x, gamma, dy, dx, dx_residual, dgamma, dbeta, dx_colsum, rows, cols, eps, static_cast<cudaStream_t>(stream));
 }
 
 int te_b200_embedding_forward(te_b200_ctx* ctx, const float* table, const int64_t* tokens, const float* pos, float* out,

@@ -241,10 +241,17 @@ __device__ __forceinline__ void epilogue_store32(float* v, int col0, const Epilo
             for (int j = 0; j < 32; ++j) res[j] = 0.0f;
         }
     }
+    // One uniform branch around each loop: written per element, the compiler predicates the (long) division sequence
+    // into every element of every call, scaled or not (measured: +200 instructions per 32 x 32 block).
+    const int scale_mode = p.scale_mode;
+    if (scale_mode == TE_SCALE_MUL) {
+        const float alpha = p.alpha;
 #pragma unroll
-    for (int j = 0; j < 32; ++j) {
-        if (p.scale_mode == TE_SCALE_MUL) v[j] *= p.alpha;
-        else if (p.scale_mode == TE_SCALE_DIV) v[j] = v[j] / p.alpha;
+        for (int j = 0; j < 32; ++j) v[j] *= alpha;
+    } else if (scale_mode == TE_SCALE_DIV) {
+        const float alpha = p.alpha;
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = v[j] / alpha;
     }
     if (p.bias) {
         // every thread of the warp needs the same 32 bias values: eight 16-byte loads from one address per

@@ -98,16 +98,17 @@ __global__ void __launch_bounds__(256) layernorm_forward_kernel(const float* __r
 template <int N, bool VEC>
 __global__ void __launch_bounds__(256) layernorm_backward_kernel(const float* __restrict__ x, const float* __restrict__ gamma,
                                                                  const float* __restrict__ dy, float* dx, const float* dx_residual,
-                                                                 float* __restrict__ partial, long long rows, int cols, float eps) {
+                                                                 float* __restrict__ partial, long long rows, int cols, float eps,
+                                                                 int want_dx_sum) {
     griddep_wait();
     using R = RowRegs<N, VEC>;
     extern __shared__ float red[];     // [8 warps][cols]
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const long long warps = (long long)gridDim.x * (blockDim.x >> 5);
-    R g, dg, db;
+    R g, dg, db, ds;       // ds: column sums of the result dx (asked for by want_dx_sum)
     g.load(gamma, cols, lane);
 #pragma unroll
-    for (int k = 0; k < N * R::W; ++k) dg.v[k] = db.v[k] = 0.0f;
+    for (int k = 0; k < N * R::W; ++k) dg.v[k] = db.v[k] = ds.v[k] = 0.0f;
     const float inv_n = 1.0f / (float)cols;
     for (long long r = (long long)blockIdx.x * (blockDim.x >> 5) + warp; r < rows; r += warps) {
         R xr, gy;
@@ -146,6 +147,10 @@ __global__ void __launch_bounds__(256) layernorm_backward_kernel(const float* __
 #pragma unroll
             for (int k = 0; k < N * R::W; ++k) xr.v[k] += gy.v[k];
         }
+        if (want_dx_sum) {
+#pragma unroll
+            for (int k = 0; k < N * R::W; ++k) ds.v[k] += R::col(k / R::W, k % R::W, lane) < cols ? xr.v[k] : 0.0f;
+        }
         xr.store(dx + r * cols, cols, lane);
     }
     // block sums of the two column accumulators, warps added in warp order
@@ -161,40 +166,46 @@ __global__ void __launch_bounds__(256) layernorm_backward_kernel(const float* __
             float t = 0.0f;
 #pragma unroll
             for (int w = 0; w < 8; ++w) t += red[w * cols + c];
-            partial[((long long)blockIdx.x * 2 + which) * cols + c] = t;
+            partial[((long long)blockIdx.x * 3 + which) * cols + c] = t;
         }
     };
     block_sum(dg, 0);
     block_sum(db, 1);
+    if (want_dx_sum) block_sum(ds, 2);
 }
 
 // One block per 32 columns: warp w adds the partial rows w, w + 8, ... in ascending order, then the eight warp sums
 // are added in warp order.
 __global__ void __launch_bounds__(256) layernorm_param_grad_kernel(const float* __restrict__ partial, int blocks, int cols,
-                                                                   float* __restrict__ dgamma, float* __restrict__ dbeta) {
+                                                                   float* __restrict__ dgamma, float* __restrict__ dbeta,
+                                                                   float* __restrict__ dx_colsum) {
     griddep_wait();
-    __shared__ float red[2][8][32];
+    __shared__ float red[3][8][32];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int c = blockIdx.x * 32 + lane;
-    float a = 0.0f, b = 0.0f;
+    float a = 0.0f, b = 0.0f, s = 0.0f;
     if (c < cols) {
         for (int i = warp; i < blocks; i += 8) {
-            a += partial[((long long)i * 2) * cols + c];
-            b += partial[((long long)i * 2 + 1) * cols + c];
+            a += partial[((long long)i * 3) * cols + c];
+            b += partial[((long long)i * 3 + 1) * cols + c];
+            if (dx_colsum) s += partial[((long long)i * 3 + 2) * cols + c];
         }
     }
     red[0][warp][lane] = a;
     red[1][warp][lane] = b;
+    red[2][warp][lane] = s;
     __syncthreads();
     if (warp == 0 && c < cols) {
-        float ta = 0.0f, tb = 0.0f;
+        float ta = 0.0f, tb = 0.0f, ts = 0.0f;
 #pragma unroll
         for (int w = 0; w < 8; ++w) {
             ta += red[0][w][lane];
             tb += red[1][w][lane];
+            ts += red[2][w][lane];
         }
         if (dgamma) dgamma[c] = ta;
         if (dbeta) dbeta[c] = tb;
+        if (dx_colsum) dx_colsum[c] = ts;
     }
 }
 
@@ -398,8 +409,8 @@ int launch_layernorm_forward(te_b200_ctx* ctx, const float* x, const float* gamm
 }
 
 int launch_layernorm_backward(te_b200_ctx* ctx, const float* x, const float* gamma, const float* dy, float* dx,
-                              const float* dx_residual, float* dgamma, float* dbeta, int64_t rows, int64_t cols64, float eps,
-                              cudaStream_t st) {
+                              const float* dx_residual, float* dgamma, float* dbeta, float* dx_colsum, int64_t rows, int64_t cols64,
+                              float eps, cudaStream_t st) {
     if (cols64 == 0) return TE_OK;
     if (cols64 > 1024) {
         set_error("LayerNorm rows longer than 1024 elements are not supported");
@@ -409,19 +420,19 @@ int launch_layernorm_backward(te_b200_ctx* ctx, const float* x, const float* gam
     const bool vec = (cols & 3) == 0 && aligned16(x) && aligned16(dy) && aligned16(dx) && aligned16(gamma) &&
                      (!dx_residual || aligned16(dx_residual));
     const int grid = row_grid(rows, ctx->sm_count, 2);
-    const size_t need = (size_t)grid * 2 * cols * sizeof(float);
+    const size_t need = (size_t)grid * 3 * cols * sizeof(float);
     if (need > ctx->workspace_bytes) {
         set_error("context workspace too small for the LayerNorm parameter-gradient partials");
         return TE_ERR_WORKSPACE;
     }
     float* partial = static_cast<float*>(ctx->workspace);
     const size_t smem = (size_t)8 * cols * sizeof(float);
-#define CALL(N, V) launch_pdl(layernorm_backward_kernel<N, V>, dim3(grid), dim3(256), smem, st, x, gamma, dy, dx, dx_residual, partial, rows, cols, eps)
+#define CALL(N, V) launch_pdl(layernorm_backward_kernel<N, V>, dim3(grid), dim3(256), smem, st, x, gamma, dy, dx, dx_residual, partial, rows, cols, eps, dx_colsum ? 1 : 0)
     TE_LN_DISPATCH(CALL)
 #undef CALL
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return cuda_fail(e, "layernorm_backward_kernel launch");
-    launch_pdl(layernorm_param_grad_kernel, dim3((cols + 31) / 32), dim3(256), 0, st, partial, grid, cols, dgamma, dbeta);
+    launch_pdl(layernorm_param_grad_kernel, dim3((cols + 31) / 32), dim3(256), 0, st, partial, grid, cols, dgamma, dbeta, dx_colsum);
     e = cudaGetLastError();
     if (e != cudaSuccess) return cuda_fail(e, "layernorm_param_grad_kernel launch");
     ctx->launches += 2;

@@ -200,6 +200,81 @@ __global__ void __launch_bounds__(256) gelu_backward_vec4_kernel(const float4* _
     }
 }
 
+__device__ __forceinline__ bool colsum_is_last_block(unsigned* counter, unsigned slabs, bool* flag_smem);
+
+// dx = dy * gelu'(x) over a dense [rows, cols] matrix AND the column sums of dx in the same pass (the bias gradient of
+// the Linear that produced x: FeedForward's first Linear, src/nn/ffn.cpp:12-14 / src/core/grad_fn.cpp:93-102).  Thread
+// layout of colsum_slab_vec4_kernel: a block owns 128 columns and a slab of rows, its eight warps stride the rows four
+// at a time (eight 16-byte loads in flight per thread); slab sums go to `partial`, the last block of a column block
+// adds them in slab order.  dx may alias dy (each element is read before it is written, by the same thread).
+__global__ void __launch_bounds__(256) gelu_backward_colsum_kernel(const float* __restrict__ x, const float* dy, float* dx,
+                                                                   long long rows, long long cols, long long rows_per_slab,
+                                                                   float* __restrict__ partial, int slabs, unsigned* counters,
+                                                                   float* out) {
+    griddep_wait();
+    __shared__ float4 red[8][32];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const long long col = (long long)blockIdx.x * 128 + lane * 4;
+    const long long r0 = (long long)blockIdx.y * rows_per_slab;
+    const long long r1 = r0 + rows_per_slab < rows ? r0 + rows_per_slab : rows;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (col < cols) {
+        for (long long r = r0 + warp; r < r1; r += 32) {
+            float4 xv[4], gv[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const long long rr = r + 8 * u;
+                if (rr < r1) {
+                    xv[u] = *reinterpret_cast<const float4*>(x + rr * cols + col);
+                    gv[u] = *reinterpret_cast<const float4*>(dy + rr * cols + col);
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const long long rr = r + 8 * u;
+                if (rr < r1) {
+                    float4 t;
+                    t.x = gelu_bwd(xv[u].x, gv[u].x); t.y = gelu_bwd(xv[u].y, gv[u].y);
+                    t.z = gelu_bwd(xv[u].z, gv[u].z); t.w = gelu_bwd(xv[u].w, gv[u].w);
+                    *reinterpret_cast<float4*>(dx + rr * cols + col) = t;
+                    acc.x += t.x; acc.y += t.y; acc.z += t.z; acc.w += t.w;
+                }
+            }
+        }
+    }
+    red[warp][lane] = acc;
+    __syncthreads();
+    if (warp == 0 && col < cols) {
+        float4 t = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int w = 0; w < 8; ++w) {
+            const float4 v = red[w][lane];
+            t.x += v.x; t.y += v.y; t.z += v.z; t.w += v.w;
+        }
+        *reinterpret_cast<float4*>(partial + (long long)blockIdx.y * cols + col) = t;
+    }
+    __shared__ bool last;
+    if (!colsum_is_last_block(counters + blockIdx.x, (unsigned)slabs, &last)) return;
+    float4 s4 = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (col < cols)
+        for (int sl = warp; sl < slabs; sl += 8) {
+            const float4 v = __ldcg(reinterpret_cast<const float4*>(partial + (long long)sl * cols + col));
+            s4.x += v.x; s4.y += v.y; s4.z += v.z; s4.w += v.w;
+        }
+    __syncthreads();
+    red[warp][lane] = s4;
+    __syncthreads();
+    if (warp == 0 && col < cols) {
+        float4 t = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int w = 0; w < 8; ++w) {
+            const float4 v = red[w][lane];
+            t.x += v.x; t.y += v.y; t.z += v.z; t.w += v.w;
+        }
+        *reinterpret_cast<float4*>(out + col) = t;
+    }
+}
+
 // out[j] = sum over rows of in[i*ld + j].  One block owns 32 columns; its 32 row-lanes stride the rows,
 // then a shared-memory tree adds the 32 partials in a fixed order (deterministic, unlike an atomicAdd).
 __global__ void __launch_bounds__(1024) colsum_kernel(const float* __restrict__ in, long long rows, long long cols,
@@ -411,6 +486,32 @@ int launch_gelu_backward(te_b200_ctx* ctx, const float* x, const float* dy, floa
     if (e != cudaSuccess) return cuda_fail(e, "gelu_backward_kernel launch");
     ctx->launches += 1;
     return TE_OK;
+}
+
+// dx = dy * gelu'(x) and colsum_out = column sums of dx, x / dy / dx dense [rows, cols].  One launch where the layout
+// allows the fused kernel, otherwise the two kernels one after the other.
+int launch_gelu_backward_colsum(te_b200_ctx* ctx, const float* x, const float* dy, float* dx, int64_t rows, int64_t cols,
+                                float* colsum_out, cudaStream_t st) {
+    if (rows == 0 || cols == 0) return TE_OK;
+    const long long cb = (cols + 127) / 128;
+    const bool aligned = ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(dy) | reinterpret_cast<uintptr_t>(dx) |
+                           reinterpret_cast<uintptr_t>(colsum_out)) & 15) == 0;
+    long long slabs = ((long long)ctx->sm_count * 4 + cb - 1) / cb;
+    if (slabs > rows / 64) slabs = rows / 64;
+    if (slabs > 65535) slabs = 65535;
+    if ((cols & 3) == 0 && aligned && slabs >= 1 && (size_t)(slabs * cols * 4) <= ctx->workspace_bytes && cb <= STATUS_COUNTER_WORDS) {
+        const long long rows_per_slab = (rows + slabs - 1) / slabs;
+        slabs = (rows + rows_per_slab - 1) / rows_per_slab;
+        unsigned* counters = reinterpret_cast<unsigned*>(ctx->d_status) + STATUS_COUNTER_WORD;
+        launch_pdl(gelu_backward_colsum_kernel, dim3((unsigned)cb, (unsigned)slabs), dim3(256), 0, st, x, dy, dx, (long long)rows,
+                   (long long)cols, rows_per_slab, static_cast<float*>(ctx->workspace), (int)slabs, counters, colsum_out);
+        cudaError_t e = cudaGetLastError();
+        if (e != cudaSuccess) return cuda_fail(e, "gelu_backward_colsum_kernel launch");
+        ctx->launches += 1;
+        return TE_OK;
+    }
+    if (int rc = launch_gelu_backward(ctx, x, dy, dx, rows * cols, st)) return rc;
+    return launch_colsum(ctx, dx, rows, cols, cols, colsum_out, false, st);
 }
 
 int launch_colsum(te_b200_ctx* ctx, const float* in, int64_t rows, int64_t cols, int64_t ld, float* out, bool accumulate,

@@ -136,6 +136,8 @@ int launch_softmax_backward_rows(te_b200_ctx*, const float* s, const float* dy, 
 int launch_gelu(te_b200_ctx*, const float*, float*, int64_t n, cudaStream_t);
 int launch_gelu_backward(te_b200_ctx*, const float* x, const float* dy, float* dx, int64_t n,
                          cudaStream_t);
+int launch_gelu_backward_colsum(te_b200_ctx*, const float* x, const float* dy, float* dx, int64_t rows, int64_t cols,
+                                float* colsum_out, cudaStream_t);
 int launch_colsum(te_b200_ctx*, const float* in, int64_t rows, int64_t cols, int64_t ld, float* out, bool accumulate,
                   cudaStream_t);
 
@@ -143,8 +145,8 @@ int launch_colsum(te_b200_ctx*, const float* in, int64_t rows, int64_t cols, int
 int launch_layernorm_forward(te_b200_ctx*, const float* x, const float* gamma, const float* beta, float* y, int64_t rows,
                              int64_t cols, float eps, cudaStream_t);
 int launch_layernorm_backward(te_b200_ctx*, const float* x, const float* gamma, const float* dy, float* dx,
-                              const float* dx_residual, float* dgamma, float* dbeta, int64_t rows, int64_t cols, float eps,
-                              cudaStream_t);
+                              const float* dx_residual, float* dgamma, float* dbeta, float* dx_colsum, int64_t rows, int64_t cols,
+                              float eps, cudaStream_t);
 int launch_embedding_forward(te_b200_ctx*, const float* table, const int64_t* tokens, const float* pos, float* out, int64_t n,
                              int64_t T, int64_t D, int64_t vocab, cudaStream_t);
 int launch_embedding_backward(te_b200_ctx*, const int64_t* tokens, const float* dout, float* dtable, int64_t n, int64_t D,

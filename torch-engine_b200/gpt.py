@@ -8,8 +8,10 @@ torch operator, torch only owns the memory.  Per pre-LN block (src/nn/transforme
   forward   LayerNorm -> te_b200_mha_forward (three projections, attention on head views, out projection, the block's
             residual input added in the last GEMM's epilogue) -> LayerNorm -> Linear+GELU (pre-activation kept) ->
             Linear with the second residual in its epilogue;
-  backward  te_b200_linear_backward_ex twice (the first hands back the gradient of the GELU's pre-activation),
-            te_b200_layernorm_backward_ex (adds the gradient that bypasses the LayerNorm over the residual branch),
+  backward  te_b200_linear_backward_ex twice (the first hands back the gradient of the GELU's pre-activation and,
+            from the same pass, its column sums = the bias gradient of the first FeedForward Linear),
+            te_b200_layernorm_backward_ex (adds the gradient that bypasses the LayerNorm over the residual branch, and
+            sums its result over the rows = the bias gradient of the Linear that fed the residual stream there),
             te_b200_mha_backward, te_b200_layernorm_backward_ex.
 
 Every parameter is used once per step, so each gradient is written once, straight into its slice of one flat
@@ -146,32 +148,41 @@ class GptStep:
                                           vocab, st))                                  # mean over B*T, gradient in the same pass
 
         # ---- backward ---------------------------------------------------------------------------------------
-        L.check(lib.te_b200_linear_backward_ex(ctx, ptr(self.hf), None, P(i + 2), ptr(self.dlogits), ptr(self.dh), None, G(i + 2),
-                                               G(i + 3), 0, rows, E, vocab, prec, st))
+        L.check(lib.te_b200_linear_backward_ex(ctx, ptr(self.hf), None, P(i + 2), ptr(self.dlogits), ptr(self.dh), None, None,
+                                               G(i + 2), G(i + 3), 0, rows, E, vocab, prec, st))
+        # the gradient of x[L] is also the upstream gradient of the last block's second FeedForward Linear: its bias
+        # gradient (column sums) comes out of this pass
+        c2_last = G(1 + 16 * (n_layers - 1) + 15) if n_layers > 0 else None
         L.check(lib.te_b200_layernorm_backward_ex(ctx, ptr(self.x[n_layers]), P(i), ptr(self.dh), ptr(self.dxa), None, G(i),
-                                                  G(i + 1), rows, E, eps, st))
+                                                  G(i + 1), c2_last, rows, E, eps, st))
         for l in range(n_layers - 1, -1, -1):      # dxa holds the gradient of x[l+1]
             a = self.layers[l]
             i = 1 + 16 * l
+            # FeedForward: dW2 (its bias gradient came with dxa), d_pre with GeluBackward and the column sums of d_pre
+            # (= bias gradient of the first Linear) in one pass, then the first Linear's dX and dW
             L.check(lib.te_b200_linear_backward_ex(ctx, ptr(a["f"]), ptr(a["pre"]), P(i + 14), ptr(self.dxa), ptr(self.dpre), None,
-                                                   G(i + 14), G(i + 15), 0, rows, ff, E, prec, st))
-            L.check(lib.te_b200_linear_backward_ex(ctx, ptr(a["h2"]), None, P(i + 12), ptr(self.dpre), ptr(self.dh), None,
-                                                   G(i + 12), G(i + 13), 0, rows, E, ff, prec, st))
+                                                   G(i + 13), G(i + 14), None, 0, rows, ff, E, prec, st))
+            L.check(lib.te_b200_linear_backward_ex(ctx, ptr(a["h2"]), None, P(i + 12), ptr(self.dpre), ptr(self.dh), None, None,
+                                                   G(i + 12), None, 0, rows, E, ff, prec, st))
+            # gradient of y1 = dxa + LayerNorm backward; its column sums are the output projection's bias gradient
             L.check(lib.te_b200_layernorm_backward_ex(ctx, ptr(a["y1"]), P(i + 10), ptr(self.dh), ptr(self.dxb), ptr(self.dxa),
-                                                      G(i + 10), G(i + 11), rows, E, eps, st))      # gradient of y1
+                                                      G(i + 10), G(i + 11), G(i + 9), rows, E, eps, st))
             m = L.MhaBwdDesc()
             m.B, m.T, m.E, m.H = B, T, E, H
             m.x = a["h1"].data_ptr()
             m.wq, m.wk, m.wv, m.wo = (self._p(flat_params, j) for j in (i + 2, i + 4, i + 6, i + 8))
             m.q, m.k, m.v, m.p, m.attn = (a[n].data_ptr() for n in ("q", "k", "v", "p", "attn"))
             m.dy, m.dx, m.dx_residual = self.dxb.data_ptr(), self.dh.data_ptr(), None
-            for n, j in zip(("dwq", "dbq", "dwk", "dbk", "dwv", "dbv", "dwo", "dbo"), range(i + 2, i + 10)):
+            for n, j in zip(("dwq", "dbq", "dwk", "dbk", "dwv", "dbv", "dwo"), range(i + 2, i + 9)):
                 setattr(m, n, self._g(j))
+            m.dbo = None                                                               # came with the LayerNorm backward above
             m.dq, m.dk, m.dv, m.dattn = (t.data_ptr() for t in (self.dq, self.dk, self.dv, self.dattn))
             m.accumulate, m.precision = 0, prec
             L.check(lib.te_b200_mha_backward(ctx, C.byref(m), st))                     # gradient of LN1's output
+            # gradient of x[l]; for l > 0 its column sums are the bias gradient of block l-1's second FeedForward Linear
+            c2_prev = G(1 + 16 * (l - 1) + 15) if l > 0 else None
             L.check(lib.te_b200_layernorm_backward_ex(ctx, ptr(self.x[l]), P(i), ptr(self.dh), ptr(self.dxa), ptr(self.dxb), G(i),
-                                                      G(i + 1), rows, E, eps, st))                   # gradient of x[l]
+                                                      G(i + 1), c2_prev, rows, E, eps, st))
         L.check(lib.te_b200_embedding_backward(ctx, ptr(tokens), ptr(self.dxa), G(0), rows, E, vocab, st))
         return self.loss, self.logits, self.grads
 

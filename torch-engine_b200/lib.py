@@ -104,7 +104,7 @@ SIGNATURES = {
     "te_b200_linear_backward": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
                                           C.c_void_p, C.c_int64, C.c_int64, C.c_int64, C.c_int, C.c_void_p]),
     "te_b200_linear_backward_gelu": (C.c_int, [C.c_void_p] + [C.c_void_p] * 7 + [C.c_int64, C.c_int64, C.c_int64, C.c_int, C.c_void_p]),
-    "te_b200_linear_backward_ex": (C.c_int, [C.c_void_p] + [C.c_void_p] * 8 + [C.c_int, C.c_int64, C.c_int64, C.c_int64, C.c_int, C.c_void_p]),
+    "te_b200_linear_backward_ex": (C.c_int, [C.c_void_p] + [C.c_void_p] * 9 + [C.c_int, C.c_int64, C.c_int64, C.c_int64, C.c_int, C.c_void_p]),
     "te_b200_mha_forward": (C.c_int, [C.c_void_p, C.POINTER(MhaDesc), C.c_void_p]),
     "te_b200_mha_backward": (C.c_int, [C.c_void_p, C.POINTER(MhaBwdDesc), C.c_void_p]),
     "te_b200_set_wait_limit_ns": (C.c_int, [C.c_void_p, C.c_uint64, C.c_void_p]),
@@ -114,7 +114,7 @@ SIGNATURES = {
     "te_b200_attention_backward": (C.c_int, [C.c_void_p, C.POINTER(AttnBwdDesc), C.c_void_p]),
     "te_b200_layernorm_forward": (C.c_int, [C.c_void_p] + [C.c_void_p] * 4 + [C.c_int64, C.c_int64, C.c_float, C.c_void_p]),
     "te_b200_layernorm_backward": (C.c_int, [C.c_void_p] + [C.c_void_p] * 6 + [C.c_int64, C.c_int64, C.c_float, C.c_void_p]),
-    "te_b200_layernorm_backward_ex": (C.c_int, [C.c_void_p] + [C.c_void_p] * 7 + [C.c_int64, C.c_int64, C.c_float, C.c_void_p]),
+    "te_b200_layernorm_backward_ex": (C.c_int, [C.c_void_p] + [C.c_void_p] * 8 + [C.c_int64, C.c_int64, C.c_float, C.c_void_p]),
     "te_b200_embedding_forward": (C.c_int, [C.c_void_p] + [C.c_void_p] * 4 + [C.c_int64] * 4 + [C.c_void_p]),
     "te_b200_embedding_backward": (C.c_int, [C.c_void_p] + [C.c_void_p] * 3 + [C.c_int64] * 3 + [C.c_void_p]),
     "te_b200_cross_entropy": (C.c_int, [C.c_void_p] + [C.c_void_p] * 4 + [C.c_float, C.c_int64, C.c_int64, C.c_void_p]),

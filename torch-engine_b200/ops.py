@@ -135,11 +135,12 @@ class Backend:
         return (y, pre) if want_preact else y
 
     def linear_backward(self, x, w, dy, precision="tf32", need_dx=True, need_dw=True, need_db=True, gelu_preact=None,
-                        dx_residual=None, accumulate_into=None):
+                        dx_residual=None, accumulate_into=None, want_dx_colsum=False):
         """(dx, dw[out,in], db[out]) for y = x . w^T + b given dy.  With gelu_preact (x = gelu(gelu_preact), the second
         Linear of FeedForward) dx is the gradient of that pre-activation: the dX product, then GeluBackward in place.
         dx_residual ([rows, in]) is added into dx.  accumulate_into = (dw, db) adds the parameter gradients to those
-        tensors in place (and returns them) instead of writing fresh ones."""
+        tensors in place (and returns them) instead of writing fresh ones.  want_dx_colsum appends the column sums of dx
+        (the bias gradient of the Linear that produced x) to the result."""
         self._check_f32_cuda(x, w, dy, gelu_preact, dx_residual)
         x = x.contiguous()
         dy = dy.contiguous()
@@ -156,11 +157,12 @@ class Backend:
             raise L.BackendError(L.TE_ERR_BAD_ARGUMENT, "gelu_preact must be contiguous and shaped like x")
         if dx_residual is not None and (dx_residual.shape != x.shape or not dx_residual.is_contiguous()):
             raise L.BackendError(L.TE_ERR_BAD_ARGUMENT, "dx_residual must be contiguous and shaped like x")
+        dxs = torch.empty(in_f, dtype=torch.float32, device=x.device) if want_dx_colsum else None
         L.check(self._lib.te_b200_linear_backward_ex(self._ctx, _ptr(x), _ptr(gelu_preact), _ptr(w.contiguous()), _ptr(dy),
-                                                     _ptr(dx), _ptr(dx_residual), _ptr(dw), _ptr(db),
+                                                     _ptr(dx), _ptr(dx_residual), _ptr(dxs), _ptr(dw), _ptr(db),
                                                      int(accumulate_into is not None), rows, in_f, out_f, _prec(precision),
                                                      self._stream()))
-        return dx, dw, db
+        return (dx, dw, db, dxs) if want_dx_colsum else (dx, dw, db)
 
     # ------------------------------------------------------------------ multi-head attention
     def mha_forward(self, x, params, heads, residual=None, precision="tf32"):
@@ -289,8 +291,9 @@ class Backend:
                                                     _ptr(y), rows, cols, eps, self._stream()))
         return y
 
-    def layernorm_backward(self, x, gamma, dy, eps=1e-5, dx_residual=None):
-        """(dx, dgamma, dbeta) of LayerNormBackward::backward (src/core/grad_fn.cpp:405-538); dx_residual is added to dx."""
+    def layernorm_backward(self, x, gamma, dy, eps=1e-5, dx_residual=None, want_dx_colsum=False):
+        """(dx, dgamma, dbeta) of LayerNormBackward::backward (src/core/grad_fn.cpp:405-538); dx_residual is added to dx;
+        want_dx_colsum appends the column sums of dx."""
         self._check_f32_cuda(x, gamma, dy, dx_residual)
         x, dy = x.contiguous(), dy.contiguous()
         cols = x.shape[-1]
@@ -298,10 +301,11 @@ class Backend:
         dx = torch.empty_like(x)
         dg = torch.empty(cols, dtype=torch.float32, device=x.device)
         db = torch.empty(cols, dtype=torch.float32, device=x.device)
+        dxs = torch.empty(cols, dtype=torch.float32, device=x.device) if want_dx_colsum else None
         L.check(self._lib.te_b200_layernorm_backward_ex(self._ctx, _ptr(x), _ptr(gamma.contiguous()), _ptr(dy), _ptr(dx),
                                                         _ptr(dx_residual.contiguous() if dx_residual is not None else None),
-                                                        _ptr(dg), _ptr(db), rows, cols, eps, self._stream()))
-        return dx, dg, db
+                                                        _ptr(dg), _ptr(db), _ptr(dxs), rows, cols, eps, self._stream()))
+        return (dx, dg, db, dxs) if want_dx_colsum else (dx, dg, db)
 
     def embedding(self, table, tokens, pos=None):
         """table[tokens] (+ pos[t]) for int64 tokens [..., T]: Embedding::forward with GPT::forward's positional sum
