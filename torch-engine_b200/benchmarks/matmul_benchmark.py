@@ -196,6 +196,16 @@ def main():
         record("b200_linear_bias_gelu_fwd", mode, 4096, 768, 3072, 1, tb, tm, cub)
         tb, tm = time_gpu(lambda: be.linear_backward(x, w, dy, precision=mode), 50)
         record("b200_linear_bwd_dx_dw_db", mode, 4096, 3072, 768, 2, tb, tm, None)
+    # ---- the Linear shapes of the GPT configuration (16 384 tokens, d_model 384, ffDim 1536), TF32 mode ----
+    for (rows, inf, outf, gelu) in [(16384, 384, 384, False), (16384, 384, 1536, True), (16384, 1536, 384, False)]:
+        xg, wg = torch.randn(rows, inf, device="cuda", generator=gen), torch.randn(outf, inf, device="cuda", generator=gen) * 0.02
+        bg, dyg = torch.zeros(outf, device="cuda"), torch.randn(rows, outf, device="cuda", generator=gen)
+        _, cub = time_gpu(lambda: torch.nn.functional.linear(xg, wg, bg), 50, trials=3)
+        tb, tm = time_gpu(lambda: be.linear_forward(xg, wg, bg, gelu=gelu, precision="tf32"), 50)
+        record("b200_linear_bias%s_fwd" % ("_gelu" if gelu else ""), "tf32", rows, inf, outf, 1, tb, tm, cub)
+        tb, tm = time_gpu(lambda: be.linear_backward(xg, wg, dyg, precision="tf32"), 50)
+        record("b200_linear_bwd_dx_dw_db", "tf32", rows, outf, inf, 2, tb, tm, None)
+        del xg, wg, bg, dyg
     # ---- HBM-bound helpers around the GEMMs: softmax rows, GELU, bias-gradient column sum, 3xTF32 packing ----
     def record_stream(name, byts, tb, tm, shape):
         r = {"kernel_name": name, "dtype": "float32", "mode": "-", "shape": shape, "time_ms": tm, "time_ms_best": tb,
