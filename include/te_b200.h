@@ -284,25 +284,37 @@ TE_API int te_b200_attention_backward(te_b200_ctx* ctx, const te_attn_bwd_desc* 
  * (strides [T*E, E/H, E]: no copy), the head outputs written straight back in merged [B,T,E] order, and the output
  * projection, optionally with the block's residual input added (src/nn/transformer_block.cpp:20-24).
  * Weights are [E,E] as Linear stores them ([out,in], src/nn/linear.cpp:7); biases [E] or NULL.  q, k, v, p, attn are
- * caller-owned buffers the backward call needs again. */
+ * caller-owned buffers the backward call needs again.
+ *
+ * One-GEMM form of the three projections: with wqkv given (scratch of 3*E*E + 3*E floats) and q, k, v the three column
+ * blocks of ONE [B,T,3E] buffer (k == q + E, v == q + 2E, ld_qkv == 3*E), the call gathers the three weights and
+ * biases into wqkv ([3E,E] then [3E]) and computes x . Wqkv^T + bqkv in one product; every element is the same dot
+ * product as in the three-GEMM form.  ld_qkv == 0 or E: q, k, v are three dense [B,T,E] buffers. */
 typedef struct te_mha_desc {
     int64_t B, T, E, H;
     const float* x;                                  /* [B,T,E] */
     const float *wq, *bq, *wk, *bk, *wv, *bv, *wo, *bo;
-    float *q, *k, *v;                                /* [B,T,E] each: the projections */
+    float *q, *k, *v;                                /* the projections, row stride ld_qkv */
     float* p;                                        /* [B,H,T,T] attention probabilities */
     float* attn;                                     /* [B,T,E] merged head outputs (input of the out projection) */
     float* y;                                        /* [B,T,E] result */
     const float* residual;                           /* optional [B,T,E], added to y */
     int32_t precision;
     int32_t reserved;
+    float* wqkv;                                     /* optional scratch, see above */
+    int64_t ld_qkv;                                  /* row stride of q, k, v: 0 / E (dense) or 3*E */
 } te_mha_desc;
 TE_API int te_b200_mha_forward(te_b200_ctx* ctx, const te_mha_desc* d, te_stream_t stream);
 
 /* Backward of the call above: the graph MatMulBackward/AddBackward of four Linears, TransposeBackward and
  * ReshapeBackward of the head split and merge, and the attention core (src/core/grad_fn.cpp:93-156, :397-403,
  * :559-665).  dq, dk, dv, dattn are caller-owned [B,T,E] scratch.  dx = dx_residual + dq.Wq + dk.Wk + dv.Wv.
- * Parameter gradients are [E,E] / [E] like the parameters; NULL skips one; accumulate != 0 adds to their contents. */
+ * Parameter gradients are [E,E] / [E] like the parameters; NULL skips one; accumulate != 0 adds to their contents.
+ *
+ * One-GEMM form (see the forward call): with wqkv (as the forward call left it) and dwqkv (scratch, 3*E*E + 3*E
+ * floats) given, ld_qkv == 3*E, and dq, dk, dv the column blocks of one [B,T,3E] buffer like q, k, v, the call runs
+ * dx = dx_residual + dQKV . Wqkv as one K = 3E product, dWqkv = dQKV^T . x as one product and the three bias
+ * gradients as one column sum, then scatters dwqkv to the six gradient pointers. */
 typedef struct te_mha_bwd_desc {
     int64_t B, T, E, H;
     const float* x;
@@ -312,9 +324,12 @@ typedef struct te_mha_bwd_desc {
     float* dx;                                       /* [B,T,E] */
     const float* dx_residual;                        /* optional [B,T,E] */
     float *dwq, *dbq, *dwk, *dbk, *dwv, *dbv, *dwo, *dbo;
-    float *dq, *dk, *dv, *dattn;                     /* scratch */
+    float *dq, *dk, *dv, *dattn;                     /* scratch; dq, dk, dv with row stride ld_qkv */
     int32_t accumulate;
     int32_t precision;
+    const float* wqkv;                               /* optional, see above */
+    float* dwqkv;                                    /* optional scratch */
+    int64_t ld_qkv;                                  /* row stride of q, k, v, dq, dk, dv: 0 / E or 3*E */
 } te_mha_bwd_desc;
 TE_API int te_b200_mha_backward(te_b200_ctx* ctx, const te_mha_bwd_desc* d, te_stream_t stream);
 

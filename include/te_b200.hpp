@@ -366,22 +366,25 @@ public:
     Linear& v_proj() { return v_; }
     Linear& out_proj() { return out_; }
 
-    // What forward() keeps for backward(): the projections, the probabilities and the merged head outputs.
-    struct Saved { Tensor x, q, k, v, p, attn; };
+    // What forward() keeps for backward(): the projections (q | k | v as the column blocks of one [B,T,3E] tensor,
+    // computed as one product against the gathered [3E,E] weight wqkv), the probabilities, the merged head outputs.
+    struct Saved { Tensor x, qkv, wqkv, p, attn; };
 
     // x: [B, T, E] contiguous.  residual (optional, [B, T, E]) is added to the result: x + MHA(...) of a transformer block.
     Tensor forward(const Tensor& x, Saved* saved = nullptr, const Tensor* residual = nullptr) {
         if (x.shape().size() != 3 || x.shape()[2] != embed_) throw std::runtime_error("Inner dimensions must match for matmul");
         if (!x.is_contiguous()) throw std::runtime_error("MultiHeadAttention::forward expects a contiguous input");
         const int64_t B = x.shape()[0], T = x.shape()[1];
-        Saved s{x, Tensor(x.shape()), Tensor(x.shape()), Tensor(x.shape()), Tensor({B, heads_, T, T}), Tensor(x.shape())};
+        Saved s{x, Tensor({B, T, 3 * embed_}), Tensor({3 * embed_ * embed_ + 3 * embed_}), Tensor({B, heads_, T, T}),
+                Tensor(x.shape())};
         Tensor y(x.shape());
         te_mha_desc m{};
         m.B = B; m.T = T; m.E = embed_; m.H = heads_;
         m.x = x.data();
         m.wq = q_.weight().data(); m.bq = q_.bias().data(); m.wk = k_.weight().data(); m.bk = k_.bias().data();
         m.wv = v_.weight().data(); m.bv = v_.bias().data(); m.wo = out_.weight().data(); m.bo = out_.bias().data();
-        m.q = s.q.data(); m.k = s.k.data(); m.v = s.v.data(); m.p = s.p.data(); m.attn = s.attn.data();
+        m.q = s.qkv.data(); m.k = m.q + embed_; m.v = m.q + 2 * embed_; m.ld_qkv = 3 * embed_; m.wqkv = s.wqkv.data();
+        m.p = s.p.data(); m.attn = s.attn.data();
         m.y = y.data();
         m.residual = residual ? residual->data() : nullptr;
         Backend& be = Backend::instance();
@@ -401,16 +404,18 @@ public:
             g.emplace_back(std::vector<int64_t>{embed_, embed_});
             g.emplace_back(std::vector<int64_t>{embed_});
         }
-        Tensor dq(s.x.shape()), dk(s.x.shape()), dv(s.x.shape()), dattn(s.x.shape());
+        Tensor dqkv(s.qkv.shape()), dwqkv(s.wqkv.shape()), dattn(s.x.shape());
         te_mha_bwd_desc m{};
         m.B = B; m.T = T; m.E = embed_; m.H = heads_;
         m.x = s.x.data();
         m.wq = q_.weight().data(); m.wk = k_.weight().data(); m.wv = v_.weight().data(); m.wo = out_.weight().data();
-        m.q = s.q.data(); m.k = s.k.data(); m.v = s.v.data(); m.p = s.p.data(); m.attn = s.attn.data();
+        m.q = s.qkv.data(); m.k = m.q + embed_; m.v = m.q + 2 * embed_; m.ld_qkv = 3 * embed_;
+        m.wqkv = s.wqkv.data(); m.dwqkv = dwqkv.data();
+        m.p = s.p.data(); m.attn = s.attn.data();
         m.dy = dy.data(); m.dx = g[0].data();
         m.dwq = g[1].data(); m.dbq = g[2].data(); m.dwk = g[3].data(); m.dbk = g[4].data();
         m.dwv = g[5].data(); m.dbv = g[6].data(); m.dwo = g[7].data(); m.dbo = g[8].data();
-        m.dq = dq.data(); m.dk = dk.data(); m.dv = dv.data(); m.dattn = dattn.data();
+        m.dq = dqkv.data(); m.dk = m.dq + embed_; m.dv = m.dq + 2 * embed_; m.dattn = dattn.data();
         Backend& be = Backend::instance();
         m.precision = be.precision();
         check(te_b200_mha_backward(be.ctx(), &m, nullptr));

@@ -108,14 +108,16 @@ def test_feed_forward_goldens(backend, prec):
     backend.check_device_status()
 
 
+@pytest.mark.parametrize("one_gemm", [True, False], ids=["qkv_one_gemm", "qkv_three_gemms"])
 @pytest.mark.parametrize("prec", PRECS)
-def test_multi_head_attention_goldens(backend, prec):
-    """te_b200_mha_forward / _backward against MultiHeadAttention::forward + backward of the reference (CPU autograd)."""
+def test_multi_head_attention_goldens(backend, prec, one_gemm):
+    """te_b200_mha_forward / _backward against MultiHeadAttention::forward + backward of the reference (CPU autograd),
+    with the three input projections as one product against the gathered weights and as three products."""
     m = gc.nn_inputs()["mha"]
     gold = np.load(os.path.join(GOLD, "nn_cases.npz"))
     x, dy = dev(m["x"]), dev(m["dy"])
     params = [dev(p) for p in m["params"]]
-    y, saved = backend.mha_forward(x, params, m["H"], precision=prec)
+    y, saved = backend.mha_forward(x, params, m["H"], precision=prec, one_projection_gemm=one_gemm)
     assert rel_err(y.cpu().numpy(), gold["mha.y"]) <= ATTN_TOL[prec]
     dx, grads = backend.mha_backward(saved, dy, precision=prec)
     assert rel_err(dx.cpu().numpy(), gold["mha.dx"]) <= CHAIN_TOL[prec]
@@ -126,10 +128,53 @@ def test_multi_head_attention_goldens(backend, prec):
         floor = gmax if float(np.abs(gold[f"mha.dparam{i}"]).max()) < 1e-3 * gmax else 0.0
         assert rel_err_floored(g.cpu().numpy(), gold[f"mha.dparam{i}"], floor) <= CHAIN_TOL[prec], i
     # with the block's residual input and the gradient of the bypassing branch
-    y2, saved2 = backend.mha_forward(x, params, m["H"], residual=x, precision=prec)
+    y2, saved2 = backend.mha_forward(x, params, m["H"], residual=x, precision=prec, one_projection_gemm=one_gemm)
     assert rel_err((y2 - x).cpu().numpy(), gold["mha.y"]) <= ATTN_TOL[prec]
     dx2, _ = backend.mha_backward(saved2, dy, dx_residual=dy, precision=prec)
     assert rel_err((dx2 - dy).cpu().numpy(), gold["mha.dx"]) <= CHAIN_TOL[prec]
+    backend.check_device_status()
+
+
+def test_multi_head_attention_projection_forms_agree(backend):
+    """One product against the gathered [3E,E] weight computes each projection element as the same dot product as the
+    three-product form: the forward results are identical; so are the parameter gradients of the projections (the
+    same products, the same column sums).  Bad layouts of the one-product form are refused."""
+    torch.manual_seed(5)
+    B, T, E, H = 3, 128, 256, 4
+    x = torch.randn(B, T, E, device="cuda")
+    dy = torch.randn(B, T, E, device="cuda")
+    params = []
+    for _ in range(4):
+        params += [torch.randn(E, E, device="cuda") / 16, torch.randn(E, device="cuda")]
+    y1, s1 = backend.mha_forward(x, params, H, one_projection_gemm=True)
+    y3, s3 = backend.mha_forward(x, params, H, one_projection_gemm=False)
+    assert s1["qkv"].shape == (B, T, 3 * E) and s1["q"].stride() == (T * 3 * E, 3 * E, 1)
+    packed_w = s1["wqkv"][:3 * E * E].reshape(3, E, E)
+    packed_b = s1["wqkv"][3 * E * E:].reshape(3, E)
+    for i in range(3):
+        assert torch.equal(packed_w[i], params[2 * i]) and torch.equal(packed_b[i], params[2 * i + 1])
+        assert torch.equal(s1["qkv"][:, :, i * E:(i + 1) * E], s3[("q", "k", "v")[i]]), i
+    assert torch.equal(s1["p"], s3["p"]) and torch.equal(y1, y3)
+    dx1, g1 = backend.mha_backward(s1, dy)
+    dx3, g3 = backend.mha_backward(s3, dy)
+    for i in range(8):
+        # projection weight gradients: split-K slices differ between a [3E,E] and an [E,E] product, so the sums
+        # are the same terms in another order
+        assert rel_err(g1[i].cpu().numpy(), g3[i].cpu().numpy()) <= 1e-5, i
+    assert rel_err(dx1.cpu().numpy(), dx3.cpu().numpy()) <= 1e-5    # one K = 3E sum against three chained K = E sums
+    m = L.MhaDesc()
+    m.B, m.T, m.E, m.H = B, T, E, H
+    m.x = x.data_ptr()
+    for n, t in zip(("wq", "bq", "wk", "bk", "wv", "bv", "wo", "bo"), params):
+        setattr(m, n, t.data_ptr())
+    q = s1["qkv"].data_ptr()
+    m.q, m.k, m.v, m.p, m.attn, m.y = q, q + 4 * E, q + 8 * E, s1["p"].data_ptr(), s1["attn"].data_ptr(), y1.data_ptr()
+    m.ld_qkv = 3 * E                      # the scratch is missing
+    assert backend._lib.te_b200_mha_forward(backend._ctx, C.byref(m), None) == L.TE_ERR_BAD_ARGUMENT
+    m.wqkv, m.k = s1["wqkv"].data_ptr(), q + 8 * E      # k is not the second column block
+    assert backend._lib.te_b200_mha_forward(backend._ctx, C.byref(m), None) == L.TE_ERR_BAD_ARGUMENT
+    m.k, m.ld_qkv = q + 4 * E, 2 * E
+    assert backend._lib.te_b200_mha_forward(backend._ctx, C.byref(m), None) == L.TE_ERR_BAD_ARGUMENT
     backend.check_device_status()
 
 

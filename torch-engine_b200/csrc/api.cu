@@ -636,6 +636,20 @@ static int validate_mha(int64_t B, int64_t T, int64_t E, int64_t H) {
     return TE_OK;
 }
 
+// Row stride of the q / k / v projection buffers: E (three dense buffers) or 3*E (column blocks of one buffer, which
+// is what the one-GEMM form of the three projections needs together with its scratch).
+static float* const kNoSegments[3] = {nullptr, nullptr, nullptr};
+static int mha_projection_stride(int64_t ld_qkv, int64_t E, const float* q, const float* k, const float* v, bool have_scratch,
+                                 int64_t* ld) {
+    if (ld_qkv == 0 || ld_qkv == E) { *ld = E; return TE_OK; }
+    if (ld_qkv != 3 * E) return fail(TE_ERR_BAD_ARGUMENT, "multi-head attention: ld_qkv must be 0, E or 3*E");
+    if (!(k == q + E && v == q + 2 * E))
+        return fail(TE_ERR_BAD_ARGUMENT, "multi-head attention: with ld_qkv == 3*E, q, k, v must be the column blocks of one [B,T,3E] buffer");
+    if (!have_scratch) return fail(TE_ERR_BAD_ARGUMENT, "multi-head attention: ld_qkv == 3*E needs the wqkv (and, backward, dwqkv) scratch");
+    *ld = 3 * E;
+    return TE_OK;
+}
+
 int te_b200_mha_forward(te_b200_ctx* ctx, const te_mha_desc* m, te_stream_t stream) {
     if (int bad = check_ctx(ctx)) return bad;
     if (!m) return fail(TE_ERR_BAD_ARGUMENT, "multi-head attention: descriptor is NULL");
@@ -644,19 +658,29 @@ int te_b200_mha_forward(te_b200_ctx* ctx, const te_mha_desc* m, te_stream_t stre
     if (!m->x || !m->wq || !m->wk || !m->wv || !m->wo || !m->q || !m->k || !m->v || !m->p || !m->attn || !m->y)
         return fail(TE_ERR_BAD_ARGUMENT, "multi-head attention: NULL pointer");
     const int64_t rows = m->B * m->T, E = m->E, hd = E / m->H;
+    int64_t ld = 0;
+    if (int bad = mha_projection_stride(m->ld_qkv, E, m->q, m->k, m->v, m->wqkv != nullptr, &ld)) return bad;
     int rc;
     // Q, K, V = Linear(x)  (multi_head_attention.cpp:20-22), bias in the epilogue
-    if ((rc = te_b200_linear_forward(ctx, m->x, m->wq, m->bq, m->q, nullptr, rows, E, E, 0, m->precision, stream))) return rc;
-    if ((rc = te_b200_linear_forward(ctx, m->x, m->wk, m->bk, m->k, nullptr, rows, E, E, 0, m->precision, stream))) return rc;
-    if ((rc = te_b200_linear_forward(ctx, m->x, m->wv, m->bv, m->v, nullptr, rows, E, E, 0, m->precision, stream))) return rc;
-    // heads are views [B,H,T,hd] with strides [T*E, hd, E] of the [B,T,E] projections (:27-32); the attention output is
-    // written with the same strides, i.e. already merged back to [B,T,E] (:37-39 without the gather copy)
+    if (ld == 3 * E) {   // one product against the gathered [3E, E] weight
+        const float* const w3[3] = {m->wq, m->wk, m->wv};
+        const float* const b3[3] = {m->bq, m->bk, m->bv};
+        if ((rc = launch_pack_qkv(ctx, w3, b3, m->wqkv, E * E, E, static_cast<cudaStream_t>(stream)))) return rc;
+        const float* bias = (m->bq || m->bk || m->bv) ? m->wqkv + 3 * E * E : nullptr;
+        if ((rc = te_b200_linear_forward(ctx, m->x, m->wqkv, bias, m->q, nullptr, rows, E, 3 * E, 0, m->precision, stream))) return rc;
+    } else {
+        if ((rc = te_b200_linear_forward(ctx, m->x, m->wq, m->bq, m->q, nullptr, rows, E, E, 0, m->precision, stream))) return rc;
+        if ((rc = te_b200_linear_forward(ctx, m->x, m->wk, m->bk, m->k, nullptr, rows, E, E, 0, m->precision, stream))) return rc;
+        if ((rc = te_b200_linear_forward(ctx, m->x, m->wv, m->bv, m->v, nullptr, rows, E, E, 0, m->precision, stream))) return rc;
+    }
+    // heads are views [B,H,T,hd] with strides [T*ld, hd, ld] of the projections (:27-32); the attention output is
+    // written with strides [T*E, hd, E], i.e. already merged back to [B,T,E] (:37-39 without the gather copy)
     te_attn_desc a;
     memset(&a, 0, sizeof a);
     a.B = m->B; a.H = m->H; a.T = m->T; a.d = hd;
     a.q = m->q; a.k = m->k; a.v = m->v; a.p_out = m->p; a.o = m->attn;
-    const int64_t hs[3] = {m->T * E, hd, E};
-    for (int i = 0; i < 3; ++i) a.q_strides[i] = a.k_strides[i] = a.v_strides[i] = a.o_strides[i] = hs[i];
+    const int64_t hs[3] = {m->T * ld, hd, ld}, os[3] = {m->T * E, hd, E};
+    for (int i = 0; i < 3; ++i) { a.q_strides[i] = a.k_strides[i] = a.v_strides[i] = hs[i]; a.o_strides[i] = os[i]; }
     a.precision = m->precision;
     if ((rc = te_b200_attention_forward(ctx, &a, stream))) return rc;
     // y = Linear(attn) [+ residual]  (:41)
@@ -683,6 +707,10 @@ int te_b200_mha_backward(te_b200_ctx* ctx, const te_mha_bwd_desc* m, te_stream_t
         return fail(TE_ERR_BAD_ARGUMENT, "multi-head attention backward: NULL pointer");
     const int64_t rows = m->B * m->T, E = m->E, hd = E / m->H;
     const int acc = m->accumulate;
+    int64_t ld = 0;
+    if (int bad = mha_projection_stride(m->ld_qkv, E, m->q, m->k, m->v, m->wqkv && m->dwqkv, &ld)) return bad;
+    if (ld == 3 * E && !(m->dk == m->dq + E && m->dv == m->dq + 2 * E))
+        return fail(TE_ERR_BAD_ARGUMENT, "multi-head attention backward: with ld_qkv == 3*E, dq, dk, dv must be the column blocks of one [B,T,3E] buffer");
     int rc;
     // out projection: d_attn = dY . Wo, dWo = dY^T . attn, dbo = colsum(dY)
     if ((rc = te_b200_linear_backward_ex(ctx, m->attn, nullptr, m->wo, m->dy, m->dattn, nullptr, nullptr, m->dwo, m->dbo, acc, rows, E, E,
@@ -693,12 +721,26 @@ int te_b200_mha_backward(te_b200_ctx* ctx, const te_mha_bwd_desc* m, te_stream_t
     a.B = m->B; a.H = m->H; a.T = m->T; a.d = hd;
     a.q = m->q; a.k = m->k; a.v = m->v; a.p = m->p; a.o = m->attn; a.d_o = m->dattn;
     a.dq = m->dq; a.dk = m->dk; a.dv = m->dv;
-    const int64_t hs[3] = {m->T * E, hd, E};
-    for (int i = 0; i < 3; ++i)
-        a.q_strides[i] = a.k_strides[i] = a.v_strides[i] = a.o_strides[i] = a.d_o_strides[i] = a.dq_strides[i] =
-            a.dk_strides[i] = a.dv_strides[i] = hs[i];
+    const int64_t hs[3] = {m->T * ld, hd, ld}, os[3] = {m->T * E, hd, E};
+    for (int i = 0; i < 3; ++i) {
+        a.q_strides[i] = a.k_strides[i] = a.v_strides[i] = a.dq_strides[i] = a.dk_strides[i] = a.dv_strides[i] = hs[i];
+        a.o_strides[i] = a.d_o_strides[i] = os[i];
+    }
     a.precision = m->precision;
     if ((rc = te_b200_attention_backward(ctx, &a, stream))) return rc;
+    if (ld == 3 * E) {
+        // dx = dx_residual + dQKV . Wqkv (K = 3E), dWqkv = dQKV^T . x, dbqkv = column sums of dQKV; then the six
+        // gradients leave the scratch for their own buffers
+        const bool any_w = m->dwq || m->dwk || m->dwv, any_b = m->dbq || m->dbk || m->dbv;
+        if ((rc = te_b200_linear_backward_ex(ctx, m->x, nullptr, m->wqkv, m->dq, m->dx, m->dx_residual, nullptr,
+                                             any_w ? m->dwqkv : nullptr, any_b ? m->dwqkv + 3 * E * E : nullptr, 0, rows, E, 3 * E,
+                                             m->precision, stream))) return rc;
+        if (!any_w && !any_b) return TE_OK;
+        float* const w3[3] = {m->dwq, m->dwk, m->dwv};
+        float* const b3[3] = {m->dbq, m->dbk, m->dbv};
+        return launch_unpack_qkv(ctx, m->dwqkv, any_w ? w3 : kNoSegments, any_b ? b3 : kNoSegments, E * E, E, acc != 0,
+                                 static_cast<cudaStream_t>(stream));
+    }
     // the three input projections; their dX contributions are chained through the residual input:
     // dx = dx_residual + dq.Wq + dk.Wk + dv.Wv
     if ((rc = te_b200_linear_backward_ex(ctx, m->x, nullptr, m->wq, m->dq, m->dx, m->dx_residual, nullptr, m->dwq, m->dbq, acc, rows, E, E,

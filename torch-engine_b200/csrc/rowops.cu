@@ -418,6 +418,39 @@ __global__ void __launch_bounds__(256) colsum_slab_vec4_kernel(const float* __re
     }
 }
 
+// ---- q / k / v parameter packing ---------------------------------------------------------------------------------
+// Three equally sized weights and three equally sized biases gathered into one buffer  w0 | w1 | w2 | b0 | b1 | b2
+// (PACK), or that buffer scattered back to six places (gradients; ACC adds to what is there).  A NULL source packs
+// zeros, a NULL destination is skipped.  VEC = 4 needs wn and bn multiples of 4 and 16-byte aligned pointers.
+struct SixSegments { float* w[3]; float* b[3]; };
+template <bool PACK, int VEC>
+__global__ void __launch_bounds__(256) qkv_segments_kernel(SixSegments seg, float* packed, long long wn, long long bn, int acc) {
+    griddep_wait();
+    const long long total = 3 * (wn + bn) / VEC;
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    for (long long v = (long long)blockIdx.x * blockDim.x + threadIdx.x; v < total; v += stride) {
+        const long long i = v * VEC;
+        float* base;
+        long long j;
+        if (i < 3 * wn) { const int s = (int)(i / wn); base = seg.w[s]; j = i - s * wn; }
+        else { const long long r = i - 3 * wn; const int s = (int)(r / bn); base = seg.b[s]; j = r - s * bn; }
+        if (VEC == 4) {
+            float4* pk = reinterpret_cast<float4*>(packed + i);
+            if (PACK) {
+                *pk = base ? *reinterpret_cast<const float4*>(base + j) : make_float4(0.f, 0.f, 0.f, 0.f);
+            } else if (base) {
+                float4 g = *pk;
+                float4* dst = reinterpret_cast<float4*>(base + j);
+                if (acc) { const float4 o = *dst; g.x += o.x; g.y += o.y; g.z += o.z; g.w += o.w; }
+                *dst = g;
+            }
+        } else {
+            if (PACK) packed[i] = base ? base[j] : 0.f;
+            else if (base) base[j] = acc ? base[j] + packed[i] : packed[i];
+        }
+    }
+}
+
 static int grid_for(long long work_items, int per_block, int sm_count) {
     long long blocks = (work_items + per_block - 1) / per_block;
     const long long cap = (long long)sm_count * 8;
@@ -561,6 +594,42 @@ int launch_colsum(te_b200_ctx* ctx, const float* in, int64_t rows, int64_t cols,
     if (e != cudaSuccess) return cuda_fail(e, "colsum_kernel launch");
     ctx->launches += 1;
     return TE_OK;
+}
+
+static int launch_qkv_segments(te_b200_ctx* ctx, bool pack, float* const w[3], float* const b[3], float* packed, int64_t wn,
+                               int64_t bn, bool accumulate, cudaStream_t st) {
+    if (wn + bn == 0) return TE_OK;
+    SixSegments seg;
+    uintptr_t bits = reinterpret_cast<uintptr_t>(packed);
+    for (int i = 0; i < 3; ++i) {
+        seg.w[i] = w[i]; seg.b[i] = b[i];
+        bits |= reinterpret_cast<uintptr_t>(w[i]) | reinterpret_cast<uintptr_t>(b[i]);
+    }
+    const bool vec = (bits & 15) == 0 && (wn & 3) == 0 && (bn & 3) == 0;
+    const long long items = 3 * (wn + bn) / (vec ? 4 : 1);
+    const dim3 grid(grid_for(items, 256, ctx->sm_count)), block(256);
+    const int acc = accumulate ? 1 : 0;
+    if (pack && vec) launch_pdl(qkv_segments_kernel<true, 4>, grid, block, 0, st, seg, packed, (long long)wn, (long long)bn, acc);
+    else if (pack) launch_pdl(qkv_segments_kernel<true, 1>, grid, block, 0, st, seg, packed, (long long)wn, (long long)bn, acc);
+    else if (vec) launch_pdl(qkv_segments_kernel<false, 4>, grid, block, 0, st, seg, packed, (long long)wn, (long long)bn, acc);
+    else launch_pdl(qkv_segments_kernel<false, 1>, grid, block, 0, st, seg, packed, (long long)wn, (long long)bn, acc);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return cuda_fail(e, "qkv_segments_kernel launch");
+    ctx->launches += 1;
+    return TE_OK;
+}
+
+// packed = w0 | w1 | w2 | b0 | b1 | b2  (wn floats per weight, bn per bias; NULL sources pack zeros)
+int launch_pack_qkv(te_b200_ctx* ctx, const float* const w[3], const float* const b[3], float* packed, int64_t wn, int64_t bn,
+                    cudaStream_t st) {
+    float* wm[3]; float* bm[3];
+    for (int i = 0; i < 3; ++i) { wm[i] = const_cast<float*>(w[i]); bm[i] = const_cast<float*>(b[i]); }
+    return launch_qkv_segments(ctx, true, wm, bm, packed, wn, bn, false, st);
+}
+// the reverse, for gradients: NULL destinations are skipped, accumulate adds to the destinations
+int launch_unpack_qkv(te_b200_ctx* ctx, const float* packed, float* const w[3], float* const b[3], int64_t wn, int64_t bn,
+                      bool accumulate, cudaStream_t st) {
+    return launch_qkv_segments(ctx, false, w, b, const_cast<float*>(packed), wn, bn, accumulate, st);
 }
 
 }  // namespace te

@@ -140,6 +140,10 @@ int launch_gelu_backward_colsum(te_b200_ctx*, const float* x, const float* dy, f
                                 float* colsum_out, cudaStream_t);
 int launch_colsum(te_b200_ctx*, const float* in, int64_t rows, int64_t cols, int64_t ld, float* out, bool accumulate,
                   cudaStream_t);
+int launch_pack_qkv(te_b200_ctx*, const float* const w[3], const float* const b[3], float* packed, int64_t wn, int64_t bn,
+                    cudaStream_t st);
+int launch_unpack_qkv(te_b200_ctx*, const float* packed, float* const w[3], float* const b[3], int64_t wn, int64_t bn,
+                      bool accumulate, cudaStream_t st);
 
 // norm_embed_loss.cu: the GPT step's kernels around the matmuls
 int launch_layernorm_forward(te_b200_ctx*, const float* x, const float* gamma, const float* beta, float* y, int64_t rows,

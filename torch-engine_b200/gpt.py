@@ -5,8 +5,9 @@ the optimizer): GPT::forward (src/nn/gpt.cpp:26-86) -> crossEntropyLoss::forward
 The step is an explicit schedule of C-ABI calls over buffers allocated once per configuration: nothing in it is a
 torch operator, torch only owns the memory.  Per pre-LN block (src/nn/transformer_block.cpp:15-35):
 
-  forward   LayerNorm -> te_b200_mha_forward (three projections, attention on head views, out projection, the block's
-            residual input added in the last GEMM's epilogue) -> LayerNorm -> Linear+GELU (pre-activation kept) ->
+  forward   LayerNorm -> te_b200_mha_forward (the three projections as one product against the gathered [3E,E]
+            weight, attention on head views, out projection, the block's residual input added in the last GEMM's
+            epilogue) -> LayerNorm -> Linear+GELU (pre-activation kept) ->
             Linear with the second residual in its epilogue;
   backward  te_b200_linear_backward_ex twice (the first hands back the gradient of the GELU's pre-activation and,
             from the same pass, its column sums = the bias gradient of the first FeedForward Linear),
@@ -83,16 +84,18 @@ class GptStep:
         self.x = [bte() for _ in range(n_layers + 1)]          # block inputs; x[0] is the embedding output
         self.layers = []
         for _ in range(n_layers):
-            self.layers.append(dict(h1=bte(), q=bte(), k=bte(), v=bte(), attn=bte(), y1=bte(), h2=bte(),
-                                    p=torch.empty(B, H, T, T, **f32), pre=torch.empty(B, T, ff, **f32),
-                                    f=torch.empty(B, T, ff, **f32)))
+            # qkv: the three projections as column blocks of one buffer (one GEMM against the gathered weights wqkv)
+            self.layers.append(dict(h1=bte(), qkv=torch.empty(B, T, 3 * E, **f32), wqkv=torch.empty(3 * E * E + 3 * E, **f32),
+                                    attn=bte(), y1=bte(), h2=bte(), p=torch.empty(B, H, T, T, **f32),
+                                    pre=torch.empty(B, T, ff, **f32), f=torch.empty(B, T, ff, **f32)))
         self.hf = bte()
         self.logits = torch.empty(B, T, vocab, **f32)
         self.dlogits = torch.empty(B, T, vocab, **f32)
         self.loss = torch.empty(1, **f32)
         # backward scratch
         self.dxa, self.dxb, self.dh = bte(), bte(), bte()
-        self.dq, self.dk, self.dv, self.dattn = bte(), bte(), bte(), bte()
+        self.dqkv, self.dattn = torch.empty(B, T, 3 * E, **f32), bte()
+        self.dwqkv = torch.empty(3 * E * E + 3 * E, **f32)
         self.dpre = torch.empty(B, T, ff, **f32)
         self.pos = positional_table(T, E, dev)
 
@@ -126,7 +129,9 @@ class GptStep:
             m.x = a["h1"].data_ptr()
             for n, j in zip(("wq", "bq", "wk", "bk", "wv", "bv", "wo", "bo"), range(i + 2, i + 10)):
                 setattr(m, n, self._p(flat_params, j))
-            m.q, m.k, m.v, m.p, m.attn = (a[n].data_ptr() for n in ("q", "k", "v", "p", "attn"))
+            q = a["qkv"].data_ptr()
+            m.q, m.k, m.v, m.ld_qkv, m.wqkv = q, q + 4 * E, q + 8 * E, 3 * E, a["wqkv"].data_ptr()
+            m.p, m.attn = a["p"].data_ptr(), a["attn"].data_ptr()
             m.y, m.residual, m.precision = a["y1"].data_ptr(), self.x[l].data_ptr(), prec
             L.check(lib.te_b200_mha_forward(ctx, C.byref(m), st))                       # y1 = x + MHA(LN1(x))
             L.check(lib.te_b200_layernorm_forward(ctx, ptr(a["y1"]), P(i + 10), P(i + 11), ptr(a["h2"]), rows, E, eps, st))
@@ -171,12 +176,14 @@ class GptStep:
             m.B, m.T, m.E, m.H = B, T, E, H
             m.x = a["h1"].data_ptr()
             m.wq, m.wk, m.wv, m.wo = (self._p(flat_params, j) for j in (i + 2, i + 4, i + 6, i + 8))
-            m.q, m.k, m.v, m.p, m.attn = (a[n].data_ptr() for n in ("q", "k", "v", "p", "attn"))
+            q, dq = a["qkv"].data_ptr(), self.dqkv.data_ptr()
+            m.q, m.k, m.v, m.ld_qkv, m.wqkv = q, q + 4 * E, q + 8 * E, 3 * E, a["wqkv"].data_ptr()
+            m.p, m.attn = a["p"].data_ptr(), a["attn"].data_ptr()
             m.dy, m.dx, m.dx_residual = self.dxb.data_ptr(), self.dh.data_ptr(), None
             for n, j in zip(("dwq", "dbq", "dwk", "dbk", "dwv", "dbv", "dwo"), range(i + 2, i + 9)):
                 setattr(m, n, self._g(j))
             m.dbo = None                                                               # came with the LayerNorm backward above
-            m.dq, m.dk, m.dv, m.dattn = (t.data_ptr() for t in (self.dq, self.dk, self.dv, self.dattn))
+            m.dq, m.dk, m.dv, m.dattn, m.dwqkv = dq, dq + 4 * E, dq + 8 * E, self.dattn.data_ptr(), self.dwqkv.data_ptr()
             m.accumulate, m.precision = 0, prec
             L.check(lib.te_b200_mha_backward(ctx, C.byref(m), st))                     # gradient of LN1's output
             # gradient of x[l]; for l > 0 its column sums are the bias gradient of block l-1's second FeedForward Linear

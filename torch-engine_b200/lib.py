@@ -67,7 +67,8 @@ class MhaDesc(C.Structure):
     """struct te_mha_desc"""
     _fields_ = [("B", C.c_int64), ("T", C.c_int64), ("E", C.c_int64), ("H", C.c_int64), ("x", C.c_void_p)] + \
                [(n, C.c_void_p) for n in ("wq", "bq", "wk", "bk", "wv", "bv", "wo", "bo", "q", "k", "v", "p", "attn", "y",
-                                          "residual")] + [("precision", C.c_int32), ("reserved", C.c_int32)]
+                                          "residual")] + [("precision", C.c_int32), ("reserved", C.c_int32),
+                                                         ("wqkv", C.c_void_p), ("ld_qkv", C.c_int64)]
 
 
 class MhaBwdDesc(C.Structure):
@@ -75,7 +76,8 @@ class MhaBwdDesc(C.Structure):
     _fields_ = [("B", C.c_int64), ("T", C.c_int64), ("E", C.c_int64), ("H", C.c_int64)] + \
                [(n, C.c_void_p) for n in ("x", "wq", "wk", "wv", "wo", "q", "k", "v", "p", "attn", "dy", "dx", "dx_residual",
                                           "dwq", "dbq", "dwk", "dbk", "dwv", "dbv", "dwo", "dbo", "dq", "dk", "dv",
-                                          "dattn")] + [("accumulate", C.c_int32), ("precision", C.c_int32)]
+                                          "dattn")] + [("accumulate", C.c_int32), ("precision", C.c_int32),
+                                                      ("wqkv", C.c_void_p), ("dwqkv", C.c_void_p), ("ld_qkv", C.c_int64)]
 
 
 # name -> (restype, argtypes); every symbol include/te_b200.h declares

@@ -165,15 +165,22 @@ class Backend:
         return (dx, dw, db, dxs) if want_dx_colsum else (dx, dw, db)
 
     # ------------------------------------------------------------------ multi-head attention
-    def mha_forward(self, x, params, heads, residual=None, precision="tf32"):
+    def mha_forward(self, x, params, heads, residual=None, precision="tf32", one_projection_gemm=True):
         """MultiHeadAttention::forward for x [B,T,E]; params in parameters() order (wq,bq,wk,bk,wv,bv,wo,bo).
-        Returns (y, saved) where saved holds what mha_backward needs."""
+        Returns (y, saved) where saved holds what mha_backward needs.  one_projection_gemm: the three projections as
+        one product against the gathered [3E,E] weight (q, k, v are then column blocks of one [B,T,3E] buffer);
+        False runs them as three products into three dense buffers."""
         self._check_f32_cuda(x, residual, *params)
         x = x.contiguous()
         B, T, E = x.shape
         new = lambda *shape: torch.empty(shape, dtype=torch.float32, device=x.device)
-        saved = dict(x=x, q=new(B, T, E), k=new(B, T, E), v=new(B, T, E), p=new(B, heads, T, T), attn=new(B, T, E),
-                     params=[t.contiguous() for t in params], heads=heads)
+        saved = dict(x=x, p=new(B, heads, T, T), attn=new(B, T, E), params=[t.contiguous() for t in params], heads=heads,
+                     fused=bool(one_projection_gemm))
+        if one_projection_gemm:
+            saved["qkv"], saved["wqkv"] = new(B, T, 3 * E), new(3 * E * E + 3 * E)
+            saved["q"], saved["k"], saved["v"] = (saved["qkv"][:, :, i * E:(i + 1) * E] for i in range(3))
+        else:
+            saved["q"], saved["k"], saved["v"] = new(B, T, E), new(B, T, E), new(B, T, E)
         y = new(B, T, E)
         m = L.MhaDesc()
         m.B, m.T, m.E, m.H = B, T, E, heads
@@ -182,6 +189,8 @@ class Backend:
             setattr(m, n, t.data_ptr())
         for n in ("q", "k", "v", "p", "attn"):
             setattr(m, n, saved[n].data_ptr())
+        if one_projection_gemm:
+            m.ld_qkv, m.wqkv = 3 * E, saved["wqkv"].data_ptr()
         m.y = y.data_ptr()
         m.residual = residual.contiguous().data_ptr() if residual is not None else None
         m.precision = _prec(precision)
@@ -196,7 +205,7 @@ class Backend:
         B, T, E = x.shape
         dx = torch.empty_like(x)
         grads = [torch.empty_like(t) for t in saved["params"]]
-        scratch = [torch.empty_like(x) for _ in range(4)]
+        dattn = torch.empty_like(x)
         m = L.MhaBwdDesc()
         m.B, m.T, m.E, m.H = B, T, E, saved["heads"]
         m.x = x.data_ptr()
@@ -207,7 +216,14 @@ class Backend:
         m.dx_residual = dx_residual.contiguous().data_ptr() if dx_residual is not None else None
         for n, t in zip(("dwq", "dbq", "dwk", "dbk", "dwv", "dbv", "dwo", "dbo"), grads):
             setattr(m, n, t.data_ptr())
-        m.dq, m.dk, m.dv, m.dattn = (t.data_ptr() for t in scratch)
+        if saved["fused"]:
+            dqkv, dwqkv = torch.empty_like(saved["qkv"]), torch.empty_like(saved["wqkv"])
+            m.dq, m.dk, m.dv = (dqkv.data_ptr() + 4 * E * i for i in range(3))
+            m.ld_qkv, m.wqkv, m.dwqkv = 3 * E, saved["wqkv"].data_ptr(), dwqkv.data_ptr()
+        else:
+            scratch = [torch.empty_like(x) for _ in range(3)]
+            m.dq, m.dk, m.dv = (t.data_ptr() for t in scratch)
+        m.dattn = dattn.data_ptr()
         m.accumulate, m.precision = 0, _prec(precision)
         L.check(self._lib.te_b200_mha_backward(self._ctx, C.byref(m), self._stream()))
         return dx, grads
