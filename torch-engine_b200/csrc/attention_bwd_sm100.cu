@@ -18,10 +18,13 @@
 //   warps   P^T from global memory (lane = key: a warp reads 128 contiguous bytes of one row of P), then
 //           dS^T = P^T o (dP^T - D_query) / sqrt(d)    -> TMEM [0,128) in place, P^T -> TMEM [128,256),
 //           and dS^T also into shared memory in the M-major operand layout (for dQ, whose left operand is dS)
-//   MMA 2   dV_j += P^T  . dO_i   (A from TMEM)        -> TMEM [256,320)
-//   MMA 3   dK_j += dS^T . Q_i    (A from TMEM)        -> TMEM [320,384)
-//   MMA 4   dQ_i += dS   . K_j    (A from shared)      -> TMEM [384 + 64 i, ..)
-// dV_j and dK_j leave after the last query block, dQ after the last key block, through TMA stores.
+//   MMA 2   dQ_i += dS   . K_j    (A from shared)      -> TMEM [384 + 64 i, ..)
+//   MMA 3   dV_j += P^T  . dO_i   (A from TMEM)        -> TMEM [256,320)
+//   MMA 4   dK_j += dS^T . Q_i    (A from TMEM)        -> TMEM [320,384)
+// The dQ product goes first because it is the only reader of the dS^T tile in shared memory: once it is done the next
+// step's block of P may land there, while MMAs 3 and 4 are still running.
+// dV_j and dK_j leave after the last query block, dQ after the last key block, through TMA stores staged in the
+// dO / Q operand buffers (free at that point; for d = 32 they are too small and the dS^T region is used instead).
 // Warp roles as in the forward kernel: warp 8 TMA producer, warp 9 MMA issue, warps 0-7 element work and output
 // (warp w: TMEM lanes 32 (w % 4).., query-column half w / 4).  All waits are bounded.
 // Limits: TF32 mode, T <= 256, T % 4 == 0, d in {32, 64}; other problems take the GEMM sequence.
@@ -118,6 +121,9 @@ attention_bwd_tf32_kernel(const __grid_constant__ CUtensorMap tm_v, const __grid
     const uint32_t tmem_slot_addr = aux_addr + 80;
     volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(aux + 80);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(aux + 84);
+    const uint32_t bar_dsfree = aux_addr + 88; // the dQ product has read dS^T: the region may take the next P block (MMA -> producer)
+    // Output staging: in the dO (N-major) + Q buffers when they hold 64 KB together, else in the dS^T region.
+    const bool stage_in_operands = dchunks == 2;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
@@ -132,6 +138,7 @@ attention_bwd_tf32_kernel(const __grid_constant__ CUtensorMap tm_v, const __grid
         mbar_init(bar_td, 1);
         mbar_init(bar_p, 1);
         mbar_init(bar_pr, EPI_WARPS);
+        mbar_init(bar_dsfree, 1);
         *abort_flag = 0;
         fence_barrier_init();
         fence_proxy_async_smem();
@@ -177,36 +184,42 @@ attention_bwd_tf32_kernel(const __grid_constant__ CUtensorMap tm_v, const __grid
                             tma_load_4d(dok_smem + c * BWD_CHUNK, &tm_dok, bar_a, 32 * c, 128 * i, h, b);
                             if (i == 0) tma_load_4d(v_smem + c * BWD_CHUNK, &tm_v, bar_a, 32 * c, 128 * j, h, b);
                         }
+                        // The dS^T region takes the step's P block.  It is free once the previous step's dQ product is done
+                        // and, where outputs are staged in it, once the stores of a key block's last step have read them.
+                        // The operands of MMAs 3-4 follow when all of the previous step's MMAs are done and, where the
+                        // outputs are staged in their buffers, the stores have read those.
+                        const bool after_outputs = s > 0 && i == 0;
+                        if (s > 0 && !wait_bounded(bar_dsfree, (s - 1) & 1, abort_flag, p.status, WAIT_PRODUCER_EMPTY)) {
+                            ok = false;
+                            break;
+                        }
+                        const bool p_first = !(after_outputs && !stage_in_operands);
+                        if (p_first) {
+                            mbar_arrive_expect_tx(bar_p, p.pbox * p.pbox * 4);
+                            tma_load_4d(ds_smem, &tm_p, bar_p, 128 * j, 128 * i, h, b);
+                        }
                         if (s > 0 && !wait_bounded(bar_step, (s - 1) & 1, abort_flag, p.status, WAIT_PRODUCER_EMPTY)) {
                             ok = false;
                             break;
                         }
-                        // The dS^T region takes the step's P block.  It is free once the previous step's MMA 4 is done
-                        // (waited for above) and, after a key block's last step, once the outputs staged in it have been
-                        // read by their stores.  The element warps need P first, so it goes ahead of the operands of
-                        // MMAs 2-4 unless it has to wait for those stores.
-                        const bool after_outputs = s > 0 && i == 0;
-                        for (int pass = 0; pass < 2; ++pass) {
-                            if ((pass == 0) != after_outputs) {
-                                if (after_outputs) {
-                                    if (!wait_bounded(bar_free, jc & 1, abort_flag, p.status, WAIT_PRODUCER_EMPTY)) {
-                                        ok = false;
-                                        break;
-                                    }
-                                    ++jc;
-                                }
-                                mbar_arrive_expect_tx(bar_p, p.pbox * p.pbox * 4);
-                                tma_load_4d(ds_smem, &tm_p, bar_p, 128 * j, 128 * i, h, b);
-                            } else {
-                                mbar_arrive_expect_tx(bar_b, i == 0 ? 3 * opnd : 2 * opnd);
-                                for (int c = 0; c < dchunks; ++c) {
-                                    for (int kb = 0; kb < 4; ++kb) {
-                                        tma_load_4d(dom_smem + c * BWD_CHUNK + kb * 4096, &tm_dom, bar_b, 32 * c, 128 * i + 32 * kb, h, b);
-                                        tma_load_4d(q_smem + c * BWD_CHUNK + kb * 4096, &tm_q, bar_b, 32 * c, 128 * i + 32 * kb, h, b);
-                                        if (i == 0)
-                                            tma_load_4d(k_smem + c * BWD_CHUNK + kb * 4096, &tm_k, bar_b, 32 * c, 128 * j + 32 * kb, h, b);
-                                    }
-                                }
+                        if (after_outputs) {
+                            if (!wait_bounded(bar_free, jc & 1, abort_flag, p.status, WAIT_PRODUCER_EMPTY)) {
+                                ok = false;
+                                break;
+                            }
+                            ++jc;
+                        }
+                        if (!p_first) {
+                            mbar_arrive_expect_tx(bar_p, p.pbox * p.pbox * 4);
+                            tma_load_4d(ds_smem, &tm_p, bar_p, 128 * j, 128 * i, h, b);
+                        }
+                        mbar_arrive_expect_tx(bar_b, i == 0 ? 3 * opnd : 2 * opnd);
+                        for (int c = 0; c < dchunks; ++c) {
+                            for (int kb = 0; kb < 4; ++kb) {
+                                tma_load_4d(dom_smem + c * BWD_CHUNK + kb * 4096, &tm_dom, bar_b, 32 * c, 128 * i + 32 * kb, h, b);
+                                tma_load_4d(q_smem + c * BWD_CHUNK + kb * 4096, &tm_q, bar_b, 32 * c, 128 * i + 32 * kb, h, b);
+                                if (i == 0)
+                                    tma_load_4d(k_smem + c * BWD_CHUNK + kb * 4096, &tm_k, bar_b, 32 * c, 128 * j + 32 * kb, h, b);
                             }
                         }
                         if (!ok) break;
@@ -256,6 +269,13 @@ attention_bwd_tf32_kernel(const __grid_constant__ CUtensorMap tm_v, const __grid
                         tc_fence_after_sync();
 #pragma unroll
                         for (int kk = 0; kk < 16; ++kk) {
+                            const uint64_t da = make_smem_desc(ds_smem + kk * 1024, BWD_CHUNK, 512, SMEM_LAYOUT_SW128_BASE32B);
+                            const uint64_t db = make_smem_desc(k_smem + kk * 1024, BWD_CHUNK, 512, SMEM_LAYOUT_SW128_BASE32B);
+                            umma_tf32(tmem_base + BWD_COL_DQ + i * 64, da, db, idesc_dq, (j | kk) != 0);
+                        }
+                        umma_commit(bar_dsfree);
+#pragma unroll
+                        for (int kk = 0; kk < 16; ++kk) {
                             const uint64_t db = make_smem_desc(dom_smem + kk * 1024, BWD_CHUNK, 512, SMEM_LAYOUT_SW128_BASE32B);
                             umma_tf32_a_tmem(tmem_base + BWD_COL_DV, tmem_base + BWD_COL_P + kk * 8, db, idesc_ta, (i | kk) != 0);
                         }
@@ -263,12 +283,6 @@ attention_bwd_tf32_kernel(const __grid_constant__ CUtensorMap tm_v, const __grid
                         for (int kk = 0; kk < 16; ++kk) {
                             const uint64_t db = make_smem_desc(q_smem + kk * 1024, BWD_CHUNK, 512, SMEM_LAYOUT_SW128_BASE32B);
                             umma_tf32_a_tmem(tmem_base + BWD_COL_DK, tmem_base + BWD_COL_DP + kk * 8, db, idesc_ta, (i | kk) != 0);
-                        }
-#pragma unroll
-                        for (int kk = 0; kk < 16; ++kk) {
-                            const uint64_t da = make_smem_desc(ds_smem + kk * 1024, BWD_CHUNK, 512, SMEM_LAYOUT_SW128_BASE32B);
-                            const uint64_t db = make_smem_desc(k_smem + kk * 1024, BWD_CHUNK, 512, SMEM_LAYOUT_SW128_BASE32B);
-                            umma_tf32(tmem_base + BWD_COL_DQ + i * 64, da, db, idesc_dq, (j | kk) != 0);
                         }
                         umma_commit(bar_step);
                     }
@@ -282,8 +296,8 @@ attention_bwd_tf32_kernel(const __grid_constant__ CUtensorMap tm_v, const __grid
         const uint32_t t_row = tmem_base + (uint32_t(quad * 32) << 16);
         const int krow = quad * 32 + lane;                       // this thread's key row within the key block
         const uint32_t swz = uint32_t(lane & 3) << 1;            // 32-byte-atom swizzle of that row, in 16-byte units
-        // This warp's two 4 KB blocks of the dS^T tile double as its output staging tiles.
-        const uint32_t my_blk0 = ds_smem + (half * 2) * BWD_CHUNK + quad * 4096;
+        // This warp's two 4 KB output staging tiles: blocks of the dO (N-major) + Q buffers, or of the dS^T tile.
+        const uint32_t my_blk0 = (stage_in_operands ? dom_smem : ds_smem) + (half * 2) * BWD_CHUNK + quad * 4096;
         int s = 0, jc = 0, tc = 0;
         bool ok = true;
         EpilogueRow er;
@@ -387,7 +401,7 @@ attention_bwd_tf32_kernel(const __grid_constant__ CUtensorMap tm_v, const __grid
                         }
                     }
                     tc_fence_before_sync();
-                    if (lane == 0) bulk_wait_read_all();       // the staging blocks go back to the producer (next P block)
+                    if (lane == 0) bulk_wait_read_all();       // the staging blocks go back to the producer
                     __syncwarp();
                     if (lane == 0) mbar_arrive(bar_free);
                 }
