@@ -65,11 +65,34 @@ private:
     int precision_ = TE_PREC_TF32;
 };
 
-// Device memory for tensors, cached by block size.  The reference's CUDAAllocator calls cudaMalloc / cudaFree for every
-// tensor (src/core/allocators.h:35-52); both synchronise the device, and a training step creates hundreds of
-// temporaries.  Here a freed block goes to a free list of its (rounded) size and the next tensor of that size takes
-// it without touching the driver.  All work of this adapter is issued on the default stream, so a block handed out
-// again is only written by kernels that the stream orders after its last use.
+// The CUDA stream this thread's adapter calls are issued on.  Default: the legacy default stream, like the reference's
+// launches.  StreamGuard switches it for a scope.  One te_b200 context serves the process, so calls that use its
+// workspace must not run concurrently on two streams (te_b200.h); one thread moving from stream to stream is fine.
+inline cudaStream_t& current_stream_slot() {
+    static thread_local cudaStream_t s = nullptr;
+    return s;
+}
+inline cudaStream_t current_stream() { return current_stream_slot(); }
+class StreamGuard {
+public:
+    explicit StreamGuard(cudaStream_t s) : previous_(current_stream_slot()) { current_stream_slot() = s; }
+    ~StreamGuard() { current_stream_slot() = previous_; }
+    StreamGuard(const StreamGuard&) = delete;
+    StreamGuard& operator=(const StreamGuard&) = delete;
+private:
+    cudaStream_t previous_;
+};
+
+// Device memory for tensors, cached by block size, with stream-ordered reuse.  The reference's CUDAAllocator calls
+// cudaMalloc / cudaFree for every tensor (src/core/allocators.h:35-52); both synchronise the device, and a training step
+// creates hundreds of temporaries.  Here a freed block goes to a free list of its (rounded) size and the next tensor
+// of that size takes it without touching the driver and without waiting for the GPU:
+//   * a block belongs to the stream that was current when it was allocated (plus any stream named through
+//     record_stream); freeing it costs nothing, because work queued on that stream after the free runs after the
+//     block's last use anyway;
+//   * a request from the same stream takes the block as it is; a request from another stream takes it after making
+//     that stream wait (cudaStreamWaitEvent, no host wait) for an event recorded now on the block's streams.
+// set_caching(false) turns it into the reference's behaviour (cudaMalloc / cudaFree per tensor) for comparisons.
 class CachingAllocator {
 public:
     static CachingAllocator& instance() {
@@ -81,17 +104,29 @@ public:
         if (bytes < (size_t(1) << 20)) return (bytes + 511) & ~size_t(511);
         return (bytes + (size_t(2) << 20) - 1) & ~((size_t(2) << 20) - 1);      // large blocks in 2 MiB steps
     }
-    void* allocate(size_t bytes, size_t* block_bytes) {
+    void* allocate(size_t bytes, size_t* block_bytes) { return allocate(bytes, block_bytes, current_stream()); }
+    void* allocate(size_t bytes, size_t* block_bytes, cudaStream_t stream) {
         const size_t n = rounded(bytes);
         *block_bytes = n;
         {
             std::lock_guard<std::mutex> g(mu_);
-            auto it = free_.find(n);
-            if (it != free_.end()) {
-                void* p = it->second;
-                free_.erase(it);
+            auto range = free_.equal_range(n);
+            auto pick = range.second;
+            for (auto it = range.first; it != range.second; ++it) {
+                if (it->second.used_only_on(stream)) { pick = it; break; }      // same stream: no ordering needed
+                if (pick == range.second) pick = it;
+            }
+            if (pick != range.second) {
+                Block blk = std::move(pick->second);
+                free_.erase(pick);
+                if (!blk.used_only_on(stream)) {
+                    order_after(stream, blk.stream);
+                    for (cudaStream_t s : blk.also) order_after(stream, s);
+                    ++cross_stream_reuses_;
+                }
                 ++hits_;
-                return p;
+                live_[blk.ptr] = Block{blk.ptr, stream, {}};
+                return blk.ptr;
             }
         }
         void* p = nullptr;
@@ -104,27 +139,69 @@ public:
         cuda_check(e, "cudaMalloc");
         std::lock_guard<std::mutex> g(mu_);
         ++device_mallocs_;
+        live_[p] = Block{p, stream, {}};
         return p;
     }
-    void release(void* p, size_t block_bytes) {
+    // The block is (also) used by work on `stream`: reuse from any other stream will wait for that work too.
+    void record_stream(void* p, cudaStream_t stream) {
         std::lock_guard<std::mutex> g(mu_);
-        free_.emplace(block_bytes, p);
+        auto it = live_.find(p);
+        if (it == live_.end() || it->second.stream == stream) return;
+        for (cudaStream_t s : it->second.also)
+            if (s == stream) return;
+        it->second.also.push_back(stream);
+    }
+    void release(void* p, size_t block_bytes) {
+        bool give_back = false;
+        {
+            std::lock_guard<std::mutex> g(mu_);
+            auto it = live_.find(p);
+            Block blk = it != live_.end() ? std::move(it->second) : Block{p, nullptr, {}};
+            if (it != live_.end()) live_.erase(it);
+            if (caching_) free_.emplace(block_bytes, std::move(blk));
+            else give_back = true;
+        }
+        if (give_back) cudaFree(p);      // waits for the device, as the reference's allocator does
     }
     void empty_cache() {
-        std::multimap<size_t, void*> blocks;
+        std::multimap<size_t, Block> blocks;
         {
             std::lock_guard<std::mutex> g(mu_);
             blocks.swap(free_);
         }
-        for (auto& kv : blocks) cudaFree(kv.second);
+        for (auto& kv : blocks) cudaFree(kv.second.ptr);
     }
-    size_t device_mallocs() const { return device_mallocs_; }   // cudaMalloc calls so far
+    void set_caching(bool on) {
+        {
+            std::lock_guard<std::mutex> g(mu_);
+            caching_ = on;
+        }
+        if (!on) empty_cache();
+    }
+    size_t device_mallocs() const { return device_mallocs_; }            // cudaMalloc calls so far
     size_t cache_hits() const { return hits_; }
+    size_t cross_stream_reuses() const { return cross_stream_reuses_; }  // hits that had to order one stream after another
 private:
+    struct Block {
+        void* ptr;
+        cudaStream_t stream;                 // the stream the block was allocated for
+        std::vector<cudaStream_t> also;      // further streams named through record_stream
+        bool used_only_on(cudaStream_t s) const { return stream == s && also.empty(); }
+    };
     CachingAllocator() = default;
+    // Work queued on `waiter` from now on runs after everything queued on `other` so far.  Called with mu_ held.
+    void order_after(cudaStream_t waiter, cudaStream_t other) {
+        if (waiter == other) return;
+        if (!event_) cuda_check(cudaEventCreateWithFlags(&event_, cudaEventDisableTiming), "cudaEventCreateWithFlags");
+        cuda_check(cudaEventRecord(event_, other), "cudaEventRecord");
+        cuda_check(cudaStreamWaitEvent(waiter, event_, 0), "cudaStreamWaitEvent");   // captures the record above; the event may be re-recorded at once
+    }
     std::mutex mu_;
-    std::multimap<size_t, void*> free_;
-    size_t device_mallocs_ = 0, hits_ = 0;
+    std::multimap<size_t, Block> free_;
+    std::map<void*, Block> live_;
+    cudaEvent_t event_ = nullptr;
+    bool caching_ = true;
+    size_t device_mallocs_ = 0, hits_ = 0, cross_stream_reuses_ = 0;
 };
 
 class Tensor {
@@ -141,7 +218,8 @@ public:
     static Tensor from_host(const std::vector<float>& v, std::vector<int64_t> shape) {
         Tensor t(std::move(shape));
         if (v.size() != t.numel()) throw std::runtime_error("from_host: element count does not match the shape");
-        cuda_check(cudaMemcpy(t.data(), v.data(), v.size() * sizeof(float), cudaMemcpyHostToDevice), "cudaMemcpy H2D");
+        cuda_check(cudaMemcpyAsync(t.data(), v.data(), v.size() * sizeof(float), cudaMemcpyHostToDevice, current_stream()), "cudaMemcpy H2D");
+        cuda_check(cudaStreamSynchronize(current_stream()), "cudaStreamSynchronize");      // v may go away after the call
         return t;
     }
     // Row-major copy of the logical contents (views are gathered on the host side).
@@ -152,7 +230,8 @@ public:
         std::vector<float> raw((size_t)(hi - lo + 1));
         std::vector<float> out(numel());
         if (out.empty()) return out;
-        cuda_check(cudaMemcpy(raw.data(), data() + lo, raw.size() * sizeof(float), cudaMemcpyDeviceToHost), "cudaMemcpy D2H");
+        cuda_check(cudaMemcpyAsync(raw.data(), data() + lo, raw.size() * sizeof(float), cudaMemcpyDeviceToHost, current_stream()), "cudaMemcpy D2H");
+        cuda_check(cudaStreamSynchronize(current_stream()), "cudaStreamSynchronize");
         std::vector<int64_t> idx(shape_.size(), 0);
         for (size_t flat = 0; flat < out.size(); ++flat) {
             int64_t off = -lo;
@@ -174,6 +253,8 @@ public:
     const std::vector<int64_t>& shape() const { return shape_; }
     const std::vector<int64_t>& strides() const { return strides_; }   // in elements
     float* data() const { return static_cast<float*>(storage_.get()) + offset_; }   // includes the view offset
+    // Tells the allocator that work on `stream` (other than the one the tensor was created on) uses this tensor.
+    void record_stream(cudaStream_t stream) const { CachingAllocator::instance().record_stream(storage_.get(), stream); }
     bool is_contiguous() const {
         int64_t run = 1;
         for (int i = (int)shape_.size() - 1; i >= 0; --i) {
@@ -216,7 +297,7 @@ public:
         Backend& be = Backend::instance();
         check(te_b200_matmul_nd(be.ctx(), data(), shape_.data(), strides_.data(), (int)shape_.size(), other.data(),
                                 other.shape_.data(), other.strides_.data(), (int)other.shape_.size(), result.data(),
-                                nullptr, nullptr, be.precision(), nullptr));
+                                nullptr, nullptr, be.precision(), current_stream()));
         return result;
     }
 
@@ -250,7 +331,7 @@ private:
             if (shape[i] != 1) throw std::runtime_error("reduce_gradient: only leading broadcast dimensions are supported");
         Tensor out(shape);
         // g is contiguous [lead, target]: the batch sum is a column sum over `lead` rows
-        check(te_b200_colsum_f32(Backend::instance().ctx(), g.data(), lead, (int64_t)target, (int64_t)target, out.data(), nullptr));
+        check(te_b200_colsum_f32(Backend::instance().ctx(), g.data(), lead, (int64_t)target, (int64_t)target, out.data(), current_stream()));
         return out;
     }
 };
@@ -272,15 +353,17 @@ public:
         Backend& be = Backend::instance();
         check(te_b200_linear_forward(be.ctx(), x.data(), weight_.data(), bias_.data(), y.data(),
                                      preact ? preact->data() : nullptr, (int64_t)(x.numel() / (size_t)in_), in_, out_,
-                                     gelu ? 1 : 0, be.precision(), nullptr));
+                                     gelu ? 1 : 0, be.precision(), current_stream()));
         return y;
     }
-    // {dX, dW[out,in], db[out]} in the order the reference's backward nodes produce them.
-    std::vector<Tensor> backward(const Tensor& x, const Tensor& dy) const {
+    // {dX, dW[out,in], db[out]} in the order the reference's backward nodes produce them.  With x_preact (x is then
+    // GELU(x_preact), the output of a forward(.., gelu = true) call) dX is the gradient of the pre-activation.
+    std::vector<Tensor> backward(const Tensor& x, const Tensor& dy, const Tensor* x_preact = nullptr) const {
         Tensor dx(x.shape()), dw({out_, in_}), db({out_});
         Backend& be = Backend::instance();
-        check(te_b200_linear_backward(be.ctx(), x.data(), weight_.data(), dy.data(), dx.data(), dw.data(), db.data(),
-                                      (int64_t)(x.numel() / (size_t)in_), in_, out_, be.precision(), nullptr));
+        check(te_b200_linear_backward_ex(be.ctx(), x.data(), x_preact ? x_preact->data() : nullptr, weight_.data(), dy.data(),
+                                         dx.data(), nullptr, nullptr, dw.data(), db.data(), 0, (int64_t)(x.numel() / (size_t)in_),
+                                         in_, out_, be.precision(), current_stream()));
         return {dx, dw, db};
     }
 private:
@@ -318,7 +401,7 @@ public:
         a.p_out = p.data(); a.o = o.data();
         Backend& be = Backend::instance();
         a.precision = be.precision();
-        check(te_b200_attention_forward(be.ctx(), &a, nullptr));
+        check(te_b200_attention_forward(be.ctx(), &a, current_stream()));
         if (probabilities) *probabilities = p;
         return o;
     }
@@ -346,7 +429,7 @@ public:
         }
         Backend& be = Backend::instance();
         a.precision = be.precision();
-        check(te_b200_attention_backward(be.ctx(), &a, nullptr));
+        check(te_b200_attention_backward(be.ctx(), &a, current_stream()));
         return {dq, dk, dv};
     }
 };
@@ -389,7 +472,7 @@ public:
         m.residual = residual ? residual->data() : nullptr;
         Backend& be = Backend::instance();
         m.precision = be.precision();
-        check(te_b200_mha_forward(be.ctx(), &m, nullptr));
+        check(te_b200_mha_forward(be.ctx(), &m, current_stream()));
         if (saved) *saved = s;
         return y;
     }
@@ -418,7 +501,7 @@ public:
         m.dq = dqkv.data(); m.dk = m.dq + embed_; m.dv = m.dq + 2 * embed_; m.dattn = dattn.data();
         Backend& be = Backend::instance();
         m.precision = be.precision();
-        check(te_b200_mha_backward(be.ctx(), &m, nullptr));
+        check(te_b200_mha_backward(be.ctx(), &m, current_stream()));
         return g;
     }
 private:
@@ -433,7 +516,8 @@ public:
         size_t block = 0;
         void* p = CachingAllocator::instance().allocate((n_ ? n_ : 1) * sizeof(int64_t), &block);
         storage_ = std::shared_ptr<void>(p, [block](void* q) { CachingAllocator::instance().release(q, block); });
-        cuda_check(cudaMemcpy(p, host.data(), n_ * sizeof(int64_t), cudaMemcpyHostToDevice), "cudaMemcpy H2D");
+        cuda_check(cudaMemcpyAsync(p, host.data(), n_ * sizeof(int64_t), cudaMemcpyHostToDevice, current_stream()), "cudaMemcpy H2D");
+        cuda_check(cudaStreamSynchronize(current_stream()), "cudaStreamSynchronize");
     }
     const int64_t* data() const { return static_cast<const int64_t*>(storage_.get()); }
     size_t size() const { return n_; }
@@ -459,7 +543,7 @@ public:
         Tensor y(x.shape());
         Backend& be = Backend::instance();
         check(te_b200_layernorm_forward(be.ctx(), x.data(), weight_.data(), bias_.data(), y.data(),
-                                        (int64_t)(x.numel() / (size_t)dim_), dim_, eps_, nullptr));
+                                        (int64_t)(x.numel() / (size_t)dim_), dim_, eps_, current_stream()));
         return y;
     }
     std::vector<Tensor> backward(const Tensor& x, const Tensor& dy) const {
@@ -468,7 +552,7 @@ public:
         Tensor dx(x.shape()), dg({dim_}), db({dim_});
         Backend& be = Backend::instance();
         check(te_b200_layernorm_backward(be.ctx(), x.data(), weight_.data(), dy.data(), dx.data(), dg.data(), db.data(),
-                                         (int64_t)(x.numel() / (size_t)dim_), dim_, eps_, nullptr));
+                                         (int64_t)(x.numel() / (size_t)dim_), dim_, eps_, current_stream()));
         return {dx, dg, db};
     }
 private:
@@ -489,13 +573,13 @@ public:
         Tensor out({batch, seq_len, dim_});
         Backend& be = Backend::instance();
         check(te_b200_embedding_forward(be.ctx(), weight_.data(), tokens.data(), positional ? positional->data() : nullptr,
-                                        out.data(), batch * seq_len, seq_len, dim_, vocab_, nullptr));
+                                        out.data(), batch * seq_len, seq_len, dim_, vocab_, current_stream()));
         return out;
     }
     Tensor backward(const IndexArray& tokens, const Tensor& dout) const {
         Tensor dw({vocab_, dim_});
         Backend& be = Backend::instance();
-        check(te_b200_embedding_backward(be.ctx(), tokens.data(), dout.data(), dw.data(), (int64_t)tokens.size(), dim_, vocab_, nullptr));
+        check(te_b200_embedding_backward(be.ctx(), tokens.data(), dout.data(), dw.data(), (int64_t)tokens.size(), dim_, vocab_, current_stream()));
         return dw;
     }
 private:
@@ -514,7 +598,7 @@ inline Tensor cross_entropy(const Tensor& logits, const IndexArray& targets, Ten
     Tensor loss({1});
     Tensor grad = dlogits ? Tensor(logits.shape()) : Tensor();
     Backend& be = Backend::instance();
-    check(te_b200_cross_entropy(be.ctx(), logits.data(), targets.data(), loss.data(), dlogits ? grad.data() : nullptr, 1.0f, rows, V, nullptr));
+    check(te_b200_cross_entropy(be.ctx(), logits.data(), targets.data(), loss.data(), dlogits ? grad.data() : nullptr, 1.0f, rows, V, current_stream()));
     if (dlogits) *dlogits = grad;
     return loss;
 }

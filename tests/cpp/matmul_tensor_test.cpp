@@ -211,6 +211,84 @@ int main() {
                 std::cout << "ok   caching allocator reuses blocks\n";
             }
         }
+        {   // stream-ordered reuse: a block freed by work on one stream and taken by another stream is ordered behind it
+            te::Backend::instance().synchronize();
+            cudaStream_t s1 = nullptr, s2 = nullptr;
+            te::cuda_check(cudaStreamCreateWithFlags(&s1, cudaStreamNonBlocking), "cudaStreamCreate");
+            te::cuda_check(cudaStreamCreateWithFlags(&s2, cudaStreamNonBlocking), "cudaStreamCreate");
+            te::CachingAllocator& al = te::CachingAllocator::instance();
+            const int64_t n = 1536;          // a size no other check uses, so the free list holds exactly the blocks below
+            std::vector<float> ones((size_t)(n * n), 1.0f), eye((size_t)(n * n), 0.0f);
+            for (int64_t i = 0; i < n; ++i) eye[(size_t)(i * n + i)] = 2.0f;
+            bool ok = true;
+            float* first_block = nullptr;
+            Tensor a, w, y2;
+            {
+                te::StreamGuard on1(s1);
+                a = Tensor::from_host(ones, {n, n});
+                w = Tensor::from_host(eye, {n, n});
+                Tensor chain = a;
+                for (int it = 0; it < 20; ++it) chain = chain.matmul(w);      // 20 products queued on s1; temporaries reused in stream order
+                first_block = chain.data();
+                y2 = chain;                                                   // keep the last one
+            }
+            const size_t cross0 = al.cross_stream_reuses(), hits0 = al.cache_hits();
+            Tensor z;
+            {
+                te::StreamGuard on2(s2);
+                // the temporaries of the chain above are free blocks of s1 whose kernels may still be running: s2 may
+                // take one, but only behind s1's queue
+                Tensor t = Tensor::from_host(ones, {n, n});
+                z = t.matmul(w);
+            }
+            te::cuda_check(cudaStreamSynchronize(s1), "sync s1");
+            te::cuda_check(cudaStreamSynchronize(s2), "sync s2");
+            ok = ok && al.cache_hits() > hits0 && al.cross_stream_reuses() > cross0;
+            {
+                te::StreamGuard on1(s1);
+                const std::vector<float> got = y2.to_host();       // 2^20 everywhere if no block was overwritten early
+                ok = ok && got[0] == 1048576.0f && got[(size_t)(n * n - 1)] == 1048576.0f && got[(size_t)(n * (n / 2) + 7)] == 1048576.0f;
+            }
+            {
+                te::StreamGuard on2(s2);
+                const std::vector<float> got = z.to_host();
+                ok = ok && got[0] == 2.0f && got[(size_t)(n * n - 1)] == 2.0f;
+            }
+            // record_stream: a tensor of s1 used by work on s2 is only handed to s1 again behind s2
+            {
+                const size_t cross1 = al.cross_stream_reuses();
+                {
+                    Tensor shared_t;
+                    {
+                        te::StreamGuard on1(s1);
+                        shared_t = Tensor::from_host(ones, {n, n});
+                    }
+                    te::StreamGuard on2(s2);
+                    shared_t.record_stream(s2);
+                    Tensor r = shared_t.matmul(w);
+                }   // shared_t and r are free now; shared_t's block lists s1 and s2
+                te::StreamGuard on1(s1);
+                std::vector<Tensor> grab;
+                for (int i = 0; i < 8; ++i) grab.emplace_back(std::vector<int64_t>{n, n});     // drains the free list of this size
+                ok = ok && al.cross_stream_reuses() > cross1;
+            }
+            // the reference's behaviour for comparison runs: every tensor is a cudaMalloc, every release a cudaFree
+            al.set_caching(false);
+            const size_t mallocs0 = al.device_mallocs();
+            { Tensor t1({n, n}); Tensor t2({n, n}); }
+            { Tensor t3({n, n}); }
+            ok = ok && al.device_mallocs() == mallocs0 + 3;
+            al.set_caching(true);
+            (void)first_block;
+            te::cuda_check(cudaStreamDestroy(s1), "cudaStreamDestroy");
+            te::cuda_check(cudaStreamDestroy(s2), "cudaStreamDestroy");
+            if (!ok) {
+                std::cout << "FAIL caching allocator: stream-ordered reuse\n";
+                ++failures;
+            } else {
+                std::cout << "ok   caching allocator orders reuse across streams\n";
+            }
+        }
         te::Backend::instance().synchronize();
     } catch (const std::exception& e) {
         std::cout << "FAIL unexpected exception: " << e.what() << "\n";

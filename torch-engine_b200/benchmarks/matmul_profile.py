@@ -22,7 +22,8 @@ def main():
     ap.add_argument("--n", type=int, default=4096)
     ap.add_argument("--k", type=int, default=4096)
     ap.add_argument("--precision", default="tf32", choices=["tf32", "3xtf32"])
-    ap.add_argument("--layout", default="nn", choices=["nn", "nt"], help="nn: row-major B; nt: column-major B (Linear weight)")
+    ap.add_argument("--layout", default="nn", choices=["nn", "nt", "tn"],
+                    help="nn: row-major A and B; nt: column-major B (Linear weight); tn: column-major A, row-major B (weight gradient dY^T . X)")
     ap.add_argument("--launches", type=int, default=3)
     ap.add_argument("--epilogue", default="none", choices=["none", "bias", "bias_gelu"],
                     help="with --layout nt: run the product as Linear::forward with the bias (and GELU) in the GEMM epilogue")
@@ -30,7 +31,9 @@ def main():
     be = ops.Backend(0, workspace_bytes=2 << 30)
     g = torch.Generator(device="cuda").manual_seed(42)
     a = torch.rand(args.m, args.k, device="cuda", generator=g) * 2 - 1
-    if args.layout == "nn":
+    if args.layout == "tn":
+        a = (torch.rand(args.k, args.m, device="cuda", generator=g) * 2 - 1).t()
+    if args.layout in ("nn", "tn"):
         b = torch.rand(args.k, args.n, device="cuda", generator=g) * 2 - 1
     else:
         b = (torch.rand(args.n, args.k, device="cuda", generator=g) * 2 - 1).t()

@@ -54,5 +54,23 @@ def build(force=False, verbose=False):
     return LIB
 
 
+ADAPTER_BENCH_SRC = os.path.join(HERE, "benchmarks", "adapter_step_benchmark.cpp")
+ADAPTER_BENCH = os.path.join(HERE, "benchmarks", "adapter_step_benchmark")
+
+
+def build_adapter_benchmark(out=ADAPTER_BENCH):
+    """Compiles benchmarks/adapter_step_benchmark.cpp (the C++ adapter's transformer-block step, caching allocator
+    against cudaMalloc per tensor) against libte_b200.so.  Returns the program's path."""
+    cuda = os.environ.get("CUDA_HOME", "/usr/local/cuda")
+    deps = [ADAPTER_BENCH_SRC, os.path.join(ROOT, "include", "te_b200.hpp"), os.path.join(ROOT, "include", "te_b200.h")]
+    if _stale(out, deps):
+        cmd = ["g++", "-std=c++17", "-O2", "-I" + os.path.join(ROOT, "include"), "-I" + os.path.join(cuda, "include"),
+               ADAPTER_BENCH_SRC, "-o", out, "-L" + HERE, "-lte_b200", "-L" + os.path.join(cuda, "lib64"), "-lcudart",
+               "-Wl,-rpath,$ORIGIN/..", "-Wl,-rpath," + os.path.join(cuda, "lib64")]
+        subprocess.run(cmd, check=True)
+    return out
+
+
 if __name__ == "__main__":
     print(build(force="--force" in sys.argv, verbose="-v" in sys.argv))
+    print(build_adapter_benchmark())
