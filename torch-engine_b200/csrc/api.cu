@@ -486,7 +486,8 @@ int te_b200_gemm_f32_host(te_b200_ctx* ctx, const te_gemm_desc* h) {
             }
         }
         constexpr int MAX_BLOCKS = 16;
-        int64_t rows_per = round_up((h->M + 7) / 8, 256);
+        // up to 16 row blocks: what the pipeline cannot hide is the last block's product and copy out
+        int64_t rows_per = round_up((h->M + 15) / 16, 256);
         int nblk = (int)((h->M + rows_per - 1) / rows_per);
         if (nblk > MAX_BLOCKS) { rows_per = round_up((h->M + MAX_BLOCKS - 1) / MAX_BLOCKS, 256); nblk = (int)((h->M + rows_per - 1) / rows_per); }
         if ((e = cudaMemcpyAsync(db, h->b, b_el * 4, cudaMemcpyHostToDevice, s_in)) != cudaSuccess) return drained(cuda_fail(e, "H2D B"));

@@ -259,9 +259,27 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
         const int ct = threadIdx.x - (MMA_WARP + 1) * 32;
         int converted = 0;
         bool ok = true;
+        constexpr int A_PIECES = A_PLANE_BYTES / 16 / CONVERTER_THREADS, B_PIECES = B_PLANE_BYTES / 16 / CONVERTER_THREADS;
+        // Rows of a K-major A tile past the end of the matrix (a thin M: 16 rows in a 128-row tile) hold the zeros TMA
+        // filled in and belong to output rows that are never stored: they are not converted.  Their lo rows are
+        // zeroed once here so that the MMAs of those rows read numbers.
+        if (!A_MN) {
+            for (int st = 0; st < STAGES; ++st) {
+                float4* a_lo = reinterpret_cast<float4*>(smem_raw + (ring - raw_addr) + st * STAGE_BYTES) + A_PIECES * CONVERTER_THREADS;
+#pragma unroll
+                for (int i = 0; i < A_PIECES; ++i) a_lo[ct + i * CONVERTER_THREADS] = make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+        }
         for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x) {
             WorkUnit w;
             decode_unit(u, p, kblocks, w);
+            // 16-byte pieces of the A plane that hold rows of the matrix: a row is 128 bytes, rows come in swizzle
+            // groups of eight
+            int a_valid = A_PIECES * CONVERTER_THREADS;
+            if (!A_MN) {
+                const long long rows_left = p.M - (long long)w.m_blk * BM;
+                if (rows_left < BM) a_valid = (int)((rows_left + 7) / 8) * 64;
+            }
             for (int kb = w.kb0; kb < w.kb1 && ok; ++kb, ++converted) {
                 const int s = converted % STAGES;
                 ok = wait_bounded(bar_full + 8 * s, (converted / STAGES) & 1, abort_flag, p.status, WAIT_CONVERTER_FULL);
@@ -270,14 +288,16 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                 // all loads of a plane are issued before the first conversion, so that their latencies overlap
                 float4* a_hi = reinterpret_cast<float4*>(smem_raw + (ring - raw_addr) + s * STAGE_BYTES);
                 float4* b_hi = a_hi + 2 * (A_PLANE_BYTES / 16);
-                auto split_plane = [&](float4* hi_plane, auto pieces_tag) {
+                auto split_plane = [&](float4* hi_plane, auto pieces_tag, int valid) {
                     constexpr int PIECES = decltype(pieces_tag)::value;      // 16-byte pieces per thread
                     float4* lo_plane = hi_plane + PIECES * CONVERTER_THREADS;
                     float4 x[PIECES];
 #pragma unroll
-                    for (int i = 0; i < PIECES; ++i) x[i] = hi_plane[ct + i * CONVERTER_THREADS];
+                    for (int i = 0; i < PIECES; ++i)
+                        if (ct + i * CONVERTER_THREADS < valid) x[i] = hi_plane[ct + i * CONVERTER_THREADS];
 #pragma unroll
                     for (int i = 0; i < PIECES; ++i) {
+                        if (ct + i * CONVERTER_THREADS >= valid) continue;
                         float4 hi, lo;
                         hi.x = to_tf32_rn(x[i].x); hi.y = to_tf32_rn(x[i].y); hi.z = to_tf32_rn(x[i].z); hi.w = to_tf32_rn(x[i].w);
                         lo.x = to_tf32_rn(x[i].x - hi.x); lo.y = to_tf32_rn(x[i].y - hi.y);
@@ -286,8 +306,8 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                         lo_plane[ct + i * CONVERTER_THREADS] = lo;
                     }
                 };
-                split_plane(a_hi, std::integral_constant<int, A_PLANE_BYTES / 16 / CONVERTER_THREADS>{});
-                split_plane(b_hi, std::integral_constant<int, B_PLANE_BYTES / 16 / CONVERTER_THREADS>{});
+                split_plane(a_hi, std::integral_constant<int, A_PIECES>{}, a_valid);
+                split_plane(b_hi, std::integral_constant<int, B_PIECES>{}, B_PIECES * CONVERTER_THREADS);
                 fence_proxy_async_smem();      // the tensor core reads these planes through the async proxy
                 __syncwarp();
                 if (lane == 0) mbar_arrive(bar_conv + 8 * s);
@@ -597,22 +617,88 @@ struct SplitReduceParams {
     float alpha; int scale_mode; int epilogue;
 };
 
+// VEC = 4: N, ldc and the batch strides are multiples of 4 and every pointer is 16-byte aligned, so a thread owns four
+// consecutive columns of one row.  The partial tiles sit in L2 (they were just written); what a thread waits for is
+// the latency of its loads, so four splits are fetched before the first is added -- in split order all the same.
+template <int VEC>
 __global__ void __launch_bounds__(256) splitk_reduce_kernel(const SplitReduceParams r) {
     griddep_wait();
     const long long stride = (long long)gridDim.x * blockDim.x;
-    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < r.total; i += stride) {
-        float v = 0.0f;
-        for (int s = 0; s < r.k_splits; ++s) v += r.partial[s * r.split_stride + i];
-        const long long n = i % r.N, row = (i / r.N) % r.M, batch = i / (r.N * r.M);
-        const long long bo = batch / r.batch_inner, bi = batch - bo * r.batch_inner;
-        if (r.scale_mode == TE_SCALE_MUL) v *= r.alpha;
-        else if (r.scale_mode == TE_SCALE_DIV) v = v / r.alpha;
-        if (r.bias) v += r.bias[n];
-        const long long o = bo * r.c_stride_outer + bi * r.c_stride_inner + row * r.ldc + n;
-        if (r.preact) r.preact[o] = v;
-        if (r.epilogue == TE_EPI_BIAS_GELU) v = gelu_tanh(v);
-        if (r.residual) v += r.residual[o];
-        r.c[o] = v;
+    const long long total_v = r.total / VEC;
+    // the output is one dense block in the order of the partial tiles: no index arithmetic beyond the column
+    const bool dense = r.ldc == r.N && (r.total == r.M * r.N ||
+                                        (r.c_stride_inner == r.M * r.N &&
+                                         (r.total == r.batch_inner * r.M * r.N || r.c_stride_outer == r.batch_inner * r.M * r.N)));
+    for (long long iv = (long long)blockIdx.x * blockDim.x + threadIdx.x; iv < total_v; iv += stride) {
+        const long long i = iv * VEC;
+        float v[VEC];
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) v[e] = 0.0f;
+        auto fetch = [&](int s, float* dst) {
+            const float* src = r.partial + s * r.split_stride + i;
+            if (VEC == 4) {
+                const float4 t = *reinterpret_cast<const float4*>(src);
+                dst[0] = t.x; dst[1] = t.y; dst[2] = t.z; dst[3] = t.w;
+            } else {
+                dst[0] = *src;
+            }
+        };
+        int s = 0;
+        for (; s + 4 <= r.k_splits; s += 4) {
+            float t0[VEC], t1[VEC], t2[VEC], t3[VEC];
+            fetch(s, t0); fetch(s + 1, t1); fetch(s + 2, t2); fetch(s + 3, t3);
+#pragma unroll
+            for (int e = 0; e < VEC; ++e) { v[e] += t0[e]; v[e] += t1[e]; v[e] += t2[e]; v[e] += t3[e]; }
+        }
+        for (; s < r.k_splits; ++s) {
+            float t0[VEC];
+            fetch(s, t0);
+#pragma unroll
+            for (int e = 0; e < VEC; ++e) v[e] += t0[e];
+        }
+        long long n, o;
+        if (r.total <= 0x7fffffffLL) {      // 32-bit index arithmetic where it fits
+            const unsigned iu = (unsigned)i, N = (unsigned)r.N, M = (unsigned)r.M;
+            const unsigned rowb = iu / N;
+            n = iu - rowb * N;
+            if (dense) {
+                o = i;
+            } else {
+                const unsigned batch = rowb / M, row = rowb - batch * M;
+                const unsigned bo = batch / (unsigned)r.batch_inner, bi = batch - bo * (unsigned)r.batch_inner;
+                o = bo * r.c_stride_outer + bi * r.c_stride_inner + (long long)row * r.ldc + n;
+            }
+        } else {
+            n = i % r.N;
+            const long long row = (i / r.N) % r.M, batch = i / (r.N * r.M);
+            const long long bo = batch / r.batch_inner, bi = batch - bo * r.batch_inner;
+            o = bo * r.c_stride_outer + bi * r.c_stride_inner + row * r.ldc + n;
+        }
+        if (r.scale_mode == TE_SCALE_MUL) {
+#pragma unroll
+            for (int e = 0; e < VEC; ++e) v[e] *= r.alpha;
+        } else if (r.scale_mode == TE_SCALE_DIV) {
+#pragma unroll
+            for (int e = 0; e < VEC; ++e) v[e] = v[e] / r.alpha;
+        }
+        if (r.bias) {
+#pragma unroll
+            for (int e = 0; e < VEC; ++e) v[e] += r.bias[n + e];
+        }
+        auto store = [&](float* base) {
+            if (VEC == 4) *reinterpret_cast<float4*>(base + o) = make_float4(v[0], v[1], v[2], v[3]);
+            else base[o] = v[0];
+        };
+        if (r.preact) store(r.preact);
+        if (r.epilogue == TE_EPI_BIAS_GELU) {
+#pragma unroll
+            for (int e = 0; e < VEC; ++e) v[e] = gelu_tanh(v[e]);
+        }
+        if (r.residual) {
+#pragma unroll
+            for (int e = 0; e < VEC; ++e) v[e] += r.residual[o + e];
+        }
+        store(r.c);
     }
 }
 
@@ -626,9 +712,14 @@ int finish_split(te_b200_ctx* ctx, const GemmProblem& g, int k_splits, cudaStrea
     r.c = g.c; r.preact = g.preact; r.bias = g.bias; r.residual = g.residual;
     r.ldc = g.ldc; r.c_stride_inner = g.c_stride_inner; r.c_stride_outer = g.c_stride_outer;
     r.alpha = g.alpha; r.scale_mode = g.scale_mode; r.epilogue = g.epilogue;
-    long long blocks = (r.total + 255) / 256;
+    const uintptr_t ptr_bits = reinterpret_cast<uintptr_t>(r.partial) | reinterpret_cast<uintptr_t>(r.c) | reinterpret_cast<uintptr_t>(r.preact) |
+                               reinterpret_cast<uintptr_t>(r.bias) | reinterpret_cast<uintptr_t>(r.residual);
+    const bool vec = ((r.N | r.ldc | r.c_stride_inner | r.c_stride_outer) & 3) == 0 && (ptr_bits & 15) == 0;
+    long long blocks = (r.total / (vec ? 4 : 1) + 255) / 256;
     if (blocks > (long long)ctx->sm_count * 16) blocks = (long long)ctx->sm_count * 16;
-    launch_pdl(splitk_reduce_kernel, dim3((unsigned)blocks), dim3(256), 0, stream, r);
+    if (blocks < 1) blocks = 1;
+    if (vec) launch_pdl(splitk_reduce_kernel<4>, dim3((unsigned)blocks), dim3(256), 0, stream, r);
+    else launch_pdl(splitk_reduce_kernel<1>, dim3((unsigned)blocks), dim3(256), 0, stream, r);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return cuda_fail(e, "splitk_reduce_kernel launch");
     ctx->launches += 1;
@@ -661,7 +752,7 @@ int prepare_3xtf32_kernels(te_b200_ctx* ctx) {
     if ((rc = ensure_kernel_attributes<64, 2, false, false>(ctx))) return rc;
     if ((rc = ensure_kernel_attributes<128, 2, false, false>(ctx))) return rc;
     cudaFuncAttributes fa;
-    cudaError_t e = cudaFuncGetAttributes(&fa, splitk_reduce_kernel);      // loads the kernel
+    cudaError_t e = cudaFuncGetAttributes(&fa, splitk_reduce_kernel<4>);      // loads the kernel
     if (e != cudaSuccess) return cuda_fail(e, "cudaFuncGetAttributes(splitk_reduce_kernel)");
     if ((rc = prepare_pair_3xtf32_kernel(ctx))) return rc;
     return prepare_pack_kernels();

@@ -185,7 +185,24 @@ __global__ void __launch_bounds__(256) layernorm_param_grad_kernel(const float* 
     const int c = blockIdx.x * 32 + lane;
     float a = 0.0f, b = 0.0f, s = 0.0f;
     if (c < cols) {
-        for (int i = warp; i < blocks; i += 8) {
+        // what a warp waits for is the latency of its loads: four partial rows are fetched before the first is added
+        // (in ascending row order all the same)
+        const long long row_stride = 3LL * cols;
+        const float* base = partial + c;
+        int i = warp;
+        for (; i + 24 < blocks; i += 32) {
+            float ta[4], tb[4], ts[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const float* row = base + (long long)(i + 8 * u) * row_stride;
+                ta[u] = row[0];
+                tb[u] = row[cols];
+                ts[u] = dx_colsum ? row[2 * cols] : 0.0f;
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) { a += ta[u]; b += tb[u]; s += ts[u]; }
+        }
+        for (; i < blocks; i += 8) {
             a += partial[((long long)i * 3) * cols + c];
             b += partial[((long long)i * 3 + 1) * cols + c];
             if (dx_colsum) s += partial[((long long)i * 3 + 2) * cols + c];

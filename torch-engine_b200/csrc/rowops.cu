@@ -202,6 +202,26 @@ __global__ void __launch_bounds__(256) gelu_backward_vec4_kernel(const float4* _
 
 __device__ __forceinline__ bool colsum_is_last_block(unsigned* counter, unsigned slabs, bool* flag_smem);
 
+// Sum of the slab partials warp, warp + 8, ... of four columns, added in ascending slab order.  The partials were
+// written by other blocks (read through L2); four are fetched before the first is added, because what the finishing
+// block waits for is the latency of these loads.
+__device__ __forceinline__ float4 slab_partials_in_order(const float* partial_col, long long cols, int warp, int slabs) {
+    float4 s4 = make_float4(0.f, 0.f, 0.f, 0.f);
+    int sl = warp;
+    for (; sl + 24 < slabs; sl += 32) {
+        float4 t[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) t[u] = __ldcg(reinterpret_cast<const float4*>(partial_col + (long long)(sl + 8 * u) * cols));
+#pragma unroll
+        for (int u = 0; u < 4; ++u) { s4.x += t[u].x; s4.y += t[u].y; s4.z += t[u].z; s4.w += t[u].w; }
+    }
+    for (; sl < slabs; sl += 8) {
+        const float4 v = __ldcg(reinterpret_cast<const float4*>(partial_col + (long long)sl * cols));
+        s4.x += v.x; s4.y += v.y; s4.z += v.z; s4.w += v.w;
+    }
+    return s4;
+}
+
 // dx = dy * gelu'(x) over a dense [rows, cols] matrix AND the column sums of dx in the same pass (the bias gradient of
 // the Linear that produced x: FeedForward's first Linear, src/nn/ffn.cpp:12-14 / src/core/grad_fn.cpp:93-102).  Thread
 // layout of colsum_slab_vec4_kernel: a block owns 128 columns and a slab of rows, its eight warps stride the rows four
@@ -257,10 +277,7 @@ __global__ void __launch_bounds__(256) gelu_backward_colsum_kernel(const float* 
     if (!colsum_is_last_block(counters + blockIdx.x, (unsigned)slabs, &last)) return;
     float4 s4 = make_float4(0.f, 0.f, 0.f, 0.f);
     if (col < cols)
-        for (int sl = warp; sl < slabs; sl += 8) {
-            const float4 v = __ldcg(reinterpret_cast<const float4*>(partial + (long long)sl * cols + col));
-            s4.x += v.x; s4.y += v.y; s4.z += v.z; s4.w += v.w;
-        }
+        s4 = slab_partials_in_order(partial + col, cols, warp, slabs);
     __syncthreads();
     red[warp][lane] = s4;
     __syncthreads();
@@ -395,10 +412,7 @@ __global__ void __launch_bounds__(256) colsum_slab_vec4_kernel(const float* __re
     if (!colsum_is_last_block(counters + blockIdx.x, (unsigned)slabs, &last)) return;
     float4 s4 = make_float4(0.f, 0.f, 0.f, 0.f);
     if (col < cols)
-        for (int sl = warp; sl < slabs; sl += 8) {
-            const float4 x = __ldcg(reinterpret_cast<const float4*>(partial + (long long)sl * cols + col));
-            s4.x += x.x; s4.y += x.y; s4.z += x.z; s4.w += x.w;
-        }
+        s4 = slab_partials_in_order(partial + col, cols, warp, slabs);
     __syncthreads();                 // red[] is reused
     red[warp][lane] = s4;
     __syncthreads();
