@@ -33,7 +33,6 @@ namespace te {
 constexpr int ATT_MAX_T = 256;
 constexpr int ATT_O_COL = 256;     // TMEM column where the output accumulator starts
 constexpr int ATT_EPI_WARPS = 8;    // two warps per TMEM lane quadrant, each owning half of the columns
-constexpr int ATT_WARP_CHUNKS = ATT_MAX_T / 32 / 2;   // 32-column chunks of a score row one softmax warp owns at most
 
 __device__ __forceinline__ float ex2_approx(float x) {
     float y;
@@ -73,7 +72,7 @@ attention_tf32_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
     const uint32_t bar_td = aux_addr + 48;     // teardown
     const uint32_t bar_x1 = aux_addr + 56;     // row maxima of both column halves written   (8 softmax warps)
     const uint32_t bar_x2 = aux_addr + 64;     // row sums written                           (8 softmax warps)
-    const uint32_t bar_sfree = aux_addr + 72;  // S columns no longer read by the softmax warps (8 softmax warps -> MMA)
+    const uint32_t bar_sfree = aux_addr + 72;  // S columns no longer read                   (8 softmax warps -> MMA)
     const uint32_t bar_ofree = aux_addr + 80;  // O columns no longer read                   (8 softmax warps -> MMA)
     const uint32_t tmem_slot_addr = aux_addr + 40;
     volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(aux + 40);
@@ -187,26 +186,19 @@ attention_tf32_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             tc_fence_after_sync();
-            // This warp's share of the score row (up to four 32-column chunks) is read from TMEM once and stays in
-            // registers through all three passes.
-            uint32_t r[ATT_WARP_CHUNKS][32];
-#pragma unroll
-            for (int ci = 0; ci < ATT_WARP_CHUNKS; ++ci)
-                if (c_begin + ci < c_end) tmem_ld_32x32b_x32(t_row + (c_begin + ci) * 32, r[ci]);
-            tmem_ld_wait();
             // pass 1: row maximum of the raw scores (the scale is positive, so the maximum commutes with it)
             float m = -INFINITY;
-#pragma unroll
-            for (int ci = 0; ci < ATT_WARP_CHUNKS; ++ci) {
-                const int cc = c_begin + ci;
-                if (cc >= c_end) continue;
+            for (int cc = c_begin; cc < c_end; ++cc) {
+                uint32_t r[32];
+                tmem_ld_32x32b_x32(t_row + cc * 32, r);
+                tmem_ld_wait();
                 if ((cc + 1) * 32 <= p.T) {
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) m = fmaxf(m, __uint_as_float(r[ci][j]));
+                    for (int j = 0; j < 32; ++j) m = fmaxf(m, __uint_as_float(r[j]));
                 } else {
 #pragma unroll
                     for (int j = 0; j < 32; ++j)
-                        if (cc * 32 + j < p.T) m = fmaxf(m, __uint_as_float(r[ci][j]));
+                        if (cc * 32 + j < p.T) m = fmaxf(m, __uint_as_float(r[j]));
                 }
             }
             // The two warps of a row group own the same TMEM lanes: they exchange through two spare columns.
@@ -224,29 +216,29 @@ attention_tf32_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
             const float mk = m * k2;
             // pass 2: e = exp(s - m), row sum; e goes back to TMEM as the A operand of P.V
             float sum = 0.0f;
-#pragma unroll
-            for (int ci = 0; ci < ATT_WARP_CHUNKS; ++ci) {
-                const int cc = c_begin + ci;
-                if (cc >= c_end) continue;
+            for (int cc = c_begin; cc < c_end; ++cc) {
+                uint32_t r[32];
+                tmem_ld_32x32b_x32(t_row + cc * 32, r);
+                tmem_ld_wait();
                 if ((cc + 1) * 32 <= p.T) {
 #pragma unroll
                     for (int j = 0; j < 32; ++j) {
-                        const float e = ex2_approx(fmaf(__uint_as_float(r[ci][j]), k2, -mk));
+                        const float e = ex2_approx(fmaf(__uint_as_float(r[j]), k2, -mk));
                         sum += e;
-                        r[ci][j] = __float_as_uint(e);
+                        r[j] = __float_as_uint(e);
                     }
                 } else {
 #pragma unroll
                     for (int j = 0; j < 32; ++j) {
                         float e = 0.0f;
                         if (cc * 32 + j < p.T) {
-                            e = ex2_approx(fmaf(__uint_as_float(r[ci][j]), k2, -mk));
+                            e = ex2_approx(fmaf(__uint_as_float(r[j]), k2, -mk));
                             sum += e;
                         }
-                        r[ci][j] = __float_as_uint(e);
+                        r[j] = __float_as_uint(e);
                     }
                 }
-                tmem_st_32x32b_x32(t_row + cc * 32, r[ci]);
+                tmem_st_32x32b_x32(t_row + cc * 32, r);
             }
             tmem_st_32x32b_x1(x_col + 2 + half, __float_as_uint(sum));
             tmem_st_wait();
@@ -254,7 +246,6 @@ attention_tf32_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
             __syncwarp();
             if (lane == 0) {
                 mbar_arrive(bar_p);      // this warp's part of the PV operand is in place
-                mbar_arrive(bar_sfree);  // and this warp reads the S columns no more: once P.V is done they may take the next scores
                 mbar_arrive(bar_x2);
             }
             ok = wait_bounded(bar_x2, par, abort_flag, p.status, WAIT_EPI_TMEM_FULL);
@@ -270,18 +261,21 @@ attention_tf32_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
             er.tm_c = &tm_p; er.tm_pre = &tm_p;
             er.row0 = q0 + quad * 32;
             er.bi = h; er.bo = b;
-            // pass 3: P = e / sum out of the registers, written out once (while the tensor core computes P.V, and then
-            // the next tile's scores, from and into the TMEM columns)
-#pragma unroll
-            for (int ci = 0; ci < ATT_WARP_CHUNKS; ++ci) {
-                const int cc = c_begin + ci;
-                if (cc >= c_end || cc * 32 >= p.T) continue;
+            // pass 3: P = e / sum, written out once (while the tensor core computes P.V from the same columns)
+            for (int cc = c_begin; cc < c_end && cc * 32 < p.T; ++cc) {
+                uint32_t r[32];
+                tmem_ld_32x32b_x32(t_row + cc * 32, r);
+                tmem_ld_wait();
                 if (er.row0 < p.T) {
+                    float v[32];
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) r[ci][j] = __float_as_uint(__uint_as_float(r[ci][j]) * inv_sum);
-                    stage_and_store32(reinterpret_cast<const float*>(r[ci]), cc * 32, er, &tm_p, lane, true, (stores++) & 1);
+                    for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * inv_sum;
+                    stage_and_store32(v, cc * 32, er, &tm_p, lane, true, (stores++) & 1);
                 }
             }
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_sfree);     // the S columns may be overwritten by the next tile's scores
             ok = wait_bounded(bar_o, par, abort_flag, p.status, WAIT_EPI_TMEM_FULL);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
