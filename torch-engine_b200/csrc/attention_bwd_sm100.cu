@@ -80,13 +80,6 @@ __global__ void __launch_bounds__(256) rowdot_bht_kernel(const float* __restrict
     }
 }
 
-// Asks the TMA unit to bring one box of a tensor into L2 (no shared-memory destination, nothing to wait for).
-__device__ __forceinline__ void tma_prefetch_l2_4d(const void* tmap, int c0, int c1, int c2, int c3) {
-    asm volatile("cp.async.bulk.prefetch.tensor.4d.L2.global.tile [%0, {%1, %2, %3, %4}];" ::"l"(reinterpret_cast<uint64_t>(tmap)),
-                 "r"(c0), "r"(c1), "r"(c2), "r"(c3)
-                 : "memory");
-}
-
 __global__ void __launch_bounds__(CTA_THREADS, 1)
 attention_bwd_tf32_kernel(const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_k,
                           const __grid_constant__ CUtensorMap tm_dok, const __grid_constant__ CUtensorMap tm_dom,
