@@ -95,6 +95,15 @@ __device__ __forceinline__ float to_tf32_rn(float x) {
     return __uint_as_float(u & 0xFFFFE000u);
 }
 
+// The same rounding with integer instructions: half a tf32 ulp added to the magnitude bits, low 13 bits cleared.
+// Equal to to_tf32_rn for every finite input and for infinity; a NaN may come out as another NaN or, with a mantissa
+// of all ones, as zero, so this form is for values whose NaN case is already decided elsewhere (the lo part
+// x - hi of a hi / lo split: a NaN x makes hi a NaN, and the product with it).  It keeps the conversion unit, which
+// issues a quarter as many lanes per clock as the integer unit, free for the hi parts.
+__device__ __forceinline__ float to_tf32_rn_finite(float x) {
+    return __uint_as_float((__float_as_uint(x) + 0x1000u) & 0xFFFFE000u);
+}
+
 __device__ __forceinline__ bool wait_bounded(uint32_t bar, uint32_t parity, volatile int* abort_flag,
                                              int* status, int code) {
     if (mbar_try_wait(bar, parity)) return true;

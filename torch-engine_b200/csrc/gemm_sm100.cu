@@ -300,8 +300,8 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                         if (ct + i * CONVERTER_THREADS >= valid) continue;
                         float4 hi, lo;
                         hi.x = to_tf32_rn(x[i].x); hi.y = to_tf32_rn(x[i].y); hi.z = to_tf32_rn(x[i].z); hi.w = to_tf32_rn(x[i].w);
-                        lo.x = to_tf32_rn(x[i].x - hi.x); lo.y = to_tf32_rn(x[i].y - hi.y);
-                        lo.z = to_tf32_rn(x[i].z - hi.z); lo.w = to_tf32_rn(x[i].w - hi.w);
+                        lo.x = to_tf32_rn_finite(x[i].x - hi.x); lo.y = to_tf32_rn_finite(x[i].y - hi.y);
+                        lo.z = to_tf32_rn_finite(x[i].z - hi.z); lo.w = to_tf32_rn_finite(x[i].w - hi.w);
                         hi_plane[ct + i * CONVERTER_THREADS] = hi;
                         lo_plane[ct + i * CONVERTER_THREADS] = lo;
                     }
