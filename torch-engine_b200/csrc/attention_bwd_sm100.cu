@@ -23,6 +23,10 @@
 //   MMA 4   dK_j += dS^T . Q_i    (A from TMEM)        -> TMEM [320,384)
 // The dQ product goes first because it is the only reader of the dS^T tile in shared memory: once it is done the next
 // step's block of P may land there, while MMAs 3 and 4 are still running.
+// A tile is one head (all key blocks in turn) or, when that fills the SMs better (p.split_keys; for example 192 heads
+// on 148 SMs), one (head, key block): dV_j / dK_j are complete either way, and the two tiles of a head add their dQ
+// onto memory that the row-dot pre-pass has filled with zeros (cp.reduce.async.bulk, fp32 add): with exactly two
+// addends per element the result does not depend on which arrives first.
 // dV_j and dK_j leave after the last query block, dQ after the last key block, through TMA stores staged in the
 // dO / Q operand buffers (free at that point; for d = 32 they are too small and the dS^T region is used instead).
 // Warp roles as in the forward kernel: warp 8 TMA producer, warp 9 MMA issue, warps 0-7 element work and output
@@ -47,7 +51,8 @@ constexpr int BWD_CHUNK = 128 * 128;     // bytes of one [128 rows x 32 floats] 
 struct AttnBwdParams {
     int T, d, H, B;
     int nblk;          // 128-row blocks per head (1 or 2)
-    int total_tiles;   // B * H
+    int split_keys;    // 1: a tile is one (head, key block) and dQ is added onto zero-filled memory by the two tiles of a head
+    int total_tiles;   // B * H, or B * H * nblk with split_keys
     float inv_scale;   // 1 / sqrt(d)
     int pbox;          // rows and columns of the P box: min(T, 128)
     const float* dvec; // [B,H,T]: rowsum(dO o O), written by rowdot_bht_kernel
@@ -56,9 +61,12 @@ struct AttnBwdParams {
 
 // D[b,h,t] = sum_c dO[b,h,t,c] * O[b,h,t,c] (= rowsum(P o dP), the inner product SoftmaxBackward subtracts).  A row is
 // d/4 float4 wide, so one warp instruction covers 32/(d/4) whole rows; partial dot products meet by shuffles.
+// `zero` (optional): a third [B,H,T,d] view that is filled with zeros in the same pass (the dQ buffer when two tiles
+// per head add their parts onto it).
 __global__ void __launch_bounds__(256) rowdot_bht_kernel(const float* __restrict__ x, long long xs0, long long xs1, long long xs2,
                                                          const float* __restrict__ y, long long ys0, long long ys1, long long ys2,
-                                                         float* __restrict__ out, int H, int T, int d, long long rows) {
+                                                         float* __restrict__ out, int H, int T, int d, long long rows,
+                                                         float* __restrict__ zero, long long zs0, long long zs1, long long zs2) {
     griddep_wait();
     const int lane = threadIdx.x & 31;
     const int f4 = d >> 2, rpi = 32 / f4;
@@ -74,6 +82,7 @@ __global__ void __launch_bounds__(256) rowdot_bht_kernel(const float* __restrict
             const float4 a = __ldg(reinterpret_cast<const float4*>(x + b * xs0 + h * xs1 + t * xs2) + col);
             const float4 c = __ldg(reinterpret_cast<const float4*>(y + b * ys0 + h * ys1 + t * ys2) + col);
             acc = a.x * c.x + a.y * c.y + a.z * c.z + a.w * c.w;
+            if (zero) reinterpret_cast<float4*>(zero + b * zs0 + h * zs1 + t * zs2)[col] = make_float4(0.f, 0.f, 0.f, 0.f);
         }
         for (int off = f4 >> 1; off >= 1; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
         if (col == 0 && r < rows) out[r] = acc;
@@ -147,6 +156,11 @@ attention_bwd_tf32_kernel(const __grid_constant__ CUtensorMap tm_v, const __grid
     griddep_launch_dependents();   // persistent grid, every CTA resident: the next kernel may move in as CTAs exit
     griddep_wait();                // the prologue above overlapped the previous kernel's tail; global memory from here on
     const int nblk = p.nblk;
+    // tile -> head and the key blocks [jb, je) it covers
+    const int units_per_head = p.split_keys ? nblk : 1;
+    auto tile_head = [&](int t) { return t / units_per_head; };
+    auto tile_jb = [&](int t) { return p.split_keys ? t % units_per_head : 0; };
+    auto tile_je = [&](int t) { return p.split_keys ? t % units_per_head + 1 : nblk; };
 
     if (warp == PRODUCER_WARP) {
         if (lane == 0) {
@@ -161,10 +175,12 @@ attention_bwd_tf32_kernel(const __grid_constant__ CUtensorMap tm_v, const __grid
             bool ok = true;
             // The step's 128 x 128 block of P is copied into the (still unused) dS^T region, from where the element
             // warps take it transposed; the block of the NEXT step is pulled into L2 a step ahead.
-            if ((int)blockIdx.x < p.total_tiles) tma_prefetch_l2_4d(&tm_p, 0, 0, blockIdx.x % p.H, blockIdx.x / p.H);
+            if ((int)blockIdx.x < p.total_tiles)
+                tma_prefetch_l2_4d(&tm_p, 128 * tile_jb(blockIdx.x), 0, tile_head(blockIdx.x) % p.H, tile_head(blockIdx.x) / p.H);
             for (int t = blockIdx.x; t < p.total_tiles && ok; t += gridDim.x) {
-                const int h = t % p.H, b = t / p.H;
-                for (int j = 0; j < nblk && ok; ++j) {
+                const int h = tile_head(t) % p.H, b = tile_head(t) / p.H;
+                const int jb = tile_jb(t), je = tile_je(t);
+                for (int j = jb; j < je && ok; ++j) {
                     for (int i = 0; i < nblk; ++i, ++s) {
                         // Every buffer is single.  The operands of MMA 1 are free as soon as the previous step's MMA 1 is
                         // done, so they are fetched while that step is still in its element work and MMAs 2-4.
@@ -219,8 +235,11 @@ attention_bwd_tf32_kernel(const __grid_constant__ CUtensorMap tm_v, const __grid
                         {   // P block of the step after this one
                             int ni = i + 1, nj = j, nt = t;
                             if (ni == nblk) { ni = 0; ++nj; }
-                            if (nj == nblk) { nj = 0; nt += gridDim.x; }
-                            if (nt < p.total_tiles) tma_prefetch_l2_4d(&tm_p, 128 * nj, 128 * ni, nt % p.H, nt / p.H);
+                            if (nj == je) {
+                                nt += gridDim.x;
+                                nj = nt < p.total_tiles ? tile_jb(nt) : 0;
+                            }
+                            if (nt < p.total_tiles) tma_prefetch_l2_4d(&tm_p, 128 * nj, 128 * ni, tile_head(nt) % p.H, tile_head(nt) / p.H);
                         }
                     }
                 }
@@ -239,7 +258,8 @@ attention_bwd_tf32_kernel(const __grid_constant__ CUtensorMap tm_v, const __grid
             int s = 0, jc = 0;
             bool ok = true;
             for (int t = blockIdx.x; t < p.total_tiles && ok; t += gridDim.x) {
-                for (int j = 0; j < nblk && ok; ++j, ++jc) {
+                const int jb = tile_jb(t), je = tile_je(t);
+                for (int j = jb; j < je && ok; ++j, ++jc) {
                     for (int i = 0; i < nblk; ++i, ++s) {
                         if (!wait_bounded(bar_a, s & 1, abort_flag, p.status, WAIT_MMA_FULL)) { ok = false; break; }
                         tc_fence_after_sync();
@@ -264,7 +284,7 @@ attention_bwd_tf32_kernel(const __grid_constant__ CUtensorMap tm_v, const __grid
                         for (int kk = 0; kk < 16; ++kk) {
                             const uint64_t da = make_smem_desc(ds_smem + kk * 1024, BWD_CHUNK, 512, SMEM_LAYOUT_SW128_BASE32B);
                             const uint64_t db = make_smem_desc(k_smem + kk * 1024, BWD_CHUNK, 512, SMEM_LAYOUT_SW128_BASE32B);
-                            umma_tf32(tmem_base + BWD_COL_DQ + i * 64, da, db, idesc_dq, (j | kk) != 0);
+                            umma_tf32(tmem_base + BWD_COL_DQ + i * 64, da, db, idesc_dq, j != jb || kk != 0);
                         }
                         umma_commit(bar_dsfree);
 #pragma unroll
@@ -298,11 +318,12 @@ attention_bwd_tf32_kernel(const __grid_constant__ CUtensorMap tm_v, const __grid
         er.tm_c = nullptr; er.tm_pre = nullptr;
         int stores = 0;
         for (int t = blockIdx.x; t < p.total_tiles && ok; t += gridDim.x, ++tc) {
-            const int h = t % p.H, b = t / p.H;
+            const int head = tile_head(t), h = head % p.H, b = head / p.H;
+            const int jb = tile_jb(t), je = tile_je(t);
             er.bi = h; er.bo = b;
             // D of this head's queries: fetched now, published to the other warps just before its first use
-            const float d_mine = (int)threadIdx.x < p.T ? __ldg(p.dvec + (size_t)t * p.T + threadIdx.x) : 0.0f;
-            for (int j = 0; j < nblk && ok; ++j, ++jc) {
+            const float d_mine = (int)threadIdx.x < p.T ? __ldg(p.dvec + (size_t)head * p.T + threadIdx.x) : 0.0f;
+            for (int j = jb; j < je && ok; ++j, ++jc) {
                 for (int i = 0; i < nblk; ++i, ++s) {
                     // P^T for this thread's key and its 64 queries, out of the block the producer copied in
                     float pt[64];
@@ -318,7 +339,7 @@ attention_bwd_tf32_kernel(const __grid_constant__ CUtensorMap tm_v, const __grid
                     }
                     __syncwarp();
                     if (lane == 0) mbar_arrive(bar_pr);
-                    if ((i | j) == 0) {
+                    if (i == 0 && j == jb) {
                         // every warp is past the previous tile's last element pass (its outputs were read after that
                         // step's MMAs, which waited for all eight warps), so the D array may be rewritten
                         d_sm[threadIdx.x] = d_mine;
@@ -380,7 +401,7 @@ attention_bwd_tf32_kernel(const __grid_constant__ CUtensorMap tm_v, const __grid
                             stage_and_store32(reinterpret_cast<const float*>(r), c * 32, er, which ? &tm_dk : &tm_dv, lane, true, 0);
                         }
                     }
-                    if (j == nblk - 1) {   // last key block: dQ of every query block is complete as well
+                    if (j == je - 1) {   // last key block of the tile: its dQ (whole, or this key block's part) goes out as well
                         for (int item = half; item < nblk * dchunks; item += 2) {
                             const int qi = item / dchunks, c = item % dchunks;
                             uint32_t r[32];
@@ -389,7 +410,7 @@ attention_bwd_tf32_kernel(const __grid_constant__ CUtensorMap tm_v, const __grid
                             er.row0 = qi * 128 + quad * 32;
                             if (er.row0 < p.T) {
                                 er.stage = my_blk0 + ((stores++) & 1) * BWD_CHUNK;
-                                stage_and_store32(reinterpret_cast<const float*>(r), c * 32, er, &tm_dq, lane, true, 0);
+                                stage_and_store32(reinterpret_cast<const float*>(r), c * 32, er, &tm_dq, lane, true, 0, p.split_keys != 0);
                             }
                         }
                     }
@@ -450,7 +471,14 @@ int launch_attention_backward_fused(te_b200_ctx* ctx, const te_attn_bwd_desc* t,
     AttnBwdParams p;
     p.T = (int)t->T; p.d = (int)t->d; p.H = (int)t->H; p.B = (int)t->B;
     p.nblk = (int)((t->T + 127) / 128);
-    p.total_tiles = (int)(t->B * t->H);
+    {
+        // steps a CTA runs with one tile per head (nblk^2 each) against one tile per (head, key block) (nblk each)
+        const long long heads = t->B * t->H, sms = ctx->sm_count;
+        const long long per_head = ((heads + sms - 1) / sms) * p.nblk * p.nblk;
+        const long long per_key_block = ((heads * p.nblk + sms - 1) / sms) * p.nblk;
+        p.split_keys = (p.nblk == 2 && per_key_block < per_head && heads * p.nblk <= INT32_MAX) ? 1 : 0;
+    }
+    p.total_tiles = (int)(t->B * t->H) * (p.split_keys ? p.nblk : 1);
     p.inv_scale = 1.0f / sqrtf((float)t->d);
     p.pbox = (int)(t->T < 128 ? t->T : 128);
     p.status = ctx->d_status;
@@ -466,7 +494,8 @@ int launch_attention_backward_fused(te_b200_ctx* ctx, const te_attn_bwd_desc* t,
         if (blocks > (long long)ctx->sm_count * 16) blocks = (long long)ctx->sm_count * 16;
         launch_pdl(rowdot_bht_kernel, dim3((unsigned)blocks), dim3(256), 0, stream, t->d_o, t->d_o_strides[0], t->d_o_strides[1], t->d_o_strides[2],
                                                                  t->o, t->o_strides[0], t->o_strides[1], t->o_strides[2], dvec,
-                                                                 (int)t->H, (int)t->T, (int)t->d, rows);
+                                                                 (int)t->H, (int)t->T, (int)t->d, rows,
+                                                                 p.split_keys ? t->dq : (float*)nullptr, t->dq_strides[0], t->dq_strides[1], t->dq_strides[2]);
         cudaError_t e = cudaGetLastError();
         if (e != cudaSuccess) return cuda_fail(e, "rowdot_bht_kernel launch");
         ctx->launches += 1;

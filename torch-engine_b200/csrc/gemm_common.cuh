@@ -179,8 +179,9 @@ struct EpilogueRow {
 // the TMA unit instead of 32 scattered 16-byte pieces per store instruction.  Lane 0 owns the bulk group.
 // With `alternate` the caller switches between two staging tiles (er.stage and er.stage + EPI_STAGE_BYTES, chosen by
 // `which`), so only the store before the previous one has to have drained.
+// With `add` the tile is added onto what global memory holds (cp.reduce.async.bulk) instead of replacing it.
 __device__ __forceinline__ void stage_and_store32(const float* v, int col0, const EpilogueRow& er, const CUtensorMap* tm,
-                                                  int lane, bool alternate = false, int which = 0) {
+                                                  int lane, bool alternate = false, int which = 0, bool add = false) {
     if (lane == 0) {
         if (alternate) bulk_wait_read_all_but_one();
         else bulk_wait_read_all();           // the previous store has finished reading the staging tile
@@ -198,7 +199,8 @@ __device__ __forceinline__ void stage_and_store32(const float* v, int col0, cons
     fence_proxy_async_smem();
     __syncwarp();
     if (lane == 0) {
-        tma_store_4d(tm, stage, col0, er.row0, er.bi, er.bo);
+        if (add) tma_reduce_add_4d(tm, stage, col0, er.row0, er.bi, er.bo);
+        else tma_store_4d(tm, stage, col0, er.row0, er.bi, er.bo);
         bulk_commit_group();
     }
 }

@@ -74,6 +74,15 @@ __device__ __forceinline__ void tma_prefetch_l2_4d(const void* tmap, int c0, int
                  : "memory");
 }
 
+// 4-D tiled add of a shared-memory tile onto global memory (fp32 element type taken from the tensor map; out-of-range
+// parts of the box are clipped), tracked by this thread's bulk group like a store.
+__device__ __forceinline__ void tma_reduce_add_4d(const void* tmap, uint32_t src_smem, int c0, int c1, int c2, int c3) {
+    asm volatile("cp.reduce.async.bulk.tensor.4d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3, %4, %5}], [%1];" ::"l"(
+                     reinterpret_cast<uint64_t>(tmap)),
+                 "r"(src_smem), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+                 : "memory");
+}
+
 // 4-D tiled store shared -> global (out-of-range parts of the box are clipped), tracked by this thread's bulk group.
 __device__ __forceinline__ void tma_store_4d(const void* tmap, uint32_t src_smem, int c0, int c1, int c2, int c3) {
     asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5}], [%1];" ::"l"(
