@@ -753,6 +753,7 @@ int prepare_3xtf32_kernels(te_b200_ctx* ctx) {
     if ((rc = ensure_kernel_attributes<128, 2, false, false>(ctx))) return rc;
     cudaFuncAttributes fa;
     cudaError_t e = cudaFuncGetAttributes(&fa, splitk_reduce_kernel<4>);      // loads the kernel
+    if (e == cudaSuccess) e = cudaFuncGetAttributes(&fa, splitk_reduce_kernel<1>);
     if (e != cudaSuccess) return cuda_fail(e, "cudaFuncGetAttributes(splitk_reduce_kernel)");
     if ((rc = prepare_pair_3xtf32_kernel(ctx))) return rc;
     return prepare_pack_kernels();
