@@ -330,6 +330,49 @@ def test_host_buffer_entry_point(backend, oracle):
     assert np.abs(c - oracle.gelu(pre)).max() <= 1e-5
 
 
+@pytest.mark.parametrize("M,K,N", [(16, 8192, 8192), (1, 4100, 2048), (7, 1000, 516), (16, 300, 1024)])
+def test_thin_rows_fp32_accurate_mode(backend, M, K, N):
+    """At most 16 rows in the FP32-accurate mode: the memory-bound FP32-FMA form (two launches: the product in K
+    slices, the reduction with the epilogue).  Error against float64 at FP32 level, K tails and column tails
+    included; scale, bias + GELU and residual come out of the reduction like for the tensor-core kernels; the
+    same call with a layout the form does not take (N not a multiple of 4, a batch) gives the same numbers."""
+    g = torch.Generator(device="cuda").manual_seed(M * 131 + K)
+    a = torch.rand(M, K, device="cuda", generator=g) * 2 - 1
+    b = torch.rand(K, N, device="cuda", generator=g) * 2 - 1
+    ref = a.double() @ b.double()
+    n0 = backend.launches
+    c = backend.matmul(a, b, precision="3xtf32")
+    assert backend.launches == n0 + 2
+    assert float((c.double() - ref).abs().max() / ref.abs().max()) <= 2e-6
+    # a row-strided A (a slice of a wider matrix) and a B that is a column block of a wider matrix
+    wide_a = torch.rand(M, K + 8, device="cuda", generator=g)
+    wide_b = torch.rand(K, N + 64, device="cuda", generator=g)
+    a2, b2 = wide_a[:, 4:4 + K], wide_b[:, 32:32 + N]
+    c2 = backend.matmul(a2, b2, precision="3xtf32")
+    ref2 = a2.double() @ b2.double()
+    assert float((c2.double() - ref2).abs().max() / ref2.abs().max()) <= 2e-6
+    # epilogue forms
+    bias = torch.randn(N, device="cuda", generator=g)
+    res = torch.randn(M, N, device="cuda", generator=g)
+    out = torch.empty(M, N, device="cuda")
+    d = L.GemmDesc()
+    d.M, d.N, d.K = M, N, K
+    d.a, d.b, d.c = a.data_ptr(), b.data_ptr(), out.data_ptr()
+    d.lda, d.ldb, d.ldc = K, N, N
+    d.batch_outer = d.batch_inner = 1
+    d.alpha, d.scale_mode = 4.0, L.TE_SCALE_DIV
+    d.bias, d.epilogue, d.residual = bias.data_ptr(), L.TE_EPI_BIAS_GELU, res.data_ptr()
+    d.precision = L.TE_PREC_3XTF32
+    backend.gemm(d)
+    want = torch.nn.functional.gelu(ref / 4.0 + bias.double(), approximate="tanh") + res.double()
+    assert float((out.double() - want).abs().max()) <= 2e-6 * float(want.abs().max()) + 2e-6
+    # outside the form's limits the tensor-core path answers, within the mode's tolerance of the same reference
+    b_odd = b[:, :N - 1].contiguous()
+    c_odd = backend.matmul(a, b_odd, precision="3xtf32")
+    assert float((c_odd.double() - ref[:, :N - 1]).abs().max() / ref.abs().max()) <= 1e-5
+    backend.check_device_status()
+
+
 def test_launch_counter_moves(backend):
     n0 = backend.launches
     backend.matmul(torch.ones(8, 8, device="cuda"), torch.ones(8, 8, device="cuda"))

@@ -13,7 +13,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(HERE)
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libte_b200.so")
-SOURCES = ["gemm_sm100.cu", "gemm_sm100_2cta.cu", "attention_sm100.cu", "attention_bwd_sm100.cu", "pack.cu", "rowops.cu", "norm_embed_loss.cu", "api.cu", "static_scratch.cu", "dist.cu"]
+SOURCES = ["gemm_sm100.cu", "gemm_sm100_2cta.cu", "attention_sm100.cu", "attention_bwd_sm100.cu", "pack.cu", "rowops.cu", "norm_embed_loss.cu", "api.cu", "static_scratch.cu", "dist.cu", "thin_fp32.cu"]
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",

@@ -153,6 +153,13 @@ static int gemm_device(te_b200_ctx* ctx, const te_gemm_desc* d, cudaStream_t st,
     g.preact = d->preact_out; g.bias = d->bias; g.residual = d->residual; g.alpha = d->alpha; g.scale_mode = d->scale_mode;
     g.epilogue = d->epilogue;
     Carver ws(ctx->workspace, ctx->workspace_bytes - reserve_tail);
+    if (d->precision == TE_PREC_3XTF32 && d->K > 0) {
+        // FP32-accurate mode, at most 16 rows: memory-bound, computed with FP32 FMAs (thin_fp32.cu) where it applies
+        g.split_ws = reinterpret_cast<float*>(ws.base);
+        g.split_ws_bytes = ws.cap;
+        rc = launch_thin_fp32(ctx, g, st);
+        if (rc != -1) return rc;
+    }
     if (d->K > 0) {
         // 3xTF32: thin and small products are split inside the kernel from the operands as they are; large ones read
         // hi / lo planes written by the packing pass (see three_x_split_in_kernel)

@@ -140,6 +140,8 @@ int launch_gelu_backward_colsum(te_b200_ctx*, const float* x, const float* dy, f
                                 float* colsum_out, cudaStream_t);
 int launch_colsum(te_b200_ctx*, const float* in, int64_t rows, int64_t cols, int64_t ld, float* out, bool accumulate,
                   cudaStream_t);
+// FP32-FMA form of a thin (M <= 16) FP32-accurate product; -1 when the problem is outside its limits.
+int launch_thin_fp32(te_b200_ctx*, const te::GemmProblem& g, cudaStream_t st);
 int launch_pack_qkv(te_b200_ctx*, const float* const w[3], const float* const b[3], float* packed, int64_t wn, int64_t bn,
                     cudaStream_t st);
 int launch_unpack_qkv(te_b200_ctx*, const float* packed, float* const w[3], float* const b[3], int64_t wn, int64_t bn,
