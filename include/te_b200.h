@@ -158,8 +158,10 @@ TE_API int te_b200_matmul_nd(te_b200_ctx* ctx,
  * loads this part of the library there, which (with the default lazy loading) is during the first call on that
  * device; from then on the GPU holds it until the process exits.
  *   - d->precision must be TE_PREC_3XTF32; the device that is current when called is used.
- *   - A problem whose planes need more than TE_B200_STATIC_SCRATCH_BYTES (see te_b200_gemm_workspace_size)
- *     is refused with TE_ERR_WORKSPACE; nothing is launched.
+ *   - This entry always reads tf32 hi / lo planes out of the array: two planes of M x K4 and two of N x K4 floats per
+ *     batch (K4 = K rounded up to 4), each rounded up to 256 bytes.  A problem that needs more than
+ *     TE_B200_STATIC_SCRATCH_BYTES is refused with TE_ERR_WORKSPACE; nothing is launched.  (te_b200_gemm_workspace_size
+ *     describes the context path, which needs no plane storage for thin and small problems.)
  *   - The first successful call on a device does all one-time work (the load above, the array's address, and the
  *     attributes of every kernel any problem shape can reach): make it before any stream capture begins and while
  *     the device still has the array's size free.  If it fails, the next call tries again.

@@ -92,6 +92,13 @@ def test_static_scratch_entry_refuses_what_does_not_fit():
     rc = lib.te_b200_gemm_3xtf32_static(C.byref(d), None, None)
     assert rc == L.TE_ERR_WORKSPACE
     assert b"static scratch array holds" in lib.te_b200_last_error()
+    # a thin product too: the context path needs no plane storage for it (it splits inside the kernel), this entry
+    # always packs planes, so the 2 x 268 MB of B's planes are refused here
+    d = _desc(a, a, a)
+    d.M, d.N, d.K = 16, 8192, 8192
+    d.lda = d.ldb = d.ldc = 8192
+    assert lib.te_b200_gemm_3xtf32_static(C.byref(d), None, None) == L.TE_ERR_WORKSPACE
+    assert b"static scratch array holds" in lib.te_b200_last_error()
     d = _desc(a, a, a)
     d.precision = L.TE_PREC_TF32
     assert lib.te_b200_gemm_3xtf32_static(C.byref(d), None, None) == L.TE_ERR_BAD_ARGUMENT

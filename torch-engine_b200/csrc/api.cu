@@ -100,7 +100,7 @@ static size_t workspace_need(const te_gemm_desc* d) {
     Operand a, b;
     operands_from_desc(d, a, b);
     size_t need = 0;
-    if (d->precision == TE_PREC_3XTF32 && !three_x_split_in_kernel(d->M, d->N, d->K)) {
+    if (d->precision == TE_PREC_3XTF32 && !three_x_split_in_kernel(d->M, d->N, d->K, a.mn_major)) {
         // large products read hi / lo planes written by the packing pass
         need += 2 * (size_t)plane_bytes(a, d->K, d->batch_inner, d->batch_outer);
         need += 2 * (size_t)plane_bytes(b, d->K, d->batch_inner, d->batch_outer);
@@ -163,7 +163,7 @@ static int gemm_device(te_b200_ctx* ctx, const te_gemm_desc* d, cudaStream_t st,
     if (d->K > 0) {
         // 3xTF32: thin and small products are split inside the kernel from the operands as they are; large ones read
         // hi / lo planes written by the packing pass (see three_x_split_in_kernel)
-        const bool packed_3x = d->precision == TE_PREC_3XTF32 && !three_x_split_in_kernel(d->M, d->N, d->K);
+        const bool packed_3x = d->precision == TE_PREC_3XTF32 && !three_x_split_in_kernel(d->M, d->N, d->K, g.a.mn_major);
         if (packed_3x) {
             if ((rc = pack_into(ctx, ws, g.a, &g.a_lo, d->K, d->batch_inner, d->batch_outer, true, st))) return rc;
             if ((rc = pack_into(ctx, ws, g.b, &g.b_lo, d->K, d->batch_inner, d->batch_outer, true, st))) return rc;

@@ -95,6 +95,22 @@ extern "C" int te_b200_gemm_3xtf32_static(const te_gemm_desc* d, te_stream_t str
         set_error("te_b200_gemm_3xtf32_static runs the 3xTF32 mode only; set precision = TE_PREC_3XTF32");
         return TE_ERR_BAD_ARGUMENT;
     }
+    // This entry always reads hi / lo planes out of the scratch array (the context path splits thin and small problems
+    // inside the kernel and reports no scratch for them): what has to fit is counted here, plane by plane, exactly as
+    // the packing loop below lays the planes out.
+    need = 0;
+    if (d->K > 0 && d->M > 0 && d->N > 0) {
+        const int64_t kp = round_up(d->K, 4);
+        const int64_t rows[2] = {d->M, d->N};
+        const int64_t si[2] = {d->a_stride_inner, d->b_stride_inner}, so[2] = {d->a_stride_outer, d->b_stride_outer};
+        for (int i = 0; i < 2; ++i) {
+            const int64_t bi = (d->batch_inner > 1 && si[i] != 0) ? d->batch_inner : 1;
+            const int64_t bo = (d->batch_outer > 1 && so[i] != 0) ? d->batch_outer : 1;
+            const double planes = 2.0 * (double)bi * (double)bo * (double)rows[i] * (double)kp * 4.0;
+            if (planes > 4.0 * (double)TE_B200_STATIC_SCRATCH_BYTES) { need = SIZE_MAX; break; }
+            need += 2 * (size_t)round_up(bi * bo * rows[i] * kp * 4, 256);
+        }
+    }
     if (need > (size_t)TE_B200_STATIC_SCRATCH_BYTES) {
         char msg[200];
         snprintf(msg, sizeof msg, "problem needs %zu bytes of plane storage; the static scratch array holds %lld",

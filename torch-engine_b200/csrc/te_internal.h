@@ -113,9 +113,13 @@ struct TileChoice { int bn; bool pair; int k_splits; };
 // bandwidth the tensor core feeds from.  Measured: it wins where one extent is thin (16x8192x8192: 0.138 against
 // 0.275 ms) and on small problems (no two extra launches); the packing pre-pass wins on large squares (4096^3: 0.72
 // against 0.96 ms).
-inline bool three_x_split_in_kernel(int64_t M, int64_t N, int64_t K) {
+// A left operand stored M-major (a weight gradient dY^T . X) would have to be transposed by the packing pass, which
+// costs more than the split in shared memory up to a larger size (384x16384x1536: 0.125 against 0.206 ms,
+// 3072x4096x768: 0.126 against 0.140 ms).
+inline bool three_x_split_in_kernel(int64_t M, int64_t N, int64_t K, bool a_m_major) {
     const int64_t thin = M < N ? M : N;
-    return thin <= 256 || (double)M * (double)N * (double)K <= 2147483648.0;
+    const double mnk = (double)M * (double)N * (double)K;
+    return thin <= 256 || mnk <= 2147483648.0 || (a_m_major && mnk <= 17179869184.0);
 }
 TileChoice choose_tile(const te_b200_ctx* ctx, const GemmProblem& p);
 
