@@ -133,6 +133,21 @@ def test_workspace_sizing():
     assert n == (8 + 1) * 64 * 64 * 4
     # empty problems need nothing
     assert _ws(_desc(M=0))[1] == 0
+    # a left operand stored M-major (a weight gradient dY^T . X) is split inside the kernel up to M*N*K = 2^34 ...
+    wgrad = dict(M=384, N=1536, K=16384, a_major=L.TE_COL_MAJOR, lda=384, ldb=1536, ldc=1536, precision=L.TE_PREC_3XTF32)
+    assert _ws(_desc(**wgrad)) == (L.TE_OK, 0)
+    # ... the same extents with a K-major left operand read packed planes
+    assert _ws(_desc(**dict(wgrad, a_major=L.TE_ROW_MAJOR, lda=16384)))[1] == 2 * (384 + 1536) * 16384 * 4
+
+
+def test_static_entry_counts_its_own_planes():
+    """The no-allocation entry always packs hi / lo planes into its fixed array, whatever the context path would do
+    with the same problem: a thin product whose planes exceed the array is refused on the host, before any CUDA call."""
+    lib = L.load()
+    thin = _desc(M=16, N=8192, K=8192, lda=8192, ldb=8192, ldc=8192, precision=L.TE_PREC_3XTF32)
+    assert _ws(thin) == (L.TE_OK, 0)
+    assert lib.te_b200_gemm_3xtf32_static(C.byref(thin), None, None) == L.TE_ERR_WORKSPACE
+    assert b"static scratch array holds" in lib.te_b200_last_error()
 
 
 @pytest.mark.parametrize("total,world,align", [(8192, 8, 256), (8192, 4, 256), (65, 4, 1), (16, 8, 1), (16, 3, 1), (1000, 8, 128),
