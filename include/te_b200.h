@@ -429,6 +429,13 @@ TE_API int te_b200_all_gather_columns(te_b200_comm* comm, const float* c_local, 
  * (te_b200_shard_range(rows, world, rank, align)) are already at their position inside `full`. */
 TE_API int te_b200_all_gather_rows(te_b200_comm* comm, float* full, int64_t rows, int64_t cols, int64_t align,
                             te_stream_t stream);
+/* The one exchange of a data-parallel training step (every rank ran forward + backward on its own slice of the batch,
+ * with a mean loss over `local_rows` rows): grads (n floats on the device) becomes the row-weighted average of the
+ * ranks' gradients, i.e. the gradient of the mean loss over the whole batch.  One all-reduce of the gradient and one of
+ * the row count, in place, asynchronous on `stream`.  A rank with local_rows == 0 contributes nothing.  (The reference
+ * has no multi-device code; its single-device step divides by the batch's rows in CrossEntropyBatchedBackward,
+ * src/core/grad_fn.cpp:295.) */
+TE_API int te_b200_all_reduce_batch_mean(te_b200_comm* comm, float* grads, int64_t n, int64_t local_rows, te_stream_t stream);
 /* te_b200_gemm_f32_host for `world` ranks that all hold the same HOST operands (row-major A [M,K] and B [K,N]): each
  * rank copies 1/world of A's rows and its column block of B (te_b200_shard_range(N, world, rank, column_align)) to
  * its GPU, the ranks replicate A over NVLink, each multiplies and copies its columns of C back into its host C.

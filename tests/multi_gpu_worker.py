@@ -85,6 +85,19 @@ def main():
     torch.cuda.synchronize()
     assert torch.equal(gathered.view(B, H, T, dh), o_whole), "batch-sharded attention after the gather"
 
+    # ---- the data-parallel step's gradient exchange: row-weighted average over ranks with unequal (one empty) slices
+    n = 100003
+    rows_of = [37 * (r + 1) if r != world - 1 or world == 1 else 0 for r in range(world)]      # the last rank averaged over nothing
+    gs = [torch.randn(n, device="cuda", generator=torch.Generator(device="cuda").manual_seed(100 + r)) for r in range(world)]
+    want = sum(g_.double() * rows_of[r] for r, g_ in enumerate(gs)) / float(sum(rows_of))
+    mine = gs[rank].clone()
+    comm.all_reduce_batch_mean_(mine, rows_of[rank])
+    via_torch = gs[rank].clone()
+    sharding.all_reduce_batch_mean_(via_torch, rows_of[rank])
+    torch.cuda.synchronize()
+    assert float((mine.double() - want).abs().max()) <= 1e-6 * float(want.abs().max()) + 1e-7, "native gradient all-reduce"
+    assert float((mine - via_torch).abs().max()) <= 2e-6 * float(want.abs().max()), "native and torch.distributed exchanges differ"
+
     be.check_device_status()
     dist.barrier()
     comm.close()

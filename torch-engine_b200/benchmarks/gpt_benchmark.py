@@ -44,8 +44,10 @@ def main():
     torch.cuda.set_device(local)
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
-    sync = (lambda grads, rows: sharding.all_reduce_batch_mean_(grads, rows)) if world > 1 else None
     be = ops.Backend(local, workspace_bytes=2 << 30)
+    # the step's one exchange goes through the library's own communicator (csrc/dist.cu, te_b200_all_reduce_batch_mean)
+    comm = sharding.Communicator(be, world, rank) if world > 1 else None
+    sync = (lambda grads, rows: comm.all_reduce_batch_mean_(grads, rows)) if world > 1 else None
     g = torch.Generator(device="cuda").manual_seed(42)
     n_params = vocab * E + L * (4 * E + 4 * (E * E + E) + 2 * E * ff + ff + E) + 2 * E + vocab * E + vocab
     flat = torch.randn(n_params, device="cuda", generator=g) * 0.02

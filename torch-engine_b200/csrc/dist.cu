@@ -37,11 +37,12 @@ typedef int (*GetUniqueIdFn)(NcclId*);
 typedef int (*CommInitRankFn)(void**, int, NcclId, int);
 typedef int (*CommDestroyFn)(void*);
 typedef int (*AllGatherFn)(const void*, void*, size_t, int, void*, cudaStream_t);
+typedef int (*AllReduceFn)(const void*, void*, size_t, int, int, void*, cudaStream_t);
 typedef int (*SendFn)(const void*, size_t, int, int, void*, cudaStream_t);
 typedef int (*RecvFn)(void*, size_t, int, int, void*, cudaStream_t);
 typedef int (*GroupFn)(void);
 typedef const char* (*ErrStrFn)(int);
-constexpr int NCCL_FLOAT32 = 7;
+constexpr int NCCL_FLOAT32 = 7, NCCL_FLOAT64 = 8, NCCL_SUM = 0;
 
 struct NcclApi {
     void* handle = nullptr;
@@ -49,6 +50,7 @@ struct NcclApi {
     CommInitRankFn comm_init_rank = nullptr;
     CommDestroyFn comm_destroy = nullptr;
     AllGatherFn all_gather = nullptr;
+    AllReduceFn all_reduce = nullptr;
     SendFn send = nullptr;
     RecvFn recv = nullptr;
     GroupFn group_start = nullptr, group_end = nullptr;
@@ -69,12 +71,13 @@ int load_nccl() {
     a.comm_init_rank = reinterpret_cast<CommInitRankFn>(dlsym(h, "ncclCommInitRank"));
     a.comm_destroy = reinterpret_cast<CommDestroyFn>(dlsym(h, "ncclCommDestroy"));
     a.all_gather = reinterpret_cast<AllGatherFn>(dlsym(h, "ncclAllGather"));
+    a.all_reduce = reinterpret_cast<AllReduceFn>(dlsym(h, "ncclAllReduce"));
     a.send = reinterpret_cast<SendFn>(dlsym(h, "ncclSend"));
     a.recv = reinterpret_cast<RecvFn>(dlsym(h, "ncclRecv"));
     a.group_start = reinterpret_cast<GroupFn>(dlsym(h, "ncclGroupStart"));
     a.group_end = reinterpret_cast<GroupFn>(dlsym(h, "ncclGroupEnd"));
     a.error_string = reinterpret_cast<ErrStrFn>(dlsym(h, "ncclGetErrorString"));
-    if (!a.get_unique_id || !a.comm_init_rank || !a.comm_destroy || !a.all_gather || !a.send || !a.recv || !a.group_start ||
+    if (!a.get_unique_id || !a.comm_init_rank || !a.comm_destroy || !a.all_gather || !a.all_reduce || !a.send || !a.recv || !a.group_start ||
         !a.group_end || !a.error_string) {
         te::set_error("libnccl.so.2 lacks an entry point this driver needs");
         return TE_ERR_CUDA;
@@ -122,6 +125,21 @@ __global__ void __launch_bounds__(256) retile_columns_kernel(const RetileParams 
 
 }  // namespace
 
+// x *= s, and *rows = r: every rank weights its gradient by the number of rows it averaged over ...
+__global__ void __launch_bounds__(256) scale_set_rows_kernel(float* x, long long n, float s, double* rows, double r) {
+    te::griddep_wait();
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) x[i] *= s;
+    if (blockIdx.x == 0 && threadIdx.x == 0) *rows = r;
+}
+// ... and after the sums over the ranks, x /= total rows.
+__global__ void __launch_bounds__(256) divide_by_rows_kernel(float* x, long long n, const double* rows) {
+    te::griddep_wait();
+    const float inv = (float)(1.0 / *rows);
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) x[i] *= inv;
+}
+
 struct te_b200_comm {
     te_b200_ctx* ctx = nullptr;
     void* nccl = nullptr;
@@ -131,6 +149,7 @@ struct te_b200_comm {
     float* dev_b = nullptr;
     float* dev_c = nullptr;
     size_t dev_a_bytes = 0, dev_b_bytes = 0, dev_c_bytes = 0;
+    double* dev_rows = nullptr;         // row count of the data-parallel gradient average (one double)
     cudaStream_t stream = nullptr;
 };
 
@@ -177,6 +196,7 @@ int te_b200_comm_destroy(te_b200_comm* c) {
     if (c->dev_a) cudaFree(c->dev_a);
     if (c->dev_b) cudaFree(c->dev_b);
     if (c->dev_c) cudaFree(c->dev_c);
+    if (c->dev_rows) cudaFree(c->dev_rows);
     if (c->nccl) g_nccl.comm_destroy(c->nccl);
     delete c;
     return TE_OK;
@@ -256,6 +276,32 @@ int te_b200_all_gather_rows(te_b200_comm* c, float* full, int64_t rows, int64_t 
     }
     // in place: this rank's rows already sit at their position inside `full`
     return all_gather_v(c, full + offsets[c->rank], full, counts, offsets, static_cast<cudaStream_t>(stream));
+}
+
+int te_b200_all_reduce_batch_mean(te_b200_comm* c, float* grads, int64_t n, int64_t local_rows, te_stream_t stream) {
+    if (int rc = check_comm(c)) return rc;
+    if (n < 0 || local_rows < 0) return bad("all_reduce_batch_mean: negative count");
+    if (n == 0) return TE_OK;
+    if (!grads) return bad("all_reduce_batch_mean: NULL pointer");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (!c->dev_rows) {
+        cudaError_t e = cudaMalloc(reinterpret_cast<void**>(&c->dev_rows), 2 * sizeof(double));
+        if (e != cudaSuccess) return te::cuda_fail(e, "cudaMalloc(row count)");
+    }
+    long long blocks = (n + 255) / 256;
+    if (blocks > (long long)c->ctx->sm_count * 16) blocks = (long long)c->ctx->sm_count * 16;
+    cudaError_t e = te::launch_pdl(scale_set_rows_kernel, dim3((unsigned)blocks), dim3(256), 0, st, grads, (long long)n, (float)local_rows,
+                                   c->dev_rows, (double)local_rows);
+    if (e != cudaSuccess) return te::cuda_fail(e, "scale_set_rows_kernel launch");
+    int rr;
+    if (c->world > 1) {
+        if ((rr = g_nccl.all_reduce(grads, grads, (size_t)n, NCCL_FLOAT32, NCCL_SUM, c->nccl, st))) return nccl_fail(rr, "ncclAllReduce");
+        if ((rr = g_nccl.all_reduce(c->dev_rows, c->dev_rows, 1, NCCL_FLOAT64, NCCL_SUM, c->nccl, st))) return nccl_fail(rr, "ncclAllReduce");
+    }
+    e = te::launch_pdl(divide_by_rows_kernel, dim3((unsigned)blocks), dim3(256), 0, st, grads, (long long)n, (const double*)c->dev_rows);
+    if (e != cudaSuccess) return te::cuda_fail(e, "divide_by_rows_kernel launch");
+    c->ctx->launches += 2;
+    return TE_OK;
 }
 
 static int grow(float** buf, size_t* have, size_t need) {

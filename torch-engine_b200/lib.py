@@ -127,6 +127,7 @@ SIGNATURES = {
     "te_b200_all_gather_columns": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_int64, C.c_void_p, C.c_void_p,
                                               C.c_int64, C.c_void_p]),
     "te_b200_all_gather_rows": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_int64, C.c_void_p]),
+    "te_b200_all_reduce_batch_mean": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_void_p]),
     "te_b200_gemm_f32_host_sharded": (C.c_int, [C.c_void_p, C.POINTER(GemmDesc), C.c_int64]),
     "te_b200_shard_range": (C.c_int, [C.c_int64, C.c_int, C.c_int, C.c_int64, c_i64_p, c_i64_p]),
 }

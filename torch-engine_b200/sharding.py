@@ -119,6 +119,14 @@ class Communicator:
                                                      self.be._stream()))
         return out
 
+    def all_reduce_batch_mean_(self, grads, local_rows):
+        """te_b200_all_reduce_batch_mean: the data-parallel step's gradient exchange through the library's own
+        communicator (the counterpart of all_reduce_batch_mean_ above, which goes through torch.distributed); in place."""
+        assert grads.is_contiguous() and grads.dtype == torch.float32
+        L.check(self._lib.te_b200_all_reduce_batch_mean(self._comm, C.c_void_p(grads.data_ptr()), grads.numel(), int(local_rows),
+                                                        self.be._stream()))
+        return grads
+
     def all_gather_rows(self, full, align=1):
         """In place: every rank filled its own row block of the dense [rows, cols] tensor `full`."""
         rows = full.shape[0]
