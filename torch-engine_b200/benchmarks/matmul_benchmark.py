@@ -140,7 +140,7 @@ def main():
                ("%.0f%% of cuBLAS-TF32" % r["pct_of_cublas"]) if cublas_ms else ""), flush=True)
 
     # ---- GEMM sweep: squares and skinny shapes, given as (M, K, N) like the reference ----
-    shapes = [(1024, 1024, 1024), (2048, 2048, 2048), (4096, 4096, 4096), (8192, 8192, 8192),
+    shapes = [(512, 512, 512), (1024, 1024, 1024), (2048, 2048, 2048), (4096, 4096, 4096), (8192, 8192, 8192),
               (8192, 512, 8192), (8192, 8192, 512), (16, 8192, 8192)]
     if not args.quick:
         shapes.append((16384, 16384, 16384))
