@@ -32,7 +32,9 @@ enum : int {  // where a bounded wait gave up (stored in the device status word)
     WAIT_MMA_TMEM_EMPTY = 103,
     WAIT_EPI_TMEM_FULL = 104,
     WAIT_TEARDOWN = 105,
-    WAIT_CONVERTER_FULL = 106
+    WAIT_CONVERTER_FULL = 106,
+    WAIT_THIN_FULL = 107,        // thin FP32 product: a consumer warp waiting for a stage of B
+    WAIT_THIN_EMPTY = 108        // ... its producer waiting for a stage to be released
 };
 
 // How an epilogue thread's 32 consecutive columns of one row reach global memory.

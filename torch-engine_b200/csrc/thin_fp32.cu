@@ -17,6 +17,7 @@
 // the epilogue (scale, bias, GELU, residual), as for the tensor-core kernels.
 // Limits: one product (no batch), A with K contiguous, B with N contiguous, M <= 16; everything else stays on the
 // tensor-core path.
+#include <cuda.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -120,6 +121,134 @@ __global__ void __launch_bounds__(THIN_THREADS) thin_fp32_kernel(const ThinParam
     }
 }
 
+// ---- the same product with B staged by TMA ---------------------------------------------------------------------
+// Above, what bounds the kernel is the bytes of B a thread can keep in flight in registers (96 KB per SM).  Here a
+// producer warp lands 8-row x 1024-column slabs of B in a ring of six 32 KB shared-memory stages (160 KB in flight per
+// SM, no register cost), eight consumer warps read their four columns of a slab back with one 16-byte load per k and
+// keep the same 64 accumulators.  One CTA per SM; used when the grid of column blocks x K slices fills the GPU.
+constexpr int TT_CONSUMERS = 256;
+constexpr int TT_THREADS = TT_CONSUMERS + 32;
+constexpr int TT_COLS = 4 * TT_CONSUMERS;            // 1024 columns of C per CTA
+constexpr int TT_KS = 8;                              // rows of B per stage
+constexpr int TT_BOX_COLS = 256;                      // a TMA box is at most 256 elements wide
+constexpr int TT_BOXES = TT_COLS / TT_BOX_COLS;
+constexpr int TT_STAGE_BYTES = TT_KS * TT_COLS * 4;   // 32 KB
+constexpr int TT_STAGES = 6;
+constexpr int TT_SMEM_BYTES = TT_STAGES * TT_STAGE_BYTES + THIN_KC * THIN_M * 4 + 256 + 128;
+
+__global__ void __launch_bounds__(TT_THREADS, 1) thin_fp32_tma_kernel(const __grid_constant__ CUtensorMap tm_b, const ThinParams p, int* status) {
+    extern __shared__ uint8_t tt_smem[];
+    const uint32_t raw = smem_u32(tt_smem);
+    const uint32_t ring = (raw + 127u) & ~127u;
+    const uint32_t a_addr = ring + TT_STAGES * TT_STAGE_BYTES;
+    float (*a_sm)[THIN_M] = reinterpret_cast<float (*)[THIN_M]>(tt_smem + (a_addr - raw));
+    const uint32_t bar_full = a_addr + THIN_KC * THIN_M * 4;
+    const uint32_t bar_empty = bar_full + 8 * TT_STAGES;
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tt_smem + (bar_empty + 8 * TT_STAGES - raw));
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < TT_STAGES; ++s) {
+            mbar_init(bar_full + 8 * s, 1);
+            mbar_init(bar_empty + 8 * s, TT_CONSUMERS / 32);
+        }
+        *abort_flag = 0;
+        fence_barrier_init();
+        fence_proxy_async_smem();
+        tma_prefetch_desc(&tm_b);
+    }
+    __syncthreads();
+    griddep_launch_dependents();
+    griddep_wait();
+    const int k_begin = blockIdx.y * p.k_per_slice;
+    const int k_end = min(k_begin + p.k_per_slice, p.K);
+    const int stages = (k_end - k_begin + TT_KS - 1) / TT_KS;
+    const int col0 = blockIdx.x * TT_COLS;
+    if (warp == TT_CONSUMERS / 32) {
+        // ------------------------------------------------------------ producer: slabs of B, K ascending
+        if (lane == 0) {
+            for (int i = 0; i < stages; ++i) {
+                const int s = i % TT_STAGES;
+                if (!wait_bounded(bar_empty + 8 * s, ((i / TT_STAGES) & 1) ^ 1, abort_flag, status, WAIT_THIN_EMPTY)) break;
+                mbar_arrive_expect_tx(bar_full + 8 * s, TT_STAGE_BYTES);     // rows past K and columns past N arrive as zeros
+#pragma unroll
+                for (int b = 0; b < TT_BOXES; ++b)
+                    tma_load_4d(ring + s * TT_STAGE_BYTES + b * (TT_KS * TT_BOX_COLS * 4), &tm_b, bar_full + 8 * s,
+                                col0 + b * TT_BOX_COLS, k_begin + i * TT_KS, 0, 0);
+            }
+            if (*abort_flag) {      // copies already issued still write shared memory: let them land
+                const uint64_t t0 = global_timer_ns();
+                while (global_timer_ns() - t0 < 200000ull) {
+                }
+            }
+        }
+    } else {
+        // ------------------------------------------------------------ consumers: four columns x 16 rows each
+        const int t = threadIdx.x;
+        const int c0 = col0 + 4 * t;
+        unsigned long long acc[4][THIN_M / 2];
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+#pragma unroll
+            for (int q = 0; q < THIN_M / 2; ++q) acc[c][q] = 0ull;
+        const int sm_m = t & 15, sm_k = t >> 4;                           // 16 k rows of A per staging pass
+        // this thread's 16 bytes of a slab row: box t / 64, 16-byte unit t % 64
+        const uint32_t b_off = (uint32_t)(t >> 6) * (TT_KS * TT_BOX_COLS * 4) + (uint32_t)(t & 63) * 16;
+        // A warp whose wait ran out keeps walking the loop for the two barriers of every A chunk (the other warps
+        // count on all 256 threads there) and does nothing else.
+        bool ok = true;
+        for (int i = 0; i < stages; ++i) {
+            const int kk0 = (i * TT_KS) % THIN_KC;
+            if (kk0 == 0) {          // next 128 k of A: [k][m], zeros past the slice and past M
+                asm volatile("bar.sync 1, %0;" ::"n"(TT_CONSUMERS) : "memory");
+                const int kc = k_begin + i * TT_KS;
+                if (ok) {
+#pragma unroll
+                    for (int j = 0; j < THIN_KC / 16; ++j) {
+                        const int kk = sm_k + 16 * j, k = kc + kk;
+                        a_sm[kk][sm_m] = (sm_m < p.M && k < k_end) ? __ldg(p.a + (long long)sm_m * p.lda + k) : 0.0f;
+                    }
+                }
+                asm volatile("bar.sync 1, %0;" ::"n"(TT_CONSUMERS) : "memory");
+            }
+            if (!ok) continue;
+            const int s = i % TT_STAGES;
+            ok = wait_bounded(bar_full + 8 * s, (i / TT_STAGES) & 1, abort_flag, status, WAIT_THIN_FULL);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) continue;
+            const uint32_t slab = ring + s * TT_STAGE_BYTES + b_off;
+            float4 v[TT_KS];
+#pragma unroll
+            for (int u = 0; u < TT_KS; ++u) v[u] = ld_shared_v4(slab + u * (TT_BOX_COLS * 4));
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_empty + 8 * s);                 // the slab is in registers
+#pragma unroll
+            for (int u = 0; u < TT_KS; ++u) {
+                const ulonglong2* row = reinterpret_cast<const ulonglong2*>(&a_sm[kk0 + u][0]);
+                const unsigned long long w0 = pair_of(v[u].x), w1 = pair_of(v[u].y), w2 = pair_of(v[u].z), w3 = pair_of(v[u].w);
+#pragma unroll
+                for (int q = 0; q < THIN_M / 4; ++q) {
+                    const ulonglong2 a = row[q];
+                    fma2(acc[0][2 * q], a.x, w0); fma2(acc[0][2 * q + 1], a.y, w0);
+                    fma2(acc[1][2 * q], a.x, w1); fma2(acc[1][2 * q + 1], a.y, w1);
+                    fma2(acc[2][2 * q], a.x, w2); fma2(acc[2][2 * q + 1], a.y, w2);
+                    fma2(acc[3][2 * q], a.x, w3); fma2(acc[3][2 * q + 1], a.y, w3);
+                }
+            }
+        }
+        if (ok && c0 < p.N) {
+            float* out = p.partial + (long long)blockIdx.y * p.M * p.N + c0;
+#pragma unroll
+            for (int q = 0; q < THIN_M / 2; ++q) {
+                float lo[4], hi[4];
+#pragma unroll
+                for (int c = 0; c < 4; ++c) unpack(acc[c][q], lo[c], hi[c]);
+                if (2 * q < p.M) *reinterpret_cast<float4*>(out + (long long)(2 * q) * p.N) = make_float4(lo[0], lo[1], lo[2], lo[3]);
+                if (2 * q + 1 < p.M) *reinterpret_cast<float4*>(out + (long long)(2 * q + 1) * p.N) = make_float4(hi[0], hi[1], hi[2], hi[3]);
+            }
+        }
+    }
+}
+
 }  // namespace
 
 // Returns TE_OK when the product was issued here, -1 when it is outside this form's limits (the caller then takes the
@@ -129,6 +258,40 @@ int launch_thin_fp32(te_b200_ctx* ctx, const GemmProblem& g, cudaStream_t stream
     if (g.a.mn_major || !g.b.mn_major || g.preact) return -1;
     if ((g.N & 3) || (g.b.ld & 3) || (reinterpret_cast<uintptr_t>(g.b.ptr) & 15) || (reinterpret_cast<uintptr_t>(g.split_ws) & 15)) return -1;
     if (g.N > INT32_MAX || g.K > INT32_MAX) return -1;
+    // B staged by TMA (one CTA per SM) when its grid of 1024-column blocks x K slices fills most of the GPU
+    {
+        const long long cb = (g.N + TT_COLS - 1) / TT_COLS;
+        long long sl = ctx->sm_count / cb;
+        if (sl > g.K / 128) sl = g.K / 128;
+        if (sl > 64) sl = 64;
+        if (sl >= 2 && cb * sl * 10 >= (long long)ctx->sm_count * 8) {
+            long long k_per = (g.K + sl - 1) / sl;
+            k_per = (k_per + 15) / 16 * 16;
+            sl = (g.K + k_per - 1) / k_per;
+            CUtensorMap mb;
+            const int64_t strides[3] = {0, 0, g.b.ld};
+            if (sl >= 2 && g.split_ws && (size_t)sl * (size_t)g.M * (size_t)g.N * sizeof(float) <= g.split_ws_bytes &&
+                make_bhtc_map(ctx, &mb, g.b.ptr, g.N, g.K, 1, 1, strides, TT_BOX_COLS, TT_KS, CU_TENSOR_MAP_SWIZZLE_NONE)) {
+                int& attr = ctx->kernel_state[reinterpret_cast<const void*>(thin_fp32_tma_kernel)];
+                if (attr < TT_SMEM_BYTES) {
+                    cudaError_t ea = cudaFuncSetAttribute(thin_fp32_tma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TT_SMEM_BYTES);
+                    if (ea != cudaSuccess) return cuda_fail(ea, "cudaFuncSetAttribute(thin_fp32_tma_kernel)");
+                    attr = TT_SMEM_BYTES;
+                }
+                ThinParams p;
+                p.a = g.a.ptr; p.lda = g.a.ld;
+                p.b = g.b.ptr; p.ldb = g.b.ld;
+                p.partial = g.split_ws;
+                p.M = (int)g.M; p.N = (int)g.N; p.K = (int)g.K;
+                p.k_per_slice = (int)k_per;
+                cudaError_t e = launch_pdl(thin_fp32_tma_kernel, dim3((unsigned)cb, (unsigned)sl), dim3(TT_THREADS), (size_t)TT_SMEM_BYTES, stream,
+                                           mb, p, ctx->d_status);
+                if (e != cudaSuccess) return cuda_fail(e, "thin_fp32_tma_kernel launch");
+                ctx->launches += 1;
+                return finish_split(ctx, g, (int)sl, stream);
+            }
+        }
+    }
     const long long col_blocks = (g.N + THIN_COLS - 1) / THIN_COLS;
     // about three CTAs per SM (each keeps 16 KB of B in flight), at least 128 k per slice, at least two slices (the
     // reduction applies the epilogue)
