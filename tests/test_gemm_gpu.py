@@ -373,6 +373,33 @@ def test_thin_rows_fp32_accurate_mode(backend, M, K, N):
     backend.check_device_status()
 
 
+@pytest.mark.parametrize("M,K,N,pad", [(16, 4096, 4096, 0), (8, 2048, 8192, 0), (3, 1000, 1536, 0), (13, 1031, 777, 0),
+                                       (16, 1024, 1024, 3), (1, 8192, 512, 0)])
+def test_thin_rows_linear_layout_fp32_accurate_mode(backend, M, K, N, pad):
+    """The same mode for Linear's layout, X[M,K] . W[N,K]^T with at most 16 rows of X: two launches (lanes along k
+    with a fixed reduction tree over the lanes, then the K-slice reduction with the epilogue).  W on 16-byte rows is
+    staged by TMA; an odd K or an odd leading dimension (pad) takes the plain-load form.  Error against float64 at
+    FP32 level for both, with bias + GELU from the reduction."""
+    g = torch.Generator(device="cuda").manual_seed(M * 137 + K + pad)
+    x = torch.rand(M, K, device="cuda", generator=g) * 2 - 1
+    w = (torch.rand(N, K + pad, device="cuda", generator=g) * 2 - 1)[:, :K]
+    ref = x.double() @ w.double().t()
+    n0 = backend.launches
+    c = backend.matmul(x, w.t(), precision="3xtf32")
+    assert backend.launches == n0 + 2
+    assert float((c.double() - ref).abs().max() / ref.abs().max()) <= 2e-6
+    if pad == 0:
+        bias = torch.randn(N, device="cuda", generator=g)
+        n0 = backend.launches
+        y = backend.linear_forward(x, w, bias, gelu=True, precision="3xtf32")
+        assert backend.launches == n0 + 2
+        want = torch.nn.functional.gelu(ref + bias.double(), approximate="tanh")
+        assert float((y.double() - want).abs().max()) <= 2e-6 * float(want.abs().max()) + 2e-6
+    # repeated calls give the same bits (no atomics, one reduction tree)
+    assert torch.equal(c, backend.matmul(x, w.t(), precision="3xtf32"))
+    backend.check_device_status()
+
+
 def test_launch_counter_moves(backend):
     n0 = backend.launches
     backend.matmul(torch.ones(8, 8, device="cuda"), torch.ones(8, 8, device="cuda"))

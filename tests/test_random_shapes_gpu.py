@@ -1,5 +1,5 @@
 """Seeded random shapes through the C ABI against float64: the forms whose limits are easy to get wrong -- thin
-FP32-accurate products around their row / column / alignment limits, the fused attention kernels around their
+FP32-accurate products (both layouts of the right operand) around their row / column / alignment limits, the fused attention kernels around their
 sequence-length and head-size limits (dense operands and MultiHeadAttention head views), and MultiHeadAttention with
 its three input projections as one product against three.
 
@@ -30,6 +30,33 @@ def test_thin_products_around_the_limits(backend):
         b = (torch.rand(K, N + pad_b, device="cuda", generator=g) * 2 - 1)[:, :N]
         c = backend.matmul(a, b, precision="3xtf32")
         assert _rel(c, a.double() @ b.double()) <= 1e-5, (M, K, N, pad_a, pad_b)
+    backend.check_device_status()
+
+
+def test_thin_linear_layout_around_the_limits(backend):
+    """X[M,K] . W[N,K]^T with M <= 16 in FP32-accurate mode (lanes along k, W staged by TMA when its rows sit on
+    16-byte boundaries, by plain loads otherwise): through Linear with bias / GELU and through matmul on W's
+    transposed view."""
+    rnd = random.Random(17)
+    g = torch.Generator(device="cuda").manual_seed(17)
+    for it in range(48):
+        M = rnd.randint(1, 18)                                        # 17 and 18 rows take the tensor cores
+        K = rnd.choice([256, 257, 300, 511, 1000, 1024, 2049, 4097, 8192])
+        N = rnd.choice([512, 513, 1000, 1024, 2052, 3001, 4096])
+        pad_x, pad_w = rnd.choice([0, 4, 7]), rnd.choice([0, 4, 3])   # a pad of 3 or an odd K takes W off 16-byte rows
+        x = (torch.rand(M, K + pad_x, device="cuda", generator=g) * 2 - 1)[:, :K]
+        w = (torch.rand(N, K + pad_w, device="cuda", generator=g) * 2 - 1)[:, :K]
+        ref = x.double() @ w.double().t()
+        c = backend.matmul(x, w.t(), precision="3xtf32")
+        assert _rel(c, ref) <= 1e-5, (M, K, N, pad_x, pad_w)
+        if it % 3 == 0:
+            bias = torch.rand(N, device="cuda", generator=g)
+            gelu = it % 2 == 0
+            y = backend.linear_forward(x.contiguous(), w.contiguous(), bias, gelu=gelu, precision="3xtf32")
+            want = ref + bias.double()
+            if gelu:
+                want = torch.nn.functional.gelu(want, approximate="tanh")
+            assert _rel(y, want) <= 1e-5, (M, K, N, gelu)
     backend.check_device_status()
 
 

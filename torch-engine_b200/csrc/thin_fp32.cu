@@ -15,8 +15,9 @@
 // K is cut into slices so that a few CTAs per SM exist (the grid is column blocks x slices); every slice writes a
 // partial [M, N] tile to the split-K scratch and the common reduction adds the slices in slice order and applies
 // the epilogue (scale, bias, GELU, residual), as for the tensor-core kernels.
-// Limits: one product (no batch), A with K contiguous, B with N contiguous, M <= 16; everything else stays on the
-// tensor-core path.
+// Limits: one product (no batch), A with K contiguous, M <= 16, K >= 256, N >= 512; everything else stays on the
+// tensor-core path.  B with N contiguous (a row-major right operand) takes the kernels below; B with K contiguous
+// (Linear's weight, [N, K]) takes the pair of kernels further down, which run the lanes along k instead.
 #include <cuda.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
@@ -249,13 +250,370 @@ __global__ void __launch_bounds__(TT_THREADS, 1) thin_fp32_tma_kernel(const __gr
     }
 }
 
+
+// ---- the Linear layout: C[M,N] = X[M,K] . W[N,K]^T, both operands with K contiguous --------------------------------------
+// Here a row of W is one column of C, so the lanes of a warp run along k (their loads of a row of W are one contiguous
+// 128-byte line) and the sum over k ends with a reduction over the lanes.  A warp task is eight rows of W over one K
+// slice: every lane keeps 8 x 16 accumulators (as 64 row pairs (m, m + 1)), reads per step four k (k = base + 32.j + lane)
+// of each of the eight rows -- the next step's 32 values are requested before the current ones are used -- and takes
+// the sixteen values of X for a k as four 16-byte reads of shared memory, where the CTA has laid its K slice of X out
+// as [k][m] with a pitch of 20 floats (consecutive k then fall in distinct bank groups).  Eight rows per task is what
+// keeps the shared-memory reads (64 wavefronts per step) under the FMA issue (256 packed FMAs per step).  The task ends
+// with a halving exchange over the lanes (128 values -> 4 per lane in 124 shuffles, the same tree for every task) and
+// 4 stores per lane into the slice's partial tile; the common reduction adds the slices and applies the epilogue.
+constexpr int NT_ROWS = 8;
+constexpr int NT_WARPS = 8;
+constexpr int NT_THREADS = NT_WARPS * 32;
+constexpr int NT_PITCH = 20;                // floats per k of the staged X slice: 16 rows + 4 of padding
+constexpr int NT_STEP = 128;                // k per warp step: four per lane
+constexpr int NT_KMAX = 2048;               // K slice of X held in shared memory (160 KB)
+
+struct ThinNtParams {
+    const float* x; long long ldx;
+    const float* w; long long ldw;
+    float* partial;                  // [slices][M][N]
+    int M, N, K;
+    int k_per_slice;                 // multiple of NT_STEP, <= NT_KMAX
+    int rows_per_cta;                // multiple of NT_ROWS
+};
+
+template <int HALF>
+__device__ __forceinline__ void halve_over_lanes(float* v, int off, bool up) {
+#pragma unroll
+    for (int i = 0; i < HALF; ++i) {
+        const float send = up ? v[i] : v[i + HALF];
+        const float keep = up ? v[i + HALF] : v[i];
+        v[i] = keep + __shfl_xor_sync(0xffffffffu, send, off);
+    }
+}
+
+__device__ __forceinline__ void nt_load_step(float (&w)[NT_ROWS][4], const float* const (&row)[NT_ROWS], int k, int k_end) {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const int kj = k + 32 * j;
+        const bool in = kj < k_end;                 // past the slice the X rows are zero, W is not read
+#pragma unroll
+        for (int r = 0; r < NT_ROWS; ++r) w[r][j] = in ? __ldg(row[r] + kj) : 0.0f;
+    }
+}
+
+template <int MP>
+__device__ __forceinline__ void nt_fma_step(unsigned long long (&acc)[NT_ROWS][MP], const float (&w)[NT_ROWS][4], const float* x_lane) {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const ulonglong2* xr = reinterpret_cast<const ulonglong2*>(x_lane + 32 * j * NT_PITCH);
+        ulonglong2 x[MP / 2];                        // rows 0 .. 2 MP - 1 of X at this k, as pairs
+#pragma unroll
+        for (int q = 0; q < MP / 2; ++q) x[q] = xr[q];
+#pragma unroll
+        for (int r = 0; r < NT_ROWS; ++r) {
+            const unsigned long long wp = pair_of(w[r][j]);
+#pragma unroll
+            for (int q = 0; q < MP / 2; ++q) {
+                fma2(acc[r][2 * q], x[q].x, wp);
+                fma2(acc[r][2 * q + 1], x[q].y, wp);
+            }
+        }
+    }
+}
+
+// End of a warp task: the lanes' 8 x 2 MP sums are added over the lanes by a halving exchange (the same tree for every
+// task), after which lane l holds entries l V / 32 .. of v[r * 2 MP + m], and stored into the slice's partial tile.
+template <int MP>
+__device__ __forceinline__ void nt_reduce_store(const unsigned long long (&acc)[NT_ROWS][MP], int lane, int n_first, int slice, const ThinNtParams& p) {
+    constexpr int V = NT_ROWS * 2 * MP, PER = V / 32;
+    float v[V];
+#pragma unroll
+    for (int r = 0; r < NT_ROWS; ++r)
+#pragma unroll
+        for (int q = 0; q < MP; ++q) unpack(acc[r][q], v[r * 2 * MP + 2 * q], v[r * 2 * MP + 2 * q + 1]);
+    halve_over_lanes<V / 2>(v, 16, lane & 16);
+    halve_over_lanes<V / 4>(v, 8, lane & 8);
+    halve_over_lanes<V / 8>(v, 4, lane & 4);
+    halve_over_lanes<V / 16>(v, 2, lane & 2);
+    halve_over_lanes<V / 32>(v, 1, lane & 1);
+    const int n = n_first + (lane * PER) / (2 * MP), m0 = (lane * PER) % (2 * MP);
+    if (n < p.N) {
+        float* out = p.partial + ((long long)slice * p.M + m0) * p.N + n;
+#pragma unroll
+        for (int j = 0; j < PER; ++j)
+            if (m0 + j < p.M) out[(long long)j * p.N] = v[j];
+    }
+}
+
+// The CTA's K slice of X, [m][k] in global memory, laid out as [k][m] in shared memory; rows past M and k past the
+// slice are zero.  A thread owns every 256th k and has its sixteen loads of a k in flight together.
+__device__ __forceinline__ void nt_stage_x(float* x_sm, const ThinNtParams& p, int k_begin, int k_len, int k_pad, int t) {
+#pragma unroll 2
+    for (int k = t; k < k_pad; k += NT_THREADS) {
+        float v[THIN_M];
+#pragma unroll
+        for (int m = 0; m < THIN_M; ++m) v[m] = (m < p.M && k < k_len) ? __ldg(p.x + (long long)m * p.ldx + k_begin + k) : 0.0f;
+        float4* dst = reinterpret_cast<float4*>(x_sm + k * NT_PITCH);
+#pragma unroll
+        for (int q = 0; q < THIN_M / 4; ++q) dst[q] = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+    }
+}
+
+template <int MP>
+__global__ void __launch_bounds__(NT_THREADS, 1) thin_nt_fp32_kernel(const ThinNtParams p) {
+    extern __shared__ __align__(16) float nt_x[];               // [k_per_slice][NT_PITCH]
+    griddep_launch_dependents();
+    griddep_wait();
+    const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
+    const int k_begin = blockIdx.y * p.k_per_slice;
+    const int k_end = min(k_begin + p.k_per_slice, p.K);
+    const int k_len = k_end - k_begin;
+    const int k_pad = (k_len + NT_STEP - 1) / NT_STEP * NT_STEP;
+    nt_stage_x(nt_x, p, k_begin, k_len, k_pad, t);
+    __syncthreads();
+    const int row_begin = blockIdx.x * p.rows_per_cta;
+    const int row_end = min(row_begin + p.rows_per_cta, p.N);
+    const int steps = k_pad / NT_STEP;
+    for (int n0 = row_begin + warp * NT_ROWS; n0 < row_end; n0 += NT_WARPS * NT_ROWS) {
+        const float* row[NT_ROWS];                               // rows past N read the last row (their sums are not stored)
+#pragma unroll
+        for (int r = 0; r < NT_ROWS; ++r) row[r] = p.w + (long long)min(n0 + r, p.N - 1) * p.ldw + k_begin + lane;
+        unsigned long long acc[NT_ROWS][MP];
+#pragma unroll
+        for (int r = 0; r < NT_ROWS; ++r)
+#pragma unroll
+            for (int q = 0; q < MP; ++q) acc[r][q] = 0ull;
+        float wa[NT_ROWS][4], wb[NT_ROWS][4];
+        const float* x_lane = nt_x + lane * NT_PITCH;
+        nt_load_step(wa, row, 0, k_len - lane);                  // "k < k_len - lane" is "k + lane < k_len"
+        for (int s = 0; s < steps; s += 2) {
+            if (s + 1 < steps) nt_load_step(wb, row, (s + 1) * NT_STEP, k_len - lane);
+            nt_fma_step(acc, wa, x_lane + s * NT_STEP * NT_PITCH);
+            if (s + 1 < steps) {
+                if (s + 2 < steps) nt_load_step(wa, row, (s + 2) * NT_STEP, k_len - lane);
+                nt_fma_step(acc, wb, x_lane + (s + 1) * NT_STEP * NT_PITCH);
+            }
+        }
+        nt_reduce_store<MP>(acc, lane, n0, blockIdx.y, p);
+    }
+}
+
+
+// The same warp task with W staged by TMA: 64-row x 128-k tiles of W (the eight tasks of the CTA's eight warps, one
+// step) land in a ring of four 32 KB stages, so the bytes in flight cost no registers, and the warps read their values
+// of W back from shared memory (lanes along k: conflict-free).  There is no producer warp -- a ninth warp would cap
+// the kernel at 168 registers, under what 128 accumulators need: lane 0 of warp 0 refills a stage one step after the
+// warps took its tile into registers (three tiles stay in flight).  One CTA per SM; a CTA takes a contiguous range of
+// the (K slice, 64-row group) list, slice-major, and restages its slice of X when the range crosses into the next
+// slice.  Needs W on 16-byte boundaries (pointer and leading dimension).
+constexpr int NTT_THREADS = NT_THREADS;
+constexpr int NTT_GROUP = NT_WARPS * NT_ROWS;                 // 64 rows of W per stage
+constexpr int NTT_STAGE_BYTES = NTT_GROUP * NT_STEP * 4;      // 32 KB
+constexpr int NTT_STAGES = 4;
+constexpr int NTT_KMAX = 1024;                                // K slice of X held in shared memory (80 KB)
+constexpr int NTT_SMEM_BYTES = 128 + NTT_STAGES * NTT_STAGE_BYTES + NTT_KMAX * NT_PITCH * 4 + 16 * NTT_STAGES + 16;
+
+struct ThinNtTmaParams {
+    ThinNtParams q;                  // rows_per_cta unused
+    int slices, groups;              // K slices, 64-row groups of W
+};
+
+// Walks the tiles of a CTA's task range in the order they are consumed.
+struct NtTileCursor {
+    int t, s, steps, k_begin, grp;
+    __device__ __forceinline__ void open(const ThinNtTmaParams& pp, int task) {
+        t = task; s = 0;
+        const int slice = t / pp.groups;
+        grp = t - slice * pp.groups;
+        k_begin = slice * pp.q.k_per_slice;
+        steps = (min(pp.q.k_per_slice, pp.q.K - k_begin) + NT_STEP - 1) / NT_STEP;
+    }
+    __device__ __forceinline__ void next(const ThinNtTmaParams& pp, int t_end) {
+        if (++s == steps && t + 1 < t_end) open(pp, t + 1);
+    }
+};
+
+template <int MP>
+__global__ void __launch_bounds__(NTT_THREADS, 1) thin_nt_tma_kernel(const __grid_constant__ CUtensorMap tm_w, const ThinNtTmaParams pp, int* status) {
+    extern __shared__ uint8_t ntt_smem[];
+    const ThinNtParams& p = pp.q;
+    const uint32_t raw = smem_u32(ntt_smem);
+    const uint32_t ring = (raw + 127u) & ~127u;
+    const uint32_t x_addr = ring + NTT_STAGES * NTT_STAGE_BYTES;
+    float* x_sm = reinterpret_cast<float*>(ntt_smem + (x_addr - raw));
+    const uint32_t bar_full = x_addr + NTT_KMAX * NT_PITCH * 4;
+    const uint32_t bar_empty = bar_full + 8 * NTT_STAGES;
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(ntt_smem + (bar_empty + 8 * NTT_STAGES - raw));
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const bool feeder = threadIdx.x == 0;
+    if (feeder) {
+        for (int s = 0; s < NTT_STAGES; ++s) {
+            mbar_init(bar_full + 8 * s, 1);
+            mbar_init(bar_empty + 8 * s, NT_WARPS);
+        }
+        *abort_flag = 0;
+        fence_barrier_init();
+        fence_proxy_async_smem();
+        tma_prefetch_desc(&tm_w);
+    }
+    __syncthreads();
+    griddep_launch_dependents();
+    griddep_wait();
+    const long long tasks = (long long)pp.slices * pp.groups;
+    const int t_begin = (int)(tasks * blockIdx.x / gridDim.x), t_end = (int)(tasks * (blockIdx.x + 1) / gridDim.x);
+    if (t_begin >= t_end) return;
+    // the feeder's view: tiles of this CTA in consumption order, `fed` of `tiles` issued so far
+    NtTileCursor cur;
+    int tiles = 0, fed = 0;
+    if (feeder) {
+        for (int t = t_begin; t < t_end; ++t) {
+            cur.open(pp, t);
+            tiles += cur.steps;
+        }
+        cur.open(pp, t_begin);
+        for (; fed < NTT_STAGES && fed < tiles; ++fed) {          // k past K and rows past N arrive as zeros
+            mbar_arrive_expect_tx(bar_full + 8 * fed, NTT_STAGE_BYTES);
+            tma_load_4d(ring + fed * NTT_STAGE_BYTES, &tm_w, bar_full + 8 * fed, cur.k_begin + cur.s * NT_STEP, cur.grp * NTT_GROUP, 0, 0);
+            cur.next(pp, t_end);
+        }
+    }
+    const float* x_lane = x_sm + lane * NT_PITCH;
+    const uint32_t w_off = (uint32_t)(warp * NT_ROWS) * (NT_STEP * 4) + (uint32_t)lane * 4;
+    int cur_slice = -1, i = 0;
+    // A warp whose wait ran out keeps walking the task list for the two barriers around every restaging of X (the
+    // other warps count on all 256 threads there) and does nothing else.
+    bool ok = true;
+    for (int t = t_begin; t < t_end; ++t) {
+        const int slice = t / pp.groups, grp = t - slice * pp.groups;
+        const int k_begin = slice * p.k_per_slice;
+        const int k_len = min(p.k_per_slice, p.K - k_begin);
+        const int steps = (k_len + NT_STEP - 1) / NT_STEP;
+        if (slice != cur_slice) {
+            cur_slice = slice;
+            __syncthreads();
+            if (ok) nt_stage_x(x_sm, p, k_begin, k_len, steps * NT_STEP, threadIdx.x);
+            __syncthreads();
+        }
+        if (!ok) continue;
+        unsigned long long acc[NT_ROWS][MP];
+#pragma unroll
+        for (int r = 0; r < NT_ROWS; ++r)
+#pragma unroll
+            for (int q = 0; q < MP; ++q) acc[r][q] = 0ull;
+        for (int s = 0; s < steps; ++s, ++i) {
+            const int st = i % NTT_STAGES;
+            bool mine = wait_bounded(bar_full + 8 * st, (i / NTT_STAGES) & 1, abort_flag, status, WAIT_THIN_FULL);
+            const uint32_t wt = ring + st * NTT_STAGE_BYTES + w_off;
+            float w[NT_ROWS][4];                                         // the warp's share of the tile, then release it
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+#pragma unroll
+                for (int r = 0; r < NT_ROWS; ++r) w[r][j] = ld_shared_f32(wt + r * (NT_STEP * 4) + j * 128);
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_empty + 8 * st);
+            if (feeder && i >= 1 && fed < tiles) {                       // refill the stage of the previous step
+                const int sp = (i - 1) % NTT_STAGES;
+                mine = mine && wait_bounded(bar_empty + 8 * sp, ((i - 1) / NTT_STAGES) & 1, abort_flag, status, WAIT_THIN_EMPTY);
+                if (mine) {
+                    mbar_arrive_expect_tx(bar_full + 8 * sp, NTT_STAGE_BYTES);
+                    tma_load_4d(ring + sp * NTT_STAGE_BYTES, &tm_w, bar_full + 8 * sp, cur.k_begin + cur.s * NT_STEP, cur.grp * NTT_GROUP, 0, 0);
+                    cur.next(pp, t_end);
+                    ++fed;
+                }
+            }
+            ok = __all_sync(0xffffffffu, mine);
+            if (!ok) break;
+            nt_fma_step<MP>(acc, w, x_lane + s * NT_STEP * NT_PITCH);
+        }
+        if (!ok) continue;
+        nt_reduce_store<MP>(acc, lane, grp * NTT_GROUP + warp * NT_ROWS, slice, p);
+    }
+    if (feeder && *abort_flag) {      // copies already issued still write shared memory: let them land
+        const uint64_t t0 = global_timer_ns();
+        while (global_timer_ns() - t0 < 200000ull) {
+        }
+    }
+}
+
 }  // namespace
+
+// The Linear layout (W as [N, K]): a grid of row blocks x K slices of one CTA per SM.
+// MP: row pairs of X the kernels accumulate (4 for M <= 8, 8 for M <= 16).
+template <int MP>
+static int launch_thin_nt_mp(te_b200_ctx* ctx, const GemmProblem& g, cudaStream_t stream) {
+    if (g.N > INT32_MAX || g.K > INT32_MAX || !g.split_ws) return -1;
+    // W staged by TMA (one CTA per SM over the list of K slices x 64-row groups) when that list fills most of the GPU
+    {
+        long long sl = (g.K + NTT_KMAX - 1) / NTT_KMAX;
+        if (sl < 2) sl = 2;
+        const long long k_per = ((g.K + sl - 1) / sl + NT_STEP - 1) / NT_STEP * NT_STEP;
+        sl = (g.K + k_per - 1) / k_per;
+        const long long groups = (g.N + NTT_GROUP - 1) / NTT_GROUP;
+        const long long tasks = sl * groups;
+        CUtensorMap mw;
+        const int64_t strides[3] = {0, 0, g.b.ld};
+        if (sl >= 2 && sl <= 64 && tasks * 10 >= (long long)ctx->sm_count * 8 && tasks <= INT32_MAX &&
+            (size_t)sl * (size_t)g.M * (size_t)g.N * sizeof(float) <= g.split_ws_bytes &&
+            make_bhtc_map(ctx, &mw, g.b.ptr, g.K, g.N, 1, 1, strides, NT_STEP, NTT_GROUP, CU_TENSOR_MAP_SWIZZLE_NONE)) {
+            int& attr = ctx->kernel_state[reinterpret_cast<const void*>(thin_nt_tma_kernel<MP>)];
+            if (attr < NTT_SMEM_BYTES) {
+                cudaError_t ea = cudaFuncSetAttribute(thin_nt_tma_kernel<MP>, cudaFuncAttributeMaxDynamicSharedMemorySize, NTT_SMEM_BYTES);
+                if (ea != cudaSuccess) return cuda_fail(ea, "cudaFuncSetAttribute(thin_nt_tma_kernel)");
+                attr = NTT_SMEM_BYTES;
+            }
+            ThinNtTmaParams pp;
+            pp.q.x = g.a.ptr; pp.q.ldx = g.a.ld;
+            pp.q.w = g.b.ptr; pp.q.ldw = g.b.ld;
+            pp.q.partial = g.split_ws;
+            pp.q.M = (int)g.M; pp.q.N = (int)g.N; pp.q.K = (int)g.K;
+            pp.q.k_per_slice = (int)k_per;
+            pp.q.rows_per_cta = 0;
+            pp.slices = (int)sl; pp.groups = (int)groups;
+            const unsigned grid = (unsigned)(tasks < ctx->sm_count ? tasks : ctx->sm_count);
+            cudaError_t e = launch_pdl(thin_nt_tma_kernel<MP>, dim3(grid), dim3(NTT_THREADS), (size_t)NTT_SMEM_BYTES, stream, mw, pp, ctx->d_status);
+            if (e != cudaSuccess) return cuda_fail(e, "thin_nt_tma_kernel launch");
+            ctx->launches += 1;
+            return finish_split(ctx, g, (int)sl, stream);
+        }
+    }
+    // slices of at most NT_KMAX k, at least two (the reduction applies the epilogue); row blocks fill the SMs
+    long long slices = (g.K + NT_KMAX - 1) / NT_KMAX;
+    if (slices < 2) slices = 2;
+    long long k_per = ((g.K + slices - 1) / slices + NT_STEP - 1) / NT_STEP * NT_STEP;
+    slices = (g.K + k_per - 1) / k_per;
+    if (slices < 2 || slices > 64) return -1;
+    long long row_blocks = ctx->sm_count / slices;
+    if (row_blocks < 1) row_blocks = 1;
+    const long long task_rows = NT_WARPS * NT_ROWS;
+    long long rows_per = ((g.N + row_blocks - 1) / row_blocks + task_rows - 1) / task_rows * task_rows;
+    row_blocks = (g.N + rows_per - 1) / rows_per;
+    if ((size_t)slices * (size_t)g.M * (size_t)g.N * sizeof(float) > g.split_ws_bytes) return -1;
+    const int smem = (int)(k_per * NT_PITCH * sizeof(float));
+    int& attr = ctx->kernel_state[reinterpret_cast<const void*>(thin_nt_fp32_kernel<MP>)];
+    if (attr < smem) {
+        cudaError_t ea = cudaFuncSetAttribute(thin_nt_fp32_kernel<MP>, cudaFuncAttributeMaxDynamicSharedMemorySize, NT_KMAX * NT_PITCH * (int)sizeof(float));
+        if (ea != cudaSuccess) return cuda_fail(ea, "cudaFuncSetAttribute(thin_nt_fp32_kernel)");
+        attr = NT_KMAX * NT_PITCH * (int)sizeof(float);
+    }
+    ThinNtParams p;
+    p.x = g.a.ptr; p.ldx = g.a.ld;
+    p.w = g.b.ptr; p.ldw = g.b.ld;
+    p.partial = g.split_ws;
+    p.M = (int)g.M; p.N = (int)g.N; p.K = (int)g.K;
+    p.k_per_slice = (int)k_per;
+    p.rows_per_cta = (int)rows_per;
+    cudaError_t e = launch_pdl(thin_nt_fp32_kernel<MP>, dim3((unsigned)row_blocks, (unsigned)slices), dim3(NT_THREADS), (size_t)smem, stream, p);
+    if (e != cudaSuccess) return cuda_fail(e, "thin_nt_fp32_kernel launch");
+    ctx->launches += 1;
+    return finish_split(ctx, g, (int)slices, stream);
+}
+
+static int launch_thin_nt(te_b200_ctx* ctx, const GemmProblem& g, cudaStream_t stream) {
+    return g.M <= 8 ? launch_thin_nt_mp<4>(ctx, g, stream) : launch_thin_nt_mp<8>(ctx, g, stream);
+}
 
 // Returns TE_OK when the product was issued here, -1 when it is outside this form's limits (the caller then takes the
 // tensor-core path), or an error status.
 int launch_thin_fp32(te_b200_ctx* ctx, const GemmProblem& g, cudaStream_t stream) {
     if (g.batch_inner * g.batch_outer != 1 || g.M < 1 || g.M > THIN_M || g.K < 256 || g.N < 512) return -1;
-    if (g.a.mn_major || !g.b.mn_major || g.preact) return -1;
+    if (g.a.mn_major || g.preact) return -1;
+    if (!g.b.mn_major) return launch_thin_nt(ctx, g, stream);
     if ((g.N & 3) || (g.b.ld & 3) || (reinterpret_cast<uintptr_t>(g.b.ptr) & 15) || (reinterpret_cast<uintptr_t>(g.split_ws) & 15)) return -1;
     if (g.N > INT32_MAX || g.K > INT32_MAX) return -1;
     // B staged by TMA (one CTA per SM) when its grid of 1024-column blocks x K slices fills most of the GPU
