@@ -531,6 +531,124 @@ __global__ void __launch_bounds__(NTT_THREADS, 1) thin_nt_tma_kernel(const __gri
     }
 }
 
+
+// For large W the ring is what limits the rate (three 32 KB tiles in flight per SM against the latency of a loaded
+// HBM), and the 80 KB slice of X is what limits the ring.  This form takes X out of the way: a small kernel first
+// writes X transposed, [k][20] (16 rows + 4 floats of padding, the shared-memory pitch), and the tile of X for a
+// step then arrives by TMA together with the tile of W (10 KB beside 32 KB).  Five stages, no CTA-wide staging, and
+// the K slices can be as long as the balance over the SMs allows, so fewer reductions over the lanes.  Costs one
+// more launch; used when W is large.
+constexpr int NTX_STAGES = 5;
+constexpr int NTX_W_BYTES = NTT_GROUP * NT_STEP * 4;          // 32 KB
+constexpr int NTX_X_BYTES = NT_STEP * NT_PITCH * 4;           // 10 KB
+constexpr int NTX_STAGE_BYTES = NTX_W_BYTES + NTX_X_BYTES;
+constexpr int NTX_SMEM_BYTES = 128 + NTX_STAGES * NTX_STAGE_BYTES + 16 * NTX_STAGES + 16;
+
+__global__ void __launch_bounds__(256) thin_nt_transpose_x_kernel(const float* __restrict__ x, long long ldx, int M, int K, float* __restrict__ xt) {
+    griddep_launch_dependents();
+    griddep_wait();
+    const int k = blockIdx.x * 256 + threadIdx.x;
+    if (k >= K) return;
+    float v[THIN_M];
+#pragma unroll
+    for (int m = 0; m < THIN_M; ++m) v[m] = m < M ? __ldg(x + (long long)m * ldx + k) : 0.0f;
+    float4* dst = reinterpret_cast<float4*>(xt + (long long)k * NT_PITCH);
+#pragma unroll
+    for (int q = 0; q < THIN_M / 4; ++q) dst[q] = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+    dst[THIN_M / 4] = make_float4(0.f, 0.f, 0.f, 0.f);
+}
+
+template <int MP>
+__global__ void __launch_bounds__(NTT_THREADS, 1) thin_nt_tma_xt_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x,
+                                                                          const ThinNtTmaParams pp, int* status) {
+    extern __shared__ uint8_t ntx_smem[];
+    const ThinNtParams& p = pp.q;
+    const uint32_t raw = smem_u32(ntx_smem);
+    const uint32_t ring = (raw + 127u) & ~127u;
+    const uint32_t bar_full = ring + NTX_STAGES * NTX_STAGE_BYTES;
+    const uint32_t bar_empty = bar_full + 8 * NTX_STAGES;
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(ntx_smem + (bar_empty + 8 * NTX_STAGES - raw));
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const bool feeder = threadIdx.x == 0;
+    if (feeder) {
+        for (int s = 0; s < NTX_STAGES; ++s) {
+            mbar_init(bar_full + 8 * s, 1);
+            mbar_init(bar_empty + 8 * s, NT_WARPS);
+        }
+        *abort_flag = 0;
+        fence_barrier_init();
+        fence_proxy_async_smem();
+        tma_prefetch_desc(&tm_w);
+        tma_prefetch_desc(&tm_x);
+    }
+    __syncthreads();
+    griddep_launch_dependents();
+    griddep_wait();
+    const long long tasks = (long long)pp.slices * pp.groups;
+    const int t_begin = (int)(tasks * blockIdx.x / gridDim.x), t_end = (int)(tasks * (blockIdx.x + 1) / gridDim.x);
+    if (t_begin >= t_end) return;
+    NtTileCursor cur = {};
+    int tiles = 0, fed = 0;
+    // one tile of W (k past K and rows past N arrive as zeros) and the same k of the transposed X into a stage
+    auto feed_stage = [&](int st) {
+        const uint32_t dst = ring + st * NTX_STAGE_BYTES, bar = bar_full + 8 * st;
+        const int k = cur.k_begin + cur.s * NT_STEP;
+        mbar_arrive_expect_tx(bar, NTX_STAGE_BYTES);
+        tma_load_4d(dst, &tm_w, bar, k, cur.grp * NTT_GROUP, 0, 0);
+        tma_load_4d(dst + NTX_W_BYTES, &tm_x, bar, 0, k, 0, 0);
+        cur.next(pp, t_end);
+        ++fed;
+    };
+    if (feeder) {
+        for (int t = t_begin; t < t_end; ++t) {
+            cur.open(pp, t);
+            tiles += cur.steps;
+        }
+        cur.open(pp, t_begin);
+        while (fed < NTX_STAGES && fed < tiles) feed_stage(fed);
+    }
+    const uint32_t w_off = (uint32_t)(warp * NT_ROWS) * (NT_STEP * 4) + (uint32_t)lane * 4;
+    const uint8_t* x_lane0 = ntx_smem + (ring - raw) + NTX_W_BYTES + lane * (NT_PITCH * 4);
+    int i = 0;
+    bool ok = true;
+    for (int t = t_begin; t < t_end && ok; ++t) {
+        const int slice = t / pp.groups, grp = t - slice * pp.groups;
+        const int k_begin = slice * p.k_per_slice;
+        const int steps = (min(p.k_per_slice, p.K - k_begin) + NT_STEP - 1) / NT_STEP;
+        unsigned long long acc[NT_ROWS][MP];
+#pragma unroll
+        for (int r = 0; r < NT_ROWS; ++r)
+#pragma unroll
+            for (int q = 0; q < MP; ++q) acc[r][q] = 0ull;
+        for (int s = 0; s < steps; ++s, ++i) {
+            const int st = i % NTX_STAGES;
+            const bool mine = wait_bounded(bar_full + 8 * st, (i / NTX_STAGES) & 1, abort_flag, status, WAIT_THIN_FULL);
+            ok = __all_sync(0xffffffffu, mine);
+            if (!ok) break;
+            const uint32_t wt = ring + st * NTX_STAGE_BYTES + w_off;
+            float w[NT_ROWS][4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+#pragma unroll
+                for (int r = 0; r < NT_ROWS; ++r) w[r][j] = ld_shared_f32(wt + r * (NT_STEP * 4) + j * 128);
+            if (feeder && i >= 1 && fed < tiles) {                       // refill the stage of the previous step
+                const int sp = (i - 1) % NTX_STAGES;
+                if (wait_bounded(bar_empty + 8 * sp, ((i - 1) / NTX_STAGES) & 1, abort_flag, status, WAIT_THIN_EMPTY)) feed_stage(sp);
+            }
+            nt_fma_step<MP>(acc, w, reinterpret_cast<const float*>(x_lane0 + st * NTX_STAGE_BYTES));
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_empty + 8 * st);              // W and X of the stage have been read
+        }
+        if (!ok) break;
+        nt_reduce_store<MP>(acc, lane, grp * NTT_GROUP + warp * NT_ROWS, slice, p);
+    }
+    if (feeder && *abort_flag) {      // copies already issued still write shared memory: let them land
+        const uint64_t t0 = global_timer_ns();
+        while (global_timer_ns() - t0 < 200000ull) {
+        }
+    }
+}
+
 }  // namespace
 
 // The Linear layout (W as [N, K]): a grid of row blocks x K slices of one CTA per SM.
@@ -538,6 +656,52 @@ __global__ void __launch_bounds__(NTT_THREADS, 1) thin_nt_tma_kernel(const __gri
 template <int MP>
 static int launch_thin_nt_mp(te_b200_ctx* ctx, const GemmProblem& g, cudaStream_t stream) {
     if (g.N > INT32_MAX || g.K > INT32_MAX || !g.split_ws) return -1;
+    // large W with 16-byte rows: X transposed by a small kernel, tiles of W and X by TMA (see thin_nt_tma_xt_kernel)
+    if ((double)g.N * (double)g.K >= 8.0e6 && g.K >= 1024) {
+        const long long groups = (g.N + NTT_GROUP - 1) / NTT_GROUP;
+        // K slices: the fewest waves of (steps + the reduction's ~2 steps) over the SMs
+        long long best_sl = 0, best_cost = 0, best_k_per = 0;
+        for (long long sl = 2; sl <= 16; ++sl) {
+            const long long k_per = ((g.K + sl - 1) / sl + NT_STEP - 1) / NT_STEP * NT_STEP;
+            if ((g.K + k_per - 1) / k_per != sl) continue;
+            const long long waves = (groups * sl + ctx->sm_count - 1) / ctx->sm_count;
+            const long long cost = waves * (k_per / NT_STEP + 2);
+            if (!best_sl || cost < best_cost) { best_sl = sl; best_cost = cost; best_k_per = k_per; }
+        }
+        const size_t partial_bytes = ((size_t)best_sl * (size_t)g.M * (size_t)g.N * sizeof(float) + 255) & ~size_t(255);
+        const size_t xt_bytes = (size_t)g.K * NT_PITCH * sizeof(float);
+        CUtensorMap mw, mx;
+        const int64_t w_strides[3] = {0, 0, g.b.ld}, x_strides[3] = {0, 0, NT_PITCH};
+        float* xt = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(g.split_ws) + partial_bytes);
+        if (best_sl && groups * best_sl <= INT32_MAX && partial_bytes + xt_bytes <= g.split_ws_bytes &&
+            !(reinterpret_cast<uintptr_t>(g.split_ws) & 15) &&
+            make_bhtc_map(ctx, &mw, g.b.ptr, g.K, g.N, 1, 1, w_strides, NT_STEP, NTT_GROUP, CU_TENSOR_MAP_SWIZZLE_NONE) &&
+            make_bhtc_map(ctx, &mx, xt, NT_PITCH, g.K, 1, 1, x_strides, NT_PITCH, NT_STEP, CU_TENSOR_MAP_SWIZZLE_NONE)) {
+            int& attr = ctx->kernel_state[reinterpret_cast<const void*>(thin_nt_tma_xt_kernel<MP>)];
+            if (attr < NTX_SMEM_BYTES) {
+                cudaError_t ea = cudaFuncSetAttribute(thin_nt_tma_xt_kernel<MP>, cudaFuncAttributeMaxDynamicSharedMemorySize, NTX_SMEM_BYTES);
+                if (ea != cudaSuccess) return cuda_fail(ea, "cudaFuncSetAttribute(thin_nt_tma_xt_kernel)");
+                attr = NTX_SMEM_BYTES;
+            }
+            cudaError_t e = launch_pdl(thin_nt_transpose_x_kernel, dim3((unsigned)((g.K + 255) / 256)), dim3(256), (size_t)0, stream,
+                                       g.a.ptr, (long long)g.a.ld, (int)g.M, (int)g.K, xt);
+            if (e != cudaSuccess) return cuda_fail(e, "thin_nt_transpose_x_kernel launch");
+            ThinNtTmaParams pp;
+            pp.q.x = g.a.ptr; pp.q.ldx = g.a.ld;
+            pp.q.w = g.b.ptr; pp.q.ldw = g.b.ld;
+            pp.q.partial = g.split_ws;
+            pp.q.M = (int)g.M; pp.q.N = (int)g.N; pp.q.K = (int)g.K;
+            pp.q.k_per_slice = (int)best_k_per;
+            pp.q.rows_per_cta = 0;
+            pp.slices = (int)best_sl; pp.groups = (int)groups;
+            const long long tasks = groups * best_sl;
+            const unsigned grid = (unsigned)(tasks < ctx->sm_count ? tasks : ctx->sm_count);
+            e = launch_pdl(thin_nt_tma_xt_kernel<MP>, dim3(grid), dim3(NTT_THREADS), (size_t)NTX_SMEM_BYTES, stream, mw, mx, pp, ctx->d_status);
+            if (e != cudaSuccess) return cuda_fail(e, "thin_nt_tma_xt_kernel launch");
+            ctx->launches += 2;
+            return finish_split(ctx, g, (int)best_sl, stream);
+        }
+    }
     // W staged by TMA (one CTA per SM over the list of K slices x 64-row groups) when that list fills most of the GPU
     {
         long long sl = (g.K + NTT_KMAX - 1) / NTT_KMAX;
