@@ -374,7 +374,8 @@ def test_thin_rows_fp32_accurate_mode(backend, M, K, N):
 
 
 @pytest.mark.parametrize("M,K,N,pad", [(16, 4096, 4096, 0), (8, 2048, 8192, 0), (3, 1000, 1536, 0), (13, 1031, 777, 0),
-                                       (16, 1024, 1024, 3), (1, 8192, 512, 0), (11, 4100, 3000, 0), (16, 8192, 1100, 3)])
+                                       (16, 1024, 1024, 3), (1, 8192, 512, 0), (11, 4100, 3000, 0), (16, 8192, 1100, 3), (4, 1024, 9600, 0),
+                                       (16, 16384, 512, 0)])
 def test_thin_rows_linear_layout_fp32_accurate_mode(backend, M, K, N, pad):
     """The same mode for Linear's layout, X[M,K] . W[N,K]^T with at most 16 rows of X: two launches (lanes along k
     with a fixed reduction tree over the lanes, then the K-slice reduction with the epilogue), three for a large W

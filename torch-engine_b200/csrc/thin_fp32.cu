@@ -341,6 +341,19 @@ __device__ __forceinline__ void nt_reduce_store(const unsigned long long (&acc)[
     }
 }
 
+// The same stores with zeros: the second partial slot of a task that one CTA computed alone.
+template <int MP>
+__device__ __forceinline__ void nt_store_zeros(int lane, int n_first, int slot, const ThinNtParams& p) {
+    constexpr int PER = NT_ROWS * 2 * MP / 32;
+    const int n = n_first + (lane * PER) / (2 * MP), m0 = (lane * PER) % (2 * MP);
+    if (n < p.N) {
+        float* out = p.partial + ((long long)slot * p.M + m0) * p.N + n;
+#pragma unroll
+        for (int j = 0; j < PER; ++j)
+            if (m0 + j < p.M) out[(long long)j * p.N] = 0.0f;
+    }
+}
+
 // The CTA's K slice of X, [m][k] in global memory, laid out as [k][m] in shared memory; rows past M and k past the
 // slice are zero.  A thread owns every 256th k and has its sixteen loads of a k in flight together.
 __device__ __forceinline__ void nt_stage_x(float* x_sm, const ThinNtParams& p, int k_begin, int k_len, int k_pad, int t) {
@@ -558,9 +571,46 @@ __global__ void __launch_bounds__(256) thin_nt_transpose_x_kernel(const float* _
     dst[THIN_M / 4] = make_float4(0.f, 0.f, 0.f, 0.f);
 }
 
+// The tile list of the product: K slices outermost, then 64-row groups of W, then the steps of a slice (the last
+// slice may be shorter).  A CTA takes a contiguous range of it, cut at tile granularity so that every SM gets the same
+// number of steps; a task cut by a range boundary is finished by the next CTA, and its two parts go to two partial
+// slots (slot 2.slice for the CTA that began the task, 2.slice + 1 for the one that continued it -- zeros when one CTA
+// did it all), which the common reduction adds in slot order.  The launcher keeps a task no longer than a range, so
+// no task has three parts.
+struct NtxParams {
+    ThinNtParams q;                  // k_per_slice = 128 * steps_full; rows_per_cta unused
+    int groups, slices, steps_full, steps_last;
+    long long tiles_full;            // groups * steps_full * (slices - 1)
+    long long tiles;
+};
+
+struct NtxCursor {
+    int slice, grp, s, steps;
+    __device__ __forceinline__ void open(const NtxParams& pp, long long g) {
+        if (g < pp.tiles_full) {
+            const long long per = (long long)pp.groups * pp.steps_full;
+            slice = (int)(g / per);
+            const int r = (int)(g - slice * per);
+            grp = r / pp.steps_full; s = r - grp * pp.steps_full; steps = pp.steps_full;
+        } else {
+            const int r = (int)(g - pp.tiles_full);
+            slice = pp.slices - 1;
+            grp = r / pp.steps_last; s = r - grp * pp.steps_last; steps = pp.steps_last;
+        }
+    }
+    __device__ __forceinline__ void next(const NtxParams& pp) {
+        if (++s < steps) return;
+        s = 0;
+        if (++grp < pp.groups) return;
+        grp = 0;
+        ++slice;
+        steps = slice == pp.slices - 1 ? pp.steps_last : pp.steps_full;
+    }
+};
+
 template <int MP>
 __global__ void __launch_bounds__(NTT_THREADS, 1) thin_nt_tma_xt_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x,
-                                                                          const ThinNtTmaParams pp, int* status) {
+                                                                          const NtxParams pp, int* status) {
     extern __shared__ uint8_t ntx_smem[];
     const ThinNtParams& p = pp.q;
     const uint32_t raw = smem_u32(ntx_smem);
@@ -584,63 +634,63 @@ __global__ void __launch_bounds__(NTT_THREADS, 1) thin_nt_tma_xt_kernel(const __
     __syncthreads();
     griddep_launch_dependents();
     griddep_wait();
-    const long long tasks = (long long)pp.slices * pp.groups;
-    const int t_begin = (int)(tasks * blockIdx.x / gridDim.x), t_end = (int)(tasks * (blockIdx.x + 1) / gridDim.x);
-    if (t_begin >= t_end) return;
-    NtTileCursor cur = {};
-    int tiles = 0, fed = 0;
+    const long long g_begin = pp.tiles * blockIdx.x / gridDim.x, g_end = pp.tiles * (blockIdx.x + 1) / gridDim.x;
+    const int tiles = (int)(g_end - g_begin);
+    if (tiles <= 0) return;
+    NtxCursor feed = {}, cc;
+    int fed = 0;
     // one tile of W (k past K and rows past N arrive as zeros) and the same k of the transposed X into a stage
     auto feed_stage = [&](int st) {
         const uint32_t dst = ring + st * NTX_STAGE_BYTES, bar = bar_full + 8 * st;
-        const int k = cur.k_begin + cur.s * NT_STEP;
+        const int k = feed.slice * p.k_per_slice + feed.s * NT_STEP;
         mbar_arrive_expect_tx(bar, NTX_STAGE_BYTES);
-        tma_load_4d(dst, &tm_w, bar, k, cur.grp * NTT_GROUP, 0, 0);
+        tma_load_4d(dst, &tm_w, bar, k, feed.grp * NTT_GROUP, 0, 0);
         tma_load_4d(dst + NTX_W_BYTES, &tm_x, bar, 0, k, 0, 0);
-        cur.next(pp, t_end);
+        feed.next(pp);
         ++fed;
     };
     if (feeder) {
-        for (int t = t_begin; t < t_end; ++t) {
-            cur.open(pp, t);
-            tiles += cur.steps;
-        }
-        cur.open(pp, t_begin);
+        feed.open(pp, g_begin);
         while (fed < NTX_STAGES && fed < tiles) feed_stage(fed);
     }
     const uint32_t w_off = (uint32_t)(warp * NT_ROWS) * (NT_STEP * 4) + (uint32_t)lane * 4;
     const uint8_t* x_lane0 = ntx_smem + (ring - raw) + NTX_W_BYTES + lane * (NT_PITCH * 4);
-    int i = 0;
-    bool ok = true;
-    for (int t = t_begin; t < t_end && ok; ++t) {
-        const int slice = t / pp.groups, grp = t - slice * pp.groups;
-        const int k_begin = slice * p.k_per_slice;
-        const int steps = (min(p.k_per_slice, p.K - k_begin) + NT_STEP - 1) / NT_STEP;
-        unsigned long long acc[NT_ROWS][MP];
+    cc.open(pp, g_begin);
+    bool began_here = cc.s == 0;             // the task under way was begun by this CTA
+    unsigned long long acc[NT_ROWS][MP];
 #pragma unroll
-        for (int r = 0; r < NT_ROWS; ++r)
+    for (int r = 0; r < NT_ROWS; ++r)
 #pragma unroll
-            for (int q = 0; q < MP; ++q) acc[r][q] = 0ull;
-        for (int s = 0; s < steps; ++s, ++i) {
-            const int st = i % NTX_STAGES;
-            const bool mine = wait_bounded(bar_full + 8 * st, (i / NTX_STAGES) & 1, abort_flag, status, WAIT_THIN_FULL);
-            ok = __all_sync(0xffffffffu, mine);
-            if (!ok) break;
-            const uint32_t wt = ring + st * NTX_STAGE_BYTES + w_off;
-            float w[NT_ROWS][4];
+        for (int q = 0; q < MP; ++q) acc[r][q] = 0ull;
+    for (int i = 0; i < tiles; ++i) {
+        const int st = i % NTX_STAGES;
+        const bool mine = wait_bounded(bar_full + 8 * st, (i / NTX_STAGES) & 1, abort_flag, status, WAIT_THIN_FULL);
+        if (!__all_sync(0xffffffffu, mine)) break;
+        const uint32_t wt = ring + st * NTX_STAGE_BYTES + w_off;
+        float w[NT_ROWS][4];
 #pragma unroll
-            for (int j = 0; j < 4; ++j)
+        for (int j = 0; j < 4; ++j)
 #pragma unroll
-                for (int r = 0; r < NT_ROWS; ++r) w[r][j] = ld_shared_f32(wt + r * (NT_STEP * 4) + j * 128);
-            if (feeder && i >= 1 && fed < tiles) {                       // refill the stage of the previous step
-                const int sp = (i - 1) % NTX_STAGES;
-                if (wait_bounded(bar_empty + 8 * sp, ((i - 1) / NTX_STAGES) & 1, abort_flag, status, WAIT_THIN_EMPTY)) feed_stage(sp);
-            }
-            nt_fma_step<MP>(acc, w, reinterpret_cast<const float*>(x_lane0 + st * NTX_STAGE_BYTES));
-            __syncwarp();
-            if (lane == 0) mbar_arrive(bar_empty + 8 * st);              // W and X of the stage have been read
+            for (int r = 0; r < NT_ROWS; ++r) w[r][j] = ld_shared_f32(wt + r * (NT_STEP * 4) + j * 128);
+        if (feeder && i >= 1 && fed < tiles) {                       // refill the stage of the previous step
+            const int sp = (i - 1) % NTX_STAGES;
+            if (wait_bounded(bar_empty + 8 * sp, ((i - 1) / NTX_STAGES) & 1, abort_flag, status, WAIT_THIN_EMPTY)) feed_stage(sp);
         }
-        if (!ok) break;
-        nt_reduce_store<MP>(acc, lane, grp * NTT_GROUP + warp * NT_ROWS, slice, p);
+        nt_fma_step<MP>(acc, w, reinterpret_cast<const float*>(x_lane0 + st * NTX_STAGE_BYTES));
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_empty + 8 * st);              // W and X of the stage have been read
+        const bool task_ends = cc.s + 1 == cc.steps;
+        if (task_ends || i + 1 == tiles) {
+            const int n_first = cc.grp * NTT_GROUP + warp * NT_ROWS;
+            nt_reduce_store<MP>(acc, lane, n_first, 2 * cc.slice + (began_here ? 0 : 1), p);
+            if (task_ends && began_here) nt_store_zeros<MP>(lane, n_first, 2 * cc.slice + 1, p);
+            began_here = true;
+#pragma unroll
+            for (int r = 0; r < NT_ROWS; ++r)
+#pragma unroll
+                for (int q = 0; q < MP; ++q) acc[r][q] = 0ull;
+        }
+        cc.next(pp);
     }
     if (feeder && *abort_flag) {      // copies already issued still write shared memory: let them land
         const uint64_t t0 = global_timer_ns();
@@ -656,25 +706,25 @@ __global__ void __launch_bounds__(NTT_THREADS, 1) thin_nt_tma_xt_kernel(const __
 template <int MP>
 static int launch_thin_nt_mp(te_b200_ctx* ctx, const GemmProblem& g, cudaStream_t stream) {
     if (g.N > INT32_MAX || g.K > INT32_MAX || !g.split_ws) return -1;
-    // large W with 16-byte rows: X transposed by a small kernel, tiles of W and X by TMA (see thin_nt_tma_xt_kernel)
+    // large W with 16-byte rows: X transposed by a small kernel, tiles of W and X by TMA, ranges of the tile list cut
+    // at tile granularity (see thin_nt_tma_xt_kernel)
     if ((double)g.N * (double)g.K >= 8.0e6 && g.K >= 1024) {
         const long long groups = (g.N + NTT_GROUP - 1) / NTT_GROUP;
-        // K slices: the fewest waves of (steps + the reduction's ~2 steps) over the SMs
-        long long best_sl = 0, best_cost = 0, best_k_per = 0;
-        for (long long sl = 2; sl <= 16; ++sl) {
-            const long long k_per = ((g.K + sl - 1) / sl + NT_STEP - 1) / NT_STEP * NT_STEP;
-            if ((g.K + k_per - 1) / k_per != sl) continue;
-            const long long waves = (groups * sl + ctx->sm_count - 1) / ctx->sm_count;
-            const long long cost = waves * (k_per / NT_STEP + 2);
-            if (!best_sl || cost < best_cost) { best_sl = sl; best_cost = cost; best_k_per = k_per; }
+        const long long steps_total = (g.K + NT_STEP - 1) / NT_STEP;
+        const long long total = groups * steps_total;
+        const long long grid = total < ctx->sm_count ? total : ctx->sm_count;
+        // the fewest K slices whose tasks are no longer than a CTA's range (then a task has at most two parts)
+        long long sl = 0, steps_full = 0;
+        for (long long c = 1; c <= 16 && !sl; ++c) {
+            const long long sf = (steps_total + c - 1) / c;
+            if (sf <= total / grid && (steps_total + sf - 1) / sf == c) { sl = c; steps_full = sf; }
         }
-        const size_t partial_bytes = ((size_t)best_sl * (size_t)g.M * (size_t)g.N * sizeof(float) + 255) & ~size_t(255);
+        const size_t partial_bytes = ((size_t)(2 * sl) * (size_t)g.M * (size_t)g.N * sizeof(float) + 255) & ~size_t(255);
         const size_t xt_bytes = (size_t)g.K * NT_PITCH * sizeof(float);
         CUtensorMap mw, mx;
         const int64_t w_strides[3] = {0, 0, g.b.ld}, x_strides[3] = {0, 0, NT_PITCH};
         float* xt = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(g.split_ws) + partial_bytes);
-        if (best_sl && groups * best_sl <= INT32_MAX && partial_bytes + xt_bytes <= g.split_ws_bytes &&
-            !(reinterpret_cast<uintptr_t>(g.split_ws) & 15) &&
+        if (sl && total <= INT32_MAX && partial_bytes + xt_bytes <= g.split_ws_bytes && !(reinterpret_cast<uintptr_t>(g.split_ws) & 15) &&
             make_bhtc_map(ctx, &mw, g.b.ptr, g.K, g.N, 1, 1, w_strides, NT_STEP, NTT_GROUP, CU_TENSOR_MAP_SWIZZLE_NONE) &&
             make_bhtc_map(ctx, &mx, xt, NT_PITCH, g.K, 1, 1, x_strides, NT_PITCH, NT_STEP, CU_TENSOR_MAP_SWIZZLE_NONE)) {
             int& attr = ctx->kernel_state[reinterpret_cast<const void*>(thin_nt_tma_xt_kernel<MP>)];
@@ -686,20 +736,22 @@ static int launch_thin_nt_mp(te_b200_ctx* ctx, const GemmProblem& g, cudaStream_
             cudaError_t e = launch_pdl(thin_nt_transpose_x_kernel, dim3((unsigned)((g.K + 255) / 256)), dim3(256), (size_t)0, stream,
                                        g.a.ptr, (long long)g.a.ld, (int)g.M, (int)g.K, xt);
             if (e != cudaSuccess) return cuda_fail(e, "thin_nt_transpose_x_kernel launch");
-            ThinNtTmaParams pp;
+            NtxParams pp;
             pp.q.x = g.a.ptr; pp.q.ldx = g.a.ld;
             pp.q.w = g.b.ptr; pp.q.ldw = g.b.ld;
             pp.q.partial = g.split_ws;
             pp.q.M = (int)g.M; pp.q.N = (int)g.N; pp.q.K = (int)g.K;
-            pp.q.k_per_slice = (int)best_k_per;
+            pp.q.k_per_slice = (int)(steps_full * NT_STEP);
             pp.q.rows_per_cta = 0;
-            pp.slices = (int)best_sl; pp.groups = (int)groups;
-            const long long tasks = groups * best_sl;
-            const unsigned grid = (unsigned)(tasks < ctx->sm_count ? tasks : ctx->sm_count);
-            e = launch_pdl(thin_nt_tma_xt_kernel<MP>, dim3(grid), dim3(NTT_THREADS), (size_t)NTX_SMEM_BYTES, stream, mw, mx, pp, ctx->d_status);
+            pp.groups = (int)groups; pp.slices = (int)sl;
+            pp.steps_full = (int)steps_full;
+            pp.steps_last = (int)(steps_total - steps_full * (sl - 1));
+            pp.tiles_full = groups * steps_full * (sl - 1);
+            pp.tiles = total;
+            e = launch_pdl(thin_nt_tma_xt_kernel<MP>, dim3((unsigned)grid), dim3(NTT_THREADS), (size_t)NTX_SMEM_BYTES, stream, mw, mx, pp, ctx->d_status);
             if (e != cudaSuccess) return cuda_fail(e, "thin_nt_tma_xt_kernel launch");
             ctx->launches += 2;
-            return finish_split(ctx, g, (int)best_sl, stream);
+            return finish_split(ctx, g, (int)(2 * sl), stream);
         }
     }
     // W staged by TMA (one CTA per SM over the list of K slices x 64-row groups) when that list fills most of the GPU
