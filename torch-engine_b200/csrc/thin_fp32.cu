@@ -57,6 +57,8 @@ __device__ __forceinline__ void unpack(unsigned long long v, float& lo, float& h
     asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
 }
 
+// MR: rows of A a thread accumulates (8 for M <= 8, else 16); the staged A keeps 16-row pitch either way.
+template <int MR>
 __global__ void __launch_bounds__(THIN_THREADS) thin_fp32_kernel(const ThinParams p) {
     __shared__ __align__(16) float a_sm[THIN_KC][THIN_M];        // [k][m]: the M values of one k are one 64-byte row
     griddep_wait();
@@ -66,11 +68,11 @@ __global__ void __launch_bounds__(THIN_THREADS) thin_fp32_kernel(const ThinParam
     const int k_begin = blockIdx.y * p.k_per_slice;
     const int k_end = min(k_begin + p.k_per_slice, p.K);
     // accumulators as pairs of rows (m, m + 1): acc[c][q] holds rows 2q and 2q + 1 of column c0 + c
-    unsigned long long acc[4][THIN_M / 2];
+    unsigned long long acc[4][MR / 2];
 #pragma unroll
     for (int c = 0; c < 4; ++c)
 #pragma unroll
-        for (int q = 0; q < THIN_M / 2; ++q) acc[c][q] = 0ull;       // two +0.0f
+        for (int q = 0; q < MR / 2; ++q) acc[c][q] = 0ull;       // two +0.0f
     // staging map: 16 threads cover the rows of one k, a warp covers two k (conflict-free shared-memory writes)
     const int sm_m = t & 15, sm_k = t >> 4;
     // columns past N read the last four columns instead (their sums are not stored): the loads need no predicate
@@ -100,7 +102,7 @@ __global__ void __launch_bounds__(THIN_THREADS) thin_fp32_kernel(const ThinParam
                 const ulonglong2* row = reinterpret_cast<const ulonglong2*>(&a_sm[kk + u][0]);
                 const unsigned long long w0 = pair_of(v[u].x), w1 = pair_of(v[u].y), w2 = pair_of(v[u].z), w3 = pair_of(v[u].w);
 #pragma unroll
-                for (int q = 0; q < THIN_M / 4; ++q) {
+                for (int q = 0; q < MR / 4; ++q) {
                     const ulonglong2 a = row[q];             // rows 4q .. 4q + 3 of A at this k
                     fma2(acc[0][2 * q], a.x, w0); fma2(acc[0][2 * q + 1], a.y, w0);
                     fma2(acc[1][2 * q], a.x, w1); fma2(acc[1][2 * q + 1], a.y, w1);
@@ -113,7 +115,7 @@ __global__ void __launch_bounds__(THIN_THREADS) thin_fp32_kernel(const ThinParam
     if (!live) return;
     float* out = p.partial + (long long)blockIdx.y * p.M * p.N + c0;
 #pragma unroll
-    for (int q = 0; q < THIN_M / 2; ++q) {
+    for (int q = 0; q < MR / 2; ++q) {
         float lo[4], hi[4];
 #pragma unroll
         for (int c = 0; c < 4; ++c) unpack(acc[c][q], lo[c], hi[c]);
@@ -137,6 +139,7 @@ constexpr int TT_STAGE_BYTES = TT_KS * TT_COLS * 4;   // 32 KB
 constexpr int TT_STAGES = 6;
 constexpr int TT_SMEM_BYTES = TT_STAGES * TT_STAGE_BYTES + THIN_KC * THIN_M * 4 + 256 + 128;
 
+template <int MR>
 __global__ void __launch_bounds__(TT_THREADS, 1) thin_fp32_tma_kernel(const __grid_constant__ CUtensorMap tm_b, const ThinParams p, int* status) {
     extern __shared__ uint8_t tt_smem[];
     const uint32_t raw = smem_u32(tt_smem);
@@ -186,11 +189,11 @@ __global__ void __launch_bounds__(TT_THREADS, 1) thin_fp32_tma_kernel(const __gr
         // ------------------------------------------------------------ consumers: four columns x 16 rows each
         const int t = threadIdx.x;
         const int c0 = col0 + 4 * t;
-        unsigned long long acc[4][THIN_M / 2];
+        unsigned long long acc[4][MR / 2];
 #pragma unroll
         for (int c = 0; c < 4; ++c)
 #pragma unroll
-            for (int q = 0; q < THIN_M / 2; ++q) acc[c][q] = 0ull;
+            for (int q = 0; q < MR / 2; ++q) acc[c][q] = 0ull;
         const int sm_m = t & 15, sm_k = t >> 4;                           // 16 k rows of A per staging pass
         // this thread's 16 bytes of a slab row: box t / 64, 16-byte unit t % 64
         const uint32_t b_off = (uint32_t)(t >> 6) * (TT_KS * TT_BOX_COLS * 4) + (uint32_t)(t & 63) * 16;
@@ -227,7 +230,7 @@ __global__ void __launch_bounds__(TT_THREADS, 1) thin_fp32_tma_kernel(const __gr
                 const ulonglong2* row = reinterpret_cast<const ulonglong2*>(&a_sm[kk0 + u][0]);
                 const unsigned long long w0 = pair_of(v[u].x), w1 = pair_of(v[u].y), w2 = pair_of(v[u].z), w3 = pair_of(v[u].w);
 #pragma unroll
-                for (int q = 0; q < THIN_M / 4; ++q) {
+                for (int q = 0; q < MR / 4; ++q) {
                     const ulonglong2 a = row[q];
                     fma2(acc[0][2 * q], a.x, w0); fma2(acc[0][2 * q + 1], a.y, w0);
                     fma2(acc[1][2 * q], a.x, w1); fma2(acc[1][2 * q + 1], a.y, w1);
@@ -239,7 +242,7 @@ __global__ void __launch_bounds__(TT_THREADS, 1) thin_fp32_tma_kernel(const __gr
         if (ok && c0 < p.N) {
             float* out = p.partial + (long long)blockIdx.y * p.M * p.N + c0;
 #pragma unroll
-            for (int q = 0; q < THIN_M / 2; ++q) {
+            for (int q = 0; q < MR / 2; ++q) {
                 float lo[4], hi[4];
 #pragma unroll
                 for (int c = 0; c < 4; ++c) unpack(acc[c][q], lo[c], hi[c]);
@@ -824,12 +827,9 @@ static int launch_thin_nt(te_b200_ctx* ctx, const GemmProblem& g, cudaStream_t s
     return g.M <= 8 ? launch_thin_nt_mp<4>(ctx, g, stream) : launch_thin_nt_mp<8>(ctx, g, stream);
 }
 
-// Returns TE_OK when the product was issued here, -1 when it is outside this form's limits (the caller then takes the
-// tensor-core path), or an error status.
-int launch_thin_fp32(te_b200_ctx* ctx, const GemmProblem& g, cudaStream_t stream) {
-    if (g.batch_inner * g.batch_outer != 1 || g.M < 1 || g.M > THIN_M || g.K < 256 || g.N < 512) return -1;
-    if (g.a.mn_major || g.preact) return -1;
-    if (!g.b.mn_major) return launch_thin_nt(ctx, g, stream);
+// The row-major right operand (B as [K, N]).
+template <int MR>
+static int launch_thin_nn(te_b200_ctx* ctx, const GemmProblem& g, cudaStream_t stream) {
     if ((g.N & 3) || (g.b.ld & 3) || (reinterpret_cast<uintptr_t>(g.b.ptr) & 15) || (reinterpret_cast<uintptr_t>(g.split_ws) & 15)) return -1;
     if (g.N > INT32_MAX || g.K > INT32_MAX) return -1;
     // B staged by TMA (one CTA per SM) when its grid of 1024-column blocks x K slices fills most of the GPU
@@ -846,9 +846,9 @@ int launch_thin_fp32(te_b200_ctx* ctx, const GemmProblem& g, cudaStream_t stream
             const int64_t strides[3] = {0, 0, g.b.ld};
             if (sl >= 2 && g.split_ws && (size_t)sl * (size_t)g.M * (size_t)g.N * sizeof(float) <= g.split_ws_bytes &&
                 make_bhtc_map(ctx, &mb, g.b.ptr, g.N, g.K, 1, 1, strides, TT_BOX_COLS, TT_KS, CU_TENSOR_MAP_SWIZZLE_NONE)) {
-                int& attr = ctx->kernel_state[reinterpret_cast<const void*>(thin_fp32_tma_kernel)];
+                int& attr = ctx->kernel_state[reinterpret_cast<const void*>(thin_fp32_tma_kernel<MR>)];
                 if (attr < TT_SMEM_BYTES) {
-                    cudaError_t ea = cudaFuncSetAttribute(thin_fp32_tma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TT_SMEM_BYTES);
+                    cudaError_t ea = cudaFuncSetAttribute(thin_fp32_tma_kernel<MR>, cudaFuncAttributeMaxDynamicSharedMemorySize, TT_SMEM_BYTES);
                     if (ea != cudaSuccess) return cuda_fail(ea, "cudaFuncSetAttribute(thin_fp32_tma_kernel)");
                     attr = TT_SMEM_BYTES;
                 }
@@ -858,7 +858,7 @@ int launch_thin_fp32(te_b200_ctx* ctx, const GemmProblem& g, cudaStream_t stream
                 p.partial = g.split_ws;
                 p.M = (int)g.M; p.N = (int)g.N; p.K = (int)g.K;
                 p.k_per_slice = (int)k_per;
-                cudaError_t e = launch_pdl(thin_fp32_tma_kernel, dim3((unsigned)cb, (unsigned)sl), dim3(TT_THREADS), (size_t)TT_SMEM_BYTES, stream,
+                cudaError_t e = launch_pdl(thin_fp32_tma_kernel<MR>, dim3((unsigned)cb, (unsigned)sl), dim3(TT_THREADS), (size_t)TT_SMEM_BYTES, stream,
                                            mb, p, ctx->d_status);
                 if (e != cudaSuccess) return cuda_fail(e, "thin_fp32_tma_kernel launch");
                 ctx->launches += 1;
@@ -884,10 +884,19 @@ int launch_thin_fp32(te_b200_ctx* ctx, const GemmProblem& g, cudaStream_t stream
     p.partial = g.split_ws;
     p.M = (int)g.M; p.N = (int)g.N; p.K = (int)g.K;
     p.k_per_slice = (int)k_per;
-    cudaError_t e = launch_pdl(thin_fp32_kernel, dim3((unsigned)col_blocks, (unsigned)slices), dim3(THIN_THREADS), 0, stream, p);
+    cudaError_t e = launch_pdl(thin_fp32_kernel<MR>, dim3((unsigned)col_blocks, (unsigned)slices), dim3(THIN_THREADS), 0, stream, p);
     if (e != cudaSuccess) return cuda_fail(e, "thin_fp32_kernel launch");
     ctx->launches += 1;
     return finish_split(ctx, g, (int)slices, stream);
+}
+
+// Returns TE_OK when the product was issued here, -1 when it is outside this form's limits (the caller then takes the
+// tensor-core path), or an error status.
+int launch_thin_fp32(te_b200_ctx* ctx, const GemmProblem& g, cudaStream_t stream) {
+    if (g.batch_inner * g.batch_outer != 1 || g.M < 1 || g.M > THIN_M || g.K < 256 || g.N < 512) return -1;
+    if (g.a.mn_major || g.preact) return -1;
+    if (!g.b.mn_major) return launch_thin_nt(ctx, g, stream);
+    return g.M <= 8 ? launch_thin_nn<8>(ctx, g, stream) : launch_thin_nn<16>(ctx, g, stream);
 }
 
 }  // namespace te
