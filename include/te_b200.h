@@ -47,7 +47,7 @@ enum { TE_ROW_MAJOR = 0, TE_COL_MAJOR = 1 };
 /* TE_PREC_TF32: operands rounded to tf32 by the tensor core (max relative error ~1e-3).  TE_PREC_3XTF32: the
  * FP32-accurate mode (<= 1e-5, typically 2e-6): hi / lo tf32 split with three tensor-core products per term; a product
  * with at most 16 rows, which is bound by reading B once, is computed with FP32 FMAs instead (same accuracy class,
- * error ~4e-7). */
+ * error ~4e-7), for a row-major B and for Linear's weight layout alike. */
 enum { TE_PREC_TF32 = 0, TE_PREC_3XTF32 = 1 };
 enum { TE_EPI_NONE = 0, TE_EPI_BIAS = 1, TE_EPI_BIAS_GELU = 2 };
 enum { TE_SCALE_NONE = 0, TE_SCALE_MUL = 1, TE_SCALE_DIV = 2 };
