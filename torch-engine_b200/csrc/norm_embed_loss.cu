@@ -95,8 +95,8 @@ __global__ void __launch_bounds__(256) layernorm_forward_kernel(const float* __r
 // Backward: 8 B read + 4 B written per element.  Each warp walks its rows, writes dx and keeps the column sums of
 // dy * x_hat and dy for its rows in registers; the block adds its warps' sums through shared memory and writes one
 // partial row pair; layernorm_param_grad_kernel adds the partials of all blocks in block order.
-template <int N, bool VEC>
-__global__ void __launch_bounds__(256) layernorm_backward_kernel(const float* __restrict__ x, const float* __restrict__ gamma,
+template <int N, bool VEC, bool AHEAD>
+__global__ void __launch_bounds__(256, (N <= 2 || (N == 3 && !AHEAD)) ? 2 : 1) layernorm_backward_kernel(const float* __restrict__ x, const float* __restrict__ gamma,
                                                                  const float* __restrict__ dy, float* dx, const float* dx_residual,
                                                                  float* __restrict__ partial, long long rows, int cols, float eps,
                                                                  int want_dx_sum) {
@@ -110,10 +110,29 @@ __global__ void __launch_bounds__(256) layernorm_backward_kernel(const float* __
 #pragma unroll
     for (int k = 0; k < N * R::W; ++k) dg.v[k] = db.v[k] = ds.v[k] = 0.0f;
     const float inv_n = 1.0f / (float)cols;
-    for (long long r = (long long)blockIdx.x * (blockDim.x >> 5) + warp; r < rows; r += warps) {
-        R xr, gy;
-        xr.load(x + r * cols, cols, lane);
-        gy.load(dy + r * cols, cols, lane);
+    // the next row's loads are issued before the current row's arithmetic (four dependent warp reductions per row):
+    // a warp otherwise has nothing in flight while it computes
+    long long r = (long long)blockIdx.x * (blockDim.x >> 5) + warp;
+    // (AHEAD: rows of at most 256 floats, and of 257-384 floats at one block per SM when there is a residual to fetch;
+    // longer rows have no registers to spare for a second row)
+    R xn, gn;
+    if (AHEAD && r < rows) {
+        xn.load(x + r * cols, cols, lane);
+        gn.load(dy + r * cols, cols, lane);
+    }
+    for (; r < rows; r += warps) {
+        R xr, gy, res;
+        if constexpr (AHEAD) {
+            xr = xn; gy = gn;
+        } else {
+            xr.load(x + r * cols, cols, lane);
+            gy.load(dy + r * cols, cols, lane);
+        }
+        if (AHEAD && dx_residual) res.load(dx_residual + r * cols, cols, lane);     // needed last: in flight during the arithmetic
+        if (AHEAD && r + warps < rows) {
+            xn.load(x + (r + warps) * cols, cols, lane);
+            gn.load(dy + (r + warps) * cols, cols, lane);
+        }
         float s = 0.0f;
 #pragma unroll
         for (int k = 0; k < N * R::W; ++k) s += xr.v[k];
@@ -143,9 +162,9 @@ __global__ void __launch_bounds__(256) layernorm_backward_kernel(const float* __
 #pragma unroll
         for (int k = 0; k < N * R::W; ++k) xr.v[k] = (gy.v[k] - m1 - xr.v[k] * m2) * inv_std;
         if (dx_residual) {     // the gradient arriving over the branch that bypasses this LayerNorm (may be dx itself)
-            gy.load(dx_residual + r * cols, cols, lane);
+            if constexpr (!AHEAD) gy.load(dx_residual + r * cols, cols, lane);
 #pragma unroll
-            for (int k = 0; k < N * R::W; ++k) xr.v[k] += gy.v[k];
+            for (int k = 0; k < N * R::W; ++k) xr.v[k] += AHEAD ? res.v[k] : gy.v[k];
         }
         if (want_dx_sum) {
 #pragma unroll
@@ -436,7 +455,9 @@ int launch_layernorm_backward(te_b200_ctx* ctx, const float* x, const float* gam
     const int cols = (int)cols64;
     const bool vec = (cols & 3) == 0 && aligned16(x) && aligned16(dy) && aligned16(dx) && aligned16(gamma) &&
                      (!dx_residual || aligned16(dx_residual));
-    const int grid = row_grid(rows, ctx->sm_count, 2);
+    // rows of 257-384 floats with a residual keep two rows per warp in registers and run one block per SM
+    const bool mid = vec && cols > 256 && cols <= 384 && dx_residual;
+    const int grid = row_grid(rows, ctx->sm_count, mid ? 1 : 2);
     const size_t need = (size_t)grid * 3 * cols * sizeof(float);
     if (need > ctx->workspace_bytes) {
         set_error("context workspace too small for the LayerNorm parameter-gradient partials");
@@ -444,7 +465,11 @@ int launch_layernorm_backward(te_b200_ctx* ctx, const float* x, const float* gam
     }
     float* partial = static_cast<float*>(ctx->workspace);
     const size_t smem = (size_t)8 * cols * sizeof(float);
-#define CALL(N, V) launch_pdl(layernorm_backward_kernel<N, V>, dim3(grid), dim3(256), smem, st, x, gamma, dy, dx, dx_residual, partial, rows, cols, eps, dx_colsum ? 1 : 0)
+#define CALL(N, V)                                                                                                                        \
+    if (N <= 2 || (N == 3 && V && mid))                                                                                                   \
+        launch_pdl(layernorm_backward_kernel<N, V, (N <= 3)>, dim3(grid), dim3(256), smem, st, x, gamma, dy, dx, dx_residual, partial, rows, cols, eps, dx_colsum ? 1 : 0); \
+    else                                                                                                                                  \
+        launch_pdl(layernorm_backward_kernel<N, V, false>, dim3(grid), dim3(256), smem, st, x, gamma, dy, dx, dx_residual, partial, rows, cols, eps, dx_colsum ? 1 : 0);
     TE_LN_DISPATCH(CALL)
 #undef CALL
     cudaError_t e = cudaGetLastError();
