@@ -3,7 +3,8 @@ them on a [rows, cols] activation, meant to be run under `ncu -k regex:<kernel>`
 
     python torch-engine_b200/benchmarks/rowop_profile.py --op gelu_backward --rows 16384 --cols 3072
 
-Ops: gelu, gelu_backward, colsum, layernorm, layernorm_backward, softmax, softmax_backward.  The printed GB/s uses the
+Ops: gelu, gelu_backward, colsum, layernorm, layernorm_backward, layernorm_backward_residual (with the gradient of a
+bypassing branch added and the column sums of the result), softmax, softmax_backward.  The printed GB/s uses the
 algorithmic bytes (every input read once, every output written once).
 """
 import argparse
@@ -31,6 +32,7 @@ def main():
     dy = torch.randn(args.rows, args.cols, device="cuda", generator=g)
     gamma = torch.rand(args.cols, device="cuda", generator=g) + 0.5
     beta = torch.randn(args.cols, device="cuda", generator=g)
+    beta_rows = torch.randn(args.rows, args.cols, device="cuda", generator=g) if args.op == "layernorm_backward_residual" else None
     n = 4.0 * x.numel()
     calls = {
         "gelu": (lambda: be.gelu(x), 2 * n),
@@ -38,6 +40,7 @@ def main():
         "colsum": (lambda: be.colsum(dy), n),
         "layernorm": (lambda: be.layernorm(x, gamma, beta), 2 * n),
         "layernorm_backward": (lambda: be.layernorm_backward(x, gamma, dy)[0], 3 * n),
+        "layernorm_backward_residual": (lambda: be.layernorm_backward(x, gamma, dy, dx_residual=beta_rows, want_dx_colsum=True)[0], 4 * n),
         "softmax": (lambda: be.softmax(x), 2 * n),
         "softmax_backward": (lambda: be.softmax_backward(x, dy), 3 * n),
     }
