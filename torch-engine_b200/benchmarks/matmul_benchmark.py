@@ -206,6 +206,16 @@ def main():
         tb, tm = time_gpu(lambda: be.linear_backward(xg, wg, dyg, precision="tf32"), 50)
         record("b200_linear_bwd_dx_dw_db", "tf32", rows, outf, inf, 2, tb, tm, None)
         del xg, wg, bg, dyg
+    # ---- Linear on a thin batch (16 and 8 rows through an 8192 -> 8192 layer): bound by reading the weight once ----
+    wt, bt = torch.randn(8192, 8192, device="cuda", generator=gen) * 0.02, torch.zeros(8192, device="cuda")
+    for rows in (16, 8):
+        xt = torch.randn(rows, 8192, device="cuda", generator=gen)
+        _, cub = time_gpu(lambda: torch.nn.functional.linear(xt, wt, bt), 30, trials=3)
+        for mode in ("tf32", "3xtf32"):
+            tb, tm = time_gpu(lambda: be.linear_forward(xt, wt, bt, precision=mode), 30)
+            record("b200_linear_bias_fwd_thin", mode, rows, 8192, 8192, 1, tb, tm, cub)
+    del wt, bt
+    torch.cuda.empty_cache()
     # ---- HBM-bound helpers around the GEMMs: softmax rows, GELU, bias-gradient column sum, 3xTF32 packing ----
     def record_stream(name, byts, tb, tm, shape):
         r = {"kernel_name": name, "dtype": "float32", "mode": "-", "shape": shape, "time_ms": tm, "time_ms_best": tb,
@@ -237,6 +247,10 @@ def main():
     dyn = torch.randn_like(xn)
     tb, tm = time_gpu(lambda: be.layernorm_backward(xn, gam, dyn), 20)
     record_stream("b200_layernorm_backward", 3 * 4.0 * xn.numel(), tb, tm, "65536x384")
+    res_n = torch.randn_like(xn)
+    tb, tm = time_gpu(lambda: be.layernorm_backward(xn, gam, dyn, dx_residual=res_n, want_dx_colsum=True), 20)
+    record_stream("b200_layernorm_backward_residual_colsum", 4 * 4.0 * xn.numel(), tb, tm, "65536x384")
+    del res_n
     lg = torch.randn(16384, 65, device="cuda", generator=gen)
     tg = torch.randint(0, 65, (16384,), device="cuda", generator=gen)
     tb, tm = time_gpu(lambda: be.cross_entropy(lg, tg), 50)
