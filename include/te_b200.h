@@ -216,8 +216,10 @@ TE_API int te_b200_linear_backward(te_b200_ctx* ctx, const float* x, const float
  * Linear of FeedForward, src/nn/ffn.cpp:12-16): dx receives the gradient with respect to the
  * PRE-activation, dX o gelu'(x_preact): the dX product followed by GeluBackward
  * (src/core/grad_fn.cpp:169-204) in place, one call for both.  (Folding GeluBackward into the
- * product's epilogue was built and measured: the extra loads sit on the epilogue's critical path and
- * the added code slowed every other epilogue, so the two-kernel form is the faster one.)
+ * product's epilogue was built and measured: a second [rows,in] input read in the epilogue costs this
+ * short-K product more than the separate pass does -- 16384 x 384 -> 1536 goes from 42 to 63 us with a
+ * residual-like input against 49 us for the pass -- because the product is bound by what an SM takes in
+ * from L2, and the extra tile competes with the operand tiles for it.)
  * x_preact == NULL: identical to te_b200_linear_backward. */
 TE_API int te_b200_linear_backward_gelu(te_b200_ctx* ctx, const float* x, const float* x_preact,
                                  const float* w, const float* dy, float* dx, float* dw, float* db,
